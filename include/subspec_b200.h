@@ -1,0 +1,235 @@
+/*
+ * subspec_b200 — C ABI of the sm_100a speculative-decoding hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*), returns an int status (0 = ok, negative = error), never
+ * throws, never allocates device memory unless its comment says so and never
+ * synchronises the device.  Outputs go to caller-allocated device buffers.
+ *
+ * The reference project (NYCU-EDgeAi/subspec) has no FFI of its own: its seam
+ * is a set of Python call signatures.  Each entry point below cites the
+ * reference function(s) whose arithmetic it replaces; the Python package
+ * `subspec_b200` keeps those signatures and calls into this library.
+ */
+#ifndef SUBSPEC_B200_H
+#define SUBSPEC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define SUBSPEC_API __attribute__((visibility("default")))
+#else
+#define SUBSPEC_API
+#endif
+
+typedef void* subspec_stream_t; /* a cudaStream_t; NULL = legacy default stream */
+
+/* status codes */
+#define SUBSPEC_OK 0
+#define SUBSPEC_EINVAL (-1)       /* bad argument (null pointer, negative size, bad enum) */
+#define SUBSPEC_EUNSUPPORTED (-2) /* shape outside the supported range */
+#define SUBSPEC_ECUDA (-3)        /* a CUDA runtime call failed; see subspec_last_cuda_error */
+#define SUBSPEC_ESCRATCH (-4)     /* scratch buffer too small / misaligned */
+
+/* element types of logits / probabilities / KV rows */
+#define SUBSPEC_F32 0
+#define SUBSPEC_BF16 1
+#define SUBSPEC_F16 2
+
+/* what the [rows, vocab] matrix given to the verifier holds */
+#define SUBSPEC_IN_LOGITS 0 /* raw target logits: softmax is fused into the pass */
+#define SUBSPEC_IN_PROBS 1  /* already-normalised probabilities */
+
+#define SUBSPEC_VERIFY_EXACT 0 /* verify_method="exact" */
+#define SUBSPEC_VERIFY_LOSSY 1 /* verify_method="lossy" */
+
+#define SUBSPEC_GATE_PROB 0    /* threshold_method="prob"    */
+#define SUBSPEC_GATE_ENTROPY 1 /* threshold_method="entropy" */
+
+/* bits of the device status word written by the kernels (0 = clean run) */
+#define SUBSPEC_DEV_BAD_TOKEN 1u /* a draft token id was outside [0, vocab) */
+#define SUBSPEC_DEV_BAD_CHILD 2u /* a child index was outside [0, n_nodes) */
+#define SUBSPEC_DEV_BAD_ROOT 4u  /* a root index was outside [0, n_rows)   */
+#define SUBSPEC_DEV_BAD_PAGE 8u  /* a page id was outside [0, num_pages)   */
+#define SUBSPEC_DEV_BAD_INDEX 16u /* an accepted-path index was out of range */
+#define SUBSPEC_DEV_TIMEOUT 32u  /* a bounded device-side wait ran out       */
+
+SUBSPEC_API const char* subspec_version(void);
+/* cudaGetErrorString of the last CUDA error an entry point saw on this thread */
+SUBSPEC_API const char* subspec_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------
+ * Tree verify + accept, one launch per batch of independent sequences.
+ *
+ * Replaces, per sequence (reference file:line):
+ *   - GeneratorBase._sample_token(return_probs=True): softmax over every
+ *     tree node's target logits   specdecodes/models/generators/base.py:109-139
+ *   - verify_tree, exact branch: greedy / sample-and-match walk with bonus
+ *     token                       specdecodes/models/utils/tree_verify.py:49-106
+ *   - ClassicSDGeneratorBase._verify_step
+ *                                 specdecodes/models/generators/classic_sd.py:111-116
+ *   - verify_tree, lossy wrapper  specdecodes/models/utils/tree_verify.py:108-163
+ *   - lossy_bottom_up_verify: per-node target token, normalised entropy,
+ *     reverse-index DP, top-down walk
+ *                                 specdecodes/models/utils/lossy_tree_verify.py:9-291
+ *
+ * Layout.  `logits` is [batch, rows, vocab] with element strides
+ * `seq_stride` / `row_stride` (vocab contiguous).  Row u of sequence b is the
+ * target distribution produced AT tree node u (local numbering: node 0 is the
+ * first decoded node).  Per-node int32 arrays are [batch, max_nodes]; the
+ * children of node u are child_idx[b][child_off[b][u] .. child_off[b][u+1])
+ * in the reference's list order (child_off is [batch, max_nodes + 1]).
+ * `n_nodes[b]` nodes are described; `n_rows[b] <= n_nodes[b]` of them have a
+ * logits row.  For the lossy method the caller passes n_nodes == n_rows and
+ * only children inside the decoded range (tree_verify.py:137-145).
+ *
+ * Sampling.  do_sample = 0: the target token of a node is the first-index
+ * argmax of its row.  do_sample = 1: the row is divided by `temperature`,
+ * filtered by nucleus `top_p` (top_p >= 1 disables the filter), renormalised,
+ * and the target token is the inverse-CDF pick for uniforms[b][u] in
+ * vocabulary order (this stands in for torch.multinomial's global RNG).
+ *
+ * Outputs.  out_tokens / out_hidden are [batch, max_out] int64:
+ * accepted draft tokens followed by the bonus token, and for each the local
+ * index of the context node whose row produced it.  out_meta is [batch, 4]
+ * int32: {L = entries written, accept_len, total_len, 0}.
+ * The per-node arrays node_* are filled for every decoded node and are what
+ * the host needs to rebuild the reference's diagnostics
+ * (lossy_tree_verify.py:171-194, 249-337):
+ *   node_target[u]     target token of node u
+ *   node_entropy[u]    normalised entropy of row u (lossy only, else 0)
+ *   node_child_prob[c] P[parent(c), token(c)] (lossy only; root entry unused)
+ *   node_exact_after / node_best_len / node_best_next   the DP tables
+ *   node_rowmax[u], node_rowsum[u]  softmax shift (log2 domain) and
+ *                      denominator, so that P[u, t] =
+ *                      exp2(logit[u, t] * log2(e) / T - rowmax[u]) / rowsum[u]
+ *
+ * Scratch: `scratch` must hold subspec_verify_scratch_bytes() bytes, 256-byte
+ * aligned.  It needs no initialisation; calls that share one scratch buffer
+ * must not overlap on the GPU.
+ * ---------------------------------------------------------------------- */
+typedef struct subspec_verify_args {
+  uint32_t struct_size; /* sizeof(subspec_verify_args), checked */
+  int32_t batch;
+  int32_t max_nodes; /* stride of per-node arrays, 1..1024 */
+  int32_t vocab;     /* 1..(1<<20) */
+  int32_t dtype;     /* SUBSPEC_F32 / BF16 / F16 */
+  int32_t input_kind;
+  int64_t seq_stride; /* elements between sequences in `logits` */
+  int64_t row_stride; /* elements between rows */
+  const void* logits;
+  const int32_t* n_nodes;   /* [batch] */
+  const int32_t* n_rows;    /* [batch] */
+  const int32_t* token_ids; /* [batch, max_nodes] */
+  const int32_t* child_off; /* [batch, max_nodes + 1] */
+  const int32_t* child_idx; /* [batch, max_nodes] */
+  const int32_t* root;      /* [batch] local root index */
+  /* sampling */
+  int32_t do_sample;
+  float temperature;
+  float top_p;
+  const float* uniforms; /* [batch, max_nodes], required iff do_sample */
+  /* method */
+  int32_t method; /* SUBSPEC_VERIFY_* */
+  int32_t gate;   /* SUBSPEC_GATE_*   */
+  double threshold;
+  int32_t window; /* clamped at >= 0 like the reference (:55) */
+  int64_t eos;    /* -1 = no EOS token */
+  /* outputs */
+  int32_t max_out; /* >= 2, stride of out_tokens / out_hidden */
+  int64_t* out_tokens;
+  int64_t* out_hidden;
+  int32_t* out_meta; /* [batch, 4] */
+  int32_t* node_target;
+  float* node_entropy;
+  float* node_child_prob;
+  float* node_rowmax;
+  float* node_rowsum;
+  int32_t* node_exact_after;
+  int32_t* node_best_len;
+  int32_t* node_best_next;
+  uint32_t* dev_status; /* one word, OR-ed with SUBSPEC_DEV_* bits; caller zeroes it */
+  void* scratch;
+  size_t scratch_bytes;
+} subspec_verify_args;
+
+SUBSPEC_API int subspec_verify_scratch_bytes(int32_t batch, int32_t max_nodes, size_t* bytes);
+SUBSPEC_API int subspec_verify_batched(const subspec_verify_args* args, subspec_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Accepted-path KV compaction.
+ *
+ * For i in [0, n[b]):  row(offset[b] + i) <- row(offset[b] + beam[b][i]) for
+ * every layer and for K and V, all sources read before any destination is
+ * written.  Replaces
+ *   - KvCachePool.reorder_cache_with_offset (clone whole pool, index_copy_,
+ *     copy whole pool back)
+ *       specdecodes/models/utils/flashinfer/cache_manager.py:119-213
+ *   - TreeStaticCache / TreeDynamicCache.reorder_cache_with_offset
+ *       specdecodes/models/utils/cache_utils.py:85-103, 166-208
+ *
+ * Paged layout: pool is [layers, num_pages, 2, page_len, heads, head_dim]
+ * (the reference's KvCachePool.cache_data).  Logical position p of sequence b
+ * lives in physical page page_table[b][p / page_len] at slot p % page_len
+ * (page_table is [batch, pages_per_seq] int32).  page_table == NULL means the
+ * identity table the reference assumes (physical page = p / page_len).
+ * One row is heads * head_dim elements and must be a multiple of 16 bytes.
+ *
+ * beam is [batch, max_beam] int32, strictly increasing with beam[i] >= i
+ * (the verifier's out_hidden).  n may be a device array ([batch]) so that a
+ * verify launch can feed this one without a host round trip.
+ * ---------------------------------------------------------------------- */
+typedef struct subspec_kv_paged_args {
+  uint32_t struct_size;
+  int32_t batch;
+  int32_t layers;
+  int32_t num_pages; /* physical pages in the pool */
+  int32_t page_len;
+  int32_t heads;
+  int32_t head_dim;
+  int32_t elem_bytes; /* 2 for bf16/fp16, 4 for fp32 */
+  void* pool;
+  const int32_t* page_table; /* [batch, pages_per_seq] or NULL */
+  int32_t pages_per_seq;
+  const int32_t* offset; /* [batch] */
+  const int32_t* n;      /* [batch] rows kept */
+  const int64_t* beam;   /* [batch, max_beam] */
+  int32_t max_beam;      /* <= 64 */
+  uint32_t* dev_status;
+} subspec_kv_paged_args;
+
+SUBSPEC_API int subspec_kv_compact_paged(const subspec_kv_paged_args* args, subspec_stream_t stream);
+
+/* HF layout: `layer_ptrs` is a device array of 2 * layers pointers (K then V
+ * of layer 0, K then V of layer 1, ...), each a [batch, heads, tokens,
+ * head_dim] tensor with the given element strides (head_dim contiguous). */
+typedef struct subspec_kv_hf_args {
+  uint32_t struct_size;
+  int32_t batch;
+  int32_t num_tensors; /* 2 * layers */
+  int32_t heads;
+  int32_t tokens;
+  int32_t head_dim;
+  int32_t elem_bytes;
+  int64_t batch_stride; /* elements */
+  int64_t head_stride;
+  int64_t token_stride;
+  void* const* layer_ptrs;
+  const int32_t* offset; /* [batch] */
+  const int32_t* n;      /* [batch] */
+  const int64_t* beam;   /* [batch, max_beam] */
+  int32_t max_beam;
+  uint32_t* dev_status;
+} subspec_kv_hf_args;
+
+SUBSPEC_API int subspec_kv_compact_hf(const subspec_kv_hf_args* args, subspec_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SUBSPEC_B200_H */

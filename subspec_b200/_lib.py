@@ -1,0 +1,141 @@
+"""ctypes binding of `libsubspec_b200.so` (declared in include/subspec_b200.h).
+
+There is no CPU fallback: if the CUDA library has not been built, importing a
+compute entry point raises.  Build it with `python -m subspec_b200.build`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libsubspec_b200.so"
+
+OK, EINVAL, EUNSUPPORTED, ECUDA, ESCRATCH = 0, -1, -2, -3, -4
+F32, BF16, F16 = 0, 1, 2
+IN_LOGITS, IN_PROBS = 0, 1
+VERIFY_EXACT, VERIFY_LOSSY = 0, 1
+GATE_PROB, GATE_ENTROPY = 0, 1
+DEV_BAD_TOKEN, DEV_BAD_CHILD, DEV_BAD_ROOT, DEV_BAD_PAGE, DEV_BAD_INDEX, DEV_TIMEOUT = 1, 2, 4, 8, 16, 32
+
+_STATUS_TEXT = {
+    EINVAL: "invalid argument",
+    EUNSUPPORTED: "unsupported shape",
+    ECUDA: "CUDA error",
+    ESCRATCH: "scratch buffer too small or misaligned",
+}
+
+_DEV_TEXT = {
+    DEV_BAD_TOKEN: "draft token id outside [0, vocab)",
+    DEV_BAD_CHILD: "child index outside the tree",
+    DEV_BAD_ROOT: "root index outside the decoded rows",
+    DEV_BAD_PAGE: "page id outside the pool",
+    DEV_BAD_INDEX: "accepted-path index out of range",
+    DEV_TIMEOUT: "a bounded device-side wait ran out",
+}
+
+_vp, _i32, _i64, _u32, _f32, _f64 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint32, C.c_float, C.c_double
+
+
+class VerifyArgs(C.Structure):
+    """Mirror of `subspec_verify_args`."""
+
+    _fields_ = [
+        ("struct_size", _u32), ("batch", _i32), ("max_nodes", _i32), ("vocab", _i32), ("dtype", _i32),
+        ("input_kind", _i32), ("seq_stride", _i64), ("row_stride", _i64), ("logits", _vp),
+        ("n_nodes", _vp), ("n_rows", _vp), ("token_ids", _vp), ("child_off", _vp), ("child_idx", _vp),
+        ("root", _vp),
+        ("do_sample", _i32), ("temperature", _f32), ("top_p", _f32), ("uniforms", _vp),
+        ("method", _i32), ("gate", _i32), ("threshold", _f64), ("window", _i32), ("eos", _i64),
+        ("max_out", _i32), ("out_tokens", _vp), ("out_hidden", _vp), ("out_meta", _vp),
+        ("node_target", _vp), ("node_entropy", _vp), ("node_child_prob", _vp), ("node_rowmax", _vp),
+        ("node_rowsum", _vp), ("node_exact_after", _vp), ("node_best_len", _vp), ("node_best_next", _vp),
+        ("dev_status", _vp), ("scratch", _vp), ("scratch_bytes", C.c_size_t),
+    ]
+
+
+class KvPagedArgs(C.Structure):
+    """Mirror of `subspec_kv_paged_args`."""
+
+    _fields_ = [
+        ("struct_size", _u32), ("batch", _i32), ("layers", _i32), ("num_pages", _i32), ("page_len", _i32),
+        ("heads", _i32), ("head_dim", _i32), ("elem_bytes", _i32), ("pool", _vp), ("page_table", _vp),
+        ("pages_per_seq", _i32), ("offset", _vp), ("n", _vp), ("beam", _vp), ("max_beam", _i32),
+        ("dev_status", _vp),
+    ]
+
+
+class KvHfArgs(C.Structure):
+    """Mirror of `subspec_kv_hf_args`."""
+
+    _fields_ = [
+        ("struct_size", _u32), ("batch", _i32), ("num_tensors", _i32), ("heads", _i32), ("tokens", _i32),
+        ("head_dim", _i32), ("elem_bytes", _i32), ("batch_stride", _i64), ("head_stride", _i64),
+        ("token_stride", _i64), ("layer_ptrs", _vp), ("offset", _vp), ("n", _vp), ("beam", _vp),
+        ("max_beam", _i32), ("dev_status", _vp),
+    ]
+
+
+# every symbol include/subspec_b200.h declares: name -> (restype, argtypes)
+SYMBOLS = {
+    "subspec_version": (C.c_char_p, []),
+    "subspec_last_cuda_error": (C.c_char_p, []),
+    "subspec_verify_scratch_bytes": (C.c_int, [_i32, _i32, C.POINTER(C.c_size_t)]),
+    "subspec_verify_batched": (C.c_int, [C.POINTER(VerifyArgs), _vp]),
+    "subspec_kv_compact_paged": (C.c_int, [C.POINTER(KvPagedArgs), _vp]),
+    "subspec_kv_compact_hf": (C.c_int, [C.POINTER(KvHfArgs), _vp]),
+}
+
+_lib = None
+
+
+class SubspecError(RuntimeError):
+    pass
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def lib() -> C.CDLL:
+    """Load the CUDA library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise SubspecError(
+                f"{_LIB_PATH} is missing: build the sm_100a kernels with `python -m subspec_b200.build`. "
+                "subspec_b200 has no CPU or PyTorch fallback."
+            )
+        handle = C.CDLL(str(_LIB_PATH))
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc == OK:
+        return
+    msg = _STATUS_TEXT.get(rc, f"status {rc}")
+    if rc == ECUDA:
+        msg += ": " + lib().subspec_last_cuda_error().decode()
+    if rc in (EINVAL, EUNSUPPORTED, ESCRATCH):
+        raise ValueError(f"{what}: {msg}")
+    raise SubspecError(f"{what}: {msg}")
+
+
+def dev_status_text(word: int) -> str:
+    return "; ".join(t for bit, t in _DEV_TEXT.items() if word & bit)
+
+
+def torch_dtype_code(dtype) -> int:
+    import torch
+
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    if dtype == torch.float16:
+        return F16
+    raise ValueError(f"unsupported dtype {dtype}: expected float32, bfloat16 or float16")

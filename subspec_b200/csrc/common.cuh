@@ -1,0 +1,58 @@
+// Shared device/host helpers for the subspec_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/subspec_b200.h"
+
+namespace subspec {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
+
+// Host side: remember the last CUDA error for subspec_last_cuda_error().
+int cuda_fail(cudaError_t e);
+inline int cuda_check(cudaError_t e) { return e == cudaSuccess ? SUBSPEC_OK : cuda_fail(e); }
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2f(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 128-bit streaming load: the rows are read exactly once, keep them out of L1.
+__device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+__device__ __forceinline__ void flag(uint32_t* status, uint32_t bit) {
+  if (status) atomicOr(status, bit);
+}
+
+#endif  // __CUDACC__
+
+}  // namespace subspec

@@ -1,0 +1,754 @@
+// Fused tree verify + accept for sm_100a.
+//
+// One launch per batch.  Each CTA streams one chunk of one [vocab] row with
+// 128-bit loads and reduces, in a single pass over HBM:
+//   - the first-index argmax (the greedy target token),
+//   - the softmax denominator in the log2 domain,
+//   - sum((x*k - c) * 2^(x*k - c))  from which the normalised entropy follows.
+// The CTA that completes a row (an atomic ticket, no spinning) finalises the
+// row statistics and gathers P[u, token(child)] for the node's children.  The
+// CTA that completes the last row of a sequence then runs the accept walk for
+// that sequence (exact walk, or the lossy reverse-index DP + top-down walk)
+// out of shared memory while other CTAs keep streaming other sequences.
+//
+// Semantics follow the reference's verify_tree (tree_verify.py:49-163),
+// _verify_step (classic_sd.py:111-116) and lossy_bottom_up_verify
+// (lossy_tree_verify.py:9-291).
+#include <limits.h>
+#include <math.h>
+
+#include "common.cuh"
+
+namespace subspec {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kUnroll = 4;
+constexpr int kMaxSplits = 32;
+constexpr int kMaxNodes = 1024;
+
+// Row statistics relative to a shift `c` in the log2 domain:
+//   s  = sum 2^(y),  t2 = sum y * 2^(y)   with y = x * k - c.
+// In SUBSPEC_IN_PROBS mode c stays 0, s = sum p, t2 = sum p * log2(p).
+struct RowStat {
+  float c, s, t2, vmax;
+  int amax;
+};
+
+__device__ __forceinline__ RowStat empty_stat(bool probs) {
+  RowStat r;
+  r.c = probs ? 0.f : -INFINITY;
+  r.s = 0.f;
+  r.t2 = 0.f;
+  r.vmax = -INFINITY;
+  r.amax = INT_MAX;
+  return r;
+}
+
+__device__ __forceinline__ RowStat combine(const RowStat& a, const RowStat& b) {
+  RowStat r;
+  r.c = fmaxf(a.c, b.c);
+  float fa = 0.f, fb = 0.f, ta = 0.f, tb = 0.f;
+  if (a.c != -INFINITY) {
+    const float d = a.c - r.c;
+    fa = ex2f(d);
+    ta = fa * fmaf(d, a.s, a.t2);
+  }
+  if (b.c != -INFINITY) {
+    const float d = b.c - r.c;
+    fb = ex2f(d);
+    tb = fb * fmaf(d, b.s, b.t2);
+  }
+  r.s = a.s * fa + b.s * fb;
+  r.t2 = ta + tb;
+  const bool pick_a = (a.vmax > b.vmax) || (a.vmax == b.vmax && a.amax < b.amax);
+  r.vmax = pick_a ? a.vmax : b.vmax;
+  r.amax = pick_a ? a.amax : b.amax;
+  return r;
+}
+
+__device__ __forceinline__ RowStat shfl_down_stat(const RowStat& v, int off) {
+  RowStat r;
+  r.c = __shfl_down_sync(0xffffffffu, v.c, off);
+  r.s = __shfl_down_sync(0xffffffffu, v.s, off);
+  r.t2 = __shfl_down_sync(0xffffffffu, v.t2, off);
+  r.vmax = __shfl_down_sync(0xffffffffu, v.vmax, off);
+  r.amax = __shfl_down_sync(0xffffffffu, v.amax, off);
+  return r;
+}
+
+__device__ __forceinline__ RowStat warp_reduce(RowStat v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v = combine(v, shfl_down_stat(v, off));
+  return v;
+}
+
+// Per-thread accumulator.  SOFT = false keeps only the argmax.
+template <int KIND, bool SOFT>
+struct Acc {
+  float c, s0, s1, t0, t1, vmax, k;
+  int amax;
+
+  __device__ __forceinline__ void init(float k_) {
+    k = k_;
+    c = (KIND == SUBSPEC_IN_PROBS) ? 0.f : -INFINITY;
+    s0 = s1 = t0 = t1 = 0.f;
+    vmax = -INFINITY;
+    amax = INT_MAX;
+  }
+
+  // A new running maximum `m` first seen at element `idx`.
+  __device__ __forceinline__ void raise(float m, int idx) {
+    vmax = m;
+    amax = idx;
+    if (SOFT && KIND == SUBSPEC_IN_LOGITS) {
+      const float cn = m * k;
+      if (c != -INFINITY) {
+        const float d = c - cn;
+        const float f = ex2f(d);
+        t0 = f * fmaf(d, s0, t0);
+        t1 = f * fmaf(d, s1, t1);
+        s0 *= f;
+        s1 *= f;
+      }
+      c = cn;
+    }
+  }
+
+  // One element whose value is known to be <= vmax (finite, clamped).
+  template <int LANE>
+  __device__ __forceinline__ void add(float x) {
+    if (!SOFT) return;
+    if (KIND == SUBSPEC_IN_LOGITS) {
+      const float y = fmaf(x, k, -c);
+      const float e = ex2f(y);
+      if (LANE & 1) {
+        s1 += e;
+        t1 = fmaf(y, e, t1);
+      } else {
+        s0 += e;
+        t0 = fmaf(y, e, t0);
+      }
+    } else {
+      const float l = x > 0.f ? lg2f(x) : 0.f;
+      if (LANE & 1) {
+        s1 += x;
+        t1 = fmaf(x, l, t1);
+      } else {
+        s0 += x;
+        t0 = fmaf(x, l, t0);
+      }
+    }
+  }
+
+  // Generic scalar path (unaligned rows, tails).
+  __device__ __forceinline__ void one(float x, int idx) {
+    if (KIND == SUBSPEC_IN_LOGITS) x = fmaxf(x, -1.0e30f);
+    if (x > vmax) raise(x, idx);
+    add<0>(x);
+  }
+
+  __device__ __forceinline__ RowStat stat() const {
+    RowStat r;
+    r.c = (vmax == -INFINITY && KIND == SUBSPEC_IN_LOGITS) ? -INFINITY : c;
+    r.s = s0 + s1;
+    r.t2 = t0 + t1;
+    r.vmax = vmax;
+    r.amax = amax;
+    return r;
+  }
+};
+
+// ---- 16-byte vector consumers -------------------------------------------------
+template <typename T>
+struct Vec;
+
+template <>
+struct Vec<float> {
+  static constexpr int N = 4;
+  template <int KIND, bool SOFT>
+  static __device__ __forceinline__ void consume(Acc<KIND, SOFT>& a, const uint4& q, int base) {
+    float x[4] = {__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w)};
+    if (KIND == SUBSPEC_IN_LOGITS) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) x[i] = fmaxf(x[i], -1.0e30f);
+    }
+    const float vm = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+    if (vm > a.vmax) {
+      int j = 0;
+#pragma unroll
+      for (int i = 3; i >= 0; --i)
+        if (x[i] == vm) j = i;
+      a.raise(vm, base + j);
+    }
+    a.template add<0>(x[0]);
+    a.template add<1>(x[1]);
+    a.template add<0>(x[2]);
+    a.template add<1>(x[3]);
+  }
+};
+
+template <>
+struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  template <int KIND, bool SOFT>
+  static __device__ __forceinline__ void consume(Acc<KIND, SOFT>& a, const uint4& q, int base) {
+    uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    __nv_bfloat162 h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      h[i] = *reinterpret_cast<__nv_bfloat162*>(&w[i]);
+      if (KIND == SUBSPEC_IN_LOGITS) {
+        // -1.0e30 is finite in bf16 and stays finite after scaling; this turns -inf (masked logits) into a
+        // value whose exponential flushes to zero without producing NaN.
+        h[i] = __hmax2(h[i], __floats2bfloat162_rn(-1.0e30f, -1.0e30f));
+        w[i] = *reinterpret_cast<uint32_t*>(&h[i]);
+      }
+    }
+    const __nv_bfloat162 m2 = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+    const float vm = fmaxf(__low2float(m2), __high2float(m2));
+    float x[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      x[2 * i] = __uint_as_float(w[i] << 16);
+      x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+    if (vm > a.vmax) {
+      int j = 0;
+#pragma unroll
+      for (int i = 7; i >= 0; --i)
+        if (x[i] == vm) j = i;
+      a.raise(vm, base + j);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (i & 1)
+        a.template add<1>(x[i]);
+      else
+        a.template add<0>(x[i]);
+    }
+  }
+};
+
+template <>
+struct Vec<__half> {
+  static constexpr int N = 8;
+  template <int KIND, bool SOFT>
+  static __device__ __forceinline__ void consume(Acc<KIND, SOFT>& a, const uint4& q, int base) {
+    uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    __half2 h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      h[i] = *reinterpret_cast<__half2*>(&w[i]);
+      if (KIND == SUBSPEC_IN_LOGITS) h[i] = __hmax2(h[i], __floats2half2_rn(-65504.f, -65504.f));
+    }
+    const __half2 m2 = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+    const float vm = fmaxf(__low2float(m2), __high2float(m2));
+    float x[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      x[2 * i] = f.x;
+      x[2 * i + 1] = f.y;
+    }
+    if (vm > a.vmax) {
+      int j = 0;
+#pragma unroll
+      for (int i = 7; i >= 0; --i)
+        if (x[i] == vm) j = i;
+      a.raise(vm, base + j);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (i & 1)
+        a.template add<1>(x[i]);
+      else
+        a.template add<0>(x[i]);
+    }
+  }
+};
+
+struct Scratch {
+  int* seq_ticket;   // [batch]
+  int* row_ticket;   // [batch * max_nodes]
+  RowStat* partial;  // [batch * max_nodes * kMaxSplits]
+};
+
+__host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+__host__ __device__ inline size_t ticket_bytes(int batch, int max_nodes) {
+  return align_up(sizeof(int) * ((size_t)batch + (size_t)batch * max_nodes), 256);
+}
+
+__host__ __device__ inline Scratch carve(void* base, int batch, int max_nodes) {
+  Scratch s;
+  s.seq_ticket = reinterpret_cast<int*>(base);
+  s.row_ticket = s.seq_ticket + batch;
+  s.partial = reinterpret_cast<RowStat*>(reinterpret_cast<char*>(base) + ticket_bytes(batch, max_nodes));
+  return s;
+}
+
+struct KArgs {
+  subspec_verify_args a;
+  Scratch sc;
+  int splits;
+  int vec_ok;  // every row start is 16-byte aligned
+  float k;     // log2(e) / temperature
+};
+
+// ---- the accept walk, run by one CTA per sequence out of shared memory -----------
+struct WalkSmem {
+  int* tok;
+  int* tgt;
+  float* ent;
+  float* cprob;
+  int* coff;
+  int* cidx;
+  int* ea;
+  int* bl;
+  int* bn;
+};
+
+__device__ __forceinline__ WalkSmem carve_walk(unsigned char* base, int n) {
+  WalkSmem w;
+  int* p = reinterpret_cast<int*>(base);
+  w.tok = p;
+  p += n;
+  w.tgt = p;
+  p += n;
+  w.ent = reinterpret_cast<float*>(p);
+  p += n;
+  w.cprob = reinterpret_cast<float*>(p);
+  p += n;
+  w.coff = p;
+  p += n + 1;
+  w.cidx = p;
+  p += n;
+  w.ea = p;
+  p += n;
+  w.bl = p;
+  p += n;
+  w.bn = p;
+  return w;
+}
+
+__device__ void run_walk(const KArgs& ka, int b, unsigned char* smem_raw) {
+  const subspec_verify_args& a = ka.a;
+  const int N = a.max_nodes;
+  const int n_nodes = a.n_nodes[b];
+  const int n_rows = a.n_rows[b];
+  WalkSmem w = carve_walk(smem_raw, N);
+  const size_t nb = (size_t)b * N;
+  const bool lossy = a.method == SUBSPEC_VERIFY_LOSSY;
+
+  for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) {
+    w.tok[i] = a.token_ids[nb + i];
+    int ci = a.child_idx[nb + i];
+    if (ci < 0 || ci >= n_nodes) ci = 0;  // only entries below child_off[n_nodes] are ever read; those were checked
+    w.cidx[i] = ci;
+    w.ea[i] = 0;
+    w.bl[i] = 0;
+    w.bn[i] = -1;
+    if (i < n_rows) {
+      w.tgt[i] = __ldcg(a.node_target + nb + i);
+      w.ent[i] = lossy ? __ldcg(a.node_entropy + nb + i) : 0.f;
+    } else {
+      w.tgt[i] = -1;
+      w.ent[i] = 0.f;
+    }
+    w.cprob[i] = lossy ? __ldcg(a.node_child_prob + nb + i) : 0.f;
+  }
+  for (int i = threadIdx.x; i <= n_nodes; i += blockDim.x) {
+    int o = a.child_off[(size_t)b * (N + 1) + i];
+    if (o < 0 || o > n_nodes) {
+      flag(a.dev_status, SUBSPEC_DEV_BAD_CHILD);
+      o = o < 0 ? 0 : n_nodes;
+    }
+    w.coff[i] = o;
+  }
+  __syncthreads();
+
+  if (threadIdx.x == 0) {
+    int64_t* out_tok = a.out_tokens + (size_t)b * a.max_out;
+    int64_t* out_hid = a.out_hidden + (size_t)b * a.max_out;
+    const int max_out = a.max_out;
+    const int64_t eos = a.eos;
+    int root = a.root[b];
+    if (root < 0 || root >= n_rows) {
+      flag(a.dev_status, SUBSPEC_DEV_BAD_ROOT);
+      root = 0;
+    }
+    int L = 0, acc = 0, total = 0;
+    if (!lossy) {
+      // tree_verify.py:61-104
+      int cur = root;
+      int bonus = -1;
+      bool go = (w.coff[cur + 1] - w.coff[cur]) > 0;
+      while (go) {
+        ++total;
+        const int s = w.tgt[cur];
+        int match = -1;
+        for (int e = w.coff[cur]; e < w.coff[cur + 1]; ++e) {
+          const int c = w.cidx[e];
+          if (w.tok[c] == s) {
+            match = c;
+            break;
+          }
+        }
+        if (match < 0) {
+          bonus = s;
+          break;
+        }
+        ++acc;
+        if (L < max_out) {
+          out_tok[L] = s;
+          out_hid[L] = cur;
+        }
+        ++L;
+        if (eos >= 0 && (int64_t)s == eos) break;
+        cur = match;
+        const int cb = w.coff[cur], ce = w.coff[cur + 1];
+        if (ce - cb == 0) break;
+        int mn = INT_MAX;
+        for (int e = cb; e < ce; ++e) mn = min(mn, w.cidx[e]);
+        if (mn >= n_rows) break;
+      }
+      const bool ended_on_eos = (L > 0) && (eos >= 0) && (L - 1 < max_out) && (out_tok[L - 1] == eos);
+      if (!ended_on_eos) {
+        if (bonus < 0) bonus = w.tgt[cur];
+        if (L < max_out) {
+          out_tok[L] = bonus;
+          out_hid[L] = cur;
+        }
+        ++L;
+      }
+    } else {
+      // lossy_tree_verify.py:107-168 (DP) and :247-291 (walk)
+      const bool use_entropy = a.gate == SUBSPEC_GATE_ENTROPY;
+      const double thr = a.threshold;
+      const int window = a.window > 0 ? a.window : 0;
+      for (int u = n_nodes - 1; u >= 0; --u) {
+        const int cb = w.coff[u], ce = w.coff[u + 1];
+        if (ce == cb) continue;
+        const int tgt = w.tgt[u];
+        bool has_exact = false;
+        int max_ea = 0;
+        for (int e = cb; e < ce; ++e) {
+          const int c = w.cidx[e];
+          if (w.tok[c] == tgt) {
+            has_exact = true;
+            max_ea = max(max_ea, w.ea[c]);
+          }
+        }
+        if (has_exact) w.ea[u] = 1 + max_ea;
+        int best_c = -1, best_total = 0;
+        bool best_exact = false;
+        float best_p = -1.f;
+        const bool ent_blocks = use_entropy && ((double)w.ent[u] >= thr);
+        for (int e = cb; e < ce; ++e) {
+          const int c = w.cidx[e];
+          const bool is_exact = w.tok[c] == tgt;
+          float p = -1.f;
+          if (!is_exact) {
+            if (w.ea[c] < window) continue;
+            if (ent_blocks) continue;
+            p = w.cprob[c];
+            if (!use_entropy && (double)p < thr) continue;
+          }
+          const int tl = 1 + w.bl[c];
+          if (tl > best_total) {
+            best_c = c;
+            best_total = tl;
+            best_exact = is_exact;
+            best_p = p;
+            continue;
+          }
+          if (tl == best_total) {
+            if (is_exact && !best_exact) {
+              best_c = c;
+              best_exact = true;
+              best_p = p;
+            } else if (!is_exact && !best_exact && p > best_p) {
+              best_c = c;
+              best_p = p;
+            }
+          }
+        }
+        if (best_c >= 0 && best_total > 0) {
+          w.bn[u] = best_c;
+          w.bl[u] = best_total;
+        }
+      }
+      int ctx = root;
+      while (true) {
+        const int nxt = w.bn[ctx];
+        if (nxt < 0) break;
+        const int t = w.tok[nxt];
+        if (L < max_out) {
+          out_tok[L] = t;
+          out_hid[L] = ctx;
+        }
+        ++L;
+        ++acc;
+        if (eos >= 0 && (int64_t)t == eos) break;
+        ctx = nxt;
+      }
+      const bool ended_on_eos = (L > 0) && (eos >= 0) && (L - 1 < max_out) && (out_tok[L - 1] == eos);
+      if (!ended_on_eos) {
+        if (L < max_out) {
+          out_tok[L] = w.tgt[ctx];
+          out_hid[L] = ctx;
+        }
+        ++L;
+      }
+      total = L;
+    }
+    int* meta = a.out_meta + (size_t)b * 4;
+    meta[0] = L < max_out ? L : max_out;
+    meta[1] = acc;
+    meta[2] = total;
+    meta[3] = L > max_out ? 1 : 0;
+  }
+  __syncthreads();
+  if (lossy) {
+    for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) {
+      a.node_exact_after[nb + i] = w.ea[i];
+      a.node_best_len[nb + i] = w.bl[i];
+      a.node_best_next[nb + i] = w.bn[i];
+    }
+  }
+}
+
+// ---- the streaming kernel --------------------------------------------------------
+template <typename T, int KIND, bool SOFT>
+__global__ void __launch_bounds__(kThreads, 4) verify_rows_kernel(const KArgs ka) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ RowStat s_warp[kWarps];
+  __shared__ RowStat s_row;
+  __shared__ int s_flag;
+
+  const subspec_verify_args& a = ka.a;
+  const int splits = ka.splits;
+  const int row = blockIdx.x / splits;
+  const int split = blockIdx.x - row * splits;
+  const int b = row / a.max_nodes;
+  const int u = row - b * a.max_nodes;
+  const int n_rows = a.n_rows[b];
+  if (u >= n_rows) return;
+
+  const int V = a.vocab;
+  const T* rowp = reinterpret_cast<const T*>(a.logits) + (size_t)b * a.seq_stride + (size_t)u * a.row_stride;
+
+  Acc<KIND, SOFT> acc;
+  acc.init(ka.k);
+
+  constexpr int VN = Vec<T>::N;
+  // chunk of this split, in elements; boundaries are multiples of VN
+  const int nvec_total = ka.vec_ok ? V / VN : 0;
+  const int vec_per_split = (nvec_total + splits - 1) / splits;
+  const int v0 = min(split * vec_per_split, nvec_total);
+  const int v1 = min(v0 + vec_per_split, nvec_total);
+  {
+    const uint4* vp = reinterpret_cast<const uint4*>(rowp);
+    int i = v0 + threadIdx.x;
+    for (; i + (kUnroll - 1) * kThreads < v1; i += kUnroll * kThreads) {
+      uint4 q[kUnroll];
+#pragma unroll
+      for (int j = 0; j < kUnroll; ++j) q[j] = ld_stream_u4(vp + i + j * kThreads);
+#pragma unroll
+      for (int j = 0; j < kUnroll; ++j) Vec<T>::template consume<KIND, SOFT>(acc, q[j], (i + j * kThreads) * VN);
+    }
+    for (; i < v1; i += kThreads) {
+      const uint4 q = ld_stream_u4(vp + i);
+      Vec<T>::template consume<KIND, SOFT>(acc, q, i * VN);
+    }
+  }
+  // scalar remainder (and the whole row when it is not 16-byte aligned): last split only
+  if (split == splits - 1) {
+    for (int i = nvec_total * VN + threadIdx.x; i < V; i += kThreads) acc.one(to_f32<T>(rowp[i]), i);
+  }
+
+  // CTA reduction
+  RowStat st = warp_reduce(acc.stat());
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) s_warp[warp] = st;
+  __syncthreads();
+  if (warp == 0) {
+    st = lane < kWarps ? s_warp[lane] : empty_stat(KIND == SUBSPEC_IN_PROBS);
+    st = warp_reduce(st);
+    if (lane == 0) s_row = st;
+  }
+  __syncthreads();
+
+  if (splits > 1) {
+    if (threadIdx.x == 0) {
+      ka.sc.partial[(size_t)row * kMaxSplits + split] = s_row;
+      __threadfence();
+      const int t = atomicAdd(ka.sc.row_ticket + row, 1);
+      s_flag = (t == splits - 1);
+    }
+    __syncthreads();
+    if (!s_flag) return;
+    __threadfence();
+    if (warp == 0) {
+      RowStat p = empty_stat(KIND == SUBSPEC_IN_PROBS);
+      if (lane < splits) {
+        const volatile RowStat* src = ka.sc.partial + (size_t)row * kMaxSplits + lane;
+        p.c = src->c;
+        p.s = src->s;
+        p.t2 = src->t2;
+        p.vmax = src->vmax;
+        p.amax = src->amax;
+      }
+      p = warp_reduce(p);
+      if (lane == 0) s_row = p;
+    }
+    __syncthreads();
+  }
+
+  // ---- finalise the row ----
+  const RowStat r = s_row;
+  const size_t nb = (size_t)b * a.max_nodes;
+  if (threadIdx.x == 0) {
+    a.node_target[nb + u] = r.amax == INT_MAX ? 0 : r.amax;
+    float ent = 0.f;
+    if (SOFT) {
+      const float denom = V > 1 ? logf((float)V) : 1.f;
+      if (KIND == SUBSPEC_IN_LOGITS)
+        ent = kLn2 * (lg2f(r.s) - r.t2 / r.s) / denom;
+      else
+        ent = -kLn2 * r.t2 / denom;
+    }
+    a.node_entropy[nb + u] = ent;
+    a.node_rowmax[nb + u] = r.c;
+    a.node_rowsum[nb + u] = (KIND == SUBSPEC_IN_PROBS) ? 1.f : r.s;
+  }
+  if (SOFT) {
+    // P[u, token(c)] for every child c of u
+    const int* coff = a.child_off + (size_t)b * (a.max_nodes + 1);
+    const int cb = coff[u], ce = coff[u + 1];
+    const int n_nodes = a.n_nodes[b];
+    for (int e = cb + threadIdx.x; e < ce; e += kThreads) {
+      const int c = a.child_idx[nb + e];
+      if (c < 0 || c >= n_nodes) {
+        flag(a.dev_status, SUBSPEC_DEV_BAD_CHILD);
+        continue;
+      }
+      const int tok = a.token_ids[nb + c];
+      float p = 0.f;
+      if (tok < 0 || tok >= V) {
+        flag(a.dev_status, SUBSPEC_DEV_BAD_TOKEN);
+      } else {
+        const float x = to_f32<T>(rowp[tok]);
+        p = (KIND == SUBSPEC_IN_PROBS) ? x : ex2f(fmaf(x, ka.k, -r.c)) / r.s;
+      }
+      a.node_child_prob[nb + c] = p;
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(ka.sc.seq_ticket + b, 1);
+    s_flag = (t == n_rows - 1);
+  }
+  __syncthreads();
+  if (!s_flag) return;
+  __threadfence();
+  run_walk(ka, b, smem_raw);
+}
+
+template <typename T>
+cudaError_t launch_rows(const KArgs& ka, int grid, size_t smem, cudaStream_t st) {
+  const bool soft = ka.a.method == SUBSPEC_VERIFY_LOSSY;
+  const bool probs = ka.a.input_kind == SUBSPEC_IN_PROBS;
+#define SUBSPEC_LAUNCH(KIND, SOFT) verify_rows_kernel<T, KIND, SOFT><<<grid, kThreads, smem, st>>>(ka)
+  if (probs) {
+    if (soft)
+      SUBSPEC_LAUNCH(SUBSPEC_IN_PROBS, true);
+    else
+      SUBSPEC_LAUNCH(SUBSPEC_IN_PROBS, false);
+  } else {
+    if (soft)
+      SUBSPEC_LAUNCH(SUBSPEC_IN_LOGITS, true);
+    else
+      SUBSPEC_LAUNCH(SUBSPEC_IN_LOGITS, false);
+  }
+#undef SUBSPEC_LAUNCH
+  return cudaGetLastError();
+}
+
+size_t walk_smem_bytes(int max_nodes) { return sizeof(int) * (9 * (size_t)max_nodes + 1); }
+
+}  // namespace
+}  // namespace subspec
+
+using namespace subspec;
+
+extern "C" int subspec_verify_scratch_bytes(int32_t batch, int32_t max_nodes, size_t* bytes) {
+  if (!bytes || batch < 0 || max_nodes < 1 || max_nodes > kMaxNodes) return SUBSPEC_EINVAL;
+  *bytes = ticket_bytes(batch, max_nodes) + sizeof(RowStat) * (size_t)batch * max_nodes * kMaxSplits;
+  return SUBSPEC_OK;
+}
+
+extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_stream_t stream) {
+  if (!args || args->struct_size != sizeof(subspec_verify_args)) return SUBSPEC_EINVAL;
+  const subspec_verify_args& a = *args;
+  if (a.batch < 0 || a.max_nodes < 1 || a.vocab < 1 || a.max_out < 2) return SUBSPEC_EINVAL;
+  if (a.max_nodes > kMaxNodes || a.vocab > (1 << 20)) return SUBSPEC_EUNSUPPORTED;
+  if (a.dtype != SUBSPEC_F32 && a.dtype != SUBSPEC_BF16 && a.dtype != SUBSPEC_F16) return SUBSPEC_EINVAL;
+  if (a.input_kind != SUBSPEC_IN_LOGITS && a.input_kind != SUBSPEC_IN_PROBS) return SUBSPEC_EINVAL;
+  if (a.method != SUBSPEC_VERIFY_EXACT && a.method != SUBSPEC_VERIFY_LOSSY) return SUBSPEC_EINVAL;
+  if (a.gate != SUBSPEC_GATE_PROB && a.gate != SUBSPEC_GATE_ENTROPY) return SUBSPEC_EINVAL;
+  if (a.batch == 0) return SUBSPEC_OK;
+  if (!a.logits || !a.n_nodes || !a.n_rows || !a.token_ids || !a.child_off || !a.child_idx || !a.root ||
+      !a.out_tokens || !a.out_hidden || !a.out_meta || !a.node_target || !a.node_entropy || !a.node_child_prob ||
+      !a.node_rowmax || !a.node_rowsum || !a.node_exact_after || !a.node_best_len || !a.node_best_next ||
+      !a.scratch)
+    return SUBSPEC_EINVAL;
+  if (a.do_sample) return SUBSPEC_EUNSUPPORTED;
+  size_t need = 0;
+  subspec_verify_scratch_bytes(a.batch, a.max_nodes, &need);
+  if (a.scratch_bytes < need || (reinterpret_cast<uintptr_t>(a.scratch) & 255u)) return SUBSPEC_ESCRATCH;
+  if ((int64_t)a.batch * a.max_nodes > (int64_t)INT_MAX / kMaxSplits) return SUBSPEC_EUNSUPPORTED;
+
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  KArgs ka;
+  ka.a = a;
+  ka.sc = carve(a.scratch, a.batch, a.max_nodes);
+  ka.k = kLog2e;
+  const size_t esz = a.dtype == SUBSPEC_F32 ? 4 : 2;
+  ka.vec_ok = ((reinterpret_cast<uintptr_t>(a.logits) & 15u) == 0) && ((a.seq_stride * esz) % 16 == 0) &&
+              ((a.row_stride * esz) % 16 == 0);
+  // Fill the machine: with few rows, split every row over several CTAs.
+  const int64_t rows = (int64_t)a.batch * a.max_nodes;
+  const int64_t target = 4LL * kNumSMs;
+  int splits = 1;
+  if (rows < target) {
+    splits = (int)((target + rows - 1) / rows);
+    const int64_t vecs = a.vocab / (esz == 4 ? 4 : 8);
+    const int64_t max_by_len = vecs / (2 * kThreads) > 1 ? vecs / (2 * kThreads) : 1;
+    if (splits > max_by_len) splits = (int)max_by_len;
+    if (splits > kMaxSplits) splits = kMaxSplits;
+    if (splits < 1) splits = 1;
+  }
+  ka.splits = splits;
+
+  int rc = cuda_check(cudaMemsetAsync(a.scratch, 0, ticket_bytes(a.batch, a.max_nodes), st));
+  if (rc) return rc;
+  const int grid = (int)(rows * splits);
+  const size_t smem = walk_smem_bytes(a.max_nodes);
+  cudaError_t e;
+  switch (a.dtype) {
+    case SUBSPEC_F32:
+      e = launch_rows<float>(ka, grid, smem, st);
+      break;
+    case SUBSPEC_BF16:
+      e = launch_rows<__nv_bfloat16>(ka, grid, smem, st);
+      break;
+    default:
+      e = launch_rows<__half>(ka, grid, smem, st);
+      break;
+  }
+  return cuda_check(e);
+}

@@ -1,0 +1,111 @@
+"""Seeded synthetic inputs with the shapes and value distributions of the benchmark configs.
+
+The reference measures on MT-Bench prompts with real checkpoints; neither is
+available offline, so these generators stand in: random draft trees, Gaussian
+target logits with the drafted child boosted at a fraction of the nodes, random
+page tables.  Everything is driven by an explicit `torch.Generator`, so the same
+seed gives the same tensors on any machine with the same torch build.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+
+
+@dataclass
+class SynthTree:
+    token_ids: torch.Tensor  # [n] int64, node 0 is the root
+    parents: torch.Tensor    # [n] int64, -1 for the root, parent < child
+    depths: torch.Tensor     # [n] int64
+
+    @property
+    def n(self) -> int:
+        return int(self.token_ids.numel())
+
+    def children(self) -> List[List[int]]:
+        ch: List[List[int]] = [[] for _ in range(self.n)]
+        for i, p in enumerate(self.parents.tolist()):
+            if p >= 0:
+                ch[p].append(i)
+        return ch
+
+
+def random_tree(n_nodes: int, max_depth: int, max_branch: int, vocab: int, gen: torch.Generator) -> SynthTree:
+    """Grow a tree one node at a time under a uniformly chosen eligible parent
+    (fewer than `max_branch` children, depth below `max_depth`), then renumber in
+    level order so that parent < child, as the reference's `Tree.add_nodes` numbers its nodes."""
+    parent = [-1]
+    depth = [0]
+    nchild = [0]
+    for _ in range(1, n_nodes):
+        elig = [i for i in range(len(parent)) if nchild[i] < max_branch and depth[i] < max_depth]
+        p = elig[int(torch.randint(len(elig), (1,), generator=gen))]
+        parent.append(p)
+        depth.append(depth[p] + 1)
+        nchild.append(0)
+        nchild[p] += 1
+    order = sorted(range(n_nodes), key=lambda i: (depth[i], i))
+    new_of = {old: new for new, old in enumerate(order)}
+    parents = torch.tensor([-1 if parent[o] < 0 else new_of[parent[o]] for o in order], dtype=torch.long)
+    depths = torch.tensor([depth[o] for o in order], dtype=torch.long)
+    tokens = torch.randint(vocab, (n_nodes,), generator=gen, dtype=torch.long)
+    # sibling tokens must differ (a draft never proposes the same token twice under one node)
+    seen = {}
+    for i in range(1, n_nodes):
+        key = int(parents[i])
+        used = seen.setdefault(key, set())
+        while int(tokens[i]) in used:
+            tokens[i] = (int(tokens[i]) + 1) % vocab
+        used.add(int(tokens[i]))
+    return SynthTree(tokens, parents, depths)
+
+
+def verify_logits(tree: SynthTree, vocab: int, gen: torch.Generator, *, sigma: float = 3.0, boost: float = 6.0,
+                  boost_frac: float = 0.6, dtype: torch.dtype = torch.float32, peaked: bool = False,
+                  sharp_frac: float = 0.3, device: Optional[torch.device] = None) -> torch.Tensor:
+    """Target logits [n, vocab]: sigma * randn, with one random child's token boosted at
+    `boost_frac` of the internal nodes.
+
+    `peaked=False` is the literal benchmark distribution (+`boost` on the child's
+    logit).  With V ~ 150k the row maximum sits near 4.4 sigma, so a +6 boost almost
+    never wins the argmax and the normalised entropy stays near 0.6: the accept
+    walk and the entropy gate are barely exercised.  `peaked=True` is the parity
+    variant: the boosted child is set to row_max + 4, and `sharp_frac` of the
+    rows are scaled by 4 so their entropy drops below the usual 0.3 threshold.
+    """
+    n = tree.n
+    g_dev = gen.device
+    x = torch.randn((n, vocab), generator=gen, device=g_dev, dtype=torch.float32) * sigma
+    children = tree.children()
+    cpu_gen = gen if g_dev.type == "cpu" else torch.Generator().manual_seed(int(gen.initial_seed()) + 1)
+    for u in range(n):
+        if not children[u]:
+            continue
+        if float(torch.rand((), generator=cpu_gen)) < boost_frac:
+            c = children[u][int(torch.randint(len(children[u]), (1,), generator=cpu_gen))]
+            t = int(tree.token_ids[c])
+            if peaked:
+                x[u, t] = x[u].max() + 4.0
+            else:
+                x[u, t] += boost
+    if peaked:
+        sharp = torch.rand(n, generator=cpu_gen) < sharp_frac
+        x[sharp.to(x.device)] *= 4.0
+    x = x.to(dtype)
+    return x if device is None else x.to(device)
+
+
+def config1_case(seed: int, *, vocab: int = 152064, n_nodes: int = 64, max_depth: int = 8, max_branch: int = 4,
+                 dtype: torch.dtype = torch.float32, peaked: bool = False) -> Tuple[SynthTree, torch.Tensor]:
+    """Config 1 / 5 verify input: one 64-node tree and its [n, vocab] target logits."""
+    gen = torch.Generator().manual_seed(seed)
+    tree = random_tree(n_nodes, max_depth, max_branch, vocab, gen)
+    return tree, verify_logits(tree, vocab, gen, dtype=dtype, peaked=peaked)
+
+
+def random_page_table(batch: int, pages_per_seq: int, gen: torch.Generator) -> torch.Tensor:
+    """[batch, pages_per_seq] int32: a random permutation of the pool's pages split across sequences."""
+    perm = torch.randperm(batch * pages_per_seq, generator=gen)
+    return perm.reshape(batch, pages_per_seq).to(torch.int32)

@@ -1,0 +1,236 @@
+"""Generate the golden fixtures under tests/golden/ by running the UNMODIFIED reference.
+
+Usage (only where a read-only checkout of NYCU-EDgeAi/subspec is available):
+
+    python tests/golden/make_golden.py --reference /path/to/subspec [--only verify|expand|kv]
+
+The reference is imported, never copied.  Two third-party modules it imports but
+does not need on this path (`nvtx`, `prettytable`) are replaced by throw-away
+stubs in a temporary directory.  Inputs come from `subspec_b200.synthetic`
+(seeded); small cases also store their inputs inline so the fixture does not
+depend on the RNG stream.  Outputs written:
+
+    verify_cases.json / verify_small.npz   verify_tree (exact, lossy) results
+    lossy_unit_cases.json                  every call made by the reference's tests/test_lossy_tree_verify.py
+    expand_cases.json / expand_small.npz   _topk_flatten / Tree / TreeMaskCache results
+    kv_cases.json                          KvCachePool.reorder_cache_with_offset checksums
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import json
+import sys
+import tempfile
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+sys.path.insert(0, str(ROOT))
+
+from subspec_b200 import synthetic  # noqa: E402
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
+
+
+def import_reference(ref: str):
+    stub = Path(tempfile.mkdtemp(prefix="subspec_stub_"))
+    (stub / "nvtx.py").write_text(
+        "import contextlib\n@contextlib.contextmanager\ndef annotate(*a, **k):\n    yield\n")
+    (stub / "prettytable.py").write_text("class PrettyTable:\n    pass\n")
+    sys.path.insert(0, str(stub))
+    sys.path.insert(0, ref)
+    import specdecodes.models.utils.tree_verify as tv
+    import specdecodes.models.utils.lossy_tree_verify as ltv
+    import specdecodes.models.utils.cpu_tree as ct
+    import specdecodes.models.generators.base as gb
+    import specdecodes.models.generators.classic_sd as csd
+    import specdecodes.models.draft_models.base as db
+    import specdecodes.models.utils.flashinfer.cache_manager as cm
+    from specdecodes.models.utils.wandb_logger import wandb_logger
+    return dict(tv=tv, ltv=ltv, ct=ct, gb=gb, csd=csd, db=db, cm=cm, wandb_logger=wandb_logger)
+
+
+def ref_tree(ct, tree: synthetic.SynthTree):
+    """Build the reference's Tree by appending TreeNodes directly."""
+    t = ct.Tree(tree.token_ids[0], torch.float32)
+    for i in range(1, tree.n):
+        p = int(tree.parents[i])
+        node = ct.TreeNode(parent=p, token_id=int(tree.token_ids[i]), cumulative_probability=1.0,
+                           depth=int(tree.depths[i]))
+        t.nodes.append(node)
+        t.nodes[p].children.append(i)
+    t.current_size = tree.n
+    return t
+
+
+def run_ref_verify(ref, tree, logits, *, method, kwargs, eos, skip_nodes, root_ind):
+    rt = ref_tree(ref["ct"], tree)
+    ref["wandb_logger"].clear_log_data()
+    toks, hidden, (total, acc) = ref["tv"].verify_tree(
+        tree=rt, root_ind=root_ind, logits=logits.unsqueeze(0),
+        sample_token_fn=lambda *a, **k: ref["gb"].GeneratorBase._sample_token(None, *a, **k),
+        verify_step_fn=lambda *a, **k: ref["csd"].ClassicSDGeneratorBase._verify_step(None, *a, **k),
+        eos_token_id=eos, logits_processor=None, do_sample=False, skip_nodes=skip_nodes,
+        verify_method=method, verify_kwargs=kwargs)
+    return {"tokens": toks.squeeze(0).tolist(), "hidden": hidden.tolist(), "total_len": int(total),
+            "accept_len": int(acc)}
+
+
+def oracle_upcast(tree, logits, *, method, kwargs, eos, skip_nodes, root_ind):
+    """The fp32-upcast restatement, to flag cases whose outcome depends on 16-bit rounding of probabilities."""
+    sys.path.insert(0, str(ROOT))
+    from oracle import verify_oracle as vo
+    rows = logits.shape[0]
+    ch_all = tree.children()
+    n_loc = tree.n - skip_nodes
+    ch = [[c - skip_nodes for c in ch_all[v + skip_nodes] if c - skip_nodes >= 0] for v in range(n_loc)]
+    tok = tree.token_ids[skip_nodes:].tolist()
+    probs = vo.target_probs(logits, upcast=True)
+    tgt = probs.argmax(-1).tolist()
+    if method == "exact":
+        r = vo.exact_walk(target=tgt + [-1] * (n_loc - rows), token_ids=tok, children=ch, root=root_ind - skip_nodes,
+                          n_rows=rows, eos=eos)
+    else:
+        n = min(rows, n_loc)
+        root = root_ind - skip_nodes
+        if root < 0 or root >= n:
+            root = 0
+        r = vo.lossy_verify(probs=probs[:n], token_ids=tok[:n], children=[[c for c in k if c < n] for k in ch[:n]],
+                            root=root, eos=eos, threshold=float(kwargs.get("threshold", 0.0)),
+                            window=int(kwargs.get("window_size", 1)),
+                            use_entropy=str(kwargs.get("threshold_method", "prob")) == "entropy", target=tgt[:n])
+    return {"tokens": r.tokens, "hidden": [h + skip_nodes for h in r.hidden], "total_len": r.total_len,
+            "accept_len": r.accept_len}, r.min_gate_margin
+
+
+METHODS = [
+    ("exact", {}),
+    ("lossy", {"threshold_method": "entropy", "threshold": 0.3, "window_size": 6}),
+    ("lossy", {"threshold_method": "entropy", "threshold": 0.3, "window_size": 1}),
+    ("lossy", {"threshold_method": "prob", "threshold": 0.05, "window_size": 0}),
+    ("lossy", {"threshold_method": "prob", "threshold": 0.2, "window_size": 2}),
+]
+
+
+def gen_verify(ref, out_dir: Path):
+    cases, small = [], {}
+    skipped = []
+
+    def add(name, tree, logits, *, gen_params, store_inline, eos=None, skip_nodes=0, root_ind=0, rows=None):
+        rows = logits.shape[0] if rows is None else rows
+        lg = logits[:rows]
+        for mi, (method, kwargs) in enumerate(METHODS):
+            exp = run_ref_verify(ref, tree, lg, method=method, kwargs=kwargs, eos=eos, skip_nodes=skip_nodes,
+                                 root_ind=root_ind)
+            up, margin = oracle_upcast(tree, lg, method=method, kwargs=kwargs, eos=eos, skip_nodes=skip_nodes,
+                                       root_ind=root_ind)
+            case = dict(name=f"{name}/m{mi}", input=name, method=method, kwargs=kwargs, eos=eos,
+                        skip_nodes=skip_nodes, root_ind=root_ind, rows=rows, expected=exp,
+                        upcast_agrees=(up == exp), gate_margin=None if margin == float("inf") else margin,
+                        **gen_params)
+            if up != exp:
+                skipped.append(case["name"])
+            cases.append(case)
+        if store_inline:
+            small[name + "/logits"] = logits.float().numpy()
+            small[name + "/tokens"] = tree.token_ids.numpy()
+            small[name + "/parents"] = tree.parents.numpy()
+
+    # --- small vocab, inputs stored inline ---
+    k = 0
+    for vocab, n_nodes, depth, branch in [(11, 6, 3, 3), (50, 16, 5, 3), (257, 24, 6, 4), (1000, 40, 8, 4)]:
+        for dtype in ("float32", "bfloat16", "float16"):
+            for rep in range(2):
+                seed = 1000 + k
+                k += 1
+                gen = torch.Generator().manual_seed(seed)
+                tree = synthetic.random_tree(n_nodes, depth, branch, vocab, gen)
+                logits = synthetic.verify_logits(tree, vocab, gen, dtype=DT[dtype], peaked=True, sigma=2.0)
+                eos = int(tree.token_ids[n_nodes // 2]) if rep == 1 else None
+                add(f"small/v{vocab}_n{n_nodes}_{dtype}_{rep}", tree, logits,
+                    gen_params=dict(dtype=dtype, vocab=vocab, n_nodes=n_nodes, inline=True), store_inline=True,
+                    eos=eos)
+    # --- skip_nodes / root_ind / fewer rows than nodes (SubSpec v2 post-verify call pattern) ---
+    for rep in range(4):
+        seed = 2000 + rep
+        gen = torch.Generator().manual_seed(seed)
+        vocab, n_nodes = 97, 30
+        tree = synthetic.random_tree(n_nodes, 6, 3, vocab, gen)
+        skip = 1 + rep
+        ch = tree.children()
+        # root_ind = first node at or after `skip` that has children
+        root_ind = next(i for i in range(skip, n_nodes) if ch[i])
+        sub = synthetic.SynthTree(tree.token_ids[skip:], tree.parents[skip:] - skip, tree.depths[skip:])
+        logits_local = synthetic.verify_logits(sub, vocab, gen, dtype=torch.float32, peaked=True, sigma=2.0)
+        rows = logits_local.shape[0] - (rep % 2) * 5
+        name = f"skip/v{vocab}_n{n_nodes}_s{skip}_{rep}"
+        add(name, tree, logits_local, gen_params=dict(dtype="float32", vocab=vocab, n_nodes=n_nodes, inline=True),
+            store_inline=True, skip_nodes=skip, root_ind=root_ind, rows=rows)
+    # --- benchmark shapes, regenerated from the seed ---
+    for dtype, peaked, seeds in [("float32", False, [1]), ("float32", True, [11, 12, 13]),
+                                 ("bfloat16", False, [5]), ("bfloat16", True, [51, 52, 53]),
+                                 ("float16", True, [61])]:
+        for seed in seeds:
+            tree, logits = synthetic.config1_case(seed, dtype=DT[dtype], peaked=peaked)
+            add(f"config1/{dtype}_{'peaked' if peaked else 'literal'}_{seed}", tree, logits,
+                gen_params=dict(dtype=dtype, vocab=152064, n_nodes=64, inline=False, seed=seed, peaked=peaked),
+                store_inline=False)
+    (out_dir / "verify_cases.json").write_text(json.dumps(
+        {"torch": torch.__version__, "cases": cases, "dtype_sensitive": skipped}, indent=1))
+    np.savez_compressed(out_dir / "verify_small.npz", **small)
+    print(f"verify: {len(cases)} cases, {len(skipped)} depend on 16-bit probability rounding: {skipped}")
+
+
+def gen_lossy_unit(ref, ref_root: str, out_dir: Path):
+    """Run the reference's own unit tests of the lossy verifier and record every call they make
+    to lossy_bottom_up_verify: inputs, outputs and the wandb_logger metrics left behind."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("ref_test_lossy", str(Path(ref_root) / "tests" /
+                                                                      "test_lossy_tree_verify.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    real = mod.lossy_bottom_up_verify
+    records = []
+    current = {"name": None}
+
+    def recorder(**kw):
+        sampled, hidden, acc = real(**kw)
+        log = {k: v for k, v in ref["wandb_logger"].log_data.items() if isinstance(v, (int, float, str))}
+        records.append(dict(
+            test=current["name"], probs=kw["probs"].tolist(), token_ids=kw["token_ids"].tolist(),
+            parent_indices=kw["parent_indices"].tolist(), children_lists=[list(c) for c in kw["children_lists"]],
+            root_index=int(kw["root_index"]), eos_token_id=kw["eos_token_id"], do_sample=bool(kw["do_sample"]),
+            threshold=float(kw["threshold"]), window_size=int(kw["window_size"]),
+            threshold_method=kw.get("threshold_method", "prob"),
+            expected=dict(sampled=sampled.tolist(), hidden=hidden.tolist(), accept_len=int(acc), log_data=log)))
+        return sampled, hidden, acc
+
+    mod.lossy_bottom_up_verify = recorder
+    for name in sorted(n for n in dir(mod) if n.startswith("test_")):
+        current["name"] = name
+        ref["wandb_logger"].clear_log_data()
+        getattr(mod, name)()  # the reference's own assertions run here
+    (out_dir / "lossy_unit_cases.json").write_text(json.dumps({"cases": records}, indent=1))
+    print(f"lossy unit: {len(records)} recorded calls from {len(set(r['test'] for r in records))} reference tests")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only", default=None)
+    args = ap.parse_args()
+    ref = import_reference(args.reference)
+    torch.set_num_threads(8)
+    if args.only in (None, "verify"):
+        gen_verify(ref, HERE)
+    if args.only in (None, "lossy_unit"):
+        gen_lossy_unit(ref, args.reference, HERE)
+
+
+if __name__ == "__main__":
+    main()

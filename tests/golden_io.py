@@ -1,0 +1,51 @@
+"""Load the committed golden fixtures (tests/golden/) back into tensors."""
+from __future__ import annotations
+
+import json
+from functools import lru_cache
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from subspec_b200 import synthetic
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
+
+
+@lru_cache(maxsize=None)
+def verify_cases():
+    return json.loads((GOLDEN / "verify_cases.json").read_text())["cases"]
+
+
+@lru_cache(maxsize=None)
+def _verify_small():
+    return dict(np.load(GOLDEN / "verify_small.npz"))
+
+
+@lru_cache(maxsize=4)
+def _config1(seed: int, dtype: str, peaked: bool):
+    return synthetic.config1_case(seed, dtype=DT[dtype], peaked=peaked)
+
+
+def verify_input(case):
+    """(SynthTree over the whole tree, logits [rows, V] in the case's dtype) for one golden verify case."""
+    if case["inline"]:
+        z = _verify_small()
+        name = case["input"]
+        tok = torch.from_numpy(z[name + "/tokens"])
+        par = torch.from_numpy(z[name + "/parents"])
+        depth = torch.zeros_like(par)
+        for i in range(1, len(par)):
+            depth[i] = depth[par[i]] + 1
+        tree = synthetic.SynthTree(tok, par, depth)
+        logits = torch.from_numpy(z[name + "/logits"]).to(DT[case["dtype"]])
+    else:
+        tree, logits = _config1(case["seed"], case["dtype"], case["peaked"])
+    return tree, logits[:case["rows"]]
+
+
+@lru_cache(maxsize=None)
+def lossy_unit_cases():
+    return json.loads((GOLDEN / "lossy_unit_cases.json").read_text())["cases"]

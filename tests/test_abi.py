@@ -1,0 +1,54 @@
+"""The C-ABI library builds for sm_100a, loads, and exports every symbol the header declares (no GPU needed)."""
+import ctypes as C
+import re
+from pathlib import Path
+
+from subspec_b200 import _lib
+
+HEADER = Path(__file__).resolve().parent.parent / "include" / "subspec_b200.h"
+
+
+def _declared():
+    text = HEADER.read_text()
+    return set(re.findall(r"SUBSPEC_API\s+[\w\s\*]+?\b(subspec_\w+)\s*\(", text))
+
+
+def test_header_symbols_are_exported(cuda_lib):
+    declared = _declared()
+    assert declared, "no SUBSPEC_API declarations found"
+    assert declared == set(_lib.SYMBOLS), (declared ^ set(_lib.SYMBOLS))
+    for name in declared:
+        assert hasattr(cuda_lib, name), name
+    assert b"sm_100a" in cuda_lib.subspec_version()
+
+
+def test_struct_sizes_are_checked(cuda_lib):
+    a = _lib.VerifyArgs()
+    a.struct_size = C.sizeof(_lib.VerifyArgs) - 8
+    assert cuda_lib.subspec_verify_batched(C.byref(a), None) == _lib.EINVAL
+    # a correctly sized, empty batch is accepted without touching the device
+    a.struct_size = C.sizeof(_lib.VerifyArgs)
+    a.batch, a.max_nodes, a.vocab, a.max_out = 0, 8, 16, 9
+    assert cuda_lib.subspec_verify_batched(C.byref(a), None) == _lib.OK
+    k = _lib.KvPagedArgs()
+    k.struct_size = C.sizeof(_lib.KvPagedArgs)
+    k.batch, k.layers, k.num_pages, k.page_len, k.heads, k.head_dim, k.elem_bytes = 0, 1, 1, 16, 4, 128, 2
+    assert cuda_lib.subspec_kv_compact_paged(C.byref(k), None) == _lib.OK
+    k.elem_bytes = 3
+    assert cuda_lib.subspec_kv_compact_paged(C.byref(k), None) == _lib.EINVAL
+    h = _lib.KvHfArgs()
+    h.struct_size = 4
+    assert cuda_lib.subspec_kv_compact_hf(C.byref(h), None) == _lib.EINVAL
+
+
+def test_argument_validation(cuda_lib):
+    n = C.c_size_t(0)
+    assert cuda_lib.subspec_verify_scratch_bytes(4, 64, C.byref(n)) == _lib.OK and n.value > 0
+    assert cuda_lib.subspec_verify_scratch_bytes(4, 5000, C.byref(n)) == _lib.EINVAL
+    a = _lib.VerifyArgs()
+    a.struct_size = C.sizeof(_lib.VerifyArgs)
+    a.batch, a.max_nodes, a.vocab, a.max_out = 1, 8, 16, 9
+    # null pointers are rejected before any launch
+    assert cuda_lib.subspec_verify_batched(C.byref(a), None) == _lib.EINVAL
+    a.max_nodes = 4096
+    assert cuda_lib.subspec_verify_batched(C.byref(a), None) == _lib.EUNSUPPORTED

@@ -1,0 +1,66 @@
+"""The CPU oracle against vectors produced by the reference itself (tests/golden/make_golden.py)."""
+import pytest
+import torch
+
+from oracle import verify_oracle as vo
+from tests import golden_io
+
+
+def _run_oracle(case, upcast):
+    tree, logits = golden_io.verify_input(case)
+    skip, rows = case["skip_nodes"], case["rows"]
+    ch_all = tree.children()
+    n_loc = tree.n - skip
+    ch = [[c - skip for c in ch_all[v + skip] if c - skip >= 0] for v in range(n_loc)]
+    tok = tree.token_ids[skip:].tolist()
+    probs = vo.target_probs(logits, upcast=upcast)
+    tgt = probs.argmax(-1).tolist()
+    kw = case["kwargs"]
+    if case["method"] == "exact":
+        r = vo.exact_walk(target=tgt + [-1] * (n_loc - rows), token_ids=tok, children=ch,
+                          root=case["root_ind"] - skip, n_rows=rows, eos=case["eos"])
+    else:
+        n = min(rows, n_loc)
+        root = case["root_ind"] - skip
+        if root < 0 or root >= n:
+            root = 0
+        r = vo.lossy_verify(probs=probs[:n], token_ids=tok[:n], children=[[c for c in k if c < n] for k in ch[:n]],
+                            root=root, eos=case["eos"], threshold=float(kw.get("threshold", 0.0)),
+                            window=int(kw.get("window_size", 1)),
+                            use_entropy=kw.get("threshold_method", "prob") == "entropy", target=tgt[:n])
+    return dict(tokens=r.tokens, hidden=[h + skip for h in r.hidden], total_len=r.total_len, accept_len=r.accept_len)
+
+
+@pytest.mark.parametrize("upcast", [False, True])
+def test_oracle_matches_reference_verify_tree(upcast):
+    cases = golden_io.verify_cases()
+    assert len(cases) >= 150
+    bad = []
+    for case in cases:
+        if upcast and not case["upcast_agrees"]:
+            continue
+        if _run_oracle(case, upcast) != case["expected"]:
+            bad.append(case["name"])
+    assert not bad, bad
+
+
+def test_oracle_matches_reference_unit_tests():
+    cases = golden_io.lossy_unit_cases()
+    assert len(cases) == 8
+    for c in cases:
+        probs = torch.tensor(c["probs"], dtype=torch.float32)
+        r = vo.lossy_verify(probs=probs, token_ids=c["token_ids"], children=c["children_lists"],
+                            root=c["root_index"], eos=c["eos_token_id"], threshold=c["threshold"],
+                            window=c["window_size"], use_entropy=c["threshold_method"] == "entropy")
+        assert r.tokens == c["expected"]["sampled"], c["test"]
+        assert r.hidden == c["expected"]["hidden"], c["test"]
+        assert r.accept_len == c["expected"]["accept_len"], c["test"]
+
+
+def test_inverse_cdf_pick_edges():
+    row = torch.tensor([0.0, 0.25, 0.0, 0.5, 0.25, 0.0])
+    assert vo.inverse_cdf_pick(row, 0.0) == 1
+    assert vo.inverse_cdf_pick(row, 0.2499) == 1
+    assert vo.inverse_cdf_pick(row, 0.25) == 3
+    assert vo.inverse_cdf_pick(row, 0.9999999) == 4
+    assert vo.inverse_cdf_pick(row, 1.0) == 4

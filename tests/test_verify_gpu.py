@@ -1,0 +1,134 @@
+"""Parity of the fused CUDA verifier with the reference's outputs (golden) and with the CPU oracle."""
+import pytest
+import torch
+
+from oracle import verify_oracle as vo
+from subspec_b200 import synthetic
+from subspec_b200.tree import Tree
+from subspec_b200.verify import lossy_bottom_up_verify, verify_tree, verify_tree_batched
+from subspec_b200.wandb_logger import wandb_logger
+from tests import golden_io
+
+pytestmark = pytest.mark.gpu
+
+
+def _tree_of(st: synthetic.SynthTree) -> Tree:
+    return Tree.from_arrays(st.token_ids.tolist(), st.parents.tolist())
+
+
+def test_reference_unit_cases_through_the_kernel(cuda_lib):
+    """The eight hand-built cases of the reference's own test file, same signature, on the GPU."""
+    for c in golden_io.lossy_unit_cases():
+        wandb_logger.clear_log_data()
+        sampled, hidden, acc = lossy_bottom_up_verify(
+            probs=torch.tensor(c["probs"], dtype=torch.float32), token_ids=torch.tensor(c["token_ids"]),
+            parent_indices=torch.tensor(c["parent_indices"]), children_lists=c["children_lists"],
+            root_index=c["root_index"], eos_token_id=c["eos_token_id"], do_sample=c["do_sample"],
+            threshold=c["threshold"], window_size=c["window_size"], threshold_method=c["threshold_method"])
+        exp = c["expected"]
+        assert sampled.tolist() == exp["sampled"], c["test"]
+        assert hidden.tolist() == exp["hidden"], c["test"]
+        assert acc == exp["accept_len"], c["test"]
+        for key, val in exp["log_data"].items():
+            got = wandb_logger.log_data[key]
+            if isinstance(val, str):
+                assert got == val, (c["test"], key)
+            else:
+                assert got == pytest.approx(val, rel=1e-6, abs=1e-7), (c["test"], key)
+
+
+def test_golden_verify_tree(cuda_lib):
+    """verify_tree on the GPU reproduces what the reference returned for every golden case, bit for bit."""
+    bad = []
+    for case in golden_io.verify_cases():
+        if not case["upcast_agrees"]:
+            continue
+        st, logits = golden_io.verify_input(case)
+        toks, hidden, (total, acc) = verify_tree(
+            tree=_tree_of(st), root_ind=case["root_ind"], logits=logits.unsqueeze(0).cuda(), eos_token_id=case["eos"],
+            logits_processor=None, do_sample=False, skip_nodes=case["skip_nodes"], verify_method=case["method"],
+            verify_kwargs=case["kwargs"])
+        got = dict(tokens=toks.squeeze(0).tolist(), hidden=hidden.tolist(), total_len=total, accept_len=acc)
+        if got != case["expected"]:
+            bad.append((case["name"], got, case["expected"]))
+    assert not bad, bad[:3]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_entropy_and_probabilities_match_fp32_oracle(cuda_lib, dtype):
+    """Entropy and P[parent, child token] within 1e-5 relative of the fp32 oracle (the stated tolerance)."""
+    from subspec_b200 import _lib
+    from subspec_b200.verify import get_workspace, flatten_tree
+
+    st, logits = synthetic.config1_case(77, dtype=dtype, peaked=True)
+    tree = _tree_of(st)
+    tok, off, idx = flatten_tree(tree, 0, limit=st.n, restrict=True)
+    ws = get_workspace(1, st.n, torch.device("cuda", 0))
+    ws.set_trees([(tok, off, idx, st.n, 0)])
+    ws.run(logits.unsqueeze(0).cuda(), input_kind=_lib.IN_LOGITS, method=_lib.VERIFY_LOSSY, gate=_lib.GATE_ENTROPY,
+           threshold=0.3, window=6)
+    out = ws.fetch()
+    probs = vo.target_probs(logits, upcast=True).double()
+    ent = torch.tensor(vo.normalised_entropy(probs))
+    got_ent = torch.from_numpy(out["node_entropy"][0, :st.n]).double()
+    assert torch.allclose(got_ent, ent, rtol=1e-5, atol=1e-7), (got_ent - ent).abs().max()
+    assert out["node_target"][0, :st.n].tolist() == probs.argmax(-1).tolist()
+    par = st.parents.tolist()
+    for c in range(1, st.n):
+        ref = float(probs[par[c], int(st.token_ids[c])])
+        assert out["node_child_prob"][0, c] == pytest.approx(ref, rel=1e-5, abs=1e-30)
+
+
+def test_batched_equals_per_sequence(cuda_lib):
+    """A batch in one launch gives, per sequence, what the single-sequence call gives (and the oracle)."""
+    B, vocab, n = 12, 4099, 33  # vocab not a multiple of 8: exercises the unaligned row path
+    gen = torch.Generator().manual_seed(5)
+    sts = [synthetic.random_tree(n - (b % 3), 6, 4, vocab, gen) for b in range(B)]
+    logits = torch.zeros(B, n, vocab, dtype=torch.bfloat16)
+    for b, st in enumerate(sts):
+        logits[b, :st.n] = synthetic.verify_logits(st, vocab, gen, dtype=torch.bfloat16, peaked=True)
+    trees = [_tree_of(st) for st in sts]
+    for method, kw in [("exact", {}), ("lossy", {"threshold_method": "entropy", "threshold": 0.3, "window_size": 1}),
+                       ("lossy", {"threshold_method": "prob", "threshold": 0.1, "window_size": 0})]:
+        res = verify_tree_batched(trees=trees, root_inds=[0] * B, logits=logits.cuda(), eos_token_id=None,
+                                  verify_method=method, verify_kwargs=kw)
+        for b, st in enumerate(sts):
+            r = vo.verify(logits=logits[b, :st.n], token_ids=st.token_ids.tolist(), children=st.children(),
+                          method=method, threshold=kw.get("threshold", 0.0), window=kw.get("window_size", 1),
+                          threshold_method=kw.get("threshold_method", "prob"), upcast=True)
+            assert res[b].sampled_tokens.squeeze(0).tolist() == r.tokens, (method, b)
+            assert res[b].hidden_indices.tolist() == r.hidden, (method, b)
+            assert (res[b].total_len, res[b].accept_len) == (r.total_len, r.accept_len)
+
+
+def test_edge_cases(cuda_lib):
+    # a single root node: no children, the only output is the bonus token
+    t = Tree(torch.tensor(3))
+    logits = torch.randn(1, 1, 17)
+    toks, hidden, (total, acc) = verify_tree(tree=t, root_ind=0, logits=logits, eos_token_id=None,
+                                             logits_processor=None, do_sample=False)
+    assert toks.tolist() == [[int(logits[0, 0].argmax())]] and hidden.tolist() == [0] and (total, acc) == (0, 0)
+    # argmax ties resolve to the first index, as torch.argmax does
+    logits = torch.zeros(1, 1, 40)
+    logits[0, 0, 7] = logits[0, 0, 31] = 2.0
+    toks, _, _ = verify_tree(tree=t, root_ind=0, logits=logits, eos_token_id=None, logits_processor=None,
+                             do_sample=False, verify_method="lossy")
+    assert toks.tolist() == [[7]]
+    # -inf (masked) logits do not poison the entropy
+    logits = torch.full((1, 1, 64), float("-inf"))
+    logits[0, 0, 5], logits[0, 0, 9] = 1.0, 1.0
+    st = synthetic.SynthTree(torch.tensor([0, 5]), torch.tensor([-1, 0]), torch.tensor([0, 1]))
+    toks, hidden, (total, acc) = verify_tree(tree=_tree_of(st), root_ind=0, logits=logits.expand(1, 2, 64).contiguous(),
+                                             eos_token_id=None, logits_processor=None, do_sample=False,
+                                             verify_method="lossy",
+                                             verify_kwargs={"threshold_method": "entropy", "threshold": 0.5,
+                                                            "window_size": 0})
+    assert toks.tolist() == [[5, 5]] and acc == 1
+    with pytest.raises(ValueError):
+        verify_tree(tree=t, root_ind=0, logits=torch.randn(1, 1, 17), eos_token_id=None, logits_processor=None,
+                    do_sample=False, verify_method="nonsense")
+    # an out-of-vocabulary draft token is reported, not read
+    st = synthetic.SynthTree(torch.tensor([0, 99]), torch.tensor([-1, 0]), torch.tensor([0, 1]))
+    with pytest.raises(ValueError):
+        verify_tree(tree=_tree_of(st), root_ind=0, logits=torch.randn(1, 2, 17), eos_token_id=None,
+                    logits_processor=None, do_sample=False, verify_method="lossy")
