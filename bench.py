@@ -1,0 +1,485 @@
+#!/usr/bin/env python
+"""Benchmark of the speculative-decoding hot path on B200: tree verify + accept, then accepted-path KV compaction.
+
+Workload (BASELINE.json configs[4], "8-GPU sharded speculative step"): 512 independent sequences
+split over the N GPUs of one box.  Each sequence owns a 64-node draft tree and target logits
+bf16 [64, 152064] ~ N(0, 3^2) with one drafted child boosted by +6 at 60 % of the internal nodes,
+and a paged bf16 KV region of 28 layers x 4 KV heads x 128 dim x 4096 tokens (page 16, random page
+table).  One "step" of a sequence = greedy (exact) verify, lossy verify (entropy gate 0.3, window 6)
+and compaction of the accepted path's KV rows.  Sequences are processed in waves of `--wave`
+sequences (one launch per kernel per wave); there is no collective on the hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]            # N > 1: launched by torchrun
+    python bench.py --impl reference ...                            # the CPU restatement of the reference path
+
+Prints ONE JSON line (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+VOCAB = 152064
+NODES = 64
+KV_LAYERS, KV_HEADS, KV_DIM, KV_TOKENS, PAGE_LEN = 28, 4, 128, 4096, 16
+LOSSY_KW = {"threshold_method": "entropy", "threshold": 0.3, "window_size": 6}
+METRIC = "tree verify+accept steps/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--seqs", type=int, default=512, help="sequences in the whole job (split over the GPUs)")
+    ap.add_argument("--wave", type=int, default=64, help="sequences per kernel launch")
+    ap.add_argument("--variant", default="literal", choices=["literal", "peaked"],
+                    help="literal: +6 boost as BASELINE.json states; peaked: boosted child = row max + 4")
+    ap.add_argument("--kv-tokens", type=int, default=KV_TOKENS)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--cpu-sample", type=int, default=0, help="sequences per CPU-baseline sample (0 = auto)")
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------------------
+# inputs
+# --------------------------------------------------------------------------------------
+def make_wave_inputs(seq_ids, variant: str, device, with_logits=True):
+    """Trees (host) and logits (device) for the given global sequence ids; everything seeded by the id."""
+    from subspec_b200 import synthetic
+
+    trees = []
+    for sid in seq_ids:
+        gen = torch.Generator().manual_seed(1_000_003 * 5 + sid)
+        trees.append(synthetic.random_tree(NODES, 8, 4, VOCAB, gen))
+    if not with_logits:
+        return trees, None
+    S = len(seq_ids)
+    dgen = torch.Generator(device=device).manual_seed(7_000_001 + seq_ids[0])
+    logits = torch.empty(S, NODES, VOCAB, dtype=torch.bfloat16, device=device)
+    for b in range(S):  # fp32 noise generated one sequence at a time to bound the transient footprint
+        logits[b] = (torch.randn(NODES, VOCAB, generator=dgen, device=device) * 3.0).to(torch.bfloat16)
+    bi, ui, ti = [], [], []
+    for b, (sid, st) in enumerate(zip(seq_ids, trees)):
+        cgen = torch.Generator().manual_seed(9_000_011 + sid)
+        ch = st.children()
+        for u in range(st.n):
+            if ch[u] and float(torch.rand((), generator=cgen)) < 0.6:
+                c = ch[u][int(torch.randint(len(ch[u]), (1,), generator=cgen))]
+                bi.append(b)
+                ui.append(u)
+                ti.append(int(st.token_ids[c]))
+    bi, ui, ti = (torch.tensor(x, device=device) for x in (bi, ui, ti))
+    if variant == "peaked":
+        rowmax = logits.float().amax(dim=-1)
+        logits[bi, ui, ti] = (rowmax[bi, ui] + 4.0).to(torch.bfloat16)
+    else:
+        logits[bi, ui, ti] = (logits[bi, ui, ti].float() + 6.0).to(torch.bfloat16)
+    return trees, logits
+
+
+def flats_of(trees):
+    from subspec_b200.tree import Tree
+    from subspec_b200.verify import flatten_tree
+
+    out = []
+    for st in trees:
+        t = Tree.from_arrays(st.token_ids.tolist(), st.parents.tolist())
+        tok, off, idx = flatten_tree(t, 0, limit=st.n, restrict=True)
+        out.append((tok, off, idx, st.n, 0))
+    return out
+
+
+# --------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, device_index: int, period_s: float = 0.02):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            uuid = torch.cuda.get_device_properties(device_index).uuid
+            self._nv = pynvml
+            try:
+                self._h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+            except Exception:
+                self._h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+            self._period = period_s
+        except Exception as e:  # NVML missing: report that instead of numbers
+            self._nv = None
+            self.error = repr(e)
+
+    def _loop(self):
+        nv = self._nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self._period)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if self._nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "error": self.error}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# --------------------------------------------------------------------------------------
+# CPU restatement of the reference path (oracle), used as baseline and as the reference arm
+# --------------------------------------------------------------------------------------
+def cpu_step(trees, logits_cpu, pools, beams_out=None):
+    """One pass of the reference's CPU path over a list of sequences: verify exact, verify lossy, KV reorder."""
+    from oracle import kv_oracle as ko
+    from oracle import verify_oracle as vo
+
+    accepted = 0
+    for i, st in enumerate(trees):
+        lg = logits_cpu[i]
+        tok, ch = st.token_ids.tolist(), st.children()
+        vo.verify(logits=lg, token_ids=tok, children=ch, method="exact")
+        r = vo.verify(logits=lg, token_ids=tok, children=ch, method="lossy", threshold=LOSSY_KW["threshold"],
+                      window=LOSSY_KW["window_size"], threshold_method="entropy")
+        accepted += len(r.tokens)
+        if pools is not None:
+            ko.paged_reorder(pools[i % len(pools)], torch.tensor(r.hidden), KV_TOKENS - NODES)
+    return accepted
+
+
+def cpu_baseline(sample: int, reps: int, variant: str):
+    """Times `reps` passes of the CPU path over `sample` sequences; returns (seq-steps/s, description)."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    seq_ids = list(range(sample))
+    trees, _ = make_wave_inputs(seq_ids, variant, "cpu", with_logits=False)
+    gen = torch.Generator().manual_seed(123)
+    logits = (torch.randn(sample, NODES, VOCAB, generator=gen) * 3.0).to(torch.bfloat16)
+    # one identity-table pool per sequence in flight, as the reference's FlashInferCache allocates it
+    pool = (torch.randn(KV_LAYERS, KV_TOKENS // PAGE_LEN, 2, PAGE_LEN, KV_HEADS, KV_DIM, generator=gen)
+            .to(torch.bfloat16))
+    cpu_step(trees[:1], logits[:1], [pool])  # warm-up
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        cpu_step(trees, logits, [pool])
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    med = times[len(times) // 2]
+    return sample / med, (f"{sample} sequences x {reps} passes (median): torch-CPU softmax/entropy/argmax + Python walk "
+                          f"(exact, then lossy) on bf16 [64,{VOCAB}] logits, then clone-whole-pool KV reorder of a "
+                          f"{pool.numel() * 2 / 1e6:.1f} MB pool, as the reference does per sequence")
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    sample = args.cpu_sample or 4
+    torch.set_num_threads(cores)
+    seq_ids = list(range(sample))
+    trees, _ = make_wave_inputs(seq_ids, args.variant, "cpu", with_logits=False)
+    gen = torch.Generator().manual_seed(123)
+    logits = (torch.randn(sample, NODES, VOCAB, generator=gen) * 3.0).to(torch.bfloat16)
+    pool = (torch.randn(KV_LAYERS, KV_TOKENS // PAGE_LEN, 2, PAGE_LEN, KV_HEADS, KV_DIM, generator=gen)
+            .to(torch.bfloat16))
+    accepted = 0
+    for _ in range(args.warmup):
+        cpu_step(trees[:1], logits[:1], [pool])
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        accepted += cpu_step(trees, logits, [pool])
+    dt = time.perf_counter() - t0
+    value = sample * args.steps / dt
+    desc = (f"each step = {sample} sequences of the workload through the CPU restatement of the reference path "
+            f"(oracle/verify_oracle.py + oracle/kv_oracle.py), {cores} torch threads")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "steps/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, sample, 1, sample),
+        "accepted_tok_per_s": accepted / dt,
+        "cpu_baseline": {"value": value, "unit": "steps/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, total_seqs, world, per_rank):
+    return {
+        "workload": "BASELINE.json configs[4]: sharded speculative step (greedy + lossy verify of 64-node trees, "
+                    "vocab 152064, bf16 logits; accepted-path KV compaction, 28x4x128x4096 bf16 paged cache, page 16, "
+                    "random page table)",
+        "sequences": total_seqs, "sequences_per_gpu": per_rank, "wave": args.wave, "variant": args.variant,
+        "lossy": LOSSY_KW, "kv_tokens": args.kv_tokens, "parallelism": f"dp{world}",
+        "l2": "inputs larger than L2 (each wave streams 1.25 GB of logits per verify pass; no flush needed)",
+    }
+
+
+# --------------------------------------------------------------------------------------
+# native arm
+# --------------------------------------------------------------------------------------
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch.distributed as dist
+
+    from subspec_b200 import build as _build
+    from subspec_b200 import synthetic
+    from subspec_b200.step import SpeculativeStepBatch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if rank == 0:
+        _build.build()
+    if world > 1:
+        dist.barrier()
+
+    total = args.seqs
+    per_rank = total // world
+    wave = min(args.wave, per_rank)
+    n_waves = per_rank // wave
+    per_rank = n_waves * wave
+    total = per_rank * world
+    pages_per_seq = args.kv_tokens // PAGE_LEN
+    kv_bytes_seq = KV_LAYERS * pages_per_seq * 2 * PAGE_LEN * KV_HEADS * KV_DIM * 2
+    need = per_rank * (NODES * VOCAB * 2 + kv_bytes_seq) + (6 << 30)
+    free, _ = torch.cuda.mem_get_info(device)
+    if need > free:
+        raise SystemExit(f"rank {rank}: needs {need / 2**30:.1f} GiB, {free / 2**30:.1f} GiB free; "
+                         f"use --kv-tokens to shrink the per-sequence cache")
+
+    # ---- build the waves ----
+    waves = []
+    first = rank * per_rank
+    for w in range(n_waves):
+        ids = list(range(first + w * wave, first + (w + 1) * wave))
+        trees, logits = make_wave_inputs(ids, args.variant, device)
+        pgen = torch.Generator().manual_seed(31 + ids[0])
+        sb = SpeculativeStepBatch(wave, NODES, device, kv_layers=KV_LAYERS, kv_heads=KV_HEADS, head_dim=KV_DIM,
+                                  page_len=PAGE_LEN, pages_per_seq=pages_per_seq,
+                                  page_table=synthetic.random_page_table(wave, pages_per_seq, pgen))
+        for layer in range(KV_LAYERS):
+            sb.pool[layer].normal_()
+        sb.set_trees(flats_of(trees))
+        sb.set_kv_offsets([args.kv_tokens - NODES] * wave)
+        waves.append((sb, logits, trees, ids))
+    torch.cuda.synchronize()
+
+    def one_step(events=None):
+        for sb, logits, _, _ in waves:
+            if events is not None:
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+                ev[0].record()
+            sb.verify(logits, verify_method="exact")
+            if events is not None:
+                ev[1].record()
+            sb.verify(logits, verify_method="lossy", verify_kwargs=LOSSY_KW)
+            if events is not None:
+                ev[2].record()
+            sb.compact_kv()
+            if events is not None:
+                ev[3].record()
+                events.append(ev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    # ---- device-resident timing ----
+    for _ in range(args.warmup):
+        one_step()
+    torch.cuda.synchronize()
+    barrier()
+    kernel_events = []
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        torch.cuda.synchronize()
+        t_start.record()
+        for _ in range(args.steps):
+            one_step(kernel_events)
+        t_end.record()
+        torch.cuda.synchronize()
+    barrier()
+    ms_total = t_start.elapsed_time(t_end)
+    ms_exact = sum(e[0].elapsed_time(e[1]) for e in kernel_events) / len(kernel_events)
+    ms_lossy = sum(e[1].elapsed_time(e[2]) for e in kernel_events) / len(kernel_events)
+    ms_kv = sum(e[2].elapsed_time(e[3]) for e in kernel_events) / len(kernel_events)
+
+    # ---- results of the last step: acceptance statistics + parity spot check ----
+    accepted_tokens, kept_rows = 0, 0
+    outs = []
+    for sb, _, _, _ in waves:
+        out = sb.results()
+        outs.append(out)
+        accepted_tokens += int(out["out_meta"][:, 0].sum())
+        kept_rows += int(out["out_meta"][:, 0].sum())
+    parity_checked = 0
+    if rank == 0:
+        from oracle import verify_oracle as vo
+
+        sb, logits, trees, ids = waves[0]
+        for b in range(min(4, wave)):
+            st = trees[b]
+            r = vo.verify(logits=logits[b].cpu(), token_ids=st.token_ids.tolist(), children=st.children(),
+                          method="lossy", threshold=LOSSY_KW["threshold"], window=LOSSY_KW["window_size"],
+                          threshold_method="entropy", upcast=True)
+            L = int(outs[0]["out_meta"][b, 0])
+            got = (outs[0]["out_tokens"][b, :L].tolist(), outs[0]["out_hidden"][b, :L].tolist())
+            if got != (r.tokens, r.hidden):
+                raise SystemExit(f"parity check failed on sequence {ids[b]}: {got} vs {(r.tokens, r.hidden)}")
+            parity_checked += 1
+
+    # ---- end-to-end: logits start in pinned host memory, results end in host memory ----
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = max(2, min(args.steps, 5))
+        host_logits = torch.empty(wave, NODES, VOCAB, dtype=torch.bfloat16).pin_memory()
+        host_logits.copy_(waves[0][1])
+        stage = [torch.empty_like(waves[0][1]) for _ in range(2)]
+        copy_stream, comp_stream = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        ready = [torch.cuda.Event() for _ in range(2)]
+        freed = [torch.cuda.Event() for _ in range(2)]
+
+        def e2e_step():
+            for i, (sb, _, _, _) in enumerate(waves):
+                s = i % 2
+                with torch.cuda.stream(copy_stream):
+                    copy_stream.wait_event(freed[s])
+                    stage[s].copy_(host_logits, non_blocking=True)
+                    ready[s].record(copy_stream)
+                with torch.cuda.stream(comp_stream):
+                    comp_stream.wait_event(ready[s])
+                    sb.verify(stage[s], verify_method="exact")
+                    sb.verify(stage[s], verify_method="lossy", verify_kwargs=LOSSY_KW)
+                    sb.compact_kv()
+                    freed[s].record(comp_stream)
+                    sb.ws._out_host.copy_(sb.ws._out_dev, non_blocking=True)
+            comp_stream.synchronize()
+
+        for _ in range(2):
+            e2e_step()
+        torch.cuda.synchronize()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        dt_e2e = time.perf_counter() - t0
+        barrier()
+        e2e = {"dt": dt_e2e, "steps": e2e_steps,
+               "h2d": n_waves * host_logits.numel() * 2, "d2h": n_waves * waves[0][0].ws._out_host.numel()}
+
+    # ---- gather (max over ranks of the times; sums of the counts) ----
+    stats = torch.tensor([ms_total, ms_exact, ms_lossy, ms_kv, e2e["dt"] if e2e else 0.0], device=device,
+                         dtype=torch.float64)
+    counts = torch.tensor([accepted_tokens, kept_rows], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(counts, op=dist.ReduceOp.SUM)
+    ms_total, ms_exact, ms_lossy, ms_kv, dt_e2e = stats.tolist()
+    accepted_tokens, kept_rows = counts.tolist()
+
+    if rank == 0:
+        peaks = {}
+        pk = ROOT / "MEASURED_PEAKS.json"
+        if pk.exists():
+            peaks = json.loads(pk.read_text())
+        peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+        peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s"
+        rows_bytes = wave * NODES * VOCAB * 2  # algorithmic bytes of one verify launch
+        achieved = rows_bytes / (ms_lossy * 1e-3) / 1e9
+        secs = ms_total * 1e-3
+        line = {
+            "metric": METRIC, "value": total * args.steps / secs, "unit": "steps/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, total, world, per_rank),
+            "accepted_tok_per_s": accepted_tokens * args.steps / secs,
+            "mean_tokens_per_step": accepted_tokens / total,
+            "kernels_ms": {"verify_exact": ms_exact, "verify_lossy": ms_lossy, "kv_compact": ms_kv,
+                           "per": f"launch over a wave of {wave} sequences"},
+            "roofline": {"bound": "hbm", "kernel": "verify_rows_kernel<bf16, logits, softmax+entropy> (lossy verify)",
+                         "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
+                         "peak_source": peak_src, "traffic": None,
+                         "exact_kernel_gbs": rows_bytes / (ms_exact * 1e-3) / 1e9,
+                         "kv_kernel_gbs": 2 * (kept_rows / (world * n_waves)) * waves[0][0].kv_row_bytes
+                         / (ms_kv * 1e-3) / 1e9},
+            "gpu_launches": args.steps * n_waves * 3,
+            "parity_checked_sequences": parity_checked,
+            "clocks": clocks.summary(),
+        }
+        if e2e:
+            line["e2e"] = {"value": total * e2e["steps"] / dt_e2e, "unit": "steps/s",
+                           "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                           "steps": e2e["steps"],
+                           "note": "per GPU and step; logits copied from pinned host memory wave by wave "
+                                   "(double-buffered), results read back to pinned host memory"}
+        if world == 1 and not args.no_cpu_baseline:
+            sample = args.cpu_sample or 8
+            v, desc = cpu_baseline(sample, 3, args.variant)
+            line["cpu_baseline"] = {"value": v, "unit": "steps/s", "cores": os.cpu_count(), "kind": "port",
+                                    "sample": desc}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -181,8 +181,10 @@ SUBSPEC_API int subspec_verify_batched(const subspec_verify_args* args, subspec_
  * One row is heads * head_dim elements and must be a multiple of 16 bytes.
  *
  * beam is [batch, max_beam] int32, strictly increasing with beam[i] >= i
- * (the verifier's out_hidden).  n may be a device array ([batch]) so that a
- * verify launch can feed this one without a host round trip.
+ * (the verifier's out_hidden).  offset, n and beam are device arrays, and n
+ * may be strided, so that a verify launch can feed this one without a host
+ * round trip: n = out_meta with n_stride = 4, beam = out_hidden with
+ * max_beam = max_out.
  * ---------------------------------------------------------------------- */
 typedef struct subspec_kv_paged_args {
   uint32_t struct_size;
@@ -197,9 +199,10 @@ typedef struct subspec_kv_paged_args {
   const int32_t* page_table; /* [batch, pages_per_seq] or NULL */
   int32_t pages_per_seq;
   const int32_t* offset; /* [batch] */
-  const int32_t* n;      /* [batch] rows kept */
+  const int32_t* n;      /* rows kept: n[b * n_stride] */
   const int64_t* beam;   /* [batch, max_beam] */
-  int32_t max_beam;      /* <= 64 */
+  int32_t max_beam;      /* row stride of beam */
+  int32_t n_stride;      /* elements between consecutive entries of n (0 is read as 1) */
   uint32_t* dev_status;
 } subspec_kv_paged_args;
 
@@ -221,9 +224,10 @@ typedef struct subspec_kv_hf_args {
   int64_t token_stride;
   void* const* layer_ptrs;
   const int32_t* offset; /* [batch] */
-  const int32_t* n;      /* [batch] */
+  const int32_t* n;      /* rows kept: n[b * n_stride] */
   const int64_t* beam;   /* [batch, max_beam] */
   int32_t max_beam;
+  int32_t n_stride;
   uint32_t* dev_status;
 } subspec_kv_hf_args;
 

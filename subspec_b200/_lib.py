@@ -60,7 +60,7 @@ class KvPagedArgs(C.Structure):
         ("struct_size", _u32), ("batch", _i32), ("layers", _i32), ("num_pages", _i32), ("page_len", _i32),
         ("heads", _i32), ("head_dim", _i32), ("elem_bytes", _i32), ("pool", _vp), ("page_table", _vp),
         ("pages_per_seq", _i32), ("offset", _vp), ("n", _vp), ("beam", _vp), ("max_beam", _i32),
-        ("dev_status", _vp),
+        ("n_stride", _i32), ("dev_status", _vp),
     ]
 
 
@@ -71,7 +71,7 @@ class KvHfArgs(C.Structure):
         ("struct_size", _u32), ("batch", _i32), ("num_tensors", _i32), ("heads", _i32), ("tokens", _i32),
         ("head_dim", _i32), ("elem_bytes", _i32), ("batch_stride", _i64), ("head_stride", _i64),
         ("token_stride", _i64), ("layer_ptrs", _vp), ("offset", _vp), ("n", _vp), ("beam", _vp),
-        ("max_beam", _i32), ("dev_status", _vp),
+        ("max_beam", _i32), ("n_stride", _i32), ("dev_status", _vp),
     ]
 
 

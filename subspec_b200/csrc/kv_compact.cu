@@ -111,7 +111,7 @@ template <typename Addr>
 __global__ void __launch_bounds__(32) kv_compact_kernel(const Addr ad, const int32_t* __restrict__ offset,
                                                         const int32_t* __restrict__ n_keep,
                                                         const int64_t* __restrict__ beam, int max_beam,
-                                                        uint32_t* dev_status) {
+                                                        int n_stride, uint32_t* dev_status) {
   extern __shared__ __align__(128) unsigned char stage[];
   __shared__ __align__(8) uint64_t bar;
 
@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(32) kv_compact_kernel(const Addr ad, const int
   const int b = blockIdx.x / groups;
   const int g = blockIdx.x - b * groups;
   const int lane = threadIdx.x;
-  int n = n_keep[b];
+  int n = n_keep[(size_t)b * n_stride];
   if (n > max_beam) {
     flag(dev_status, SUBSPEC_DEV_BAD_INDEX);
     n = max_beam;
@@ -210,7 +210,7 @@ extern "C" int subspec_kv_compact_paged(const subspec_kv_paged_args* args, subsp
     if (rc) return rc;
   }
   kv_compact_kernel<PagedAddr><<<(unsigned)grid, 32, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-      ad, a.offset, a.n, a.beam, a.max_beam, a.dev_status);
+      ad, a.offset, a.n, a.beam, a.max_beam, a.n_stride > 0 ? a.n_stride : 1, a.dev_status);
   return cuda_check(cudaGetLastError());
 }
 
@@ -231,6 +231,6 @@ extern "C" int subspec_kv_compact_hf(const subspec_kv_hf_args* args, subspec_str
   HfAddr ad{a, row_bytes};
   const size_t smem = row_bytes * kChunk;
   kv_compact_kernel<HfAddr><<<(unsigned)grid, 32, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-      ad, a.offset, a.n, a.beam, a.max_beam, a.dev_status);
+      ad, a.offset, a.n, a.beam, a.max_beam, a.n_stride > 0 ? a.n_stride : 1, a.dev_status);
   return cuda_check(cudaGetLastError());
 }

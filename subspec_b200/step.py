@@ -1,0 +1,86 @@
+"""Batched, device-resident speculative step: verify a batch of draft trees, then compact the accepted KV rows.
+
+This is the data-parallel form of the reference's per-request loop body
+(generators/classic_sd.py:225-257: `_verify` followed by
+`kv_reorder` / `reorder_cache_with_offset`): the reference asserts batch size 1
+and walks on the CPU between the two; here a batch of independent sequences goes
+through two kernel launches with no host round trip in between -- the verify
+kernel's `out_hidden` / `out_meta` feed the compaction kernel directly.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib, kv_cache
+from .verify import VerifyWorkspace, _gate_code, _method_code
+
+
+class SpeculativeStepBatch:
+    """`batch` independent sequences, each with a draft tree of up to `max_nodes` nodes and a paged KV region.
+
+    The KV pool is [layers, batch * pages_per_seq, 2, page_len, heads, head_dim];
+    `page_table[b]` lists the physical pages of sequence b.
+    """
+
+    def __init__(self, batch: int, max_nodes: int, device, *, kv_layers: int = 0, kv_heads: int = 4,
+                 head_dim: int = 128, page_len: int = 16, pages_per_seq: int = 0,
+                 kv_dtype: torch.dtype = torch.bfloat16, page_table: Optional[torch.Tensor] = None):
+        self.device = torch.device(device)
+        self.batch, self.max_nodes = int(batch), int(max_nodes)
+        self.ws = VerifyWorkspace(batch, max_nodes, self.device)
+        self.pool: Optional[torch.Tensor] = None
+        self.page_table: Optional[torch.Tensor] = None
+        self.kv_offset = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if kv_layers and pages_per_seq:
+            self.pool = torch.empty(kv_layers, batch * pages_per_seq, 2, page_len, kv_heads, head_dim,
+                                    dtype=kv_dtype, device=self.device)
+            if page_table is None:
+                page_table = torch.arange(batch * pages_per_seq, dtype=torch.int32).reshape(batch, pages_per_seq)
+            self.page_table = page_table.to(self.device, torch.int32).contiguous()
+
+    @property
+    def kv_row_bytes(self) -> int:
+        """Bytes of one token's K and V rows over all layers."""
+        L, _, _, _, H, D = self.pool.shape
+        return int(L * 2 * H * D * self.pool.element_size())
+
+    def set_trees(self, flats: Sequence) -> None:
+        self.ws.set_trees(flats)
+
+    def set_kv_offsets(self, offsets) -> None:
+        self.kv_offset.copy_(torch.as_tensor(offsets, dtype=torch.int32))
+
+    def verify(self, logits: torch.Tensor, *, verify_method: str = "exact", verify_kwargs: Optional[dict] = None,
+               eos_token_id: Optional[int] = None) -> None:
+        """Launch the fused verify kernel on the current stream (no synchronisation)."""
+        method = _method_code(verify_method)
+        vk = dict(verify_kwargs or {})
+        gate, threshold, window = _lib.GATE_PROB, 0.0, 1
+        if method == _lib.VERIFY_LOSSY:
+            gate = _gate_code(vk.get("threshold_method", "prob") or "prob")
+            threshold = float(vk.get("threshold", 0.0))
+            window = max(0, int(vk.get("window_size", 1)))
+        self.ws.run(logits, input_kind=_lib.IN_LOGITS, method=method, gate=gate, threshold=threshold, window=window,
+                    eos=eos_token_id)
+
+    def compact_kv(self) -> None:
+        """Move the accepted path's KV rows into place, reading the verify kernel's outputs on the device."""
+        if self.pool is None:
+            raise ValueError("this batch was created without a KV pool")
+        meta = self.ws.dev_view("out_meta")
+        beam = self.ws.dev_view("out_hidden").view(self.batch, self.ws.max_out)
+        kv_cache.compact_paged(self.pool, page_table=self.page_table, offset=self.kv_offset, n=meta, beam=beam,
+                               status=self.status, n_stride=4)
+
+    def results(self) -> Dict[str, np.ndarray]:
+        """Synchronise and fetch every verify output (tokens, hidden indices, lengths, per-node arrays)."""
+        out = self.ws.fetch()
+        word = int(self.status.item())
+        if word:
+            self.status.zero_()
+            raise ValueError("KV compaction rejected its input: " + _lib.dev_status_text(word))
+        return out

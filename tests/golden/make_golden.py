@@ -219,6 +219,41 @@ def gen_lossy_unit(ref, ref_root: str, out_dir: Path):
     print(f"lossy unit: {len(records)} recorded calls from {len(set(r['test'] for r in records))} reference tests")
 
 
+def gen_kv(ref, out_dir: Path):
+    """Reorder small pools with the reference's KvCachePool / RequestKvCache and store checksums."""
+    sys.path.insert(0, str(ROOT))
+    from oracle.kv_oracle import checksum
+    cm = ref["cm"]
+    cases = []
+    shapes = [(3, 8, 16, 4, 128, "bfloat16"), (2, 6, 8, 2, 64, "float16"), (1, 5, 4, 1, 8, "float32"),
+              (28, 16, 16, 4, 128, "bfloat16")]
+    seed = 300
+    for (L, P, page_len, H, D, dtype) in shapes:
+        for rep in range(3):
+            seed += 1
+            gen = torch.Generator().manual_seed(seed)
+            pool = cm.KvCachePool(P, L, H, D, page_len, DT[dtype], "cpu")
+            pool.cache_data.copy_(torch.randn(pool.cache_data.shape, generator=gen).to(DT[dtype]))
+            tokens = P * page_len
+            tree_n = min(24, tokens // 2)
+            offset = int(torch.randint(0, tokens - tree_n + 1, (1,), generator=gen))
+            n = int(torch.randint(1, min(11, tree_n) + 1, (1,), generator=gen))
+            beam = torch.sort(torch.randperm(tree_n - 1, generator=gen)[:n - 1] + 1).values
+            beam = torch.cat([torch.zeros(1, dtype=torch.long), beam]) if rep != 2 else \
+                torch.sort(torch.randperm(tree_n, generator=gen)[:n]).values
+            before = checksum(pool.cache_data)
+            # through the request object: callers pass kv_len + 1 and the callee subtracts 1
+            req = cm.RequestKvCache(pool, page_len, offset + tree_n)
+            req.reorder_cache_with_offset(beam, offset=offset + 1 if offset else 0)
+            cases.append(dict(seed=seed, layers=L, pages=P, page_len=page_len, heads=H, head_dim=D, dtype=dtype,
+                              offset=offset, tree_n=tree_n, beam=beam.tolist(), before=before,
+                              after=checksum(pool.cache_data), kv_len=req.kv_len,
+                              kv_last_page_len=req.kv_last_page_len, n_pages=len(req.kv_page_indices),
+                              free_pages=int(pool.num_free_pages())))
+    (out_dir / "kv_cases.json").write_text(json.dumps({"cases": cases}, indent=1))
+    print(f"kv: {len(cases)} cases")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -228,6 +263,8 @@ def main():
     torch.set_num_threads(8)
     if args.only in (None, "verify"):
         gen_verify(ref, HERE)
+    if args.only in (None, "kv"):
+        gen_kv(ref, HERE)
     if args.only in (None, "lossy_unit"):
         gen_lossy_unit(ref, args.reference, HERE)
 

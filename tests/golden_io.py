@@ -49,3 +49,15 @@ def verify_input(case):
 @lru_cache(maxsize=None)
 def lossy_unit_cases():
     return json.loads((GOLDEN / "lossy_unit_cases.json").read_text())["cases"]
+
+
+@lru_cache(maxsize=None)
+def kv_cases():
+    return json.loads((GOLDEN / "kv_cases.json").read_text())["cases"]
+
+
+def kv_pool(case) -> torch.Tensor:
+    """The pool contents the golden generator started from (same seed, same draw order)."""
+    gen = torch.Generator().manual_seed(case["seed"])
+    shape = (case["layers"], case["pages"], 2, case["page_len"], case["heads"], case["head_dim"])
+    return torch.randn(shape, generator=gen).to(DT[case["dtype"]])

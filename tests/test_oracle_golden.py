@@ -64,3 +64,30 @@ def test_inverse_cdf_pick_edges():
     assert vo.inverse_cdf_pick(row, 0.25) == 3
     assert vo.inverse_cdf_pick(row, 0.9999999) == 4
     assert vo.inverse_cdf_pick(row, 1.0) == 4
+
+
+def test_kv_oracle_matches_reference_pool_reorder():
+    from oracle import kv_oracle as ko
+
+    cases = golden_io.kv_cases()
+    assert len(cases) >= 12
+    for c in cases:
+        pool = golden_io.kv_pool(c)
+        assert ko.checksum(pool) == c["before"]
+        ko.paged_reorder(pool, torch.tensor(c["beam"]), c["offset"])
+        assert ko.checksum(pool) == c["after"], c["seed"]
+
+
+def test_kv_oracle_page_table_is_consistent_with_identity():
+    from oracle import kv_oracle as ko
+
+    gen = torch.Generator().manual_seed(9)
+    pool = torch.randn(2, 6, 2, 4, 2, 8, generator=gen)
+    ident = pool.clone()
+    ko.paged_reorder(ident, torch.tensor([0, 3, 4, 9]), 5)
+    # scatter the logical pages over physical pages with a permutation, reorder, and undo the permutation
+    perm = torch.tensor([4, 0, 5, 2, 1, 3])
+    phys = torch.empty_like(pool)
+    phys[:, perm] = pool
+    ko.paged_reorder(phys, torch.tensor([0, 3, 4, 9]), 5, page_table=perm.tolist())
+    assert torch.equal(phys[:, perm], ident)

