@@ -35,6 +35,7 @@ typedef void* subspec_stream_t; /* a cudaStream_t; NULL = legacy default stream 
 #define SUBSPEC_EUNSUPPORTED (-2) /* shape outside the supported range */
 #define SUBSPEC_ECUDA (-3)        /* a CUDA runtime call failed; see subspec_last_cuda_error */
 #define SUBSPEC_ESCRATCH (-4)     /* scratch buffer too small / misaligned */
+#define SUBSPEC_ETOOLARGE (-5)    /* batch * max_nodes exceeds SUBSPEC_STATIC_SCRATCH_MAX_ROWS */
 
 /* element types of logits / probabilities / KV rows */
 #define SUBSPEC_F32 0
@@ -160,6 +161,40 @@ typedef struct subspec_verify_args {
 
 SUBSPEC_API int subspec_verify_scratch_bytes(int32_t batch, int32_t max_nodes, size_t* bytes);
 SUBSPEC_API int subspec_verify_batched(const subspec_verify_args* args, subspec_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * subspec_verify_batched without any allocation on the caller's side.
+ * (No counterpart in the reference: it exists for hosts of this library.)
+ *
+ * Some programs that embed the verifier have no way to produce the scratch
+ * buffer subspec_verify_batched asks for: a serving loop that handed all of
+ * HBM to its KV pool and weight arena at start-up and may not call cudaMalloc
+ * afterwards, or a thin foreign-language binding that owns its input and
+ * output buffers but has no device allocator at hand.  For them this entry
+ * point runs the same kernel with its scratch (row tickets and split
+ * partials) in an array that is part of the library image: a file-scope
+ * device array of about 2.7 MB that every GPU loading the library holds until
+ * the process ends.  It calls no cudaMalloc / cudaFree and no allocating
+ * library routine.  `args->scratch` and `args->scratch_bytes` are ignored;
+ * every other field means what it means for subspec_verify_batched, and the
+ * results are identical.
+ *
+ * Limit: batch * max_nodes <= SUBSPEC_STATIC_SCRATCH_MAX_ROWS (for example 64
+ * sequences of 64-node trees, or 4 trees of 1024 nodes).  Larger launches
+ * return SUBSPEC_ETOOLARGE and do nothing; split the batch or use
+ * subspec_verify_batched with a caller-owned buffer.
+ *
+ * The first call on each device looks up the array's device address (with that
+ * device current) and remembers it; make that first call outside any stream
+ * capture.  All calls on a device share the one array.  It keeps whatever the
+ * previous call left there; the part that must start at zero (the tickets) is
+ * cleared on the stream at the start of every call.  Two calls whose kernels
+ * can overlap on the same GPU (different streams, or different host threads)
+ * race on it and give wrong results: serialise them, or give the concurrent
+ * ones their own buffer through subspec_verify_batched.
+ * ---------------------------------------------------------------------- */
+#define SUBSPEC_STATIC_SCRATCH_MAX_ROWS 4096
+SUBSPEC_API int subspec_verify_batched_static_scratch(const subspec_verify_args* args, subspec_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * Accepted-path KV compaction.

@@ -10,7 +10,8 @@ from pathlib import Path
 
 _LIB_PATH = Path(__file__).resolve().parent / "lib" / "libsubspec_b200.so"
 
-OK, EINVAL, EUNSUPPORTED, ECUDA, ESCRATCH = 0, -1, -2, -3, -4
+OK, EINVAL, EUNSUPPORTED, ECUDA, ESCRATCH, ETOOLARGE = 0, -1, -2, -3, -4, -5
+STATIC_SCRATCH_MAX_ROWS = 4096
 F32, BF16, F16 = 0, 1, 2
 IN_LOGITS, IN_PROBS = 0, 1
 VERIFY_EXACT, VERIFY_LOSSY = 0, 1
@@ -22,6 +23,7 @@ _STATUS_TEXT = {
     EUNSUPPORTED: "unsupported shape",
     ECUDA: "CUDA error",
     ESCRATCH: "scratch buffer too small or misaligned",
+    ETOOLARGE: "batch * max_nodes exceeds the built-in scratch of the no-allocation entry point (4096 rows)",
 }
 
 _DEV_TEXT = {
@@ -81,6 +83,7 @@ SYMBOLS = {
     "subspec_last_cuda_error": (C.c_char_p, []),
     "subspec_verify_scratch_bytes": (C.c_int, [_i32, _i32, C.POINTER(C.c_size_t)]),
     "subspec_verify_batched": (C.c_int, [C.POINTER(VerifyArgs), _vp]),
+    "subspec_verify_batched_static_scratch": (C.c_int, [C.POINTER(VerifyArgs), _vp]),
     "subspec_kv_compact_paged": (C.c_int, [C.POINTER(KvPagedArgs), _vp]),
     "subspec_kv_compact_hf": (C.c_int, [C.POINTER(KvHfArgs), _vp]),
 }
@@ -120,7 +123,7 @@ def check(rc: int, what: str) -> None:
     msg = _STATUS_TEXT.get(rc, f"status {rc}")
     if rc == ECUDA:
         msg += ": " + lib().subspec_last_cuda_error().decode()
-    if rc in (EINVAL, EUNSUPPORTED, ESCRATCH):
+    if rc in (EINVAL, EUNSUPPORTED, ESCRATCH, ETOOLARGE):
         raise ValueError(f"{what}: {msg}")
     raise SubspecError(f"{what}: {msg}")
 

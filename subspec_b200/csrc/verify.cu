@@ -752,3 +752,43 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
   }
   return cuda_check(e);
 }
+
+// ---- no-allocation variant -------------------------------------------------------
+// Scratch for subspec_verify_batched_static_scratch: room for the tickets and split
+// partials of up to SUBSPEC_STATIC_SCRATCH_MAX_ROWS tree nodes per launch.  The array is
+// part of the library image, so every GPU that loads the library holds it until the
+// process exits.
+namespace subspec {
+namespace {
+constexpr size_t kStaticRows = SUBSPEC_STATIC_SCRATCH_MAX_ROWS;
+constexpr size_t kStaticScratchBytes =
+    (sizeof(int) * 2 * kStaticRows + 255) / 256 * 256 + sizeof(RowStat) * kStaticRows * kMaxSplits;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {};  // device address of g_static_scratch, per device ordinal
+}  // namespace
+}  // namespace subspec
+
+extern "C" int subspec_verify_batched_static_scratch(const subspec_verify_args* args, subspec_stream_t stream) {
+  if (!args || args->struct_size != sizeof(subspec_verify_args)) return SUBSPEC_EINVAL;
+  if (args->batch < 0 || args->max_nodes < 1) return SUBSPEC_EINVAL;
+  if ((int64_t)args->batch * args->max_nodes > (int64_t)kStaticRows) return SUBSPEC_ETOOLARGE;
+  int dev = -1;
+  int rc = cuda_check(cudaGetDevice(&dev));
+  if (rc) return rc;
+  if (dev < 0 || dev >= kMaxDevices) return SUBSPEC_EUNSUPPORTED;
+  if (!g_static_scratch_ptr[dev]) {
+    // In host code `g_static_scratch` is only a handle for the symbol; the address a kernel can use
+    // has to be asked for, with the device that will run the kernel current.
+    void* p = nullptr;
+    rc = cuda_check(cudaGetSymbolAddress(&p, g_static_scratch));
+    if (rc) return rc;
+    if (!p || (reinterpret_cast<uintptr_t>(p) & 255u)) return SUBSPEC_ESCRATCH;
+    g_static_scratch_ptr[dev] = p;
+  }
+  subspec_verify_args a = *args;
+  a.scratch = g_static_scratch_ptr[dev];
+  a.scratch_bytes = kStaticScratchBytes;
+  return subspec_verify_batched(&a, stream);
+}
