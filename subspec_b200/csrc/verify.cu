@@ -18,6 +18,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace subspec {
 namespace {
@@ -25,6 +26,9 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kUnroll = 4;
+constexpr int kStageVecs = kThreads * kUnroll;  // 16-byte vectors per TMA stage: one group per thread
+constexpr int kStageBytes = kStageVecs * 16;    // 16 KB
+constexpr int kStages = 4;                      // shared-memory ring depth
 constexpr int kMaxSplits = 32;
 constexpr int kMaxNodes = 1024;
 
@@ -84,73 +88,126 @@ __device__ __forceinline__ RowStat warp_reduce(RowStat v) {
   return v;
 }
 
+// ---- packed fp32x2 arithmetic (sm_100: two fp32 lanes per instruction) -------------------
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// Headroom (log2 domain) a new row maximum may have over the thread's reference shift
+// before the accumulators are rescaled: 2^64 * vocab still sits far below FLT_MAX.
+constexpr float kRefHeadroom = 64.f;
+
 // Per-thread accumulator.  SOFT = false keeps only the argmax.
+//
+// Logits mode keeps S = sum 2^y and T2 = sum y * 2^y with y = x * k - c in packed fp32x2
+// lanes (even / odd elements).  The shift c is taken from the first maximum the thread
+// meets and only moves when a later maximum exceeds it by kRefHeadroom; any c gives the
+// same entropy and probabilities, it just has to keep 2^y inside the fp32 range.
 template <int KIND, bool SOFT>
 struct Acc {
-  float c, s0, s1, t0, t1, vmax, k;
-  int amax;
+  uint64_t s2, t2, k2, nc2;  // packed: (even, odd) lanes
+  float c, vmax, k;
+  // Where vmax was first met: rec >= 0 is the first vector index of a group of kUnroll vectors
+  // (the position inside the group is looked up once, after streaming, by the threads that hold
+  // the row maximum); rec < 0 is ~element_index, recorded exactly by the scalar path.
+  int rec;
 
   __device__ __forceinline__ void init(float k_) {
     k = k_;
+    k2 = f2_pack(k_, k_);
     c = (KIND == SUBSPEC_IN_PROBS) ? 0.f : -INFINITY;
-    s0 = s1 = t0 = t1 = 0.f;
+    nc2 = f2_pack(-c, -c);
+    s2 = t2 = f2_pack(0.f, 0.f);
     vmax = -INFINITY;
-    amax = INT_MAX;
+    rec = ~INT_MAX;
   }
 
-  // A new running maximum `m` first seen at element `idx`.
-  __device__ __forceinline__ void raise(float m, int idx) {
-    vmax = m;
-    amax = idx;
+  __device__ __forceinline__ void set_ref(float cn) {
+    c = cn;
+    nc2 = f2_pack(-cn, -cn);
+  }
+
+  // Move the shift to cn (first use, or a maximum that outgrew the headroom).
+  __device__ __forceinline__ void move_ref(float cn) {
+    if (c != -INFINITY) {
+      const float d = c - cn;
+      const float f = ex2f(d);
+      float s0, s1, t0, t1;
+      f2_unpack(s2, s0, s1);
+      f2_unpack(t2, t0, t1);
+      t2 = f2_pack(f * fmaf(d, s0, t0), f * fmaf(d, s1, t1));
+      s2 = f2_pack(s0 * f, s1 * f);
+    }
+    set_ref(cn);
+  }
+
+  // Maximum `gm` of a group of vectors starting at vector index v0: branch-free bookkeeping.
+  __device__ __forceinline__ void note_group(float gm, int v0) {
+    const bool up = gm > vmax;
+    vmax = up ? gm : vmax;
+    rec = up ? v0 : rec;
     if (SOFT && KIND == SUBSPEC_IN_LOGITS) {
-      const float cn = m * k;
-      if (c != -INFINITY) {
-        const float d = c - cn;
-        const float f = ex2f(d);
-        t0 = f * fmaf(d, s0, t0);
-        t1 = f * fmaf(d, s1, t1);
-        s0 *= f;
-        s1 *= f;
-      }
-      c = cn;
+      if (fmaf(gm, k, -c) > kRefHeadroom) move_ref(gm * k);  // first group of the thread; otherwise almost never
     }
   }
 
-  // One element whose value is known to be <= vmax (finite, clamped).
-  template <int LANE>
-  __device__ __forceinline__ void add(float x) {
+  // Two logits (finite, reference already set).
+  __device__ __forceinline__ void add_pair(float x0, float x1) {
+    const uint64_t y2 = f2_fma(f2_pack(x0, x1), k2, nc2);
+    float y0, y1;
+    f2_unpack(y2, y0, y1);
+    const uint64_t e2 = f2_pack(ex2f(y0), ex2f(y1));
+    s2 = f2_add(s2, e2);
+    t2 = f2_fma(y2, e2, t2);
+  }
+
+  // One value through the scalar path (probabilities, unaligned rows, tails, masked logits).
+  __device__ __forceinline__ void one(float x, int idx) {
+    if (KIND == SUBSPEC_IN_LOGITS) x = fmaxf(x, -1.0e30f);  // -inf (masked) must not turn 0 * inf into NaN
+    if (x > vmax) {
+      vmax = x;
+      rec = ~idx;
+      if (SOFT && KIND == SUBSPEC_IN_LOGITS && fmaf(x, k, -c) > kRefHeadroom) move_ref(x * k);
+    }
     if (!SOFT) return;
+    float s0, s1, t0, t1;
+    f2_unpack(s2, s0, s1);
+    f2_unpack(t2, t0, t1);
     if (KIND == SUBSPEC_IN_LOGITS) {
       const float y = fmaf(x, k, -c);
       const float e = ex2f(y);
-      if (LANE & 1) {
-        s1 += e;
-        t1 = fmaf(y, e, t1);
-      } else {
-        s0 += e;
-        t0 = fmaf(y, e, t0);
-      }
+      s0 += e;
+      t0 = fmaf(y, e, t0);
     } else {
       const float l = x > 0.f ? lg2f(x) : 0.f;
-      if (LANE & 1) {
-        s1 += x;
-        t1 = fmaf(x, l, t1);
-      } else {
-        s0 += x;
-        t0 = fmaf(x, l, t0);
-      }
+      s0 += x;
+      t0 = fmaf(x, l, t0);
     }
+    s2 = f2_pack(s0, s1);
+    t2 = f2_pack(t0, t1);
   }
 
-  // Generic scalar path (unaligned rows, tails).
-  __device__ __forceinline__ void one(float x, int idx) {
-    if (KIND == SUBSPEC_IN_LOGITS) x = fmaxf(x, -1.0e30f);
-    if (x > vmax) raise(x, idx);
-    add<0>(x);
-  }
-
-  __device__ __forceinline__ RowStat stat() const {
+  // `amax`: exact first index of vmax for this thread (INT_MAX when the thread cannot hold the row maximum).
+  __device__ __forceinline__ RowStat stat(int amax) const {
     RowStat r;
+    float s0, s1, t0, t1;
+    f2_unpack(s2, s0, s1);
+    f2_unpack(t2, t0, t1);
     r.c = (vmax == -INFINITY && KIND == SUBSPEC_IN_LOGITS) ? -INFINITY : c;
     r.s = s0 + s1;
     r.t2 = t0 + t1;
@@ -160,73 +217,77 @@ struct Acc {
   }
 };
 
-// ---- 16-byte vector consumers -------------------------------------------------
+// ---- consumers of a group of kUnroll 16-byte vectors ----------------------------------------
+// The group maximum is formed with packed 16-bit max instructions and compared with the
+// running maximum once per group; only when it wins (a handful of times per thread) is the
+// group searched for the first position of that value.  Vectors of a group are kThreads
+// vectors apart and ascending, so "first in the group" is "lowest vocabulary index".
 template <typename T>
 struct Vec;
 
 template <>
 struct Vec<float> {
   static constexpr int N = 4;
+  // Element index of the first value equal to gm in the group of vectors v0, v0 + kThreads, ...
+  static __device__ __noinline__ int first_of(const uint4* vp, int v0, float gm) {
+    for (int j = 0; j < kUnroll; ++j) {
+      const uint4 q = vp[v0 + j * kThreads];
+      const float x[4] = {__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w)};
+      for (int i = 0; i < 4; ++i)
+        if (x[i] == gm) return (v0 + j * kThreads) * N + i;
+    }
+    return INT_MAX;
+  }
   template <int KIND, bool SOFT>
-  static __device__ __forceinline__ void consume(Acc<KIND, SOFT>& a, const uint4& q, int base) {
-    float x[4] = {__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w)};
-    if (KIND == SUBSPEC_IN_LOGITS) {
+  static __device__ __forceinline__ void consume(Acc<KIND, SOFT>& a, const uint4 (&q)[kUnroll], int v0) {
+    float gm = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) x[i] = fmaxf(x[i], -1.0e30f);
-    }
-    const float vm = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
-    if (vm > a.vmax) {
-      int j = 0;
+    for (int j = 0; j < kUnroll; ++j)
+      gm = fmaxf(gm, fmaxf(fmaxf(__uint_as_float(q[j].x), __uint_as_float(q[j].y)),
+                           fmaxf(__uint_as_float(q[j].z), __uint_as_float(q[j].w))));
+    a.note_group(gm, v0);
+    if (SOFT) {
 #pragma unroll
-      for (int i = 3; i >= 0; --i)
-        if (x[i] == vm) j = i;
-      a.raise(vm, base + j);
+      for (int j = 0; j < kUnroll; ++j) {
+        a.add_pair(__uint_as_float(q[j].x), __uint_as_float(q[j].y));
+        a.add_pair(__uint_as_float(q[j].z), __uint_as_float(q[j].w));
+      }
     }
-    a.template add<0>(x[0]);
-    a.template add<1>(x[1]);
-    a.template add<0>(x[2]);
-    a.template add<1>(x[3]);
   }
 };
 
 template <>
 struct Vec<__nv_bfloat16> {
   static constexpr int N = 8;
-  template <int KIND, bool SOFT>
-  static __device__ __forceinline__ void consume(Acc<KIND, SOFT>& a, const uint4& q, int base) {
-    uint32_t w[4] = {q.x, q.y, q.z, q.w};
-    __nv_bfloat162 h[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      h[i] = *reinterpret_cast<__nv_bfloat162*>(&w[i]);
-      if (KIND == SUBSPEC_IN_LOGITS) {
-        // -1.0e30 is finite in bf16 and stays finite after scaling; this turns -inf (masked logits) into a
-        // value whose exponential flushes to zero without producing NaN.
-        h[i] = __hmax2(h[i], __floats2bfloat162_rn(-1.0e30f, -1.0e30f));
-        w[i] = *reinterpret_cast<uint32_t*>(&h[i]);
+  static __device__ __noinline__ int first_of(const uint4* vp, int v0, float gm) {
+    for (int j = 0; j < kUnroll; ++j) {
+      const uint4 q = vp[v0 + j * kThreads];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      for (int i = 0; i < 4; ++i) {
+        if (__uint_as_float(w[i] << 16) == gm) return (v0 + j * kThreads) * N + 2 * i;
+        if (__uint_as_float(w[i] & 0xffff0000u) == gm) return (v0 + j * kThreads) * N + 2 * i + 1;
       }
     }
-    const __nv_bfloat162 m2 = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
-    const float vm = fmaxf(__low2float(m2), __high2float(m2));
-    float x[8];
+    return INT_MAX;
+  }
+  template <int KIND, bool SOFT>
+  static __device__ __forceinline__ void consume(Acc<KIND, SOFT>& a, const uint4 (&q)[kUnroll], int v0) {
+    __nv_bfloat162 m[kUnroll];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      x[2 * i] = __uint_as_float(w[i] << 16);
-      x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    for (int j = 0; j < kUnroll; ++j) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q[j]);
+      m[j] = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
     }
-    if (vm > a.vmax) {
-      int j = 0;
+    const __nv_bfloat162 m2 = __hmax2(__hmax2(m[0], m[1]), __hmax2(m[2], m[3]));
+    const float gm = fmaxf(__low2float(m2), __high2float(m2));
+    a.note_group(gm, v0);
+    if (SOFT) {
 #pragma unroll
-      for (int i = 7; i >= 0; --i)
-        if (x[i] == vm) j = i;
-      a.raise(vm, base + j);
-    }
+      for (int j = 0; j < kUnroll; ++j) {
+        const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (i & 1)
-        a.template add<1>(x[i]);
-      else
-        a.template add<0>(x[i]);
+        for (int i = 0; i < 4; ++i) a.add_pair(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+      }
     }
   }
 };
@@ -234,37 +295,39 @@ struct Vec<__nv_bfloat16> {
 template <>
 struct Vec<__half> {
   static constexpr int N = 8;
+  static __device__ __noinline__ int first_of(const uint4* vp, int v0, float gm) {
+    for (int j = 0; j < kUnroll; ++j) {
+      const uint4 q = vp[v0 + j * kThreads];
+      const __half2* h = reinterpret_cast<const __half2*>(&q);
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        if (f.x == gm) return (v0 + j * kThreads) * N + 2 * i;
+        if (f.y == gm) return (v0 + j * kThreads) * N + 2 * i + 1;
+      }
+    }
+    return INT_MAX;
+  }
   template <int KIND, bool SOFT>
-  static __device__ __forceinline__ void consume(Acc<KIND, SOFT>& a, const uint4& q, int base) {
-    uint32_t w[4] = {q.x, q.y, q.z, q.w};
-    __half2 h[4];
+  static __device__ __forceinline__ void consume(Acc<KIND, SOFT>& a, const uint4 (&q)[kUnroll], int v0) {
+    __half2 m[kUnroll];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      h[i] = *reinterpret_cast<__half2*>(&w[i]);
-      if (KIND == SUBSPEC_IN_LOGITS) h[i] = __hmax2(h[i], __floats2half2_rn(-65504.f, -65504.f));
+    for (int j = 0; j < kUnroll; ++j) {
+      const __half2* h = reinterpret_cast<const __half2*>(&q[j]);
+      m[j] = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
     }
-    const __half2 m2 = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
-    const float vm = fmaxf(__low2float(m2), __high2float(m2));
-    float x[8];
+    const __half2 m2 = __hmax2(__hmax2(m[0], m[1]), __hmax2(m[2], m[3]));
+    const float gm = fmaxf(__low2float(m2), __high2float(m2));
+    a.note_group(gm, v0);
+    if (SOFT) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = __half22float2(h[i]);
-      x[2 * i] = f.x;
-      x[2 * i + 1] = f.y;
-    }
-    if (vm > a.vmax) {
-      int j = 0;
+      for (int j = 0; j < kUnroll; ++j) {
+        const __half2* h = reinterpret_cast<const __half2*>(&q[j]);
 #pragma unroll
-      for (int i = 7; i >= 0; --i)
-        if (x[i] == vm) j = i;
-      a.raise(vm, base + j);
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (i & 1)
-        a.template add<1>(x[i]);
-      else
-        a.template add<0>(x[i]);
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __half22float2(h[i]);
+          a.add_pair(f.x, f.y);
+        }
+      }
     }
   }
 };
@@ -520,11 +583,30 @@ __device__ void run_walk(const KArgs& ka, int b, unsigned char* smem_raw) {
   }
 }
 
+// CTA-wide combine of the per-thread statistics into *out (shared memory); ends with a barrier.
+template <int KIND>
+__device__ __forceinline__ void block_reduce(RowStat st, RowStat* s_warp, RowStat* out) {
+  st = warp_reduce(st);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();  // s_warp / *out may still be read from a previous round
+  if (lane == 0) s_warp[warp] = st;
+  __syncthreads();
+  if (warp == 0) {
+    st = lane < kWarps ? s_warp[lane] : empty_stat(KIND == SUBSPEC_IN_PROBS);
+    st = warp_reduce(st);
+    if (lane == 0) *out = st;
+  }
+  __syncthreads();
+}
+
 // ---- the streaming kernel --------------------------------------------------------
 template <typename T, int KIND, bool SOFT>
-__global__ void __launch_bounds__(kThreads, 4) verify_rows_kernel(const KArgs ka) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+__global__ void __launch_bounds__(kThreads, 3) verify_rows_kernel(const KArgs ka) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ RowStat s_warp[kWarps];
+  __shared__ float s_max[kWarps];
+  __shared__ __align__(8) uint64_t s_full[kStages];
+  __shared__ int s_abort;
   __shared__ RowStat s_row;
   __shared__ int s_flag;
 
@@ -549,37 +631,83 @@ __global__ void __launch_bounds__(kThreads, 4) verify_rows_kernel(const KArgs ka
   const int vec_per_split = (nvec_total + splits - 1) / splits;
   const int v0 = min(split * vec_per_split, nvec_total);
   const int v1 = min(v0 + vec_per_split, nvec_total);
-  {
+  static_assert(kUnroll == 4, "the group consumers take four vectors");
+  if (KIND == SUBSPEC_IN_LOGITS) {
+    // The chunk [v0, v1) is staged through a ring of kStages shared-memory buffers by TMA bulk
+    // copies that thread 0 issues kStages - 1 stages ahead; every thread then reads its group of
+    // kUnroll vectors (kThreads apart, ascending) from shared memory.  The barrier at the top of
+    // iteration k proves that stage k - 1 has been read by everyone, so its buffer is refilled.
     const uint4* vp = reinterpret_cast<const uint4*>(rowp);
-    int i = v0 + threadIdx.x;
-    for (; i + (kUnroll - 1) * kThreads < v1; i += kUnroll * kThreads) {
-      uint4 q[kUnroll];
-#pragma unroll
-      for (int j = 0; j < kUnroll; ++j) q[j] = ld_stream_u4(vp + i + j * kThreads);
-#pragma unroll
-      for (int j = 0; j < kUnroll; ++j) Vec<T>::template consume<KIND, SOFT>(acc, q[j], (i + j * kThreads) * VN);
+    uint4* ring = reinterpret_cast<uint4*>(smem_raw);
+    const int nst = (v1 - v0 + kStageVecs - 1) / kStageVecs;
+    if (threadIdx.x == 0) {
+      for (int st = 0; st < kStages; ++st) mbar_init(&s_full[st], 1);
+      mbar_init_fence();
+      s_abort = 0;
     }
-    for (; i < v1; i += kThreads) {
-      const uint4 q = ld_stream_u4(vp + i);
-      Vec<T>::template consume<KIND, SOFT>(acc, q, i * VN);
+    fence_async_smem();
+    __syncthreads();
+    auto issue = [&](int st) {
+      const int a0 = v0 + st * kStageVecs;
+      const uint32_t bytes = (uint32_t)(min(kStageVecs, v1 - a0) * 16);
+      uint64_t* bar = &s_full[st % kStages];
+      mbar_expect_tx(bar, bytes);
+      bulk_g2s(ring + (size_t)(st % kStages) * kStageVecs, vp + a0, bytes, bar);
+    };
+    if (threadIdx.x == 0)
+      for (int st = 0; st < kStages - 1 && st < nst; ++st) issue(st);
+    for (int st = 0; st < nst; ++st) {
+      __syncthreads();
+      if (s_abort) break;
+      if (threadIdx.x == 0 && st + kStages - 1 < nst) issue(st + kStages - 1);
+      if (!mbar_wait_bounded(&s_full[st % kStages], (uint32_t)(st / kStages) & 1u)) s_abort = 1;
+      const uint4* buf = ring + (size_t)(st % kStages) * kStageVecs;
+      const int a0 = v0 + st * kStageVecs;
+      const int i = a0 + threadIdx.x;
+      if (a0 + kStageVecs <= v1) {
+        uint4 q[kUnroll];
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) q[j] = buf[threadIdx.x + j * kThreads];
+        Vec<T>::template consume<KIND, SOFT>(acc, q, i);
+      } else {
+        // last, partial stage: its vectors go element by element through the scalar path
+        for (int j = 0; j < kUnroll && i + j * kThreads < v1; ++j) {
+          const uint4 q = buf[threadIdx.x + j * kThreads];
+          const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+          for (int l = 0; l < VN; ++l) acc.one(to_f32<T>(e[l]), (i + j * kThreads) * VN + l);
+        }
+      }
     }
+    __syncthreads();
+    if (s_abort) {  // a bulk copy never completed: report and leave together
+      if (threadIdx.x == 0) flag(a.dev_status, SUBSPEC_DEV_TIMEOUT);
+      return;
+    }
+  } else {
+    for (int i = v0 * VN + threadIdx.x; i < v1 * VN; i += kThreads) acc.one(to_f32<T>(rowp[i]), i);
   }
   // scalar remainder (and the whole row when it is not 16-byte aligned): last split only
   if (split == splits - 1) {
     for (int i = nvec_total * VN + threadIdx.x; i < V; i += kThreads) acc.one(to_f32<T>(rowp[i]), i);
   }
 
-  // CTA reduction
-  RowStat st = warp_reduce(acc.stat());
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane == 0) s_warp[warp] = st;
-  __syncthreads();
-  if (warp == 0) {
-    st = lane < kWarps ? s_warp[lane] : empty_stat(KIND == SUBSPEC_IN_PROBS);
-    st = warp_reduce(st);
-    if (lane == 0) s_row = st;
+  // Row (chunk) maximum first; only the threads that hold it look up where in their group it sits.
+  {
+    float m = acc.vmax;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if (lane == 0) s_max[warp] = m;
+    __syncthreads();
+    m = s_max[0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) m = fmaxf(m, s_max[w]);
+    int amax = INT_MAX;
+    if (acc.vmax == m && m != -INFINITY)
+      amax = acc.rec < 0 ? ~acc.rec : Vec<T>::first_of(reinterpret_cast<const uint4*>(rowp), acc.rec, m);
+    block_reduce<KIND>(acc.stat(amax), s_warp, &s_row);
   }
-  __syncthreads();
 
   if (splits > 1) {
     if (threadIdx.x == 0) {
@@ -605,6 +733,15 @@ __global__ void __launch_bounds__(kThreads, 4) verify_rows_kernel(const KArgs ka
       if (lane == 0) s_row = p;
     }
     __syncthreads();
+  }
+
+  // A -inf (masked) logit makes the fast path produce 0 * inf = NaN.  Such rows are rare on this
+  // path; the CTA that finalises the row streams it once more through the clamping scalar path.
+  if (SOFT && KIND == SUBSPEC_IN_LOGITS && !(isfinite(s_row.s) && isfinite(s_row.t2))) {
+    __syncthreads();
+    acc.init(ka.k);
+    for (int i = threadIdx.x; i < V; i += kThreads) acc.one(to_f32<T>(rowp[i]), i);
+    block_reduce<KIND>(acc.stat(acc.rec == ~INT_MAX ? INT_MAX : ~acc.rec), s_warp, &s_row);
   }
 
   // ---- finalise the row ----
@@ -662,7 +799,13 @@ template <typename T>
 cudaError_t launch_rows(const KArgs& ka, int grid, size_t smem, cudaStream_t st) {
   const bool soft = ka.a.method == SUBSPEC_VERIFY_LOSSY;
   const bool probs = ka.a.input_kind == SUBSPEC_IN_PROBS;
-#define SUBSPEC_LAUNCH(KIND, SOFT) verify_rows_kernel<T, KIND, SOFT><<<grid, kThreads, smem, st>>>(ka)
+#define SUBSPEC_LAUNCH(KIND, SOFT)                                                                        \
+  do {                                                                                                    \
+    cudaError_t e_ = cudaFuncSetAttribute(verify_rows_kernel<T, KIND, SOFT>,                              \
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+    if (e_ != cudaSuccess) return e_;                                                                     \
+    verify_rows_kernel<T, KIND, SOFT><<<grid, kThreads, smem, st>>>(ka);                                  \
+  } while (0)
   if (probs) {
     if (soft)
       SUBSPEC_LAUNCH(SUBSPEC_IN_PROBS, true);
@@ -678,7 +821,12 @@ cudaError_t launch_rows(const KArgs& ka, int grid, size_t smem, cudaStream_t st)
   return cudaGetLastError();
 }
 
-size_t walk_smem_bytes(int max_nodes) { return sizeof(int) * (9 * (size_t)max_nodes + 1); }
+// Dynamic shared memory: the TMA ring while streaming, reused for the walk's tree arrays afterwards.
+size_t kernel_smem_bytes(int max_nodes) {
+  const size_t walk = sizeof(int) * (9 * (size_t)max_nodes + 1);
+  const size_t ring = (size_t)kStages * kStageBytes;
+  return walk > ring ? walk : ring;
+}
 
 }  // namespace
 }  // namespace subspec
@@ -737,7 +885,7 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
   int rc = cuda_check(cudaMemsetAsync(a.scratch, 0, ticket_bytes(a.batch, a.max_nodes), st));
   if (rc) return rc;
   const int grid = (int)(rows * splits);
-  const size_t smem = walk_smem_bytes(a.max_nodes);
+  const size_t smem = kernel_smem_bytes(a.max_nodes);
   cudaError_t e;
   switch (a.dtype) {
     case SUBSPEC_F32:
