@@ -59,6 +59,7 @@ typedef void* subspec_stream_t; /* a cudaStream_t; NULL = legacy default stream 
 #define SUBSPEC_DEV_BAD_PAGE 8u  /* a page id was outside [0, num_pages)   */
 #define SUBSPEC_DEV_BAD_INDEX 16u /* an accepted-path index was out of range */
 #define SUBSPEC_DEV_TIMEOUT 32u  /* a bounded device-side wait ran out       */
+#define SUBSPEC_DEV_HIST_OVERFLOW 64u /* sampling: one finite logit value occurs > 65535 times in a row */
 
 SUBSPEC_API const char* subspec_version(void);
 /* cudaGetErrorString of the last CUDA error an entry point saw on this thread */
@@ -91,9 +92,12 @@ SUBSPEC_API const char* subspec_last_cuda_error(void);
  *
  * Sampling.  do_sample = 0: the target token of a node is the first-index
  * argmax of its row.  do_sample = 1: the row is divided by `temperature`,
- * filtered by nucleus `top_p` (top_p >= 1 disables the filter), renormalised,
- * and the target token is the inverse-CDF pick for uniforms[b][u] in
- * vocabulary order (this stands in for torch.multinomial's global RNG).
+ * filtered by nucleus `top_p` with the semantics of transformers'
+ * TopPLogitsWarper (top_p >= 1 disables the filter), renormalised, and the
+ * target token is the inverse-CDF pick for uniforms[b][u] in vocabulary order
+ * (this stands in for torch.multinomial's global RNG).  Supported for bf16 /
+ * fp16 logits with the exact method (sample-and-match); other combinations
+ * return SUBSPEC_EUNSUPPORTED.
  *
  * Outputs.  out_tokens / out_hidden are [batch, max_out] int64:
  * accepted draft tokens followed by the bonus token, and for each the local
@@ -132,8 +136,8 @@ typedef struct subspec_verify_args {
   const int32_t* root;      /* [batch] local root index */
   /* sampling */
   int32_t do_sample;
-  float temperature;
-  float top_p;
+  double temperature; /* > 0 */
+  double top_p;       /* >= 1 disables the nucleus filter */
   const float* uniforms; /* [batch, max_nodes], required iff do_sample */
   /* method */
   int32_t method; /* SUBSPEC_VERIFY_* */

@@ -37,8 +37,13 @@ import torch
 # ---------------------------------------------------------------------------------
 def top_p_filter(scores: torch.Tensor, top_p: float) -> torch.Tensor:
     """Nucleus filter as HF's TopPLogitsWarper (min_tokens_to_keep=1): sort ascending,
-    drop entries whose cumulative softmax mass is <= 1 - top_p, always keep the largest."""
-    sorted_logits, sorted_idx = torch.sort(scores, descending=False, dim=-1)
+    drop entries whose cumulative softmax mass is <= 1 - top_p, always keep the largest.
+
+    One deliberate difference: the sort here is STABLE.  transformers calls torch.sort
+    without `stable=True`, and on CPU that sort leaves tied logits in an arbitrary order, so
+    which of the tokens tied at the nucleus boundary get dropped is an accident of the sort
+    implementation there.  Here (and in the CUDA path) the lowest vocabulary indices go first."""
+    sorted_logits, sorted_idx = torch.sort(scores, descending=False, dim=-1, stable=True)
     cum = sorted_logits.softmax(dim=-1).cumsum(dim=-1)
     remove = cum <= (1 - top_p)
     remove[..., -1:] = False
@@ -73,6 +78,35 @@ def inverse_cdf_pick(row: torch.Tensor, u01: float) -> int:
     nz = torch.nonzero(row > 0).reshape(-1)
     last = int(nz[-1]) if nz.numel() else 0
     return min(i, last)
+
+
+def sampling_margins(logits: torch.Tensor, temperature: float, top_p: float, uniforms: Sequence[float]):
+    """Per row, how far the two discrete decisions of the sampler are from flipping (fp64):
+    `boundary`: distance of the nucleus threshold from the nearest cumulative probability, in
+    units of that token's probability; `pick`: distance of u from the nearest CDF edge, relative
+    to the total.  Rows with tiny margins are decided by rounding, not by the algorithm."""
+    x = logits.double().reshape(-1, logits.shape[-1]) / temperature
+    out = []
+    for u in range(x.shape[0]):
+        sorted_logits, sorted_idx = torch.sort(x[u], descending=False, stable=True)
+        p = sorted_logits.softmax(dim=-1)
+        boundary = float("inf")
+        keep = torch.ones_like(p, dtype=torch.bool)
+        if top_p < 1.0:
+            cum = p.cumsum(0)
+            thr = float(torch.tensor(1.0 - top_p, dtype=torch.float32))
+            j = int(torch.argmin((cum - thr).abs()))
+            boundary = float((cum[j] - thr).abs() / p[j])
+            remove = cum <= thr
+            remove[-1] = False
+            keep = ~remove
+        q = torch.zeros_like(p)
+        q[sorted_idx] = torch.where(keep, p, torch.zeros_like(p))
+        cdf = q.cumsum(0)
+        total = float(cdf[-1])
+        pick = float(((cdf - float(uniforms[u]) * total).abs()).min() / total)
+        out.append((boundary, pick))
+    return out
 
 
 def target_tokens(probs: torch.Tensor, do_sample: bool, uniforms: Optional[Sequence[float]]) -> List[int]:

@@ -16,7 +16,7 @@ F32, BF16, F16 = 0, 1, 2
 IN_LOGITS, IN_PROBS = 0, 1
 VERIFY_EXACT, VERIFY_LOSSY = 0, 1
 GATE_PROB, GATE_ENTROPY = 0, 1
-DEV_BAD_TOKEN, DEV_BAD_CHILD, DEV_BAD_ROOT, DEV_BAD_PAGE, DEV_BAD_INDEX, DEV_TIMEOUT = 1, 2, 4, 8, 16, 32
+DEV_BAD_TOKEN, DEV_BAD_CHILD, DEV_BAD_ROOT, DEV_BAD_PAGE, DEV_BAD_INDEX, DEV_TIMEOUT, DEV_HIST_OVERFLOW = 1, 2, 4, 8, 16, 32, 64
 
 _STATUS_TEXT = {
     EINVAL: "invalid argument",
@@ -33,6 +33,7 @@ _DEV_TEXT = {
     DEV_BAD_PAGE: "page id outside the pool",
     DEV_BAD_INDEX: "accepted-path index out of range",
     DEV_TIMEOUT: "a bounded device-side wait ran out",
+    DEV_HIST_OVERFLOW: "sampling: one finite logit value occurs more than 65535 times in a row",
 }
 
 _vp, _i32, _i64, _u32, _f32, _f64 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint32, C.c_float, C.c_double
@@ -46,7 +47,7 @@ class VerifyArgs(C.Structure):
         ("input_kind", _i32), ("seq_stride", _i64), ("row_stride", _i64), ("logits", _vp),
         ("n_nodes", _vp), ("n_rows", _vp), ("token_ids", _vp), ("child_off", _vp), ("child_idx", _vp),
         ("root", _vp),
-        ("do_sample", _i32), ("temperature", _f32), ("top_p", _f32), ("uniforms", _vp),
+        ("do_sample", _i32), ("temperature", _f64), ("top_p", _f64), ("uniforms", _vp),
         ("method", _i32), ("gate", _i32), ("threshold", _f64), ("window", _i32), ("eos", _i64),
         ("max_out", _i32), ("out_tokens", _vp), ("out_hidden", _vp), ("out_meta", _vp),
         ("node_target", _vp), ("node_entropy", _vp), ("node_child_prob", _vp), ("node_rowmax", _vp),

@@ -358,6 +358,7 @@ struct KArgs {
   int splits;
   int vec_ok;  // every row start is 16-byte aligned
   float k;     // log2(e) / temperature
+  float remove_below;  // nucleus filter: drop tokens while the ascending cumulative probability is <= this
 };
 
 // ---- the accept walk, run by one CTA per sequence out of shared memory -----------
@@ -795,6 +796,396 @@ __global__ void __launch_bounds__(kThreads, 3) verify_rows_kernel(const KArgs ka
   run_walk(ka, b, smem_raw);
 }
 
+// ---- sampled target tokens: temperature + nucleus (top-p) + inverse-CDF pick -----------------
+//
+// One CTA per [vocab] row of 16-bit logits.  A 16-bit float has only 65536 values, so a COUNT
+// histogram over all of them (128 KB of shared memory, two 16-bit counters per word) describes the
+// row's distribution exactly: the softmax denominator, the nucleus boundary value and how many
+// of the tokens tied at that value fall outside the nucleus all follow from it, with one
+// exponential per distinct value instead of one per token.  A second sweep over the row (served
+// by L2) then adds up, chunk by chunk in vocabulary order, the mass that survives the filter, and
+// the chunk / element where the cumulative mass passes u * Z is the sampled token.
+//
+// Filter semantics = transformers' TopPLogitsWarper (min_tokens_to_keep = 1) applied to
+// logits / temperature, as the reference's _sample_token does (generators/base.py:57-62, 116-126):
+// ascending stable sort, remove while the cumulative probability is <= 1 - top_p, never remove
+// the last.  Among tokens tied at the boundary value the lowest vocabulary indices go first.
+constexpr int kSThreads = 1024;
+constexpr int kSWarps = kSThreads / 32;
+constexpr int kHistWords = 32768;   // 65536 16-bit counters
+constexpr int kChunkElems = 256;    // one warp sweep: 32 lanes x 8 elements
+constexpr int kMaxChunks = (1 << 20) / kChunkElems;
+constexpr size_t kSampleSmem = sizeof(uint32_t) * kHistWords + (sizeof(float) + sizeof(uint32_t)) * kMaxChunks;
+
+template <typename T>
+struct Bits16;
+template <>
+struct Bits16<__nv_bfloat16> {
+  static constexpr uint32_t kNegInf = 0xFF80u;
+  static __device__ __forceinline__ float value(uint32_t bits) { return __uint_as_float(bits << 16); }
+};
+template <>
+struct Bits16<__half> {
+  static constexpr uint32_t kNegInf = 0xFC00u;
+  static __device__ __forceinline__ float value(uint32_t bits) {
+    return __half2float(__ushort_as_half((unsigned short)bits));
+  }
+};
+// order-preserving key of a 16-bit float pattern, and back
+__device__ __forceinline__ uint32_t key_of(uint32_t bits) {
+  return (bits & 0x8000u) ? (~bits & 0xFFFFu) : (bits | 0x8000u);
+}
+// Histogram word w lives at swz(w): each 32-word row is XOR-rotated by its row number, so that the
+// per-thread scans (thread t walks row t) hit 32 different banks across a warp.
+__device__ __forceinline__ uint32_t swz(uint32_t w) { return (w & ~31u) | ((w ^ (w >> 5)) & 31u); }
+__device__ __forceinline__ uint32_t bits_of(uint32_t key) {
+  return (key & 0x8000u) ? (key & 0x7FFFu) : (~key & 0xFFFFu);
+}
+
+// Eight consecutive raw 16-bit patterns starting at element i0 (a multiple of 8); elements at or beyond
+// V read as -inf.
+template <typename T>
+__device__ __forceinline__ void load8(const T* rowp, int i0, int V, bool vec_ok, uint32_t (&b)[8]) {
+  if (vec_ok && i0 + 8 <= V) {
+    const uint4 q = *reinterpret_cast<const uint4*>(rowp + i0);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      b[2 * j] = w[j] & 0xFFFFu;
+      b[2 * j + 1] = w[j] >> 16;
+    }
+  } else {
+    const unsigned short* p = reinterpret_cast<const unsigned short*>(rowp);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) b[j] = (i0 + j < V) ? (uint32_t)p[i0 + j] : Bits16<T>::kNegInf;
+  }
+}
+
+__device__ __forceinline__ double shfl_up_f64(double v, int d) {
+  int lo = __double2loint(v), hi = __double2hiint(v);
+  lo = __shfl_up_sync(0xffffffffu, lo, d);
+  hi = __shfl_up_sync(0xffffffffu, hi, d);
+  return __hiloint2double(hi, lo);
+}
+__device__ __forceinline__ double shfl_f64(double v, int src) {
+  int lo = __double2loint(v), hi = __double2hiint(v);
+  lo = __shfl_sync(0xffffffffu, lo, src);
+  hi = __shfl_sync(0xffffffffu, hi, src);
+  return __hiloint2double(hi, lo);
+}
+// inclusive scan over the warp
+__device__ __forceinline__ double warp_scan_f64(double v) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const double o = shfl_up_f64(v, d);
+    if (lane >= d) v += o;
+  }
+  return v;
+}
+__device__ __forceinline__ int warp_scan_i32(int v) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int o = __shfl_up_sync(0xffffffffu, v, d);
+    if (lane >= d) v += o;
+  }
+  return v;
+}
+
+struct SampleShared {
+  double warp_tot[kSWarps];
+  double S, cum_before, Z;
+  float c, e_b;
+  int kmax, k_b, r, n_b, overflow, flag;
+  int warp_max[kSWarps];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const KArgs ka) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ SampleShared sh;
+  uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw);
+  float* ch_mass = reinterpret_cast<float*>(hist + kHistWords);
+  uint32_t* ch_ties = reinterpret_cast<uint32_t*>(ch_mass + kMaxChunks);
+
+  const subspec_verify_args& a = ka.a;
+  const int row = blockIdx.x;
+  const int b = row / a.max_nodes;
+  const int u = row - b * a.max_nodes;
+  const int n_rows = a.n_rows[b];
+  if (u >= n_rows) return;
+  const int V = a.vocab;
+  const T* rowp = reinterpret_cast<const T*>(a.logits) + (size_t)b * a.seq_stride + (size_t)u * a.row_stride;
+  const bool vec_ok = ka.vec_ok != 0;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float kT = ka.k;
+
+  // ---- 0. clear the histogram ----
+  for (int i = tid; i < kHistWords / 4; i += kSThreads) reinterpret_cast<uint4*>(hist)[i] = make_uint4(0, 0, 0, 0);
+  if (tid == 0) sh.overflow = 0;
+  __syncthreads();
+
+  // ---- 1. count every value of the row (HBM pass) ----
+  const int nchunks = (V + kChunkElems - 1) / kChunkElems;
+  for (int c = warp; c < nchunks; c += kSWarps) {
+    uint32_t bits[8];
+    load8<T>(rowp, c * kChunkElems + lane * 8, V, vec_ok, bits);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (bits[j] == Bits16<T>::kNegInf) continue;  // masked: no mass, and often far too many to count
+      const uint32_t key = key_of(bits[j]);
+      const uint32_t sh16 = (key & 1u) * 16u;
+      const uint32_t old = atomicAdd(&hist[swz(key >> 1)], 1u << sh16);
+      if (((old >> sh16) & 0xFFFFu) == 0xFFFFu) sh.overflow = 1;
+    }
+  }
+  __syncthreads();
+  if (sh.overflow) {  // one value more than 65535 times in a row: the 16-bit counters cannot hold it
+    if (tid == 0) flag(a.dev_status, SUBSPEC_DEV_HIST_OVERFLOW);
+    return;
+  }
+
+  // ---- 2. the histogram: maximum, denominator, nucleus boundary ----
+  // thread t owns keys [64 t, 64 t + 64) = words [32 t, 32 t + 32)
+  auto cnt_of = [&](int i) -> uint32_t {  // counter of key 64 t + i
+    const uint32_t w = hist[swz((uint32_t)(tid * 32 + (i >> 1)))];
+    return (i & 1) ? (w >> 16) : (w & 0xFFFFu);
+  };
+  int kmax = -1;
+  for (int i = 0; i < 64; ++i)
+    if (cnt_of(i)) kmax = tid * 64 + i;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, off));
+  if (lane == 0) sh.warp_max[warp] = kmax;
+  __syncthreads();
+  if (tid == 0) {
+    int m = -1;
+    for (int w = 0; w < kSWarps; ++w) m = max(m, sh.warp_max[w]);
+    sh.kmax = m;
+    sh.c = m >= 0 ? Bits16<T>::value(bits_of((uint32_t)m)) * kT : 0.f;
+  }
+  __syncthreads();
+  const int K_max = sh.kmax;
+  const size_t nb = (size_t)b * a.max_nodes;
+  if (K_max < 0) {  // nothing but -inf / empty: no distribution to sample from
+    if (tid == 0) {
+      a.node_target[nb + u] = 0;
+      a.node_entropy[nb + u] = 0.f;
+      a.node_rowmax[nb + u] = 0.f;
+      a.node_rowsum[nb + u] = 0.f;
+    }
+  } else {
+    const float c = sh.c;
+    // masses of this thread's values, ascending
+    double M_t = 0.0;
+    for (int i = 0; i < 64; ++i) {
+      const uint32_t n = cnt_of(i);
+      if (n) {
+        const float e = ex2f(fmaf(Bits16<T>::value(bits_of((uint32_t)(tid * 64 + i))), kT, -c));
+        M_t += (double)n * (double)e;
+      }
+    }
+    // block exclusive scan of M_t in key order
+    const double incl = warp_scan_f64(M_t);
+    if (lane == 31) sh.warp_tot[warp] = incl;
+    __syncthreads();
+    double base = 0.0, total = 0.0;
+    for (int w = 0; w < kSWarps; ++w) {
+      const double t = sh.warp_tot[w];
+      if (w < warp) base += t;
+      total += t;
+    }
+    const double P_t = base + incl - M_t;
+    const double thrS = (double)ka.remove_below * total;  // remove while cumulative mass <= thrS
+    if (tid == 0) {
+      // default: the filter is off, or the threshold is never passed (keep only the last of the maximum)
+      sh.S = total;
+      sh.k_b = -1;
+      sh.r = 0;
+      sh.n_b = 0;
+      sh.e_b = 0.f;
+      sh.cum_before = 0.0;
+    }
+    __syncthreads();
+    if (ka.remove_below > 0.f) {
+      if (M_t > 0.0 && P_t <= thrS && thrS < P_t + M_t) {
+        double cum = P_t;
+        for (int i = 0; i < 64; ++i) {
+          const int n = (int)cnt_of(i);
+          if (!n) continue;
+          const int key = tid * 64 + i;
+          const float e = ex2f(fmaf(Bits16<T>::value(bits_of((uint32_t)key)), kT, -c));
+          const double me = (double)n * (double)e;
+          if (cum + me > thrS) {
+            int r = (int)floor((thrS - cum) / (double)e);
+            r = min(max(r, 0), n);
+            if (key == K_max) r = min(r, n - 1);
+            sh.k_b = key;
+            sh.r = r;
+            sh.n_b = n;
+            sh.e_b = e;
+            sh.cum_before = cum;
+            break;
+          }
+          cum += me;
+        }
+      }
+      __syncthreads();
+      if (tid == 0 && sh.k_b < 0) {
+        // thrS >= total (top_p ~ 0): everything below the maximum goes, and all but the last of the maximum
+        sh.k_b = K_max;
+        const uint32_t w = hist[swz((uint32_t)K_max >> 1)];
+        const int n = (int)((K_max & 1) ? (w >> 16) : (w & 0xFFFFu));
+        const float e = ex2f(fmaf(Bits16<T>::value(bits_of((uint32_t)K_max)), kT, -c));
+        sh.n_b = n;
+        sh.r = n - 1;
+        sh.e_b = e;
+        sh.cum_before = total - (double)n * (double)e;
+      }
+    }
+    __syncthreads();
+    const int k_b = sh.k_b, r_rm = sh.r;
+    const float e_b = sh.e_b;
+    if (tid == 0) sh.Z = sh.S - sh.cum_before - (double)r_rm * (double)e_b;
+    __syncthreads();  // the histogram is no longer needed after this point
+
+    // ---- 3. second sweep: surviving mass and boundary ties per chunk, vocabulary order (L2 pass) ----
+    for (int cidx = warp; cidx < nchunks; cidx += kSWarps) {
+      uint32_t bits[8];
+      load8<T>(rowp, cidx * kChunkElems + lane * 8, V, vec_ok, bits);
+      float mass = 0.f;
+      int ties = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (bits[j] == Bits16<T>::kNegInf) continue;
+        const int key = (int)key_of(bits[j]);
+        if (key > k_b)
+          mass += ex2f(fmaf(Bits16<T>::value(bits[j]), kT, -c));
+        else if (key == k_b)
+          ++ties;
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        mass += __shfl_xor_sync(0xffffffffu, mass, off);
+        ties += __shfl_xor_sync(0xffffffffu, ties, off);
+      }
+      if (lane == 0) {
+        ch_mass[cidx] = mass;
+        ch_ties[cidx] = (uint32_t)ties;
+      }
+    }
+    __syncthreads();
+
+    // ---- 4./5. locate the chunk, then the element, where the cumulative surviving mass passes u * Z ----
+    if (warp == 0) {
+      const double Z = sh.Z;
+      const double target = (double)a.uniforms[nb + u] * Z;
+      const int per = (nchunks + 31) / 32;
+      const int c0 = min(lane * per, nchunks), c1 = min(c0 + per, nchunks);
+      int tl = 0;
+      for (int cc = c0; cc < c1; ++cc) tl += (int)ch_ties[cc];
+      const int T_lane0 = warp_scan_i32(tl) - tl;
+      double local = 0.0;
+      int Trun = T_lane0;
+      for (int cc = c0; cc < c1; ++cc) {
+        const int T1 = Trun + (int)ch_ties[cc];
+        local += (double)ch_mass[cc] + (double)e_b * (double)(max(T1 - r_rm, 0) - max(Trun - r_rm, 0));
+        Trun = T1;
+      }
+      const double lincl = warp_scan_f64(local);
+      const double lbase = lincl - local;
+      const uint32_t cross = __ballot_sync(0xffffffffu, local > 0.0 && lbase + local > target);
+      const uint32_t nonzero = __ballot_sync(0xffffffffu, local > 0.0);
+      // no crossing (u * Z rounds up to the total): the last token with surviving mass
+      const bool pick_last = cross == 0;
+      const int L = pick_last ? (nonzero ? 31 - __clz(nonzero) : 0) : __ffs(cross) - 1;
+      int cstar = 0, T0 = 0;
+      double cbase = 0.0;
+      if (lane == L) {
+        double cum = lbase;
+        Trun = T_lane0;
+        cstar = c0;
+        T0 = Trun;
+        cbase = cum;
+        for (int cc = c0; cc < c1; ++cc) {
+          const int T1 = Trun + (int)ch_ties[cc];
+          const double cm = (double)ch_mass[cc] + (double)e_b * (double)(max(T1 - r_rm, 0) - max(Trun - r_rm, 0));
+          if (cm > 0.0) {  // candidate: the crossing chunk, or (pick_last) the last chunk with mass
+            cstar = cc;
+            T0 = Trun;
+            cbase = cum;
+            if (!pick_last && cum + cm > target) break;
+          }
+          cum += cm;
+          Trun = T1;
+        }
+      }
+      cstar = __shfl_sync(0xffffffffu, cstar, L);
+      T0 = __shfl_sync(0xffffffffu, T0, L);
+      cbase = shfl_f64(cbase, L);
+
+      uint32_t bits[8];
+      load8<T>(rowp, cstar * kChunkElems + lane * 8, V, vec_ok, bits);
+      int lt = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (bits[j] != Bits16<T>::kNegInf && (int)key_of(bits[j]) == k_b) ++lt;
+      int trank = T0 + warp_scan_i32(lt) - lt;
+      float km[8];
+      double lsum = 0.0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        km[j] = 0.f;
+        if (bits[j] == Bits16<T>::kNegInf) continue;
+        const int key = (int)key_of(bits[j]);
+        if (key > k_b) {
+          km[j] = ex2f(fmaf(Bits16<T>::value(bits[j]), kT, -c));
+        } else if (key == k_b) {
+          km[j] = trank >= r_rm ? e_b : 0.f;
+          ++trank;
+        }
+        lsum += (double)km[j];
+      }
+      const double eincl = warp_scan_f64(lsum);
+      double run = cbase + eincl - lsum;
+      int pick = -1, last = -1;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (km[j] > 0.f) {
+          last = lane * 8 + j;
+          run += (double)km[j];
+          if (pick < 0 && run > target) pick = lane * 8 + j;
+        }
+      }
+      const uint32_t hit = __ballot_sync(0xffffffffu, pick >= 0);
+      const uint32_t any = __ballot_sync(0xffffffffu, last >= 0);
+      int within;
+      if (hit && !pick_last) {
+        within = __shfl_sync(0xffffffffu, pick, __ffs(hit) - 1);
+      } else {
+        within = any ? __shfl_sync(0xffffffffu, last, 31 - __clz(any)) : 0;
+      }
+      if (lane == 0) {
+        a.node_target[nb + u] = min(cstar * kChunkElems + within, V - 1);
+        a.node_entropy[nb + u] = 0.f;
+        a.node_rowmax[nb + u] = c;
+        a.node_rowsum[nb + u] = (float)Z;
+      }
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int t = atomicAdd(ka.sc.seq_ticket + b, 1);
+    sh.flag = (t == n_rows - 1);
+  }
+  __syncthreads();
+  if (!sh.flag) return;
+  __threadfence();
+  run_walk(ka, b, smem_raw);
+}
+
 template <typename T>
 cudaError_t launch_rows(const KArgs& ka, int grid, size_t smem, cudaStream_t st) {
   const bool soft = ka.a.method == SUBSPEC_VERIFY_LOSSY;
@@ -818,6 +1209,15 @@ cudaError_t launch_rows(const KArgs& ka, int grid, size_t smem, cudaStream_t st)
       SUBSPEC_LAUNCH(SUBSPEC_IN_LOGITS, false);
   }
 #undef SUBSPEC_LAUNCH
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_sample(const KArgs& ka, int rows, cudaStream_t st) {
+  cudaError_t e = cudaFuncSetAttribute(verify_sample_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)kSampleSmem);
+  if (e != cudaSuccess) return e;
+  verify_sample_rows_kernel<T><<<rows, kSThreads, kSampleSmem, st>>>(ka);
   return cudaGetLastError();
 }
 
@@ -854,7 +1254,12 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
       !a.node_rowmax || !a.node_rowsum || !a.node_exact_after || !a.node_best_len || !a.node_best_next ||
       !a.scratch)
     return SUBSPEC_EINVAL;
-  if (a.do_sample) return SUBSPEC_EUNSUPPORTED;
+  if (a.do_sample) {
+    // sampled targets: 16-bit logits, exact (sample-and-match) walk
+    if (a.dtype == SUBSPEC_F32 || a.input_kind != SUBSPEC_IN_LOGITS || a.method != SUBSPEC_VERIFY_EXACT)
+      return SUBSPEC_EUNSUPPORTED;
+    if (!a.uniforms || !(a.temperature > 0.0) || !(a.top_p >= 0.0)) return SUBSPEC_EINVAL;
+  }
   size_t need = 0;
   subspec_verify_scratch_bytes(a.batch, a.max_nodes, &need);
   if (a.scratch_bytes < need || (reinterpret_cast<uintptr_t>(a.scratch) & 255u)) return SUBSPEC_ESCRATCH;
@@ -864,7 +1269,9 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
   KArgs ka;
   ka.a = a;
   ka.sc = carve(a.scratch, a.batch, a.max_nodes);
-  ka.k = kLog2e;
+  ka.k = a.do_sample ? (float)(1.4426950408889634 / a.temperature) : kLog2e;
+  // transformers compares float32 cumulative probabilities with the Python double 1 - top_p cast to float32
+  ka.remove_below = (a.do_sample && a.top_p < 1.0) ? (float)(1.0 - a.top_p) : 0.f;
   const size_t esz = a.dtype == SUBSPEC_F32 ? 4 : 2;
   ka.vec_ok = ((reinterpret_cast<uintptr_t>(a.logits) & 15u) == 0) && ((a.seq_stride * esz) % 16 == 0) &&
               ((a.row_stride * esz) % 16 == 0);
@@ -884,9 +1291,14 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
 
   int rc = cuda_check(cudaMemsetAsync(a.scratch, 0, ticket_bytes(a.batch, a.max_nodes), st));
   if (rc) return rc;
+  cudaError_t e;
+  if (a.do_sample) {
+    e = a.dtype == SUBSPEC_BF16 ? launch_sample<__nv_bfloat16>(ka, (int)rows, st)
+                                : launch_sample<__half>(ka, (int)rows, st);
+    return cuda_check(e);
+  }
   const int grid = (int)(rows * splits);
   const size_t smem = kernel_smem_bytes(a.max_nodes);
-  cudaError_t e;
   switch (a.dtype) {
     case SUBSPEC_F32:
       e = launch_rows<float>(ka, grid, smem, st);

@@ -138,3 +138,52 @@ def test_edge_cases(cuda_lib):
     with pytest.raises(ValueError):
         verify_tree(tree=_tree_of(st), root_ind=0, logits=torch.randn(1, 2, 17), eos_token_id=None,
                     logits_processor=None, do_sample=False, verify_method="lossy")
+
+
+def _sampled_case(seed, batch, nodes, vocab, dtype, sigma):
+    gen = torch.Generator().manual_seed(seed)
+    sts = [synthetic.random_tree(nodes, 10, 8, vocab, gen) for _ in range(batch)]
+    logits = torch.stack([synthetic.verify_logits(st, vocab, gen, dtype=dtype, sigma=sigma, boost=6.0) for st in sts])
+    uniforms = torch.rand(batch, nodes, generator=gen)
+    return sts, logits, uniforms
+
+
+@pytest.mark.parametrize("vocab,nodes,dtype,temperature,top_p", [
+    (152064, 24, torch.bfloat16, 1.0, 0.9),   # config-2 distribution at reduced node count
+    (32000, 40, torch.float16, 0.7, 0.95),
+    (4099, 33, torch.bfloat16, 1.3, 1.0),     # no nucleus filter, unaligned rows
+    (50, 12, torch.bfloat16, 1.0, 0.5),       # tiny vocabulary: heavy ties at the boundary
+])
+def test_stochastic_sample_and_match(cuda_lib, vocab, nodes, dtype, temperature, top_p):
+    """Sampled targets (temperature, nucleus, injected uniforms) and the sample-and-match walk vs the oracle."""
+    from transformers.generation.logits_process import (LogitsProcessorList, TemperatureLogitsWarper,
+                                                        TopPLogitsWarper)
+    B = 3
+    sts, logits, uniforms = _sampled_case(500 + nodes, B, nodes, vocab, dtype, 2.5)
+    procs = LogitsProcessorList()
+    if temperature != 1.0:
+        procs.append(TemperatureLogitsWarper(temperature))
+    if top_p < 1.0:
+        procs.append(TopPLogitsWarper(top_p=top_p))
+    res = verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
+                              eos_token_id=None, logits_processor=procs, do_sample=True, verify_method="stochastic",
+                              uniforms=uniforms)
+    from subspec_b200.verify import get_workspace
+    targets = get_workspace(B, nodes, torch.device("cuda", 0)).fetch()["node_target"]
+    decided_by_rounding = 0
+    for b, st in enumerate(sts):
+        probs = vo.target_probs(logits[b], True, temperature, top_p, upcast=True)
+        want = vo.target_tokens(probs, True, uniforms[b].tolist())
+        margins = vo.sampling_margins(logits[b], temperature, top_p, uniforms[b].tolist())
+        safe = [mb > 1e-3 and mp > 1e-6 for mb, mp in margins]
+        decided_by_rounding += safe.count(False)
+        for u in range(st.n):
+            if safe[u]:
+                assert int(targets[b, u]) == want[u], (b, u, margins[u])
+        # the walk itself is integer work: replay it on the kernel's own targets
+        r = vo.exact_walk(target=targets[b, :st.n].tolist(), token_ids=st.token_ids.tolist(), children=st.children(),
+                          root=0, n_rows=st.n, eos=None)
+        assert res[b].sampled_tokens.squeeze(0).tolist() == r.tokens
+        assert res[b].hidden_indices.tolist() == r.hidden
+        assert (res[b].total_len, res[b].accept_len) == (r.total_len, r.accept_len)
+    assert decided_by_rounding <= max(2, B * nodes // 10)
