@@ -272,6 +272,110 @@ typedef struct subspec_kv_hf_args {
 
 SUBSPEC_API int subspec_kv_compact_hf(const subspec_kv_hf_args* args, subspec_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Draft-tree expansion, one depth step for a batch of sequences.
+ *
+ * Replaces (reference file:line):
+ *   - softmax(logits / temperature) in the draft forward
+ *       specdecodes/models/draft_models/classic_sd.py:10-16
+ *   - DraftModelBase.topk_sampling / _topk_flatten: probs * parent_probs,
+ *     flatten [leaves * vocab], torch.topk(k, sorted), idx // vocab, idx % vocab
+ *       specdecodes/models/draft_models/base.py:267-305 (graph variant :307-323)
+ *   - TreeData.update + Tree.add_nodes numbering when the tree_* arrays are given
+ *       specdecodes/models/draft_models/base.py:31-47,
+ *       specdecodes/models/utils/cpu_tree.py:69-117
+ *
+ * `scores` is [batch, leaves, vocab] (element strides seq_stride / row_stride):
+ * draft logits (input_kind = SUBSPEC_IN_LOGITS: probabilities are
+ * softmax(logits / temperature) rounded to the dtype, as the reference's
+ * forward(with_softmax=True) returns them) or probabilities already
+ * (SUBSPEC_IN_PROBS, what topk_sampling takes).  parent_probs is [batch, leaves]
+ * in the same dtype (NULL = ones, the first step).  A candidate's score is
+ * round(prob * parent_prob) in the dtype.  Outputs, [batch, k], best first, ties
+ * by ascending flat index leaf * vocab + token: out_tokens / out_parents int64,
+ * out_probs in the dtype (the next step's parent_probs).
+ *
+ * Optional tree arrays (all NULL, or all given): int32 / fp32 [batch,
+ * tree_stride]; node 0 is the root, level `level` fills nodes
+ * 1 + level*k .. level*k + k in rank order, with parent node index, cumulative
+ * probability (the score) and depth level + 1.
+ * ---------------------------------------------------------------------- */
+typedef struct subspec_expand_args {
+  uint32_t struct_size;
+  int32_t batch;
+  int32_t leaves; /* rows per sequence: 1 on the first step, k afterwards */
+  int32_t vocab;
+  int32_t k; /* 1..32 */
+  int32_t dtype;
+  int32_t input_kind;
+  int64_t seq_stride;
+  int64_t row_stride;
+  const void* scores;
+  const void* parent_probs;
+  double temperature; /* used with SUBSPEC_IN_LOGITS */
+  int64_t* out_tokens;
+  void* out_probs;
+  int64_t* out_parents;
+  int32_t level;
+  int32_t tree_stride;
+  int32_t* tree_tokens;
+  int32_t* tree_parents;
+  float* tree_probs;
+  int32_t* tree_depths;
+  void* scratch; /* subspec_expand_scratch_bytes(), 256-byte aligned, no initialisation needed */
+  size_t scratch_bytes;
+  uint32_t* dev_status;
+} subspec_expand_args;
+
+SUBSPEC_API int subspec_expand_scratch_bytes(int32_t batch, int32_t leaves, int32_t k, size_t* bytes);
+SUBSPEC_API int subspec_expand_step(const subspec_expand_args* args, subspec_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Tree finaliser: prune to the `keep` nodes of largest cumulative probability,
+ * renumber by rank, and emit everything the tree-decoding forward and the
+ * verifier need.
+ *
+ * Replaces (reference file:line):
+ *   - Tree.prune_to_top_n         specdecodes/models/utils/cpu_tree.py:175-215
+ *   - Tree.get_tree_data          cpu_tree.py:238-251
+ *   - Tree.create_attention_mask  cpu_tree.py:263-286 (ancestor-or-self matrix)
+ *   - position ids = depths + position_offset
+ *                                 specdecodes/models/generators/classic_sd.py:73-75
+ *
+ * Input: the tree arrays subspec_expand_step fills, n_nodes nodes per
+ * sequence (node 0 = root, probability 1).  Ranking is (probability desc,
+ * index asc); the reference leaves ties to torch.topk.  Outputs are
+ * [batch, keep]: keep_idx (old index of new node r), tokens, parents (new
+ * numbering, -1 for the root), depths, probs, position_ids (int64); mask is
+ * [batch, keep, keep] bytes, mask[i][j] = 1 iff j is i or an ancestor of i;
+ * child_off [batch, keep + 1] / child_idx [batch, keep] are the children lists
+ * in the layout subspec_verify_batched takes; n_out[b] = nodes kept.
+ * ---------------------------------------------------------------------- */
+typedef struct subspec_tree_finalize_args {
+  uint32_t struct_size;
+  int32_t batch;
+  int32_t n_nodes; /* <= 4096 */
+  int32_t tree_stride;
+  int32_t keep; /* <= 1024 */
+  const int32_t* tree_tokens;
+  const int32_t* tree_parents;
+  const float* tree_probs;
+  const int32_t* tree_depths;
+  const int32_t* position_offset; /* [batch] or NULL (= 0) */
+  int32_t* keep_idx;
+  int32_t* tokens;
+  int32_t* parents;
+  int32_t* depths;
+  float* probs;
+  int64_t* position_ids;
+  uint8_t* mask;
+  int32_t* child_off;
+  int32_t* child_idx;
+  int32_t* n_out;
+} subspec_tree_finalize_args;
+
+SUBSPEC_API int subspec_tree_finalize(const subspec_tree_finalize_args* args, subspec_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

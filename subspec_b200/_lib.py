@@ -78,6 +78,30 @@ class KvHfArgs(C.Structure):
     ]
 
 
+class ExpandArgs(C.Structure):
+    """Mirror of `subspec_expand_args`."""
+
+    _fields_ = [
+        ("struct_size", _u32), ("batch", _i32), ("leaves", _i32), ("vocab", _i32), ("k", _i32), ("dtype", _i32),
+        ("input_kind", _i32), ("seq_stride", _i64), ("row_stride", _i64), ("scores", _vp), ("parent_probs", _vp),
+        ("temperature", _f64), ("out_tokens", _vp), ("out_probs", _vp), ("out_parents", _vp), ("level", _i32),
+        ("tree_stride", _i32), ("tree_tokens", _vp), ("tree_parents", _vp), ("tree_probs", _vp),
+        ("tree_depths", _vp), ("scratch", _vp), ("scratch_bytes", C.c_size_t), ("dev_status", _vp),
+    ]
+
+
+class TreeFinalizeArgs(C.Structure):
+    """Mirror of `subspec_tree_finalize_args`."""
+
+    _fields_ = [
+        ("struct_size", _u32), ("batch", _i32), ("n_nodes", _i32), ("tree_stride", _i32), ("keep", _i32),
+        ("tree_tokens", _vp), ("tree_parents", _vp), ("tree_probs", _vp), ("tree_depths", _vp),
+        ("position_offset", _vp), ("keep_idx", _vp), ("tokens", _vp), ("parents", _vp), ("depths", _vp),
+        ("probs", _vp), ("position_ids", _vp), ("mask", _vp), ("child_off", _vp), ("child_idx", _vp),
+        ("n_out", _vp),
+    ]
+
+
 # every symbol include/subspec_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "subspec_version": (C.c_char_p, []),
@@ -87,6 +111,9 @@ SYMBOLS = {
     "subspec_verify_batched_static_scratch": (C.c_int, [C.POINTER(VerifyArgs), _vp]),
     "subspec_kv_compact_paged": (C.c_int, [C.POINTER(KvPagedArgs), _vp]),
     "subspec_kv_compact_hf": (C.c_int, [C.POINTER(KvHfArgs), _vp]),
+    "subspec_expand_scratch_bytes": (C.c_int, [_i32, _i32, _i32, C.POINTER(C.c_size_t)]),
+    "subspec_expand_step": (C.c_int, [C.POINTER(ExpandArgs), _vp]),
+    "subspec_tree_finalize": (C.c_int, [C.POINTER(TreeFinalizeArgs), _vp]),
 }
 
 _lib = None

@@ -1,0 +1,597 @@
+// Draft-tree expansion for sm_100a: fused softmax + global top-k over leaves x vocab, and the
+// tree finaliser (prune to the best n nodes, renumber, ancestor mask, position ids, children CSR).
+//
+// Reference semantics (specdecodes/models/draft_models/base.py:281-305, classic_sd.py:10-16):
+//   probs  = softmax(logits / T)                       in the model dtype
+//   score  = probs[l, v] * parent_probs[l]             in the model dtype
+//   top-k over the flattened [leaves * vocab] scores, sorted descending;
+//   parent = idx // vocab, token = idx % vocab.
+// The reference materialises the scores (a full-size write and read) and runs a generic top-k
+// over ~2M candidates per sequence.  Here each [vocab] row is streamed once: per row the k best
+// logits (value desc, index asc) and the softmax denominator; the last CTA of a sequence turns the
+// leaves * k survivors into scores with the reference's rounding (probability rounded to the
+// dtype, product rounded to the dtype) and keeps the k best (score desc, flat index asc).  Scores
+// are monotone in the logit within a row, so the survivors contain the true top-k values.
+//
+// Tree finaliser: Tree.add_nodes numbering (cpu_tree.py:87-117), prune_to_top_n (:175-215),
+// create_attention_mask (:263-286), position ids = depth + offset (classic_sd.py:73-75).
+#include <limits.h>
+#include <math.h>
+
+#include "common.cuh"
+
+namespace subspec {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kUnroll = 4;
+constexpr int kMaxK = 32;
+constexpr int kQueue = 256;  // per-warp candidate queue: one 16-byte vector per lane, 8 elements each
+
+struct Cand {
+  float v;
+  int id;
+};
+__device__ __forceinline__ bool better(float av, int ai, float bv, int bi) {
+  return av > bv || (av == bv && ai < bi);
+}
+
+// A warp-wide list of the k best (value desc, index asc): lane i holds entry i.
+struct WarpTopK {
+  float v;
+  int id;
+  int k;
+  __device__ __forceinline__ void init(int k_) {
+    k = k_;
+    v = -INFINITY;
+    id = INT_MAX;
+  }
+  __device__ __forceinline__ float kth_value() const { return __shfl_sync(0xffffffffu, v, k - 1); }
+  __device__ __forceinline__ float value_at(int j) const { return __shfl_sync(0xffffffffu, v, j); }
+  // All lanes call with the same candidate.
+  __device__ __forceinline__ void insert(float cv, int cid) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t ahead = __ballot_sync(0xffffffffu, lane < k && better(v, id, cv, cid));
+    const int pos = __popc(ahead);
+    if (pos >= k) return;
+    const float pv = __shfl_up_sync(0xffffffffu, v, 1);
+    const int pi = __shfl_up_sync(0xffffffffu, id, 1);
+    if (lane > pos) {
+      v = pv;
+      id = pi;
+    } else if (lane == pos) {
+      v = cv;
+      id = cid;
+    }
+    if (lane >= k) {
+      v = -INFINITY;
+      id = INT_MAX;
+    }
+  }
+};
+
+struct RowOut {  // per (sequence, leaf) row, in scratch
+  float c, s;    // softmax shift (log2 domain) and denominator; unused for probabilities in
+};
+
+struct KArgs {
+  subspec_expand_args a;
+  int* ticket;     // [batch]
+  RowOut* rowout;  // [batch * leaves]
+  Cand* rowtop;    // [batch * leaves * k]
+  float kT;        // scale inside 2^(x * kT - c): log2(e) / temperature, or log2(e) when the logits are pre-scaled
+  float invT, T;   // 16-bit dtypes with temperature != 1: the reference rounds logits / T to the dtype first
+  int prescale;
+  int vec_ok;
+};
+
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(const uint4& q, float (&x)[4]) {
+    x[0] = __uint_as_float(q.x);
+    x[1] = __uint_as_float(q.y);
+    x[2] = __uint_as_float(q.z);
+    x[3] = __uint_as_float(q.w);
+  }
+  static __device__ __forceinline__ float vmax(const uint4& q) {
+    return fmaxf(fmaxf(__uint_as_float(q.x), __uint_as_float(q.y)), fmaxf(__uint_as_float(q.z), __uint_as_float(q.w)));
+  }
+  static __device__ __forceinline__ float round_to(float x) { return x; }
+  static __device__ __forceinline__ float load(const void* p, size_t i) { return reinterpret_cast<const float*>(p)[i]; }
+  static __device__ __forceinline__ void store(void* p, size_t i, float x) { reinterpret_cast<float*>(p)[i] = x; }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& q, float (&x)[8]) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      x[2 * i] = __uint_as_float(w[i] << 16);
+      x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  static __device__ __forceinline__ float vmax(const uint4& q) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+    const __nv_bfloat162 m = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+    return fmaxf(__low2float(m), __high2float(m));
+  }
+  static __device__ __forceinline__ float round_to(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+  static __device__ __forceinline__ float load(const void* p, size_t i) {
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  }
+  static __device__ __forceinline__ void store(void* p, size_t i, float x) {
+    reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(x);
+  }
+};
+template <>
+struct Elem<__half> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& q, float (&x)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      x[2 * i] = f.x;
+      x[2 * i + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ float vmax(const uint4& q) {
+    const __half2* h = reinterpret_cast<const __half2*>(&q);
+    const __half2 m = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+    return fmaxf(__low2float(m), __high2float(m));
+  }
+  static __device__ __forceinline__ float round_to(float x) { return __half2float(__float2half_rn(x)); }
+  static __device__ __forceinline__ float load(const void* p, size_t i) {
+    return __half2float(reinterpret_cast<const __half*>(p)[i]);
+  }
+  static __device__ __forceinline__ void store(void* p, size_t i, float x) {
+    reinterpret_cast<__half*>(p)[i] = __float2half_rn(x);
+  }
+};
+
+// Softmax denominator with a movable shift, packed lanes (see verify.cu for the reasoning).
+struct SoftAcc {
+  uint64_t s2, k2, nc2;
+  float c, k;
+  __device__ __forceinline__ void init(float k_) {
+    k = k_;
+    k2 = f2_pack(k_, k_);
+    c = -INFINITY;
+    nc2 = f2_pack(INFINITY, INFINITY);
+    s2 = f2_pack(0.f, 0.f);
+  }
+  __device__ __forceinline__ void ensure(float m) {  // m: a maximum met so far
+    const float y = fmaf(m, k, -c);
+    if (y > 64.f) {
+      const float cn = m * k;
+      if (c != -INFINITY) {
+        const float f = ex2f(c - cn);
+        float s0, s1;
+        f2_unpack(s2, s0, s1);
+        s2 = f2_pack(s0 * f, s1 * f);
+      }
+      c = cn;
+      nc2 = f2_pack(-cn, -cn);
+    }
+  }
+  __device__ __forceinline__ void add_pair(float x0, float x1) {
+    float y0, y1;
+    f2_unpack(f2_fma(f2_pack(x0, x1), k2, nc2), y0, y1);
+    s2 = f2_add(s2, f2_pack(ex2f(y0), ex2f(y1)));
+  }
+  __device__ __forceinline__ void add_one(float x) {
+    float s0, s1;
+    f2_unpack(s2, s0, s1);
+    s0 += ex2f(fmaf(fmaxf(x, -1.0e30f), k, -c));
+    s2 = f2_pack(s0, s1);
+  }
+  __device__ __forceinline__ float sum() const {
+    float s0, s1;
+    f2_unpack(s2, s0, s1);
+    return s0 + s1;
+  }
+};
+
+__device__ __forceinline__ void combine_soft(float& c, float& s, float oc, float os) {
+  const float cn = fmaxf(c, oc);
+  float r = 0.f;
+  if (c != -INFINITY) r += s * ex2f(c - cn);
+  if (oc != -INFINITY) r += os * ex2f(oc - cn);
+  c = cn;
+  s = r;
+}
+
+// ---- per-row streaming kernel ----------------------------------------------------------------
+template <typename T, int KIND>
+__global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka) {
+  __shared__ Cand s_queue[kWarps][kQueue];
+  __shared__ int s_qn[kWarps];
+  __shared__ float s_pub[kWarps];  // each warp's j-th best value: min over warps bounds the k-th best of the row
+  __shared__ Cand s_lists[kWarps][kMaxK];
+  __shared__ float s_c[kWarps], s_s[kWarps];
+  __shared__ int s_flag;
+
+  const subspec_expand_args& a = ka.a;
+  const int L = a.leaves, V = a.vocab, k = a.k;
+  const int row = blockIdx.x;
+  const int b = row / L;
+  const T* rowp = reinterpret_cast<const T*>(a.scores) + (size_t)b * a.seq_stride + (size_t)(row - b * L) * a.row_stride;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int VN = Elem<T>::N;
+  const int jpub = (k + kWarps - 1) / kWarps;  // kWarps * jpub >= k distinct elements
+
+  WarpTopK top;
+  top.init(k);
+  SoftAcc soft;
+  soft.init(ka.kT);
+  if (lane == 0) {
+    s_qn[warp] = 0;
+    s_pub[warp] = -INFINITY;
+  }
+  __syncthreads();
+  float thr = -INFINITY;
+
+  const int nvec = ka.vec_ok ? V / VN : 0;
+  const uint4* vp = reinterpret_cast<const uint4*>(rowp);
+  for (int i0 = 0; i0 < nvec; i0 += kThreads * kUnroll) {
+    // refresh the threshold: own k-th best, and the bound the other warps have published
+    {
+      float t = s_pub[0];
+#pragma unroll
+      for (int w = 1; w < kWarps; ++w) t = fminf(t, s_pub[w]);
+      thr = fmaxf(top.kth_value(), t);
+    }
+    uint4 q[kUnroll];
+    float m[kUnroll];
+    bool have[kUnroll];
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j) {
+      const int i = i0 + threadIdx.x + j * kThreads;
+      have[j] = i < nvec;
+      if (have[j]) {
+        q[j] = ld_stream_u4(vp + i);
+        m[j] = Elem<T>::vmax(q[j]);
+      } else {
+        q[j] = make_uint4(0, 0, 0, 0);
+        m[j] = -INFINITY;
+      }
+    }
+    const float gm = fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+    if (KIND == SUBSPEC_IN_LOGITS) {
+      // With pre-scaling the sums run over round(x / T); the multiply by 1 / T used here can differ from the
+      // division by one fp32 ulp before rounding, which the k survivors (recomputed exactly below) never see.
+      soft.ensure(ka.prescale ? Elem<T>::round_to(gm * ka.invT) : gm);
+#pragma unroll
+      for (int j = 0; j < kUnroll; ++j) {
+        if (!have[j]) continue;
+        float x[VN];
+        Elem<T>::unpack(q[j], x);
+        if (ka.prescale) {
+#pragma unroll
+          for (int e = 0; e < VN; ++e) x[e] = Elem<T>::round_to(x[e] * ka.invT);
+        }
+#pragma unroll
+        for (int e = 0; e < VN; e += 2) soft.add_pair(x[e], x[e + 1]);
+      }
+    }
+    // candidates: rare after the first groups
+    if (__ballot_sync(0xffffffffu, gm >= thr)) {
+#pragma unroll
+      for (int j = 0; j < kUnroll; ++j) {
+        if (!__ballot_sync(0xffffffffu, m[j] >= thr)) continue;
+        if (m[j] >= thr) {
+          float x[VN];
+          Elem<T>::unpack(q[j], x);
+          const int base = (i0 + threadIdx.x + j * kThreads) * VN;
+#pragma unroll
+          for (int e = 0; e < VN; ++e)
+            if (x[e] >= thr) {
+              const int p = atomicAdd(&s_qn[warp], 1);
+              s_queue[warp][p] = Cand{x[e], base + e};
+            }
+        }
+        __syncwarp();
+        const int qn = s_qn[warp];
+        for (int i = 0; i < qn; ++i) {
+          const Cand cnd = s_queue[warp][i];
+          top.insert(cnd.v, cnd.id);
+        }
+        const float pub = top.value_at(jpub - 1);
+        thr = fmaxf(thr, top.kth_value());
+        __syncwarp();
+        if (lane == 0) {
+          s_qn[warp] = 0;
+          s_pub[warp] = pub;
+        }
+        __syncwarp();
+      }
+    }
+  }
+  // scalar tail (and whole unaligned rows): lane by lane through the same queue
+  for (int i0 = nvec * VN; i0 < V; i0 += kThreads) {
+    const int i = i0 + threadIdx.x;
+    float x = -INFINITY;
+    if (i < V) x = to_f32<T>(rowp[i]);
+    if (KIND == SUBSPEC_IN_LOGITS && i < V) {
+      const float xs = ka.prescale ? Elem<T>::round_to(x * ka.invT) : x;
+      soft.ensure(fmaxf(xs, -1.0e30f));
+      soft.add_one(xs);
+    }
+    thr = fmaxf(thr, top.kth_value());
+    if (__ballot_sync(0xffffffffu, i < V && x >= thr)) {
+      if (i < V && x >= thr) {
+        const int p = atomicAdd(&s_qn[warp], 1);
+        s_queue[warp][p] = Cand{x, i};
+      }
+      __syncwarp();
+      const int qn = s_qn[warp];
+      for (int t = 0; t < qn; ++t) {
+        const Cand cnd = s_queue[warp][t];
+        top.insert(cnd.v, cnd.id);
+      }
+      __syncwarp();
+      if (lane == 0) s_qn[warp] = 0;
+      __syncwarp();
+    }
+  }
+
+  // ---- merge the warps' lists and softmax sums ----
+  if (lane < k) s_lists[warp][lane] = Cand{top.v, top.id};
+  {
+    float c = soft.c, s = soft.sum();
+    if (KIND != SUBSPEC_IN_LOGITS) {
+      c = 0.f;
+      s = 1.f;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float oc = __shfl_xor_sync(0xffffffffu, c, off);
+      const float os = __shfl_xor_sync(0xffffffffu, s, off);
+      combine_soft(c, s, oc, os);
+    }
+    if (lane == 0) {
+      s_c[warp] = c;
+      s_s[warp] = s;
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    for (int w = 1; w < kWarps; ++w)
+      for (int i = 0; i < k; ++i) {
+        const Cand cnd = s_lists[w][i];
+        if (cnd.id != INT_MAX) top.insert(cnd.v, cnd.id);
+      }
+    if (lane < k) ka.rowtop[(size_t)row * k + lane] = Cand{top.v, top.id};
+    if (lane == 0) {
+      float c = s_c[0], s = s_s[0];
+      for (int w = 1; w < kWarps; ++w) combine_soft(c, s, s_c[w], s_s[w]);
+      if (KIND != SUBSPEC_IN_LOGITS) {
+        c = 0.f;
+        s = 1.f;
+      }
+      ka.rowout[row] = RowOut{c, s};
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_flag = (atomicAdd(ka.ticket + b, 1) == L - 1);
+  __syncthreads();
+  if (!s_flag) return;
+  __threadfence();
+
+  // ---- the last CTA of the sequence: scores with the reference's rounding, global top-k ----
+  if (warp == 0) {
+    WarpTopK best;
+    best.init(k);
+    const int total = L * k;
+    for (int t0 = 0; t0 < total; t0 += 32) {
+      const int t = t0 + lane;
+      float score = -INFINITY;
+      int flat = INT_MAX;
+      if (t < total) {
+        const int l = t / k;
+        const volatile Cand* src = ka.rowtop + ((size_t)b * L + l) * k + (t - l * k);
+        const float xv = src->v;
+        const int xi = src->id;
+        if (xi != INT_MAX) {
+          const volatile RowOut* ro = ka.rowout + (size_t)b * L + l;
+          float p = xv;
+          if (KIND == SUBSPEC_IN_LOGITS) {
+            const float xs = ka.prescale ? Elem<T>::round_to(__fdiv_rn(xv, ka.T)) : xv;
+            p = ex2f(fmaf(xs, ka.kT, -ro->c)) / ro->s;
+          }
+          p = Elem<T>::round_to(p);
+          const float pp = a.parent_probs ? Elem<T>::load(a.parent_probs, (size_t)b * L + l) : 1.f;
+          score = Elem<T>::round_to(p * pp);
+          flat = l * V + xi;
+        }
+      }
+      for (int src_lane = 0; src_lane < 32; ++src_lane) {
+        const float cv = __shfl_sync(0xffffffffu, score, src_lane);
+        const int ci = __shfl_sync(0xffffffffu, flat, src_lane);
+        if (ci != INT_MAX) best.insert(cv, ci);
+      }
+    }
+    if (lane < k) {
+      const size_t o = (size_t)b * k + lane;
+      const int l = best.id == INT_MAX ? 0 : best.id / V;
+      const int tok = best.id == INT_MAX ? 0 : best.id - l * V;
+      a.out_tokens[o] = tok;
+      a.out_parents[o] = l;
+      Elem<T>::store(a.out_probs, o, best.v);
+      if (a.tree_tokens) {  // Tree.add_nodes numbering: level d occupies 1 + d k ... d k + k
+        const size_t node = (size_t)b * a.tree_stride + 1 + (size_t)a.level * k + lane;
+        a.tree_tokens[node] = tok;
+        a.tree_parents[node] = a.level == 0 ? 0 : 1 + (a.level - 1) * k + l;
+        a.tree_probs[node] = best.v;
+        a.tree_depths[node] = a.level + 1;
+      }
+    }
+  }
+}
+
+// ---- tree finaliser ------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) tree_finalize_kernel(const subspec_tree_finalize_args a) {
+  extern __shared__ int sm[];
+  const int b = blockIdx.x;
+  const int n = a.n_nodes, keep = min(a.keep, a.n_nodes);
+  int* rank = sm;          // [n] rank of old node i (0 = best)
+  int* old_of = rank + n;  // [keep]
+  const size_t tb = (size_t)b * a.tree_stride;
+  const float* prob = a.tree_probs + tb;
+  const int* par = a.tree_parents + tb;
+
+  // rank by (cumulative probability desc, index asc); the root carries probability 1
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float pi = i == 0 ? 1.f : prob[i];
+    int r = 0;
+    for (int j = 0; j < n; ++j) {
+      const float pj = j == 0 ? 1.f : prob[j];
+      r += (pj > pi || (pj == pi && j < i)) ? 1 : 0;
+    }
+    rank[i] = r;
+    if (r < keep) old_of[r] = i;
+  }
+  __syncthreads();
+  const size_t ob = (size_t)b * a.keep;
+  for (int r = threadIdx.x; r < keep; r += blockDim.x) {
+    const int o = old_of[r];
+    const int p = o == 0 ? -1 : par[o];
+    const int np = (p >= 0 && rank[p] < keep) ? rank[p] : -1;
+    a.keep_idx[ob + r] = o;
+    a.tokens[ob + r] = a.tree_tokens[tb + o];
+    a.parents[ob + r] = np;
+    const int d = o == 0 ? 0 : a.tree_depths[tb + o];
+    a.depths[ob + r] = d;
+    a.probs[ob + r] = o == 0 ? 1.f : prob[o];
+    a.position_ids[ob + r] = (int64_t)d + (a.position_offset ? a.position_offset[b] : 0);
+    // ancestor-or-self row
+    uint8_t* mrow = a.mask + (ob + r) * a.keep;
+    for (int j = 0; j < a.keep; ++j) mrow[j] = 0;
+    int cur = o, guard = 0;
+    while (cur >= 0 && guard <= n) {
+      if (rank[cur] < keep) mrow[rank[cur]] = 1;
+      cur = cur == 0 ? -1 : par[cur];
+      ++guard;
+    }
+  }
+  for (int r = keep + threadIdx.x; r < a.keep; r += blockDim.x) {  // padding when the tree is smaller than `keep`
+    a.keep_idx[ob + r] = -1;
+    a.tokens[ob + r] = 0;
+    a.parents[ob + r] = -1;
+    a.depths[ob + r] = 0;
+    a.probs[ob + r] = 0.f;
+    a.position_ids[ob + r] = 0;
+    uint8_t* mrow = a.mask + (ob + r) * a.keep;
+    for (int j = 0; j < a.keep; ++j) mrow[j] = 0;
+  }
+  __syncthreads();
+  // children CSR in new numbering; a node's children keep their original relative order
+  // (ascending old index), as the reference's re-link loop leaves them (cpu_tree.py:196-199)
+  if (threadIdx.x == 0) {
+    int* off = a.child_off + (size_t)b * (a.keep + 1);
+    int* idx = a.child_idx + ob;
+    int w = 0;
+    for (int r = 0; r < keep; ++r) {
+      off[r] = w;
+      const int o = old_of[r];
+      for (int c = 0; c < n; ++c)
+        if (c != 0 && par[c] == o && rank[c] < keep) idx[w++] = rank[c];
+    }
+    for (int r = keep; r <= a.keep; ++r) off[r] = w;
+    a.n_out[b] = keep;
+  }
+}
+
+size_t align_up(size_t x, size_t al) { return (x + al - 1) / al * al; }
+
+template <typename T>
+cudaError_t launch_expand(const KArgs& ka, int grid, cudaStream_t st) {
+  if (ka.a.input_kind == SUBSPEC_IN_LOGITS)
+    expand_rows_kernel<T, SUBSPEC_IN_LOGITS><<<grid, kThreads, 0, st>>>(ka);
+  else
+    expand_rows_kernel<T, SUBSPEC_IN_PROBS><<<grid, kThreads, 0, st>>>(ka);
+  return cudaGetLastError();
+}
+
+}  // namespace
+}  // namespace subspec
+
+using namespace subspec;
+
+extern "C" int subspec_expand_scratch_bytes(int32_t batch, int32_t leaves, int32_t k, size_t* bytes) {
+  if (!bytes || batch < 0 || leaves < 1 || k < 1 || k > kMaxK) return SUBSPEC_EINVAL;
+  const size_t rows = (size_t)batch * leaves;
+  *bytes = align_up(sizeof(int) * (size_t)batch, 256) + align_up(sizeof(RowOut) * rows, 256) + sizeof(Cand) * rows * k;
+  return SUBSPEC_OK;
+}
+
+extern "C" int subspec_expand_step(const subspec_expand_args* args, subspec_stream_t stream) {
+  if (!args || args->struct_size != sizeof(subspec_expand_args)) return SUBSPEC_EINVAL;
+  const subspec_expand_args& a = *args;
+  if (a.batch < 0 || a.leaves < 1 || a.vocab < 1 || a.k < 1) return SUBSPEC_EINVAL;
+  if (a.k > kMaxK || a.k > a.vocab || a.vocab > (1 << 20) || (int64_t)a.leaves * a.vocab > INT_MAX)
+    return SUBSPEC_EUNSUPPORTED;
+  if (a.dtype != SUBSPEC_F32 && a.dtype != SUBSPEC_BF16 && a.dtype != SUBSPEC_F16) return SUBSPEC_EINVAL;
+  if (a.input_kind != SUBSPEC_IN_LOGITS && a.input_kind != SUBSPEC_IN_PROBS) return SUBSPEC_EINVAL;
+  if (a.batch == 0) return SUBSPEC_OK;
+  if (!a.scores || !a.out_tokens || !a.out_probs || !a.out_parents || !a.scratch) return SUBSPEC_EINVAL;
+  if (!(a.temperature > 0.0)) return SUBSPEC_EINVAL;
+  if (a.tree_tokens && (!a.tree_parents || !a.tree_probs || !a.tree_depths || a.level < 0 ||
+                        1 + (int64_t)(a.level + 1) * a.k > a.tree_stride))
+    return SUBSPEC_EINVAL;
+  size_t need = 0;
+  subspec_expand_scratch_bytes(a.batch, a.leaves, a.k, &need);
+  if (a.scratch_bytes < need || (reinterpret_cast<uintptr_t>(a.scratch) & 255u)) return SUBSPEC_ESCRATCH;
+  KArgs ka;
+  ka.a = a;
+  char* p = reinterpret_cast<char*>(a.scratch);
+  const size_t rows = (size_t)a.batch * a.leaves;
+  ka.ticket = reinterpret_cast<int*>(p);
+  p += align_up(sizeof(int) * (size_t)a.batch, 256);
+  ka.rowout = reinterpret_cast<RowOut*>(p);
+  p += align_up(sizeof(RowOut) * rows, 256);
+  ka.rowtop = reinterpret_cast<Cand*>(p);
+  const size_t esz = a.dtype == SUBSPEC_F32 ? 4 : 2;
+  ka.prescale = (esz == 2 && a.input_kind == SUBSPEC_IN_LOGITS && a.temperature != 1.0) ? 1 : 0;
+  ka.T = (float)a.temperature;
+  ka.invT = 1.0f / ka.T;
+  ka.kT = ka.prescale ? kLog2e : (float)(1.4426950408889634 / a.temperature);
+  ka.vec_ok = ((reinterpret_cast<uintptr_t>(a.scores) & 15u) == 0) && ((a.seq_stride * esz) % 16 == 0) &&
+              ((a.row_stride * esz) % 16 == 0);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int rc = cuda_check(cudaMemsetAsync(ka.ticket, 0, sizeof(int) * (size_t)a.batch, st));
+  if (rc) return rc;
+  cudaError_t e;
+  switch (a.dtype) {
+    case SUBSPEC_F32:
+      e = launch_expand<float>(ka, (int)rows, st);
+      break;
+    case SUBSPEC_BF16:
+      e = launch_expand<__nv_bfloat16>(ka, (int)rows, st);
+      break;
+    default:
+      e = launch_expand<__half>(ka, (int)rows, st);
+      break;
+  }
+  return cuda_check(e);
+}
+
+extern "C" int subspec_tree_finalize(const subspec_tree_finalize_args* args, subspec_stream_t stream) {
+  if (!args || args->struct_size != sizeof(subspec_tree_finalize_args)) return SUBSPEC_EINVAL;
+  const subspec_tree_finalize_args& a = *args;
+  if (a.batch < 0 || a.n_nodes < 1 || a.keep < 1 || a.tree_stride < a.n_nodes) return SUBSPEC_EINVAL;
+  if (a.n_nodes > 4096 || a.keep > 1024) return SUBSPEC_EUNSUPPORTED;
+  if (a.batch == 0) return SUBSPEC_OK;
+  if (!a.tree_tokens || !a.tree_parents || !a.tree_probs || !a.tree_depths || !a.keep_idx || !a.tokens ||
+      !a.parents || !a.depths || !a.probs || !a.position_ids || !a.mask || !a.child_off || !a.child_idx || !a.n_out)
+    return SUBSPEC_EINVAL;
+  const size_t smem = sizeof(int) * ((size_t)a.n_nodes + a.keep);
+  tree_finalize_kernel<<<a.batch, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  return cuda_check(cudaGetLastError());
+}

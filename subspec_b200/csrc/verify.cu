@@ -88,26 +88,6 @@ __device__ __forceinline__ RowStat warp_reduce(RowStat v) {
   return v;
 }
 
-// ---- packed fp32x2 arithmetic (sm_100: two fp32 lanes per instruction) -------------------
-__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-
 // Headroom (log2 domain) a new row maximum may have over the thread's reference shift
 // before the accumulators are rescaled: 2^64 * vocab still sits far below FLT_MAX.
 constexpr float kRefHeadroom = 64.f;

@@ -254,6 +254,60 @@ def gen_kv(ref, out_dir: Path):
     print(f"kv: {len(cases)} cases")
 
 
+def gen_expand(ref, out_dir: Path):
+    """Drive the reference's own expansion helpers (one sequence at a time, as the reference does)."""
+    from types import SimpleNamespace
+
+    db, ct = ref["db"], ref["ct"]
+    cases, small = [], {}
+    cfgs = [(300, 4, 5, "float32", 1.0, 12), (300, 4, 5, "bfloat16", 1.0, 12), (1000, 6, 4, "float16", 0.7, 16),
+            (2048, 16, 3, "float32", 1.0, 32), (97, 3, 6, "float32", 0.2, 10)]
+    for ci, (V, k, depth, dtype, T, keep) in enumerate(cfgs):
+        gen = torch.Generator().manual_seed(700 + ci)
+        dt = DT[dtype]
+        holder = SimpleNamespace()
+        tree_data = db.TreeData()
+        mask_cache = db.TreeMaskCache(prefix_len=5, sample_len=k, max_cache_len=None, dtype=torch.float32,
+                                      device="cpu")
+        parent_probs = torch.ones(1, 1, dtype=dt)
+        steps = []
+        for d in range(depth):
+            L = 1 if d == 0 else k
+            logits = (torch.randn(1, L, V, generator=gen) * 3.0).to(dt)
+            probs = torch.softmax(logits / T, dim=-1)
+            tok, val, par = db.DraftModelBase._topk_flatten(holder, probs, parent_probs, k)
+            tree_data.update(tok, val, par)
+            mask = mask_cache.update_tree_mask(par, return_invert=False)
+            small[f"c{ci}/logits{d}"] = logits.float().numpy()
+            steps.append(dict(tokens=tok.tolist(), parents=par.tolist(), probs=val.float().tolist(),
+                              mask=mask[0, 0].to(torch.uint8).tolist()))
+            parent_probs = val
+        tree = ct.Tree(torch.tensor(7), dt)
+        tree.add_nodes(*tree_data.get_data())
+        full = tree.get_tree_data()
+        full_mask = tree.create_attention_mask(prefix_length=3)
+        probs_all = torch.tensor([n.cumulative_probability for n in tree.nodes], dtype=dt)
+        distinct = len(set(probs_all.float().tolist())) == len(tree.nodes)
+        keep_idx = tree.prune_to_top_n(keep)
+        pruned = tree.get_tree_data()
+        cases.append(dict(
+            name=f"c{ci}", vocab=V, k=k, depth=depth, dtype=dtype, temperature=T, keep=keep, steps=steps,
+            full=dict(token_ids=full["token_ids"].tolist(), depths=full["depths"].tolist(),
+                      parent_indices=full["parent_indices"].tolist(),
+                      probs=full["cumulative_probabilities"].float().tolist(),
+                      mask=full_mask[0, 0].to(torch.uint8).tolist()),
+            probs_distinct=distinct,
+            pruned=dict(keep_idx=keep_idx.tolist(), token_ids=pruned["token_ids"].tolist(),
+                        depths=pruned["depths"].tolist(), parent_indices=pruned["parent_indices"].tolist(),
+                        probs=pruned["cumulative_probabilities"].float().tolist(),
+                        children=[list(n.children) for n in tree.nodes],
+                        leaves=list(tree.available_leaves),
+                        mask=tree.create_attention_mask()[0, 0].to(torch.uint8).tolist())))
+    (out_dir / "expand_cases.json").write_text(json.dumps({"cases": cases}))
+    np.savez_compressed(out_dir / "expand_small.npz", **small)
+    print(f"expand: {len(cases)} cases; cumulative probabilities all distinct: {[c['probs_distinct'] for c in cases]}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -263,6 +317,8 @@ def main():
     torch.set_num_threads(8)
     if args.only in (None, "verify"):
         gen_verify(ref, HERE)
+    if args.only in (None, "expand"):
+        gen_expand(ref, HERE)
     if args.only in (None, "kv"):
         gen_kv(ref, HERE)
     if args.only in (None, "lossy_unit"):

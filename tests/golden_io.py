@@ -61,3 +61,18 @@ def kv_pool(case) -> torch.Tensor:
     gen = torch.Generator().manual_seed(case["seed"])
     shape = (case["layers"], case["pages"], 2, case["page_len"], case["heads"], case["head_dim"])
     return torch.randn(shape, generator=gen).to(DT[case["dtype"]])
+
+
+@lru_cache(maxsize=None)
+def expand_cases():
+    return json.loads((GOLDEN / "expand_cases.json").read_text())["cases"]
+
+
+@lru_cache(maxsize=None)
+def _expand_small():
+    return dict(np.load(GOLDEN / "expand_small.npz"))
+
+
+def expand_logits(case, step: int) -> torch.Tensor:
+    """[1, leaves, vocab] draft logits of one depth step, in the case's dtype."""
+    return torch.from_numpy(_expand_small()[f"{case['name']}/logits{step}"]).to(DT[case["dtype"]])
