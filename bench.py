@@ -50,6 +50,7 @@ def parse_args():
     ap.add_argument("--kv-tokens", type=int, default=KV_TOKENS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the side measurements of the other kernels")
     ap.add_argument("--cpu-sample", type=int, default=0, help="sequences per CPU-baseline sample (0 = auto)")
     return ap.parse_args()
 
@@ -262,6 +263,65 @@ def workload_config(args, total_seqs, world, per_rank):
 
 
 # --------------------------------------------------------------------------------------
+# side measurements: the other kernels of the path on their own configs (not part of `value`)
+# --------------------------------------------------------------------------------------
+def _time_ms(fn, iters=10, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def extras(device, peak_gbs):
+    """Config 3 (one expansion step) and config 2 (stochastic verify), each on inputs larger than L2."""
+    from subspec_b200 import synthetic
+    from subspec_b200.draft import topk_sampling_from_logits
+    from subspec_b200.tree import Tree
+    from subspec_b200.verify import flatten_tree, get_workspace
+    from subspec_b200 import _lib
+
+    out = {}
+    gen = torch.Generator(device=device).manual_seed(3)
+    # config 3: 32 sequences x 16 leaves x 128256 bf16 draft logits, k = 16
+    B, L, V, k = 32, 16, 128256, 16
+    logits = (torch.randn(B, L, V, generator=gen, device=device) * 3.0).to(torch.bfloat16)
+    pp = torch.rand(B, L, generator=gen, device=device).to(torch.bfloat16)
+    ms = _time_ms(lambda: topk_sampling_from_logits(logits, pp, k, 1.0))
+    gbs = logits.numel() * 2 / (ms * 1e-3) / 1e9
+    out["expand_step_config3"] = {"ms": ms, "GB/s": gbs, "frac_of_measured_peak": gbs / peak_gbs,
+                                  "bytes": logits.numel() * 2}
+    del logits
+    # config 2: 64 sequences x 128-node trees, bf16 logits N(0, 2.5^2), T = 1, top-p 0.9, injected uniforms
+    B, N, V = 64, 128, 152064
+    cgen = torch.Generator().manual_seed(4)
+    flats = []
+    for _ in range(B):
+        st = synthetic.random_tree(N, 10, 8, V, cgen)
+        t = Tree.from_arrays(st.token_ids.tolist(), st.parents.tolist())
+        tok, off, idx = flatten_tree(t, 0, limit=N, restrict=False)
+        flats.append((tok, off, idx, N, 0))
+    logits = torch.empty(B, N, V, dtype=torch.bfloat16, device=device)
+    for b in range(B):
+        logits[b] = (torch.randn(N, V, generator=gen, device=device) * 2.5).to(torch.bfloat16)
+    ws = get_workspace(B, N, device)
+    ws.set_trees(flats)
+    ws.uniforms.uniform_(generator=gen)
+    ms = _time_ms(lambda: ws.run(logits, input_kind=_lib.IN_LOGITS, method=_lib.VERIFY_EXACT, do_sample=True,
+                                 temperature=1.0, top_p=0.9), iters=5, warm=2)
+    ws.fetch()
+    gbs = logits.numel() * 2 / (ms * 1e-3) / 1e9
+    out["stochastic_verify_config2"] = {"ms": ms, "GB/s": gbs, "frac_of_measured_peak": gbs / peak_gbs,
+                                        "bytes": logits.numel() * 2}
+    return out
+
+
+# --------------------------------------------------------------------------------------
 # native arm
 # --------------------------------------------------------------------------------------
 def main():
@@ -470,6 +530,12 @@ def main():
                            "steps": e2e["steps"],
                            "note": "per GPU and step; logits copied from pinned host memory wave by wave "
                                    "(double-buffered), results read back to pinned host memory"}
+        if world == 1 and not args.no_extras:
+            for w in waves:
+                w[0].pool = None
+            del waves[:]
+            torch.cuda.empty_cache()
+            line["other_kernels"] = extras(device, peak_gbs)
         if world == 1 and not args.no_cpu_baseline:
             sample = args.cpu_sample or 8
             v, desc = cpu_baseline(sample, 3, args.variant)

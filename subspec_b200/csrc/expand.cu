@@ -71,6 +71,22 @@ struct WarpTopK {
   }
 };
 
+// k-th largest (k = 1..32) of the 32 lane values: bitonic sort across the warp, descending.
+__device__ __forceinline__ float warp_kth_largest(float v, int k) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      const float o = __shfl_xor_sync(0xffffffffu, v, stride);
+      const bool desc = (lane & size) == 0;       // direction of this bitonic block
+      const bool lower = (lane & stride) == 0;    // this lane keeps the "first" element of the pair
+      v = (desc == lower) ? fmaxf(v, o) : fminf(v, o);
+    }
+  }
+  return __shfl_sync(0xffffffffu, v, k - 1);
+}
+
 struct RowOut {  // per (sequence, leaf) row, in scratch
   float c, s;    // softmax shift (log2 domain) and denominator; unused for probabilities in
 };
@@ -262,6 +278,11 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
       }
     }
     const float gm = fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+    if (i0 == 0) {
+      // First group: the k-th largest of the 32 lane maxima is k distinct elements' worth of evidence that the
+      // warp's k-th best is at least that, which keeps the first round of candidates to a few dozen.
+      thr = fmaxf(thr, warp_kth_largest(gm, k));
+    }
     if (KIND == SUBSPEC_IN_LOGITS) {
       // With pre-scaling the sums run over round(x / T); the multiply by 1 / T used here can differ from the
       // division by one fp32 ulp before rounding, which the k survivors (recomputed exactly below) never see.
@@ -361,11 +382,28 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
   }
   __syncthreads();
   if (warp == 0) {
-    for (int w = 1; w < kWarps; ++w)
-      for (int i = 0; i < k; ++i) {
-        const Cand cnd = s_lists[w][i];
-        if (cnd.id != INT_MAX) top.insert(cnd.v, cnd.id);
+    // Fold the other warps' lists into this one.  Entry `lane` of every list sits in this lane; the k-th
+    // largest of the per-lane maxima bounds the merged k-th best from below and filters most entries out.
+    float lv[kWarps - 1];
+    int li[kWarps - 1];
+    float lmax = lane < k ? top.v : -INFINITY;
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) {
+      const Cand cnd = lane < k ? s_lists[w][lane] : Cand{-INFINITY, INT_MAX};
+      lv[w - 1] = cnd.v;
+      li[w - 1] = cnd.id;
+      lmax = fmaxf(lmax, cnd.v);
+    }
+    const float mthr = warp_kth_largest(lmax, k);
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) {
+      uint32_t todo = __ballot_sync(0xffffffffu, li[w - 1] != INT_MAX && lv[w - 1] >= mthr);
+      while (todo) {
+        const int src = __ffs(todo) - 1;
+        todo &= todo - 1;
+        top.insert(__shfl_sync(0xffffffffu, lv[w - 1], src), __shfl_sync(0xffffffffu, li[w - 1], src));
       }
+    }
     if (lane < k) ka.rowtop[(size_t)row * k + lane] = Cand{top.v, top.id};
     if (lane == 0) {
       float c = s_c[0], s = s_s[0];
@@ -389,10 +427,16 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
     WarpTopK best;
     best.init(k);
     const int total = L * k;
-    for (int t0 = 0; t0 < total; t0 += 32) {
-      const int t = t0 + lane;
-      float score = -INFINITY;
-      int flat = INT_MAX;
+    constexpr int kSlots = 8;  // 256 candidates per round
+    for (int t0 = 0; t0 < total; t0 += 32 * kSlots) {
+    float sc[kSlots];
+    int fl[kSlots];
+    float lmax = -INFINITY;
+#pragma unroll
+    for (int sidx = 0; sidx < kSlots; ++sidx) {
+      const int t = t0 + sidx * 32 + lane;
+      sc[sidx] = -INFINITY;
+      fl[sidx] = INT_MAX;
       if (t < total) {
         const int l = t / k;
         const volatile Cand* src = ka.rowtop + ((size_t)b * L + l) * k + (t - l * k);
@@ -407,15 +451,23 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
           }
           p = Elem<T>::round_to(p);
           const float pp = a.parent_probs ? Elem<T>::load(a.parent_probs, (size_t)b * L + l) : 1.f;
-          score = Elem<T>::round_to(p * pp);
-          flat = l * V + xi;
+          sc[sidx] = Elem<T>::round_to(p * pp);
+          fl[sidx] = l * V + xi;
+          lmax = fmaxf(lmax, sc[sidx]);
         }
       }
-      for (int src_lane = 0; src_lane < 32; ++src_lane) {
-        const float cv = __shfl_sync(0xffffffffu, score, src_lane);
-        const int ci = __shfl_sync(0xffffffffu, flat, src_lane);
-        if (ci != INT_MAX) best.insert(cv, ci);
+    }
+    // k lanes hold a candidate at least this good; later rounds also have to beat the running k-th best
+    const float gthr = fmaxf(warp_kth_largest(lmax, k), best.kth_value());
+#pragma unroll
+    for (int sidx = 0; sidx < kSlots; ++sidx) {
+      uint32_t todo = __ballot_sync(0xffffffffu, fl[sidx] != INT_MAX && sc[sidx] >= gthr);
+      while (todo) {
+        const int src = __ffs(todo) - 1;
+        todo &= todo - 1;
+        best.insert(__shfl_sync(0xffffffffu, sc[sidx], src), __shfl_sync(0xffffffffu, fl[sidx], src));
       }
+    }
     }
     if (lane < k) {
       const size_t o = (size_t)b * k + lane;
@@ -535,7 +587,8 @@ extern "C" int subspec_expand_step(const subspec_expand_args* args, subspec_stre
   if (!args || args->struct_size != sizeof(subspec_expand_args)) return SUBSPEC_EINVAL;
   const subspec_expand_args& a = *args;
   if (a.batch < 0 || a.leaves < 1 || a.vocab < 1 || a.k < 1) return SUBSPEC_EINVAL;
-  if (a.k > kMaxK || a.k > a.vocab || a.vocab > (1 << 20) || (int64_t)a.leaves * a.vocab > INT_MAX)
+  if (a.k > kMaxK || a.k > a.vocab || a.vocab > (1 << 20) || (int64_t)a.leaves * a.vocab > INT_MAX ||
+      a.leaves > kMaxK)
     return SUBSPEC_EUNSUPPORTED;
   if (a.dtype != SUBSPEC_F32 && a.dtype != SUBSPEC_BF16 && a.dtype != SUBSPEC_F16) return SUBSPEC_EINVAL;
   if (a.input_kind != SUBSPEC_IN_LOGITS && a.input_kind != SUBSPEC_IN_PROBS) return SUBSPEC_EINVAL;
