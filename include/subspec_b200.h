@@ -376,6 +376,47 @@ typedef struct subspec_tree_finalize_args {
 
 SUBSPEC_API int subspec_tree_finalize(const subspec_tree_finalize_args* args, subspec_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * W4A16 group-wise dequant GEMM (the HQQ 4-bit draft linear).
+ *
+ *   y[m, n] = sum_k x[m, k] * (q[n, k] - zero[n, k / 64]) * scale[n, k / 64]
+ *
+ * Replaces the forward of the modules that HqqQuantizer.quantize_model installs
+ * (specdecodes/helpers/quantizers/hqq/__init__.py:17-119: hqq's
+ * HQQLinear(nbits=4, group_size=64, axis=1) patched by
+ * prepare_for_inference(backend="gemlite"); recipe
+ * specdecodes/helpers/recipes/subspec/hqq_4bit_postspec.py:21-34).  hqq and
+ * gemlite are third-party and not part of the reference tree; the arithmetic
+ * above is what their 4-bit, group-64, axis-1 format defines.
+ *
+ * subspec_w4a16_pack converts the interchange format -- qweight int32
+ * [n, k / 8], nibble i of word j holding q[n, 8 j + i]; scale and zero fp16
+ * [n, k / 64] -- into the tiled layout the kernel streams (once, at
+ * quantisation time).  subspec_w4a16_gemm takes bf16 activations x [m, k]
+ * (row stride x_stride elements) and writes bf16 y [m, n].  Arithmetic: weights
+ * are dequantised to fp16, activations converted to fp16 (clamped to the fp16
+ * range), products accumulated in fp32 on the tensor cores.
+ * Limits: 1 <= m <= 256, n % 128 == 0, k % 64 == 0.
+ * ---------------------------------------------------------------------- */
+typedef struct subspec_w4a16_args {
+  uint32_t struct_size;
+  int32_t m, n, k;
+  const void* x; /* bf16 [m, k] */
+  int64_t x_stride;
+  const void* packed; /* subspec_w4a16_pack output, 16-byte aligned */
+  void* y;            /* bf16 [m, n] */
+  int64_t y_stride;
+  void* scratch; /* subspec_w4a16_scratch_bytes(m, n, k), 256-byte aligned, no initialisation needed */
+  size_t scratch_bytes;
+  uint32_t* dev_status;
+} subspec_w4a16_args;
+
+SUBSPEC_API int subspec_w4a16_packed_bytes(int32_t n, int32_t k, size_t* bytes);
+SUBSPEC_API int subspec_w4a16_pack(const void* qweight, const void* scale, const void* zero, void* packed,
+                                   int32_t n, int32_t k, subspec_stream_t stream);
+SUBSPEC_API int subspec_w4a16_scratch_bytes(int32_t m, int32_t n, int32_t k, size_t* bytes);
+SUBSPEC_API int subspec_w4a16_gemm(const subspec_w4a16_args* args, subspec_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -102,6 +102,16 @@ class TreeFinalizeArgs(C.Structure):
     ]
 
 
+class W4A16Args(C.Structure):
+    """Mirror of `subspec_w4a16_args`."""
+
+    _fields_ = [
+        ("struct_size", _u32), ("m", _i32), ("n", _i32), ("k", _i32), ("x", _vp), ("x_stride", _i64),
+        ("packed", _vp), ("y", _vp), ("y_stride", _i64), ("scratch", _vp), ("scratch_bytes", C.c_size_t),
+        ("dev_status", _vp),
+    ]
+
+
 # every symbol include/subspec_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "subspec_version": (C.c_char_p, []),
@@ -114,6 +124,10 @@ SYMBOLS = {
     "subspec_expand_scratch_bytes": (C.c_int, [_i32, _i32, _i32, C.POINTER(C.c_size_t)]),
     "subspec_expand_step": (C.c_int, [C.POINTER(ExpandArgs), _vp]),
     "subspec_tree_finalize": (C.c_int, [C.POINTER(TreeFinalizeArgs), _vp]),
+    "subspec_w4a16_packed_bytes": (C.c_int, [_i32, _i32, C.POINTER(C.c_size_t)]),
+    "subspec_w4a16_pack": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),
+    "subspec_w4a16_scratch_bytes": (C.c_int, [_i32, _i32, _i32, C.POINTER(C.c_size_t)]),
+    "subspec_w4a16_gemm": (C.c_int, [C.POINTER(W4A16Args), _vp]),
 }
 
 _lib = None

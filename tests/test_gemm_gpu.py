@@ -1,0 +1,83 @@
+"""W4A16 dequant GEMM on tcgen05: against the fp32 restatement, max rel err 1e-2 (bf16 tolerance)."""
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import gemm_oracle as go
+from subspec_b200 import quant
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2  # max |y - y_ref| / max |y_ref|, the stated bf16 tolerance
+
+
+def _rel_err(y, ref):
+    return float((y.float().cpu() - ref).abs().max() / ref.abs().max())
+
+
+@pytest.mark.parametrize("n,k", [(512, 3584), (3584, 3584), (18944, 3584), (3584, 18944)])
+@pytest.mark.parametrize("m", [16, 64, 256])
+def test_config4_shapes(cuda_lib, n, k, m):
+    qweight, scale, zero, x = go.config4_case(n, k, m, seed=n + k + m)
+    packed = quant.pack(qweight.cuda(), scale.cuda(), zero.cuda())
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = quant.w4a16_matmul(x.cuda(), packed, n, k, status=status)
+    assert int(status.item()) == 0
+    ref = go.w4a16_matmul(x, qweight, scale, zero)
+    assert y.shape == (m, n) and y.dtype == torch.bfloat16
+    assert _rel_err(y, ref) < TOL
+    # a second call on the same scratch gives the same bits (tickets reset, no stale partials)
+    y2 = quant.w4a16_matmul(x.cuda(), packed, n, k, status=status)
+    assert torch.equal(y, y2)
+
+
+def test_small_and_ragged_m(cuda_lib):
+    for m, n, k in [(1, 128, 64), (3, 256, 128), (17, 384, 640), (100, 128, 4096), (255, 640, 192)]:
+        qweight, scale, zero, x = go.config4_case(n, k, m, seed=m)
+        y = quant.w4a16_matmul(x.cuda(), quant.pack(qweight.cuda(), scale.cuda(), zero.cuda()), n, k)
+        assert _rel_err(y, go.w4a16_matmul(x, qweight, scale, zero)) < TOL, (m, n, k)
+    # linearity in x: f(2x) = 2 f(x) exactly (powers of two commute with every rounding involved)
+    qweight, scale, zero, x = go.config4_case(256, 512, 32, seed=9)
+    packed = quant.pack(qweight.cuda(), scale.cuda(), zero.cuda())
+    y1 = quant.w4a16_matmul(x.cuda(), packed, 256, 512)
+    y2 = quant.w4a16_matmul((x * 2).cuda(), packed, 256, 512)
+    assert torch.equal(y2.float(), y1.float() * 2)
+    with pytest.raises(ValueError):
+        quant.w4a16_matmul(x.cuda()[:, :100].contiguous(), packed, 256, 100)  # K not a multiple of 64
+
+
+def test_quantizer_hook_replaces_linears(cuda_lib):
+    """HqqQuantizer.quantize_model swaps tagged nn.Linear modules; the forward matches dequantised fp32 math."""
+    torch.manual_seed(0)
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj = nn.Linear(256, 384, bias=True)
+            self.o_proj = nn.Linear(384, 256, bias=False)
+            self.norm = nn.LayerNorm(256)
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = nn.ModuleList([Block(), Block()])
+
+    net = Net().cuda()
+    ref_w = net.layers[1].q_proj.weight.detach().clone()
+    ref_b = net.layers[1].q_proj.bias.detach().clone()
+    cfg = {f"layers.{i}.{p}": quant.BaseQuantizeConfig(nbits=4, group_size=64, axis=1)
+           for i in range(2) for p in ("q_proj", "o_proj")}
+    quant.HqqQuantizer.quantize_model(net, cfg, compute_dtype=torch.bfloat16, device="cuda")
+    assert isinstance(net.layers[1].q_proj, quant.W4A16Linear) and isinstance(net.layers[0].norm, nn.LayerNorm)
+    x = torch.randn(2, 5, 256, device="cuda", dtype=torch.bfloat16)
+    y = net.layers[1].q_proj(x)
+    assert y.shape == (2, 5, 384) and y.dtype == torch.bfloat16
+    qweight, scale, zero = quant.quantize_weight(ref_w)
+    ref = go.w4a16_matmul(x.reshape(-1, 256).cpu(), qweight.cpu(), scale.cpu(), zero.cpu()) + ref_b.float().cpu()
+    assert _rel_err(y.reshape(-1, 384), ref) < TOL
+    # 4-bit round-to-nearest keeps the layer close to the original weights
+    full = x.reshape(-1, 256).float() @ ref_w.float().t() + ref_b.float()
+    assert _rel_err(y.reshape(-1, 384), full.cpu()) < 0.15
+    with pytest.raises(ValueError):
+        quant.HqqQuantizer.quantize_model(Net().cuda(), {"layers.0.q_proj": quant.BaseQuantizeConfig(nbits=8)}, None,
+                                          "cuda")
