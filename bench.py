@@ -278,7 +278,7 @@ def _time_ms(fn, iters=10, warm=3):
     return a.elapsed_time(b) / iters
 
 
-def extras(device, peak_gbs):
+def extras(device, peak_gbs, peak_tf):
     """Config 3 (one expansion step) and config 2 (stochastic verify), each on inputs larger than L2."""
     from subspec_b200 import synthetic
     from subspec_b200.draft import topk_sampling_from_logits
@@ -318,6 +318,48 @@ def extras(device, peak_gbs):
     gbs = logits.numel() * 2 / (ms * 1e-3) / 1e9
     out["stochastic_verify_config2"] = {"ms": ms, "GB/s": gbs, "frac_of_measured_peak": gbs / peak_gbs,
                                         "bytes": logits.numel() * 2}
+    del logits
+    # config 4: HQQ W4A16 GEMM on the Qwen2.5-7B linear shapes; roofline time = max(bytes / HBM, flops / tensor)
+    from oracle.gemm_oracle import config4_case
+    from subspec_b200 import quant
+
+    gemm = {}
+    reps = 20
+    for name, (n, k) in {"qo": (3584, 3584), "kv": (512, 3584), "gate_up": (18944, 3584),
+                         "down": (3584, 18944)}.items():
+        qweight, scale, zero, _ = config4_case(n, k, 1, seed=n + k)
+        # a set of distinct weight copies larger than L2, cycled, so that every call streams from HBM
+        copies = max(2, int(200e6 // (n * k * 0.5625)) + 1)
+        packed = [quant.pack(qweight.cuda(), scale.cuda(), zero.cuda()) for _ in range(copies)]
+        for m in (16, 64, 256):
+            x = torch.randn(m, k, generator=gen, device=device).to(torch.bfloat16)
+            state = {"i": 0}
+
+            def call():
+                quant.w4a16_matmul(x, packed[state["i"] % copies], n, k)
+                state["i"] += 1
+
+            call()
+            torch.cuda.synchronize()
+            graph_ok = True
+            try:
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    for _ in range(reps):
+                        call()
+                ms = _time_ms(gr.replay, iters=5, warm=2) / reps
+            except Exception:
+                graph_ok = False
+                torch.cuda.synchronize()
+                ms = _time_ms(call, iters=reps, warm=3)
+            nbytes = n * k * 0.5625 + 2 * m * k + 2 * m * n
+            flops = 2.0 * m * n * k
+            t_roof = max(nbytes / (peak_gbs * 1e9), flops / (peak_tf * 1e12))
+            gemm[f"{name}_m{m}"] = {"us": ms * 1e3, "roofline_us": t_roof * 1e6, "frac": t_roof / (ms * 1e-3),
+                                    "TFLOP/s": flops / (ms * 1e-3) / 1e12, "GB/s": nbytes / (ms * 1e-3) / 1e9,
+                                    "timed": "cuda graph of %d calls" % reps if graph_ok else "eager"}
+        del packed
+    out["w4a16_gemm_config4"] = gemm
     return out
 
 
@@ -535,7 +577,7 @@ def main():
                 w[0].pool = None
             del waves[:]
             torch.cuda.empty_cache()
-            line["other_kernels"] = extras(device, peak_gbs)
+            line["other_kernels"] = extras(device, peak_gbs, float(peaks.get("bf16_tflops", 1590.0)))
         if world == 1 and not args.no_cpu_baseline:
             sample = args.cpu_sample or 8
             v, desc = cpu_baseline(sample, 3, args.variant)

@@ -32,8 +32,10 @@ constexpr int kTileN = 128;      // weight rows per CTA = MMA M
 constexpr int kBlockK = 64;      // K per stage = one quantisation group = one 128-byte swizzle row of fp16
 constexpr int kRawBytes = kTileN * 32 + kTileN * 4;  // nibbles + (scale, -zero*scale) half2 per row
 constexpr int kATileBytes = kTileN * 128;
-constexpr int kThreads = 256;
+constexpr int kDeqWarps = 16;        // warps 4..19 dequantise (four threads per weight row) and run the epilogue
+constexpr int kThreads = 128 + 32 * kDeqWarps;
 constexpr int kMaxM = 256;
+constexpr int kMaxRing = 32;
 
 struct GemmArgs {
   const unsigned char* wpk;  // packed weights: [N/128][K/64] blocks of kRawBytes
@@ -42,9 +44,19 @@ struct GemmArgs {
   float* partial;            // [tiles][splits][Mpad][128]
   int* ticket;               // [tiles]
   uint32_t* dev_status;
-  int M, Mpad, N, K, kblocks, splits, stages;
+  int M, Mpad, N, K, kblocks, splits, ring_a, ring_b, ring_raw;
   int64_t y_stride;
 };
+
+#ifdef SUBSPEC_GEMM_PROFILE
+__device__ long long g_prof[16];
+#define PROF_T0 const long long prof_t0 = clock64()
+#define PROF_ADD(slot) \
+  if (blockIdx.x == 0 && blockIdx.y == 0) atomicAdd((unsigned long long*)&g_prof[slot], (unsigned long long)(clock64() - prof_t0))
+#else
+#define PROF_T0
+#define PROF_ADD(slot)
+#endif
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t it = 0; it < kSpinLimit; ++it) {
@@ -180,16 +192,19 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
   // the swizzle atoms must sit on 1024-byte boundaries of the shared-memory address space
   unsigned char* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
-  __shared__ __align__(8) uint64_t raw_full[8], raw_empty[8], a_full[8], ab_empty[8], acc_full;
+  __shared__ __align__(8) uint64_t raw_full[kMaxRing], raw_empty[kMaxRing], b_full[kMaxRing], b_empty[kMaxRing],
+      a_full[kMaxRing], a_empty[kMaxRing], acc_full;
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ int s_last;
 
-  const int stages = g.stages;
+  // Three rings with their own depths: packed weight blocks (deep: this is the HBM stream), activation
+  // blocks (read by the tensor core) and dequantised fp16 tiles (written here, read by the tensor core).
+  const int Ra = g.ring_a, Rb = g.ring_b, Rr = g.ring_raw;
   const int b_bytes = g.Mpad * 128;
-  // ring layout: [stage][A tile 16 KB | B block Mpad*128 | raw block], each piece 1024-byte aligned
-  const int raw_off = kATileBytes + b_bytes;
-  const int stage_bytes = (raw_off + kRawBytes + 1023) / 1024 * 1024;
+  unsigned char* a_ring = smem;                                  // Ra x 16 KB, 1024-aligned
+  unsigned char* b_ring = a_ring + (size_t)Ra * kATileBytes;     // Rb x Mpad*128 (a multiple of 2 KB)
+  unsigned char* raw_ring = b_ring + (size_t)Rb * b_bytes;       // Rr x 4608 B
   const int tile = blockIdx.x, split = blockIdx.y;
   const int kb_per = (g.kblocks + g.splits - 1) / g.splits;
   const int kb0 = min(split * kb_per, g.kblocks), kb1 = min(kb0 + kb_per, g.kblocks);
@@ -199,11 +214,13 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
   while ((int)ncols < g.Mpad) ncols <<= 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
+    for (int s = 0; s < kMaxRing; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], 128);
-      mbar_init(&a_full[s], 128);
-      mbar_init(&ab_empty[s], 1);
+      mbar_init(&raw_empty[s], kDeqWarps);
+      mbar_init(&b_full[s], 1);
+      mbar_init(&b_empty[s], 1);
+      mbar_init(&a_full[s], kDeqWarps);
+      mbar_init(&a_empty[s], 1);
     }
     mbar_init(&acc_full, 1);
     mbar_init_fence();
@@ -222,17 +239,29 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
   volatile int* abort_flag = &s_abort;
 
   if (warp == 0) {
-    // ---- TMA producer ----
+    // ---- TMA producer, packed weights ----
     if (lane == 0) {
       for (int i = 0; i < nkb; ++i) {
-        const int s = i % stages;
-        if (i >= stages && !wait_or_abort(&raw_empty[s], (uint32_t)((i / stages) - 1) & 1u, abort_flag)) break;
-        // the activation block of this stage is read by the tensor core: wait for the MMAs that used it
-        if (i >= stages && !wait_or_abort(&ab_empty[s], (uint32_t)((i / stages) - 1) & 1u, abort_flag)) break;
-        unsigned char* st = smem + (size_t)s * stage_bytes;
-        mbar_expect_tx(&raw_full[s], (uint32_t)(kRawBytes + b_bytes));
-        bulk_g2s(st + raw_off, g.wpk + ((size_t)tile * g.kblocks + kb0 + i) * kRawBytes, kRawBytes, &raw_full[s]);
-        bulk_g2s(st + kATileBytes, g.xp + (size_t)(kb0 + i) * g.Mpad * kBlockK, (uint32_t)b_bytes, &raw_full[s]);
+        const int s = i % Rr;
+        {
+          PROF_T0;
+          if (i >= Rr && !wait_or_abort(&raw_empty[s], (uint32_t)((i / Rr) - 1) & 1u, abort_flag)) break;
+          PROF_ADD(0);
+        }
+        mbar_expect_tx(&raw_full[s], (uint32_t)kRawBytes);
+        bulk_g2s(raw_ring + (size_t)s * kRawBytes, g.wpk + ((size_t)tile * g.kblocks + kb0 + i) * kRawBytes,
+                 kRawBytes, &raw_full[s]);
+      }
+    }
+  } else if (warp == 3) {
+    // ---- TMA producer, activations ----
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % Rb;
+        if (i >= Rb && !wait_or_abort(&b_empty[s], (uint32_t)((i / Rb) - 1) & 1u, abort_flag)) break;
+        mbar_expect_tx(&b_full[s], (uint32_t)b_bytes);
+        bulk_g2s(b_ring + (size_t)s * b_bytes, g.xp + (size_t)(kb0 + i) * g.Mpad * kBlockK, (uint32_t)b_bytes,
+                 &b_full[s]);
       }
     }
   } else if (warp == 1) {
@@ -240,37 +269,55 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
     if (lane == 0) {
       const uint32_t idesc = make_idesc(kTileN, g.Mpad);
       for (int i = 0; i < nkb; ++i) {
-        const int s = i % stages;
-        if (!wait_or_abort(&a_full[s], (uint32_t)(i / stages) & 1u, abort_flag)) break;
+        const int sa = i % Ra, sb = i % Rb;
+        {
+          PROF_T0;
+          if (!wait_or_abort(&b_full[sb], (uint32_t)(i / Rb) & 1u, abort_flag)) break;
+          PROF_ADD(1);
+        }
+        {
+          PROF_T0;
+          if (!wait_or_abort(&a_full[sa], (uint32_t)(i / Ra) & 1u, abort_flag)) break;
+          PROF_ADD(2);
+        }
         tc_fence_after();
-        unsigned char* st = smem + (size_t)s * stage_bytes;
-        const uint64_t adesc = make_desc(smem_u32(st));
-        const uint64_t bdesc = make_desc(smem_u32(st + kATileBytes));
+        const uint64_t adesc = make_desc(smem_u32(a_ring + (size_t)sa * kATileBytes));
+        const uint64_t bdesc = make_desc(smem_u32(b_ring + (size_t)sb * b_bytes));
 #pragma unroll
         for (int k = 0; k < kBlockK / 16; ++k)  // +32 bytes (2 x 16-byte units) per K = 16 step inside the swizzle row
           tc_mma_f16(tmem_d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (i | k) ? 1u : 0u);
-        tc_commit(&ab_empty[s]);
+        tc_commit(&a_empty[sa]);
+        tc_commit(&b_empty[sb]);
       }
       tc_commit(&acc_full);
     }
   } else if (warp >= 4) {
-    // ---- dequantise: thread r owns weight row r of the tile ----
-    const int r = threadIdx.x - 128;
+    // ---- dequantise: threads r, r + 128, r + 256, r + 384 own the four quarters (16 weights each) of row r ----
+    const int dt = threadIdx.x - 128;
+    const int r = dt & (kTileN - 1), quarter = dt >> 7;
+    const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
     for (int i = 0; i < nkb; ++i) {
-      const int s = i % stages;
-      if (!wait_or_abort(&raw_full[s], (uint32_t)(i / stages) & 1u, abort_flag)) break;
-      if (i >= stages && !wait_or_abort(&ab_empty[s], (uint32_t)((i / stages) - 1) & 1u, abort_flag)) break;
-      unsigned char* st = smem + (size_t)s * stage_bytes;
-      const uint4* rawq = reinterpret_cast<const uint4*>(st + raw_off + r * 32);
-      const uint4 q0 = rawq[0], q1 = rawq[1];
-      const __half2 sz = reinterpret_cast<const __half2*>(st + raw_off + kTileN * 32)[r];
+      const int sr = i % Rr, sa = i % Ra;
+      {
+        PROF_T0;
+        if (!wait_or_abort(&raw_full[sr], (uint32_t)(i / Rr) & 1u, abort_flag)) break;
+        if (threadIdx.x == 128) PROF_ADD(3);
+      }
+      {
+        PROF_T0;
+        if (i >= Ra && !wait_or_abort(&a_empty[sa], (uint32_t)((i / Ra) - 1) & 1u, abort_flag)) break;
+        if (threadIdx.x == 128) PROF_ADD(4);
+      }
+      PROF_T0;
+      const unsigned char* raw = raw_ring + (size_t)sr * kRawBytes;
+      const uint2 q0 = reinterpret_cast<const uint2*>(raw + r * 32)[quarter];
+      const __half2 sz = reinterpret_cast<const __half2*>(raw + kTileN * 32)[r];
       const __half2 s2 = __half2half2(__low2half(sz));
       const __half2 b2 = __half2half2(__high2half(sz));
-      const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
-      const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-      uint4* arow = reinterpret_cast<uint4*>(st + (r >> 3) * 1024 + (r & 7) * 128);
+      const uint32_t words[2] = {q0.x, q0.y};
+      uint4* arow = reinterpret_cast<uint4*>(a_ring + (size_t)sa * kATileBytes + (r >> 3) * 1024 + (r & 7) * 128);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 2; ++j) {
         uint32_t o[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
@@ -280,18 +327,25 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
           h = __hfma2(__hsub2(h, k1024), s2, b2);  // (q * scale) + (-zero * scale)
           o[t] = *reinterpret_cast<uint32_t*>(&h);
         }
-        arow[j ^ (r & 7)] = make_uint4(o[0], o[1], o[2], o[3]);
+        arow[(2 * quarter + j) ^ (r & 7)] = make_uint4(o[0], o[1], o[2], o[3]);
       }
       fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
-      mbar_arrive(&a_full[s]);
-      mbar_arrive(&raw_empty[s]);
+      __syncwarp();
+      if (lane == 0) {     // one arrival per warp: 256 threads hitting one barrier word would serialise
+        mbar_arrive(&a_full[sa]);
+        mbar_arrive(&raw_empty[sr]);
+      }
+      if (threadIdx.x == 128) PROF_ADD(5);
     }
     // ---- epilogue ----
+    PROF_T0;
     if (wait_or_abort(&acc_full, 0, abort_flag) && !*abort_flag) {
+      if (threadIdx.x == 128) PROF_ADD(6);
       tc_fence_after();
-      const int ew = warp - 4;  // TMEM lanes 32 ew .. 32 ew + 31
+      const int ew = warp & 3;  // TMEM lanes 32 ew .. 32 ew + 31 (a warp reaches the quarter given by its id mod 4)
       const int n = tile * kTileN + ew * 32 + lane;
-      for (int c0 = 0; c0 < g.Mpad; c0 += 16) {
+      // each group of four warps takes every (kDeqWarps / 4)-th 16-column group
+      for (int c0 = 16 * ((warp - 4) >> 2); c0 < g.Mpad; c0 += 16 * (kDeqWarps / 4)) {
         float v[16];
         tmem_ld16(tmem_d + ((uint32_t)(ew * 32) << 16) + (uint32_t)c0, v);
         if (g.splits == 1) {
@@ -338,7 +392,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct Plan {
-  int Mpad, kblocks, tiles, splits, stages;
+  int Mpad, kblocks, tiles, splits, ring_a, ring_b, ring_raw;
   size_t xp_bytes, partial_bytes, ticket_bytes, smem_bytes;
 };
 
@@ -355,12 +409,26 @@ bool make_plan(int M, int N, int K, Plan* p) {
   const int per = (p->kblocks + splits - 1) / splits;
   splits = (p->kblocks + per - 1) / per;
   p->splits = splits;
-  const int stage_bytes = (kATileBytes + p->Mpad * 128 + kRawBytes + 1023) / 1024 * 1024;
-  int stages = (int)((216 * 1024) / stage_bytes);
-  if (stages > 6) stages = 6;
-  if (stages < 2) return false;
-  p->stages = stages;
-  p->smem_bytes = (size_t)stages * stage_bytes + 1024;
+  // shared-memory budget: dequantised tiles and activation blocks get 3-4 stages, the rest goes to packed blocks
+  const int budget = 212 * 1024;
+  const int b_bytes = p->Mpad * 128;
+  p->ring_a = p->Mpad > 128 ? 4 : (p->Mpad > 32 ? 6 : 8);
+  p->ring_b = p->Mpad > 128 ? 3 : (p->Mpad > 32 ? 8 : 12);
+  // shrink the two tile rings until at least eight packed blocks fit beside them
+  while (budget - p->ring_a * kATileBytes - p->ring_b * b_bytes < 8 * kRawBytes) {
+    if (p->ring_b > 3)
+      --p->ring_b;
+    else if (p->ring_a > 2)
+      --p->ring_a;
+    else if (p->ring_b > 2)
+      --p->ring_b;
+    else
+      return false;
+  }
+  int left = budget - p->ring_a * kATileBytes - p->ring_b * b_bytes;
+  p->ring_raw = left / kRawBytes;
+  if (p->ring_raw > kMaxRing) p->ring_raw = kMaxRing;
+  p->smem_bytes = (size_t)p->ring_a * kATileBytes + (size_t)p->ring_b * b_bytes + (size_t)p->ring_raw * kRawBytes + 1024;
   p->xp_bytes = align_up((size_t)p->kblocks * p->Mpad * kBlockK * sizeof(__half), 256);
   p->partial_bytes = splits > 1 ? align_up((size_t)p->tiles * splits * p->Mpad * kTileN * sizeof(float), 256) : 0;
   p->ticket_bytes = align_up(sizeof(int) * (size_t)p->tiles, 256);
@@ -371,6 +439,16 @@ bool make_plan(int M, int N, int K, Plan* p) {
 }  // namespace subspec
 
 using namespace subspec;
+
+#ifdef SUBSPEC_GEMM_PROFILE
+extern "C" __attribute__((visibility("default"))) int subspec_debug_prof(long long* out, int reset) {
+  if (reset) {
+    long long z[16] = {};
+    return (int)cudaMemcpyToSymbol(g_prof, z, sizeof(z));
+  }
+  return (int)cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 16);
+}
+#endif
 
 extern "C" int subspec_w4a16_packed_bytes(int32_t n, int32_t k, size_t* bytes) {
   if (!bytes || n < kTileN || n % kTileN || k < kBlockK || k % kBlockK) return SUBSPEC_EUNSUPPORTED;
@@ -425,7 +503,9 @@ extern "C" int subspec_w4a16_gemm(const subspec_w4a16_args* args, subspec_stream
   g.K = a.k;
   g.kblocks = p.kblocks;
   g.splits = p.splits;
-  g.stages = p.stages;
+  g.ring_a = p.ring_a;
+  g.ring_b = p.ring_b;
+  g.ring_raw = p.ring_raw;
   g.y_stride = a.y_stride;
   int rc = cuda_check(cudaMemsetAsync(g.ticket, 0, p.ticket_bytes, st));
   if (rc) return rc;
