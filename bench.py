@@ -393,11 +393,10 @@ def main():
         dist.barrier()
 
     total = args.seqs
-    per_rank = total // world
-    wave = min(args.wave, per_rank)
-    n_waves = per_rank // wave
-    per_rank = n_waves * wave
-    total = per_rank * world
+    from subspec_b200.shard import reduce_stats, shard_sequences
+
+    shard = shard_sequences(total, world, rank, args.wave)
+    per_rank, wave, n_waves, total = shard.count, shard.wave, shard.n_waves, shard.total
     pages_per_seq = args.kv_tokens // PAGE_LEN
     kv_bytes_seq = KV_LAYERS * pages_per_seq * 2 * PAGE_LEN * KV_HEADS * KV_DIM * 2
     need = per_rank * (NODES * VOCAB * 2 + kv_bytes_seq) + (6 << 30)
@@ -408,9 +407,8 @@ def main():
 
     # ---- build the waves ----
     waves = []
-    first = rank * per_rank
     for w in range(n_waves):
-        ids = list(range(first + w * wave, first + (w + 1) * wave))
+        ids = shard.wave_ids(w)
         trees, logits = make_wave_inputs(ids, args.variant, device)
         pgen = torch.Generator().manual_seed(31 + ids[0])
         sb = SpeculativeStepBatch(wave, NODES, device, kv_layers=KV_LAYERS, kv_heads=KV_HEADS, head_dim=KV_DIM,
@@ -528,14 +526,12 @@ def main():
                "h2d": n_waves * host_logits.numel() * 2, "d2h": n_waves * waves[0][0].ws._out_host.numel()}
 
     # ---- gather (max over ranks of the times; sums of the counts) ----
-    stats = torch.tensor([ms_total, ms_exact, ms_lossy, ms_kv, e2e["dt"] if e2e else 0.0], device=device,
-                         dtype=torch.float64)
-    counts = torch.tensor([accepted_tokens, kept_rows], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        dist.all_reduce(counts, op=dist.ReduceOp.SUM)
-    ms_total, ms_exact, ms_lossy, ms_kv, dt_e2e = stats.tolist()
-    accepted_tokens, kept_rows = counts.tolist()
+    red = reduce_stats({"ms_total": ms_total, "ms_exact": ms_exact, "ms_lossy": ms_lossy, "ms_kv": ms_kv,
+                        "dt_e2e": e2e["dt"] if e2e else 0.0},
+                       {"accepted_tokens": accepted_tokens, "kept_rows": kept_rows}, device=device)
+    ms_total, ms_exact, ms_lossy, ms_kv, dt_e2e = (red[k] for k in ("ms_total", "ms_exact", "ms_lossy", "ms_kv",
+                                                                     "dt_e2e"))
+    accepted_tokens, kept_rows = red["accepted_tokens"], red["kept_rows"]
 
     if rank == 0:
         peaks = {}
