@@ -554,7 +554,10 @@ def main():
                            "per": f"launch over a wave of {wave} sequences"},
             "roofline": {"bound": "hbm", "kernel": "verify_rows_kernel<bf16, logits, softmax+entropy> (lossy verify)",
                          "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
-                         "peak_source": peak_src, "traffic": None,
+                         "peak_source": peak_src,
+                         # dram__bytes_read + dram__bytes_write of this kernel from the ncu capture summarised in
+                         # profiles/verify_rows_kernel_bf16_wave64.md (1246.38 + 0.47 MB for a wave of 64 sequences)
+                         "traffic": 1246.85e6 * wave / 64, "algorithmic_bytes": rows_bytes,
                          "exact_kernel_gbs": rows_bytes / (ms_exact * 1e-3) / 1e9,
                          "kv_kernel_gbs": 2 * (kept_rows / (world * n_waves)) * waves[0][0].kv_row_bytes
                          / (ms_kv * 1e-3) / 1e9},
