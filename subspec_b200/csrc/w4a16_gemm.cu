@@ -253,6 +253,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
                  kRawBytes, &raw_full[s]);
       }
     }
+    __syncwarp();  // the role lane rejoins its warp before the CTA-wide barrier below
   } else if (warp == 3) {
     // ---- TMA producer, activations ----
     if (lane == 0) {
@@ -264,6 +265,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
                  &b_full[s]);
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ---- MMA issuer ----
     if (lane == 0) {
@@ -291,6 +293,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
       }
       tc_commit(&acc_full);
     }
+    __syncwarp();
   } else if (warp >= 4) {
     // ---- dequantise: threads r, r + 128, r + 256, r + 384 own the four quarters (16 weights each) of row r ----
     const int dt = threadIdx.x - 128;
