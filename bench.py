@@ -289,12 +289,17 @@ def _time_ms(fn, iters=10, warm=3):
 
 
 def extras(device, peak_gbs, peak_tf):
-    """Config 3 (one expansion step) and config 2 (stochastic verify), each on inputs larger than L2."""
-    from subspec_b200 import synthetic
+    """The secondary kernels at their full configurations: one expansion step (config 3), one stochastic
+    verification batch (config 2), the W4A16 GEMM shapes (config 4); each on inputs larger than L2."""
+    out = {}
+    out.update(extra_expand(device, peak_gbs))
+    out.update(extra_stochastic(device, peak_gbs))
+    out.update(extra_gemm(device, peak_gbs, peak_tf))
+    return out
+
+
+def extra_expand(device, peak_gbs):
     from subspec_b200.draft import topk_sampling_from_logits
-    from subspec_b200.tree import Tree
-    from subspec_b200.verify import flatten_tree, get_workspace
-    from subspec_b200 import _lib
 
     out = {}
     gen = torch.Generator(device=device).manual_seed(3)
@@ -307,7 +312,16 @@ def extras(device, peak_gbs, peak_tf):
     gbs = logits.numel() * 2 / (ms * 1e-3) / 1e9
     out["expand_step_config3"] = {"ms": ms, "GB/s": gbs, "frac_of_measured_peak": gbs / peak_gbs,
                                   "bytes": logits.numel() * 2}
-    del logits
+    return out
+
+
+def extra_stochastic(device, peak_gbs):
+    from subspec_b200 import _lib, synthetic
+    from subspec_b200.tree import Tree
+    from subspec_b200.verify import flatten_tree, get_workspace
+
+    out = {}
+    gen = torch.Generator(device=device).manual_seed(5)
     # config 2: 64 sequences x 128-node trees, bf16 logits N(0, 2.5^2), T = 1, top-p 0.9, injected uniforms
     B, N, V = 64, 128, 152064
     cgen = torch.Generator().manual_seed(4)
@@ -329,16 +343,21 @@ def extras(device, peak_gbs, peak_tf):
     gbs = logits.numel() * 2 / (ms * 1e-3) / 1e9
     out["stochastic_verify_config2"] = {"ms": ms, "GB/s": gbs, "frac_of_measured_peak": gbs / peak_gbs,
                                         "bytes": logits.numel() * 2}
-    del logits
-    # config 4: HQQ W4A16 GEMM on the Qwen2.5-7B linear shapes; roofline time = max(bytes / HBM, flops / tensor)
-    from oracle.gemm_oracle import config4_case
-    from subspec_b200 import quant
+    return out
 
+
+def extra_gemm(device, peak_gbs, peak_tf):
+    # config 4: HQQ W4A16 GEMM on the Qwen2.5-7B linear shapes; roofline time = max(bytes / HBM, flops / tensor)
+    from subspec_b200 import quant
+    from subspec_b200.synthetic import w4a16_case
+
+    out = {}
+    gen = torch.Generator(device=device).manual_seed(7)
     gemm = {}
     reps = 20
     for name, (n, k) in {"qo": (3584, 3584), "kv": (512, 3584), "gate_up": (18944, 3584),
                          "down": (3584, 18944)}.items():
-        qweight, scale, zero, _ = config4_case(n, k, 1, seed=n + k)
+        qweight, scale, zero, _ = w4a16_case(n, k, 1, seed=n + k)
         # a set of distinct weight copies larger than L2, cycled, so that every call streams from HBM
         copies = max(2, int(200e6 // (n * k * 0.5625)) + 1)
         packed = [quant.pack(qweight.cuda(), scale.cuda(), zero.cuda()) for _ in range(copies)]

@@ -38,10 +38,6 @@ def w4a16_matmul(x: torch.Tensor, qweight: torch.Tensor, scale: torch.Tensor, ze
 
 def config4_case(n: int, k: int, m: int, seed: int):
     """BASELINE config 4 inputs: uint4 weights, scale ~U(0.005, 0.02), zero ~U(0, 15) in fp16, x ~N(0, 1) bf16."""
-    gen = torch.Generator().manual_seed(seed)
-    q = torch.randint(0, 16, (n, k // 8, 8), generator=gen, dtype=torch.int64)
-    qweight = (q << (torch.arange(8) * 4)).sum(-1).to(torch.int32)
-    scale = (torch.rand(n, k // GROUP, generator=gen) * 0.015 + 0.005).half()
-    zero = (torch.rand(n, k // GROUP, generator=gen) * 15.0).half()
-    x = torch.randn(m, k, generator=gen).to(torch.bfloat16)
-    return qweight, scale, zero, x
+    from subspec_b200.synthetic import w4a16_case
+
+    return w4a16_case(n, k, m, seed, GROUP)

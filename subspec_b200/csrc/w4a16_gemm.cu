@@ -8,16 +8,30 @@
 // (16..256), so the weights are the large operand and the problem is swapped: the 128 rows of a
 // weight tile are the MMA's M dimension, the tokens its N dimension, D[n, m] lives in TMEM.
 //
-// Data flow per CTA (one 128-row weight tile, a contiguous range of 64-wide K blocks):
-//   warp 0, one thread : cp.async.bulk (TMA) of the packed block (4 KB of nibbles + 512 B of
-//                        scale / -zero*scale) and of the pre-arranged fp16 activation block into a
-//                        kStages-deep shared-memory ring, completion on mbarriers;
-//   warps 4-7          : dequantise the nibbles to fp16 (lop3 magic-number trick, packed half2 FMA)
-//                        straight into the 128-byte-swizzled K-major tile the tensor core reads;
-//   warp 1, one thread : tcgen05.mma (kind::f16, 128 x Mpad x 16, fp32 accumulate in TMEM), four per
-//                        K block, tcgen05.commit frees the stage;
-//   warps 4-7          : epilogue, tcgen05.ld of the accumulator, bf16 store (or fp32 split-K partial
-//                        + ticket: the last CTA of a tile adds the partials up).
+// Data flow per CTA (one 128-row weight tile, a contiguous range of 64-wide K blocks; 22 warps):
+//   warp 0, one thread : cp.async.bulk (TMA) of the packed weights, one copy per chunk of four K blocks
+//                        (4 x (4 KB of nibbles + 512 B of scale / -zero*scale)), into a shared-memory
+//                        ring, completion on mbarriers;
+//   warp 1, one thread : cp.async.bulk of the pre-arranged fp16 activation blocks, one copy per slot of
+//                        up to four K blocks, into a ring of its own that looks as far ahead in K as
+//                        the packed ring;
+//   warps 6-21         : four groups of four warps, group q dequantises K blocks q, q + 4, ... (one
+//                        thread per weight row: lop3 magic-number trick, packed half2 FMA) and stores
+//                        the fp16 row with tcgen05.st into TENSOR MEMORY, where lane = weight row and
+//                        a 32-bit column holds two consecutive k: the dequantised operand never
+//                        touches shared memory.  Four K blocks are in flight at once, eight stages;
+//   warps 2-5          : MMA issuers (1, 2 or 4 of them, as many as there are accumulators, each taking
+//                        every n-th K block): tcgen05.mma kind::f16, 128 x Mpad x 16, A from tensor
+//                        memory, B = activation block in shared memory (128-byte swizzle, K-major), fp32
+//                        accumulate in TMEM, four per K block; one tcgen05.commit frees the stage.  The
+//                        whole warp runs the loop and an elected lane issues, which keeps the
+//                        descriptors in uniform registers;
+//   warps 6-21         : epilogue, tcgen05.ld of the accumulators, sum, bf16 store (or fp32 split-K
+//                        partial + ticket: the last CTA of a tile adds the partials up).
+// What bounds it at these token counts is neither HBM nor the tensor core's arithmetic but instruction
+// issue: a warp gets one tcgen05.mma out every 100-200 cycles whatever its N, hence several issuing
+// warps with accumulators of their own, and the role loops keep (stage, parity) counters instead of
+// dividing by ring depths.
 // Every wait is bounded; a wait that runs out raises SUBSPEC_DEV_TIMEOUT and the CTA winds down
 // (TMEM is released on every path).  No clusters, no multicast.
 #include <limits.h>
@@ -31,11 +45,19 @@ namespace {
 constexpr int kTileN = 128;      // weight rows per CTA = MMA M
 constexpr int kBlockK = 64;      // K per stage = one quantisation group = one 128-byte swizzle row of fp16
 constexpr int kRawBytes = kTileN * 32 + kTileN * 4;  // nibbles + (scale, -zero*scale) half2 per row
-constexpr int kATileBytes = kTileN * 128;
-constexpr int kDeqWarps = 16;        // warps 4..19 dequantise (four threads per weight row) and run the epilogue
-constexpr int kThreads = 128 + 32 * kDeqWarps;
+constexpr int kTmemCols = 512;        // the whole tensor memory of the SM (one CTA per SM)
+constexpr int kAColBase = 256;        // accumulator in columns [0, 256), dequantised operand stages above
+constexpr int kAStageCols = kBlockK / 2;  // one stage = 128 lanes x 32 columns of packed fp16 pairs
+constexpr int kMaxStages = (kTmemCols - kAColBase) / kAStageCols;  // 8
+constexpr int kDeqWarps = 16;        // the last sixteen warps dequantise and run the epilogue
+constexpr int kDeqGroups = 4;        // groups of four warps (128 threads = 128 weight rows) taking K blocks in turn
+constexpr int kIssuerWarp0 = 2;      // warps 2..5 issue MMAs (as many as the plan asks for); warp 0, 1: TMA producers
+constexpr int kMaxIssuers = 4;
+constexpr int kDeqWarp0 = kIssuerWarp0 + kMaxIssuers;
+constexpr int kThreads = 32 * (kDeqWarp0 + kDeqWarps);
 constexpr int kMaxM = 256;
-constexpr int kMaxRing = 32;
+constexpr int kMaxRing = 8;           // packed ring, in chunks of kDeqGroups K blocks (one TMA copy each)
+constexpr int kChunkBytes = kDeqGroups * kRawBytes;
 
 struct GemmArgs {
   const unsigned char* wpk;  // packed weights: [N/128][K/64] blocks of kRawBytes
@@ -44,19 +66,10 @@ struct GemmArgs {
   float* partial;            // [tiles][splits][Mpad][128]
   int* ticket;               // [tiles]
   uint32_t* dev_status;
-  int M, Mpad, N, K, kblocks, splits, ring_a, ring_b, ring_raw;
+  int M, Mpad, N, K, kblocks, splits, ring_raw, b_slots, b_blocks, b_shift, acc_n, acc_stride, issuers;
   int64_t y_stride;
 };
 
-#ifdef SUBSPEC_GEMM_PROFILE
-__device__ long long g_prof[16];
-#define PROF_T0 const long long prof_t0 = clock64()
-#define PROF_ADD(slot) \
-  if (blockIdx.x == 0 && blockIdx.y == 0) atomicAdd((unsigned long long*)&g_prof[slot], (unsigned long long)(clock64() - prof_t0))
-#else
-#define PROF_T0
-#define PROF_ADD(slot)
-#endif
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t it = 0; it < kSpinLimit; ++it) {
@@ -65,6 +78,17 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   }
   *abort_flag = 1;
   return false;
+}
+
+// True in exactly one lane of the (converged) warp, the same one every time.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -88,16 +112,29 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
-__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                           uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem]: the 128 x 16 A fragment sits in tensor memory, lane = row, eight 32-bit
+// columns of packed fp16 pairs (k = 2c, 2c + 1 in column c).
+__device__ __forceinline__ void tc_mma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       :
-      : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// 32 lanes x 16 consecutive 32-bit columns, registers -> tensor memory; lane i of the warp writes TMEM lane
+// (lane base + i).  Asynchronous: tmem_wait_st() before anybody is told about the data.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // 32 lanes x 16 consecutive 32-bit columns; lane i of the warp reads TMEM lane (lane base + i)
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
   uint32_t r[16];
@@ -162,9 +199,11 @@ __global__ void w4a16_pack_kernel(const uint32_t* __restrict__ qweight, const __
 }
 
 // x bf16 [M, K] -> fp16 blocks [K/64][Mpad][64], 16-byte chunk c of row r stored at chunk c ^ (r & 7)
-// (the 128-byte swizzle the tensor core expects); rows >= M are zero.
+// (the 128-byte swizzle the tensor core expects); rows >= M are zero.  Also clears the split-K tickets.
 __global__ void w4a16_prep_x_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_stride, __half* __restrict__ xp,
-                                    int M, int Mpad, int K) {
+                                    int M, int Mpad, int K, int* __restrict__ ticket, int tiles) {
+  if (blockIdx.x == 0)  // split-K tickets of the GEMM launch that follows in the stream
+    for (int t = threadIdx.x; t < tiles; t += blockDim.x) ticket[t] = 0;
   const int kblocks = K / kBlockK;
   const int64_t total = (int64_t)kblocks * Mpad * 8;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
@@ -188,41 +227,59 @@ __global__ void w4a16_prep_x_kernel(const __nv_bfloat16* __restrict__ x, int64_t
   }
 }
 
+// Ring bookkeeping without divisions: the role loops are single-thread dependent chains, where one
+// integer division by a run-time ring depth costs more than the rest of the iteration.
+struct RingPos {
+  int s, ph;  // stage, parity of the current pass over the ring
+  __device__ __forceinline__ void advance(int by, int depth) {
+    s += by;
+    while (s >= depth) {
+      s -= depth;
+      ph ^= 1;
+    }
+  }
+};
+
 __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs g) {
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
   // the swizzle atoms must sit on 1024-byte boundaries of the shared-memory address space
   unsigned char* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
-  __shared__ __align__(8) uint64_t raw_full[kMaxRing], raw_empty[kMaxRing], b_full[kMaxRing], b_empty[kMaxRing],
-      a_full[kMaxRing], a_empty[kMaxRing], acc_full;
+  // raw_*: ring of packed weight blocks (the HBM stream, deep).  full / empty: ring of the dequantised
+  // 128 x 64 fp16 weight tiles in tensor memory (32 columns each).  b_*: ring of activation slots, one slot =
+  // b_blocks consecutive Mpad x 64 fp16 blocks.  The activations have a ring of their own, as deep in K as
+  // the packed one: the TMA unit serves an SM's requests in order, so an activation copy issued only when
+  // its stage frees up would queue behind every packed block already requested.
+  __shared__ __align__(8) uint64_t raw_full[kMaxRing], raw_empty[kMaxRing], full[kMaxStages], empty[kMaxStages],
+      b_full[kMaxStages], b_empty[kMaxStages], acc_full;
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ int s_last;
 
-  // Three rings with their own depths: packed weight blocks (deep: this is the HBM stream), activation
-  // blocks (read by the tensor core) and dequantised fp16 tiles (written here, read by the tensor core).
-  const int Ra = g.ring_a, Rb = g.ring_b, Rr = g.ring_raw;
-  const int b_bytes = g.Mpad * 128;
-  unsigned char* a_ring = smem;                                  // Ra x 16 KB, 1024-aligned
-  unsigned char* b_ring = a_ring + (size_t)Ra * kATileBytes;     // Rb x Mpad*128 (a multiple of 2 KB)
-  unsigned char* raw_ring = b_ring + (size_t)Rb * b_bytes;       // Rr x 4608 B
+  constexpr int R = kMaxStages;
+  const int Rr = g.ring_raw, Rb = g.b_slots, bs = g.b_blocks;
+  const int b_bytes = g.Mpad * 128;                             // one K block of activations (a multiple of 2 KB)
+  const int slot_bytes = bs * b_bytes;
+  unsigned char* b_ring = smem;                                 // Rb slots, 1024-aligned
+  unsigned char* raw_ring = b_ring + (size_t)Rb * slot_bytes;   // Rr chunks of four packed blocks
   const int tile = blockIdx.x, split = blockIdx.y;
   const int kb_per = (g.kblocks + g.splits - 1) / g.splits;
   const int kb0 = min(split * kb_per, g.kblocks), kb1 = min(kb0 + kb_per, g.kblocks);
   const int nkb = kb1 - kb0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  uint32_t ncols = 32;
-  while ((int)ncols < g.Mpad) ncols <<= 1;
+  const uint32_t ncols = kTmemCols;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kMaxRing; ++s) {
+    for (int s = 0; s < Rr; ++s) {
       mbar_init(&raw_full[s], 1);
       mbar_init(&raw_empty[s], kDeqWarps);
-      mbar_init(&b_full[s], 1);
-      mbar_init(&b_empty[s], 1);
-      mbar_init(&a_full[s], kDeqWarps);
-      mbar_init(&a_empty[s], 1);
     }
-    mbar_init(&acc_full, 1);
+    for (int s = 0; s < R; ++s) {
+      mbar_init(&full[s], kDeqWarps / kDeqGroups);
+      mbar_init(&empty[s], 1);
+      mbar_init(&b_full[s], 1);
+      mbar_init(&b_empty[s], (uint32_t)g.issuers);
+    }
+    mbar_init(&acc_full, (uint32_t)g.issuers);
     mbar_init_fence();
     s_abort = 0;
     s_last = 0;
@@ -239,118 +296,174 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
   volatile int* abort_flag = &s_abort;
 
   if (warp == 0) {
-    // ---- TMA producer, packed weights ----
+    // ---- TMA producer, packed weights: one copy per chunk of four K blocks (a single thread gets a
+    // copy out every few hundred cycles at best, which 4.5 KB copies would turn into the bound) ----
     if (lane == 0) {
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % Rr;
-        {
-          PROF_T0;
-          if (i >= Rr && !wait_or_abort(&raw_empty[s], (uint32_t)((i / Rr) - 1) & 1u, abort_flag)) break;
-          PROF_ADD(0);
-        }
-        mbar_expect_tx(&raw_full[s], (uint32_t)kRawBytes);
-        bulk_g2s(raw_ring + (size_t)s * kRawBytes, g.wpk + ((size_t)tile * g.kblocks + kb0 + i) * kRawBytes,
-                 kRawBytes, &raw_full[s]);
+      RingPos p{0, 0};
+      const unsigned char* src = g.wpk + ((size_t)tile * g.kblocks + kb0) * kRawBytes;
+      const int nchunks = (nkb + kDeqGroups - 1) / kDeqGroups;
+      for (int c = 0; c < nchunks; ++c, src += kChunkBytes) {
+        if (c >= Rr && !wait_or_abort(&raw_empty[p.s], (uint32_t)p.ph ^ 1u, abort_flag)) break;
+        const uint32_t bytes = (uint32_t)(min(kDeqGroups, nkb - c * kDeqGroups) * kRawBytes);
+        mbar_expect_tx(&raw_full[p.s], bytes);
+        bulk_g2s(raw_ring + (size_t)p.s * kChunkBytes, src, bytes, &raw_full[p.s]);
+        p.advance(1, Rr);
       }
     }
     __syncwarp();  // the role lane rejoins its warp before the CTA-wide barrier below
-  } else if (warp == 3) {
-    // ---- TMA producer, activations ----
-    if (lane == 0) {
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % Rb;
-        if (i >= Rb && !wait_or_abort(&b_empty[s], (uint32_t)((i / Rb) - 1) & 1u, abort_flag)) break;
-        mbar_expect_tx(&b_full[s], (uint32_t)b_bytes);
-        bulk_g2s(b_ring + (size_t)s * b_bytes, g.xp + (size_t)(kb0 + i) * g.Mpad * kBlockK, (uint32_t)b_bytes,
-                 &b_full[s]);
-      }
-    }
-    __syncwarp();
   } else if (warp == 1) {
-    // ---- MMA issuer ----
+    // ---- TMA producer, activations: one copy per slot of bs K blocks ----
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(kTileN, g.Mpad);
-      for (int i = 0; i < nkb; ++i) {
-        const int sa = i % Ra, sb = i % Rb;
-        {
-          PROF_T0;
-          if (!wait_or_abort(&b_full[sb], (uint32_t)(i / Rb) & 1u, abort_flag)) break;
-          PROF_ADD(1);
+      RingPos p{0, 0}, pe{0, 0};
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(g.xp) + (size_t)kb0 * b_bytes;
+      const int nslots = (nkb + bs - 1) / bs;
+      for (int j = 0; j < nslots; ++j, src += slot_bytes) {
+        if (j >= Rb) {
+          if (bs == 1) {
+            // one K block per slot: the slot is free when the block's tensor-memory stage is, so the issuing
+            // warp's one commit per block serves both (this thread sees every phase of every empty[] in turn)
+            if (!wait_or_abort(&empty[pe.s], (uint32_t)pe.ph, abort_flag)) break;
+            pe.advance(1, R);
+          } else if (!wait_or_abort(&b_empty[p.s], (uint32_t)p.ph ^ 1u, abort_flag)) {
+            break;
+          }
         }
-        {
-          PROF_T0;
-          if (!wait_or_abort(&a_full[sa], (uint32_t)(i / Ra) & 1u, abort_flag)) break;
-          PROF_ADD(2);
-        }
-        tc_fence_after();
-        const uint64_t adesc = make_desc(smem_u32(a_ring + (size_t)sa * kATileBytes));
-        const uint64_t bdesc = make_desc(smem_u32(b_ring + (size_t)sb * b_bytes));
-#pragma unroll
-        for (int k = 0; k < kBlockK / 16; ++k)  // +32 bytes (2 x 16-byte units) per K = 16 step inside the swizzle row
-          tc_mma_f16(tmem_d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (i | k) ? 1u : 0u);
-        tc_commit(&a_empty[sa]);
-        tc_commit(&b_empty[sb]);
+        const uint32_t bytes = (uint32_t)(min(bs, nkb - j * bs) * b_bytes);
+        mbar_expect_tx(&b_full[p.s], bytes);
+        bulk_g2s(b_ring + (size_t)p.s * slot_bytes, src, bytes, &b_full[p.s]);
+        p.advance(1, Rb);
       }
-      tc_commit(&acc_full);
     }
     __syncwarp();
-  } else if (warp >= 4) {
-    // ---- dequantise: threads r, r + 128, r + 256, r + 384 own the four quarters (16 weights each) of row r ----
-    const int dt = threadIdx.x - 128;
-    const int r = dt & (kTileN - 1), quarter = dt >> 7;
+  }
+  if (warp >= kIssuerWarp0 && warp < kIssuerWarp0 + g.issuers) {
+    // ---- MMA issuers: with two of them, warp 1 takes the even K blocks, warp 2 the odd ones, each into its own
+    // accumulators.  The WHOLE warp runs the loop and one elected lane issues: with warp-uniform control
+    // flow the descriptors live in uniform registers, where the tensor-core instructions take them from;
+    // under a per-lane branch every operand of every MMA first has to be moved there. ----
+    const int me = warp - kIssuerWarp0;
+    // The 256 accumulator columns hold acc_n accumulators of acc_stride columns, split evenly between the
+    // issuers; an issuer's consecutive K steps rotate over its share, and the epilogue adds everything up
+    // (above 128 tokens there is room for one accumulator, hence one issuer).
+    const uint32_t idesc = make_idesc(kTileN, g.Mpad);
+    const int share = g.acc_n / g.issuers;  // a power of two; at most four are used (one per K step)
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_d, 0);  // the same in every lane, and known to be
+    const uint32_t acc0 = tmem_u + (uint32_t)(me * share * g.acc_stride);
+    const uint64_t bdesc0 = make_desc(smem_u32(b_ring));
+    const uint32_t b_step = (uint32_t)b_bytes >> 4, slot_step = (uint32_t)slot_bytes >> 4;
+    RingPos p{0, 0}, pb{0, 0};
+    p.advance(me, R);
+    int slot_of = -1;  // activation slot (index along K) this warp has waited for
+    for (int i = me; i < nkb; i += g.issuers) {
+      const int j = i >> g.b_shift, within = i & (bs - 1);  // bs = 1 << b_shift
+      bool ok = true;
+      if (j != slot_of) {  // first block of this warp in the slot
+        if (slot_of >= 0) pb.advance(1, Rb);
+        slot_of = j;
+        ok = wait_or_abort(&b_full[pb.s], (uint32_t)pb.ph, abort_flag);
+      }
+      ok = ok && wait_or_abort(&full[p.s], (uint32_t)p.ph, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      tc_fence_after();
+      const uint32_t tmem_a = tmem_u + (uint32_t)(kAColBase + p.s * kAStageCols);
+      const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)pb.s * slot_step + (uint32_t)within * b_step);
+      const bool last_in_slot = ((i + g.issuers) >> g.b_shift) != j;
+      if (elect_one()) {
+#pragma unroll
+        for (int k = 0; k < kBlockK / 16; ++k) {  // per K = 16 step: 8 columns of A, +32 bytes (2 x 16-byte units) of B
+          tc_mma_f16_ta(acc0 + (uint32_t)((k & (share - 1)) * g.acc_stride), tmem_a + (uint32_t)(8 * k),
+                        bdesc + (uint64_t)(2 * k), idesc, (i != me || k >= share) ? 1u : 0u);
+        }
+        tc_commit(&empty[p.s]);                     // frees the stage for the dequantising group
+        if (last_in_slot && bs > 1) tc_commit(&b_empty[pb.s]);  // this warp's last block in the activation slot
+      }
+      __syncwarp();
+      p.advance(g.issuers, R);
+    }
+    if (elect_one()) {
+      if (me < nkb)
+        tc_commit(&acc_full);
+      else
+        mbar_arrive(&acc_full);  // nothing issued by this warp
+      if (me == 0) {
+      }
+    }
+    __syncwarp();
+  } else if (warp >= kDeqWarp0) {
+    // ---- dequantise: four groups of four warps; group q takes K blocks q, q + 4, ..., thread = weight row ----
+    const int r = (warp & 3) * 32 + lane, grp = (warp - kDeqWarp0) >> 2;
+    // a warp reaches the TMEM lanes 32 (warp % 4) .. + 31: the four warps of a group cover rows 0..127 in order
+    const uint32_t tmem_row = tmem_d + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)kAColBase;
     const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
-    for (int i = 0; i < nkb; ++i) {
-      const int sr = i % Rr, sa = i % Ra;
-      {
-        PROF_T0;
-        if (!wait_or_abort(&raw_full[sr], (uint32_t)(i / Rr) & 1u, abort_flag)) break;
-        if (threadIdx.x == 128) PROF_ADD(3);
-      }
-      {
-        PROF_T0;
-        if (i >= Ra && !wait_or_abort(&a_empty[sa], (uint32_t)((i / Ra) - 1) & 1u, abort_flag)) break;
-        if (threadIdx.x == 128) PROF_ADD(4);
-      }
-      PROF_T0;
-      const unsigned char* raw = raw_ring + (size_t)sr * kRawBytes;
-      const uint2 q0 = reinterpret_cast<const uint2*>(raw + r * 32)[quarter];
+    const __half2 k16th = __half2half2(__ushort_as_half((unsigned short)0x2C00));   // 1 / 16
+    const __half2 kneg64 = __half2half2(__ushort_as_half((unsigned short)0xD400));  // -64
+    RingPos pr{0, 0}, pa{0, 0};
+    pa.advance(grp, R);
+    for (int i = grp; i < nkb; i += kDeqGroups) {
+      if (!wait_or_abort(&raw_full[pr.s], (uint32_t)pr.ph, abort_flag)) break;
+      if (i >= R && !wait_or_abort(&empty[pa.s], (uint32_t)pa.ph ^ 1u, abort_flag)) break;
+      const unsigned char* raw = raw_ring + (size_t)pr.s * kChunkBytes + grp * kRawBytes;
+      const uint4 q0 = reinterpret_cast<const uint4*>(raw + r * 32)[0];
+      const uint4 q1 = reinterpret_cast<const uint4*>(raw + r * 32)[1];
       const __half2 sz = reinterpret_cast<const __half2*>(raw + kTileN * 32)[r];
       const __half2 s2 = __half2half2(__low2half(sz));
       const __half2 b2 = __half2half2(__high2half(sz));
-      const uint32_t words[2] = {q0.x, q0.y};
-      uint4* arow = reinterpret_cast<uint4*>(a_ring + (size_t)sa * kATileBytes + (r >> 3) * 1024 + (r & 7) * 128);
+      const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+      tc_fence_after();  // the stage's previous reader (the tensor core) is done: ordered before the overwrite
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        uint32_t o[4];
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        uint32_t o[16];  // column c = (k = 2c, 2c + 1) of this thread's row
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          // 0x6400 = 1024.0 in fp16: OR-ing a nibble into the mantissa gives 1024 + q exactly
-          uint32_t v = ((words[j] >> (4 * t)) & 0x000F000Fu) | 0x64006400u;
-          __half2 h = *reinterpret_cast<__half2*>(&v);
-          h = __hfma2(__hsub2(h, k1024), s2, b2);  // (q * scale) + (-zero * scale)
-          o[t] = *reinterpret_cast<uint32_t*>(&h);
+        for (int jj = 0; jj < 4; ++jj) {
+          // 0x6400 = 1024.0 in fp16: a nibble OR-ed into mantissa bits 0-3 gives 1024 + q, into bits 4-7
+          // 1024 + 16 q; (1024 + q) - 1024 and (1024 + 16 q) / 16 - 64 are both q exactly.  Two of the four
+          // nibble pairs of a word are thus reached without a shift.
+          const uint32_t w = words[4 * hlf + jj], w8 = w >> 8;
+          uint32_t v[4] = {(w & 0x000F000Fu) | 0x64006400u, (w & 0x00F000F0u) | 0x64006400u,
+                           (w8 & 0x000F000Fu) | 0x64006400u, (w8 & 0x00F000F0u) | 0x64006400u};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            __half2 h = *reinterpret_cast<__half2*>(&v[t]);
+            h = (t & 1) ? __hfma2(h, k16th, kneg64) : __hsub2(h, k1024);
+            h = __hfma2(h, s2, b2);  // (q * scale) + (-zero * scale)
+            o[4 * jj + t] = *reinterpret_cast<uint32_t*>(&h);
+          }
         }
-        arow[(2 * quarter + j) ^ (r & 7)] = make_uint4(o[0], o[1], o[2], o[3]);
+        tmem_st16(tmem_row + (uint32_t)(pa.s * kAStageCols + 16 * hlf), o);
       }
-      fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
+      tmem_wait_st();
+      tc_fence_before();
       __syncwarp();
-      if (lane == 0) {     // one arrival per warp: 256 threads hitting one barrier word would serialise
-        mbar_arrive(&a_full[sa]);
-        mbar_arrive(&raw_empty[sr]);
+      if (lane == 0) {     // one arrival per warp
+        mbar_arrive(&full[pa.s]);
+        mbar_arrive(&raw_empty[pr.s]);
       }
-      if (threadIdx.x == 128) PROF_ADD(5);
+      pr.advance(1, Rr);
+      pa.advance(kDeqGroups, R);
+    }
+    if (threadIdx.x == 32 * kDeqWarp0) {
     }
     // ---- epilogue ----
-    PROF_T0;
     if (wait_or_abort(&acc_full, 0, abort_flag) && !*abort_flag) {
-      if (threadIdx.x == 128) PROF_ADD(6);
       tc_fence_after();
       const int ew = warp & 3;  // TMEM lanes 32 ew .. 32 ew + 31 (a warp reaches the quarter given by its id mod 4)
       const int n = tile * kTileN + ew * 32 + lane;
-      // each group of four warps takes every (kDeqWarps / 4)-th 16-column group
-      for (int c0 = 16 * ((warp - 4) >> 2); c0 < g.Mpad; c0 += 16 * (kDeqWarps / 4)) {
+      // each group of four warps takes every (kDeqWarps / 4)-th group of 16 tokens
+      // accumulators that were written: an issuer's share has at most four members in use, and the second
+      // issuer has work only from two K blocks on
+      const int n_own = g.acc_n / g.issuers;
+      const int share = min(n_own, 4);
+      for (int c0 = 16 * ((warp - kDeqWarp0) >> 2); c0 < g.Mpad; c0 += 16 * (kDeqWarps / 4)) {
+        const int col = c0;  // tokens c0 .. c0 + 15 sit in columns c0 .. c0 + 15 of every accumulator
         float v[16];
-        tmem_ld16(tmem_d + ((uint32_t)(ew * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld16(tmem_d + ((uint32_t)(ew * 32) << 16) + (uint32_t)col, v);
+        for (int is = 0; is < min(g.issuers, nkb); ++is)
+          for (int a = (is == 0 ? 1 : 0); a < share; ++a) {
+            float w[16];
+            tmem_ld16(tmem_d + ((uint32_t)(ew * 32) << 16) + (uint32_t)(col + (is * n_own + a) * g.acc_stride), w);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += w[j];
+          }
         if (g.splits == 1) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
@@ -382,7 +495,6 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
           acc += __ldcg(g.partial + (((size_t)tile * g.splits + sp) * g.Mpad + m) * kTileN + c);
         g.y[(size_t)m * g.y_stride + tile * kTileN + c] = __float2bfloat16_rn(acc);
       }
-      if (threadIdx.x == 0) g.ticket[tile] = 0;  // ready for the next call
     }
   }
   __syncthreads();
@@ -395,13 +507,18 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct Plan {
-  int Mpad, kblocks, tiles, splits, ring_a, ring_b, ring_raw;
+  int Mpad, kblocks, tiles, splits, ring_raw, b_slots, b_blocks, b_shift, acc_n, acc_stride, issuers;
   size_t xp_bytes, partial_bytes, ticket_bytes, smem_bytes;
 };
 
 bool make_plan(int M, int N, int K, Plan* p) {
   if (M < 1 || M > kMaxM || N < kTileN || N % kTileN || K < kBlockK || K % kBlockK) return false;
-  p->Mpad = (M + 15) / 16 * 16;
+  p->Mpad = (M + 15) / 16 * 16;  // tokens padded to the MMA's N granule
+  // accumulators in TMEM columns [0, 256): as many as fit, a power of two, each at least 32 columns wide
+  p->acc_stride = 32;
+  while (p->acc_stride < p->Mpad) p->acc_stride <<= 1;
+  p->acc_n = 256 / p->acc_stride;
+  p->issuers = p->acc_n < kMaxIssuers ? p->acc_n : kMaxIssuers;  // every issuing warp needs an accumulator of its own
   p->kblocks = K / kBlockK;
   p->tiles = N / kTileN;
   int splits = kNumSMs / p->tiles;
@@ -412,26 +529,29 @@ bool make_plan(int M, int N, int K, Plan* p) {
   const int per = (p->kblocks + splits - 1) / splits;
   splits = (p->kblocks + per - 1) / per;
   p->splits = splits;
-  // shared-memory budget: dequantised tiles and activation blocks get 3-4 stages, the rest goes to packed blocks
-  const int budget = 212 * 1024;
+  // Shared memory.  Activation slots: b_blocks K blocks each (a power of two, at least one per issuing
+  // warp, at most 32 KB), up to eight slots in at most 128 KB.  Packed ring: the rest, in chunks of
+  // kDeqGroups K blocks, not so deep that an activation copy queues behind more packed data than its own
+  // look-ahead covers.  Every dequantising group takes one block of every chunk and every fourth stage of
+  // the eight in tensor memory, and an issuing warp always frees the same stages, in order: each waiter
+  // sees every phase of the barriers it polls, which is what keeps the parity waits sound.
+  const int budget = 220 * 1024;
   const int b_bytes = p->Mpad * 128;
-  p->ring_a = p->Mpad > 128 ? 4 : (p->Mpad > 32 ? 6 : 8);
-  p->ring_b = p->Mpad > 128 ? 3 : (p->Mpad > 32 ? 8 : 12);
-  // shrink the two tile rings until at least eight packed blocks fit beside them
-  while (budget - p->ring_a * kATileBytes - p->ring_b * b_bytes < 8 * kRawBytes) {
-    if (p->ring_b > 3)
-      --p->ring_b;
-    else if (p->ring_a > 2)
-      --p->ring_a;
-    else if (p->ring_b > 2)
-      --p->ring_b;
-    else
-      return false;
-  }
-  int left = budget - p->ring_a * kATileBytes - p->ring_b * b_bytes;
-  p->ring_raw = left / kRawBytes;
-  if (p->ring_raw > kMaxRing) p->ring_raw = kMaxRing;
-  p->smem_bytes = (size_t)p->ring_a * kATileBytes + (size_t)p->ring_b * b_bytes + (size_t)p->ring_raw * kRawBytes + 1024;
+  p->b_blocks = 4;
+  while (p->b_blocks > p->issuers && p->b_blocks * b_bytes > 32 * 1024) p->b_blocks >>= 1;
+  p->b_shift = p->b_blocks == 4 ? 2 : (p->b_blocks == 2 ? 1 : 0);
+  const int slot = p->b_blocks * b_bytes;
+  p->b_slots = 128 * 1024 / slot;
+  if (p->b_slots > kMaxStages) p->b_slots = kMaxStages;
+  if (p->b_slots < 2) return false;
+  const int ahead = p->b_slots * p->b_blocks;  // activation look-ahead in K blocks
+  int raw = (budget - p->b_slots * slot) / kChunkBytes;  // packed ring, in chunks
+  if (raw * kDeqGroups > 2 * ahead) raw = 2 * ahead / kDeqGroups;
+  if (raw > kMaxRing) raw = kMaxRing;
+  if (raw < 2) return false;
+  p->ring_raw = raw;
+  p->smem_bytes = (size_t)p->b_slots * slot + (size_t)raw * kChunkBytes + 1024;
+  if (p->smem_bytes > (size_t)budget + 1024) return false;
   p->xp_bytes = align_up((size_t)p->kblocks * p->Mpad * kBlockK * sizeof(__half), 256);
   p->partial_bytes = splits > 1 ? align_up((size_t)p->tiles * splits * p->Mpad * kTileN * sizeof(float), 256) : 0;
   p->ticket_bytes = align_up(sizeof(int) * (size_t)p->tiles, 256);
@@ -443,15 +563,6 @@ bool make_plan(int M, int N, int K, Plan* p) {
 
 using namespace subspec;
 
-#ifdef SUBSPEC_GEMM_PROFILE
-extern "C" __attribute__((visibility("default"))) int subspec_debug_prof(long long* out, int reset) {
-  if (reset) {
-    long long z[16] = {};
-    return (int)cudaMemcpyToSymbol(g_prof, z, sizeof(z));
-  }
-  return (int)cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 16);
-}
-#endif
 
 extern "C" int subspec_w4a16_packed_bytes(int32_t n, int32_t k, size_t* bytes) {
   if (!bytes || n < kTileN || n % kTileN || k < kBlockK || k % kBlockK) return SUBSPEC_EUNSUPPORTED;
@@ -506,17 +617,20 @@ extern "C" int subspec_w4a16_gemm(const subspec_w4a16_args* args, subspec_stream
   g.K = a.k;
   g.kblocks = p.kblocks;
   g.splits = p.splits;
-  g.ring_a = p.ring_a;
-  g.ring_b = p.ring_b;
+  g.b_slots = p.b_slots;
+  g.b_blocks = p.b_blocks;
+  g.b_shift = p.b_shift;
   g.ring_raw = p.ring_raw;
+  g.acc_n = p.acc_n;
+  g.acc_stride = p.acc_stride;
+  g.issuers = p.issuers;
   g.y_stride = a.y_stride;
-  int rc = cuda_check(cudaMemsetAsync(g.ticket, 0, p.ticket_bytes, st));
-  if (rc) return rc;
+  int rc;
   {
     const int64_t total = (int64_t)p.kblocks * p.Mpad * 8;
     const int grid = (int)((total + 255) / 256 > 2368 ? 2368 : (total + 255) / 256);
     w4a16_prep_x_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(a.x), a.x_stride,
-                                              reinterpret_cast<__half*>(sp), a.m, p.Mpad, a.k);
+                                              reinterpret_cast<__half*>(sp), a.m, p.Mpad, a.k, g.ticket, p.tiles);
     rc = cuda_check(cudaGetLastError());
     if (rc) return rc;
   }

@@ -109,3 +109,15 @@ def random_page_table(batch: int, pages_per_seq: int, gen: torch.Generator) -> t
     """[batch, pages_per_seq] int32: a random permutation of the pool's pages split across sequences."""
     perm = torch.randperm(batch * pages_per_seq, generator=gen)
     return perm.reshape(batch, pages_per_seq).to(torch.int32)
+
+
+def w4a16_case(n: int, k: int, m: int, seed: int, group: int = 64):
+    """Synthetic HQQ-style 4-bit linear: int32 words of eight nibbles (nibble i of word j = q[n, 8 j + i]),
+    scale ~U(0.005, 0.02) and zero ~U(0, 15) in fp16 per group of `group` inputs, activations ~N(0, 1) bf16."""
+    gen = torch.Generator().manual_seed(seed)
+    q = torch.randint(0, 16, (n, k // 8, 8), generator=gen, dtype=torch.int64)
+    qweight = (q << (torch.arange(8) * 4)).sum(-1).to(torch.int32)
+    scale = (torch.rand(n, k // group, generator=gen) * 0.015 + 0.005).half()
+    zero = (torch.rand(n, k // group, generator=gen) * 15.0).half()
+    x = torch.randn(m, k, generator=gen).to(torch.bfloat16)
+    return qweight, scale, zero, x

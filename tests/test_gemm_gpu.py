@@ -32,7 +32,11 @@ def test_config4_shapes(cuda_lib, n, k, m):
 
 
 def test_small_and_ragged_m(cuda_lib):
-    for m, n, k in [(1, 128, 64), (3, 256, 128), (17, 384, 640), (100, 128, 4096), (255, 640, 192)]:
+    # every accumulator layout (8, 4, 2, 1 accumulators), 1-4 issuing warps, K ranges that end inside a
+    # four-block chunk, one K block only, and rings that wrap many times (64 K blocks in one CTA)
+    for m, n, k in [(1, 128, 64), (3, 256, 128), (17, 384, 640), (100, 128, 4096), (255, 640, 192),
+                    (33, 256, 64 * 37), (48, 128, 64 * 5), (64, 18944, 4096), (96, 256, 64 * 9),
+                    (130, 256, 1024), (200, 18944, 576), (16, 18944, 4096)]:
         qweight, scale, zero, x = go.config4_case(n, k, m, seed=m)
         y = quant.w4a16_matmul(x.cuda(), quant.pack(qweight.cuda(), scale.cuda(), zero.cuda()), n, k)
         assert _rel_err(y, go.w4a16_matmul(x, qweight, scale, zero)) < TOL, (m, n, k)
