@@ -202,7 +202,11 @@ __global__ void w4a16_pack_kernel(const uint32_t* __restrict__ qweight, const __
 // (the 128-byte swizzle the tensor core expects); rows >= M are zero.  Also clears the split-K tickets.
 __global__ void w4a16_prep_x_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_stride, __half* __restrict__ xp,
                                     int M, int Mpad, int K, int* __restrict__ ticket, int tiles) {
-  if (blockIdx.x == 0)  // split-K tickets of the GEMM launch that follows in the stream
+  // The GEMM that follows in the stream is launched as a programmatic dependent: it may start now and run
+  // its prologue and its weight stream beside this kernel; it waits for this grid's completion (and the
+  // visibility of everything written here) before the first activation copy.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (blockIdx.x == 0)  // split-K tickets of that GEMM
     for (int t = threadIdx.x; t < tiles; t += blockDim.x) ticket[t] = 0;
   const int kblocks = K / kBlockK;
   const int64_t total = (int64_t)kblocks * Mpad * 8;
@@ -317,6 +321,9 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
       RingPos p{0, 0}, pe{0, 0};
       const unsigned char* src = reinterpret_cast<const unsigned char*>(g.xp) + (size_t)kb0 * b_bytes;
       const int nslots = (nkb + bs - 1) / bs;
+      // The activations (and the zeroed split-K tickets) come from the preparation kernel launched just
+      // before this one: wait for it here, and nowhere else; all later uses hang off these copies.
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int j = 0; j < nslots; ++j, src += slot_bytes) {
         if (j >= Rb) {
           if (bs == 1) {
@@ -488,12 +495,32 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
     __syncthreads();
     if (s_last) {
       __threadfence();
-      for (int e = threadIdx.x; e < g.M * kTileN; e += kThreads) {
-        const int m = e / kTileN, c = e - m * kTileN;
-        float acc = 0.f;
-        for (int sp = 0; sp < g.splits; ++sp)
-          acc += __ldcg(g.partial + (((size_t)tile * g.splits + sp) * g.Mpad + m) * kTileN + c);
-        g.y[(size_t)m * g.y_stride + tile * kTileN + c] = __float2bfloat16_rn(acc);
+      // four columns per thread and step, the partials of up to eight splits in flight at once, added in
+      // split order (the same bits on every call)
+      const float4* part4 = reinterpret_cast<const float4*>(g.partial + (size_t)tile * g.splits * g.Mpad * kTileN);
+      const size_t split_stride = (size_t)g.Mpad * (kTileN / 4);
+      for (int e = threadIdx.x; e < g.M * (kTileN / 4); e += kThreads) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp0 = 0; sp0 < g.splits; sp0 += 8) {
+          float4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            v[u] = sp0 + u < g.splits ? __ldcg(part4 + (size_t)(sp0 + u) * split_stride + e)
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            acc.x += v[u].x;
+            acc.y += v[u].y;
+            acc.z += v[u].z;
+            acc.w += v[u].w;
+          }
+        }
+        const int m = e / (kTileN / 4), c = (e - m * (kTileN / 4)) * 4;
+        __nv_bfloat16* dst = g.y + (size_t)m * g.y_stride + tile * kTileN + c;
+        dst[0] = __float2bfloat16_rn(acc.x);
+        dst[1] = __float2bfloat16_rn(acc.y);
+        dst[2] = __float2bfloat16_rn(acc.z);
+        dst[3] = __float2bfloat16_rn(acc.w);
       }
     }
   }
@@ -525,6 +552,8 @@ bool make_plan(int M, int N, int K, Plan* p) {
   if (splits < 1) splits = 1;
   if (splits > p->kblocks) splits = p->kblocks;
   if (splits > 64) splits = 64;
+  // the last CTA of a tile reads splits x Mpad x 128 partial sums alone: keep that under 1 MB
+  if (splits * p->Mpad > 2048) splits = 2048 / p->Mpad;
   // every split gets at least one K block
   const int per = (p->kblocks + splits - 1) / splits;
   splits = (p->kblocks + per - 1) / per;
@@ -637,6 +666,16 @@ extern "C" int subspec_w4a16_gemm(const subspec_w4a16_args* args, subspec_stream
   rc = cuda_check(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)p.smem_bytes));
   if (rc) return rc;
-  w4a16_gemm_kernel<<<dim3(p.tiles, p.splits), kThreads, p.smem_bytes, st>>>(g);
-  return cuda_check(cudaGetLastError());
+  // programmatic dependent launch: the prologue and the packed-weight copies overlap the preparation kernel
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.tiles, p.splits);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = p.smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cuda_check(cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, g));
 }
