@@ -815,13 +815,16 @@ struct Bits16<__half> {
 __device__ __forceinline__ uint32_t key_of(uint32_t bits) {
   return (bits & 0x8000u) ? (~bits & 0xFFFFu) : (bits | 0x8000u);
 }
-// Histogram word w lives at swz(w): each 32-word row is XOR-rotated by its row number, so that the
-// per-thread scans (thread t walks row t) hit 32 different banks across a warp.
-__device__ __forceinline__ uint32_t swz(uint32_t w) { return (w & ~31u) | ((w ^ (w >> 5)) & 31u); }
 __device__ __forceinline__ uint32_t bits_of(uint32_t key) {
   return (key & 0x8000u) ? (key & 0x7FFFu) : (~key & 0xFFFFu);
 }
-
+// The histogram is indexed by the RAW 16-bit pattern (no key arithmetic per counted element): counter
+// `bits` is half (bits & 1) of word bits >> 1.  A "row" is 32 words = 64 consecutive patterns = 64
+// consecutive keys (ascending patterns for positive floats, descending for negative ones), and thread t
+// of the scans owns the row of keys [64 t, 64 t + 64).  Word w lives at hist_pos(w): the 16-byte groups
+// of a row are XOR-rotated by the row number, so that the 128-bit loads of a quarter-warp (eight
+// threads, eight consecutive rows) hit eight different bank groups.
+__device__ __forceinline__ uint32_t hist_pos(uint32_t w) { return w ^ (((w >> 5) & 7u) << 2); }
 // Eight consecutive raw 16-bit patterns starting at element i0 (a multiple of 8); elements at or beyond
 // V read as -inf.
 template <typename T>
@@ -840,6 +843,42 @@ __device__ __forceinline__ void load8(const T* rowp, int i0, int V, bool vec_ok,
     for (int j = 0; j < 8; ++j) b[j] = (i0 + j < V) ? (uint32_t)p[i0 + j] : Bits16<T>::kNegInf;
   }
 }
+
+// The same eight patterns, still packed two to a word (element i0 + 2 j in the low half of word j).
+template <typename T>
+__device__ __forceinline__ uint4 load8_packed(const T* rowp, int i0, int V, bool vec_ok) {
+  if (vec_ok && i0 + 8 <= V) return *reinterpret_cast<const uint4*>(rowp + i0);
+  uint32_t b[8];
+  load8<T>(rowp, i0, V, false, b);
+  return make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16));
+}
+__device__ __forceinline__ void unpack8(const uint4& q, uint32_t (&b)[8]) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    b[2 * j] = w[j] & 0xFFFFu;
+    b[2 * j + 1] = w[j] >> 16;
+  }
+}
+// the eight values as floats, straight from the packed words
+__device__ __forceinline__ void unpack8_values(const uint4& q, float (&v)[8], __nv_bfloat16) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[2 * j] = __uint_as_float(w[j] << 16);
+    v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ void unpack8_values(const uint4& q, float (&v)[8], __half) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+    v[2 * j] = f.x;
+    v[2 * j + 1] = f.y;
+  }
+}
+constexpr int kSweepDepth = 4;  // chunks a warp has in flight in the two sweeps over the row
 
 __device__ __forceinline__ double shfl_up_f64(double v, int d) {
   int lo = __double2loint(v), hi = __double2hiint(v);
@@ -877,7 +916,8 @@ struct SampleShared {
   double warp_tot[kSWarps];
   double S, cum_before, Z;
   float c, e_b;
-  int kmax, k_b, r, n_b, overflow, flag;
+  double cbase;
+  int kmax, k_b, r, n_b, finite, counted, flag, first, last_nz, cstar, T0;
   int warp_max[kSWarps];
 };
 
@@ -903,38 +943,91 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
 
   // ---- 0. clear the histogram ----
   for (int i = tid; i < kHistWords / 4; i += kSThreads) reinterpret_cast<uint4*>(hist)[i] = make_uint4(0, 0, 0, 0);
-  if (tid == 0) sh.overflow = 0;
+  if (tid == 0) {
+    sh.finite = 0;
+    sh.counted = 0;
+  }
   __syncthreads();
 
   // ---- 1. count every value of the row (HBM pass) ----
   const int nchunks = (V + kChunkElems - 1) / kChunkElems;
-  for (int c = warp; c < nchunks; c += kSWarps) {
-    uint32_t bits[8];
-    load8<T>(rowp, c * kChunkElems + lane * 8, V, vec_ok, bits);
+  int n_finite = 0;
+  // a warp keeps kSweepDepth chunk loads in flight: one 16-byte load per thread at a time would leave the
+  // SM with 16 KB outstanding, a third of what its share of the HBM bandwidth needs
+  constexpr uint32_t kNegInf2 = Bits16<T>::kNegInf | (Bits16<T>::kNegInf << 16);
+  for (int c0 = warp; c0 < nchunks; c0 += kSweepDepth * kSWarps) {
+    uint4 raw[kSweepDepth];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (bits[j] == Bits16<T>::kNegInf) continue;  // masked: no mass, and often far too many to count
-      const uint32_t key = key_of(bits[j]);
-      const uint32_t sh16 = (key & 1u) * 16u;
-      const uint32_t old = atomicAdd(&hist[swz(key >> 1)], 1u << sh16);
-      if (((old >> sh16) & 0xFFFFu) == 0xFFFFu) sh.overflow = 1;
+    for (int d = 0; d < kSweepDepth; ++d) {
+      const int c = c0 + d * kSWarps;
+      raw[d] = c < nchunks ? load8_packed<T>(rowp, c * kChunkElems + lane * 8, V, vec_ok)
+                           : make_uint4(kNegInf2, kNegInf2, kNegInf2, kNegInf2);
+    }
+#pragma unroll
+    for (int d = 0; d < kSweepDepth; ++d) {
+      uint32_t bits[8];
+      unpack8(raw[d], bits);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t bj = bits[j];
+        if (bj != Bits16<T>::kNegInf) {  // masked: no mass, and often far too many to count
+          atomicAdd(&hist[hist_pos(bj >> 1)], 1u + (bj & 1u) * 0xFFFFu);  // no return value: a reduction
+          ++n_finite;
+        }
+      }
     }
   }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) n_finite += __shfl_xor_sync(0xffffffffu, n_finite, off);
+  if (lane == 0 && n_finite) atomicAdd(&sh.finite, n_finite);
   __syncthreads();
-  if (sh.overflow) {  // one value more than 65535 times in a row: the 16-bit counters cannot hold it
-    if (tid == 0) flag(a.dev_status, SUBSPEC_DEV_HIST_OVERFLOW);
-    return;
-  }
 
   // ---- 2. the histogram: maximum, denominator, nucleus boundary ----
-  // thread t owns keys [64 t, 64 t + 64) = words [32 t, 32 t + 32)
-  auto cnt_of = [&](int i) -> uint32_t {  // counter of key 64 t + i
-    const uint32_t w = hist[swz((uint32_t)(tid * 32 + (i >> 1)))];
-    return (i & 1) ? (w >> 16) : (w & 0xFFFFu);
+  // Thread t owns keys [64 t, 64 t + 64) = one row of raw patterns, walked downwards for the negative
+  // floats (t < 512) and upwards for the positive ones.  visit(f) calls f(count, key) for the row's
+  // non-empty counters in ascending key order; empty 16-byte groups and words cost one test each.
+  const bool desc = tid < kSThreads / 2;
+  const uint32_t rowi = desc ? (uint32_t)(kSThreads - 1 - tid) : (uint32_t)(tid - kSThreads / 2);
+  const uint4* row4 = reinterpret_cast<const uint4*>(hist) + rowi * 8;
+  auto visit = [&](auto&& f) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int gi = desc ? 7 - i : i;
+      const uint4 q = row4[gi ^ (int)(rowi & 7u)];
+      if ((q.x | q.y | q.z | q.w) == 0u) continue;
+      const uint32_t wd[4] = {desc ? q.w : q.x, desc ? q.z : q.y, desc ? q.y : q.z, desc ? q.x : q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t w = wd[j];
+        if (w == 0u) continue;
+        const uint32_t c0 = desc ? (w >> 16) : (w & 0xFFFFu), c1 = desc ? (w & 0xFFFFu) : (w >> 16);
+        const int key = tid * 64 + i * 8 + j * 2;
+        if (c0) f(c0, key);
+        if (c1) f(c1, key + 1);
+      }
+    }
   };
+  auto count_of = [&](int key) -> int {  // one counter, by key
+    const uint32_t pat = bits_of((uint32_t)key);
+    const uint32_t w = hist[hist_pos(pat >> 1)];
+    return (int)((pat & 1u) ? (w >> 16) : (w & 0xFFFFu));
+  };
+  // this thread's highest occupied key: the row's eight 16-byte groups in ascending key order, one compare
+  // and select per counter, no branches
   int kmax = -1;
-  for (int i = 0; i < 64; ++i)
-    if (cnt_of(i)) kmax = tid * 64 + i;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gi = desc ? 7 - i : i;
+    const uint4 q = row4[gi ^ (int)(rowi & 7u)];
+    const uint32_t wd[4] = {desc ? q.w : q.x, desc ? q.z : q.y, desc ? q.y : q.z, desc ? q.x : q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t lo = desc ? (wd[j] >> 16) : (wd[j] & 0xFFFFu), hi = desc ? (wd[j] & 0xFFFFu) : (wd[j] >> 16);
+      kmax = lo ? i * 8 + j * 2 : kmax;
+      kmax = hi ? i * 8 + j * 2 + 1 : kmax;
+    }
+  }
+  if (kmax >= 0) kmax += tid * 64;
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, off));
   if (lane == 0) sh.warp_max[warp] = kmax;
@@ -949,6 +1042,10 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
   const int K_max = sh.kmax;
   const size_t nb = (size_t)b * a.max_nodes;
   if (K_max < 0) {  // nothing but -inf / empty: no distribution to sample from
+    if (sh.finite != 0) {  // ... or 65536 copies of one value wrapped its counter to zero
+      if (tid == 0) flag(a.dev_status, SUBSPEC_DEV_HIST_OVERFLOW);
+      return;
+    }
     if (tid == 0) {
       a.node_target[nb + u] = 0;
       a.node_entropy[nb + u] = 0.f;
@@ -957,30 +1054,61 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
     }
   } else {
     const float c = sh.c;
-    // masses of this thread's values, ascending
-    double M_t = 0.0;
-    for (int i = 0; i < 64; ++i) {
-      const uint32_t n = cnt_of(i);
-      if (n) {
-        const float e = ex2f(fmaf(Bits16<T>::value(bits_of((uint32_t)(tid * 64 + i))), kT, -c));
-        M_t += (double)n * (double)e;
+    // Masses of this thread's values, ascending; and how many elements the counters hold.  Within a thread
+    // (64 keys) the sums run in single precision; double precision, slow on this part, is kept for the
+    // scan across threads and for the handful of scalars derived from it.
+    // An empty 16-byte group costs one test; inside a non-empty one all eight counters are processed
+    // without branches (an empty counter adds nothing), which gives the same partial sums as visiting the
+    // non-empty ones alone.
+    float m32 = 0.f;
+    int N_t = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int gi = desc ? 7 - i : i;
+      const uint4 q = row4[gi ^ (int)(rowi & 7u)];
+      if ((q.x | q.y | q.z | q.w) == 0u) continue;
+      const uint32_t wd[4] = {desc ? q.w : q.x, desc ? q.z : q.y, desc ? q.y : q.z, desc ? q.x : q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t c0 = desc ? (wd[j] >> 16) : (wd[j] & 0xFFFFu), c1 = desc ? (wd[j] & 0xFFFFu) : (wd[j] >> 16);
+        const int key = tid * 64 + i * 8 + j * 2;
+        const float e0 = ex2f(fmaf(Bits16<T>::value(bits_of((uint32_t)key)), kT, -c));
+        const float e1 = ex2f(fmaf(Bits16<T>::value(bits_of((uint32_t)key + 1u)), kT, -c));
+        const float s0 = fmaf((float)c0, e0, m32);
+        m32 = c0 ? s0 : m32;
+        const float s1 = fmaf((float)c1, e1, m32);
+        m32 = c1 ? s1 : m32;
+        N_t += (int)(c0 + c1);
       }
     }
+    const double M_t = (double)m32;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) N_t += __shfl_xor_sync(0xffffffffu, N_t, off);
+    if (lane == 0 && N_t) atomicAdd(&sh.counted, N_t);
     // block exclusive scan of M_t in key order
     const double incl = warp_scan_f64(M_t);
     if (lane == 31) sh.warp_tot[warp] = incl;
     __syncthreads();
-    double base = 0.0, total = 0.0;
-    for (int w = 0; w < kSWarps; ++w) {
-      const double t = sh.warp_tot[w];
-      if (w < warp) base += t;
-      total += t;
+    if (sh.counted != sh.finite) {
+      // a 16-bit counter wrapped (one value more than 65535 times in the row): the counters no longer add
+      // up to the number of elements counted, whichever way the carry went
+      if (tid == 0) flag(a.dev_status, SUBSPEC_DEV_HIST_OVERFLOW);
+      return;
     }
-    const double P_t = base + incl - M_t;
+    // the 32 warp totals are scanned by one warp, not added up by every thread: double-precision adds are
+    // the slowest instructions this kernel has
+    if (warp == 0) {
+      const double x = sh.warp_tot[lane];
+      const double xs = warp_scan_f64(x);
+      sh.warp_tot[lane] = xs - x;
+      if (lane == 31) sh.S = xs;
+    }
+    __syncthreads();
+    const double total = sh.S;
+    const double P_t = sh.warp_tot[warp] + incl - M_t;
     const double thrS = (double)ka.remove_below * total;  // remove while cumulative mass <= thrS
     if (tid == 0) {
       // default: the filter is off, or the threshold is never passed (keep only the last of the maximum)
-      sh.S = total;
       sh.k_b = -1;
       sh.r = 0;
       sh.n_b = 0;
@@ -990,33 +1118,41 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
     __syncthreads();
     if (ka.remove_below > 0.f) {
       if (M_t > 0.0 && P_t <= thrS && thrS < P_t + M_t) {
-        double cum = P_t;
-        for (int i = 0; i < 64; ++i) {
-          const int n = (int)cnt_of(i);
-          if (!n) continue;
-          const int key = tid * 64 + i;
+        // the same single-precision partial sums as above, against the threshold's distance from this
+        // thread's base; the boundary key is the first whose run of equal values passes it (the last
+        // non-empty key if rounding lets none pass)
+        const float rem = (float)(thrS - P_t);
+        float loc = 0.f, loc_b = 0.f, e_k = 0.f;
+        int key_b = -1, n_k = 0;
+        bool found = false;
+        visit([&](uint32_t cnt, int key) {
+          if (found) return;
           const float e = ex2f(fmaf(Bits16<T>::value(bits_of((uint32_t)key)), kT, -c));
-          const double me = (double)n * (double)e;
-          if (cum + me > thrS) {
-            int r = (int)floor((thrS - cum) / (double)e);
-            r = min(max(r, 0), n);
-            if (key == K_max) r = min(r, n - 1);
-            sh.k_b = key;
-            sh.r = r;
-            sh.n_b = n;
-            sh.e_b = e;
-            sh.cum_before = cum;
-            break;
-          }
-          cum += me;
-        }
+          const float nxt = fmaf((float)cnt, e, loc);
+          key_b = key;
+          n_k = (int)cnt;
+          e_k = e;
+          loc_b = loc;
+          if (nxt > rem)
+            found = true;
+          else
+            loc = nxt;
+        });
+        const double cum = P_t + (double)loc_b;
+        int r = found ? (int)floor((thrS - cum) / (double)e_k) : n_k;
+        r = min(max(r, 0), n_k);
+        if (key_b == K_max) r = min(r, n_k - 1);
+        sh.k_b = key_b;
+        sh.r = r;
+        sh.n_b = n_k;
+        sh.e_b = e_k;
+        sh.cum_before = cum;
       }
       __syncthreads();
       if (tid == 0 && sh.k_b < 0) {
         // thrS >= total (top_p ~ 0): everything below the maximum goes, and all but the last of the maximum
         sh.k_b = K_max;
-        const uint32_t w = hist[swz((uint32_t)K_max >> 1)];
-        const int n = (int)((K_max & 1) ? (w >> 16) : (w & 0xFFFFu));
+        const int n = count_of(K_max);
         const float e = ex2f(fmaf(Bits16<T>::value(bits_of((uint32_t)K_max)), kT, -c));
         sh.n_b = n;
         sh.r = n - 1;
@@ -1031,79 +1167,156 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
     __syncthreads();  // the histogram is no longer needed after this point
 
     // ---- 3. second sweep: surviving mass and boundary ties per chunk, vocabulary order (L2 pass) ----
-    for (int cidx = warp; cidx < nchunks; cidx += kSWarps) {
-      uint32_t bits[8];
-      load8<T>(rowp, cidx * kChunkElems + lane * 8, V, vec_ok, bits);
-      float mass = 0.f;
-      int ties = 0;
+    // Survivors are the values above the boundary value, ties the values equal to it: float compares, except
+    // when the boundary is one of the two zeros, which compare equal as floats but are two keys.
+    const uint32_t pat_b = k_b >= 0 ? bits_of((uint32_t)k_b) : (uint32_t)Bits16<T>::kNegInf;
+    const float v_b = Bits16<T>::value(pat_b);
+    const bool zero_boundary = k_b >= 0 && (pat_b & 0x7FFFu) == 0u;
+    for (int c0 = warp; c0 < nchunks; c0 += kSweepDepth * kSWarps) {
+      uint4 raw[kSweepDepth];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (bits[j] == Bits16<T>::kNegInf) continue;
-        const int key = (int)key_of(bits[j]);
-        if (key > k_b)
-          mass += ex2f(fmaf(Bits16<T>::value(bits[j]), kT, -c));
-        else if (key == k_b)
-          ++ties;
+      for (int d = 0; d < kSweepDepth; ++d) {
+        const int cidx = c0 + d * kSWarps;
+        raw[d] = cidx < nchunks ? load8_packed<T>(rowp, cidx * kChunkElems + lane * 8, V, vec_ok)
+                                : make_uint4(kNegInf2, kNegInf2, kNegInf2, kNegInf2);
       }
+      float mass[kSweepDepth];
+      int ties[kSweepDepth];
+#pragma unroll
+      for (int d = 0; d < kSweepDepth; ++d) {
+        mass[d] = 0.f;
+        ties[d] = 0;
+        if (!zero_boundary) {
+          float v[8];
+          unpack8_values(raw[d], v, T());
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (v[j] > v_b) mass[d] += ex2f(fmaf(v[j], kT, -c));
+            ties[d] += (v[j] == v_b) ? 1 : 0;
+          }
+        } else {
+          uint32_t bits[8];
+          unpack8(raw[d], bits);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (bits[j] == Bits16<T>::kNegInf) continue;
+            const int key = (int)key_of(bits[j]);
+            if (key > k_b)
+              mass[d] += ex2f(fmaf(Bits16<T>::value(bits[j]), kT, -c));
+            else if (key == k_b)
+              ++ties[d];
+          }
+        }
+      }
+      // the warp sums of the chunks in flight, their shuffle chains interleaved
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) {
-        mass += __shfl_xor_sync(0xffffffffu, mass, off);
-        ties += __shfl_xor_sync(0xffffffffu, ties, off);
+#pragma unroll
+        for (int d = 0; d < kSweepDepth; ++d) {
+          mass[d] += __shfl_xor_sync(0xffffffffu, mass[d], off);
+          ties[d] += __shfl_xor_sync(0xffffffffu, ties[d], off);
+        }
       }
-      if (lane == 0) {
-        ch_mass[cidx] = mass;
-        ch_ties[cidx] = (uint32_t)ties;
+      if (lane < kSweepDepth) {
+        const int cidx = c0 + lane * kSWarps;
+        if (cidx < nchunks) {
+          float m = mass[0];
+          int t = ties[0];
+#pragma unroll
+          for (int d = 1; d < kSweepDepth; ++d)
+            if (lane == d) {
+              m = mass[d];
+              t = ties[d];
+            }
+          ch_mass[cidx] = m;
+          ch_ties[cidx] = (uint32_t)t;
+        }
       }
     }
     __syncthreads();
 
-    // ---- 4./5. locate the chunk, then the element, where the cumulative surviving mass passes u * Z ----
-    if (warp == 0) {
-      const double Z = sh.Z;
-      const double target = (double)a.uniforms[nb + u] * Z;
-      const int per = (nchunks + 31) / 32;
-      const int c0 = min(lane * per, nchunks), c1 = min(c0 + per, nchunks);
-      int tl = 0;
-      for (int cc = c0; cc < c1; ++cc) tl += (int)ch_ties[cc];
-      const int T_lane0 = warp_scan_i32(tl) - tl;
-      double local = 0.0;
-      int Trun = T_lane0;
+    // ---- 4. locate the chunk where the cumulative surviving mass passes u * Z: the whole block, each
+    // thread a run of `per` consecutive chunks (one, up to 262144 tokens), two block scans ----
+    const double Z = sh.Z;
+    const double target = (double)a.uniforms[nb + u] * Z;
+    const int per = (nchunks + kSThreads - 1) / kSThreads;
+    const int c0 = min(tid * per, nchunks), c1 = min(c0 + per, nchunks);
+    int tl = 0;
+    for (int cc = c0; cc < c1; ++cc) tl += (int)ch_ties[cc];
+    if (tid == 0) {
+      sh.first = kSThreads;
+      sh.last_nz = -1;
+    }
+    // exclusive block scan of the tie counts
+    int T_thread0;
+    {
+      const int incl = warp_scan_i32(tl);
+      if (lane == 31) sh.warp_max[warp] = incl;
+      __syncthreads();
+      if (warp == 0) {
+        const int x = sh.warp_max[lane];
+        sh.warp_max[lane] = warp_scan_i32(x) - x;
+      }
+      __syncthreads();
+      T_thread0 = sh.warp_max[warp] + incl - tl;
+    }
+    double local = 0.0;
+    {
+      int Trun = T_thread0;
       for (int cc = c0; cc < c1; ++cc) {
         const int T1 = Trun + (int)ch_ties[cc];
         local += (double)ch_mass[cc] + (double)e_b * (double)(max(T1 - r_rm, 0) - max(Trun - r_rm, 0));
         Trun = T1;
       }
-      const double lincl = warp_scan_f64(local);
-      const double lbase = lincl - local;
-      const uint32_t cross = __ballot_sync(0xffffffffu, local > 0.0 && lbase + local > target);
-      const uint32_t nonzero = __ballot_sync(0xffffffffu, local > 0.0);
-      // no crossing (u * Z rounds up to the total): the last token with surviving mass
-      const bool pick_last = cross == 0;
-      const int L = pick_last ? (nonzero ? 31 - __clz(nonzero) : 0) : __ffs(cross) - 1;
-      int cstar = 0, T0 = 0;
-      double cbase = 0.0;
-      if (lane == L) {
-        double cum = lbase;
-        Trun = T_lane0;
-        cstar = c0;
-        T0 = Trun;
-        cbase = cum;
-        for (int cc = c0; cc < c1; ++cc) {
-          const int T1 = Trun + (int)ch_ties[cc];
-          const double cm = (double)ch_mass[cc] + (double)e_b * (double)(max(T1 - r_rm, 0) - max(Trun - r_rm, 0));
-          if (cm > 0.0) {  // candidate: the crossing chunk, or (pick_last) the last chunk with mass
-            cstar = cc;
-            T0 = Trun;
-            cbase = cum;
-            if (!pick_last && cum + cm > target) break;
-          }
-          cum += cm;
-          Trun = T1;
-        }
+    }
+    // exclusive block scan of the surviving mass, thread order = vocabulary order
+    double lbase;
+    {
+      const double incl = warp_scan_f64(local);
+      if (lane == 31) sh.warp_tot[warp] = incl;
+      __syncthreads();
+      if (warp == 0) {
+        const double x = sh.warp_tot[lane];
+        sh.warp_tot[lane] = warp_scan_f64(x) - x;
       }
-      cstar = __shfl_sync(0xffffffffu, cstar, L);
-      T0 = __shfl_sync(0xffffffffu, T0, L);
-      cbase = shfl_f64(cbase, L);
+      __syncthreads();
+      lbase = sh.warp_tot[warp] + incl - local;
+    }
+    if (local > 0.0) {
+      if (lbase + local > target) atomicMin(&sh.first, tid);
+      atomicMax(&sh.last_nz, tid);
+    }
+    __syncthreads();
+    // no crossing (u * Z rounds up to the total): the last token with surviving mass
+    const bool pick_last = sh.first == kSThreads;
+    const int L = pick_last ? max(sh.last_nz, 0) : sh.first;
+    if (tid == L) {
+      double cum = lbase;
+      int Trun = T_thread0;
+      int cstar = c0, T0 = Trun;
+      double cbase = cum;
+      for (int cc = c0; cc < c1; ++cc) {
+        const int T1 = Trun + (int)ch_ties[cc];
+        const double cm = (double)ch_mass[cc] + (double)e_b * (double)(max(T1 - r_rm, 0) - max(Trun - r_rm, 0));
+        if (cm > 0.0) {  // candidate: the crossing chunk, or (pick_last) the last chunk with mass
+          cstar = cc;
+          T0 = Trun;
+          cbase = cum;
+          if (!pick_last && cum + cm > target) break;
+        }
+        cum += cm;
+        Trun = T1;
+      }
+      sh.cstar = min(cstar, nchunks - 1);
+      sh.T0 = T0;
+      sh.cbase = cbase;
+    }
+    __syncthreads();
+
+    // ---- 5. the element inside that chunk: one warp ----
+    if (warp == 0) {
+      const int cstar = sh.cstar, T0 = sh.T0;
+      const double cbase = sh.cbase;
 
       uint32_t bits[8];
       load8<T>(rowp, cstar * kChunkElems + lane * 8, V, vec_ok, bits);

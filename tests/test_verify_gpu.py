@@ -187,3 +187,60 @@ def test_stochastic_sample_and_match(cuda_lib, vocab, nodes, dtype, temperature,
         assert res[b].hidden_indices.tolist() == r.hidden
         assert (res[b].total_len, res[b].accept_len) == (r.total_len, r.accept_len)
     assert decided_by_rounding <= max(2, B * nodes // 10)
+
+
+def test_stochastic_ties_masks_and_zeros(cuda_lib):
+    """Rows made of a handful of distinct values (-inf masks, both zeros, long runs of ties): the sampler's
+    count histogram, its tie rule (lowest vocabulary index goes first) and the second sweep's value compares."""
+    from transformers.generation.logits_process import LogitsProcessorList, TopPLogitsWarper
+    vocab, nodes, B = 3000, 16, 2
+    gen = torch.Generator().manual_seed(77)
+    sts = [synthetic.random_tree(nodes, 6, 4, vocab, gen) for _ in range(B)]
+    levels = torch.tensor([float("-inf"), -3.0, -0.0, 0.0, 0.5, 1.0, 2.5, 4.0])
+    weights = torch.tensor([0.3, 0.2, 0.1, 0.1, 0.15, 0.1, 0.04, 0.01])
+    idx = torch.multinomial(weights, B * nodes * vocab, replacement=True, generator=gen).reshape(B, nodes, vocab)
+    logits = levels[idx].to(torch.bfloat16)
+    logits[:, :, 7] = 4.0  # never a row without a finite value
+    uniforms = torch.rand(B, nodes, generator=gen)
+    checked = 0
+    # the ascending cumulative probability passes 1 - top_p inside the run of -3s, of 0.5s, of 2.5s, of 4s;
+    # with 0.9 it passes inside the run of zeros, where the kernel orders -0 before +0 and a stable sort on
+    # values does not: there only what both agree on is checked (nothing at or below -3 survives)
+    for top_p in (0.999, 0.8, 0.5, 0.05, 0.9):
+        procs = LogitsProcessorList([TopPLogitsWarper(top_p=top_p)])
+        verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
+                            eos_token_id=None, logits_processor=procs, do_sample=True, verify_method="stochastic",
+                            uniforms=uniforms)
+        from subspec_b200.verify import get_workspace
+        targets = get_workspace(B, nodes, torch.device("cuda", 0)).fetch()["node_target"]
+        for b, st in enumerate(sts):
+            probs = vo.target_probs(logits[b], True, 1.0, top_p, upcast=True)
+            want = vo.target_tokens(probs, True, uniforms[b].tolist())
+            margins = vo.sampling_margins(logits[b], 1.0, top_p, uniforms[b].tolist())
+            for u in range(st.n):
+                assert float(logits[b, u, int(targets[b, u])]) > float("-inf")  # never a masked token
+                if top_p == 0.9:
+                    assert float(logits[b, u, int(targets[b, u])]) >= 0.0
+                elif margins[u][0] > 1e-3 and margins[u][1] > 1e-6:
+                    assert int(targets[b, u]) == want[u], (top_p, b, u, margins[u])
+                    checked += 1
+    assert checked >= B * nodes * 2
+
+
+def test_stochastic_counter_overflow_is_reported(cuda_lib):
+    """More than 65535 equal finite values in one row do not fit the sampler's 16-bit counters: reported."""
+    vocab, nodes = 70016, 2
+    st = synthetic.SynthTree(torch.tensor([0, 5]), torch.tensor([-1, 0]), torch.tensor([0, 1]))
+    for copies in (65536, 66000):
+        logits = torch.randn(1, nodes, vocab).to(torch.bfloat16)
+        logits[0, 1, :copies] = 0.75
+        with pytest.raises(ValueError, match="65535"):
+            verify_tree_batched(trees=[_tree_of(st)], root_inds=[0], logits=logits.cuda(), eos_token_id=None,
+                                logits_processor=None, do_sample=True, verify_method="stochastic",
+                                uniforms=torch.rand(1, nodes))
+    # exactly 65535 copies still fit
+    logits = torch.randn(1, nodes, vocab).to(torch.bfloat16)
+    logits[0, 1, :65535] = 0.75
+    logits[0, 1, 65535:][logits[0, 1, 65535:] == 0.75] = 0.5
+    verify_tree_batched(trees=[_tree_of(st)], root_inds=[0], logits=logits.cuda(), eos_token_id=None,
+                        logits_processor=None, do_sample=True, verify_method="stochastic", uniforms=torch.rand(1, nodes))
