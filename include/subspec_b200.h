@@ -136,6 +136,7 @@ typedef struct subspec_verify_args {
   const int32_t* root;      /* [batch] local root index */
   /* sampling */
   int32_t do_sample;
+  int32_t top_k;      /* 0 = off; else keep every score >= the k-th largest (TopKLogitsWarper, base.py:58-59) */
   double temperature; /* > 0 */
   double top_p;       /* >= 1 disables the nucleus filter */
   const float* uniforms; /* [batch, max_nodes], required iff do_sample */

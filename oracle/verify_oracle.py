@@ -51,14 +51,24 @@ def top_p_filter(scores: torch.Tensor, top_p: float) -> torch.Tensor:
     return scores.masked_fill(mask, -float("inf"))
 
 
+def top_k_filter(scores: torch.Tensor, top_k: int) -> torch.Tensor:
+    """HF's TopKLogitsWarper: everything strictly below the k-th largest score goes (ties with it stay)."""
+    k = min(int(top_k), scores.shape[-1])
+    kth = torch.topk(scores, k, dim=-1).values[..., -1:]
+    return scores.masked_fill(scores < kth, -float("inf"))
+
+
 def target_probs(logits: torch.Tensor, do_sample: bool = False, temperature: float = 1.0,
-                 top_p: float = 1.0, upcast: bool = False) -> torch.Tensor:
-    """[N, V] probabilities in the logits' dtype (or fp32 when `upcast`), as _sample_token returns them."""
+                 top_p: float = 1.0, upcast: bool = False, top_k: int = 0) -> torch.Tensor:
+    """[N, V] probabilities in the logits' dtype (or fp32 when `upcast`), as _sample_token returns them
+    (generators/base.py:109-139 with the warpers of :42-64: temperature, top-k, top-p in that order)."""
     x = logits.float() if upcast else logits
     x = x.reshape(-1, x.shape[-1])
     if do_sample:
         if temperature != 1.0:
             x = x / temperature
+        if top_k:
+            x = top_k_filter(x, top_k)
         if top_p < 1.0:
             x = top_p_filter(x, top_p)
     return torch.softmax(x, dim=-1)
@@ -80,12 +90,15 @@ def inverse_cdf_pick(row: torch.Tensor, u01: float) -> int:
     return min(i, last)
 
 
-def sampling_margins(logits: torch.Tensor, temperature: float, top_p: float, uniforms: Sequence[float]):
+def sampling_margins(logits: torch.Tensor, temperature: float, top_p: float, uniforms: Sequence[float],
+                     top_k: int = 0):
     """Per row, how far the two discrete decisions of the sampler are from flipping (fp64):
     `boundary`: distance of the nucleus threshold from the nearest cumulative probability, in
     units of that token's probability; `pick`: distance of u from the nearest CDF edge, relative
     to the total.  Rows with tiny margins are decided by rounding, not by the algorithm."""
     x = logits.double().reshape(-1, logits.shape[-1]) / temperature
+    if top_k:
+        x = top_k_filter(x, top_k)
     out = []
     for u in range(x.shape[0]):
         sorted_logits, sorted_idx = torch.sort(x[u], descending=False, stable=True)
@@ -247,9 +260,9 @@ def verify(*, logits: torch.Tensor, token_ids: Sequence[int], children: Sequence
            eos: Optional[int] = None, method: str = "exact", do_sample: bool = False, temperature: float = 1.0,
            top_p: float = 1.0, uniforms: Optional[Sequence[float]] = None, threshold: float = 0.0,
            window: int = 1, threshold_method: str = "prob", upcast: bool = False,
-           input_is_probs: bool = False) -> VerifyResult:
+           input_is_probs: bool = False, top_k: int = 0) -> VerifyResult:
     """One sequence, local indexing, every node decoded (n_rows = len(token_ids) = logits.shape[0])."""
-    probs = logits if input_is_probs else target_probs(logits, do_sample, temperature, top_p, upcast)
+    probs = logits if input_is_probs else target_probs(logits, do_sample, temperature, top_p, upcast, top_k)
     n = int(probs.shape[0])
     tgt = target_tokens(probs, do_sample, uniforms)
     if method == "exact":

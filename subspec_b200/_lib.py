@@ -47,7 +47,7 @@ class VerifyArgs(C.Structure):
         ("input_kind", _i32), ("seq_stride", _i64), ("row_stride", _i64), ("logits", _vp),
         ("n_nodes", _vp), ("n_rows", _vp), ("token_ids", _vp), ("child_off", _vp), ("child_idx", _vp),
         ("root", _vp),
-        ("do_sample", _i32), ("temperature", _f64), ("top_p", _f64), ("uniforms", _vp),
+        ("do_sample", _i32), ("top_k", _i32), ("temperature", _f64), ("top_p", _f64), ("uniforms", _vp),
         ("method", _i32), ("gate", _i32), ("threshold", _f64), ("window", _i32), ("eos", _i64),
         ("max_out", _i32), ("out_tokens", _vp), ("out_hidden", _vp), ("out_meta", _vp),
         ("node_target", _vp), ("node_entropy", _vp), ("node_child_prob", _vp), ("node_rowmax", _vp),

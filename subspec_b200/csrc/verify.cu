@@ -886,6 +886,12 @@ __device__ __forceinline__ double shfl_up_f64(double v, int d) {
   hi = __shfl_up_sync(0xffffffffu, hi, d);
   return __hiloint2double(hi, lo);
 }
+__device__ __forceinline__ double shfl_xor_f64(double v, int mask) {
+  int lo = __double2loint(v), hi = __double2hiint(v);
+  lo = __shfl_xor_sync(0xffffffffu, lo, mask);
+  hi = __shfl_xor_sync(0xffffffffu, hi, mask);
+  return __hiloint2double(hi, lo);
+}
 __device__ __forceinline__ double shfl_f64(double v, int src) {
   int lo = __double2loint(v), hi = __double2hiint(v);
   lo = __shfl_sync(0xffffffffu, lo, src);
@@ -917,7 +923,8 @@ struct SampleShared {
   double S, cum_before, Z;
   float c, e_b;
   double cbase;
-  int kmax, k_b, r, n_b, finite, counted, flag, first, last_nz, cstar, T0;
+  double T2;
+  int kmax, k_b, r, n_b, finite, counted, flag, first, last_nz, cstar, T0, k_k, itotal, rank;
   int warp_max[kSWarps];
 };
 
@@ -946,6 +953,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
   if (tid == 0) {
     sh.finite = 0;
     sh.counted = 0;
+    sh.k_k = 0;
   }
   __syncthreads();
 
@@ -1015,6 +1023,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
   // this thread's highest occupied key: the row's eight 16-byte groups in ascending key order, one compare
   // and select per counter, no branches
   int kmax = -1;
+  int N_all = 0;  // elements in this thread's 64 counters
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int gi = desc ? 7 - i : i;
@@ -1025,9 +1034,18 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
       const uint32_t lo = desc ? (wd[j] >> 16) : (wd[j] & 0xFFFFu), hi = desc ? (wd[j] & 0xFFFFu) : (wd[j] >> 16);
       kmax = lo ? i * 8 + j * 2 : kmax;
       kmax = hi ? i * 8 + j * 2 + 1 : kmax;
+      N_all += (int)(lo + hi);
     }
   }
   if (kmax >= 0) kmax += tid * 64;
+  // counter of this thread's m-th key (0..63, ascending), for the walks that one thread does alone
+  auto counter_at = [&](int m) -> int {
+    const int gi = desc ? 7 - (m >> 3) : (m >> 3);
+    const int wj = desc ? 3 - ((m >> 1) & 3) : ((m >> 1) & 3);
+    const uint32_t w = hist[(rowi * 8 + (uint32_t)(gi ^ (int)(rowi & 7u))) * 4 + (uint32_t)wj];
+    const bool high = desc ? (m & 1) == 0 : (m & 1) != 0;
+    return (int)(high ? (w >> 16) : (w & 0xFFFFu));
+  };
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, off));
   if (lane == 0) sh.warp_max[warp] = kmax;
@@ -1041,6 +1059,32 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
   __syncthreads();
   const int K_max = sh.kmax;
   const size_t nb = (size_t)b * a.max_nodes;
+  // ---- top-k (TopKLogitsWarper): every value below the k-th largest goes; k_k = lowest key that stays ----
+  if (ka.a.top_k > 0 && K_max >= 0) {
+    const int incl = warp_scan_i32(N_all);
+    if (lane == 31) sh.warp_max[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      const int x = sh.warp_max[lane];
+      const int xs = warp_scan_i32(x);
+      sh.warp_max[lane] = xs - x;
+      if (lane == 31) sh.itotal = xs;
+    }
+    __syncthreads();
+    const int above = sh.itotal - (sh.warp_max[warp] + incl);  // elements with keys above this thread's range
+    if (N_all > 0 && above < ka.a.top_k && ka.a.top_k <= above + N_all) {
+      int need = ka.a.top_k - above;
+      for (int m = 63; m >= 0; --m) {
+        need -= counter_at(m);
+        if (need <= 0) {
+          sh.k_k = tid * 64 + m;
+          break;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  const int k_k = sh.k_k;
   if (K_max < 0) {  // nothing but -inf / empty: no distribution to sample from
     if (sh.finite != 0) {  // ... or 65536 copies of one value wrapped its counter to zero
       if (tid == 0) flag(a.dev_status, SUBSPEC_DEV_HIST_OVERFLOW);
@@ -1075,9 +1119,9 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
         const float e0 = ex2f(fmaf(Bits16<T>::value(bits_of((uint32_t)key)), kT, -c));
         const float e1 = ex2f(fmaf(Bits16<T>::value(bits_of((uint32_t)key + 1u)), kT, -c));
         const float s0 = fmaf((float)c0, e0, m32);
-        m32 = c0 ? s0 : m32;
+        m32 = (c0 && key >= k_k) ? s0 : m32;  // what top-k removed carries no mass
         const float s1 = fmaf((float)c1, e1, m32);
-        m32 = c1 ? s1 : m32;
+        m32 = (c1 && key + 1 >= k_k) ? s1 : m32;
         N_t += (int)(c0 + c1);
       }
     }
@@ -1126,7 +1170,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
         int key_b = -1, n_k = 0;
         bool found = false;
         visit([&](uint32_t cnt, int key) {
-          if (found) return;
+          if (found || key < k_k) return;
           const float e = ex2f(fmaf(Bits16<T>::value(bits_of((uint32_t)key)), kT, -c));
           const float nxt = fmaf((float)cnt, e, loc);
           key_b = key;
@@ -1161,10 +1205,106 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
       }
     }
     __syncthreads();
+    if (tid == 0 && k_k > 0 && sh.k_b < k_k) {
+      // no nucleus boundary above the top-k cut: the cut is the boundary, as a key just below it whose own
+      // elements (if any) carry no mass
+      sh.k_b = k_k - 1;
+      sh.r = 0;
+      sh.n_b = 0;
+      sh.e_b = 0.f;
+      sh.cum_before = 0.0;
+    }
+    __syncthreads();
     const int k_b = sh.k_b, r_rm = sh.r;
     const float e_b = sh.e_b;
-    if (tid == 0) sh.Z = sh.S - sh.cum_before - (double)r_rm * (double)e_b;
-    __syncthreads();  // the histogram is no longer needed after this point
+    if (tid == 0) {
+      sh.Z = sh.S - sh.cum_before - (double)r_rm * (double)e_b;
+      sh.T2 = 0.0;
+    }
+    __syncthreads();
+
+    // ---- 2b. lossy verification on sampled targets: entropy of the filtered distribution and the
+    // filtered probability of every child's token (lossy_tree_verify.py:66-72, 135-146) ----
+    if (a.method == SUBSPEC_VERIFY_LOSSY) {
+      // sum of e * y over the survivors (y = log2 of the unnormalised mass), from the histogram
+      float t2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int gi = desc ? 7 - i : i;
+        const uint4 q = row4[gi ^ (int)(rowi & 7u)];
+        if ((q.x | q.y | q.z | q.w) == 0u) continue;
+        const uint32_t wd[4] = {desc ? q.w : q.x, desc ? q.z : q.y, desc ? q.y : q.z, desc ? q.x : q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t cn[2] = {desc ? (wd[j] >> 16) : (wd[j] & 0xFFFFu), desc ? (wd[j] & 0xFFFFu) : (wd[j] >> 16)};
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int key = tid * 64 + i * 8 + j * 2 + h;
+            const float y = fmaf(Bits16<T>::value(bits_of((uint32_t)key)), kT, -c);
+            // above the boundary everything stays; at it, what the nucleus filter left of the run of equal
+            // values (nothing when the boundary is only the top-k cut, which has e_b = 0)
+            const float wgt = key > k_b ? (float)cn[h]
+                                        : ((key == k_b && e_b > 0.f) ? (float)max((int)cn[h] - r_rm, 0) : 0.f);
+            t2 += wgt > 0.f ? wgt * ex2f(y) * y : 0.f;
+          }
+        }
+      }
+      double t2d = (double)t2;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) t2d += shfl_xor_f64(t2d, off);
+      if (lane == 0 && t2d != 0.0) atomicAdd(&sh.T2, t2d);
+      __syncthreads();
+      const float Zf = (float)sh.Z;
+      if (tid == 0) {
+        const float denom = V > 1 ? logf((float)V) : 1.f;
+        a.node_entropy[nb + u] = kLn2 * (lg2f(Zf) - (float)sh.T2 / Zf) / denom;
+      }
+      // children of u
+      const int* coff = a.child_off + (size_t)b * (a.max_nodes + 1);
+      const int cb = coff[u], ce = coff[u + 1];
+      const int n_nodes = a.n_nodes[b];
+      for (int e = cb; e < ce; ++e) {  // the same trip count and decisions in every thread
+        const int cnode = a.child_idx[nb + e];
+        if (cnode < 0 || cnode >= n_nodes) {
+          if (tid == 0) flag(a.dev_status, SUBSPEC_DEV_BAD_CHILD);
+          continue;
+        }
+        const int tok = a.token_ids[nb + cnode];
+        float p = 0.f;
+        if (tok < 0 || tok >= V) {
+          if (tid == 0) flag(a.dev_status, SUBSPEC_DEV_BAD_TOKEN);
+        } else {
+          const uint32_t pat = reinterpret_cast<const unsigned short*>(rowp)[tok];
+          const int key = pat == Bits16<T>::kNegInf ? -1 : (int)key_of(pat);
+          if (key > k_b) {
+            p = ex2f(fmaf(Bits16<T>::value(pat), kT, -c)) / Zf;
+          } else if (key == k_b && e_b > 0.f && r_rm < sh.n_b) {
+            bool stays = r_rm == 0;
+            if (!stays) {
+              // part of the run of equal values stays: this token does if at least r_rm equal values
+              // precede it in the vocabulary
+              int before = 0;
+              for (int i0 = tid * 8; i0 < tok; i0 += kSThreads * 8) {
+                uint32_t bits[8];
+                load8<T>(rowp, i0, V, vec_ok, bits);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) before += (i0 + j < tok && bits[j] == pat) ? 1 : 0;
+              }
+#pragma unroll
+              for (int off = 16; off > 0; off >>= 1) before += __shfl_xor_sync(0xffffffffu, before, off);
+              if (tid == 0) sh.rank = 0;
+              __syncthreads();
+              if (lane == 0 && before) atomicAdd(&sh.rank, before);
+              __syncthreads();
+              stays = sh.rank >= r_rm;
+              __syncthreads();
+            }
+            p = stays ? e_b / Zf : 0.f;
+          }
+        }
+        if (tid == 0) a.node_child_prob[nb + cnode] = p;
+      }
+    }
 
     // ---- 3. second sweep: surviving mass and boundary ties per chunk, vocabulary order (L2 pass) ----
     // Survivors are the values above the boundary value, ties the values equal to it: float compares, except
@@ -1361,7 +1501,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
       }
       if (lane == 0) {
         a.node_target[nb + u] = min(cstar * kChunkElems + within, V - 1);
-        a.node_entropy[nb + u] = 0.f;
+        if (a.method != SUBSPEC_VERIFY_LOSSY) a.node_entropy[nb + u] = 0.f;
         a.node_rowmax[nb + u] = c;
         a.node_rowsum[nb + u] = (float)Z;
       }
@@ -1448,10 +1588,9 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
       !a.scratch)
     return SUBSPEC_EINVAL;
   if (a.do_sample) {
-    // sampled targets: 16-bit logits, exact (sample-and-match) walk
-    if (a.dtype == SUBSPEC_F32 || a.input_kind != SUBSPEC_IN_LOGITS || a.method != SUBSPEC_VERIFY_EXACT)
-      return SUBSPEC_EUNSUPPORTED;
-    if (!a.uniforms || !(a.temperature > 0.0) || !(a.top_p >= 0.0)) return SUBSPEC_EINVAL;
+    // sampled targets: 16-bit logits; exact (sample-and-match) walk or the lossy DP on the filtered distribution
+    if (a.dtype == SUBSPEC_F32 || a.input_kind != SUBSPEC_IN_LOGITS) return SUBSPEC_EUNSUPPORTED;
+    if (!a.uniforms || !(a.temperature > 0.0) || !(a.top_p >= 0.0) || a.top_k < 0) return SUBSPEC_EINVAL;
   }
   size_t need = 0;
   subspec_verify_scratch_bytes(a.batch, a.max_nodes, &need);

@@ -133,7 +133,7 @@ class VerifyWorkspace:
     # -- launch ---------------------------------------------------------------------
     def run(self, logits: torch.Tensor, *, input_kind: int, method: int, gate: int = _lib.GATE_PROB,
             threshold: float = 0.0, window: int = 1, eos: Optional[int] = None, do_sample: bool = False,
-            temperature: float = 1.0, top_p: float = 1.0) -> None:
+            temperature: float = 1.0, top_p: float = 1.0, top_k: int = 0) -> None:
         """Launch the fused kernel on the current stream.  `logits` is [batch, rows, vocab] on this device."""
         B, N = self.batch, self.max_nodes
         if logits.dim() != 3 or logits.shape[0] != B:
@@ -152,6 +152,7 @@ class VerifyWorkspace:
         for name in ("n_nodes", "n_rows", "token_ids", "child_off", "child_idx", "root"):
             setattr(a, name, self._in_ptr(name))
         a.do_sample = int(bool(do_sample))
+        a.top_k = int(top_k)
         a.temperature, a.top_p = float(temperature), float(top_p)
         a.uniforms = self.uniforms.data_ptr()
         a.method, a.gate = int(method), int(gate)
@@ -242,23 +243,33 @@ def _children_csr(children_lists: Sequence[Sequence[int]]):
     return off, np.asarray(idx, dtype=np.int32)
 
 
-def _sampling_params(logits_processor, do_sample: bool) -> Tuple[float, float]:
-    """Temperature and nucleus top-p out of a HF LogitsProcessorList (generators/base.py:42-64)."""
-    temperature, top_p = 1.0, 1.0
+def _sampling_params(logits_processor, do_sample: bool) -> Tuple[float, int, float]:
+    """Temperature, top-k and nucleus top-p out of a HF LogitsProcessorList, in the order the reference
+    builds it: temperature, top-k, top-p (generators/base.py:42-64).  top_k = 0 means off."""
+    temperature, top_k, top_p = 1.0, 0, 1.0
     if not do_sample or not logits_processor:
-        return temperature, top_p
+        return temperature, top_k, top_p
+    stage = 0
     for proc in logits_processor:
         kind = type(proc).__name__
-        if kind == "TemperatureLogitsWarper":
+        order = {"TemperatureLogitsWarper": 1, "TopKLogitsWarper": 2, "TopPLogitsWarper": 3}.get(kind)
+        if order is None:
+            raise ValueError(f"logits processor {kind} is not supported by the fused verifier "
+                             "(supported: TemperatureLogitsWarper, TopKLogitsWarper, TopPLogitsWarper)")
+        if order <= stage:
+            raise ValueError("logits processors must come in the order temperature, top-k, top-p, each at most once")
+        stage = order
+        if order == 1:
             temperature = float(proc.temperature)
-        elif kind == "TopPLogitsWarper":
+        elif order == 2:
+            top_k = int(proc.top_k)  # transformers has already folded min_tokens_to_keep into it
+            if float(getattr(proc, "filter_value", -float("inf"))) != -float("inf"):
+                raise ValueError("TopKLogitsWarper.filter_value other than -inf is not supported")
+        else:
             top_p = float(proc.top_p)
             if int(getattr(proc, "min_tokens_to_keep", 1)) != 1:
                 raise ValueError("TopPLogitsWarper.min_tokens_to_keep != 1 is not supported")
-        else:
-            raise ValueError(f"logits processor {kind} is not supported by the fused verifier "
-                             "(supported: TemperatureLogitsWarper, TopPLogitsWarper)")
-    return temperature, top_p
+    return temperature, top_k, top_p
 
 
 def _method_code(verify_method) -> int:
@@ -477,7 +488,7 @@ def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logit
         gate = _gate_code(vk.get("threshold_method", "prob") or "prob")
         threshold = float(vk.get("threshold", 0.0))
         window = max(0, int(vk.get("window_size", 1)))
-    temperature, top_p = _sampling_params(logits_processor, do_sample)
+    temperature, top_k, top_p = _sampling_params(logits_processor, do_sample)
     n_max = max(max(len(f[0]) for f in flats), 1)
     ws = workspace or get_workspace(B, n_max, device)
     ws.set_trees(flats)
@@ -488,7 +499,7 @@ def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logit
             u = torch.as_tensor(uniforms, dtype=torch.float32, device=device)
             ws.uniforms.view(B, ws.max_nodes)[:, :u.shape[1]].copy_(u)
     ws.run(logits, input_kind=_lib.IN_LOGITS, method=method, gate=gate, threshold=threshold, window=window,
-           eos=eos_token_id, do_sample=do_sample, temperature=temperature, top_p=top_p)
+           eos=eos_token_id, do_sample=do_sample, temperature=temperature, top_p=top_p, top_k=top_k)
     out = ws.fetch()
     results: List[VerifyOutput] = []
     for b in range(B):

@@ -91,3 +91,25 @@ def test_kv_oracle_page_table_is_consistent_with_identity():
     phys[:, perm] = pool
     ko.paged_reorder(phys, torch.tensor([0, 3, 4, 9]), 5, page_table=perm.tolist())
     assert torch.equal(phys[:, perm], ident)
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 0.9), (0.7, 50, 1.0), (1.3, 20, 0.8), (1.0, 1, 1.0),
+                                                      (0.5, 5000, 0.95)])
+def test_oracle_filters_match_transformers_warpers(temperature, top_k, top_p):
+    """`target_probs` against the processors the reference's `_sample_token` runs (generators/base.py:42-64,
+    109-139): transformers' temperature / top-k / top-p warpers followed by softmax, on tie-free rows."""
+    from transformers.generation.logits_process import (LogitsProcessorList, TemperatureLogitsWarper,
+                                                        TopKLogitsWarper, TopPLogitsWarper)
+    gen = torch.Generator().manual_seed(11)
+    logits = torch.randn(7, 3001, generator=gen) * 3.0
+    procs = LogitsProcessorList()
+    if temperature != 1.0:
+        procs.append(TemperatureLogitsWarper(temperature))
+    if top_k:
+        procs.append(TopKLogitsWarper(top_k=top_k))
+    if top_p < 1.0:
+        procs.append(TopPLogitsWarper(top_p=top_p))
+    want = torch.softmax(procs(None, logits.clone()), dim=-1)
+    got = vo.target_probs(logits, True, temperature, top_p, upcast=False, top_k=top_k)
+    assert torch.equal(want > 0, got > 0)
+    assert torch.allclose(want, got, rtol=1e-6, atol=0)

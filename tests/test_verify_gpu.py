@@ -225,6 +225,31 @@ def test_stochastic_ties_masks_and_zeros(cuda_lib):
                     assert int(targets[b, u]) == want[u], (top_p, b, u, margins[u])
                     checked += 1
     assert checked >= B * nodes * 2
+    # the same rows through the lossy verifier: a child whose token sits in the run of equal values that the
+    # nucleus boundary cuts has probability e/Z or 0 according to its place in that run
+    cut_children = 0
+    for top_p in (0.999, 0.8, 0.5):
+        procs = LogitsProcessorList([TopPLogitsWarper(top_p=top_p)])
+        verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
+                            eos_token_id=None, logits_processor=procs, do_sample=True, verify_method="lossy",
+                            verify_kwargs={"threshold_method": "prob", "threshold": 0.01, "window_size": 0},
+                            uniforms=uniforms)
+        cprob = get_workspace(B, nodes, torch.device("cuda", 0)).fetch()["node_child_prob"]
+        for b, st in enumerate(sts):
+            probs = vo.target_probs(logits[b], True, 1.0, top_p, upcast=True)
+            margins = vo.sampling_margins(logits[b], 1.0, top_p, uniforms[b].tolist())
+            ch = st.children()
+            for u in range(st.n):
+                if margins[u][0] <= 1e-3:
+                    continue
+                row = logits[b, u].float()
+                kept = row[probs[u] > 0]
+                for c in ch[u]:
+                    tok = int(st.token_ids[c])
+                    want, got = float(probs[u, tok]), float(cprob[b, c])
+                    assert (want == 0.0) == (got == 0.0) and abs(got - want) <= 2e-4 * want, (top_p, b, u, c, got, want)
+                    cut_children += int(float(row[tok]) == float(kept.min()) and bool((row == row[tok]).sum() > (kept == kept.min()).sum()))
+    assert cut_children > 0  # the partial-run path was exercised
 
 
 def test_stochastic_counter_overflow_is_reported(cuda_lib):
@@ -244,3 +269,84 @@ def test_stochastic_counter_overflow_is_reported(cuda_lib):
     logits[0, 1, 65535:][logits[0, 1, 65535:] == 0.75] = 0.5
     verify_tree_batched(trees=[_tree_of(st)], root_inds=[0], logits=logits.cuda(), eos_token_id=None,
                         logits_processor=None, do_sample=True, verify_method="stochastic", uniforms=torch.rand(1, nodes))
+
+
+@pytest.mark.parametrize("vocab,nodes,dtype,temperature,top_k,top_p", [
+    (32000, 20, torch.float16, 0.8, 50, 1.0),      # top-k alone
+    (152064, 12, torch.bfloat16, 1.0, 40, 0.9),    # the reference's usual trio: temperature, top-k, top-p
+    (4099, 16, torch.bfloat16, 1.2, 1, 1.0),       # k = 1: greedy by another name
+    (5000, 16, torch.bfloat16, 1.0, 100000, 0.7),  # k beyond the vocabulary: no cut
+])
+def test_stochastic_top_k(cuda_lib, vocab, nodes, dtype, temperature, top_k, top_p):
+    from transformers.generation.logits_process import (LogitsProcessorList, TemperatureLogitsWarper,
+                                                        TopKLogitsWarper, TopPLogitsWarper)
+    from subspec_b200.verify import get_workspace
+    B = 2
+    sts, logits, uniforms = _sampled_case(900 + nodes, B, nodes, vocab, dtype, 2.5)
+    procs = LogitsProcessorList()
+    if temperature != 1.0:
+        procs.append(TemperatureLogitsWarper(temperature))
+    procs.append(TopKLogitsWarper(top_k=top_k))
+    if top_p < 1.0:
+        procs.append(TopPLogitsWarper(top_p=top_p))
+    verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(), eos_token_id=None,
+                        logits_processor=procs, do_sample=True, verify_method="stochastic", uniforms=uniforms)
+    targets = get_workspace(B, nodes, torch.device("cuda", 0)).fetch()["node_target"]
+    checked = 0
+    for b, st in enumerate(sts):
+        probs = vo.target_probs(logits[b], True, temperature, top_p, upcast=True, top_k=min(top_k, vocab))
+        want = vo.target_tokens(probs, True, uniforms[b].tolist())
+        margins = vo.sampling_margins(logits[b], temperature, top_p, uniforms[b].tolist(), top_k=min(top_k, vocab))
+        for u in range(st.n):
+            assert float(probs[u, int(targets[b, u])]) > 0.0  # never a token the filters removed
+            if margins[u][0] > 1e-3 and margins[u][1] > 1e-6:
+                assert int(targets[b, u]) == want[u], (b, u, margins[u])
+                checked += 1
+    assert checked >= B * nodes // 2
+    with pytest.raises(ValueError):  # the reference's order is temperature, top-k, top-p
+        verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
+                            eos_token_id=None, do_sample=True, verify_method="stochastic", uniforms=uniforms,
+                            logits_processor=LogitsProcessorList([TopPLogitsWarper(top_p=0.9),
+                                                                  TopKLogitsWarper(top_k=5)]))
+
+
+@pytest.mark.parametrize("gate,threshold", [("entropy", 0.25), ("prob", 0.02)])
+@pytest.mark.parametrize("dtype,top_k,top_p", [(torch.bfloat16, 0, 0.9), (torch.float16, 64, 0.95),
+                                               (torch.bfloat16, 0, 1.0)])
+def test_lossy_on_sampled_targets(cuda_lib, dtype, top_k, top_p, gate, threshold):
+    """verify_method='lossy' with do_sample: sampled targets, and the gates (entropy of the filtered
+    distribution, filtered probability of the child token) as lossy_tree_verify.py:66-77, 135-146 computes them
+    from the processed probabilities."""
+    from transformers.generation.logits_process import (LogitsProcessorList, TemperatureLogitsWarper,
+                                                        TopKLogitsWarper, TopPLogitsWarper)
+    from subspec_b200.verify import get_workspace
+    B, nodes, vocab, temperature = 3, 24, 32000, 0.9
+    sts, logits, uniforms = _sampled_case(1300 + top_k, B, nodes, vocab, dtype, 2.0)
+    procs = LogitsProcessorList([TemperatureLogitsWarper(temperature)])
+    if top_k:
+        procs.append(TopKLogitsWarper(top_k=top_k))
+    if top_p < 1.0:
+        procs.append(TopPLogitsWarper(top_p=top_p))
+    kw = {"threshold_method": gate, "threshold": threshold, "window_size": 1}
+    res = verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
+                              eos_token_id=None, logits_processor=procs, do_sample=True, verify_method="lossy",
+                              verify_kwargs=kw, uniforms=uniforms)
+    out = get_workspace(B, nodes, torch.device("cuda", 0)).fetch()
+    for b, st in enumerate(sts):
+        probs = vo.target_probs(logits[b], True, temperature, top_p, upcast=True, top_k=top_k)
+        ent = torch.tensor(vo.normalised_entropy(probs))
+        assert torch.allclose(torch.from_numpy(out["node_entropy"][b, :st.n].copy()), ent, rtol=2e-4, atol=2e-6)
+        ch = st.children()
+        for u in range(st.n):
+            for c in ch[u]:
+                want = float(probs[u, int(st.token_ids[c])])
+                got = float(out["node_child_prob"][b, c])
+                assert (want == 0.0) == (got == 0.0) and abs(got - want) <= 2e-4 * want + 1e-9, (b, u, c, got, want)
+        # the DP and the walk are integer work on top of these: replay them on the kernel's own targets and gates
+        r = vo.lossy_verify(probs=probs, token_ids=st.token_ids.tolist(), children=ch, root=0, eos=None,
+                            threshold=threshold, window=1, use_entropy=gate == "entropy",
+                            target=out["node_target"][b, :st.n].tolist())
+        if r.min_gate_margin > 1e-4:  # no gate decision within rounding of its threshold
+            assert res[b].sampled_tokens.squeeze(0).tolist() == r.tokens
+            assert res[b].hidden_indices.tolist() == r.hidden
+            assert (res[b].total_len, res[b].accept_len) == (r.total_len, r.accept_len)
