@@ -110,7 +110,7 @@ def flats_of(trees):
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
 
-    def __init__(self, device_index: int, period_s: float = 0.02):
+    def __init__(self, device_index: int, period_s: float = 0.002):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._thread = None
