@@ -71,10 +71,27 @@ struct GemmArgs {
 };
 
 
+// try_wait with a suspend-time hint: the warp sleeps in hardware (up to the hint) instead of coming back
+// to poll, and the polls of the waiting roles stop competing with the dequantisation for issue slots.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+constexpr uint32_t kWaitHintNs = 2000;
+constexpr uint32_t kWaitLimit = 1u << 20;  // polls; with the hint at most ~2 s before a wait gives up
+
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  if (mbar_try_wait(bar, parity)) return true;  // the common case: already complete
+  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    if (mbar_try_wait_hint(bar, parity, kWaitHintNs)) return true;
+    if ((it & 255u) == 255u && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;
