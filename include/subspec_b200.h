@@ -48,6 +48,10 @@ typedef void* subspec_stream_t; /* a cudaStream_t; NULL = legacy default stream 
 
 #define SUBSPEC_VERIFY_EXACT 0 /* verify_method="exact" */
 #define SUBSPEC_VERIFY_LOSSY 1 /* verify_method="lossy" */
+/* Both of the above from ONE pass over the logits (a step that verifies greedily and then lossily reads the
+ * same rows twice in the reference): the lossy results go to out_*, the exact ones to out2_*.  The two
+ * walks must see the same flattened tree, i.e. every node decoded (n_rows == n_nodes). */
+#define SUBSPEC_VERIFY_EXACT_AND_LOSSY 2
 
 #define SUBSPEC_GATE_PROB 0    /* threshold_method="prob"    */
 #define SUBSPEC_GATE_ENTROPY 1 /* threshold_method="entropy" */
@@ -162,6 +166,10 @@ typedef struct subspec_verify_args {
   uint32_t* dev_status; /* one word, OR-ed with SUBSPEC_DEV_* bits; caller zeroes it */
   void* scratch;
   size_t scratch_bytes;
+  /* results of the exact walk under SUBSPEC_VERIFY_EXACT_AND_LOSSY (same shapes as out_*); else unused */
+  int64_t* out2_tokens;
+  int64_t* out2_hidden;
+  int32_t* out2_meta;
 } subspec_verify_args;
 
 SUBSPEC_API int subspec_verify_scratch_bytes(int32_t batch, int32_t max_nodes, size_t* bytes);

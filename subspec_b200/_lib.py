@@ -14,7 +14,7 @@ OK, EINVAL, EUNSUPPORTED, ECUDA, ESCRATCH, ETOOLARGE = 0, -1, -2, -3, -4, -5
 STATIC_SCRATCH_MAX_ROWS = 4096
 F32, BF16, F16 = 0, 1, 2
 IN_LOGITS, IN_PROBS = 0, 1
-VERIFY_EXACT, VERIFY_LOSSY = 0, 1
+VERIFY_EXACT, VERIFY_LOSSY, VERIFY_EXACT_AND_LOSSY = 0, 1, 2
 GATE_PROB, GATE_ENTROPY = 0, 1
 DEV_BAD_TOKEN, DEV_BAD_CHILD, DEV_BAD_ROOT, DEV_BAD_PAGE, DEV_BAD_INDEX, DEV_TIMEOUT, DEV_HIST_OVERFLOW = 1, 2, 4, 8, 16, 32, 64
 
@@ -53,6 +53,7 @@ class VerifyArgs(C.Structure):
         ("node_target", _vp), ("node_entropy", _vp), ("node_child_prob", _vp), ("node_rowmax", _vp),
         ("node_rowsum", _vp), ("node_exact_after", _vp), ("node_best_len", _vp), ("node_best_next", _vp),
         ("dev_status", _vp), ("scratch", _vp), ("scratch_bytes", C.c_size_t),
+        ("out2_tokens", _vp), ("out2_hidden", _vp), ("out2_meta", _vp),
     ]
 
 

@@ -384,7 +384,7 @@ __device__ void run_walk(const KArgs& ka, int b, unsigned char* smem_raw) {
   const int n_rows = a.n_rows[b];
   WalkSmem w = carve_walk(smem_raw, N);
   const size_t nb = (size_t)b * N;
-  const bool lossy = a.method == SUBSPEC_VERIFY_LOSSY;
+  const bool lossy = a.method != SUBSPEC_VERIFY_EXACT;  // the lossy walk runs (alone, or after the exact one)
 
   for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) {
     w.tok[i] = a.token_ids[nb + i];
@@ -414,8 +414,6 @@ __device__ void run_walk(const KArgs& ka, int b, unsigned char* smem_raw) {
   __syncthreads();
 
   if (threadIdx.x == 0) {
-    int64_t* out_tok = a.out_tokens + (size_t)b * a.max_out;
-    int64_t* out_hid = a.out_hidden + (size_t)b * a.max_out;
     const int max_out = a.max_out;
     const int64_t eos = a.eos;
     int root = a.root[b];
@@ -423,8 +421,16 @@ __device__ void run_walk(const KArgs& ka, int b, unsigned char* smem_raw) {
       flag(a.dev_status, SUBSPEC_DEV_BAD_ROOT);
       root = 0;
     }
+    // Pass 0: the exact walk; pass 1: the lossy DP and walk.  SUBSPEC_VERIFY_EXACT_AND_LOSSY runs both on
+    // the same per-node targets (one pass over the logits): the exact results then go to the out2_* arrays.
+    for (int pass = 0; pass < 2; ++pass) {
+    const bool walk_lossy = pass == 1;
+    if (walk_lossy ? a.method == SUBSPEC_VERIFY_EXACT : a.method == SUBSPEC_VERIFY_LOSSY) continue;
+    const bool second = a.method == SUBSPEC_VERIFY_EXACT_AND_LOSSY && !walk_lossy;
+    int64_t* out_tok = (second ? a.out2_tokens : a.out_tokens) + (size_t)b * a.max_out;
+    int64_t* out_hid = (second ? a.out2_hidden : a.out_hidden) + (size_t)b * a.max_out;
     int L = 0, acc = 0, total = 0;
-    if (!lossy) {
+    if (!walk_lossy) {
       // tree_verify.py:61-104
       int cur = root;
       int bonus = -1;
@@ -548,11 +554,12 @@ __device__ void run_walk(const KArgs& ka, int b, unsigned char* smem_raw) {
       }
       total = L;
     }
-    int* meta = a.out_meta + (size_t)b * 4;
+    int* meta = (second ? a.out2_meta : a.out_meta) + (size_t)b * 4;
     meta[0] = L < max_out ? L : max_out;
     meta[1] = acc;
     meta[2] = total;
     meta[3] = L > max_out ? 1 : 0;
+    }
   }
   __syncthreads();
   if (lossy) {
@@ -1225,7 +1232,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
 
     // ---- 2b. lossy verification on sampled targets: entropy of the filtered distribution and the
     // filtered probability of every child's token (lossy_tree_verify.py:66-72, 135-146) ----
-    if (a.method == SUBSPEC_VERIFY_LOSSY) {
+    if (a.method != SUBSPEC_VERIFY_EXACT) {
       // sum of e * y over the survivors (y = log2 of the unnormalised mass), from the histogram
       float t2 = 0.f;
 #pragma unroll
@@ -1501,7 +1508,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
       }
       if (lane == 0) {
         a.node_target[nb + u] = min(cstar * kChunkElems + within, V - 1);
-        if (a.method != SUBSPEC_VERIFY_LOSSY) a.node_entropy[nb + u] = 0.f;
+        if (a.method == SUBSPEC_VERIFY_EXACT) a.node_entropy[nb + u] = 0.f;
         a.node_rowmax[nb + u] = c;
         a.node_rowsum[nb + u] = (float)Z;
       }
@@ -1521,7 +1528,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
 
 template <typename T>
 cudaError_t launch_rows(const KArgs& ka, int grid, size_t smem, cudaStream_t st) {
-  const bool soft = ka.a.method == SUBSPEC_VERIFY_LOSSY;
+  const bool soft = ka.a.method != SUBSPEC_VERIFY_EXACT;
   const bool probs = ka.a.input_kind == SUBSPEC_IN_PROBS;
 #define SUBSPEC_LAUNCH(KIND, SOFT)                                                                        \
   do {                                                                                                    \
@@ -1579,7 +1586,11 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
   if (a.max_nodes > kMaxNodes || a.vocab > (1 << 20)) return SUBSPEC_EUNSUPPORTED;
   if (a.dtype != SUBSPEC_F32 && a.dtype != SUBSPEC_BF16 && a.dtype != SUBSPEC_F16) return SUBSPEC_EINVAL;
   if (a.input_kind != SUBSPEC_IN_LOGITS && a.input_kind != SUBSPEC_IN_PROBS) return SUBSPEC_EINVAL;
-  if (a.method != SUBSPEC_VERIFY_EXACT && a.method != SUBSPEC_VERIFY_LOSSY) return SUBSPEC_EINVAL;
+  if (a.method != SUBSPEC_VERIFY_EXACT && a.method != SUBSPEC_VERIFY_LOSSY &&
+      a.method != SUBSPEC_VERIFY_EXACT_AND_LOSSY)
+    return SUBSPEC_EINVAL;
+  if (a.method == SUBSPEC_VERIFY_EXACT_AND_LOSSY && (!a.out2_tokens || !a.out2_hidden || !a.out2_meta))
+    return SUBSPEC_EINVAL;
   if (a.gate != SUBSPEC_GATE_PROB && a.gate != SUBSPEC_GATE_ENTROPY) return SUBSPEC_EINVAL;
   if (a.batch == 0) return SUBSPEC_OK;
   if (!a.logits || !a.n_nodes || !a.n_rows || !a.token_ids || !a.child_off || !a.child_idx || !a.root ||

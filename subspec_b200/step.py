@@ -60,7 +60,7 @@ class SpeculativeStepBatch:
         method = _method_code(verify_method)
         vk = dict(verify_kwargs or {})
         gate, threshold, window = _lib.GATE_PROB, 0.0, 1
-        if method == _lib.VERIFY_LOSSY:
+        if method != _lib.VERIFY_EXACT:
             gate = _gate_code(vk.get("threshold_method", "prob") or "prob")
             threshold = float(vk.get("threshold", 0.0))
             window = max(0, int(vk.get("window_size", 1)))

@@ -73,7 +73,10 @@ class VerifyWorkspace:
                               ("node_entropy", B * N, np.float32), ("node_child_prob", B * N, np.float32),
                               ("node_rowmax", B * N, np.float32), ("node_rowsum", B * N, np.float32),
                               ("node_exact_after", B * N, np.int32), ("node_best_len", B * N, np.int32),
-                              ("node_best_next", B * N, np.int32), ("dev_status", 1, np.uint32)):
+                              ("node_best_next", B * N, np.int32), ("dev_status", 1, np.uint32),
+                              # results of the exact walk when one launch verifies exactly AND lossily
+                              ("out2_tokens", B * self.max_out, np.int64), ("out2_hidden", B * self.max_out, np.int64),
+                              ("out2_meta", B * 4, np.int32)):
             dt = np.dtype(dt)
             self._out_off[name] = (cur, cnt, dt)
             cur += _align(cnt * dt.itemsize, 16)
@@ -161,7 +164,7 @@ class VerifyWorkspace:
         a.max_out = self.max_out
         for name in ("out_tokens", "out_hidden", "out_meta", "node_target", "node_entropy", "node_child_prob",
                      "node_rowmax", "node_rowsum", "node_exact_after", "node_best_len", "node_best_next",
-                     "dev_status"):
+                     "dev_status", "out2_tokens", "out2_hidden", "out2_meta"):
             setattr(a, name, self._out_ptr(name))
         a.scratch, a.scratch_bytes = self._scratch_ptr, self._scratch_bytes
         self._rows = int(logits.shape[1])
@@ -182,9 +185,9 @@ class VerifyWorkspace:
         out: Dict[str, np.ndarray] = {}
         for name, (off, cnt, dt) in self._out_off.items():
             arr = raw[off:off + cnt * dt.itemsize].view(dt)
-            if name in ("out_tokens", "out_hidden"):
+            if name in ("out_tokens", "out_hidden", "out2_tokens", "out2_hidden"):
                 arr = arr.reshape(B, self.max_out)
-            elif name == "out_meta":
+            elif name in ("out_meta", "out2_meta"):
                 arr = arr.reshape(B, 4)
             elif name != "dev_status":
                 arr = arr.reshape(B, N)
@@ -278,6 +281,8 @@ def _method_code(verify_method) -> int:
         return _lib.VERIFY_EXACT
     if m == "lossy":
         return _lib.VERIFY_LOSSY
+    if m in ("exact+lossy", "greedy+lossy"):
+        return _lib.VERIFY_EXACT_AND_LOSSY
     raise ValueError(f"Unsupported verify_method: {verify_method!r} (supported: 'exact', 'lossy')")
 
 
@@ -449,6 +454,13 @@ def lossy_bottom_up_verify(*, probs: torch.Tensor, token_ids: torch.Tensor, pare
 
 def _prepare_tree(tree, root_ind: int, skip_nodes: int, rows: int, method: int):
     skip = int(skip_nodes)
+    if method == _lib.VERIFY_EXACT_AND_LOSSY:
+        # one flattening has to serve both walks: that is the case when every node is decoded
+        tok, off, idx = flatten_tree(tree, skip, restrict=False)
+        root = int(root_ind) - skip
+        if len(tok) > rows or not 0 <= root < len(tok):
+            raise ValueError("verify_method='exact+lossy' needs logits for every tree node and a root inside them")
+        return tok, off, idx, len(tok), root
     if method == _lib.VERIFY_LOSSY:
         tok, off, idx = flatten_tree(tree, skip, limit=rows, restrict=True)
         n_rows = len(tok)
@@ -471,7 +483,9 @@ def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logit
     """Verify `len(trees)` independent draft trees against `logits` [batch, rows, vocab] in one launch.
 
     Per sequence the result equals the reference's `verify_tree` on
-    `logits[b:b+1]` (tree_verify.py:7-163).
+    `logits[b:b+1]` (tree_verify.py:7-163).  `verify_method="exact+lossy"` returns, per sequence, the pair
+    (exact result, lossy result) of the two calls a step that verifies greedily and then lossily makes, from
+    one pass over the logits; it needs logits for every tree node.
     """
     method = _method_code(verify_method)
     vk = dict(verify_kwargs or {})
@@ -484,7 +498,7 @@ def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logit
     skips = [int(skip_nodes)] * B if isinstance(skip_nodes, int) else [int(s) for s in skip_nodes]
     flats = [_prepare_tree(t, r, s, rows, method) for t, r, s in zip(trees, root_inds, skips)]
     gate, threshold, window = _lib.GATE_PROB, 0.0, 1
-    if method == _lib.VERIFY_LOSSY:
+    if method != _lib.VERIFY_EXACT:
         gate = _gate_code(vk.get("threshold_method", "prob") or "prob")
         threshold = float(vk.get("threshold", 0.0))
         window = max(0, int(vk.get("window_size", 1)))
@@ -501,21 +515,28 @@ def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logit
     ws.run(logits, input_kind=_lib.IN_LOGITS, method=method, gate=gate, threshold=threshold, window=window,
            eos=eos_token_id, do_sample=do_sample, temperature=temperature, top_p=top_p, top_k=top_k)
     out = ws.fetch()
-    results: List[VerifyOutput] = []
+    results: List[Any] = []
     for b in range(B):
         L, acc, total = (int(x) for x in out["out_meta"][b, :3])
         hidden_local = out["out_hidden"][b, :L]
-        if log_diagnostics and method == _lib.VERIFY_LOSSY:
+        if log_diagnostics and method != _lib.VERIFY_EXACT:
             tok, off, idx = flats[b][:3]
             log_lossy_diagnostics(token_ids=tok, child_off=off, child_idx=idx, target=out["node_target"][b],
                                   entropy=out["node_entropy"][b], child_prob=out["node_child_prob"][b],
                                   exact_after=out["node_exact_after"][b], best_next=out["node_best_next"][b],
                                   hidden=hidden_local, n_out=L, accept_len=acc,
                                   use_entropy=gate == _lib.GATE_ENTROPY, threshold=threshold, window=window)
-        results.append(VerifyOutput(
+        res = VerifyOutput(
             sampled_tokens=torch.from_numpy(out["out_tokens"][b, :L].copy()).unsqueeze(0),
             hidden_indices=torch.from_numpy(hidden_local + skips[b]),
-            total_len=total, accept_len=acc))
+            total_len=total, accept_len=acc)
+        if method == _lib.VERIFY_EXACT_AND_LOSSY:  # (exact result, lossy result)
+            L2, acc2, total2 = (int(x) for x in out["out2_meta"][b, :3])
+            res = (VerifyOutput(
+                sampled_tokens=torch.from_numpy(out["out2_tokens"][b, :L2].copy()).unsqueeze(0),
+                hidden_indices=torch.from_numpy(out["out2_hidden"][b, :L2] + skips[b]),
+                total_len=total2, accept_len=acc2), res)
+        results.append(res)
     return results
 
 

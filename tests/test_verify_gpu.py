@@ -350,3 +350,32 @@ def test_lossy_on_sampled_targets(cuda_lib, dtype, top_k, top_p, gate, threshold
             assert res[b].sampled_tokens.squeeze(0).tolist() == r.tokens
             assert res[b].hidden_indices.tolist() == r.hidden
             assert (res[b].total_len, res[b].accept_len) == (r.total_len, r.accept_len)
+
+
+@pytest.mark.parametrize("dtype,vocab", [(torch.bfloat16, 152064), (torch.float32, 4099), (torch.float16, 32000)])
+@pytest.mark.parametrize("gate,threshold,window", [("entropy", 0.3, 6), ("prob", 0.05, 1), ("entropy", 0.9, 0)])
+def test_exact_and_lossy_in_one_pass(cuda_lib, dtype, vocab, gate, threshold, window):
+    """verify_method='exact+lossy' (one pass over the logits) returns exactly what the two separate calls return."""
+    B, nodes = 5, 48
+    gen = torch.Generator().manual_seed(4242 + vocab)
+    sts = [synthetic.random_tree(nodes, 8, 4, vocab, gen) for _ in range(B)]
+    logits = torch.stack([synthetic.verify_logits(st, vocab, gen, dtype=dtype, sigma=3.0, boost=18.0) for st in sts])
+    kw = {"threshold_method": gate, "threshold": threshold, "window_size": window}
+    trees = [_tree_of(st) for st in sts]
+    common = dict(trees=trees, root_inds=[0] * B, logits=logits.cuda(), eos_token_id=int(sts[0].token_ids[3]),
+                  logits_processor=None, do_sample=False)
+    exact = verify_tree_batched(verify_method="exact", **common)
+    lossy = verify_tree_batched(verify_method="lossy", verify_kwargs=kw, **common)
+    both = verify_tree_batched(verify_method="exact+lossy", verify_kwargs=kw, **common)
+    accepted = 0
+    for b in range(B):
+        for got, want in ((both[b][0], exact[b]), (both[b][1], lossy[b])):
+            assert got.sampled_tokens.tolist() == want.sampled_tokens.tolist()
+            assert got.hidden_indices.tolist() == want.hidden_indices.tolist()
+            assert (got.total_len, got.accept_len) == (want.total_len, want.accept_len)
+        accepted += lossy[b].accept_len
+    assert accepted > 0
+    # a partially decoded tree cannot share one flattening between the two walks
+    with pytest.raises(ValueError):
+        verify_tree_batched(trees=trees, root_inds=[0] * B, logits=logits[:, :nodes - 3].cuda(), eos_token_id=None,
+                            logits_processor=None, do_sample=False, verify_method="exact+lossy", verify_kwargs=kw)
