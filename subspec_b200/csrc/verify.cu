@@ -28,7 +28,7 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kUnroll = 4;
 constexpr int kStageVecs = kThreads * kUnroll;  // 16-byte vectors per TMA stage: one group per thread
 constexpr int kStageBytes = kStageVecs * 16;    // 16 KB
-constexpr int kStages = 4;                      // shared-memory ring depth
+constexpr int kStages = 3;                      // shared-memory ring depth
 constexpr int kMaxSplits = 32;
 constexpr int kMaxNodes = 1024;
 
@@ -589,7 +589,7 @@ __device__ __forceinline__ void block_reduce(RowStat st, RowStat* s_warp, RowSta
 
 // ---- the streaming kernel --------------------------------------------------------
 template <typename T, int KIND, bool SOFT>
-__global__ void __launch_bounds__(kThreads, 3) verify_rows_kernel(const KArgs ka) {
+__global__ void __launch_bounds__(kThreads, 4) verify_rows_kernel(const KArgs ka) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ RowStat s_warp[kWarps];
   __shared__ float s_max[kWarps];
@@ -897,12 +897,6 @@ __device__ __forceinline__ double shfl_xor_f64(double v, int mask) {
   int lo = __double2loint(v), hi = __double2hiint(v);
   lo = __shfl_xor_sync(0xffffffffu, lo, mask);
   hi = __shfl_xor_sync(0xffffffffu, hi, mask);
-  return __hiloint2double(hi, lo);
-}
-__device__ __forceinline__ double shfl_f64(double v, int src) {
-  int lo = __double2loint(v), hi = __double2hiint(v);
-  lo = __shfl_sync(0xffffffffu, lo, src);
-  hi = __shfl_sync(0xffffffffu, hi, src);
   return __hiloint2double(hi, lo);
 }
 // inclusive scan over the warp
