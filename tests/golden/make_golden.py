@@ -310,7 +310,7 @@ def gen_expand(ref, out_dir: Path):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the unmodified reference repository")
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
     ref = import_reference(args.reference)
