@@ -28,9 +28,9 @@ class SpeculativeStepBatch:
     def __init__(self, batch: int, max_nodes: int, device, *, kv_layers: int = 0, kv_heads: int = 4,
                  head_dim: int = 128, page_len: int = 16, pages_per_seq: int = 0,
                  kv_dtype: torch.dtype = torch.bfloat16, page_table: Optional[torch.Tensor] = None):
-        self.device = torch.device(device)
         self.batch, self.max_nodes = int(batch), int(max_nodes)
-        self.ws = VerifyWorkspace(batch, max_nodes, self.device)
+        self.ws = VerifyWorkspace(batch, max_nodes, torch.device(device))
+        self.device = self.ws.device
         self.pool: Optional[torch.Tensor] = None
         self.page_table: Optional[torch.Tensor] = None
         self.kv_offset = torch.zeros(batch, dtype=torch.int32, device=self.device)

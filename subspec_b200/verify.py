@@ -53,7 +53,10 @@ class VerifyWorkspace:
     def __init__(self, batch: int, max_nodes: int, device: torch.device):
         if not 1 <= max_nodes <= 1024:
             raise ValueError("max_nodes must be in [1, 1024]")
-        self.batch, self.max_nodes, self.device = int(batch), int(max_nodes), torch.device(device)
+        device = torch.device(device)
+        if device.type == "cuda" and device.index is None:  # "cuda" means the current device
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.batch, self.max_nodes, self.device = int(batch), int(max_nodes), device
         B, N = self.batch, self.max_nodes
         self.max_out = N + 1
         # ---- int32 inputs, one block ----
