@@ -53,6 +53,8 @@ def parse_args():
                     help="verify greedily and lossily in two launches (two passes over the logits) instead of one")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the side measurements of the other kernels")
+    ap.add_argument("--extras-only", choices=["expand", "stochastic", "gemm"], default=None,
+                    help="run one of the side measurements alone on GPU 0 and print it as one JSON line")
     ap.add_argument("--cpu-sample", type=int, default=0, help="sequences per CPU-baseline sample (0 = auto)")
     return ap.parse_args()
 
@@ -411,6 +413,24 @@ def extra_gemm(device, peak_gbs, peak_tf):
     return out
 
 
+def run_extras_only(args):
+    from subspec_b200 import build as _build
+
+    _build.build()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    pk = ROOT / "MEASURED_PEAKS.json"
+    peaks = json.loads(pk.read_text()) if pk.exists() else {}
+    peak_gbs, peak_tf = float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0))
+    if args.extras_only == "expand":
+        out = extra_expand(device, peak_gbs)
+    elif args.extras_only == "stochastic":
+        out = extra_stochastic(device, peak_gbs)
+    else:
+        out = extra_gemm(device, peak_gbs, peak_tf)
+    print(json.dumps(out), flush=True)
+
+
 # --------------------------------------------------------------------------------------
 # native arm
 # --------------------------------------------------------------------------------------
@@ -418,6 +438,9 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.extras_only:
+        run_extras_only(args)
         return
 
     import torch.distributed as dist
