@@ -52,3 +52,33 @@ def test_argument_validation(cuda_lib):
     assert cuda_lib.subspec_verify_batched(C.byref(a), None) == _lib.EINVAL
     a.max_nodes = 4096
     assert cuda_lib.subspec_verify_batched(C.byref(a), None) == _lib.EUNSUPPORTED
+
+
+def test_header_is_plain_c_and_matches_the_ctypes_mirror(tmp_path):
+    """The header compiles as C99 on its own, and every argument struct has the size and field offsets the
+    ctypes mirror in subspec_b200/_lib.py assumes (a host in another language binds against the same layout)."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    assert gcc, "gcc is part of the toolchain"
+    structs = {"subspec_verify_args": _lib.VerifyArgs, "subspec_kv_paged_args": _lib.KvPagedArgs,
+               "subspec_kv_hf_args": _lib.KvHfArgs, "subspec_expand_args": _lib.ExpandArgs,
+               "subspec_tree_finalize_args": _lib.TreeFinalizeArgs, "subspec_w4a16_args": _lib.W4A16Args}
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "subspec_b200.h"', 'int main(void) {']
+    for cname, mirror in structs.items():
+        lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')
+        for field, _ in mirror._fields_:
+            lines.append(f'  printf("{cname}.{field} %zu\\n", offsetof({cname}, {field}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines) + "\n")
+    exe = tmp_path / "layout"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I", str(HEADER.parent), str(src),
+                    "-o", str(exe)], check=True)
+    got = dict(line.rsplit(" ", 1) for line in subprocess.run([str(exe)], check=True, capture_output=True,
+                                                             text=True).stdout.splitlines())
+    for cname, mirror in structs.items():
+        assert int(got[cname]) == C.sizeof(mirror), cname
+        for field, _ in mirror._fields_:
+            assert int(got[f"{cname}.{field}"]) == getattr(mirror, field).offset, (cname, field)
