@@ -650,7 +650,7 @@ def main():
             torch.cuda.empty_cache()
             line["other_kernels"] = extras(device, peak_gbs, float(peaks.get("bf16_tflops", 1590.0)))
         if world == 1 and not args.no_cpu_baseline:
-            sample = args.cpu_sample or 8
+            sample = args.cpu_sample or 64  # one wave: about ten seconds of CPU work over the three passes
             v, desc = cpu_baseline(sample, 3, args.variant)
             line["cpu_baseline"] = {"value": v, "unit": "steps/s", "cores": os.cpu_count(), "kind": "port",
                                     "sample": desc, "gpu_results_checked_sequences": spot_check(spot)}
