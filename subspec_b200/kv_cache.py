@@ -504,3 +504,38 @@ def getKvCacheBatchPosition(request_kv_caches: List[RequestKvCache], mode: str, 
     return KvCacheBatchPosition(seq_indptr=i32(seq_indptr), kv_page_indptr=i32(page_indptr),
                                 kv_page_indices=i32(page_indices), kv_last_page_len=i32(last_len),
                                 batch_indices=batch_indices, positions=positions)
+
+
+class FlashInferCache:
+    """The reference's holder of the paged pool (flashinfer/cache_manager.py:419-466): same constructor
+    (`config`, `max_tokens`, `PAGE_LEN`), same attributes (`config`, `max_cache_len`, `kvCachePool`), same
+    memory check (`CUDA_MEMORY_FRACTION`), fp16 pool on the current device.
+
+    The reference sizes the pool at ONE page whatever `max_tokens` says (its line 451); `max_pages` is an
+    addition that lets a caller get a pool that holds something, and defaults to the reference's value.
+    """
+
+    def __init__(self, config, max_tokens: Optional[int] = None, PAGE_LEN: int = 16,
+                 max_pages: Optional[int] = None) -> None:
+        import os
+
+        device = torch.device("cuda", torch.cuda.current_device())
+        dtype_size = torch.tensor([], dtype=torch.float16).element_size()
+        self.config = config
+        head_dim = getattr(config, "head_dim", config.hidden_size // config.num_attention_heads)
+        fraction = float(os.getenv("CUDA_MEMORY_FRACTION", "1.0"))
+        self.max_cache_len = max_tokens
+        page_bytes = 2 * PAGE_LEN * config.num_hidden_layers * config.num_key_value_heads * head_dim * dtype_size
+        free_now, _ = torch.cuda.mem_get_info(device)
+        total = torch.cuda.get_device_properties(device).total_memory
+        free = max(0, free_now - (1 - fraction) * total)
+        if free < page_bytes:
+            raise RuntimeError(
+                f"Not enough GPU memory to allocate even a single cache page "
+                f"({page_bytes / (1024**2):.2f} MiB required, {free / (1024**2):.2f} MiB available).")
+        self.kvCachePool = KvCachePool(max_pages=1 if max_pages is None else int(max_pages),
+                                       num_layers=config.num_hidden_layers, num_heads=config.num_key_value_heads,
+                                       head_dim=head_dim, page_len=PAGE_LEN, dtype=torch.float16, device=device)
+
+    def reset(self):
+        self.kvCachePool.reset()

@@ -103,3 +103,17 @@ def test_bad_indices_are_reported(cuda_lib):
     before = pool.cache_data.clone()
     pool.reorder_cache_with_offset(torch.arange(5), offset=3)
     assert torch.equal(pool.cache_data, before)
+
+
+def test_flashinfer_cache_holder(cuda_lib):
+    """FlashInferCache builds the pool the reference builds (cache_manager.py:419-466): fp16, one page."""
+    from types import SimpleNamespace
+    cfg = SimpleNamespace(hidden_size=512, num_attention_heads=8, num_hidden_layers=3, num_key_value_heads=2)
+    c = kc.FlashInferCache(cfg, max_tokens=100, PAGE_LEN=16)
+    assert c.max_cache_len == 100 and c.config is cfg
+    assert tuple(c.kvCachePool.cache_data.shape) == (3, 1, 2, 16, 2, 64) and c.kvCachePool.cache_data.dtype == torch.float16
+    c.kvCachePool.cache_data.fill_(1.0)
+    c.reset()
+    assert float(c.kvCachePool.cache_data.abs().sum()) == 0.0
+    big = kc.FlashInferCache(cfg, max_tokens=100, PAGE_LEN=16, max_pages=7)
+    assert big.kvCachePool.max_pages == 7 and int(big.kvCachePool.num_free_pages()) == 7
