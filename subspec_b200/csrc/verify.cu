@@ -1097,6 +1097,14 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
       a.node_rowmax[nb + u] = 0.f;
       a.node_rowsum[nb + u] = 0.f;
     }
+    if (a.method != SUBSPEC_VERIFY_EXACT) {  // no child of this node has any probability
+      const int* coff = a.child_off + (size_t)b * (a.max_nodes + 1);
+      const int n_nodes = a.n_nodes[b];
+      for (int e = coff[u] + tid; e < coff[u + 1]; e += kSThreads) {
+        const int cnode = a.child_idx[nb + e];
+        if (cnode >= 0 && cnode < n_nodes) a.node_child_prob[nb + cnode] = 0.f;
+      }
+    }
   } else {
     const float c = sh.c;
     // Masses of this thread's values, ascending; and how many elements the counters hold.  Within a thread
