@@ -24,6 +24,7 @@ import threading
 import time
 from pathlib import Path
 
+import numpy as np
 import torch
 
 ROOT = Path(__file__).resolve().parent
@@ -356,12 +357,35 @@ def extra_stochastic(device, peak_gbs):
     ws = get_workspace(B, N, device)
     ws.set_trees(flats)
     ws.uniforms.uniform_(generator=gen)
-    ms = _time_ms(lambda: ws.run(logits, input_kind=_lib.IN_LOGITS, method=_lib.VERIFY_EXACT, do_sample=True,
-                                 temperature=1.0, top_p=0.9), iters=5, warm=2)
-    ws.fetch()
+
+    def timed(mode):
+        ms_ = _time_ms(lambda: ws.run(logits, input_kind=_lib.IN_LOGITS, method=_lib.VERIFY_EXACT, do_sample=mode,
+                                      temperature=1.0, top_p=0.9), iters=5, warm=2)
+        return ms_, ws.fetch()
+
+    # every decoded row draws its target (what the lossy verifier needs): all 2.49 GB are read
+    ms, _ = timed(1)
     gbs = logits.numel() * 2 / (ms * 1e-3) / 1e9
     out["stochastic_verify_config2"] = {"ms": ms, "GB/s": gbs, "frac_of_measured_peak": gbs / peak_gbs,
-                                        "bytes": logits.numel() * 2}
+                                        "bytes": logits.numel() * 2, "draws": "every decoded row"}
+    # sample-and-match as the reference walks it: a draw only at the contexts the walk stands on.  With the
+    # config's unboosted logits no draft token is ever drawn (one context per sequence); the second figure
+    # boosts the first child of every node so that walks run down the tree.
+    ms_lazy, res = timed(2)
+    out["stochastic_verify_config2_walk"] = {"ms": ms_lazy, "contexts_visited_per_sequence":
+                                             float((res["node_target"] >= 0).sum(axis=1).mean()),
+                                             "draws": "only where the walk stands (default)"}
+    for b in range(B):
+        tok, off, idx = flats[b][:3]
+        first = idx[off[:-1][off[1:] > off[:-1]]]          # first child of every inner node
+        parent = np.nonzero(off[1:] > off[:-1])[0]
+        logits[b, torch.as_tensor(parent, device=device), torch.as_tensor(tok[first], device=device)] = 16.0
+    ms_deep, res = timed(2)
+    visited = (res["node_target"] >= 0).sum(axis=1)
+    out["stochastic_verify_config2_walk_boosted"] = {"ms": ms_deep, "contexts_visited_per_sequence":
+                                                     float(visited.mean()), "most_contexts_in_a_sequence":
+                                                     int(visited.max()),
+                                                     "accepted_per_sequence": float(res["out_meta"][:, 1].mean())}
     return out
 
 

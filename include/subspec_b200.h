@@ -139,7 +139,9 @@ typedef struct subspec_verify_args {
   const int32_t* child_idx; /* [batch, max_nodes] */
   const int32_t* root;      /* [batch] local root index */
   /* sampling */
-  int32_t do_sample;
+  int32_t do_sample;  /* 0: greedy targets; 1: every decoded row draws its target; 2 (exact method only): only the
+                         contexts the walk stands on draw, as the reference's walker does -- same results,
+                         a handful of rows read instead of all (node_target is -1 for rows not visited) */
   int32_t top_k;      /* 0 = off; else keep every score >= the k-th largest (TopKLogitsWarper, base.py:58-59) */
   double temperature; /* > 0 */
   double top_p;       /* >= 1 disables the nucleus filter */

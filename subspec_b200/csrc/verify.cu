@@ -929,20 +929,17 @@ struct SampleShared {
   int warp_max[kSWarps];
 };
 
+// The whole row pipeline for row u of sequence b, run by one 1024-thread CTA: writes node_target (and the
+// row statistics; entropy and child probabilities too unless the method is the exact walk) and ends with a
+// CTA barrier.  False when the row could not be processed (reported through dev_status); every thread
+// returns the same value.
 template <typename T>
-__global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const KArgs ka) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ SampleShared sh;
+__device__ bool sample_row(const KArgs& ka, SampleShared& sh, unsigned char* smem_raw, int b, int u) {
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw);
   float* ch_mass = reinterpret_cast<float*>(hist + kHistWords);
   uint32_t* ch_ties = reinterpret_cast<uint32_t*>(ch_mass + kMaxChunks);
 
   const subspec_verify_args& a = ka.a;
-  const int row = blockIdx.x;
-  const int b = row / a.max_nodes;
-  const int u = row - b * a.max_nodes;
-  const int n_rows = a.n_rows[b];
-  if (u >= n_rows) return;
   const int V = a.vocab;
   const T* rowp = reinterpret_cast<const T*>(a.logits) + (size_t)b * a.seq_stride + (size_t)u * a.row_stride;
   const bool vec_ok = ka.vec_ok != 0;
@@ -1089,7 +1086,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
   if (K_max < 0) {  // nothing but -inf / empty: no distribution to sample from
     if (sh.finite != 0) {  // ... or 65536 copies of one value wrapped its counter to zero
       if (tid == 0) flag(a.dev_status, SUBSPEC_DEV_HIST_OVERFLOW);
-      return;
+      return false;
     }
     if (tid == 0) {
       a.node_target[nb + u] = 0;
@@ -1146,7 +1143,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
       // a 16-bit counter wrapped (one value more than 65535 times in the row): the counters no longer add
       // up to the number of elements counted, whichever way the carry went
       if (tid == 0) flag(a.dev_status, SUBSPEC_DEV_HIST_OVERFLOW);
-      return;
+      return false;
     }
     // the 32 warp totals are scanned by one warp, not added up by every thread: double-precision adds are
     // the slowest instructions this kernel has
@@ -1516,9 +1513,26 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
       }
     }
   }
+  __syncthreads();
+  return true;
+}
+
+// One CTA per decoded row; the CTA that finishes a sequence's last row runs the walk (lossy DP on sampled
+// targets, or the exact walk when every row's target is wanted).
+template <typename T>
+__global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const KArgs ka) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ SampleShared sh;
+  const subspec_verify_args& a = ka.a;
+  const int row = blockIdx.x;
+  const int b = row / a.max_nodes;
+  const int u = row - b * a.max_nodes;
+  const int n_rows = a.n_rows[b];
+  if (u >= n_rows) return;
+  if (!sample_row<T>(ka, sh, smem_raw, b, u)) return;
   __threadfence();
   __syncthreads();
-  if (tid == 0) {
+  if (threadIdx.x == 0) {
     const int t = atomicAdd(ka.sc.seq_ticket + b, 1);
     sh.flag = (t == n_rows - 1);
   }
@@ -1526,6 +1540,134 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
   if (!sh.flag) return;
   __threadfence();
   run_walk(ka, b, smem_raw);
+}
+
+// do_sample == 2: only the contexts the walk visits are sampled -- what the reference's walker does
+// (tree_verify.py:61-104 with classic_sd.py:111-116 draws at the context it stands on) -- by one CTA per
+// sequence that alternates the row pipeline with one step of the exact walk.  A sequence touches a
+// handful of its rows instead of all of them.
+template <typename T>
+__global__ void __launch_bounds__(kSThreads, 1) verify_sample_walk_kernel(const KArgs ka) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ SampleShared sh;
+  __shared__ int s_cur, s_state;  // context to sample next; 1 = walk on, 2 = sample the bonus, 0 = done
+  const subspec_verify_args& a = ka.a;
+  const int b = blockIdx.x, N = a.max_nodes;
+  const size_t nb = (size_t)b * N;
+  const int n_nodes = a.n_nodes[b], n_rows = a.n_rows[b];
+  const int* coff = a.child_off + (size_t)b * (N + 1);
+  const int* cidx = a.child_idx + nb;
+  const int* tok = a.token_ids + nb;
+  for (int i = threadIdx.x; i < N; i += kSThreads) a.node_target[nb + i] = -1;  // not visited
+  // walk state, thread 0 only
+  int64_t* out_tok = a.out_tokens + (size_t)b * a.max_out;
+  int64_t* out_hid = a.out_hidden + (size_t)b * a.max_out;
+  const int max_out = a.max_out;
+  const int64_t eos = a.eos;
+  int L = 0, acc = 0, total = 0, bonus = -1, cur = 0;
+  if (threadIdx.x == 0) {
+    cur = a.root[b];
+    if (cur < 0 || cur >= n_rows) {
+      flag(a.dev_status, SUBSPEC_DEV_BAD_ROOT);
+      cur = 0;
+    }
+    const bool go = n_nodes > 0 && (coff[cur + 1] - coff[cur]) > 0;
+    s_cur = cur;
+    s_state = n_nodes > 0 ? (go ? 1 : 2) : 0;
+  }
+  __syncthreads();
+  while (s_state != 0) {
+    const int state = s_state, ctx = s_cur;
+    int tgt = -1;
+    if (ctx < n_rows) {
+      if (!sample_row<T>(ka, sh, smem_raw, b, ctx)) return;  // reported through dev_status
+      tgt = a.node_target[nb + ctx];                         // written inside this CTA, before its last barrier
+    }
+    if (threadIdx.x == 0) {
+      if (state == 2) {  // the bonus token of the final context
+        if (L < max_out) {
+          out_tok[L] = tgt;
+          out_hid[L] = ctx;
+        }
+        ++L;
+        s_state = 0;
+      } else {  // one step of tree_verify.py:61-104
+        ++total;
+        int match = -1;
+        for (int e = coff[cur]; e < coff[cur + 1]; ++e) {
+          const int c = cidx[e];
+          if (c < 0 || c >= n_nodes) {
+            flag(a.dev_status, SUBSPEC_DEV_BAD_CHILD);
+            continue;
+          }
+          if (tok[c] == tgt) {
+            match = c;
+            break;
+          }
+        }
+        bool stop = false;
+        if (match < 0) {
+          bonus = tgt;
+          stop = true;
+        } else {
+          ++acc;
+          if (L < max_out) {
+            out_tok[L] = tgt;
+            out_hid[L] = cur;
+          }
+          ++L;
+          if (eos >= 0 && (int64_t)tgt == eos) {
+            stop = true;
+          } else {
+            cur = match;
+            const int cb = coff[cur], ce = coff[cur + 1];
+            if (ce - cb == 0) {
+              stop = true;
+            } else {
+              int mn = INT_MAX;
+              for (int e = cb; e < ce; ++e) mn = min(mn, cidx[e]);
+              if (mn >= n_rows) stop = true;
+            }
+          }
+        }
+        if (!stop) {
+          s_cur = cur;
+        } else {
+          const bool ended_on_eos = (L > 0) && (eos >= 0) && (L - 1 < max_out) && (out_tok[L - 1] == eos);
+          if (ended_on_eos) {
+            s_state = 0;
+          } else if (bonus >= 0) {  // the draw that missed every child is the bonus
+            if (L < max_out) {
+              out_tok[L] = bonus;
+              out_hid[L] = cur;
+            }
+            ++L;
+            s_state = 0;
+          } else {  // stopped on a context that has not drawn yet
+            s_cur = cur;
+            s_state = 2;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    int* meta = a.out_meta + (size_t)b * 4;
+    meta[0] = L < max_out ? L : max_out;
+    meta[1] = acc;
+    meta[2] = total;
+    meta[3] = L > max_out ? 1 : 0;
+  }
+}
+
+template <typename T>
+cudaError_t launch_sample_walk(const KArgs& ka, int batch, cudaStream_t st) {
+  cudaError_t e = cudaFuncSetAttribute(verify_sample_walk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)kSampleSmem);
+  if (e != cudaSuccess) return e;
+  verify_sample_walk_kernel<T><<<batch, kSThreads, kSampleSmem, st>>>(ka);
+  return cudaGetLastError();
 }
 
 template <typename T>
@@ -1637,6 +1779,11 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
   int rc = cuda_check(cudaMemsetAsync(a.scratch, 0, ticket_bytes(a.batch, a.max_nodes), st));
   if (rc) return rc;
   cudaError_t e;
+  if (a.do_sample == 2 && a.method == SUBSPEC_VERIFY_EXACT) {
+    e = a.dtype == SUBSPEC_BF16 ? launch_sample_walk<__nv_bfloat16>(ka, a.batch, st)
+                                : launch_sample_walk<__half>(ka, a.batch, st);
+    return cuda_check(e);
+  }
   if (a.do_sample) {
     e = a.dtype == SUBSPEC_BF16 ? launch_sample<__nv_bfloat16>(ka, (int)rows, st)
                                 : launch_sample<__half>(ka, (int)rows, st);

@@ -157,7 +157,7 @@ class VerifyWorkspace:
         a.logits = logits.data_ptr()
         for name in ("n_nodes", "n_rows", "token_ids", "child_off", "child_idx", "root"):
             setattr(a, name, self._in_ptr(name))
-        a.do_sample = int(bool(do_sample))
+        a.do_sample = int(do_sample)  # 0 / 1 (every row draws) / 2 (only the contexts the exact walk visits)
         a.top_k = int(top_k)
         a.temperature, a.top_p = float(temperature), float(top_p)
         a.uniforms = self.uniforms.data_ptr()
@@ -515,8 +515,13 @@ def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logit
         else:
             u = torch.as_tensor(uniforms, dtype=torch.float32, device=device)
             ws.uniforms.view(B, ws.max_nodes)[:, :u.shape[1]].copy_(u)
+    # Sampled targets: the exact walk only needs them at the contexts it visits (mode 2); the lossy DP, and a
+    # caller who asks for every node's draw (`verify_kwargs={"sample_all_nodes": True}`), need all rows (mode 1).
+    sample_mode = 0
+    if do_sample:
+        sample_mode = 2 if (method == _lib.VERIFY_EXACT and not vk.get("sample_all_nodes", False)) else 1
     ws.run(logits, input_kind=_lib.IN_LOGITS, method=method, gate=gate, threshold=threshold, window=window,
-           eos=eos_token_id, do_sample=do_sample, temperature=temperature, top_p=top_p, top_k=top_k)
+           eos=eos_token_id, do_sample=sample_mode, temperature=temperature, top_p=top_p, top_k=top_k)
     out = ws.fetch()
     results: List[Any] = []
     for b in range(B):

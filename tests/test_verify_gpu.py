@@ -167,7 +167,7 @@ def test_stochastic_sample_and_match(cuda_lib, vocab, nodes, dtype, temperature,
         procs.append(TopPLogitsWarper(top_p=top_p))
     res = verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
                               eos_token_id=None, logits_processor=procs, do_sample=True, verify_method="stochastic",
-                              uniforms=uniforms)
+                              uniforms=uniforms, verify_kwargs={"sample_all_nodes": True})
     from subspec_b200.verify import get_workspace
     targets = get_workspace(B, nodes, torch.device("cuda", 0)).fetch()["node_target"]
     decided_by_rounding = 0
@@ -210,7 +210,7 @@ def test_stochastic_ties_masks_and_zeros(cuda_lib):
         procs = LogitsProcessorList([TopPLogitsWarper(top_p=top_p)])
         verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
                             eos_token_id=None, logits_processor=procs, do_sample=True, verify_method="stochastic",
-                            uniforms=uniforms)
+                            uniforms=uniforms, verify_kwargs={"sample_all_nodes": True})
         from subspec_b200.verify import get_workspace
         targets = get_workspace(B, nodes, torch.device("cuda", 0)).fetch()["node_target"]
         for b, st in enumerate(sts):
@@ -262,13 +262,14 @@ def test_stochastic_counter_overflow_is_reported(cuda_lib):
         with pytest.raises(ValueError, match="65535"):
             verify_tree_batched(trees=[_tree_of(st)], root_inds=[0], logits=logits.cuda(), eos_token_id=None,
                                 logits_processor=None, do_sample=True, verify_method="stochastic",
-                                uniforms=torch.rand(1, nodes))
+                                uniforms=torch.rand(1, nodes), verify_kwargs={"sample_all_nodes": True})
     # exactly 65535 copies still fit
     logits = torch.randn(1, nodes, vocab).to(torch.bfloat16)
     logits[0, 1, :65535] = 0.75
     logits[0, 1, 65535:][logits[0, 1, 65535:] == 0.75] = 0.5
     verify_tree_batched(trees=[_tree_of(st)], root_inds=[0], logits=logits.cuda(), eos_token_id=None,
-                        logits_processor=None, do_sample=True, verify_method="stochastic", uniforms=torch.rand(1, nodes))
+                        logits_processor=None, do_sample=True, verify_method="stochastic", uniforms=torch.rand(1, nodes),
+                        verify_kwargs={"sample_all_nodes": True})
 
 
 @pytest.mark.parametrize("vocab,nodes,dtype,temperature,top_k,top_p", [
@@ -290,7 +291,8 @@ def test_stochastic_top_k(cuda_lib, vocab, nodes, dtype, temperature, top_k, top
     if top_p < 1.0:
         procs.append(TopPLogitsWarper(top_p=top_p))
     verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(), eos_token_id=None,
-                        logits_processor=procs, do_sample=True, verify_method="stochastic", uniforms=uniforms)
+                        logits_processor=procs, do_sample=True, verify_method="stochastic", uniforms=uniforms,
+                        verify_kwargs={"sample_all_nodes": True})
     targets = get_workspace(B, nodes, torch.device("cuda", 0)).fetch()["node_target"]
     checked = 0
     for b, st in enumerate(sts):
@@ -379,3 +381,45 @@ def test_exact_and_lossy_in_one_pass(cuda_lib, dtype, vocab, gate, threshold, wi
     with pytest.raises(ValueError):
         verify_tree_batched(trees=trees, root_inds=[0] * B, logits=logits[:, :nodes - 3].cuda(), eos_token_id=None,
                             logits_processor=None, do_sample=False, verify_method="exact+lossy", verify_kwargs=kw)
+
+
+@pytest.mark.parametrize("vocab,nodes,dtype,temperature,top_k,top_p", [
+    (152064, 40, torch.bfloat16, 1.0, 0, 0.9), (32000, 64, torch.float16, 0.8, 50, 0.95), (4099, 24, torch.bfloat16, 1.0, 0, 1.0)])
+def test_stochastic_walk_samples_only_where_it_stands(cuda_lib, vocab, nodes, dtype, temperature, top_k, top_p):
+    """Default stochastic verification draws only at the contexts the walk visits (as the reference's walker
+    does): same tokens, contexts and lengths as drawing at every node, and the draws it does make are the same."""
+    from transformers.generation.logits_process import (LogitsProcessorList, TemperatureLogitsWarper,
+                                                        TopKLogitsWarper, TopPLogitsWarper)
+    from subspec_b200.verify import get_workspace
+    B = 6
+    gen = torch.Generator().manual_seed(77 + nodes)
+    sts = [synthetic.random_tree(nodes, 10, 6, vocab, gen) for _ in range(B)]
+    logits = torch.stack([synthetic.verify_logits(st, vocab, gen, dtype=dtype, sigma=2.5, boost=14.0) for st in sts])
+    uniforms = torch.rand(B, nodes, generator=gen)
+    procs = LogitsProcessorList()
+    if temperature != 1.0:
+        procs.append(TemperatureLogitsWarper(temperature))
+    if top_k:
+        procs.append(TopKLogitsWarper(top_k=top_k))
+    if top_p < 1.0:
+        procs.append(TopPLogitsWarper(top_p=top_p))
+    common = dict(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
+                  eos_token_id=int(sts[0].token_ids[2]), logits_processor=procs, do_sample=True,
+                  verify_method="stochastic", uniforms=uniforms)
+    full = verify_tree_batched(verify_kwargs={"sample_all_nodes": True}, **common)
+    t_full = get_workspace(B, nodes, torch.device("cuda", 0)).fetch()["node_target"].copy()
+    lazy = verify_tree_batched(**common)
+    t_lazy = get_workspace(B, nodes, torch.device("cuda", 0)).fetch()["node_target"].copy()
+    accepted = 0
+    for b in range(B):
+        assert lazy[b].sampled_tokens.tolist() == full[b].sampled_tokens.tolist()
+        assert lazy[b].hidden_indices.tolist() == full[b].hidden_indices.tolist()
+        assert (lazy[b].total_len, lazy[b].accept_len) == (full[b].total_len, full[b].accept_len)
+        visited = set(lazy[b].hidden_indices.tolist())
+        for u in range(sts[b].n):
+            if u in visited:
+                assert t_lazy[b, u] == t_full[b, u]
+            else:
+                assert t_lazy[b, u] == -1
+        accepted += lazy[b].accept_len
+    assert accepted > 0
