@@ -172,6 +172,19 @@ typedef struct subspec_verify_args {
   int64_t* out2_tokens;
   int64_t* out2_hidden;
   int32_t* out2_meta;
+  /* Residual (p - q) acceptance, an extension with no counterpart in the reference (which samples a target
+   * token and looks for it among the children, classic_sd.py:111-116).  acceptance = 1 with do_sample != 0 and
+   * the exact method: at a context with filtered target distribution p and draft distribution
+   * q = softmax(draft_logits row / draft_temperature), the children are tried in list order; child c with token
+   * x is accepted iff accept_uniforms[c] < min(1, p'(x) / q(x)), where p' = p at first and, after every
+   * rejection, p' <- normalise(max(p' - q, 0)); when no child is accepted the bonus token is the inverse-CDF
+   * draw from p' with uniforms[context]. */
+  int32_t acceptance;           /* 0: sample-and-match; 1: residual */
+  const void* draft_logits;     /* [batch, rows, vocab], dtype and vocab as `logits` */
+  int64_t draft_seq_stride;     /* elements */
+  int64_t draft_row_stride;
+  double draft_temperature;     /* > 0 */
+  const float* accept_uniforms; /* [batch, max_nodes], indexed by the child node */
 } subspec_verify_args;
 
 SUBSPEC_API int subspec_verify_scratch_bytes(int32_t batch, int32_t max_nodes, size_t* bytes);

@@ -272,6 +272,77 @@ def verify(*, logits: torch.Tensor, token_ids: Sequence[int], children: Sequence
                         use_entropy=threshold_method == "entropy", target=tgt)
 
 
+def residual_walk(*, logits: torch.Tensor, draft_logits: torch.Tensor, token_ids: Sequence[int],
+                  children: Sequence[Sequence[int]], accept_uniforms: Sequence[float], uniforms: Sequence[float],
+                  root: int = 0, eos: Optional[int] = None, temperature: float = 1.0, top_p: float = 1.0,
+                  top_k: int = 0, draft_temperature: float = 1.0):
+    """Residual (p - q) acceptance over the tree, fp64.  NOT in the reference (which samples and matches,
+    classic_sd.py:111-116): this is the restatement of the rule the kernel's header states.  Returns
+    (VerifyResult, margin) where margin is the smallest distance of an accept test's uniform from its
+    threshold; the bonus draws are judged separately with `sampling_margins`-style CDF distances."""
+    n = int(logits.shape[0])
+    p_all = target_probs(logits, True, temperature, top_p, upcast=True, top_k=top_k).double()
+    q_all = torch.softmax(draft_logits.double() / draft_temperature, dim=-1)
+    toks, hidden = [], []
+    acc = total = 0
+    margin = float("inf")
+    cur = root
+
+    def draw(dist: torch.Tensor, ctx: int) -> int:
+        nonlocal margin
+        cdf = dist.cumsum(0)
+        tot = float(cdf[-1])
+        margin = min(margin, float(((cdf - float(uniforms[ctx]) * tot).abs()).min() / tot) * 1e2)
+        return inverse_cdf_pick(dist, float(uniforms[ctx]))
+
+    go = len(children[cur]) > 0
+    if not go:
+        toks.append(draw(p_all[cur], cur))
+        hidden.append(cur)
+    while go:
+        ch = list(children[cur])
+        total += 1
+        pr, qr = p_all[cur].clone(), q_all[cur]
+        live = True
+        rejected = False
+        got = None
+        for c in ch:
+            x = int(token_ids[c])
+            ratio = 0.0
+            if live:
+                px, qx = float(pr[x]), float(qr[x])
+                ratio = px / qx if qx > 0 else (float("inf") if px > 0 else 0.0)
+            thr = min(1.0, ratio)
+            margin = min(margin, abs(float(accept_uniforms[c]) - thr))
+            if float(accept_uniforms[c]) < thr:
+                got = c
+                break
+            rejected = True
+            if live:
+                pr = torch.clamp(pr - qr, min=0)
+                z = float(pr.sum())
+                if z > 0:
+                    pr = pr / z
+                else:
+                    live = False
+        if got is None:
+            toks.append(draw(pr if (rejected and live) else p_all[cur], cur))
+            hidden.append(cur)
+            break
+        x = int(token_ids[got])
+        toks.append(x)
+        hidden.append(cur)
+        acc += 1
+        if eos is not None and x == eos:
+            break
+        cur = got
+        if not children[cur] or min(children[cur]) >= n:  # a leaf, or an undecoded level: a fresh draw there
+            toks.append(draw(p_all[cur], cur))
+            hidden.append(cur)
+            break
+    return VerifyResult(tokens=toks, hidden=hidden, total_len=total, accept_len=acc), margin
+
+
 def top2_logit_gap(logits: torch.Tensor) -> float:
     """Smallest gap between the two largest logits over all rows (argmax flip margin)."""
     top = torch.topk(logits.float(), 2, dim=-1).values

@@ -54,6 +54,8 @@ class VerifyArgs(C.Structure):
         ("node_rowsum", _vp), ("node_exact_after", _vp), ("node_best_len", _vp), ("node_best_next", _vp),
         ("dev_status", _vp), ("scratch", _vp), ("scratch_bytes", C.c_size_t),
         ("out2_tokens", _vp), ("out2_hidden", _vp), ("out2_meta", _vp),
+        ("acceptance", _i32), ("draft_logits", _vp), ("draft_seq_stride", _i64), ("draft_row_stride", _i64),
+        ("draft_temperature", _f64), ("accept_uniforms", _vp),
     ]
 
 

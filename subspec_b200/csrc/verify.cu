@@ -339,6 +339,8 @@ struct KArgs {
   int vec_ok;  // every row start is 16-byte aligned
   float k;     // log2(e) / temperature
   float remove_below;  // nucleus filter: drop tokens while the ascending cumulative probability is <= this
+  float kD;            // residual acceptance: log2(e) / draft temperature
+  int dvec_ok;         // every draft row start is 16-byte aligned
 };
 
 // ---- the accept walk, run by one CTA per sequence out of shared memory -----------
@@ -926,6 +928,7 @@ struct SampleShared {
   double cbase;
   double T2;
   int kmax, k_b, r, n_b, finite, counted, flag, first, last_nz, cstar, T0, k_k, itotal, rank;
+  int tie_chunk, tie_T0, tie_cut;  // where the run of values tied at the boundary is cut, in vocabulary order
   int warp_max[kSWarps];
 };
 
@@ -1392,6 +1395,7 @@ __device__ bool sample_row(const KArgs& ka, SampleShared& sh, unsigned char* sme
     if (tid == 0) {
       sh.first = kSThreads;
       sh.last_nz = -1;
+      sh.tie_chunk = -1;
     }
     // exclusive block scan of the tie counts
     int T_thread0;
@@ -1405,6 +1409,20 @@ __device__ bool sample_row(const KArgs& ka, SampleShared& sh, unsigned char* sme
       }
       __syncthreads();
       T_thread0 = sh.warp_max[warp] + incl - tl;
+    }
+    if (r_rm > 0 && r_rm < sh.n_b && T_thread0 <= r_rm && r_rm < T_thread0 + tl) {
+      // the nucleus filter removes the first r_rm of the values tied at the boundary: the tie of rank r_rm
+      // (the first that stays) is in one of this thread's chunks
+      int Trun = T_thread0;
+      for (int cc = c0; cc < c1; ++cc) {
+        const int T1 = Trun + (int)ch_ties[cc];
+        if (r_rm < T1) {
+          sh.tie_chunk = cc;
+          sh.tie_T0 = Trun;
+          break;
+        }
+        Trun = T1;
+      }
     }
     double local = 0.0;
     {
@@ -1505,6 +1523,27 @@ __device__ bool sample_row(const KArgs& ka, SampleShared& sh, unsigned char* sme
       } else {
         within = any ? __shfl_sync(0xffffffffu, last, 31 - __clz(any)) : 0;
       }
+      // vocabulary index from which the values tied at the boundary stay in the distribution
+      int tie_cut = r_rm == 0 ? 0 : V;
+      if (sh.tie_chunk >= 0) {
+        uint32_t tb[8];
+        load8<T>(rowp, sh.tie_chunk * kChunkElems + lane * 8, V, vec_ok, tb);
+        int lt2 = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (tb[j] != Bits16<T>::kNegInf && (int)key_of(tb[j]) == k_b) ++lt2;
+        int rank = sh.tie_T0 + warp_scan_i32(lt2) - lt2;
+        int found = -1;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (tb[j] != Bits16<T>::kNegInf && (int)key_of(tb[j]) == k_b) {
+            if (rank == r_rm && found < 0) found = sh.tie_chunk * kChunkElems + lane * 8 + j;
+            ++rank;
+          }
+        const uint32_t who = __ballot_sync(0xffffffffu, found >= 0);
+        if (who) tie_cut = __shfl_sync(0xffffffffu, found, __ffs(who) - 1);
+      }
+      if (lane == 0) sh.tie_cut = tie_cut;
       if (lane == 0) {
         a.node_target[nb + u] = min(cstar * kChunkElems + within, V - 1);
         if (a.method == SUBSPEC_VERIFY_EXACT) a.node_entropy[nb + u] = 0.f;
@@ -1542,6 +1581,57 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
   run_walk(ka, b, smem_raw);
 }
 
+// ---- residual (p - q) acceptance at one context: block-wide helpers ---------------------------------------
+// The filtered target distribution of the row sample_row has just processed, evaluable per element:
+// p(v) = 2^(x kT - c) / Z for a survivor of the filters, 0 otherwise.  Survivors are the values above the
+// boundary value, and of the values tied at it those from vocabulary index tie_cut on.
+template <typename T>
+struct TargetDist {
+  float kT, c, invZ, v_b;
+  int k_b, tie_cut;
+  bool ties_live, zero_boundary;
+  __device__ __forceinline__ void from(const SampleShared& sh, float kT_) {
+    kT = kT_;
+    c = sh.c;
+    invZ = (float)(1.0 / sh.Z);
+    k_b = sh.k_b;
+    const uint32_t pat_b = k_b >= 0 ? bits_of((uint32_t)k_b) : (uint32_t)Bits16<T>::kNegInf;
+    v_b = Bits16<T>::value(pat_b);
+    zero_boundary = k_b >= 0 && (pat_b & 0x7FFFu) == 0u;
+    ties_live = k_b >= 0 && sh.e_b > 0.f;
+    tie_cut = sh.tie_cut;
+  }
+  __device__ __forceinline__ bool tie_ok(uint32_t pat, int idx) const {
+    if (zero_boundary) {  // the two zeros compare equal as floats but are two keys
+      const int key = (int)key_of(pat);
+      if (key != k_b) return key > k_b;
+    }
+    return ties_live && idx >= tie_cut;
+  }
+  __device__ __forceinline__ float p(uint32_t pat, float v, int idx) const {
+    bool surv = v > v_b;
+    if (v == v_b) surv = tie_ok(pat, idx);
+    return surv ? ex2f(fmaf(v, kT, -c)) * invZ : 0.f;
+  }
+};
+
+__device__ __forceinline__ double block_sum_f64(double v, SampleShared& sh) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += shfl_xor_f64(v, off);
+  __syncthreads();  // warp_tot may still be read from a previous round
+  if (lane == 0) sh.warp_tot[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    double t = sh.warp_tot[lane];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) t += shfl_xor_f64(t, off);
+    if (lane == 0) sh.S = t;
+  }
+  __syncthreads();
+  return sh.S;
+}
+
 // do_sample == 2: only the contexts the walk visits are sampled -- what the reference's walker does
 // (tree_verify.py:61-104 with classic_sd.py:111-116 draws at the context it stands on) -- by one CTA per
 // sequence that alternates the row pipeline with one step of the exact walk.  A sequence touches a
@@ -1551,6 +1641,8 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_walk_kernel(const 
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ SampleShared sh;
   __shared__ int s_cur, s_state;  // context to sample next; 1 = walk on, 2 = sample the bonus, 0 = done
+  __shared__ int s_dec, s_pick;   // residual acceptance: the accepted child (-1: rejected); the bonus drawn
+  __shared__ float s_a, s_zr, s_dmax;  // residual p' ~ max(p - a q, 0) / zr; maximum of the draft row
   const subspec_verify_args& a = ka.a;
   const int b = blockIdx.x, N = a.max_nodes;
   const size_t nb = (size_t)b * N;
@@ -1582,6 +1674,246 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_walk_kernel(const 
     if (ctx < n_rows) {
       if (!sample_row<T>(ka, sh, smem_raw, b, ctx)) return;  // reported through dev_status
       tgt = a.node_target[nb + ctx];                         // written inside this CTA, before its last barrier
+    }
+    if (a.acceptance == 1 && state == 1 && ctx < n_rows) {
+      // ---- residual acceptance at this context (every branch below is taken by the whole CTA) ----
+      const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+      const int V = a.vocab;
+      const T* trow = reinterpret_cast<const T*>(a.logits) + (size_t)b * a.seq_stride + (size_t)ctx * a.row_stride;
+      const T* drow = reinterpret_cast<const T*>(a.draft_logits) + (size_t)b * a.draft_seq_stride +
+                      (size_t)ctx * a.draft_row_stride;
+      const bool tvec = ka.vec_ok != 0, dvec = ka.dvec_ok != 0;
+      const int nchunks = (V + kChunkElems - 1) / kChunkElems;
+      float* ch_mass = reinterpret_cast<float*>(reinterpret_cast<uint32_t*>(smem_raw) + kHistWords);
+      TargetDist<T> tp;
+      tp.from(sh, ka.k);
+      const float kD = ka.kD;
+      // draft row: maximum, then the softmax denominator
+      float dmax = -INFINITY;
+      for (int cidx2 = warp; cidx2 < nchunks; cidx2 += kSWarps) {
+        float v[8];
+        unpack8_values(load8_packed<T>(drow, cidx2 * kChunkElems + lane * 8, V, dvec), v, T());
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dmax = fmaxf(dmax, v[j]);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) dmax = fmaxf(dmax, __shfl_xor_sync(0xffffffffu, dmax, off));
+      __syncthreads();  // warp_tot may still be read from the row pipeline
+      if (lane == 0) sh.warp_tot[warp] = (double)dmax;
+      __syncthreads();
+      if (warp == 0) {
+        float t = (float)sh.warp_tot[lane];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, off));
+        if (lane == 0) s_dmax = fmaxf(t, -3.0e38f);
+      }
+      __syncthreads();
+      const float cD = s_dmax * kD;
+      double dsum = 0.0;
+      {
+        float acc32 = 0.f;
+        for (int cidx2 = warp; cidx2 < nchunks; cidx2 += kSWarps) {
+          float v[8];
+          unpack8_values(load8_packed<T>(drow, cidx2 * kChunkElems + lane * 8, V, dvec), v, T());
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc32 += ex2f(fmaf(v[j], kD, -cD));
+        }
+        dsum = block_sum_f64((double)acc32, sh);
+      }
+      const float invS = (float)(1.0 / dsum);
+      // residual mass sum_v max(p(v) - coef q(v), 0), and optionally its per-chunk parts
+      auto residual_pass = [&](float coef, bool keep_chunks) -> double {
+        float acc32 = 0.f;
+        for (int cidx2 = warp; cidx2 < nchunks; cidx2 += kSWarps) {
+          const int i0 = cidx2 * kChunkElems + lane * 8;
+          uint32_t tb[8];
+          float tv[8], dv[8];
+          const uint4 tq = load8_packed<T>(trow, i0, V, tvec);
+          unpack8(tq, tb);
+          unpack8_values(tq, tv, T());
+          unpack8_values(load8_packed<T>(drow, i0, V, dvec), dv, T());
+          float m = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float q = ex2f(fmaf(dv[j], kD, -cD)) * invS;
+            m += fmaxf(fmaf(-coef, q, tp.p(tb[j], tv[j], i0 + j)), 0.f);
+          }
+          if (keep_chunks) {
+            float cm = m;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) cm += __shfl_xor_sync(0xffffffffu, cm, off);
+            if (lane == 0) ch_mass[cidx2] = cm;
+          }
+          acc32 += m;
+        }
+        return block_sum_f64((double)acc32, sh);
+      };
+      if (tid == 0) {
+        s_a = 0.f;
+        s_zr = 1.f;
+        s_dec = -1;
+        ++total;
+      }
+      __syncthreads();
+      const int cb = coff[ctx], ce = coff[ctx + 1];
+      for (int e = cb; e < ce; ++e) {
+        if (tid == 0) {
+          const int cnode = cidx[e];
+          int dec = -1;
+          if (cnode < 0 || cnode >= n_nodes) {
+            flag(a.dev_status, SUBSPEC_DEV_BAD_CHILD);
+          } else {
+            const int x = tok[cnode];
+            if (x < 0 || x >= V) {
+              flag(a.dev_status, SUBSPEC_DEV_BAD_TOKEN);
+            } else if (s_zr > 0.f) {
+              const uint32_t tpat = reinterpret_cast<const unsigned short*>(trow)[x];
+              const uint32_t dpat = reinterpret_cast<const unsigned short*>(drow)[x];
+              const float px = tp.p(tpat, Bits16<T>::value(tpat), x);
+              const float qx = ex2f(fmaf(Bits16<T>::value(dpat), kD, -cD)) * invS;
+              const float r = fmaxf(fmaf(-s_a, qx, px), 0.f) / s_zr;
+              const float ratio = qx > 0.f ? r / qx : (r > 0.f ? INFINITY : 0.f);
+              if (a.accept_uniforms[nb + cnode] < fminf(1.f, ratio)) dec = cnode;
+            }
+          }
+          s_dec = dec;
+        }
+        __syncthreads();
+        if (s_dec >= 0) break;
+        // rejected: p' <- normalise(max(p' - q, 0)), i.e. coefficient a + zr and a new normaliser
+        const float coef = s_a + s_zr;
+        const double z = residual_pass(coef, false);
+        if (tid == 0) {
+          s_a = coef;
+          s_zr = (float)z;
+        }
+        __syncthreads();
+      }
+      if (s_dec < 0) {
+        // no child accepted: the bonus is the inverse-CDF draw from the residual (from p itself when the
+        // residual has no mass left), in vocabulary order
+        int pick = tgt;
+        if (s_a > 0.f && s_zr > 0.f) {
+          const float coef = s_a;
+          const double zsum = residual_pass(coef, true);
+          const double target = (double)a.uniforms[nb + ctx] * zsum;
+          // chunk: first whose inclusive cumulative mass passes the target
+          const int per = (nchunks + kSThreads - 1) / kSThreads;
+          const int c0 = min(tid * per, nchunks), c1 = min(c0 + per, nchunks);
+          double local = 0.0;
+          for (int cc = c0; cc < c1; ++cc) local += (double)ch_mass[cc];
+          if (tid == 0) {
+            sh.first = kSThreads;
+            sh.last_nz = -1;
+          }
+          const double incl = warp_scan_f64(local);
+          __syncthreads();
+          if (lane == 31) sh.warp_tot[warp] = incl;
+          __syncthreads();
+          if (warp == 0) {
+            const double x = sh.warp_tot[lane];
+            sh.warp_tot[lane] = warp_scan_f64(x) - x;
+          }
+          __syncthreads();
+          const double lbase = sh.warp_tot[warp] + incl - local;
+          if (local > 0.0) {
+            if (lbase + local > target) atomicMin(&sh.first, tid);
+            atomicMax(&sh.last_nz, tid);
+          }
+          __syncthreads();
+          const bool pick_last = sh.first == kSThreads;
+          const int Lt = pick_last ? max(sh.last_nz, 0) : sh.first;
+          if (tid == Lt) {
+            double cum = lbase;
+            int cstar = c0;
+            double cbase = cum;
+            for (int cc = c0; cc < c1; ++cc) {
+              const double cm = (double)ch_mass[cc];
+              if (cm > 0.0) {
+                cstar = cc;
+                cbase = cum;
+                if (!pick_last && cum + cm > target) break;
+              }
+              cum += cm;
+            }
+            sh.cstar = min(cstar, nchunks - 1);
+            sh.cbase = cbase;
+          }
+          __syncthreads();
+          if (warp == 0) {
+            const int cstar = sh.cstar;
+            const int i0 = cstar * kChunkElems + lane * 8;
+            uint32_t tb[8];
+            float tv[8], dv[8], rm[8];
+            const uint4 tq = load8_packed<T>(trow, i0, V, tvec);
+            unpack8(tq, tb);
+            unpack8_values(tq, tv, T());
+            unpack8_values(load8_packed<T>(drow, i0, V, dvec), dv, T());
+            double lsum = 0.0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float q = ex2f(fmaf(dv[j], kD, -cD)) * invS;
+              rm[j] = fmaxf(fmaf(-coef, q, tp.p(tb[j], tv[j], i0 + j)), 0.f);
+              lsum += (double)rm[j];
+            }
+            const double eincl = warp_scan_f64(lsum);
+            double run = sh.cbase + eincl - lsum;
+            int hit = -1, last = -1;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (rm[j] > 0.f) {
+                last = lane * 8 + j;
+                run += (double)rm[j];
+                if (hit < 0 && run > target) hit = lane * 8 + j;
+              }
+            const uint32_t hits = __ballot_sync(0xffffffffu, hit >= 0);
+            const uint32_t any = __ballot_sync(0xffffffffu, last >= 0);
+            int within;
+            if (hits && !pick_last)
+              within = __shfl_sync(0xffffffffu, hit, __ffs(hits) - 1);
+            else
+              within = any ? __shfl_sync(0xffffffffu, last, 31 - __clz(any)) : 0;
+            if (lane == 0) s_pick = min(cstar * kChunkElems + within, V - 1);
+          }
+          __syncthreads();
+          pick = s_pick;
+        }
+        if (tid == 0) {
+          if (L < max_out) {
+            out_tok[L] = pick;
+            out_hid[L] = ctx;
+          }
+          ++L;
+          s_state = 0;
+        }
+      } else if (tid == 0) {
+        // accepted child: emit its token, move there; a leaf or an undecoded level ends the walk with a
+        // fresh draw at that context (state 2), as in the sample-and-match walk
+        const int cnode = s_dec;
+        const int x = tok[cnode];
+        ++acc;
+        if (L < max_out) {
+          out_tok[L] = x;
+          out_hid[L] = ctx;
+        }
+        ++L;
+        cur = cnode;
+        s_cur = cur;
+        if (eos >= 0 && (int64_t)x == eos) {
+          s_state = 0;
+        } else {
+          const int cb2 = coff[cur], ce2 = coff[cur + 1];
+          bool more = ce2 - cb2 > 0;
+          if (more) {
+            int mn = INT_MAX;
+            for (int e2 = cb2; e2 < ce2; ++e2) mn = min(mn, cidx[e2]);
+            if (mn >= n_rows) more = false;
+          }
+          s_state = more ? 1 : 2;
+        }
+      }
+      __syncthreads();
+      continue;
     }
     if (threadIdx.x == 0) {
       if (state == 2) {  // the bonus token of the final context
@@ -1746,6 +2078,13 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
     // sampled targets: 16-bit logits; exact (sample-and-match) walk or the lossy DP on the filtered distribution
     if (a.dtype == SUBSPEC_F32 || a.input_kind != SUBSPEC_IN_LOGITS) return SUBSPEC_EUNSUPPORTED;
     if (!a.uniforms || !(a.temperature > 0.0) || !(a.top_p >= 0.0) || a.top_k < 0) return SUBSPEC_EINVAL;
+    if (a.acceptance != 0 && a.acceptance != 1) return SUBSPEC_EINVAL;
+    if (a.acceptance == 1) {  // residual acceptance: the exact walk, with the draft's logits of the same nodes
+      if (a.method != SUBSPEC_VERIFY_EXACT) return SUBSPEC_EUNSUPPORTED;
+      if (!a.draft_logits || !a.accept_uniforms || !(a.draft_temperature > 0.0)) return SUBSPEC_EINVAL;
+    }
+  } else if (a.acceptance != 0) {
+    return SUBSPEC_EINVAL;
   }
   size_t need = 0;
   subspec_verify_scratch_bytes(a.batch, a.max_nodes, &need);
@@ -1762,6 +2101,9 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
   const size_t esz = a.dtype == SUBSPEC_F32 ? 4 : 2;
   ka.vec_ok = ((reinterpret_cast<uintptr_t>(a.logits) & 15u) == 0) && ((a.seq_stride * esz) % 16 == 0) &&
               ((a.row_stride * esz) % 16 == 0);
+  ka.kD = a.acceptance == 1 ? (float)(1.4426950408889634 / a.draft_temperature) : 0.f;
+  ka.dvec_ok = a.acceptance == 1 && ((reinterpret_cast<uintptr_t>(a.draft_logits) & 15u) == 0) &&
+               ((a.draft_seq_stride * esz) % 16 == 0) && ((a.draft_row_stride * esz) % 16 == 0);
   // Fill the machine: with few rows, split every row over several CTAs.
   const int64_t rows = (int64_t)a.batch * a.max_nodes;
   const int64_t target = 4LL * kNumSMs;
@@ -1779,7 +2121,7 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
   int rc = cuda_check(cudaMemsetAsync(a.scratch, 0, ticket_bytes(a.batch, a.max_nodes), st));
   if (rc) return rc;
   cudaError_t e;
-  if (a.do_sample == 2 && a.method == SUBSPEC_VERIFY_EXACT) {
+  if ((a.do_sample == 2 || a.acceptance == 1) && a.method == SUBSPEC_VERIFY_EXACT) {
     e = a.dtype == SUBSPEC_BF16 ? launch_sample_walk<__nv_bfloat16>(ka, a.batch, st)
                                 : launch_sample_walk<__half>(ka, a.batch, st);
     return cuda_check(e);

@@ -86,6 +86,7 @@ class VerifyWorkspace:
         self._out_dev = torch.zeros(cur, dtype=torch.uint8, device=self.device)
         self._out_host = torch.zeros(cur, dtype=torch.uint8).pin_memory()
         self.uniforms = torch.zeros(B * N, dtype=torch.float32, device=self.device)
+        self.accept_uniforms = torch.zeros(B * N, dtype=torch.float32, device=self.device)  # residual acceptance
         need = C.c_size_t(0)
         _lib.check(_lib.lib().subspec_verify_scratch_bytes(B, N, C.byref(need)), "subspec_verify_scratch_bytes")
         self.scratch = torch.empty(need.value + 256, dtype=torch.uint8, device=self.device)
@@ -139,8 +140,10 @@ class VerifyWorkspace:
     # -- launch ---------------------------------------------------------------------
     def run(self, logits: torch.Tensor, *, input_kind: int, method: int, gate: int = _lib.GATE_PROB,
             threshold: float = 0.0, window: int = 1, eos: Optional[int] = None, do_sample: bool = False,
-            temperature: float = 1.0, top_p: float = 1.0, top_k: int = 0) -> None:
-        """Launch the fused kernel on the current stream.  `logits` is [batch, rows, vocab] on this device."""
+            temperature: float = 1.0, top_p: float = 1.0, top_k: int = 0,
+            draft_logits: Optional[torch.Tensor] = None, draft_temperature: float = 1.0) -> None:
+        """Launch the fused kernel on the current stream.  `logits` is [batch, rows, vocab] on this device.
+        With `draft_logits` (same shape and dtype) the sampled exact walk uses residual acceptance."""
         B, N = self.batch, self.max_nodes
         if logits.dim() != 3 or logits.shape[0] != B:
             raise ValueError(f"logits must be [batch={B}, rows, vocab], got {tuple(logits.shape)}")
@@ -161,6 +164,18 @@ class VerifyWorkspace:
         a.top_k = int(top_k)
         a.temperature, a.top_p = float(temperature), float(top_p)
         a.uniforms = self.uniforms.data_ptr()
+        if draft_logits is not None:
+            if draft_logits.shape != logits.shape or draft_logits.dtype != logits.dtype or \
+                    draft_logits.device != self.device:
+                raise ValueError("draft_logits must match logits in shape, dtype and device")
+            if draft_logits.stride(2) != 1:
+                draft_logits = draft_logits.contiguous()
+            a.acceptance = 1
+            a.draft_logits = draft_logits.data_ptr()
+            a.draft_seq_stride, a.draft_row_stride = int(draft_logits.stride(0)), int(draft_logits.stride(1))
+            a.draft_temperature = float(draft_temperature)
+            a.accept_uniforms = self.accept_uniforms.data_ptr()
+            self._keepalive_draft = draft_logits
         a.method, a.gate = int(method), int(gate)
         a.threshold, a.window = float(threshold), int(window)
         a.eos = -1 if eos is None else int(eos)
@@ -482,13 +497,20 @@ def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logit
                         eos_token_id: Optional[int], logits_processor=None, do_sample: bool = False,
                         skip_nodes=0, verify_method: str = "exact", verify_kwargs: Optional[dict] = None,
                         uniforms: Optional[torch.Tensor] = None, workspace: Optional[VerifyWorkspace] = None,
-                        log_diagnostics: bool = False) -> List[VerifyOutput]:
+                        log_diagnostics: bool = False, draft_logits: Optional[torch.Tensor] = None,
+                        accept_uniforms: Optional[torch.Tensor] = None) -> List[VerifyOutput]:
     """Verify `len(trees)` independent draft trees against `logits` [batch, rows, vocab] in one launch.
 
     Per sequence the result equals the reference's `verify_tree` on
     `logits[b:b+1]` (tree_verify.py:7-163).  `verify_method="exact+lossy"` returns, per sequence, the pair
     (exact result, lossy result) of the two calls a step that verifies greedily and then lossily makes, from
     one pass over the logits; it needs logits for every tree node.
+
+    `verify_kwargs={"acceptance": "residual", "draft_temperature": T}` with `draft_logits` [batch, rows, vocab]
+    (an extension, not in the reference): sampled verification accepts child c of a context with probability
+    min(1, p'(x_c) / q(x_c)) in list order, p' being the filtered target distribution from which q is
+    subtracted (and the rest renormalised) after every rejection; the bonus token is drawn from p'.
+    `accept_uniforms` [batch, nodes] are the uniforms of the accept tests, `uniforms` those of the draws.
     """
     method = _method_code(verify_method)
     vk = dict(verify_kwargs or {})
@@ -520,8 +542,23 @@ def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logit
     sample_mode = 0
     if do_sample:
         sample_mode = 2 if (method == _lib.VERIFY_EXACT and not vk.get("sample_all_nodes", False)) else 1
+    acceptance = str(vk.get("acceptance", "match") or "match").strip().lower()
+    if acceptance not in ("match", "residual"):
+        raise ValueError(f"Unsupported acceptance: {acceptance!r} (supported: 'match', 'residual')")
+    if acceptance == "residual":
+        if not do_sample or method != _lib.VERIFY_EXACT or draft_logits is None:
+            raise ValueError("residual acceptance needs do_sample=True, the exact/stochastic method and draft_logits")
+        draft_logits = draft_logits.to(device)
+        if accept_uniforms is None:
+            ws.accept_uniforms.uniform_()
+        else:
+            au = torch.as_tensor(accept_uniforms, dtype=torch.float32, device=device)
+            ws.accept_uniforms.view(B, ws.max_nodes)[:, :au.shape[1]].copy_(au)
+    else:
+        draft_logits = None
     ws.run(logits, input_kind=_lib.IN_LOGITS, method=method, gate=gate, threshold=threshold, window=window,
-           eos=eos_token_id, do_sample=sample_mode, temperature=temperature, top_p=top_p, top_k=top_k)
+           eos=eos_token_id, do_sample=sample_mode, temperature=temperature, top_p=top_p, top_k=top_k,
+           draft_logits=draft_logits, draft_temperature=float(vk.get("draft_temperature", 1.0)))
     out = ws.fetch()
     results: List[Any] = []
     for b in range(B):

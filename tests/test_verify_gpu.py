@@ -423,3 +423,49 @@ def test_stochastic_walk_samples_only_where_it_stands(cuda_lib, vocab, nodes, dt
                 assert t_lazy[b, u] == -1
         accepted += lazy[b].accept_len
     assert accepted > 0
+
+
+@pytest.mark.parametrize("vocab,nodes,dtype,temperature,top_k,top_p,draft_t", [
+    (4099, 24, torch.bfloat16, 1.0, 0, 1.0, 1.0), (32000, 32, torch.float16, 0.8, 0, 0.9, 1.2),
+    (152064, 20, torch.bfloat16, 1.0, 50, 0.9, 1.0)])
+def test_residual_acceptance(cuda_lib, vocab, nodes, dtype, temperature, top_k, top_p, draft_t):
+    """verify_kwargs={'acceptance': 'residual'}: accept child c with probability min(1, p'(x)/q(x)), subtract q
+    from p' after a rejection, draw the bonus from p'.  Against the fp64 restatement (no reference counterpart)."""
+    from transformers.generation.logits_process import (LogitsProcessorList, TemperatureLogitsWarper,
+                                                        TopKLogitsWarper, TopPLogitsWarper)
+    B = 8
+    gen = torch.Generator().manual_seed(31 + nodes)
+    sts = [synthetic.random_tree(nodes, 8, 4, vocab, gen) for _ in range(B)]
+    target = torch.stack([synthetic.verify_logits(st, vocab, gen, dtype=dtype, sigma=2.0, boost=11.0) for st in sts])
+    # a draft that resembles the target, with its own noise, and that also likes the drafted tokens
+    draft = (target.float() * 0.7 + torch.randn(target.shape, generator=gen) * 1.0).to(dtype)
+    u_draw = torch.rand(B, nodes, generator=gen)
+    u_acc = torch.rand(B, nodes, generator=gen)
+    procs = LogitsProcessorList()
+    if temperature != 1.0:
+        procs.append(TemperatureLogitsWarper(temperature))
+    if top_k:
+        procs.append(TopKLogitsWarper(top_k=top_k))
+    if top_p < 1.0:
+        procs.append(TopPLogitsWarper(top_p=top_p))
+    res = verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=target.cuda(),
+                              eos_token_id=None, logits_processor=procs, do_sample=True, verify_method="stochastic",
+                              verify_kwargs={"acceptance": "residual", "draft_temperature": draft_t},
+                              draft_logits=draft.cuda(), uniforms=u_draw, accept_uniforms=u_acc)
+    checked = accepted = rejections_then_accept = 0
+    for b, st in enumerate(sts):
+        r, margin = vo.residual_walk(logits=target[b], draft_logits=draft[b], token_ids=st.token_ids.tolist(),
+                                     children=st.children(), accept_uniforms=u_acc[b].tolist(),
+                                     uniforms=u_draw[b].tolist(), temperature=temperature, top_p=top_p, top_k=top_k,
+                                     draft_temperature=draft_t)
+        if margin > 1e-4:  # no accept test or draw within rounding of its threshold
+            assert res[b].sampled_tokens.squeeze(0).tolist() == r.tokens, (b, margin)
+            assert res[b].hidden_indices.tolist() == r.hidden
+            assert (res[b].total_len, res[b].accept_len) == (r.total_len, r.accept_len)
+            checked += 1
+            accepted += r.accept_len
+    assert checked >= B // 2 and accepted > 0
+    with pytest.raises(ValueError):  # residual acceptance needs the draft's logits
+        verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=target.cuda(),
+                            eos_token_id=None, logits_processor=procs, do_sample=True, verify_method="stochastic",
+                            verify_kwargs={"acceptance": "residual"})
