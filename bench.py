@@ -358,9 +358,9 @@ def extra_stochastic(device, peak_gbs):
     ws.set_trees(flats)
     ws.uniforms.uniform_(generator=gen)
 
-    def timed(mode):
+    def timed(mode, draft=None):
         ms_ = _time_ms(lambda: ws.run(logits, input_kind=_lib.IN_LOGITS, method=_lib.VERIFY_EXACT, do_sample=mode,
-                                      temperature=1.0, top_p=0.9), iters=5, warm=2)
+                                      temperature=1.0, top_p=0.9, draft_logits=draft), iters=5, warm=2)
         return ms_, ws.fetch()
 
     # every decoded row draws its target (what the lossy verifier needs): all 2.49 GB are read
@@ -386,6 +386,17 @@ def extra_stochastic(device, peak_gbs):
                                                      float(visited.mean()), "most_contexts_in_a_sequence":
                                                      int(visited.max()),
                                                      "accepted_per_sequence": float(res["out_meta"][:, 1].mean())}
+    # residual (p - q) acceptance on the same boosted inputs, with draft logits that resemble the target's
+    draft = torch.empty_like(logits)
+    for b in range(B):
+        draft[b] = (logits[b].float() * 0.7 + torch.randn(N, V, generator=gen, device=device)).to(torch.bfloat16)
+    ws.accept_uniforms.uniform_(generator=gen)
+    ms_res, res = timed(2, draft)
+    visited = (res["node_target"] >= 0).sum(axis=1)
+    out["stochastic_verify_config2_residual_boosted"] = {"ms": ms_res, "contexts_visited_per_sequence":
+                                                         float(visited.mean()), "most_contexts_in_a_sequence":
+                                                         int(visited.max()),
+                                                         "accepted_per_sequence": float(res["out_meta"][:, 1].mean())}
     return out
 
 

@@ -275,12 +275,17 @@ def verify(*, logits: torch.Tensor, token_ids: Sequence[int], children: Sequence
 def residual_walk(*, logits: torch.Tensor, draft_logits: torch.Tensor, token_ids: Sequence[int],
                   children: Sequence[Sequence[int]], accept_uniforms: Sequence[float], uniforms: Sequence[float],
                   root: int = 0, eos: Optional[int] = None, temperature: float = 1.0, top_p: float = 1.0,
-                  top_k: int = 0, draft_temperature: float = 1.0):
+                  top_k: int = 0, draft_temperature: float = 1.0, trace: Optional[dict] = None):
     """Residual (p - q) acceptance over the tree, fp64.  NOT in the reference (which samples and matches,
     classic_sd.py:111-116): this is the restatement of the rule the kernel's header states.  Returns
     (VerifyResult, margin) where margin is the smallest distance of an accept test's uniform from its
-    threshold; the bonus draws are judged separately with `sampling_margins`-style CDF distances."""
+    threshold or of a draw's uniform from a CDF edge.  `trace`, when given, counts the branches taken:
+    "accept_after_reject" (a child accepted from a distribution that already had q subtracted) and
+    "residual_bonus" (a bonus token drawn from such a distribution)."""
     n = int(logits.shape[0])
+    if trace is not None:
+        trace.setdefault("accept_after_reject", 0)
+        trace.setdefault("residual_bonus", 0)
     p_all = target_probs(logits, True, temperature, top_p, upcast=True, top_k=top_k).double()
     q_all = torch.softmax(draft_logits.double() / draft_temperature, dim=-1)
     toks, hidden = [], []
@@ -325,6 +330,9 @@ def residual_walk(*, logits: torch.Tensor, draft_logits: torch.Tensor, token_ids
                     pr = pr / z
                 else:
                     live = False
+        if trace is not None:
+            trace["accept_after_reject"] += int(got is not None and rejected and live)
+            trace["residual_bonus"] += int(got is None and rejected and live)
         if got is None:
             toks.append(draw(pr if (rejected and live) else p_all[cur], cur))
             hidden.append(cur)

@@ -589,7 +589,8 @@ def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logit
 def verify_tree(*, tree, root_ind: int, logits: torch.Tensor, sample_token_fn=None, verify_step_fn=None,
                 eos_token_id: Optional[int], logits_processor, do_sample: bool, skip_nodes: int = 0,
                 verify_method: str = "exact", verify_kwargs: Optional[dict] = None,
-                uniforms: Optional[torch.Tensor] = None):
+                uniforms: Optional[torch.Tensor] = None, draft_logits: Optional[torch.Tensor] = None,
+                accept_uniforms: Optional[torch.Tensor] = None):
     """Drop-in for the reference's `verify_tree` (tree_verify.py:7-163).
 
     `sample_token_fn` and `verify_step_fn` are accepted so call sites need not
@@ -597,10 +598,16 @@ def verify_tree(*, tree, root_ind: int, logits: torch.Tensor, sample_token_fn=No
     the accept walk and the lossy DP all happen inside the fused kernel.  With
     `do_sample=True` the per-node draw is the inverse-CDF pick for `uniforms[u]`
     (drawn on the device when not supplied) instead of `torch.multinomial`.
+    `draft_logits` [rows, vocab] and `accept_uniforms` [nodes] serve
+    `verify_kwargs={"acceptance": "residual"}` (see `verify_tree_batched`).
     """
+    if draft_logits is not None and draft_logits.dim() == 2:
+        draft_logits = draft_logits.unsqueeze(0)
+    if accept_uniforms is not None:
+        accept_uniforms = torch.as_tensor(accept_uniforms).reshape(1, -1)
     res = verify_tree_batched(trees=[tree], root_inds=[int(root_ind)], logits=logits, eos_token_id=eos_token_id,
                               logits_processor=logits_processor, do_sample=do_sample, skip_nodes=int(skip_nodes),
                               verify_method=verify_method, verify_kwargs=verify_kwargs,
                               uniforms=None if uniforms is None else torch.as_tensor(uniforms).reshape(1, -1),
-                              log_diagnostics=True)
+                              log_diagnostics=True, draft_logits=draft_logits, accept_uniforms=accept_uniforms)
     return res[0].as_tuple()

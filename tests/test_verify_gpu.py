@@ -452,19 +452,30 @@ def test_residual_acceptance(cuda_lib, vocab, nodes, dtype, temperature, top_k, 
                               eos_token_id=None, logits_processor=procs, do_sample=True, verify_method="stochastic",
                               verify_kwargs={"acceptance": "residual", "draft_temperature": draft_t},
                               draft_logits=draft.cuda(), uniforms=u_draw, accept_uniforms=u_acc)
-    checked = accepted = rejections_then_accept = 0
+    checked = accepted = 0
+    trace = {"accept_after_reject": 0, "residual_bonus": 0}
     for b, st in enumerate(sts):
+        tr = {}
         r, margin = vo.residual_walk(logits=target[b], draft_logits=draft[b], token_ids=st.token_ids.tolist(),
                                      children=st.children(), accept_uniforms=u_acc[b].tolist(),
                                      uniforms=u_draw[b].tolist(), temperature=temperature, top_p=top_p, top_k=top_k,
-                                     draft_temperature=draft_t)
+                                     draft_temperature=draft_t, trace=tr)
         if margin > 1e-4:  # no accept test or draw within rounding of its threshold
             assert res[b].sampled_tokens.squeeze(0).tolist() == r.tokens, (b, margin)
             assert res[b].hidden_indices.tolist() == r.hidden
             assert (res[b].total_len, res[b].accept_len) == (r.total_len, r.accept_len)
             checked += 1
             accepted += r.accept_len
+            for key in trace:
+                trace[key] += tr[key]
     assert checked >= B // 2 and accepted > 0
+    # the branches that set this rule apart from sample-and-match were taken
+    assert trace["accept_after_reject"] > 0 and trace["residual_bonus"] > 0, trace
+    one = verify_tree(tree=_tree_of(sts[0]), root_ind=0, logits=target[:1].cuda(), eos_token_id=None,
+                      logits_processor=procs, do_sample=True, verify_method="stochastic",
+                      verify_kwargs={"acceptance": "residual", "draft_temperature": draft_t},
+                      draft_logits=draft[0].cuda(), uniforms=u_draw[0], accept_uniforms=u_acc[0])
+    assert one[0].squeeze(0).tolist() == res[0].sampled_tokens.squeeze(0).tolist() and one[2][1] == res[0].accept_len
     with pytest.raises(ValueError):  # residual acceptance needs the draft's logits
         verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=target.cuda(),
                             eos_token_id=None, logits_processor=procs, do_sample=True, verify_method="stochastic",
