@@ -397,6 +397,25 @@ def extra_stochastic(device, peak_gbs):
                                                          float(visited.mean()), "most_contexts_in_a_sequence":
                                                          int(visited.max()),
                                                          "accepted_per_sequence": float(res["out_meta"][:, 1].mean())}
+    del draft, logits
+    # fp32 logits (config 1's type: one 64-node tree, V = 152064) have no 16-bit histogram; the filters'
+    # boundaries are searched with counting passes over the L2-resident row
+    B1, N1 = 1, 64
+    st = synthetic.random_tree(N1, 10, 8, V, cgen)
+    t = Tree.from_arrays(st.token_ids.tolist(), st.parents.tolist())
+    tok, off, idx = flatten_tree(t, 0, limit=N1, restrict=False)
+    ws1 = get_workspace(B1, N1, device)
+    ws1.set_trees([(tok, off, idx, N1, 0)])
+    ws1.uniforms.uniform_(generator=gen)
+    # inputs cycled through a set larger than L2
+    sets = [torch.randn(B1, N1, V, generator=gen, device=device) * 2.5 for _ in range(5)]
+    for mode, name in ((1, "every_row"), (2, "walk")):
+        it = iter(range(10 ** 9))
+        ms1 = _time_ms(lambda: ws1.run(sets[next(it) % len(sets)], input_kind=_lib.IN_LOGITS,
+                                       method=_lib.VERIFY_EXACT, do_sample=mode, temperature=1.0, top_p=0.9),
+                       iters=10, warm=3)
+        out["stochastic_verify_fp32_config1_" + name] = {"ms": ms1, "rows_sampled": N1 if mode == 1 else int(
+            (ws1.fetch()["node_target"] >= 0).sum())}
     return out
 
 

@@ -341,6 +341,8 @@ struct KArgs {
   float remove_below;  // nucleus filter: drop tokens while the ascending cumulative probability is <= this
   float kD;            // residual acceptance: log2(e) / draft temperature
   int dvec_ok;         // every draft row start is 16-byte aligned
+  int targets_only;    // row sampler: write node_target and stop, no walk
+  int keep_target;     // streaming kernel: node_target already holds the (sampled) targets
 };
 
 // ---- the accept walk, run by one CTA per sequence out of shared memory -----------
@@ -738,7 +740,7 @@ __global__ void __launch_bounds__(kThreads, 4) verify_rows_kernel(const KArgs ka
   const RowStat r = s_row;
   const size_t nb = (size_t)b * a.max_nodes;
   if (threadIdx.x == 0) {
-    a.node_target[nb + u] = r.amax == INT_MAX ? 0 : r.amax;
+    if (!ka.keep_target) a.node_target[nb + u] = r.amax == INT_MAX ? 0 : r.amax;
     float ent = 0.f;
     if (SOFT) {
       const float denom = V > 1 ? logf((float)V) : 1.f;
@@ -1556,19 +1558,415 @@ __device__ bool sample_row(const KArgs& ka, SampleShared& sh, unsigned char* sme
   return true;
 }
 
+// ---- sampled targets without the 16-bit histogram: fp32 logits, or probabilities of any type --------------
+//
+// A 32-bit float has too many values to count, so the filters' boundaries are found by searching the
+// order-preserving 32-bit key space with counting passes over the row (served by L2 after the first): three
+// thresholds per pass, seventeen passes per search.  top-k: the largest key t with count(key >= t) >= k;
+// top-p: the largest key t with mass(key < t) <= (1 - top_p) Z.  Ties at the top-p boundary are cut in
+// vocabulary order (lowest indices go first), as in the 16-bit pipeline.  Probabilities come in unfiltered
+// (the reference's lossy_bottom_up_verify draws torch.multinomial(probs), lossy_tree_verify.py:75-77).
+// Slower per row than the histogram pipeline; the walk-driven kernel samples only a handful of rows.
+template <typename T>
+struct WideRow;
+template <>
+struct WideRow<float> {
+  static constexpr int E = 4;  // elements per lane and chunk
+  static __device__ __forceinline__ void load(const float* rowp, int i0, int V, bool vec_ok, float (&v)[4]) {
+    if (vec_ok && i0 + 4 <= V) {
+      const float4 q = *reinterpret_cast<const float4*>(rowp + i0);
+      v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = (i0 + j < V) ? rowp[i0 + j] : __uint_as_float(0xFFFFFFFFu);
+    }
+  }
+};
+template <typename T16>
+struct WideRow16 {
+  static constexpr int E = 8;
+  static __device__ __forceinline__ void load(const T16* rowp, int i0, int V, bool vec_ok, float (&v)[8]) {
+    unpack8_values(load8_packed<T16>(rowp, i0, V, vec_ok), v, T16());
+    if (i0 + 8 > V) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (i0 + j >= V) v[j] = __uint_as_float(0xFFFFFFFFu);
+    }
+  }
+};
+template <>
+struct WideRow<__nv_bfloat16> : WideRow16<__nv_bfloat16> {};
+template <>
+struct WideRow<__half> : WideRow16<__half> {};
+
+// Order-preserving key of a float.  Padding (the negative NaN of all ones) has key 0 and -inf has key
+// 0x007FFFFF: everything with mass has a key of at least kKeyFloor.
+__device__ __forceinline__ uint32_t key32(float x) {
+  const uint32_t b = __float_as_uint(x);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float value_of_key32(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+}
+constexpr uint32_t kKeyFloor = 0x00800000u;
+
+// sum (or maximum) over the CTA of one double per thread; every thread gets the result
+__device__ __forceinline__ double block_reduce_f64(double v, SampleShared& sh, bool is_max) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const double o = shfl_xor_f64(v, off);
+    v = is_max ? fmax(v, o) : v + o;
+  }
+  __syncthreads();  // warp_tot may still be read from a previous round
+  if (lane == 0) sh.warp_tot[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    double t = sh.warp_tot[lane];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const double o = shfl_xor_f64(t, off);
+      t = is_max ? fmax(t, o) : t + o;
+    }
+    if (lane == 0) sh.S = t;
+  }
+  __syncthreads();
+  return sh.S;
+}
+
+// exclusive prefix over the CTA (thread order) of one double per thread, and the total
+__device__ __forceinline__ double block_excl_scan_f64(double v, SampleShared& sh, double* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const double incl = warp_scan_f64(v);
+  __syncthreads();
+  if (lane == 31) sh.warp_tot[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    const double x = sh.warp_tot[lane];
+    const double xi = warp_scan_f64(x);
+    sh.warp_tot[lane] = xi - x;
+    if (lane == 31) sh.S = xi;
+  }
+  __syncthreads();
+  *total = sh.S;
+  return sh.warp_tot[warp] + incl - v;
+}
+
+template <typename T, int KIND>
+__device__ bool sample_row_wide(const KArgs& ka, SampleShared& sh, unsigned char* smem_raw, int b, int u) {
+  using Row = WideRow<T>;
+  constexpr int E = Row::E;
+  constexpr int kElems = 32 * E;       // one warp sweep
+  constexpr int kWideDepth = 16 / E;   // chunk loads a warp keeps in flight
+  float* ch_mass = reinterpret_cast<float*>(smem_raw);           // up to 2^20 / 128 = 8192 chunks
+  int* ch_cnt = reinterpret_cast<int*>(smem_raw) + (1 << 13);
+
+  const subspec_verify_args& a = ka.a;
+  const int V = a.vocab;
+  const T* rowp = reinterpret_cast<const T*>(a.logits) + (size_t)b * a.seq_stride + (size_t)u * a.row_stride;
+  const bool vec_ok = ka.vec_ok != 0;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t nb = (size_t)b * a.max_nodes;
+  const int nchunks = (V + kElems - 1) / kElems;
+  const float kT = ka.k;
+  constexpr bool kLogits = KIND == SUBSPEC_IN_LOGITS;
+
+  // f(values, first index) for every chunk of the row, kWideDepth chunk loads in flight per warp
+  auto sweep = [&](auto&& f) {
+    for (int c0 = warp; c0 < nchunks; c0 += kWideDepth * kSWarps) {
+      float v[kWideDepth][E];
+#pragma unroll
+      for (int d = 0; d < kWideDepth; ++d) {
+        const int c = c0 + d * kSWarps;
+        if (c < nchunks) Row::load(rowp, c * kElems + lane * E, V, vec_ok, v[d]);
+      }
+#pragma unroll
+      for (int d = 0; d < kWideDepth; ++d) {
+        const int c = c0 + d * kSWarps;
+        if (c < nchunks) f(v[d], c);
+      }
+    }
+  };
+
+  // ---- 1. the row maximum (logits) ----
+  uint32_t kmax = 0xFFFFFFFFu;
+  float c = 0.f;
+  if (kLogits) {
+    uint32_t m = 0;
+    sweep([&](const float(&v)[E], int) {
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const uint32_t k = key32(v[j]);
+        if (k <= 0xFF800000u) m = max(m, k);  // up to +inf; NaNs are left out
+      }
+    });
+    kmax = (uint32_t)block_reduce_f64((double)m, sh, true);
+    if (kmax < kKeyFloor) {  // nothing but -inf: no distribution to draw from
+      if (tid == 0) {
+        a.node_target[nb + u] = 0;
+        if (a.method == SUBSPEC_VERIFY_EXACT) a.node_entropy[nb + u] = 0.f;
+        a.node_rowmax[nb + u] = 0.f;
+        a.node_rowsum[nb + u] = 0.f;
+      }
+      __syncthreads();
+      return true;
+    }
+    c = value_of_key32(kmax) * kT;
+  }
+  auto weight = [&](float x) -> float { return kLogits ? ex2f(fmaf(x, kT, -c)) : x; };
+
+  // Largest key t in [lo, hi] for which pred_of(counts) holds, given that it holds at lo and is monotone
+  // (true below, false above).  measure(v, t0, t1, t2, acc) adds a chunk's contribution for three thresholds.
+  auto search = [&](uint32_t lo, uint32_t hi, auto&& measure, auto&& holds) -> uint32_t {
+    uint64_t good = lo, bad = (uint64_t)hi + 1;  // holds at good, fails at bad (or bad is past the range)
+    while (bad - good > 1) {
+      const uint64_t span = bad - good;
+      uint32_t t[3];
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        uint64_t x = good + (span * (uint64_t)(j + 1)) / 4;
+        if (x <= good) x = good + 1;
+        if (x >= bad) x = bad - 1;
+        t[j] = (uint32_t)x;
+      }
+      float acc[3] = {0.f, 0.f, 0.f};
+      sweep([&](const float(&v)[E], int) { measure(v, t, acc); });
+      double tot[3];
+#pragma unroll
+      for (int j = 0; j < 3; ++j) tot[j] = block_reduce_f64((double)acc[j], sh, false);
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        if (holds(tot[j])) {
+          if ((uint64_t)t[j] > good) good = t[j];
+        } else {
+          if ((uint64_t)t[j] < bad) bad = t[j];
+        }
+      }
+    }
+    return (uint32_t)good;
+  };
+
+  // ---- 2. top-k: everything below the k-th largest value goes, ties with it stay ----
+  uint32_t kk = kKeyFloor;
+  if (kLogits && a.top_k > 0 && a.top_k < V) {
+    const double want = (double)a.top_k;
+    const uint32_t kth = search(
+        0u, kmax,
+        [&](const float(&v)[E], const uint32_t(&t)[3], float(&acc)[3]) {
+#pragma unroll
+          for (int j = 0; j < E; ++j) {
+            const uint32_t k = key32(v[j]);
+            const bool counted = k != 0u && k <= 0xFF800000u;  // padding and NaNs are no candidates
+#pragma unroll
+            for (int q = 0; q < 3; ++q) acc[q] += (counted && k >= t[q]) ? 1.f : 0.f;
+          }
+        },
+        [&](double n) { return n >= want; });
+    kk = max(kth, kKeyFloor);
+  }
+
+  // ---- 3. the denominator over what top-k left ----
+  double Z;
+  {
+    float acc = 0.f;
+    sweep([&](const float(&v)[E], int) {
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const uint32_t k = key32(v[j]);
+        acc += (k >= kk && k <= kmax) ? weight(v[j]) : 0.f;
+      }
+    });
+    Z = block_reduce_f64((double)acc, sh, false);
+  }
+
+  // ---- 4. top-p: drop the ascending prefix whose cumulative probability is <= 1 - top_p, keep the largest ----
+  uint32_t kb = kk;   // smallest key that (partly) survives
+  int tie_cut = 0;    // of the elements tied at kb, those from this vocabulary index on survive
+  if (kLogits && ka.remove_below > 0.f) {
+    const double thrZ = (double)ka.remove_below * Z;
+    kb = search(
+        kk, kmax,
+        [&](const float(&v)[E], const uint32_t(&t)[3], float(&acc)[3]) {
+#pragma unroll
+          for (int j = 0; j < E; ++j) {
+            const uint32_t k = key32(v[j]);
+            const float w = (k >= kk && k <= kmax) ? weight(v[j]) : 0.f;
+#pragma unroll
+            for (int q = 0; q < 3; ++q) acc[q] += k < t[q] ? w : 0.f;
+          }
+        },
+        [&](double m) { return m <= thrZ; });
+    // at the boundary: mass strictly below, the number of ties, how many of them go
+    float below = 0.f;
+    sweep([&](const float(&v)[E], int cidx) {
+      int n = 0;
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const uint32_t k = key32(v[j]);
+        below += (k >= kk && k < kb) ? weight(v[j]) : 0.f;
+        n += k == kb;
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) n += __shfl_xor_sync(0xffffffffu, n, off);
+      if (lane == 0) ch_cnt[cidx] = n;
+    });
+    const double mass_below = block_reduce_f64((double)below, sh, false);  // its barriers publish ch_cnt
+    const int per = (nchunks + kSThreads - 1) / kSThreads;
+    const int c0 = min(tid * per, nchunks), c1 = min(c0 + per, nchunks);
+    int local = 0;
+    for (int cc = c0; cc < c1; ++cc) local += ch_cnt[cc];
+    double n_b_d;
+    const double before = block_excl_scan_f64((double)local, sh, &n_b_d);
+    const int n_b = (int)n_b_d;
+    const float e_b = weight(value_of_key32(kb));
+    int r = 0;
+    if (thrZ >= mass_below) r = e_b > 0.f ? (int)fmin(floor((thrZ - mass_below) / (double)e_b), 2.0e9) : n_b;
+    r = min(r, kb == kmax ? n_b - 1 : n_b);
+    r = max(r, 0);
+    if (tid == 0) sh.tie_cut = 0;
+    __syncthreads();
+    if (r > 0) {
+      // the r-th tie in vocabulary order (1-based): the cut sits right behind it
+      if ((int)before < r && r <= (int)before + local) {
+        int seen = (int)before, cstar = c0;
+        for (int cc = c0; cc < c1; ++cc) {
+          if (seen + ch_cnt[cc] >= r) {
+            cstar = cc;
+            break;
+          }
+          seen += ch_cnt[cc];
+        }
+        sh.cstar = cstar;
+        sh.rank = r - seen;  // which tie inside that chunk
+      }
+      __syncthreads();
+      if (warp == 0) {
+        const int cstar = sh.cstar, want = sh.rank;
+        float v[E];
+        Row::load(rowp, cstar * kElems + lane * E, V, vec_ok, v);
+        int n = 0;
+#pragma unroll
+        for (int j = 0; j < E; ++j) n += key32(v[j]) == kb;
+        int seen = warp_scan_i32(n) - n;
+#pragma unroll
+        for (int j = 0; j < E; ++j)
+          if (key32(v[j]) == kb) {
+            ++seen;
+            if (seen == want) sh.tie_cut = cstar * kElems + lane * E + j + 1;
+          }
+      }
+      __syncthreads();
+    }
+    tie_cut = sh.tie_cut;
+  }
+
+  // ---- 5. the draw: inverse CDF over the survivors in vocabulary order ----
+  auto kept = [&](float x, int idx) -> float {
+    const uint32_t k = key32(x);
+    const bool in = k <= kmax && (k > kb || (k == kb && k >= kKeyFloor && idx >= tie_cut));
+    return in ? weight(x) : 0.f;
+  };
+  sweep([&](const float(&v)[E], int cidx) {
+    float m = 0.f;
+#pragma unroll
+    for (int j = 0; j < E; ++j) m += kept(v[j], cidx * kElems + lane * E + j);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m += __shfl_xor_sync(0xffffffffu, m, off);
+    if (lane == 0) ch_mass[cidx] = m;
+  });
+  if (tid == 0) {
+    sh.first = kSThreads;
+    sh.last_nz = -1;
+  }
+  __syncthreads();
+  const int per = (nchunks + kSThreads - 1) / kSThreads;
+  const int c0 = min(tid * per, nchunks), c1 = min(c0 + per, nchunks);
+  double local = 0.0;
+  for (int cc = c0; cc < c1; ++cc) local += (double)ch_mass[cc];
+  double Zs;
+  const double lbase = block_excl_scan_f64(local, sh, &Zs);
+  const double target = (double)a.uniforms[nb + u] * Zs;
+  if (local > 0.0) {
+    if (lbase + local > target) atomicMin(&sh.first, tid);
+    atomicMax(&sh.last_nz, tid);
+  }
+  __syncthreads();
+  const bool pick_last = sh.first == kSThreads;
+  const int Lt = pick_last ? max(sh.last_nz, 0) : sh.first;
+  if (tid == Lt) {
+    double cum = lbase, cbase = lbase;
+    int cstar = c0;
+    for (int cc = c0; cc < c1; ++cc) {
+      const double cm = (double)ch_mass[cc];
+      if (cm > 0.0) {
+        cstar = cc;
+        cbase = cum;
+        if (!pick_last && cum + cm > target) break;
+      }
+      cum += cm;
+    }
+    sh.cstar = min(cstar, nchunks - 1);
+    sh.cbase = cbase;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int cstar = sh.cstar;
+    const int i0 = cstar * kElems + lane * E;
+    float v[E], m[E];
+    Row::load(rowp, i0, V, vec_ok, v);
+    double lsum = 0.0;
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+      m[j] = kept(v[j], i0 + j);
+      lsum += (double)m[j];
+    }
+    const double eincl = warp_scan_f64(lsum);
+    double run = sh.cbase + eincl - lsum;
+    int hit = -1, last = -1;
+#pragma unroll
+    for (int j = 0; j < E; ++j)
+      if (m[j] > 0.f) {
+        last = lane * E + j;
+        run += (double)m[j];
+        if (hit < 0 && run > target) hit = lane * E + j;
+      }
+    const uint32_t hits = __ballot_sync(0xffffffffu, hit >= 0);
+    const uint32_t any = __ballot_sync(0xffffffffu, last >= 0);
+    int within;
+    if (hits && !pick_last)
+      within = __shfl_sync(0xffffffffu, hit, __ffs(hits) - 1);
+    else
+      within = any ? __shfl_sync(0xffffffffu, last, 31 - __clz(any)) : 0;
+    if (lane == 0) {
+      a.node_target[nb + u] = min(cstar * kElems + within, V - 1);
+      if (a.method == SUBSPEC_VERIFY_EXACT) a.node_entropy[nb + u] = 0.f;
+      a.node_rowmax[nb + u] = c;
+      a.node_rowsum[nb + u] = (float)Zs;
+    }
+  }
+  __syncthreads();
+  return true;
+}
+
 // One CTA per decoded row; the CTA that finishes a sequence's last row runs the walk (lossy DP on sampled
 // targets, or the exact walk when every row's target is wanted).
-template <typename T>
+template <typename T, int KIND>
 __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const KArgs ka) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ SampleShared sh;
+  constexpr bool kWide = sizeof(T) == 4 || KIND == SUBSPEC_IN_PROBS;
   const subspec_verify_args& a = ka.a;
   const int row = blockIdx.x;
   const int b = row / a.max_nodes;
   const int u = row - b * a.max_nodes;
   const int n_rows = a.n_rows[b];
   if (u >= n_rows) return;
-  if (!sample_row<T>(ka, sh, smem_raw, b, u)) return;
+  if constexpr (kWide) {
+    if (!sample_row_wide<T, KIND>(ka, sh, smem_raw, b, u)) return;
+  } else {
+    if (!sample_row<T>(ka, sh, smem_raw, b, u)) return;
+  }
+  if (ka.targets_only) return;  // the streaming kernel that follows takes the targets from node_target
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -1636,10 +2034,11 @@ __device__ __forceinline__ double block_sum_f64(double v, SampleShared& sh) {
 // (tree_verify.py:61-104 with classic_sd.py:111-116 draws at the context it stands on) -- by one CTA per
 // sequence that alternates the row pipeline with one step of the exact walk.  A sequence touches a
 // handful of its rows instead of all of them.
-template <typename T>
+template <typename T, int KIND>
 __global__ void __launch_bounds__(kSThreads, 1) verify_sample_walk_kernel(const KArgs ka) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ SampleShared sh;
+  constexpr bool kWide = sizeof(T) == 4 || KIND == SUBSPEC_IN_PROBS;  // no histogram pipeline, no residual mode
   __shared__ int s_cur, s_state;  // context to sample next; 1 = walk on, 2 = sample the bonus, 0 = done
   __shared__ int s_dec, s_pick;   // residual acceptance: the accepted child (-1: rejected); the bonus drawn
   __shared__ float s_a, s_zr, s_dmax;  // residual p' ~ max(p - a q, 0) / zr; maximum of the draft row
@@ -1656,8 +2055,11 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_walk_kernel(const 
   int64_t* out_hid = a.out_hidden + (size_t)b * a.max_out;
   const int max_out = a.max_out;
   const int64_t eos = a.eos;
-  int L = 0, acc = 0, total = 0, bonus = -1, cur = 0;
+  // (thread 0's walk state lives in shared memory: registers are short around the row pipeline)
+  __shared__ int s_walk[5];
+  int &L = s_walk[0], &acc = s_walk[1], &total = s_walk[2], &bonus = s_walk[3], &cur = s_walk[4];
   if (threadIdx.x == 0) {
+    L = 0, acc = 0, total = 0, bonus = -1;
     cur = a.root[b];
     if (cur < 0 || cur >= n_rows) {
       flag(a.dev_status, SUBSPEC_DEV_BAD_ROOT);
@@ -1672,10 +2074,14 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_walk_kernel(const 
     const int state = s_state, ctx = s_cur;
     int tgt = -1;
     if (ctx < n_rows) {
-      if (!sample_row<T>(ka, sh, smem_raw, b, ctx)) return;  // reported through dev_status
-      tgt = a.node_target[nb + ctx];                         // written inside this CTA, before its last barrier
+      if constexpr (kWide) {
+        if (!sample_row_wide<T, KIND>(ka, sh, smem_raw, b, ctx)) return;
+      } else {
+        if (!sample_row<T>(ka, sh, smem_raw, b, ctx)) return;  // reported through dev_status
+      }
+      tgt = a.node_target[nb + ctx];  // written inside this CTA, before its last barrier
     }
-    if (a.acceptance == 1 && state == 1 && ctx < n_rows) {
+    if constexpr (!kWide) if (a.acceptance == 1 && state == 1 && ctx < n_rows) {
       // ---- residual acceptance at this context (every branch below is taken by the whole CTA) ----
       const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
       const int V = a.vocab;
@@ -1993,12 +2399,12 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_walk_kernel(const 
   }
 }
 
-template <typename T>
+template <typename T, int KIND>
 cudaError_t launch_sample_walk(const KArgs& ka, int batch, cudaStream_t st) {
-  cudaError_t e = cudaFuncSetAttribute(verify_sample_walk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)kSampleSmem);
+  cudaError_t e = cudaFuncSetAttribute(verify_sample_walk_kernel<T, KIND>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSampleSmem);
   if (e != cudaSuccess) return e;
-  verify_sample_walk_kernel<T><<<batch, kSThreads, kSampleSmem, st>>>(ka);
+  verify_sample_walk_kernel<T, KIND><<<batch, kSThreads, kSampleSmem, st>>>(ka);
   return cudaGetLastError();
 }
 
@@ -2028,13 +2434,31 @@ cudaError_t launch_rows(const KArgs& ka, int grid, size_t smem, cudaStream_t st)
   return cudaGetLastError();
 }
 
-template <typename T>
+template <typename T, int KIND>
 cudaError_t launch_sample(const KArgs& ka, int rows, cudaStream_t st) {
-  cudaError_t e = cudaFuncSetAttribute(verify_sample_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)kSampleSmem);
+  cudaError_t e = cudaFuncSetAttribute(verify_sample_rows_kernel<T, KIND>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSampleSmem);
   if (e != cudaSuccess) return e;
-  verify_sample_rows_kernel<T><<<rows, kSThreads, kSampleSmem, st>>>(ka);
+  verify_sample_rows_kernel<T, KIND><<<rows, kSThreads, kSampleSmem, st>>>(ka);
   return cudaGetLastError();
+}
+
+// the two sampling kernels by element type and input kind
+template <bool WALK>
+cudaError_t launch_sampler(const KArgs& ka, int n, cudaStream_t st) {
+  const bool probs = ka.a.input_kind == SUBSPEC_IN_PROBS;
+#define SUBSPEC_SAMPLER(T, KIND) \
+  (WALK ? launch_sample_walk<T, KIND>(ka, n, st) : launch_sample<T, KIND>(ka, n, st))
+  switch (ka.a.dtype) {
+    case SUBSPEC_F32:
+      return probs ? SUBSPEC_SAMPLER(float, SUBSPEC_IN_PROBS) : SUBSPEC_SAMPLER(float, SUBSPEC_IN_LOGITS);
+    case SUBSPEC_BF16:
+      return probs ? SUBSPEC_SAMPLER(__nv_bfloat16, SUBSPEC_IN_PROBS)
+                   : SUBSPEC_SAMPLER(__nv_bfloat16, SUBSPEC_IN_LOGITS);
+    default:
+      return probs ? SUBSPEC_SAMPLER(__half, SUBSPEC_IN_PROBS) : SUBSPEC_SAMPLER(__half, SUBSPEC_IN_LOGITS);
+  }
+#undef SUBSPEC_SAMPLER
 }
 
 // Dynamic shared memory: the TMA ring while streaming, reused for the walk's tree arrays afterwards.
@@ -2074,15 +2498,21 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
       !a.node_rowmax || !a.node_rowsum || !a.node_exact_after || !a.node_best_len || !a.node_best_next ||
       !a.scratch)
     return SUBSPEC_EINVAL;
+  // fp32 logits and probabilities go through the sampler without the 16-bit histogram
+  const bool wide = a.dtype == SUBSPEC_F32 || a.input_kind == SUBSPEC_IN_PROBS;
   if (a.do_sample) {
-    // sampled targets: 16-bit logits; exact (sample-and-match) walk or the lossy DP on the filtered distribution
-    if (a.dtype == SUBSPEC_F32 || a.input_kind != SUBSPEC_IN_LOGITS) return SUBSPEC_EUNSUPPORTED;
+    // sampled targets: the exact (sample-and-match) walk, or the lossy DP on the processed distribution
     if (!a.uniforms || !(a.temperature > 0.0) || !(a.top_p >= 0.0) || a.top_k < 0) return SUBSPEC_EINVAL;
     if (a.acceptance != 0 && a.acceptance != 1) return SUBSPEC_EINVAL;
     if (a.acceptance == 1) {  // residual acceptance: the exact walk, with the draft's logits of the same nodes
-      if (a.method != SUBSPEC_VERIFY_EXACT) return SUBSPEC_EUNSUPPORTED;
+      if (a.method != SUBSPEC_VERIFY_EXACT || wide) return SUBSPEC_EUNSUPPORTED;
       if (!a.draft_logits || !a.accept_uniforms || !(a.draft_temperature > 0.0)) return SUBSPEC_EINVAL;
     }
+    const bool filtered = a.top_k > 0 || a.top_p < 1.0;
+    // probabilities are drawn from as they are (lossy_tree_verify.py:75-77)
+    if (a.input_kind == SUBSPEC_IN_PROBS && (filtered || a.temperature != 1.0)) return SUBSPEC_EUNSUPPORTED;
+    // the lossy gates of a wide row come from the streaming kernel, which knows the temperature but no filter
+    if (wide && a.method != SUBSPEC_VERIFY_EXACT && filtered) return SUBSPEC_EUNSUPPORTED;
   } else if (a.acceptance != 0) {
     return SUBSPEC_EINVAL;
   }
@@ -2121,15 +2551,20 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
   int rc = cuda_check(cudaMemsetAsync(a.scratch, 0, ticket_bytes(a.batch, a.max_nodes), st));
   if (rc) return rc;
   cudaError_t e;
-  if ((a.do_sample == 2 || a.acceptance == 1) && a.method == SUBSPEC_VERIFY_EXACT) {
-    e = a.dtype == SUBSPEC_BF16 ? launch_sample_walk<__nv_bfloat16>(ka, a.batch, st)
-                                : launch_sample_walk<__half>(ka, a.batch, st);
-    return cuda_check(e);
-  }
+  ka.targets_only = 0;
+  ka.keep_target = 0;
+  if ((a.do_sample == 2 || a.acceptance == 1) && a.method == SUBSPEC_VERIFY_EXACT)
+    return cuda_check(launch_sampler<true>(ka, a.batch, st));
+  if (a.do_sample && !(wide && a.method != SUBSPEC_VERIFY_EXACT))
+    return cuda_check(launch_sampler<false>(ka, (int)rows, st));
   if (a.do_sample) {
-    e = a.dtype == SUBSPEC_BF16 ? launch_sample<__nv_bfloat16>(ka, (int)rows, st)
-                                : launch_sample<__half>(ka, (int)rows, st);
-    return cuda_check(e);
+    // wide rows, lossy DP: draw the targets first, then stream the rows for entropies and child
+    // probabilities and run the DP on the targets already in node_target
+    ka.targets_only = 1;
+    e = launch_sampler<false>(ka, (int)rows, st);
+    if (e != cudaSuccess) return cuda_check(e);
+    ka.targets_only = 0;
+    ka.keep_target = 1;
   }
   const int grid = (int)(rows * splits);
   const size_t smem = kernel_smem_bytes(a.max_nodes);

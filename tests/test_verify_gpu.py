@@ -480,3 +480,151 @@ def test_residual_acceptance(cuda_lib, vocab, nodes, dtype, temperature, top_k, 
         verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=target.cuda(),
                             eos_token_id=None, logits_processor=procs, do_sample=True, verify_method="stochastic",
                             verify_kwargs={"acceptance": "residual"})
+
+
+def _wide_targets(B, nodes):
+    from subspec_b200.verify import get_workspace
+    return get_workspace(B, nodes, torch.device("cuda", 0)).fetch()["node_target"]
+
+
+@pytest.mark.parametrize("vocab,nodes,temperature,top_k,top_p", [
+    (4099, 20, 1.0, 0, 0.9), (32000, 16, 0.7, 50, 0.95), (152064, 6, 1.0, 0, 1.0), (50, 12, 1.3, 8, 0.5),
+    (32000, 10, 1.0, 200, 1.0)])
+def test_stochastic_fp32_logits(cuda_lib, vocab, nodes, temperature, top_k, top_p):
+    """fp32 logits have no 16-bit histogram: the filters' boundaries come from searches over the key space.
+    Same semantics, same oracle, same margins as the 16-bit pipeline; both the every-row and the walk-driven
+    launch."""
+    from transformers.generation.logits_process import (LogitsProcessorList, TemperatureLogitsWarper,
+                                                        TopKLogitsWarper, TopPLogitsWarper)
+    B = 3
+    sts, logits, uniforms = _sampled_case(900 + nodes, B, nodes, vocab, torch.float32, 2.5)
+    procs = LogitsProcessorList()
+    if temperature != 1.0:
+        procs.append(TemperatureLogitsWarper(temperature))
+    if top_k:
+        procs.append(TopKLogitsWarper(top_k=top_k))
+    if top_p < 1.0:
+        procs.append(TopPLogitsWarper(top_p=top_p))
+    kw = dict(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(), eos_token_id=None,
+              logits_processor=procs, do_sample=True, verify_method="stochastic", uniforms=uniforms)
+    res = verify_tree_batched(verify_kwargs={"sample_all_nodes": True}, **kw)
+    targets = _wide_targets(B, nodes).copy()
+    checked = 0
+    for b, st in enumerate(sts):
+        probs = vo.target_probs(logits[b], True, temperature, top_p, upcast=True, top_k=top_k)
+        want = vo.target_tokens(probs, True, uniforms[b].tolist())
+        margins = vo.sampling_margins(logits[b], temperature, top_p, uniforms[b].tolist(), top_k=top_k)
+        for u in range(st.n):
+            if margins[u][0] > 1e-3 and margins[u][1] > 1e-6:
+                assert int(targets[b, u]) == want[u], (b, u, margins[u])
+                checked += 1
+        r = vo.exact_walk(target=targets[b, :st.n].tolist(), token_ids=st.token_ids.tolist(), children=st.children(),
+                          root=0, n_rows=st.n, eos=None)
+        assert res[b].sampled_tokens.squeeze(0).tolist() == r.tokens
+        assert res[b].hidden_indices.tolist() == r.hidden
+    assert checked >= B * nodes * 8 // 10
+    lazy = verify_tree_batched(**kw)  # only the contexts the walk stands on
+    visited = _wide_targets(B, nodes)
+    for b in range(B):
+        assert lazy[b].sampled_tokens.tolist() == res[b].sampled_tokens.tolist()
+        assert lazy[b].hidden_indices.tolist() == res[b].hidden_indices.tolist()
+        seen = visited[b] >= 0
+        assert 1 <= int(seen.sum()) <= res[b].accept_len + 1
+        assert (visited[b][seen] == targets[b][seen]).all()
+
+
+def test_stochastic_fp32_ties_and_masks(cuda_lib):
+    """fp32 rows made of a few distinct values: the top-p boundary falls inside long runs of ties (cut in
+    vocabulary order), -inf masks carry no mass, top-k keeps every tie of the k-th value."""
+    from transformers.generation.logits_process import LogitsProcessorList, TopKLogitsWarper, TopPLogitsWarper
+    vocab, nodes, B = 3000, 12, 2
+    gen = torch.Generator().manual_seed(78)
+    sts = [synthetic.random_tree(nodes, 6, 4, vocab, gen) for _ in range(B)]
+    levels = torch.tensor([float("-inf"), -3.0, -1.0, 0.25, 0.5, 1.0, 2.5, 4.0])
+    weights = torch.tensor([0.3, 0.2, 0.1, 0.1, 0.15, 0.1, 0.04, 0.01])
+    idx = torch.multinomial(weights, B * nodes * vocab, replacement=True, generator=gen).reshape(B, nodes, vocab)
+    logits = levels[idx].to(torch.float32)
+    logits[:, :, 7] = 4.0
+    uniforms = torch.rand(B, nodes, generator=gen)
+    checked = 0
+    for top_k, top_p in ((0, 0.999), (0, 0.8), (0, 0.5), (0, 0.05), (100, 1.0), (400, 0.7)):
+        procs = LogitsProcessorList(([TopKLogitsWarper(top_k=top_k)] if top_k else []) +
+                                    ([TopPLogitsWarper(top_p=top_p)] if top_p < 1.0 else []))
+        verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
+                            eos_token_id=None, logits_processor=procs, do_sample=True, verify_method="stochastic",
+                            uniforms=uniforms, verify_kwargs={"sample_all_nodes": True})
+        targets = _wide_targets(B, nodes)
+        for b, st in enumerate(sts):
+            probs = vo.target_probs(logits[b], True, 1.0, top_p, upcast=True, top_k=top_k)
+            want = vo.target_tokens(probs, True, uniforms[b].tolist())
+            margins = vo.sampling_margins(logits[b], 1.0, top_p, uniforms[b].tolist(), top_k=top_k)
+            for u in range(st.n):
+                assert float(logits[b, u, int(targets[b, u])]) > float("-inf")
+                if margins[u][0] > 1e-3 and margins[u][1] > 1e-6:
+                    assert int(targets[b, u]) == want[u], (top_k, top_p, b, u, margins[u])
+                    checked += 1
+    assert checked >= B * nodes * 4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("gate,threshold,window", [("entropy", 0.3, 1), ("prob", 0.05, 0)])
+def test_lossy_on_probabilities_with_sampled_targets(cuda_lib, dtype, gate, threshold, window):
+    """lossy_bottom_up_verify(probs=..., do_sample=True): the reference draws torch.multinomial(probs)
+    (lossy_tree_verify.py:75-77); here the draw is the inverse-CDF pick for injected uniforms, the gates use
+    the probabilities as given."""
+    vocab, nodes = 4099, 24
+    gen = torch.Generator().manual_seed(41)
+    checked = accepted = 0
+    for trial in range(4):
+        st = synthetic.random_tree(nodes, 6, 4, vocab, gen)
+        logits = synthetic.verify_logits(st, vocab, gen, dtype=torch.float32, sigma=2.0, boost=14.0)
+        probs = torch.softmax(logits, dim=-1).to(dtype)
+        u = torch.rand(nodes, generator=gen)
+        sampled, hidden, acc = lossy_bottom_up_verify(
+            probs=probs.cuda(), token_ids=st.token_ids, parent_indices=st.parents, children_lists=st.children(),
+            root_index=0, eos_token_id=None, do_sample=True, threshold=threshold, window_size=window,
+            threshold_method=gate, uniforms=u)
+        cdf = probs.double().cumsum(-1)
+        tot = cdf[:, -1:]
+        pick_margin = float(((cdf - u.double().unsqueeze(1) * tot).abs() / tot).min())
+        r = vo.verify(logits=probs.float(), token_ids=st.token_ids.tolist(), children=st.children(), method="lossy",
+                      do_sample=True, uniforms=u.tolist(), threshold=threshold, window=window,
+                      threshold_method=gate, input_is_probs=True)
+        if pick_margin > 1e-6 and r.min_gate_margin > 1e-5:
+            assert sampled.tolist() == r.tokens, (trial, pick_margin)
+            assert hidden.tolist() == r.hidden and acc == r.accept_len
+            checked += 1
+            accepted += acc
+    assert checked >= 3 and accepted > 0
+
+
+@pytest.mark.parametrize("gate,threshold", [("entropy", 0.25), ("prob", 0.02)])
+def test_lossy_on_sampled_targets_fp32_logits(cuda_lib, gate, threshold):
+    """fp32 logits, lossy verification with sampled targets and a temperature (no top-k / top-p: those need the
+    16-bit pipeline for the gates and are refused)."""
+    from transformers.generation.logits_process import LogitsProcessorList, TemperatureLogitsWarper, TopPLogitsWarper
+    B, vocab, nodes, temperature = 4, 4099, 24, 0.8
+    gen = torch.Generator().manual_seed(43)
+    sts = [synthetic.random_tree(nodes, 6, 4, vocab, gen) for _ in range(B)]
+    logits = torch.stack([synthetic.verify_logits(st, vocab, gen, dtype=torch.float32, sigma=2.0, boost=14.0)
+                          for st in sts])
+    uniforms = torch.rand(B, nodes, generator=gen)
+    kw = {"threshold_method": gate, "threshold": threshold, "window_size": 1}
+    res = verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
+                              eos_token_id=None, logits_processor=LogitsProcessorList([TemperatureLogitsWarper(temperature)]),
+                              do_sample=True, verify_method="lossy", verify_kwargs=kw, uniforms=uniforms)
+    checked = 0
+    for b, st in enumerate(sts):
+        r = vo.verify(logits=logits[b], token_ids=st.token_ids.tolist(), children=st.children(), method="lossy",
+                      do_sample=True, temperature=temperature, uniforms=uniforms[b].tolist(), threshold=threshold,
+                      window=1, threshold_method=gate, upcast=True)
+        margins = vo.sampling_margins(logits[b], temperature, 1.0, uniforms[b].tolist())
+        if min(m[1] for m in margins) > 1e-6 and r.min_gate_margin > 1e-5:
+            assert res[b].sampled_tokens.squeeze(0).tolist() == r.tokens, b
+            assert res[b].hidden_indices.tolist() == r.hidden and res[b].accept_len == r.accept_len
+            checked += 1
+    assert checked >= B // 2
+    with pytest.raises(ValueError):
+        verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
+                            eos_token_id=None, logits_processor=LogitsProcessorList([TopPLogitsWarper(top_p=0.9)]),
+                            do_sample=True, verify_method="lossy", verify_kwargs=kw, uniforms=uniforms)
