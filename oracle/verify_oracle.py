@@ -21,7 +21,11 @@ What follows what (reference file:line):
 Sampling: the reference draws with torch.multinomial from the global RNG, which
 cannot be reproduced from a per-node uniform.  Here (and in the CUDA path) the
 draw for node u is the inverse-CDF pick for an injected uniform u01[u]: the
-first vocabulary index whose cumulative probability exceeds u01[u].
+first vocabulary index whose cumulative probability exceeds u01[u].  That mode is
+pinned too: tests/golden/sampled_cases.json holds what the reference returned with
+do_sample=True when its torch.multinomial was replaced by this pick (its warpers,
+softmax, walk and lossy verifier untouched).  residual_walk has no counterpart in
+the reference: parity unpinned for that function alone.
 """
 from __future__ import annotations
 

@@ -105,6 +105,16 @@ def config1_case(seed: int, *, vocab: int = 152064, n_nodes: int = 64, max_depth
     return tree, verify_logits(tree, vocab, gen, dtype=dtype, peaked=peaked)
 
 
+def sampled_case(seed: int, n_nodes: int, max_depth: int, max_branch: int, vocab: int, dtype: torch.dtype):
+    """Input of one sampled verification: a tree, its [n, vocab] target logits (drafted tokens likely enough
+    to be drawn now and then) and one uniform per node."""
+    gen = torch.Generator().manual_seed(seed)
+    tree = random_tree(n_nodes, max_depth, max_branch, vocab, gen)
+    logits = verify_logits(tree, vocab, gen, dtype=dtype, peaked=True, sigma=2.0)
+    uniforms = torch.rand(n_nodes, generator=gen)
+    return tree, logits, uniforms
+
+
 def random_page_table(batch: int, pages_per_seq: int, gen: torch.Generator) -> torch.Tensor:
     """[batch, pages_per_seq] int32: a random permutation of the pool's pages split across sequences."""
     perm = torch.randperm(batch * pages_per_seq, generator=gen)

@@ -2,7 +2,7 @@
 
 Usage (only where a read-only checkout of NYCU-EDgeAi/subspec is available):
 
-    python tests/golden/make_golden.py --reference /path/to/subspec [--only verify|expand|kv]
+    python tests/golden/make_golden.py --reference /path/to/subspec [--only verify|sampled|expand|kv|lossy_unit]
 
 The reference is imported, never copied.  Two third-party modules it imports but
 does not need on this path (`nvtx`, `prettytable`) are replaced by throw-away
@@ -11,6 +11,7 @@ stubs in a temporary directory.  Inputs come from `subspec_b200.synthetic`
 depend on the RNG stream.  Outputs written:
 
     verify_cases.json / verify_small.npz   verify_tree (exact, lossy) results
+    sampled_cases.json                     verify_tree with do_sample=True and injected uniforms
     lossy_unit_cases.json                  every call made by the reference's tests/test_lossy_tree_verify.py
     expand_cases.json / expand_small.npz   _topk_flatten / Tree / TreeMaskCache results
     kv_cases.json                          KvCachePool.reorder_cache_with_offset checksums
@@ -185,6 +186,110 @@ def gen_verify(ref, out_dir: Path):
     print(f"verify: {len(cases)} cases, {len(skipped)} depend on 16-bit probability rounding: {skipped}")
 
 
+class InjectedDraws:
+    """While active, torch.multinomial / Tensor.multinomial (the reference's only source of randomness on this
+    path: classic_sd.py:112, tree_verify.py:99, lossy_tree_verify.py:76) return the inverse-CDF pick for the
+    uniform injected for that node instead of a draw from the global RNG.  Everything else the reference
+    runs is its own code: warpers, softmax, dtype handling, walk, bonus-token rule."""
+
+    def __init__(self, uniforms):
+        self.u = [float(x) for x in uniforms]
+        self.rows = None  # the probabilities _sample_token returned, [N, V]: a 1-D draw is located among them
+
+    def remember(self, probs):
+        self.rows = probs.reshape(-1, probs.shape[-1]).detach().cpu()
+        return probs
+
+    def _draw(self, probs, num_samples=1, *a, **k):
+        from oracle import verify_oracle as vo
+        assert num_samples == 1
+        if probs.dim() == 1:
+            hits = (self.rows == probs.detach().cpu()).all(dim=-1).nonzero().reshape(-1)
+            assert hits.numel() == 1, "cannot tell which node this distribution belongs to"
+            return torch.tensor([vo.inverse_cdf_pick(probs, self.u[int(hits[0])])], dtype=torch.long)
+        return torch.tensor([[vo.inverse_cdf_pick(probs[i], self.u[i])] for i in range(probs.shape[0])],
+                            dtype=torch.long)
+
+    def __enter__(self):
+        self._saved = (torch.multinomial, torch.Tensor.multinomial)
+        torch.multinomial = self._draw
+        torch.Tensor.multinomial = lambda t, *a, **k: self._draw(t, *a, **k)
+        return self
+
+    def __exit__(self, *exc):
+        torch.multinomial, torch.Tensor.multinomial = self._saved
+
+
+def gen_sampled(ref, out_dir: Path):
+    """do_sample=True through the unmodified reference with injected uniforms: sample-and-match walks and the
+    lossy verifier on sampled targets, with the reference's own warper list (generators/base.py:42-64)."""
+    sys.path.insert(0, str(ROOT))
+    from oracle import verify_oracle as vo
+    cases = []
+    specs = []
+    k = 0
+    for vocab, nodes, depth, branch in [(50, 12, 4, 3), (1000, 24, 6, 4), (4099, 24, 6, 4), (32000, 20, 6, 4),
+                                        (152064, 12, 5, 3)]:
+        for dtype in ("float32", "bfloat16", "float16"):
+            for temperature, top_k, top_p in [(1.0, 0, 0.9), (0.7, 50, 0.95), (1.3, 0, 1.0), (1.0, 20, 1.0)]:
+                if top_k >= vocab:
+                    top_k = vocab // 4
+                specs.append(dict(vocab=vocab, nodes=nodes, depth=depth, branch=branch, dtype=dtype,
+                                  temperature=temperature, top_k=top_k, top_p=top_p, method="exact", kwargs={},
+                                  seed=7000 + k))
+                k += 1
+        # the lossy verifier on sampled targets: 16-bit logits with filters, fp32 with a temperature only
+        for dtype, temperature, top_k, top_p in [("bfloat16", 1.0, 0, 0.9), ("float16", 0.8, 64, 0.95),
+                                                 ("float32", 0.8, 0, 1.0), ("float32", 1.0, 0, 1.0)]:
+            for kwargs in ({"threshold_method": "entropy", "threshold": 0.3, "window_size": 1},
+                           {"threshold_method": "prob", "threshold": 0.05, "window_size": 0}):
+                if vocab > 40000:
+                    continue
+                specs.append(dict(vocab=vocab, nodes=nodes, depth=depth, branch=branch, dtype=dtype,
+                                  temperature=temperature, top_k=min(top_k, vocab // 4), top_p=top_p, method="lossy",
+                                  kwargs=kwargs, seed=7000 + k))
+                k += 1
+    for sp in specs:
+        tree, logits, uniforms = synthetic.sampled_case(sp["seed"], sp["nodes"], sp["depth"], sp["branch"],
+                                                        sp["vocab"], DT[sp["dtype"]])
+        procs = ref["gb"].GeneratorBase._get_logits_processor(None, temperature=sp["temperature"],
+                                                              top_k=sp["top_k"], top_p=sp["top_p"])
+        rt = ref_tree(ref["ct"], tree)
+        ref["wandb_logger"].clear_log_data()
+        with InjectedDraws(uniforms.tolist()) as inj:
+            toks, hidden, (total, acc) = ref["tv"].verify_tree(
+                tree=rt, root_ind=0, logits=logits.unsqueeze(0),
+                sample_token_fn=lambda *a, **kw: inj.remember(ref["gb"].GeneratorBase._sample_token(None, *a, **kw)),
+                verify_step_fn=lambda *a, **kw: ref["csd"].ClassicSDGeneratorBase._verify_step(None, *a, **kw),
+                eos_token_id=None, logits_processor=procs, do_sample=True, skip_nodes=0,
+                verify_method=sp["method"], verify_kwargs=sp["kwargs"])
+        exp = {"tokens": toks.squeeze(0).tolist(), "hidden": hidden.tolist(), "total_len": int(total),
+               "accept_len": int(acc)}
+        # the restatement in the reference's arithmetic (probabilities in the logits' type) and in fp32
+        okw = dict(logits=logits, token_ids=tree.token_ids.tolist(), children=tree.children(), method=sp["method"],
+                   do_sample=True, temperature=sp["temperature"], top_p=sp["top_p"], top_k=sp["top_k"],
+                   uniforms=uniforms.tolist(), threshold=float(sp["kwargs"].get("threshold", 0.0)),
+                   window=int(sp["kwargs"].get("window_size", 1)),
+                   threshold_method=sp["kwargs"].get("threshold_method", "prob"))
+        as_ref = vo.verify(upcast=False, **okw)
+        up = vo.verify(upcast=True, **okw)
+        same = lambda r: {"tokens": r.tokens, "hidden": r.hidden, "total_len": r.total_len,
+                          "accept_len": r.accept_len} == exp
+        margins = vo.sampling_margins(logits, sp["temperature"], sp["top_p"], uniforms.tolist(), top_k=sp["top_k"])
+        used = range(tree.n) if sp["method"] == "lossy" else sorted(set(exp["hidden"]))
+        cases.append(dict(name=f"sampled/{sp['method']}_v{sp['vocab']}_{sp['dtype']}_{sp['seed']}", **sp,
+                          uniforms=[float(x) for x in uniforms.tolist()], expected=exp,
+                          oracle_agrees=bool(same(as_ref)), upcast_agrees=bool(same(up)),
+                          boundary_margin=min(margins[u][0] for u in used),
+                          pick_margin=min(margins[u][1] for u in used),
+                          gate_margin=None if up.min_gate_margin == float("inf") else up.min_gate_margin))
+    (out_dir / "sampled_cases.json").write_text(json.dumps({"torch": torch.__version__, "cases": cases}, indent=1))
+    n = len(cases)
+    print(f"sampled: {n} cases; restatement agrees on {sum(c['oracle_agrees'] for c in cases)}, the fp32 upcast on "
+          f"{sum(c['upcast_agrees'] for c in cases)}; accepted tokens in total "
+          f"{sum(c['expected']['accept_len'] for c in cases)}")
+
+
 def gen_lossy_unit(ref, ref_root: str, out_dir: Path):
     """Run the reference's own unit tests of the lossy verifier and record every call they make
     to lossy_bottom_up_verify: inputs, outputs and the wandb_logger metrics left behind."""
@@ -321,6 +426,8 @@ def main():
         gen_expand(ref, HERE)
     if args.only in (None, "kv"):
         gen_kv(ref, HERE)
+    if args.only in (None, "sampled"):
+        gen_sampled(ref, HERE)
     if args.only in (None, "lossy_unit"):
         gen_lossy_unit(ref, args.reference, HERE)
 

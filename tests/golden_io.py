@@ -76,3 +76,30 @@ def _expand_small():
 def expand_logits(case, step: int) -> torch.Tensor:
     """[1, leaves, vocab] draft logits of one depth step, in the case's dtype."""
     return torch.from_numpy(_expand_small()[f"{case['name']}/logits{step}"]).to(DT[case["dtype"]])
+
+
+@lru_cache(maxsize=None)
+def sampled_cases():
+    return json.loads((GOLDEN / "sampled_cases.json").read_text())["cases"]
+
+
+def sampled_input(case):
+    """(SynthTree, logits [n, V] in the case's dtype) of one sampled-verification case; the uniforms the
+    reference ran with are stored in the case itself."""
+    tree, logits, _ = synthetic.sampled_case(case["seed"], case["nodes"], case["depth"], case["branch"],
+                                             case["vocab"], DT[case["dtype"]])
+    return tree, logits
+
+
+def sampled_processors(case):
+    """The warper list the reference builds for these parameters (generators/base.py:42-64)."""
+    from transformers.generation.logits_process import (LogitsProcessorList, TemperatureLogitsWarper,
+                                                        TopKLogitsWarper, TopPLogitsWarper)
+    procs = LogitsProcessorList()
+    if case["temperature"] != 1.0:
+        procs.append(TemperatureLogitsWarper(case["temperature"]))
+    if case["top_k"]:
+        procs.append(TopKLogitsWarper(top_k=case["top_k"]))
+    if case["top_p"] < 1.0:
+        procs.append(TopPLogitsWarper(top_p=case["top_p"]))
+    return procs

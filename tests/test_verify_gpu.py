@@ -628,3 +628,29 @@ def test_lossy_on_sampled_targets_fp32_logits(cuda_lib, gate, threshold):
         verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
                             eos_token_id=None, logits_processor=LogitsProcessorList([TopPLogitsWarper(top_p=0.9)]),
                             do_sample=True, verify_method="lossy", verify_kwargs=kw, uniforms=uniforms)
+
+
+def test_golden_sampled_verification(cuda_lib):
+    """The reference's own results with do_sample=True (its warpers, softmax, walk and lossy verifier; its
+    torch.multinomial replaced by the inverse-CDF pick for injected uniforms) against the CUDA path: every case
+    whose outcome does not hang on 16-bit rounding of the probabilities (the kernel computes them in fp32) or
+    on a uniform within rounding of a CDF edge."""
+    checked = {"exact": 0, "lossy": 0}
+    accepted = 0
+    for c in golden_io.sampled_cases():
+        decided = (c["upcast_agrees"] and c["boundary_margin"] > 1e-3 and c["pick_margin"] > 1e-6 and
+                   (c["gate_margin"] is None or c["gate_margin"] > 1e-5))
+        if not decided:
+            continue
+        tree, logits = golden_io.sampled_input(c)
+        modes = [{}] if c["method"] == "lossy" else [{}, {"sample_all_nodes": True}]
+        for extra in modes:
+            toks, hidden, (total, acc) = verify_tree(
+                tree=_tree_of(tree), root_ind=0, logits=logits.unsqueeze(0).cuda(), eos_token_id=None,
+                logits_processor=golden_io.sampled_processors(c), do_sample=True, verify_method=c["method"],
+                verify_kwargs={**c["kwargs"], **extra}, uniforms=torch.tensor(c["uniforms"]))
+            got = dict(tokens=toks.squeeze(0).tolist(), hidden=hidden.tolist(), total_len=total, accept_len=acc)
+            assert got == c["expected"], (c["name"], extra)
+        checked[c["method"]] += 1
+        accepted += c["expected"]["accept_len"]
+    assert checked["exact"] >= 45 and checked["lossy"] >= 20 and accepted > 40, (checked, accepted)
