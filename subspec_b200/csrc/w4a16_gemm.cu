@@ -70,7 +70,6 @@ struct GemmArgs {
   int64_t y_stride;
 };
 
-
 // try_wait with a suspend-time hint: the warp sleeps in hardware (up to the hint) instead of coming back
 // to poll, and the polls of the waiting roles stop competing with the dequantisation for issue slots.
 __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
@@ -107,7 +106,6 @@ __device__ __forceinline__ bool elect_one() {
       : "=r"(pred));
   return pred != 0;
 }
-
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
@@ -406,8 +404,6 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
         tc_commit(&acc_full);
       else
         mbar_arrive(&acc_full);  // nothing issued by this warp
-      if (me == 0) {
-      }
     }
     __syncwarp();
   } else if (warp >= kDeqWarp0) {
@@ -461,8 +457,6 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
       }
       pr.advance(1, Rr);
       pa.advance(kDeqGroups, R);
-    }
-    if (threadIdx.x == 32 * kDeqWarp0) {
     }
     // ---- epilogue ----
     if (wait_or_abort(&acc_full, 0, abort_flag) && !*abort_flag) {
@@ -565,7 +559,7 @@ bool make_plan(int M, int N, int K, Plan* p) {
   int splits = kNumSMs / p->tiles;
   if (splits < 1) splits = 1;
   if (splits > p->kblocks) splits = p->kblocks;
-  if (splits > 64) splits = 64;
+  if (splits > 16) splits = 16;  // the split-K tail reads the partials eight at a time (28 splits: a tail of 3.8 us)
   // the last CTA of a tile reads splits x Mpad x 128 partial sums alone: keep that under 1 MB
   if (splits * p->Mpad > 2048) splits = 2048 / p->Mpad;
   // every split gets at least one K block
@@ -605,7 +599,6 @@ bool make_plan(int M, int N, int K, Plan* p) {
 }  // namespace subspec
 
 using namespace subspec;
-
 
 extern "C" int subspec_w4a16_packed_bytes(int32_t n, int32_t k, size_t* bytes) {
   if (!bytes || n < kTileN || n % kTileN || k < kBlockK || k % kBlockK) return SUBSPEC_EUNSUPPORTED;
