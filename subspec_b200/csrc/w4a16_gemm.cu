@@ -56,6 +56,7 @@ constexpr int kMaxIssuers = 4;
 constexpr int kDeqWarp0 = kIssuerWarp0 + kMaxIssuers;
 constexpr int kThreads = 32 * (kDeqWarp0 + kDeqWarps);
 constexpr int kMaxM = 256;
+constexpr int kEarlyChunks = 2;       // packed chunks requested before the prologue's barrier (the ring holds at least two)
 constexpr int kMaxRing = 8;           // packed ring, in chunks of kDeqGroups K blocks (one TMA copy each)
 constexpr int kChunkBytes = kDeqGroups * kRawBytes;
 
@@ -299,6 +300,18 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
     mbar_init_fence();
     s_abort = 0;
     s_last = 0;
+    // The packed-weight stream starts here, before the CTA has its tensor memory and has met at the barrier
+    // below: the first chunks' trip from HBM (about a microsecond) runs beside the rest of the prologue.
+    // Only kEarlyChunks of them: the copy unit serves an SM's requests in order, and the first activation
+    // copy must not queue behind a whole ring of packed data.  This thread is also the producer of that
+    // ring and carries on after the barrier.
+    const unsigned char* src = g.wpk + ((size_t)tile * g.kblocks + kb0) * kRawBytes;
+    const int nchunks = (nkb + kDeqGroups - 1) / kDeqGroups;
+    for (int c = 0; c < min(nchunks, kEarlyChunks); ++c) {
+      const uint32_t bytes = (uint32_t)(min(kDeqGroups, nkb - c * kDeqGroups) * kRawBytes);
+      mbar_expect_tx(&raw_full[c], bytes);
+      bulk_g2s(raw_ring + (size_t)c * kChunkBytes, src + (size_t)c * kChunkBytes, bytes, &raw_full[c]);
+    }
   }
   if (warp == 2) {
     tmem_alloc(&s_tmem, ncols);
@@ -315,10 +328,13 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
     // ---- TMA producer, packed weights: one copy per chunk of four K blocks (a single thread gets a
     // copy out every few hundred cycles at best, which 4.5 KB copies would turn into the bound) ----
     if (lane == 0) {
+      // the first kEarlyChunks went out in the prologue
       RingPos p{0, 0};
-      const unsigned char* src = g.wpk + ((size_t)tile * g.kblocks + kb0) * kRawBytes;
+      p.advance(kEarlyChunks, Rr);
       const int nchunks = (nkb + kDeqGroups - 1) / kDeqGroups;
-      for (int c = 0; c < nchunks; ++c, src += kChunkBytes) {
+      const unsigned char* src =
+          g.wpk + ((size_t)tile * g.kblocks + kb0) * kRawBytes + (size_t)kEarlyChunks * kChunkBytes;
+      for (int c = kEarlyChunks; c < nchunks; ++c, src += kChunkBytes) {
         if (c >= Rr && !wait_or_abort(&raw_empty[p.s], (uint32_t)p.ph ^ 1u, abort_flag)) break;
         const uint32_t bytes = (uint32_t)(min(kDeqGroups, nkb - c * kDeqGroups) * kRawBytes);
         mbar_expect_tx(&raw_full[p.s], bytes);
