@@ -161,6 +161,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+// the same load without the wait: the registers are valid after tmem_wait_ld()
+__device__ __forceinline__ void tmem_ld16_async(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes, 8-row atoms
 // 1024 bytes apart.  Bits: [0,14) address >> 4; [16,30) leading byte offset >> 4 (unused for
@@ -496,13 +506,27 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
         const int col = c0;  // tokens c0 .. c0 + 15 sit in columns c0 .. c0 + 15 of every accumulator
         float v[16];
         tmem_ld16(tmem_d + ((uint32_t)(ew * 32) << 16) + (uint32_t)col, v);
-        for (int is = 0; is < min(g.issuers, nkb); ++is)
-          for (int a = (is == 0 ? 1 : 0); a < share; ++a) {
+        for (int is = 0; is < min(g.issuers, nkb); ++is) {
+          // the issuer's other accumulators: two loads in flight where its share has that many left
+          int a = (is == 0 ? 1 : 0);
+          const uint32_t tis = tmem_d + ((uint32_t)(ew * 32) << 16) + (uint32_t)(col + is * n_own * g.acc_stride);
+          for (; a + 1 < share; a += 2) {
+            uint32_t w0[16], w1[16];
+            tmem_ld16_async(tis + (uint32_t)(a * g.acc_stride), w0);
+            tmem_ld16_async(tis + (uint32_t)((a + 1) * g.acc_stride), w1);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(w0[j]);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(w1[j]);
+          }
+          if (a < share) {
             float w[16];
-            tmem_ld16(tmem_d + ((uint32_t)(ew * 32) << 16) + (uint32_t)(col + (is * n_own + a) * g.acc_stride), w);
+            tmem_ld16(tis + (uint32_t)(a * g.acc_stride), w);
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] += w[j];
           }
+        }
         if (g.splits == 1) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
