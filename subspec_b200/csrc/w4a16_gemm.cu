@@ -607,7 +607,7 @@ bool make_plan(int M, int N, int K, Plan* p) {
   int splits = kNumSMs / p->tiles;
   if (splits < 1) splits = 1;
   if (splits > p->kblocks) splits = p->kblocks;
-  if (splits > 16) splits = 16;  // the split-K tail reads the partials eight at a time (28 splits: a tail of 3.8 us)
+  if (splits > 8) splits = 8;  // the split-K tail reads the partials eight at a time: one round (28 splits: a tail of 3.8 us)
   // the last CTA of a tile reads splits x Mpad x 128 partial sums alone: keep that under 1 MB
   if (splits * p->Mpad > 2048) splits = 2048 / p->Mpad;
   // every split gets at least one K block
