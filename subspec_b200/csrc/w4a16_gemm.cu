@@ -69,6 +69,7 @@ struct GemmArgs {
   uint32_t* dev_status;
   int M, Mpad, N, K, kblocks, splits, ring_raw, b_slots, b_blocks, b_shift, acc_n, acc_stride, issuers;
   int64_t y_stride;
+  int cluster;  // the splits of a tile form a thread-block cluster (1, splits, 1): partial sums meet in shared memory
 };
 
 // try_wait with a suspend-time hint: the warp sleeps in hardware (up to the hint) instead of coming back
@@ -171,6 +172,25 @@ __device__ __forceinline__ void tmem_ld16_async(uint32_t taddr, uint32_t (&r)[16
       : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- thread-block cluster: barrier and loads from a peer CTA's shared memory ----------------
+// Every thread of every CTA of the cluster executes arrive and wait the same number of times, on every
+// path (also after an abort): the barrier has no time limit of its own.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t peer_smem(uint32_t own_addr, uint32_t rank) {
+  uint32_t d;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(d) : "r"(own_addr), "r"(rank));
+  return d;
+}
+__device__ __forceinline__ float4 ld_peer_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
 
 // Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes, 8-row atoms
 // 1024 bytes apart.  Bits: [0,14) address >> 4; [16,30) leading byte offset >> 4 (unused for
@@ -531,6 +551,11 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             if (c0 + j < g.M) g.y[(size_t)(c0 + j) * g.y_stride + n] = __float2bfloat16_rn(v[j]);
+        } else if (g.cluster) {
+          // [Mpad][128] fp32 over the rings, which nothing uses any more: every MMA has completed
+          float* part = reinterpret_cast<float*>(smem) + (size_t)c0 * kTileN + ew * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) part[(size_t)j * kTileN] = v[j];
         } else {
           float* part = g.partial + (((size_t)tile * g.splits + split) * g.Mpad + c0) * kTileN + ew * 32 + lane;
 #pragma unroll
@@ -543,8 +568,42 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
   __syncthreads();
   if (s_abort && threadIdx.x == 0) flag(g.dev_status, SUBSPEC_DEV_TIMEOUT);
 
-  // ---- split-K: the last CTA of the tile adds the partials ----
-  if (g.splits > 1 && !s_abort) {
+  // ---- split-K inside a cluster: every CTA adds its share of the outputs from all the splits' shared memory,
+  // in split order (the same bits as the path through global memory below) ----
+  if (g.cluster) {
+    cluster_arrive();  // this CTA's partial sums are written (the CTA barrier above ordered them before this)
+    cluster_wait();    // ... and so are everybody else's
+    if (!s_abort) {
+      const uint32_t own = smem_u32(smem);
+      const int total = g.M * (kTileN / 4);
+      for (int e = split * kThreads + threadIdx.x; e < total; e += g.splits * kThreads) {
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          v[u] = u < g.splits ? ld_peer_f4(peer_smem(own + (uint32_t)e * 16u, (uint32_t)u))
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          acc.x += v[u].x;
+          acc.y += v[u].y;
+          acc.z += v[u].z;
+          acc.w += v[u].w;
+        }
+        const int m = e / (kTileN / 4), c = (e - m * (kTileN / 4)) * 4;
+        __nv_bfloat16* dst = g.y + (size_t)m * g.y_stride + tile * kTileN + c;
+        dst[0] = __float2bfloat16_rn(acc.x);
+        dst[1] = __float2bfloat16_rn(acc.y);
+        dst[2] = __float2bfloat16_rn(acc.z);
+        dst[3] = __float2bfloat16_rn(acc.w);
+      }
+    }
+    cluster_arrive();  // nobody leaves while a peer may still read its shared memory
+    cluster_wait();
+  }
+
+  // ---- split-K through global memory: the last CTA of the tile adds the partials ----
+  if (g.splits > 1 && !g.cluster && !s_abort) {
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) s_last = (atomicAdd(g.ticket + tile, 1) == g.splits - 1);
@@ -643,6 +702,34 @@ bool make_plan(int M, int N, int K, Plan* p) {
   return true;
 }
 
+// How many clusters of (1, c, 1) CTAs of the GEMM kernel the device holds at once; 0 when it cannot say.
+// Asked once per device and cluster size (the kernel's footprint is one CTA per SM whatever the plan).
+int resident_clusters(int dev, int c, int smem_bytes) {
+  static int cache[64][9];  // 0 = not asked yet, -1 = asked and failed, n + 1 otherwise
+  if (dev < 0 || dev >= 64 || c < 2 || c > 8) return 0;
+  if (cache[dev][c] == 0) {
+    cudaLaunchConfig_t q = {};
+    q.gridDim = dim3(1, (unsigned)c);
+    q.blockDim = dim3(kThreads);
+    q.dynamicSmemBytes = (size_t)smem_bytes;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 1;
+    at[0].val.clusterDim.y = (unsigned)c;
+    at[0].val.clusterDim.z = 1;
+    q.attrs = at;
+    q.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, w4a16_gemm_kernel, &q) != cudaSuccess) {
+      cudaGetLastError();  // not an error of the call being served
+      cache[dev][c] = -1;
+    } else {
+      cache[dev][c] = n + 1;
+    }
+  }
+  return cache[dev][c] > 0 ? cache[dev][c] - 1 : 0;
+}
+
 }  // namespace
 }  // namespace subspec
 
@@ -736,10 +823,39 @@ extern "C" int subspec_w4a16_gemm(const subspec_w4a16_args* args, subspec_stream
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = p.smem_bytes;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  g.cluster = 0;
+  if (p.splits > 1) {
+    // Split-K inside a thread-block cluster (one cluster = the splits of a tile) when all the tiles' clusters
+    // can be resident at once: the partial sums then meet in shared memory instead of making the trip through
+    // global memory, a fence and a ticket.  Fewer splits fit more clusters of a GPC's SMs: take the largest
+    // count that leaves no tile waiting for a second wave; none does -> the path through global memory.
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int per_plan = (p.kblocks + p.splits - 1) / p.splits;
+    for (int c = p.splits; c >= 2 && !g.cluster; --c) {
+      const int per = (p.kblocks + c - 1) / c;
+      if ((p.kblocks + per - 1) / per != c) continue;  // some split would be empty
+      // what the shorter tail saves (1.5 - 2 us) is worth about six more K blocks per CTA (measured on the
+      // 3584 x 18944 shape: 74 instead of 60 K blocks per CTA cost more than the tail gave back)
+      if (per - per_plan > 6) break;
+      if (resident_clusters(dev, c, (int)p.smem_bytes) >= p.tiles) {
+        g.cluster = 1;
+        g.splits = c;
+      }
+    }
+    if (g.cluster) {
+      cfg.gridDim = dim3(p.tiles, g.splits);
+      attr[1].id = cudaLaunchAttributeClusterDimension;
+      attr[1].val.clusterDim.x = 1;
+      attr[1].val.clusterDim.y = (unsigned)g.splits;
+      attr[1].val.clusterDim.z = 1;
+      cfg.numAttrs = 2;
+    }
+  }
   return cuda_check(cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, g));
 }
