@@ -27,13 +27,15 @@
 //                        whole warp runs the loop and an elected lane issues, which keeps the
 //                        descriptors in uniform registers;
 //   warps 6-21         : epilogue, tcgen05.ld of the accumulators, sum, bf16 store (or fp32 split-K
-//                        partial + ticket: the last CTA of a tile adds the partials up).
+//                        partial: through the shared memory of a thread-block cluster formed by the
+//                        splits of a tile, or through global memory + ticket, the last CTA adding up).
 // What bounds it at these token counts is neither HBM nor the tensor core's arithmetic but instruction
 // issue: a warp gets one tcgen05.mma out every 100-200 cycles whatever its N, hence several issuing
 // warps with accumulators of their own, and the role loops keep (stage, parity) counters instead of
 // dividing by ring depths.
-// Every wait is bounded; a wait that runs out raises SUBSPEC_DEV_TIMEOUT and the CTA winds down
-// (TMEM is released on every path).  No clusters, no multicast.
+// Every mbarrier wait is bounded; a wait that runs out raises SUBSPEC_DEV_TIMEOUT and the CTA winds down
+// (TMEM is released on every path, and the cluster barriers of the split-K tail are reached on every path).
+// Clusters serve the split-K exchange only: every copy is a plain per-CTA bulk copy of this GPU's memory.
 #include <limits.h>
 
 #include "common.cuh"
