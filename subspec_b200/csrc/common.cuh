@@ -41,6 +41,11 @@ __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
 }
 
 // ---- packed fp32x2 arithmetic (sm_100: two fp32 lanes per instruction) -------------------
+// Ask L2 for `bytes` (a multiple of 16) of global memory starting at a 16-byte aligned address.
+__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
   uint64_t r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));

@@ -27,6 +27,7 @@ constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kUnroll = 4;
 constexpr int kMaxK = 32;
+constexpr int kPrefetchAhead = 6;  // iterations (16 KB each) a row's L2 prefetch runs ahead of its loads
 constexpr int kQueue = 256;  // per-warp candidate queue: one 16-byte vector per lane, 8 elements each
 
 struct Cand {
@@ -254,7 +255,18 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
 
   const int nvec = ka.vec_ok ? V / VN : 0;
   const uint4* vp = reinterpret_cast<const uint4*>(rowp);
+  // One thread asks L2 for the row a few iterations ahead of the loads (bulk prefetch, no registers, no
+  // barrier): a thread has its four loads in flight only while it waits for them, which alone leaves the
+  // SM far short of the bytes in flight that its share of the HBM bandwidth needs.
+  constexpr int kIterVecs = kThreads * kUnroll;  // 16 KB of the row per iteration
+  auto prefetch_iter = [&](int it) {
+    const int v0 = it * kIterVecs;
+    if (v0 < nvec) l2_prefetch(vp + v0, (uint32_t)(min(kIterVecs, nvec - v0) * 16));
+  };
+  if (threadIdx.x == 0)
+    for (int it = 0; it < kPrefetchAhead; ++it) prefetch_iter(it);
   for (int i0 = 0; i0 < nvec; i0 += kThreads * kUnroll) {
+    if (threadIdx.x == 0) prefetch_iter(i0 / kIterVecs + kPrefetchAhead);
     // refresh the threshold: own k-th best, and the bound the other warps have published
     {
       float t = s_pub[0];
