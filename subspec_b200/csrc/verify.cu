@@ -341,6 +341,7 @@ struct KArgs {
   float remove_below;  // nucleus filter: drop tokens while the ascending cumulative probability is <= this
   float kD;            // residual acceptance: log2(e) / draft temperature
   int dvec_ok;         // every draft row start is 16-byte aligned
+  int wide_gates;      // row sampler without the histogram: also entropy and child probabilities (lossy + filters)
   int targets_only;    // row sampler: write node_target and stop, no walk
   int keep_target;     // streaming kernel: node_target already holds the (sampled) targets
 };
@@ -1707,6 +1708,14 @@ __device__ bool sample_row_wide(const KArgs& ka, SampleShared& sh, unsigned char
         if (a.method == SUBSPEC_VERIFY_EXACT) a.node_entropy[nb + u] = 0.f;
         a.node_rowmax[nb + u] = 0.f;
         a.node_rowsum[nb + u] = 0.f;
+        if (ka.wide_gates) a.node_entropy[nb + u] = 0.f;
+      }
+      if (ka.wide_gates) {  // no distribution: every child has probability zero
+        const int* coff = a.child_off + (size_t)b * (a.max_nodes + 1);
+        for (int e = coff[u] + tid; e < coff[u + 1]; e += kSThreads) {
+          const int cn = a.child_idx[nb + e];
+          if (cn >= 0 && cn < a.n_nodes[b]) a.node_child_prob[nb + cn] = 0.f;
+        }
       }
       __syncthreads();
       return true;
@@ -1866,14 +1875,23 @@ __device__ bool sample_row_wide(const KArgs& ka, SampleShared& sh, unsigned char
     const bool in = k <= kmax && (k > kb || (k == kb && k >= kKeyFloor && idx >= tie_cut));
     return in ? weight(x) : 0.f;
   };
+  // (with the lossy gates wanted from this kernel: also T2 = sum of w * log2(w) over the survivors, for the
+  // entropy of the filtered distribution)
+  const bool gates = kLogits && ka.wide_gates != 0;
+  float t2_acc = 0.f;
   sweep([&](const float(&v)[E], int cidx) {
     float m = 0.f;
 #pragma unroll
-    for (int j = 0; j < E; ++j) m += kept(v[j], cidx * kElems + lane * E + j);
+    for (int j = 0; j < E; ++j) {
+      const float w = kept(v[j], cidx * kElems + lane * E + j);
+      m += w;
+      if (gates) t2_acc += w > 0.f ? w * fmaf(v[j], kT, -c) : 0.f;
+    }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) m += __shfl_xor_sync(0xffffffffu, m, off);
     if (lane == 0) ch_mass[cidx] = m;
   });
+  const double T2 = gates ? block_reduce_f64((double)t2_acc, sh, false) : 0.0;
   if (tid == 0) {
     sh.first = kSThreads;
     sh.last_nz = -1;
@@ -1942,6 +1960,30 @@ __device__ bool sample_row_wide(const KArgs& ka, SampleShared& sh, unsigned char
       if (a.method == SUBSPEC_VERIFY_EXACT) a.node_entropy[nb + u] = 0.f;
       a.node_rowmax[nb + u] = c;
       a.node_rowsum[nb + u] = (float)Zs;
+      if (gates) {  // entropy of the filtered distribution, normalised by ln V as the reference does
+        const float denom = V > 1 ? logf((float)V) : 1.f;
+        a.node_entropy[nb + u] = Zs > 0.0 ? (float)(0.6931471805599453 * (log2(Zs) - T2 / Zs)) / denom : 0.f;
+      }
+    }
+  }
+  if (gates) {
+    // P[u, token(c)] under the filters, for every child c of u
+    const int* coff = a.child_off + (size_t)b * (a.max_nodes + 1);
+    const int n_nodes = a.n_nodes[b];
+    const float invZ = Zs > 0.0 ? (float)(1.0 / Zs) : 0.f;
+    for (int e = coff[u] + tid; e < coff[u + 1]; e += kSThreads) {
+      const int cn = a.child_idx[nb + e];
+      if (cn < 0 || cn >= n_nodes) {
+        flag(a.dev_status, SUBSPEC_DEV_BAD_CHILD);
+        continue;
+      }
+      const int tk = a.token_ids[nb + cn];
+      float p = 0.f;
+      if (tk < 0 || tk >= V)
+        flag(a.dev_status, SUBSPEC_DEV_BAD_TOKEN);
+      else
+        p = kept(to_f32<T>(rowp[tk]), tk) * invZ;
+      a.node_child_prob[nb + cn] = p;
     }
   }
   __syncthreads();
@@ -2511,8 +2553,8 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
     const bool filtered = a.top_k > 0 || a.top_p < 1.0;
     // probabilities are drawn from as they are (lossy_tree_verify.py:75-77)
     if (a.input_kind == SUBSPEC_IN_PROBS && (filtered || a.temperature != 1.0)) return SUBSPEC_EUNSUPPORTED;
-    // the lossy gates of a wide row come from the streaming kernel, which knows the temperature but no filter
-    if (wide && a.method != SUBSPEC_VERIFY_EXACT && filtered) return SUBSPEC_EUNSUPPORTED;
+    // (the lossy gates of a wide row come from the streaming kernel, which knows the temperature; with a
+    // top-k / top-p filter on fp32 logits the sampler computes them itself)
   } else if (a.acceptance != 0) {
     return SUBSPEC_EINVAL;
   }
@@ -2553,8 +2595,13 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
   cudaError_t e;
   ka.targets_only = 0;
   ka.keep_target = 0;
+  ka.wide_gates = 0;
   if ((a.do_sample == 2 || a.acceptance == 1) && a.method == SUBSPEC_VERIFY_EXACT)
     return cuda_check(launch_sampler<true>(ka, a.batch, st));
+  if (a.do_sample && wide && a.method != SUBSPEC_VERIFY_EXACT && (a.top_k > 0 || a.top_p < 1.0)) {
+    ka.wide_gates = 1;  // fp32 logits, lossy, filtered: gates on the filtered distribution, one launch
+    return cuda_check(launch_sampler<false>(ka, (int)rows, st));
+  }
   if (a.do_sample && !(wide && a.method != SUBSPEC_VERIFY_EXACT))
     return cuda_check(launch_sampler<false>(ka, (int)rows, st));
   if (a.do_sample) {

@@ -249,6 +249,16 @@ def gen_sampled(ref, out_dir: Path):
                                   temperature=temperature, top_k=min(top_k, vocab // 4), top_p=top_p, method="lossy",
                                   kwargs=kwargs, seed=7000 + k))
                 k += 1
+    # fp32 logits, lossy, with top-k / top-p (gates on the filtered distribution)
+    k = 0
+    for vocab, nodes, depth, branch in [(1000, 24, 6, 4), (4099, 24, 6, 4), (32000, 20, 6, 4)]:
+        for temperature, top_k, top_p in [(1.0, 0, 0.9), (0.8, 64, 0.95)]:
+            for kwargs in ({"threshold_method": "entropy", "threshold": 0.3, "window_size": 1},
+                           {"threshold_method": "prob", "threshold": 0.05, "window_size": 0}):
+                specs.append(dict(vocab=vocab, nodes=nodes, depth=depth, branch=branch, dtype="float32",
+                                  temperature=temperature, top_k=top_k, top_p=top_p, method="lossy",
+                                  kwargs=kwargs, seed=8000 + k))
+                k += 1
     for sp in specs:
         tree, logits, uniforms = synthetic.sampled_case(sp["seed"], sp["nodes"], sp["depth"], sp["branch"],
                                                         sp["vocab"], DT[sp["dtype"]])

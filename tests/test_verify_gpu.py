@@ -624,10 +624,31 @@ def test_lossy_on_sampled_targets_fp32_logits(cuda_lib, gate, threshold):
             assert res[b].hidden_indices.tolist() == r.hidden and res[b].accept_len == r.accept_len
             checked += 1
     assert checked >= B // 2
-    with pytest.raises(ValueError):
-        verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
-                            eos_token_id=None, logits_processor=LogitsProcessorList([TopPLogitsWarper(top_p=0.9)]),
-                            do_sample=True, verify_method="lossy", verify_kwargs=kw, uniforms=uniforms)
+    # with top-k / top-p the gates use the filtered distribution; the sampler computes them itself
+    from transformers.generation.logits_process import TopKLogitsWarper
+    checked = accepted = 0
+    for top_k, top_p in ((0, 0.9), (64, 0.95), (200, 1.0)):
+        procs = LogitsProcessorList([TemperatureLogitsWarper(temperature)] +
+                                    ([TopKLogitsWarper(top_k=top_k)] if top_k else []) +
+                                    ([TopPLogitsWarper(top_p=top_p)] if top_p < 1.0 else []))
+        res = verify_tree_batched(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(),
+                                  eos_token_id=None, logits_processor=procs, do_sample=True, verify_method="lossy",
+                                  verify_kwargs=kw, uniforms=uniforms)
+        for b, st in enumerate(sts):
+            r = vo.verify(logits=logits[b], token_ids=st.token_ids.tolist(), children=st.children(), method="lossy",
+                          do_sample=True, temperature=temperature, top_p=top_p, top_k=top_k,
+                          uniforms=uniforms[b].tolist(), threshold=threshold, window=1, threshold_method=gate,
+                          upcast=True)
+            margins = vo.sampling_margins(logits[b], temperature, top_p, uniforms[b].tolist(), top_k=top_k)
+            if (min(m[0] for m in margins) > 1e-3 and min(m[1] for m in margins) > 1e-6 and
+                    r.min_gate_margin > 1e-5):
+                assert res[b].sampled_tokens.squeeze(0).tolist() == r.tokens, (top_k, top_p, b)
+                assert res[b].hidden_indices.tolist() == r.hidden and res[b].accept_len == r.accept_len
+                checked += 1
+                accepted += r.accept_len
+    assert checked >= 6 and accepted > 0
+    with pytest.raises(ValueError):  # probabilities in are drawn from as they are: no filter to apply
+        lossy = _lib_probs_with_filter(sts[0], logits[0])
 
 
 def test_golden_sampled_verification(cuda_lib):
@@ -654,3 +675,14 @@ def test_golden_sampled_verification(cuda_lib):
         checked[c["method"]] += 1
         accepted += c["expected"]["accept_len"]
     assert checked["exact"] >= 45 and checked["lossy"] >= 20 and accepted > 40, (checked, accepted)
+
+
+def _lib_probs_with_filter(st, logits):
+    """Probabilities in together with a nucleus filter: refused by the library."""
+    from subspec_b200 import _lib
+    from subspec_b200.verify import flatten_tree, get_workspace
+    tok, off, idx = flatten_tree(_tree_of(st), 0, limit=st.n, restrict=True)
+    ws = get_workspace(1, st.n, torch.device("cuda", 0))
+    ws.set_trees([(tok, off, idx, st.n, 0)])
+    ws.run(torch.softmax(logits, -1).unsqueeze(0).cuda(), input_kind=_lib.IN_PROBS, method=_lib.VERIFY_LOSSY,
+           gate=_lib.GATE_PROB, threshold=0.1, window=1, do_sample=1, temperature=1.0, top_p=0.9)
