@@ -418,6 +418,85 @@ __device__ void run_walk(const KArgs& ka, int b, unsigned char* smem_raw) {
   }
   __syncthreads();
 
+  if (lossy) {
+    // lossy_tree_verify.py:107-168, the reverse-index DP.  A node's (exact_after, best_len, best_next) depend
+    // on its children's only, so instead of one thread walking the indices downwards the whole CTA
+    // recomputes every node from the current values of its children until a round changes nothing: after
+    // round r every node of height <= r holds its final values (the children of a node have larger indices,
+    // so the induction is the sequential loop's), and the fixed point is the sequential result.  A tree of
+    // height h takes h + 1 rounds; one sequence alone in a launch no longer waits for a 64-step serial loop.
+    __shared__ int s_changed;
+    const bool use_entropy = a.gate == SUBSPEC_GATE_ENTROPY;
+    const double thr = a.threshold;
+    const int window = a.window > 0 ? a.window : 0;
+    for (int round = 0; round <= n_nodes; ++round) {
+      if (threadIdx.x == 0) s_changed = 0;
+      __syncthreads();
+      bool changed = false;
+      for (int u = threadIdx.x; u < n_nodes; u += blockDim.x) {
+        const int cb = w.coff[u], ce = w.coff[u + 1];
+        if (ce == cb) continue;
+        const int tgt = w.tgt[u];
+        bool has_exact = false;
+        int max_ea = 0;
+        for (int e = cb; e < ce; ++e) {
+          const int c = w.cidx[e];
+          if (w.tok[c] == tgt) {
+            has_exact = true;
+            max_ea = max(max_ea, w.ea[c]);
+          }
+        }
+        const int ea_u = has_exact ? 1 + max_ea : 0;
+        int best_c = -1, best_total = 0;
+        bool best_exact = false;
+        float best_p = -1.f;
+        const bool ent_blocks = use_entropy && ((double)w.ent[u] >= thr);
+        for (int e = cb; e < ce; ++e) {
+          const int c = w.cidx[e];
+          const bool is_exact = w.tok[c] == tgt;
+          float p = -1.f;
+          if (!is_exact) {
+            if (w.ea[c] < window) continue;
+            if (ent_blocks) continue;
+            p = w.cprob[c];
+            if (!use_entropy && (double)p < thr) continue;
+          }
+          const int tl = 1 + w.bl[c];
+          if (tl > best_total) {
+            best_c = c;
+            best_total = tl;
+            best_exact = is_exact;
+            best_p = p;
+            continue;
+          }
+          if (tl == best_total) {
+            if (is_exact && !best_exact) {
+              best_c = c;
+              best_exact = true;
+              best_p = p;
+            } else if (!is_exact && !best_exact && p > best_p) {
+              best_c = c;
+              best_p = p;
+            }
+          }
+        }
+        const int bn_u = (best_c >= 0 && best_total > 0) ? best_c : -1;
+        const int bl_u = bn_u >= 0 ? best_total : 0;
+        if (ea_u != w.ea[u] || bn_u != w.bn[u] || bl_u != w.bl[u]) {
+          w.ea[u] = ea_u;
+          w.bn[u] = bn_u;
+          w.bl[u] = bl_u;
+          changed = true;
+        }
+      }
+      if (changed) s_changed = 1;
+      __syncthreads();
+      const int again = s_changed;
+      __syncthreads();  // everybody has read the flag before the next round clears it
+      if (!again) break;
+    }
+  }
+
   if (threadIdx.x == 0) {
     const int max_out = a.max_out;
     const int64_t eos = a.eos;
@@ -479,62 +558,7 @@ __device__ void run_walk(const KArgs& ka, int b, unsigned char* smem_raw) {
         ++L;
       }
     } else {
-      // lossy_tree_verify.py:107-168 (DP) and :247-291 (walk)
-      const bool use_entropy = a.gate == SUBSPEC_GATE_ENTROPY;
-      const double thr = a.threshold;
-      const int window = a.window > 0 ? a.window : 0;
-      for (int u = n_nodes - 1; u >= 0; --u) {
-        const int cb = w.coff[u], ce = w.coff[u + 1];
-        if (ce == cb) continue;
-        const int tgt = w.tgt[u];
-        bool has_exact = false;
-        int max_ea = 0;
-        for (int e = cb; e < ce; ++e) {
-          const int c = w.cidx[e];
-          if (w.tok[c] == tgt) {
-            has_exact = true;
-            max_ea = max(max_ea, w.ea[c]);
-          }
-        }
-        if (has_exact) w.ea[u] = 1 + max_ea;
-        int best_c = -1, best_total = 0;
-        bool best_exact = false;
-        float best_p = -1.f;
-        const bool ent_blocks = use_entropy && ((double)w.ent[u] >= thr);
-        for (int e = cb; e < ce; ++e) {
-          const int c = w.cidx[e];
-          const bool is_exact = w.tok[c] == tgt;
-          float p = -1.f;
-          if (!is_exact) {
-            if (w.ea[c] < window) continue;
-            if (ent_blocks) continue;
-            p = w.cprob[c];
-            if (!use_entropy && (double)p < thr) continue;
-          }
-          const int tl = 1 + w.bl[c];
-          if (tl > best_total) {
-            best_c = c;
-            best_total = tl;
-            best_exact = is_exact;
-            best_p = p;
-            continue;
-          }
-          if (tl == best_total) {
-            if (is_exact && !best_exact) {
-              best_c = c;
-              best_exact = true;
-              best_p = p;
-            } else if (!is_exact && !best_exact && p > best_p) {
-              best_c = c;
-              best_p = p;
-            }
-          }
-        }
-        if (best_c >= 0 && best_total > 0) {
-          w.bn[u] = best_c;
-          w.bl[u] = best_total;
-        }
-      }
+      // lossy_tree_verify.py:247-291: the walk along best_next (the DP has run above, by the whole CTA)
       int ctx = root;
       while (true) {
         const int nxt = w.bn[ctx];
