@@ -119,8 +119,8 @@ SUBSPEC_API const char* subspec_last_cuda_error(void);
  *                      exp2(logit[u, t] * log2(e) / T - rowmax[u]) / rowsum[u]
  *
  * Scratch: `scratch` must hold subspec_verify_scratch_bytes() bytes, 256-byte
- * aligned.  It needs no initialisation; calls that share one scratch buffer
- * must not overlap on the GPU.
+ * aligned.  It needs no initialisation (unless `flags` says otherwise); calls
+ * that share one scratch buffer must not overlap on the GPU.
  * ---------------------------------------------------------------------- */
 typedef struct subspec_verify_args {
   uint32_t struct_size; /* sizeof(subspec_verify_args), checked */
@@ -185,7 +185,16 @@ typedef struct subspec_verify_args {
   int64_t draft_row_stride;
   double draft_temperature;     /* > 0 */
   const float* accept_uniforms; /* [batch, max_nodes], indexed by the child node */
+  uint32_t flags;               /* 0, or SUBSPEC_VERIFY_SCRATCH_CLEAN */
 } subspec_verify_args;
+
+/* The caller promises that the first 4 * batch * (max_nodes + 1) bytes of `scratch`
+ * (rounded up to 256) were zero before the first call that used the buffer, and
+ * that only subspec_verify_batched calls whose dev_status stayed clear have used
+ * it since: every such call leaves them zero, and the entry point then puts no
+ * clearing operation in front of the kernel (one launch fewer per call; it
+ * matters for a single tree, whose whole verification takes ~20 us). */
+#define SUBSPEC_VERIFY_SCRATCH_CLEAN 1u
 
 SUBSPEC_API int subspec_verify_scratch_bytes(int32_t batch, int32_t max_nodes, size_t* bytes);
 SUBSPEC_API int subspec_verify_batched(const subspec_verify_args* args, subspec_stream_t stream);

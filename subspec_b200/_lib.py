@@ -15,6 +15,7 @@ STATIC_SCRATCH_MAX_ROWS = 4096
 F32, BF16, F16 = 0, 1, 2
 IN_LOGITS, IN_PROBS = 0, 1
 VERIFY_EXACT, VERIFY_LOSSY, VERIFY_EXACT_AND_LOSSY = 0, 1, 2
+VERIFY_SCRATCH_CLEAN = 1  # SUBSPEC_VERIFY_SCRATCH_CLEAN
 GATE_PROB, GATE_ENTROPY = 0, 1
 DEV_BAD_TOKEN, DEV_BAD_CHILD, DEV_BAD_ROOT, DEV_BAD_PAGE, DEV_BAD_INDEX, DEV_TIMEOUT, DEV_HIST_OVERFLOW = 1, 2, 4, 8, 16, 32, 64
 
@@ -55,7 +56,7 @@ class VerifyArgs(C.Structure):
         ("dev_status", _vp), ("scratch", _vp), ("scratch_bytes", C.c_size_t),
         ("out2_tokens", _vp), ("out2_hidden", _vp), ("out2_meta", _vp),
         ("acceptance", _i32), ("draft_logits", _vp), ("draft_seq_stride", _i64), ("draft_row_stride", _i64),
-        ("draft_temperature", _f64), ("accept_uniforms", _vp),
+        ("draft_temperature", _f64), ("accept_uniforms", _vp), ("flags", _u32),
     ]
 
 

@@ -732,6 +732,7 @@ __global__ void __launch_bounds__(kThreads, 4) verify_rows_kernel(const KArgs ka
       __threadfence();
       const int t = atomicAdd(ka.sc.row_ticket + row, 1);
       s_flag = (t == splits - 1);
+      if (s_flag) ka.sc.row_ticket[row] = 0;  // everybody has been: left as found, zero, for the next launch
     }
     __syncthreads();
     if (!s_flag) return;
@@ -805,6 +806,7 @@ __global__ void __launch_bounds__(kThreads, 4) verify_rows_kernel(const KArgs ka
   if (threadIdx.x == 0) {
     const int t = atomicAdd(ka.sc.seq_ticket + b, 1);
     s_flag = (t == n_rows - 1);
+    if (s_flag) ka.sc.seq_ticket[b] = 0;
   }
   __syncthreads();
   if (!s_flag) return;
@@ -2038,6 +2040,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
   if (threadIdx.x == 0) {
     const int t = atomicAdd(ka.sc.seq_ticket + b, 1);
     sh.flag = (t == n_rows - 1);
+    if (sh.flag) ka.sc.seq_ticket[b] = 0;
   }
   __syncthreads();
   if (!sh.flag) return;
@@ -2614,7 +2617,11 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
   }
   ka.splits = splits;
 
-  int rc = cuda_check(cudaMemsetAsync(a.scratch, 0, ticket_bytes(a.batch, a.max_nodes), st));
+  // The tickets have to be zero; every launch leaves them so (the last arrival resets its ticket), so a caller
+  // who vouches for the buffer (SUBSPEC_VERIFY_SCRATCH_CLEAN) saves this node in front of the kernel.
+  int rc = SUBSPEC_OK;
+  if (!(a.flags & SUBSPEC_VERIFY_SCRATCH_CLEAN))
+    rc = cuda_check(cudaMemsetAsync(a.scratch, 0, ticket_bytes(a.batch, a.max_nodes), st));
   if (rc) return rc;
   cudaError_t e;
   ka.targets_only = 0;
@@ -2690,5 +2697,6 @@ extern "C" int subspec_verify_batched_static_scratch(const subspec_verify_args* 
   subspec_verify_args a = *args;
   a.scratch = g_static_scratch_ptr[dev];
   a.scratch_bytes = kStaticScratchBytes;
+  a.flags &= ~SUBSPEC_VERIFY_SCRATCH_CLEAN;  // nobody can vouch for this buffer: always cleared first
   return subspec_verify_batched(&a, stream);
 }

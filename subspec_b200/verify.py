@@ -89,7 +89,10 @@ class VerifyWorkspace:
         self.accept_uniforms = torch.zeros(B * N, dtype=torch.float32, device=self.device)  # residual acceptance
         need = C.c_size_t(0)
         _lib.check(_lib.lib().subspec_verify_scratch_bytes(B, N, C.byref(need)), "subspec_verify_scratch_bytes")
-        self.scratch = torch.empty(need.value + 256, dtype=torch.uint8, device=self.device)
+        # zeroed once: every launch leaves the ticket words at its start zero, and run() says so to the
+        # library (SUBSPEC_VERIFY_SCRATCH_CLEAN), which then puts no clearing operation in front of the kernel
+        self.scratch = torch.zeros(need.value + 256, dtype=torch.uint8, device=self.device)
+        self.scratch_clean = True  # False: the library clears the tickets itself before every launch
         self._scratch_ptr = _align(self.scratch.data_ptr(), 256)
         self._scratch_bytes = need.value
 
@@ -185,6 +188,7 @@ class VerifyWorkspace:
                      "dev_status", "out2_tokens", "out2_hidden", "out2_meta"):
             setattr(a, name, self._out_ptr(name))
         a.scratch, a.scratch_bytes = self._scratch_ptr, self._scratch_bytes
+        a.flags = _lib.VERIFY_SCRATCH_CLEAN if self.scratch_clean else 0
         self._rows = int(logits.shape[1])
         self._keepalive = logits
         stream = torch.cuda.current_stream(self.device).cuda_stream
@@ -213,6 +217,7 @@ class VerifyWorkspace:
         status = int(out["dev_status"][0])
         if status:
             self.clear_status()
+            self.scratch.zero_()  # a launch that gave up may have left tickets behind
             raise ValueError("verify kernel rejected its input: " + _lib.dev_status_text(status))
         return out
 

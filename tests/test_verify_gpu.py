@@ -686,3 +686,33 @@ def _lib_probs_with_filter(st, logits):
     ws.set_trees([(tok, off, idx, st.n, 0)])
     ws.run(torch.softmax(logits, -1).unsqueeze(0).cuda(), input_kind=_lib.IN_PROBS, method=_lib.VERIFY_LOSSY,
            gate=_lib.GATE_PROB, threshold=0.1, window=1, do_sample=1, temperature=1.0, top_p=0.9)
+
+
+def test_scratch_tickets_are_left_clean(cuda_lib):
+    """Every launch leaves its tickets zero, so a caller who vouches for the buffer (SUBSPEC_VERIFY_SCRATCH_CLEAN,
+    what VerifyWorkspace does) needs no clearing operation in front of the kernel; without the flag the
+    library clears them itself, whatever the buffer holds.  Split rows (few rows) and whole rows (many)."""
+    from subspec_b200.verify import VerifyWorkspace
+    for B, nodes, vocab in ((1, 12, 50000), (6, 40, 4099)):
+        gen = torch.Generator().manual_seed(B)
+        sts = [synthetic.random_tree(nodes, 6, 4, vocab, gen) for _ in range(B)]
+        logits = torch.stack([synthetic.verify_logits(st, vocab, gen, dtype=torch.bfloat16, peaked=True) for st in sts])
+        ws = VerifyWorkspace(B, nodes, torch.device("cuda", 0))
+        kw = dict(trees=[_tree_of(st) for st in sts], root_inds=[0] * B, logits=logits.cuda(), eos_token_id=None,
+                  verify_method="exact+lossy", verify_kwargs={"threshold_method": "entropy", "threshold": 0.3,
+                                                              "window_size": 1}, workspace=ws)
+        ws.scratch.fill_(0xFF)
+        ws.scratch_clean = False            # garbage in the buffer: the library has to clear the tickets
+        want = verify_tree_batched(**kw)
+        tickets = 4 * B * (nodes + 1)
+        off = ws._scratch_ptr - ws.scratch.data_ptr()
+        assert int(ws.scratch[off:off + tickets].max()) == 0   # ... and the launch left them zero
+        ws.scratch_clean = True
+        for _ in range(3):
+            got = verify_tree_batched(**kw)
+            for g, w in zip(got, want):
+                for x, y in zip(g, w):
+                    assert x.sampled_tokens.tolist() == y.sampled_tokens.tolist()
+                    assert x.hidden_indices.tolist() == y.hidden_indices.tolist()
+                    assert (x.total_len, x.accept_len) == (y.total_len, y.accept_len)
+        assert int(ws.scratch[off:off + tickets].max()) == 0
