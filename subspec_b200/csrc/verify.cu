@@ -2608,12 +2608,26 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
   const int64_t target = 4LL * kNumSMs;
   int splits = 1;
   if (rows < target) {
-    splits = (int)((target + rows - 1) / rows);
+    // The launch lasts (waves of resident CTAs) x (a CTA's share of a row + its fixed cost): take the split
+    // count that makes that smallest, with a small charge per split for the exchange of partials.  Rounding
+    // the count up to "at least one CTA per slot" is wrong by a wave: 64 rows x 10 splits = 640 CTAs on 592
+    // slots ran 48 CTAs behind everybody else, 5 us of a 20 us launch; nine splits fit.
     const int64_t vecs = a.vocab / (esz == 4 ? 4 : 8);
-    const int64_t max_by_len = vecs / (2 * kThreads) > 1 ? vecs / (2 * kThreads) : 1;
-    if (splits > max_by_len) splits = (int)max_by_len;
-    if (splits > kMaxSplits) splits = kMaxSplits;
-    if (splits < 1) splits = 1;
+    int64_t max_s = vecs / (2 * kThreads) > 1 ? vecs / (2 * kThreads) : 1;
+    if (max_s > kMaxSplits) max_s = kMaxSplits;
+    // in units of the time one resident CTA needs for a whole row (its slot's share of the HBM bandwidth,
+    // ~11 GB/s): ~1.5 us of fixed cost per CTA, ~0.1 us per split for the exchange
+    const double row_us = (double)a.vocab * (double)esz / 11.0e3;
+    const double per_cta = 1.5 / row_us, per_split = 0.1 / row_us;
+    double best = 1e30;
+    for (int sp = 1; sp <= (int)max_s; ++sp) {
+      const int64_t waves = (rows * sp + target - 1) / target;
+      const double cost = (double)waves * (1.0 / sp + per_cta) + per_split * sp;
+      if (cost < best - 1e-12) {
+        best = cost;
+        splits = sp;
+      }
+    }
   }
   ka.splits = splits;
 
