@@ -27,6 +27,7 @@ constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kUnroll = 4;
 constexpr int kMaxK = 32;
+constexpr int kMaxRowSplits = 16;   // slices a row may be cut into when a launch has few rows
 constexpr int kPrefetchAhead = 6;  // iterations (16 KB each) a row's L2 prefetch runs ahead of its loads
 constexpr int kQueue = 256;  // per-warp candidate queue: one 16-byte vector per lane, 8 elements each
 
@@ -88,6 +89,28 @@ __device__ __forceinline__ float warp_kth_largest(float v, int k) {
   return __shfl_sync(0xffffffffu, v, k - 1);
 }
 
+// The k best (value descending, index ascending) of n candidates, by the whole CTA: every candidate counts
+// the candidates that beat it and, if fewer than k do, is the result's entry of that rank.  n^2 compares
+// spread over the CTA's threads, against one warp inserting the candidates one after the other, each insert
+// a chain of dependent shuffles: 128 to 256 candidates took that warp 11 us, three times per step.
+// get(i) returns candidate i (id INT_MAX = empty); out[0..k) in shared memory; ends with a CTA barrier.
+template <typename Get>
+__device__ __forceinline__ void cta_topk(int n, int k, Get&& get, Cand* out) {
+  for (int i = threadIdx.x; i < k; i += blockDim.x) out[i] = Cand{-INFINITY, INT_MAX};
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const Cand me = get(i);
+    if (me.id == INT_MAX) continue;
+    int rank = 0;
+    for (int j = 0; j < n; ++j) {
+      const Cand o = get(j);
+      rank += (o.id != INT_MAX && better(o.v, o.id, me.v, me.id)) ? 1 : 0;
+    }
+    if (rank < k) out[rank] = me;
+  }
+  __syncthreads();
+}
+
 struct RowOut {  // per (sequence, leaf) row, in scratch
   float c, s;    // softmax shift (log2 domain) and denominator; unused for probabilities in
 };
@@ -101,6 +124,12 @@ struct KArgs {
   float invT, T;   // 16-bit dtypes with temperature != 1: the reference rounds logits / T to the dtype first
   int prescale;
   int vec_ok;
+  // few rows: every row is cut into `splits` slices, one CTA each; the slices' lists and softmax sums meet
+  // in scratch behind a ticket per row, and the last slice to arrive carries on as the row's CTA
+  int splits;
+  int* rowticket;   // [batch * leaves]
+  RowOut* partout;  // [batch * leaves * splits]
+  Cand* parttop;    // [batch * leaves * splits * k]
 };
 
 template <typename T>
@@ -230,12 +259,16 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
   __shared__ int s_qn[kWarps];
   __shared__ float s_pub[kWarps];  // each warp's j-th best value: min over warps bounds the k-th best of the row
   __shared__ Cand s_lists[kWarps][kMaxK];
+  __shared__ Cand s_cand[kMaxK * kMaxK];  // the candidates of a merge across slices or across a sequence's rows
+  __shared__ Cand s_best[kMaxK];
   __shared__ float s_c[kWarps], s_s[kWarps];
   __shared__ int s_flag;
 
   const subspec_expand_args& a = ka.a;
   const int L = a.leaves, V = a.vocab, k = a.k;
-  const int row = blockIdx.x;
+  const int S = ka.splits;
+  const int row = blockIdx.x / S;
+  const int split = blockIdx.x - row * S;
   const int b = row / L;
   const T* rowp = reinterpret_cast<const T*>(a.scores) + (size_t)b * a.seq_stride + (size_t)(row - b * L) * a.row_stride;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -254,19 +287,22 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
   float thr = -INFINITY;
 
   const int nvec = ka.vec_ok ? V / VN : 0;
+  // this CTA's slice of the row's vectors (the whole row when S == 1); the scalar tail goes with the last slice
+  const int vec_per = (nvec + S - 1) / S;
+  const int v0 = min(split * vec_per, nvec), v1 = min(v0 + vec_per, nvec);
   const uint4* vp = reinterpret_cast<const uint4*>(rowp);
   // One thread asks L2 for the row a few iterations ahead of the loads (bulk prefetch, no registers, no
   // barrier): a thread has its four loads in flight only while it waits for them, which alone leaves the
   // SM far short of the bytes in flight that its share of the HBM bandwidth needs.
   constexpr int kIterVecs = kThreads * kUnroll;  // 16 KB of the row per iteration
   auto prefetch_iter = [&](int it) {
-    const int v0 = it * kIterVecs;
-    if (v0 < nvec) l2_prefetch(vp + v0, (uint32_t)(min(kIterVecs, nvec - v0) * 16));
+    const int p0 = v0 + it * kIterVecs;
+    if (p0 < v1) l2_prefetch(vp + p0, (uint32_t)(min(kIterVecs, v1 - p0) * 16));
   };
   if (threadIdx.x == 0)
     for (int it = 0; it < kPrefetchAhead; ++it) prefetch_iter(it);
-  for (int i0 = 0; i0 < nvec; i0 += kThreads * kUnroll) {
-    if (threadIdx.x == 0) prefetch_iter(i0 / kIterVecs + kPrefetchAhead);
+  for (int i0 = v0; i0 < v1; i0 += kThreads * kUnroll) {
+    if (threadIdx.x == 0) prefetch_iter((i0 - v0) / kIterVecs + kPrefetchAhead);
     // refresh the threshold: own k-th best, and the bound the other warps have published
     {
       float t = s_pub[0];
@@ -280,7 +316,7 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
 #pragma unroll
     for (int j = 0; j < kUnroll; ++j) {
       const int i = i0 + threadIdx.x + j * kThreads;
-      have[j] = i < nvec;
+      have[j] = i < v1;
       if (have[j]) {
         q[j] = ld_stream_u4(vp + i);
         m[j] = Elem<T>::vmax(q[j]);
@@ -290,7 +326,7 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
       }
     }
     const float gm = fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
-    if (i0 == 0) {
+    if (i0 == v0) {
       // First group: the k-th largest of the 32 lane maxima is k distinct elements' worth of evidence that the
       // warp's k-th best is at least that, which keeps the first round of candidates to a few dozen.
       thr = fmaxf(thr, warp_kth_largest(gm, k));
@@ -346,7 +382,7 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
     }
   }
   // scalar tail (and whole unaligned rows): lane by lane through the same queue
-  for (int i0 = nvec * VN; i0 < V; i0 += kThreads) {
+  for (int i0 = (split == S - 1 ? nvec * VN : V); i0 < V; i0 += kThreads) {
     const int i = i0 + threadIdx.x;
     float x = -INFINITY;
     if (i < V) x = to_f32<T>(rowp[i]);
@@ -393,38 +429,41 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
     }
   }
   __syncthreads();
-  if (warp == 0) {
-    // Fold the other warps' lists into this one.  Entry `lane` of every list sits in this lane; the k-th
-    // largest of the per-lane maxima bounds the merged k-th best from below and filters most entries out.
-    float lv[kWarps - 1];
-    int li[kWarps - 1];
-    float lmax = lane < k ? top.v : -INFINITY;
-#pragma unroll
-    for (int w = 1; w < kWarps; ++w) {
-      const Cand cnd = lane < k ? s_lists[w][lane] : Cand{-INFINITY, INT_MAX};
-      lv[w - 1] = cnd.v;
-      li[w - 1] = cnd.id;
-      lmax = fmaxf(lmax, cnd.v);
+  // ---- the k best of the warps' lists: every candidate counts who beats it (see cta_topk) ----
+  cta_topk(
+      kWarps * k, k, [&](int i) { return s_lists[i / k][i % k]; }, s_best);
+  Cand* top_dst = S > 1 ? ka.parttop + ((size_t)row * S + split) * k : ka.rowtop + (size_t)row * k;
+  RowOut* out_dst = S > 1 ? ka.partout + (size_t)row * S + split : ka.rowout + row;
+  if (threadIdx.x < k) top_dst[threadIdx.x] = s_best[threadIdx.x];
+  if (threadIdx.x == 0) {
+    float c = s_c[0], sm = s_s[0];
+    for (int w = 1; w < kWarps; ++w) combine_soft(c, sm, s_c[w], s_s[w]);
+    if (KIND != SUBSPEC_IN_LOGITS) {
+      c = 0.f;
+      sm = 1.f;
     }
-    const float mthr = warp_kth_largest(lmax, k);
-#pragma unroll
-    for (int w = 1; w < kWarps; ++w) {
-      uint32_t todo = __ballot_sync(0xffffffffu, li[w - 1] != INT_MAX && lv[w - 1] >= mthr);
-      while (todo) {
-        const int src = __ffs(todo) - 1;
-        todo &= todo - 1;
-        top.insert(__shfl_sync(0xffffffffu, lv[w - 1], src), __shfl_sync(0xffffffffu, li[w - 1], src));
-      }
-    }
-    if (lane < k) ka.rowtop[(size_t)row * k + lane] = Cand{top.v, top.id};
-    if (lane == 0) {
-      float c = s_c[0], s = s_s[0];
-      for (int w = 1; w < kWarps; ++w) combine_soft(c, s, s_c[w], s_s[w]);
-      if (KIND != SUBSPEC_IN_LOGITS) {
-        c = 0.f;
-        s = 1.f;
-      }
-      ka.rowout[row] = RowOut{c, s};
+    *out_dst = RowOut{c, sm};
+  }
+  if (S > 1) {
+    // ---- the row's slices meet: the last one to arrive folds all S lists and sums into the row's ----
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_flag = (atomicAdd(ka.rowticket + row, 1) == S - 1);
+    __syncthreads();
+    if (!s_flag) return;
+    __threadfence();
+    const int total = S * k;  // <= kMaxRowSplits * kMaxK
+    const volatile Cand* src = ka.parttop + (size_t)row * S * k;
+    for (int t = threadIdx.x; t < total; t += kThreads) s_cand[t] = Cand{src[t].v, src[t].id};
+    __syncthreads();
+    cta_topk(
+        total, k, [&](int i) { return s_cand[i]; }, s_best);
+    if (threadIdx.x < k) ka.rowtop[(size_t)row * k + threadIdx.x] = s_best[threadIdx.x];
+    if (threadIdx.x == 0) {
+      const volatile RowOut* po = ka.partout + (size_t)row * S;
+      float c = po[0].c, sm = po[0].s;
+      for (int i = 1; i < S; ++i) combine_soft(c, sm, po[i].c, po[i].s);
+      ka.rowout[row] = RowOut{c, sm};
     }
   }
   __threadfence();
@@ -435,61 +474,41 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
   __threadfence();
 
   // ---- the last CTA of the sequence: scores with the reference's rounding, global top-k ----
-  if (warp == 0) {
-    WarpTopK best;
-    best.init(k);
-    const int total = L * k;
-    constexpr int kSlots = 8;  // 256 candidates per round
-    for (int t0 = 0; t0 < total; t0 += 32 * kSlots) {
-    float sc[kSlots];
-    int fl[kSlots];
-    float lmax = -INFINITY;
-#pragma unroll
-    for (int sidx = 0; sidx < kSlots; ++sidx) {
-      const int t = t0 + sidx * 32 + lane;
-      sc[sidx] = -INFINITY;
-      fl[sidx] = INT_MAX;
-      if (t < total) {
-        const int l = t / k;
-        const volatile Cand* src = ka.rowtop + ((size_t)b * L + l) * k + (t - l * k);
-        const float xv = src->v;
-        const int xi = src->id;
-        if (xi != INT_MAX) {
-          const volatile RowOut* ro = ka.rowout + (size_t)b * L + l;
-          float p = xv;
-          if (KIND == SUBSPEC_IN_LOGITS) {
-            const float xs = ka.prescale ? Elem<T>::round_to(__fdiv_rn(xv, ka.T)) : xv;
-            p = ex2f(fmaf(xs, ka.kT, -ro->c)) / ro->s;
-          }
-          p = Elem<T>::round_to(p);
-          const float pp = a.parent_probs ? Elem<T>::load(a.parent_probs, (size_t)b * L + l) : 1.f;
-          sc[sidx] = Elem<T>::round_to(p * pp);
-          fl[sidx] = l * V + xi;
-          lmax = fmaxf(lmax, sc[sidx]);
+  {
+    const int total = L * k;  // <= kMaxK * kMaxK
+    for (int t = threadIdx.x; t < total; t += kThreads) {
+      const int l = t / k;
+      const volatile Cand* src = ka.rowtop + ((size_t)b * L + l) * k + (t - l * k);
+      const float xv = src->v;
+      const int xi = src->id;
+      Cand out{-INFINITY, INT_MAX};
+      if (xi != INT_MAX) {
+        const volatile RowOut* ro = ka.rowout + (size_t)b * L + l;
+        float p = xv;
+        if (KIND == SUBSPEC_IN_LOGITS) {
+          const float xs = ka.prescale ? Elem<T>::round_to(__fdiv_rn(xv, ka.T)) : xv;
+          p = ex2f(fmaf(xs, ka.kT, -ro->c)) / ro->s;
         }
+        p = Elem<T>::round_to(p);
+        const float pp = a.parent_probs ? Elem<T>::load(a.parent_probs, (size_t)b * L + l) : 1.f;
+        out = Cand{Elem<T>::round_to(p * pp), l * V + xi};
       }
+      s_cand[t] = out;
     }
-    // k lanes hold a candidate at least this good; later rounds also have to beat the running k-th best
-    const float gthr = fmaxf(warp_kth_largest(lmax, k), best.kth_value());
-#pragma unroll
-    for (int sidx = 0; sidx < kSlots; ++sidx) {
-      uint32_t todo = __ballot_sync(0xffffffffu, fl[sidx] != INT_MAX && sc[sidx] >= gthr);
-      while (todo) {
-        const int src = __ffs(todo) - 1;
-        todo &= todo - 1;
-        best.insert(__shfl_sync(0xffffffffu, sc[sidx], src), __shfl_sync(0xffffffffu, fl[sidx], src));
-      }
-    }
-    }
-    if (lane < k) {
-      const size_t o = (size_t)b * k + lane;
+    __syncthreads();
+    cta_topk(
+        total, k, [&](int i) { return s_cand[i]; }, s_best);
+    if (threadIdx.x < k) {
+      const int lane_k = threadIdx.x;
+      const Cand best = s_best[lane_k];
+      const size_t o = (size_t)b * k + lane_k;
       const int l = best.id == INT_MAX ? 0 : best.id / V;
       const int tok = best.id == INT_MAX ? 0 : best.id - l * V;
       a.out_tokens[o] = tok;
       a.out_parents[o] = l;
       Elem<T>::store(a.out_probs, o, best.v);
       if (a.tree_tokens) {  // Tree.add_nodes numbering: level d occupies 1 + d k ... d k + k
-        const size_t node = (size_t)b * a.tree_stride + 1 + (size_t)a.level * k + lane;
+        const size_t node = (size_t)b * a.tree_stride + 1 + (size_t)a.level * k + lane_k;
         a.tree_tokens[node] = tok;
         a.tree_parents[node] = a.level == 0 ? 0 : 1 + (a.level - 1) * k + l;
         a.tree_probs[node] = best.v;
@@ -591,7 +610,10 @@ using namespace subspec;
 extern "C" int subspec_expand_scratch_bytes(int32_t batch, int32_t leaves, int32_t k, size_t* bytes) {
   if (!bytes || batch < 0 || leaves < 1 || k < 1 || k > kMaxK) return SUBSPEC_EINVAL;
   const size_t rows = (size_t)batch * leaves;
-  *bytes = align_up(sizeof(int) * (size_t)batch, 256) + align_up(sizeof(RowOut) * rows, 256) + sizeof(Cand) * rows * k;
+  // sequence tickets + row tickets | row sums | row lists | slice sums | slice lists (rows may be cut into slices)
+  *bytes = align_up(sizeof(int) * ((size_t)batch + rows), 256) + align_up(sizeof(RowOut) * rows, 256) +
+           align_up(sizeof(Cand) * rows * k, 256) + align_up(sizeof(RowOut) * rows * kMaxRowSplits, 256) +
+           sizeof(Cand) * rows * kMaxRowSplits * k;
   return SUBSPEC_OK;
 }
 
@@ -618,10 +640,15 @@ extern "C" int subspec_expand_step(const subspec_expand_args* args, subspec_stre
   char* p = reinterpret_cast<char*>(a.scratch);
   const size_t rows = (size_t)a.batch * a.leaves;
   ka.ticket = reinterpret_cast<int*>(p);
-  p += align_up(sizeof(int) * (size_t)a.batch, 256);
+  ka.rowticket = ka.ticket + a.batch;
+  p += align_up(sizeof(int) * ((size_t)a.batch + rows), 256);
   ka.rowout = reinterpret_cast<RowOut*>(p);
   p += align_up(sizeof(RowOut) * rows, 256);
   ka.rowtop = reinterpret_cast<Cand*>(p);
+  p += align_up(sizeof(Cand) * rows * a.k, 256);
+  ka.partout = reinterpret_cast<RowOut*>(p);
+  p += align_up(sizeof(RowOut) * rows * kMaxRowSplits, 256);
+  ka.parttop = reinterpret_cast<Cand*>(p);
   const size_t esz = a.dtype == SUBSPEC_F32 ? 4 : 2;
   ka.prescale = (esz == 2 && a.input_kind == SUBSPEC_IN_LOGITS && a.temperature != 1.0) ? 1 : 0;
   ka.T = (float)a.temperature;
@@ -629,19 +656,32 @@ extern "C" int subspec_expand_step(const subspec_expand_args* args, subspec_stre
   ka.kT = ka.prescale ? kLog2e : (float)(1.4426950408889634 / a.temperature);
   ka.vec_ok = ((reinterpret_cast<uintptr_t>(a.scores) & 15u) == 0) && ((a.seq_stride * esz) % 16 == 0) &&
               ((a.row_stride * esz) % 16 == 0);
+  // Few rows: a row alone takes one CTA ~45 us whatever else runs (sixteen dependent iterations plus the
+  // warm-up and the merges), so a single sequence's step cost almost what 32 sequences' did.  Cut every
+  // row into slices while the slices of all rows still fit the machine at once and each has at least one
+  // full iteration of vectors; at 4 x 148 rows and above nothing changes.
+  ka.splits = 1;
+  if (ka.vec_ok) {
+    const int64_t slots = 4LL * kNumSMs;
+    const int64_t iters = (a.vocab / (int)(16 / esz)) / (kThreads * kUnroll);  // full iterations in a row
+    int64_t sp = slots / (int64_t)rows;
+    if (sp > iters) sp = iters;
+    if (sp > kMaxRowSplits) sp = kMaxRowSplits;
+    if (sp >= 2) ka.splits = (int)sp;
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  int rc = cuda_check(cudaMemsetAsync(ka.ticket, 0, sizeof(int) * (size_t)a.batch, st));
+  int rc = cuda_check(cudaMemsetAsync(ka.ticket, 0, sizeof(int) * ((size_t)a.batch + rows), st));
   if (rc) return rc;
   cudaError_t e;
   switch (a.dtype) {
     case SUBSPEC_F32:
-      e = launch_expand<float>(ka, (int)rows, st);
+      e = launch_expand<float>(ka, (int)rows * ka.splits, st);
       break;
     case SUBSPEC_BF16:
-      e = launch_expand<__nv_bfloat16>(ka, (int)rows, st);
+      e = launch_expand<__nv_bfloat16>(ka, (int)rows * ka.splits, st);
       break;
     default:
-      e = launch_expand<__half>(ka, (int)rows, st);
+      e = launch_expand<__half>(ka, (int)rows * ka.splits, st);
       break;
   }
   return cuda_check(e);

@@ -103,6 +103,30 @@ def test_config3_shape_batched(cuda_lib, dtype):
     _check_topk((probs[:, :, :V - 3] * pp.unsqueeze(-1)).reshape(B, -1), ref2, tok2, val2, par2, V - 3)
 
 
+@pytest.mark.parametrize("B,L,V,dtype,temperature", [
+    (1, 1, 128256, torch.bfloat16, 1.0), (1, 16, 128256, torch.float16, 0.7), (2, 5, 32000, torch.float32, 1.3),
+    (1, 16, 152064, torch.bfloat16, 1.0), (9, 16, 32000, torch.bfloat16, 1.0)])
+def test_few_rows_are_cut_into_slices(cuda_lib, B, L, V, dtype, temperature):
+    """A launch with few rows cuts every row into slices (one CTA each) whose lists and softmax sums meet behind
+    a ticket per row: a single sequence's step, the reference's own setting.  Same answers as the oracle."""
+    k = 16
+    gen = torch.Generator().manual_seed(B * 100 + L)
+    logits = (torch.randn(B, L, V, generator=gen) * 3.0).to(dtype)
+    pp = torch.rand(B, L, generator=gen).to(dtype)
+    probs = eo.draft_probs(logits, temperature)
+    rt, ref_vals, rp = eo.topk_flatten(probs, pp, k)
+    scores = (probs * pp.unsqueeze(-1)).view(B, -1)
+    for rep in range(2):  # twice: the tickets are cleared by every call
+        tok, val, par = topk_sampling_from_logits(logits.cuda(), pp.cuda(), k, temperature)
+        if dtype == torch.float32:
+            assert torch.allclose(val.cpu(), ref_vals, rtol=2e-5, atol=0)
+            assert torch.equal((par * V + tok).cpu(), rp * V + rt)
+        else:
+            _check_topk(scores, ref_vals, tok, val, par, V)
+    tok2, val2, par2 = topk_sampling(probs.cuda(), pp.cuda(), k)   # probabilities in
+    _check_topk(scores, ref_vals, tok2, val2, par2, V)
+
+
 def test_edge_cases(cuda_lib):
     # k larger than the vocabulary is clamped like the reference (min(k, vocab)); ties resolved by flat index
     probs = torch.full((1, 2, 3), 0.25, dtype=torch.float32)
