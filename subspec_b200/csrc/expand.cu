@@ -102,6 +102,7 @@ __device__ __forceinline__ void cta_topk(int n, int k, Get&& get, Cand* out) {
     const Cand me = get(i);
     if (me.id == INT_MAX) continue;
     int rank = 0;
+#pragma unroll 8  // the loads of a group go out together: one after the other they are the whole cost
     for (int j = 0; j < n; ++j) {
       const Cand o = get(j);
       rank += (o.id != INT_MAX && better(o.v, o.id, me.v, me.id)) ? 1 : 0;
