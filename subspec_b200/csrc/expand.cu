@@ -259,7 +259,6 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
   __shared__ Cand s_queue[kWarps][kQueue];
   __shared__ int s_qn[kWarps];
   __shared__ float s_pub[kWarps];  // each warp's j-th best value: min over warps bounds the k-th best of the row
-  __shared__ Cand s_lists[kWarps][kMaxK];
   __shared__ Cand s_cand[kMaxK * kMaxK];  // the candidates of a merge across slices or across a sequence's rows
   __shared__ Cand s_best[kMaxK];
   __shared__ float s_c[kWarps], s_s[kWarps];
@@ -411,7 +410,7 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
   }
 
   // ---- merge the warps' lists and softmax sums ----
-  if (lane < k) s_lists[warp][lane] = Cand{top.v, top.id};
+  if (lane < k) s_cand[warp * k + lane] = Cand{top.v, top.id};  // the warps' lists, back to back
   {
     float c = soft.c, s = soft.sum();
     if (KIND != SUBSPEC_IN_LOGITS) {
@@ -432,7 +431,7 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
   __syncthreads();
   // ---- the k best of the warps' lists: every candidate counts who beats it (see cta_topk) ----
   cta_topk(
-      kWarps * k, k, [&](int i) { return s_lists[i / k][i % k]; }, s_best);
+      kWarps * k, k, [&](int i) { return s_cand[i]; }, s_best);
   Cand* top_dst = S > 1 ? ka.parttop + ((size_t)row * S + split) * k : ka.rowtop + (size_t)row * k;
   RowOut* out_dst = S > 1 ? ka.partout + (size_t)row * S + split : ka.rowout + row;
   if (threadIdx.x < k) top_dst[threadIdx.x] = s_best[threadIdx.x];
