@@ -67,34 +67,7 @@ def make_wave_inputs(seq_ids, variant: str, device, with_logits=True):
     """Trees (host) and logits (device) for the given global sequence ids; everything seeded by the id."""
     from subspec_b200 import synthetic
 
-    trees = []
-    for sid in seq_ids:
-        gen = torch.Generator().manual_seed(1_000_003 * 5 + sid)
-        trees.append(synthetic.random_tree(NODES, 8, 4, VOCAB, gen))
-    if not with_logits:
-        return trees, None
-    S = len(seq_ids)
-    dgen = torch.Generator(device=device).manual_seed(7_000_001 + seq_ids[0])
-    logits = torch.empty(S, NODES, VOCAB, dtype=torch.bfloat16, device=device)
-    for b in range(S):  # fp32 noise generated one sequence at a time to bound the transient footprint
-        logits[b] = (torch.randn(NODES, VOCAB, generator=dgen, device=device) * 3.0).to(torch.bfloat16)
-    bi, ui, ti = [], [], []
-    for b, (sid, st) in enumerate(zip(seq_ids, trees)):
-        cgen = torch.Generator().manual_seed(9_000_011 + sid)
-        ch = st.children()
-        for u in range(st.n):
-            if ch[u] and float(torch.rand((), generator=cgen)) < 0.6:
-                c = ch[u][int(torch.randint(len(ch[u]), (1,), generator=cgen))]
-                bi.append(b)
-                ui.append(u)
-                ti.append(int(st.token_ids[c]))
-    bi, ui, ti = (torch.tensor(x, device=device) for x in (bi, ui, ti))
-    if variant == "peaked":
-        rowmax = logits.float().amax(dim=-1)
-        logits[bi, ui, ti] = (rowmax[bi, ui] + 4.0).to(torch.bfloat16)
-    else:
-        logits[bi, ui, ti] = (logits[bi, ui, ti].float() + 6.0).to(torch.bfloat16)
-    return trees, logits
+    return synthetic.config5_wave(seq_ids, variant, device, nodes=NODES, vocab=VOCAB, with_logits=with_logits)
 
 
 def flats_of(trees):

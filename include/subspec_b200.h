@@ -64,6 +64,14 @@ typedef void* subspec_stream_t; /* a cudaStream_t; NULL = legacy default stream 
 #define SUBSPEC_DEV_BAD_INDEX 16u /* an accepted-path index was out of range */
 #define SUBSPEC_DEV_TIMEOUT 32u  /* a bounded device-side wait ran out       */
 #define SUBSPEC_DEV_HIST_OVERFLOW 64u /* sampling: one finite logit value occurs > 65535 times in a row */
+#define SUBSPEC_DEV_BAD_PARENT 128u /* tree finaliser: a parent index was not in [0, own index) */
+#define SUBSPEC_DEV_BAD_COUNT 256u  /* a device-side node / row count or children offset had to be clamped */
+
+/* element forms of a tree-attention mask written by the expander and the finaliser */
+#define SUBSPEC_MASK_BOOL 0     /* one byte per element, 1 = may attend (torch.bool) */
+#define SUBSPEC_MASK_ADD_F32 1  /* additive, invert_mask(mask, float32): -0.0 / finfo.min */
+#define SUBSPEC_MASK_ADD_BF16 2 /* additive, bfloat16 */
+#define SUBSPEC_MASK_ADD_F16 3  /* additive, float16 */
 
 SUBSPEC_API const char* subspec_version(void);
 /* cudaGetErrorString of the last CUDA error an entry point saw on this thread */
@@ -332,6 +340,18 @@ SUBSPEC_API int subspec_kv_compact_hf(const subspec_kv_hf_args* args, subspec_st
  * tree_stride]; node 0 is the root, level `level` fills nodes
  * 1 + level*k .. level*k + k in rank order, with parent node index, cumulative
  * probability (the score) and depth level + 1.
+ *
+ * Draft-side mask (replaces TreeMaskCache.update_tree_mask and get_tree_mask,
+ * specdecodes/models/draft_models/base.py:93-117, and the position ids kept by
+ * the speculate loop, draft_models/classic_sd.py:71-72, 113).  With
+ * `draft_mask` given, row i of sequence b is written whole:
+ *   [ prefix_len[b] x may-attend | column (a - 1) set for every node a that is
+ *     the new node 1 + level*k + i or one of its ancestors below the root
+ *     | masked up to draft_mask_cols ]
+ * which is what the reference's buffer holds after its update for this level:
+ * the parent's row followed by a one-hot for the node itself.  The root is the
+ * last of the prefix tokens.  prefix_len[b] + (level + 1) * k > draft_mask_cols
+ * sets SUBSPEC_DEV_BAD_INDEX and leaves that sequence's rows unwritten.
  * ---------------------------------------------------------------------- */
 typedef struct subspec_expand_args {
   uint32_t struct_size;
@@ -358,6 +378,14 @@ typedef struct subspec_expand_args {
   void* scratch; /* subspec_expand_scratch_bytes(), 256-byte aligned, no initialisation needed */
   size_t scratch_bytes;
   uint32_t* dev_status;
+  /* Optional (needs the tree arrays): the draft-side tree mask of the new level and its position ids. */
+  void* draft_mask;              /* [batch, k, cols] in the element form draft_mask_kind, or NULL */
+  int32_t draft_mask_kind;       /* SUBSPEC_MASK_* */
+  int64_t draft_mask_cols;       /* columns written per row, >= prefix_len[b] + (level + 1) * k */
+  int64_t draft_mask_row_stride; /* elements; 0 = draft_mask_cols */
+  int64_t draft_mask_seq_stride; /* elements; 0 = k * row stride */
+  const int32_t* prefix_len;     /* [batch] tokens in front of the tree's first level, or NULL (= 0) */
+  int64_t* draft_position_ids;   /* [batch, k] = prefix_len[b] + level, or NULL */
 } subspec_expand_args;
 
 SUBSPEC_API int subspec_expand_scratch_bytes(int32_t batch, int32_t leaves, int32_t k, size_t* bytes);
@@ -371,18 +399,38 @@ SUBSPEC_API int subspec_expand_step(const subspec_expand_args* args, subspec_str
  * Replaces (reference file:line):
  *   - Tree.prune_to_top_n         specdecodes/models/utils/cpu_tree.py:175-215
  *   - Tree.get_tree_data          cpu_tree.py:238-251
- *   - Tree.create_attention_mask  cpu_tree.py:263-286 (ancestor-or-self matrix)
- *   - position ids = depths + position_offset
- *                                 specdecodes/models/generators/classic_sd.py:73-75
+ *   - Tree.create_attention_mask  cpu_tree.py:263-286 (ancestor-or-self matrix,
+ *                                 prefix_length all-true columns in front, rows
+ *                                 from skip_nodes)
+ *   - position ids = depths + position_offset, the splice of the mask into the
+ *     preallocated [1, 1, max_verify, max_cache_len] buffer and its inversion
+ *                                 specdecodes/models/generators/classic_sd.py:33-55, 73-77
+ *                                 specdecodes/models/utils/utils.py:4-6
  *
  * Input: the tree arrays subspec_expand_step fills, n_nodes nodes per
- * sequence (node 0 = root, probability 1).  Ranking is (probability desc,
- * index asc); the reference leaves ties to torch.topk.  Outputs are
- * [batch, keep]: keep_idx (old index of new node r), tokens, parents (new
- * numbering, -1 for the root), depths, probs, position_ids (int64); mask is
- * [batch, keep, keep] bytes, mask[i][j] = 1 iff j is i or an ancestor of i;
- * child_off [batch, keep + 1] / child_idx [batch, keep] are the children lists
- * in the layout subspec_verify_batched takes; n_out[b] = nodes kept.
+ * sequence (node 0 = root, probability 1; every parent index is smaller than
+ * the node's own, else SUBSPEC_DEV_BAD_PARENT and the node is treated as a
+ * root).  When n_nodes <= keep nothing is pruned and the nodes keep their
+ * numbering, as the reference returns early (cpu_tree.py:176-177); otherwise
+ * ranking is (probability desc, index asc; the reference leaves ties to
+ * torch.topk) and node r of the output is the node of rank r.
+ *
+ * Outputs are [batch, keep]: keep_idx (old index of new node r), tokens,
+ * parents (new numbering, -1 for the root), depths, probs, position_ids
+ * (int64); child_off [batch, keep + 1] / child_idx [batch, keep] are the
+ * children lists in the layout subspec_verify_batched takes; n_out[b] = nodes
+ * kept.  Entries r >= n_out[b] are padding (keep_idx -1).
+ *
+ * Mask.  Row r - skip_nodes of sequence b (r = skip_nodes .. keep - 1) is
+ *   [ prefix_length[b] x may-attend | keep tree columns: column j set iff node
+ *     j is r or an ancestor of r | masked up to mask_cols ]
+ * in the element form `mask_kind` (SUBSPEC_MASK_*).  mask_cols = 0 means
+ * `keep` columns and is valid only without a prefix (prefix_length == NULL);
+ * mask_row_stride / mask_seq_stride are in elements, 0 = dense.  With
+ * mask_cols = max_cache_len and the strides of the caller's static buffer the
+ * kernel writes the rows the reference's _get_tree_mask + invert_mask produce.
+ * A padding row attends to itself only.  prefix_length[b] + keep > mask_cols
+ * sets SUBSPEC_DEV_BAD_INDEX and leaves that sequence's mask unwritten.
  * ---------------------------------------------------------------------- */
 typedef struct subspec_tree_finalize_args {
   uint32_t struct_size;
@@ -401,10 +449,17 @@ typedef struct subspec_tree_finalize_args {
   int32_t* depths;
   float* probs;
   int64_t* position_ids;
-  uint8_t* mask;
+  void* mask;
   int32_t* child_off;
   int32_t* child_idx;
   int32_t* n_out;
+  uint32_t* dev_status;          /* one word, OR-ed with SUBSPEC_DEV_* bits; may be NULL */
+  const int32_t* prefix_length;  /* [batch] or NULL (= 0) */
+  int32_t skip_nodes;            /* 0 .. keep: mask rows start at this node */
+  int32_t mask_kind;             /* SUBSPEC_MASK_* */
+  int64_t mask_cols;             /* columns written per row; 0 = keep (no prefix) */
+  int64_t mask_row_stride;       /* elements; 0 = mask_cols */
+  int64_t mask_seq_stride;       /* elements; 0 = (keep - skip_nodes) * row stride */
 } subspec_tree_finalize_args;
 
 SUBSPEC_API int subspec_tree_finalize(const subspec_tree_finalize_args* args, subspec_stream_t stream);

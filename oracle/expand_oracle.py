@@ -34,6 +34,30 @@ def topk_flatten(sampled_probs: torch.Tensor, parent_probs: torch.Tensor, k: int
     return (idx % V).long(), vals, (idx // V).long()
 
 
+def topk_flatten_ordered(sampled_probs: torch.Tensor, parent_probs: torch.Tensor, k: int):
+    """`topk_flatten` with ties in a stated order: (value descending, flat index ascending), the order the CUDA
+    path documents.  torch.topk leaves the order of equal values open, so against the reference only the values
+    can be compared where scores tie; against this function the indices can be compared too."""
+    B, L, V = sampled_probs.shape
+    k = min(int(k), int(V))
+    scores = (sampled_probs * parent_probs.unsqueeze(-1)).view(B, -1)
+    toks, vals, pars = [], [], []
+    for b in range(B):
+        row = scores[b].float()
+        m = min(row.numel(), 8 * k)
+        while True:
+            top = torch.topk(row, m, sorted=True)
+            if m == row.numel() or float(top.values[-1]) < float(top.values[k - 1]):
+                break  # every score equal to the k-th is among the m candidates
+            m = min(row.numel(), 4 * m)
+        order = sorted(range(m), key=lambda i: (-float(top.values[i]), int(top.indices[i])))[:k]
+        idx = top.indices[order]
+        toks.append(idx % V)
+        pars.append(idx // V)
+        vals.append(scores[b][idx])
+    return torch.stack(toks).long(), torch.stack(vals), torch.stack(pars).long()
+
+
 def same_topk(scores_flat: torch.Tensor, ref_vals: torch.Tensor, got_vals: torch.Tensor, got_flat_idx: torch.Tensor):
     """Tie-tolerant equality: the sorted values are bit-equal, every returned index really carries its
     value, and no index is returned twice.  (Which members of a tied group appear is not pinned.)"""
@@ -75,11 +99,15 @@ class FlatTree:
                 new.append(base + i)
             self.leaves = new
 
-    def prune_to_top_n(self, n: int, dtype=torch.float32) -> List[int]:
+    def prune_to_top_n(self, n: int, dtype=torch.float32, ordered: bool = False) -> List[int]:
+        """`ordered`: ties by ascending node index (the CUDA path's rule) instead of torch.topk's open order."""
         if n == -1 or len(self.token) <= n:
             return list(range(len(self.token)))
         probs = torch.tensor(self.prob, dtype=dtype)
-        keep = torch.topk(probs, k=n, sorted=True).indices.tolist()
+        if ordered:
+            keep = sorted(range(len(self.token)), key=lambda i: (-float(probs[i]), i))[:n]
+        else:
+            keep = torch.topk(probs, k=n, sorted=True).indices.tolist()
         new_of = {o: i for i, o in enumerate(keep)}
         self.children = [[new_of[c] for c in self.children[o] if c in new_of] for o in keep]
         self.parent = [new_of.get(self.parent[o], -1) if self.parent[o] >= 0 else -1 for o in keep]

@@ -18,6 +18,8 @@ VERIFY_EXACT, VERIFY_LOSSY, VERIFY_EXACT_AND_LOSSY = 0, 1, 2
 VERIFY_SCRATCH_CLEAN = 1  # SUBSPEC_VERIFY_SCRATCH_CLEAN
 GATE_PROB, GATE_ENTROPY = 0, 1
 DEV_BAD_TOKEN, DEV_BAD_CHILD, DEV_BAD_ROOT, DEV_BAD_PAGE, DEV_BAD_INDEX, DEV_TIMEOUT, DEV_HIST_OVERFLOW = 1, 2, 4, 8, 16, 32, 64
+DEV_BAD_PARENT, DEV_BAD_COUNT = 128, 256
+MASK_BOOL, MASK_ADD_F32, MASK_ADD_BF16, MASK_ADD_F16 = 0, 1, 2, 3
 
 _STATUS_TEXT = {
     EINVAL: "invalid argument",
@@ -35,6 +37,8 @@ _DEV_TEXT = {
     DEV_BAD_INDEX: "accepted-path index out of range",
     DEV_TIMEOUT: "a bounded device-side wait ran out",
     DEV_HIST_OVERFLOW: "sampling: one finite logit value occurs more than 65535 times in a row",
+    DEV_BAD_PARENT: "a parent index was not smaller than the node's own",
+    DEV_BAD_COUNT: "a node / row count or a children offset was out of range",
 }
 
 _vp, _i32, _i64, _u32, _f32, _f64 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint32, C.c_float, C.c_double
@@ -91,6 +95,8 @@ class ExpandArgs(C.Structure):
         ("temperature", _f64), ("out_tokens", _vp), ("out_probs", _vp), ("out_parents", _vp), ("level", _i32),
         ("tree_stride", _i32), ("tree_tokens", _vp), ("tree_parents", _vp), ("tree_probs", _vp),
         ("tree_depths", _vp), ("scratch", _vp), ("scratch_bytes", C.c_size_t), ("dev_status", _vp),
+        ("draft_mask", _vp), ("draft_mask_kind", _i32), ("draft_mask_cols", _i64), ("draft_mask_row_stride", _i64),
+        ("draft_mask_seq_stride", _i64), ("prefix_len", _vp), ("draft_position_ids", _vp),
     ]
 
 
@@ -102,7 +108,8 @@ class TreeFinalizeArgs(C.Structure):
         ("tree_tokens", _vp), ("tree_parents", _vp), ("tree_probs", _vp), ("tree_depths", _vp),
         ("position_offset", _vp), ("keep_idx", _vp), ("tokens", _vp), ("parents", _vp), ("depths", _vp),
         ("probs", _vp), ("position_ids", _vp), ("mask", _vp), ("child_off", _vp), ("child_idx", _vp),
-        ("n_out", _vp),
+        ("n_out", _vp), ("dev_status", _vp), ("prefix_length", _vp), ("skip_nodes", _i32), ("mask_kind", _i32),
+        ("mask_cols", _i64), ("mask_row_stride", _i64), ("mask_seq_stride", _i64),
     ]
 
 

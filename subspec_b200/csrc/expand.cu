@@ -19,6 +19,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "mask.cuh"
 
 namespace subspec {
 namespace {
@@ -128,6 +129,7 @@ struct KArgs {
   // few rows: every row is cut into `splits` slices, one CTA each; the slices' lists and softmax sums meet
   // in scratch behind a ticket per row, and the last slice to arrive carries on as the row's CTA
   int splits;
+  int64_t dm_row_stride, dm_seq_stride;  // draft-side mask geometry in elements, defaults resolved
   int* rowticket;   // [batch * leaves]
   RowOut* partout;  // [batch * leaves * splits]
   Cand* parttop;    // [batch * leaves * splits * k]
@@ -486,8 +488,11 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
         const volatile RowOut* ro = ka.rowout + (size_t)b * L + l;
         float p = xv;
         if (KIND == SUBSPEC_IN_LOGITS) {
+          // The survivors' probabilities in double precision: a 16-bit dtype rounds them next, and an error of
+          // 1e-6 in fp32 arithmetic on an exponent near 20 would land on the other side of a rounding boundary
+          // a few times per thousand values; what is left is the error of the fp32 denominator (~1e-7).
           const float xs = ka.prescale ? Elem<T>::round_to(__fdiv_rn(xv, ka.T)) : xv;
-          p = ex2f(fmaf(xs, ka.kT, -ro->c)) / ro->s;
+          p = (float)(exp2((double)xs * (double)ka.kT - (double)ro->c) / (double)ro->s);
         }
         p = Elem<T>::round_to(p);
         const float pp = a.parent_probs ? Elem<T>::load(a.parent_probs, (size_t)b * L + l) : 1.f;
@@ -515,38 +520,97 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
         a.tree_depths[node] = a.level + 1;
       }
     }
+    if (a.draft_mask) {
+      // ---- the new level's draft-side mask rows and position ids (TreeMaskCache, base.py:93-117) ----
+      const MaskFmt mf = mask_fmt(a.draft_mask_kind);
+      const int64_t prefix = a.prefix_len ? (int64_t)a.prefix_len[b] : 0;
+      const int64_t rs = ka.dm_row_stride;
+      uint8_t* mbase = reinterpret_cast<uint8_t*>(a.draft_mask) + (size_t)b * ka.dm_seq_stride * mf.esz;
+      const bool ok = prefix >= 0 && prefix + (int64_t)(a.level + 1) * k <= a.draft_mask_cols;
+      if (!ok && threadIdx.x == 0) flag(a.dev_status, SUBSPEC_DEV_BAD_INDEX);
+      if (ok) mask_fill_rows(mbase, rs, k, a.draft_mask_cols, prefix, mf);
+      __syncthreads();
+      if (threadIdx.x < k) {
+        const int i = threadIdx.x;
+        if (a.draft_position_ids) a.draft_position_ids[(size_t)b * k + i] = prefix + a.level;
+        if (ok) {
+          uint8_t* mrow = mbase + (size_t)i * rs * mf.esz;
+          const Cand best = s_best[i];
+          const int l = best.id == INT_MAX ? 0 : best.id / V;
+          int node = 1 + a.level * k + i;
+          mask_store(mrow, prefix + node - 1, mf, true);
+          node = a.level == 0 ? 0 : 1 + (a.level - 1) * k + l;  // this level's parents are not read back
+          const int32_t* tp = a.tree_parents + (size_t)b * a.tree_stride;
+          for (int hop = 0; hop < a.level && node > 0; ++hop) {  // one ancestor per earlier level, then the root
+            mask_store(mrow, prefix + node - 1, mf, true);
+            const int up = tp[node];
+            node = (up >= 0 && up < node) ? up : 0;
+          }
+        }
+      }
+    }
   }
 }
 
 // ---- tree finaliser ------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) tree_finalize_kernel(const subspec_tree_finalize_args a) {
+struct FinArgs {
+  subspec_tree_finalize_args a;
+  int64_t cols, row_stride, seq_stride;  // mask geometry in elements, defaults resolved on the host
+};
+
+__global__ void __launch_bounds__(256) tree_finalize_kernel(const FinArgs fa) {
   extern __shared__ int sm[];
+  const subspec_tree_finalize_args& a = fa.a;
   const int b = blockIdx.x;
   const int n = a.n_nodes, keep = min(a.keep, a.n_nodes);
+  const bool identity = a.n_nodes <= a.keep;  // nothing to prune: the reference leaves the tree alone (cpu_tree.py:176-177)
   int* rank = sm;            // [n] rank of old node i (0 = best)
   int* old_of = rank + n;    // [keep]
   int* par = old_of + keep;  // [n] parents, old numbering (a copy: the loops below read them many times)
   int* coff = par + n;       // [keep + 1] children CSR offsets, new numbering
   const size_t tb = (size_t)b * a.tree_stride;
   const float* prob = a.tree_probs + tb;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) par[i] = i == 0 ? -1 : a.tree_parents[tb + i];
-
-  // rank by (cumulative probability desc, index asc); the root carries probability 1
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float pi = i == 0 ? 1.f : prob[i];
-    int r = 0;
-    for (int j = 0; j < n; ++j) {
-      const float pj = j == 0 ? 1.f : prob[j];
-      r += (pj > pi || (pj == pi && j < i)) ? 1 : 0;
+    int p = i == 0 ? -1 : a.tree_parents[tb + i];
+    if (i > 0 && (p < 0 || p >= i)) {  // expansion appends children behind their parents; anything else could loop
+      flag(a.dev_status, SUBSPEC_DEV_BAD_PARENT);
+      p = -1;
+    }
+    par[i] = p;
+  }
+
+  // rank by (cumulative probability desc, index asc); the root carries probability 1, NaN counts as -inf
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    int r = i;
+    if (!identity) {
+      float pi = i == 0 ? 1.f : prob[i];
+      pi = pi == pi ? pi : -INFINITY;
+      r = 0;
+      for (int j = 0; j < n; ++j) {
+        float pj = j == 0 ? 1.f : prob[j];
+        pj = pj == pj ? pj : -INFINITY;
+        r += (pj > pi || (pj == pi && j < i)) ? 1 : 0;
+      }
     }
     rank[i] = r;
     if (r < keep) old_of[r] = i;
   }
+  // mask background: prefix columns "may attend", everything behind "masked"
+  const MaskFmt mf = mask_fmt(a.mask_kind);
+  const int skip = min(max(a.skip_nodes, 0), a.keep);
+  int64_t prefix = a.prefix_length ? (int64_t)a.prefix_length[b] : 0;
+  bool mask_ok = true;
+  if (prefix < 0 || prefix + a.keep > fa.cols) {
+    if (threadIdx.x == 0) flag(a.dev_status, SUBSPEC_DEV_BAD_INDEX);
+    mask_ok = false;
+  }
+  uint8_t* mbase = reinterpret_cast<uint8_t*>(a.mask) + (size_t)b * fa.seq_stride * mf.esz;
+  if (mask_ok) mask_fill_rows(mbase, fa.row_stride, a.keep - skip, fa.cols, prefix, mf);
   __syncthreads();
   const size_t ob = (size_t)b * a.keep;
   for (int r = threadIdx.x; r < keep; r += blockDim.x) {
     const int o = old_of[r];
-    const int p = o == 0 ? -1 : par[o];
+    const int p = par[o];
     const int np = (p >= 0 && rank[p] < keep) ? rank[p] : -1;
     a.keep_idx[ob + r] = o;
     a.tokens[ob + r] = a.tree_tokens[tb + o];
@@ -555,14 +619,15 @@ __global__ void __launch_bounds__(256) tree_finalize_kernel(const subspec_tree_f
     a.depths[ob + r] = d;
     a.probs[ob + r] = o == 0 ? 1.f : prob[o];
     a.position_ids[ob + r] = (int64_t)d + (a.position_offset ? a.position_offset[b] : 0);
-    // ancestor-or-self row
-    uint8_t* mrow = a.mask + (ob + r) * a.keep;
-    for (int j = 0; j < a.keep; ++j) mrow[j] = 0;
-    int cur = o, guard = 0;
-    while (cur >= 0 && guard <= n) {
-      if (rank[cur] < keep) mrow[rank[cur]] = 1;
-      cur = cur == 0 ? -1 : par[cur];
-      ++guard;
+    // ancestor-or-self row (parents are smaller than their children, so the walk ends within n steps)
+    if (mask_ok && r >= skip) {
+      uint8_t* mrow = mbase + (size_t)(r - skip) * fa.row_stride * mf.esz;
+      int cur = o, guard = 0;
+      while (cur >= 0 && guard <= n) {
+        if (rank[cur] < keep) mask_store(mrow, prefix + rank[cur], mf, true);
+        cur = par[cur];
+        ++guard;
+      }
     }
   }
   for (int r = keep + threadIdx.x; r < a.keep; r += blockDim.x) {  // padding when the tree is smaller than `keep`
@@ -572,8 +637,8 @@ __global__ void __launch_bounds__(256) tree_finalize_kernel(const subspec_tree_f
     a.depths[ob + r] = 0;
     a.probs[ob + r] = 0.f;
     a.position_ids[ob + r] = 0;
-    uint8_t* mrow = a.mask + (ob + r) * a.keep;
-    for (int j = 0; j < a.keep; ++j) mrow[j] = 0;
+    // a padding row attends to itself only, so that a caller who runs all `keep` rows has no fully masked row
+    if (mask_ok && r >= skip) mask_store(mbase + (size_t)(r - skip) * fa.row_stride * mf.esz, prefix + r, mf, true);
   }
   __syncthreads();
   // children CSR in new numbering; a node's children keep their original relative order
@@ -648,11 +713,20 @@ extern "C" int subspec_expand_step(const subspec_expand_args* args, subspec_stre
   if (a.tree_tokens && (!a.tree_parents || !a.tree_probs || !a.tree_depths || a.level < 0 ||
                         1 + (int64_t)(a.level + 1) * a.k > a.tree_stride))
     return SUBSPEC_EINVAL;
+  if (a.draft_mask) {
+    if (!a.tree_tokens || !mask_kind_ok(a.draft_mask_kind) || a.draft_mask_cols < (int64_t)(a.level + 1) * a.k ||
+        a.draft_mask_row_stride < 0 || a.draft_mask_seq_stride < 0 ||
+        (a.draft_mask_row_stride && a.draft_mask_row_stride < a.draft_mask_cols) ||
+        (reinterpret_cast<uintptr_t>(a.draft_mask) % mask_elem_bytes(a.draft_mask_kind)) != 0)
+      return SUBSPEC_EINVAL;
+  }
   size_t need = 0;
   subspec_expand_scratch_bytes(a.batch, a.leaves, a.k, &need);
   if (a.scratch_bytes < need || (reinterpret_cast<uintptr_t>(a.scratch) & 255u)) return SUBSPEC_ESCRATCH;
   KArgs ka;
   ka.a = a;
+  ka.dm_row_stride = a.draft_mask_row_stride ? a.draft_mask_row_stride : a.draft_mask_cols;
+  ka.dm_seq_stride = a.draft_mask_seq_stride ? a.draft_mask_seq_stride : (int64_t)a.k * ka.dm_row_stride;
   char* p = reinterpret_cast<char*>(a.scratch);
   const size_t rows = (size_t)a.batch * a.leaves;
   ka.ticket = reinterpret_cast<int*>(p);
@@ -708,11 +782,22 @@ extern "C" int subspec_tree_finalize(const subspec_tree_finalize_args* args, sub
   const subspec_tree_finalize_args& a = *args;
   if (a.batch < 0 || a.n_nodes < 1 || a.keep < 1 || a.tree_stride < a.n_nodes) return SUBSPEC_EINVAL;
   if (a.n_nodes > 4096 || a.keep > 1024) return SUBSPEC_EUNSUPPORTED;
+  if (a.skip_nodes < 0 || a.skip_nodes > a.keep || !mask_kind_ok(a.mask_kind)) return SUBSPEC_EINVAL;
+  if (a.mask_cols < 0 || a.mask_row_stride < 0 || a.mask_seq_stride < 0) return SUBSPEC_EINVAL;
+  if (a.mask_cols == 0 && a.prefix_length) return SUBSPEC_EINVAL;  // the host cannot size the rows from device values
   if (a.batch == 0) return SUBSPEC_OK;
   if (!a.tree_tokens || !a.tree_parents || !a.tree_probs || !a.tree_depths || !a.keep_idx || !a.tokens ||
       !a.parents || !a.depths || !a.probs || !a.position_ids || !a.mask || !a.child_off || !a.child_idx || !a.n_out)
     return SUBSPEC_EINVAL;
+  FinArgs fa;
+  fa.a = a;
+  fa.cols = a.mask_cols ? a.mask_cols : a.keep;
+  if (fa.cols < a.keep) return SUBSPEC_EINVAL;
+  fa.row_stride = a.mask_row_stride ? a.mask_row_stride : fa.cols;
+  if (fa.row_stride < fa.cols) return SUBSPEC_EINVAL;
+  fa.seq_stride = a.mask_seq_stride ? a.mask_seq_stride : (int64_t)(a.keep - a.skip_nodes) * fa.row_stride;
+  if ((reinterpret_cast<uintptr_t>(a.mask) % mask_elem_bytes(a.mask_kind)) != 0) return SUBSPEC_EINVAL;
   const size_t smem = sizeof(int) * (2 * (size_t)a.n_nodes + 2 * (size_t)a.keep + 1);
-  tree_finalize_kernel<<<a.batch, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  tree_finalize_kernel<<<a.batch, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(fa);
   return cuda_check(cudaGetLastError());
 }

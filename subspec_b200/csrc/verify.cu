@@ -346,6 +346,32 @@ struct KArgs {
   int keep_target;     // streaming kernel: node_target already holds the (sampled) targets
 };
 
+// Node and row counts of a sequence as every kernel uses them: 0 <= n_rows <= n_nodes <= max_nodes.  Values
+// outside that are clamped (the same way in every CTA, so the tickets still add up) and reported.
+__device__ __forceinline__ void seq_counts(const subspec_verify_args& a, int b, int& n_nodes, int& n_rows) {
+  const int nn = a.n_nodes[b], nr = a.n_rows[b];
+  n_nodes = min(max(nn, 0), a.max_nodes);
+  n_rows = min(max(nr, 0), n_nodes);
+  if (n_nodes != nn || n_rows != nr) flag(a.dev_status, SUBSPEC_DEV_BAD_COUNT);
+}
+// The children of node u as a range of child_idx, kept inside [0, n_nodes] whatever child_off holds.
+__device__ __forceinline__ void child_range(const subspec_verify_args& a, int b, int u, int n_nodes, int& cb, int& ce) {
+  const int* coff = a.child_off + (size_t)b * (a.max_nodes + 1);
+  const int lo = coff[u], hi = coff[u + 1];
+  cb = min(max(lo, 0), n_nodes);
+  ce = min(max(hi, cb), n_nodes);
+  if (cb != lo || ce != hi) flag(a.dev_status, SUBSPEC_DEV_BAD_COUNT);
+}
+// A sequence without a decoded row launches no walk: its result is "nothing accepted, nothing emitted".
+__device__ __forceinline__ void write_empty_result(const subspec_verify_args& a, int b) {
+  int* meta = a.out_meta + (size_t)b * 4;
+  meta[0] = meta[1] = meta[2] = meta[3] = 0;
+  if (a.method == SUBSPEC_VERIFY_EXACT_AND_LOSSY && a.out2_meta) {
+    int* m2 = a.out2_meta + (size_t)b * 4;
+    m2[0] = m2[1] = m2[2] = m2[3] = 0;
+  }
+}
+
 // ---- the accept walk, run by one CTA per sequence out of shared memory -----------
 struct WalkSmem {
   int* tok;
@@ -385,8 +411,8 @@ __device__ __forceinline__ WalkSmem carve_walk(unsigned char* base, int n) {
 __device__ void run_walk(const KArgs& ka, int b, unsigned char* smem_raw) {
   const subspec_verify_args& a = ka.a;
   const int N = a.max_nodes;
-  const int n_nodes = a.n_nodes[b];
-  const int n_rows = a.n_rows[b];
+  int n_nodes, n_rows;
+  seq_counts(a, b, n_nodes, n_rows);
   WalkSmem w = carve_walk(smem_raw, N);
   const size_t nb = (size_t)b * N;
   const bool lossy = a.method != SUBSPEC_VERIFY_EXACT;  // the lossy walk runs (alone, or after the exact one)
@@ -429,6 +455,7 @@ __device__ void run_walk(const KArgs& ka, int b, unsigned char* smem_raw) {
     const bool use_entropy = a.gate == SUBSPEC_GATE_ENTROPY;
     const double thr = a.threshold;
     const int window = a.window > 0 ? a.window : 0;
+    bool settled = false;
     for (int round = 0; round <= n_nodes; ++round) {
       if (threadIdx.x == 0) s_changed = 0;
       __syncthreads();
@@ -493,8 +520,13 @@ __device__ void run_walk(const KArgs& ka, int b, unsigned char* smem_raw) {
       __syncthreads();
       const int again = s_changed;
       __syncthreads();  // everybody has read the flag before the next round clears it
-      if (!again) break;
+      if (!again) {
+        settled = true;
+        break;
+      }
     }
+    // a forest settles within height + 1 <= n_nodes rounds; children lists with a loop in them never do
+    if (!settled && threadIdx.x == 0) flag(a.dev_status, SUBSPEC_DEV_BAD_CHILD);
   }
 
   if (threadIdx.x == 0) {
@@ -520,6 +552,10 @@ __device__ void run_walk(const KArgs& ka, int b, unsigned char* smem_raw) {
       int bonus = -1;
       bool go = (w.coff[cur + 1] - w.coff[cur]) > 0;
       while (go) {
+        if (total >= n_nodes) {  // a walk over a tree visits every node at most once: the children lists loop
+          flag(a.dev_status, SUBSPEC_DEV_BAD_CHILD);
+          break;
+        }
         ++total;
         const int s = w.tgt[cur];
         int match = -1;
@@ -563,6 +599,10 @@ __device__ void run_walk(const KArgs& ka, int b, unsigned char* smem_raw) {
       while (true) {
         const int nxt = w.bn[ctx];
         if (nxt < 0) break;
+        if (acc >= n_nodes) {  // longer than any path of a tree: the children lists loop
+          flag(a.dev_status, SUBSPEC_DEV_BAD_CHILD);
+          break;
+        }
         const int t = w.tok[nxt];
         if (L < max_out) {
           out_tok[L] = t;
@@ -633,8 +673,12 @@ __global__ void __launch_bounds__(kThreads, 4) verify_rows_kernel(const KArgs ka
   const int split = blockIdx.x - row * splits;
   const int b = row / a.max_nodes;
   const int u = row - b * a.max_nodes;
-  const int n_rows = a.n_rows[b];
-  if (u >= n_rows) return;
+  int n_nodes, n_rows;
+  seq_counts(a, b, n_nodes, n_rows);
+  if (u >= n_rows) {
+    if (n_rows == 0 && u == 0 && split == 0 && threadIdx.x == 0) write_empty_result(a, b);
+    return;
+  }
 
   const int V = a.vocab;
   const T* rowp = reinterpret_cast<const T*>(a.logits) + (size_t)b * a.seq_stride + (size_t)u * a.row_stride;
@@ -781,9 +825,8 @@ __global__ void __launch_bounds__(kThreads, 4) verify_rows_kernel(const KArgs ka
   }
   if (SOFT) {
     // P[u, token(c)] for every child c of u
-    const int* coff = a.child_off + (size_t)b * (a.max_nodes + 1);
-    const int cb = coff[u], ce = coff[u + 1];
-    const int n_nodes = a.n_nodes[b];
+    int cb, ce;
+    child_range(a, b, u, n_nodes, cb, ce);
     for (int e = cb + threadIdx.x; e < ce; e += kThreads) {
       const int c = a.child_idx[nb + e];
       if (c < 0 || c >= n_nodes) {
@@ -1127,9 +1170,10 @@ __device__ bool sample_row(const KArgs& ka, SampleShared& sh, unsigned char* sme
       a.node_rowsum[nb + u] = 0.f;
     }
     if (a.method != SUBSPEC_VERIFY_EXACT) {  // no child of this node has any probability
-      const int* coff = a.child_off + (size_t)b * (a.max_nodes + 1);
-      const int n_nodes = a.n_nodes[b];
-      for (int e = coff[u] + tid; e < coff[u + 1]; e += kSThreads) {
+      int n_nodes, n_rows_unused, cb, ce;
+      seq_counts(a, b, n_nodes, n_rows_unused);
+      child_range(a, b, u, n_nodes, cb, ce);
+      for (int e = cb + tid; e < ce; e += kSThreads) {
         const int cnode = a.child_idx[nb + e];
         if (cnode >= 0 && cnode < n_nodes) a.node_child_prob[nb + cnode] = 0.f;
       }
@@ -1298,9 +1342,9 @@ __device__ bool sample_row(const KArgs& ka, SampleShared& sh, unsigned char* sme
         a.node_entropy[nb + u] = kLn2 * (lg2f(Zf) - (float)sh.T2 / Zf) / denom;
       }
       // children of u
-      const int* coff = a.child_off + (size_t)b * (a.max_nodes + 1);
-      const int cb = coff[u], ce = coff[u + 1];
-      const int n_nodes = a.n_nodes[b];
+      int n_nodes, n_rows_unused, cb, ce;
+      seq_counts(a, b, n_nodes, n_rows_unused);
+      child_range(a, b, u, n_nodes, cb, ce);
       for (int e = cb; e < ce; ++e) {  // the same trip count and decisions in every thread
         const int cnode = a.child_idx[nb + e];
         if (cnode < 0 || cnode >= n_nodes) {
@@ -1737,10 +1781,12 @@ __device__ bool sample_row_wide(const KArgs& ka, SampleShared& sh, unsigned char
         if (ka.wide_gates) a.node_entropy[nb + u] = 0.f;
       }
       if (ka.wide_gates) {  // no distribution: every child has probability zero
-        const int* coff = a.child_off + (size_t)b * (a.max_nodes + 1);
-        for (int e = coff[u] + tid; e < coff[u + 1]; e += kSThreads) {
+        int n_nodes, n_rows_unused, cb, ce;
+        seq_counts(a, b, n_nodes, n_rows_unused);
+        child_range(a, b, u, n_nodes, cb, ce);
+        for (int e = cb + tid; e < ce; e += kSThreads) {
           const int cn = a.child_idx[nb + e];
-          if (cn >= 0 && cn < a.n_nodes[b]) a.node_child_prob[nb + cn] = 0.f;
+          if (cn >= 0 && cn < n_nodes) a.node_child_prob[nb + cn] = 0.f;
         }
       }
       __syncthreads();
@@ -1994,10 +2040,11 @@ __device__ bool sample_row_wide(const KArgs& ka, SampleShared& sh, unsigned char
   }
   if (gates) {
     // P[u, token(c)] under the filters, for every child c of u
-    const int* coff = a.child_off + (size_t)b * (a.max_nodes + 1);
-    const int n_nodes = a.n_nodes[b];
+    int n_nodes, n_rows_unused, cb, ce;
+    seq_counts(a, b, n_nodes, n_rows_unused);
+    child_range(a, b, u, n_nodes, cb, ce);
     const float invZ = Zs > 0.0 ? (float)(1.0 / Zs) : 0.f;
-    for (int e = coff[u] + tid; e < coff[u + 1]; e += kSThreads) {
+    for (int e = cb + tid; e < ce; e += kSThreads) {
       const int cn = a.child_idx[nb + e];
       if (cn < 0 || cn >= n_nodes) {
         flag(a.dev_status, SUBSPEC_DEV_BAD_CHILD);
@@ -2027,8 +2074,12 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_rows_kernel(const 
   const int row = blockIdx.x;
   const int b = row / a.max_nodes;
   const int u = row - b * a.max_nodes;
-  const int n_rows = a.n_rows[b];
-  if (u >= n_rows) return;
+  int n_nodes, n_rows;
+  seq_counts(a, b, n_nodes, n_rows);
+  if (u >= n_rows) {
+    if (n_rows == 0 && u == 0 && threadIdx.x == 0 && !ka.targets_only) write_empty_result(a, b);
+    return;
+  }
   if constexpr (kWide) {
     if (!sample_row_wide<T, KIND>(ka, sh, smem_raw, b, u)) return;
   } else {
@@ -2114,8 +2165,13 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_walk_kernel(const 
   const subspec_verify_args& a = ka.a;
   const int b = blockIdx.x, N = a.max_nodes;
   const size_t nb = (size_t)b * N;
-  const int n_nodes = a.n_nodes[b], n_rows = a.n_rows[b];
-  const int* coff = a.child_off + (size_t)b * (N + 1);
+  int n_nodes, n_rows;
+  seq_counts(a, b, n_nodes, n_rows);
+  const int* coff_raw = a.child_off + (size_t)b * (N + 1);
+  // children offsets as read, kept inside [0, n_nodes]: whatever they hold, child_idx is read inside the sequence
+  auto coff = [&](int i) { return min(max(coff_raw[i], 0), n_nodes); };
+  for (int i = threadIdx.x; i <= n_nodes; i += kSThreads)
+    if (coff_raw[i] < 0 || coff_raw[i] > n_nodes) flag(a.dev_status, SUBSPEC_DEV_BAD_COUNT);
   const int* cidx = a.child_idx + nb;
   const int* tok = a.token_ids + nb;
   for (int i = threadIdx.x; i < N; i += kSThreads) a.node_target[nb + i] = -1;  // not visited
@@ -2134,12 +2190,17 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_walk_kernel(const 
       flag(a.dev_status, SUBSPEC_DEV_BAD_ROOT);
       cur = 0;
     }
-    const bool go = n_nodes > 0 && (coff[cur + 1] - coff[cur]) > 0;
+    const bool go = n_nodes > 0 && (coff(cur + 1) - coff(cur)) > 0;
     s_cur = cur;
     s_state = n_nodes > 0 ? (go ? 1 : 2) : 0;
   }
   __syncthreads();
+  int visits = 0;  // the same count in every thread: one context per round of the loop
   while (s_state != 0) {
+    if (++visits > n_nodes + 1) {  // a walk stands on every node at most once (plus the bonus draw): the lists loop
+      if (threadIdx.x == 0) flag(a.dev_status, SUBSPEC_DEV_BAD_CHILD);
+      break;
+    }
     const int state = s_state, ctx = s_cur;
     int tgt = -1;
     if (ctx < n_rows) {
@@ -2230,7 +2291,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_walk_kernel(const 
         ++total;
       }
       __syncthreads();
-      const int cb = coff[ctx], ce = coff[ctx + 1];
+      const int cb = coff(ctx), ce = coff(ctx + 1);
       for (int e = cb; e < ce; ++e) {
         if (tid == 0) {
           const int cnode = cidx[e];
@@ -2377,7 +2438,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_walk_kernel(const 
         if (eos >= 0 && (int64_t)x == eos) {
           s_state = 0;
         } else {
-          const int cb2 = coff[cur], ce2 = coff[cur + 1];
+          const int cb2 = coff(cur), ce2 = coff(cur + 1);
           bool more = ce2 - cb2 > 0;
           if (more) {
             int mn = INT_MAX;
@@ -2401,7 +2462,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_walk_kernel(const 
       } else {  // one step of tree_verify.py:61-104
         ++total;
         int match = -1;
-        for (int e = coff[cur]; e < coff[cur + 1]; ++e) {
+        for (int e = coff(cur); e < coff(cur + 1); ++e) {
           const int c = cidx[e];
           if (c < 0 || c >= n_nodes) {
             flag(a.dev_status, SUBSPEC_DEV_BAD_CHILD);
@@ -2427,7 +2488,7 @@ __global__ void __launch_bounds__(kSThreads, 1) verify_sample_walk_kernel(const 
             stop = true;
           } else {
             cur = match;
-            const int cb = coff[cur], ce = coff[cur + 1];
+            const int cb = coff(cur), ce = coff(cur + 1);
             if (ce - cb == 0) {
               stop = true;
             } else {

@@ -148,6 +148,14 @@ def _expand(scores: torch.Tensor, parent_probs: Optional[torch.Tensor], k: int, 
         a.level, a.tree_stride = int(level), tree.stride
         a.tree_tokens, a.tree_parents = tree.tokens.data_ptr(), tree.parents.data_ptr()
         a.tree_probs, a.tree_depths = tree.probs.data_ptr(), tree.depths.data_ptr()
+        a.dev_status = tree.status.data_ptr()
+        if tree.draft_mask is not None:
+            m = tree.draft_mask
+            a.draft_mask, a.draft_mask_kind = m.data_ptr(), tree._mask_kind
+            a.draft_mask_cols = int(m.shape[3])
+            a.draft_mask_row_stride, a.draft_mask_seq_stride = int(m.stride(2)), int(m.stride(0))
+            a.prefix_len = tree.prefix_len.data_ptr()
+            a.draft_position_ids = tree.draft_position_ids.data_ptr()
     a.scratch, a.scratch_bytes = _scratch_for(dev, B, L, k)
     stream = torch.cuda.current_stream(dev).cuda_stream
     _lib.check(_lib.lib().subspec_expand_step(C.byref(a), C.c_void_p(stream)), "subspec_expand_step")
@@ -170,12 +178,49 @@ def topk_sampling_from_logits(logits: torch.Tensor, parent_probs: Optional[torch
     return _expand(logits, parent_probs, sample_k, _lib.IN_LOGITS, temperature)
 
 
-class DraftTreeBatch:
-    """Device-resident draft trees of `batch` sequences grown level by level with `k` nodes per level."""
+_MASK_KIND = {torch.bool: _lib.MASK_BOOL, torch.uint8: _lib.MASK_BOOL, torch.float32: _lib.MASK_ADD_F32,
+              torch.bfloat16: _lib.MASK_ADD_BF16, torch.float16: _lib.MASK_ADD_F16}
 
-    def __init__(self, batch: int, k: int, max_depth: int, device, root_tokens: Optional[torch.Tensor] = None):
+
+def _mask_kind(dtype: torch.dtype) -> int:
+    try:
+        return _MASK_KIND[dtype]
+    except KeyError:
+        raise ValueError(f"mask dtype {dtype}: expected bool (raw mask) or float32 / bfloat16 / float16 (additive)")
+
+
+def _per_sequence_i32(x, batch: int, device) -> torch.Tensor:
+    if isinstance(x, torch.Tensor):
+        t = x.to(device=device, dtype=torch.int32).reshape(-1)
+    elif isinstance(x, (list, tuple)):
+        t = torch.tensor([int(v) for v in x], dtype=torch.int32, device=device)
+    else:
+        t = torch.full((batch,), int(x), dtype=torch.int32, device=device)
+    if t.numel() == 1 and batch > 1:
+        t = t.expand(batch)
+    if t.numel() != batch:
+        raise ValueError(f"expected one value per sequence ({batch}), got {t.numel()}")
+    return t.contiguous()
+
+
+class DraftTreeBatch:
+    """Device-resident draft trees of `batch` sequences grown level by level with `k` nodes per level.
+
+    With `prefix_len` (tokens in front of the first level, the root last among them: the draft's `kv_len`,
+    draft_models/classic_sd.py:57-63) every `expand` also writes the level's draft-side tree mask and
+    position ids -- what `TreeMaskCache.update_tree_mask` / `get_tree_mask` and the speculate loop's
+    `position_ids` hold (draft_models/base.py:93-117, classic_sd.py:71-72, 113) -- into `draft_mask`
+    [batch, 1, k, cols] and `draft_position_ids` [batch, k]: raw bool for `mask_dtype=torch.bool`, the
+    inverted additive form for a float dtype.  `cols` is `max_cache_len` (the reference's static buffer) or,
+    without it, `max(prefix_len) + k * max_depth`.
+    """
+
+    def __init__(self, batch: int, k: int, max_depth: int, device, root_tokens: Optional[torch.Tensor] = None, *,
+                 prefix_len=None, max_cache_len: Optional[int] = None, mask_dtype: torch.dtype = torch.bool):
         self.batch, self.k, self.max_depth = int(batch), int(k), int(max_depth)
         self.device = torch.device(device)
+        if self.device.type == "cuda" and self.device.index is None:  # "cuda" means the current device
+            self.device = torch.device("cuda", torch.cuda.current_device())
         self.stride = 1 + self.k * self.max_depth
         z = dict(device=self.device)
         self.tokens = torch.zeros(batch, self.stride, dtype=torch.int32, **z)
@@ -187,10 +232,38 @@ class DraftTreeBatch:
             self.tokens[:, 0] = root_tokens.to(self.device, torch.int32)
         self.level = 0
         self.parent_probs: Optional[torch.Tensor] = None
+        self.status = torch.zeros(1, dtype=torch.int32, **z)
+        self.prefix_len: Optional[torch.Tensor] = None
+        self.draft_mask: Optional[torch.Tensor] = None
+        self.draft_position_ids: Optional[torch.Tensor] = None
+        if prefix_len is not None:
+            longest = (max(int(v) for v in prefix_len) if isinstance(prefix_len, (list, tuple)) else
+                       int(prefix_len.max()) if isinstance(prefix_len, torch.Tensor) else int(prefix_len))
+            self.prefix_len = _per_sequence_i32(prefix_len, self.batch, self.device)
+            cols = int(max_cache_len) if max_cache_len is not None else longest + self.k * self.max_depth
+            if cols < longest + self.k * self.max_depth:
+                raise ValueError("max_cache_len is shorter than prefix_len + k * max_depth")
+            self._mask_kind = _mask_kind(mask_dtype)
+            self._longest_prefix = longest
+            self.draft_mask = torch.zeros(batch, 1, self.k, cols, dtype=mask_dtype, **z)
+            self.draft_position_ids = torch.zeros(batch, self.k, dtype=torch.int64, **z)
 
     @property
     def n_nodes(self) -> int:
         return 1 + self.level * self.k
+
+    def get_tree_mask(self) -> torch.Tensor:
+        """The draft-side mask after the last `expand`: [batch, 1, k, cols] (all columns of the buffer)."""
+        if self.draft_mask is None:
+            raise ValueError("this batch was created without prefix_len: no draft-side mask is kept")
+        return self.draft_mask
+
+    def check_status(self) -> None:
+        """Synchronise and raise if a kernel of this batch rejected its input."""
+        word = int(self.status.item())
+        if word:
+            self.status.zero_()
+            raise ValueError("draft-tree kernel rejected its input: " + _lib.dev_status_text(word))
 
     @torch.no_grad()
     def expand(self, scores: torch.Tensor, *, from_logits: bool = True, temperature: float = 1.0):
@@ -205,10 +278,43 @@ class DraftTreeBatch:
         return toks, probs, parents
 
     @torch.no_grad()
-    def finalize(self, keep: int, position_offset: Optional[torch.Tensor] = None) -> Dict[str, torch.Tensor]:
-        """prune_to_top_n(keep) + renumbering + tree mask + position ids + children lists, all on the device."""
+    def finalize(self, keep: int, position_offset=None, *, prefix_length=None, skip_nodes: int = 0,
+                 mask_out: Optional[torch.Tensor] = None, mask_dtype: torch.dtype = torch.bool,
+                 mask_cols: Optional[int] = None) -> Dict[str, torch.Tensor]:
+        """prune_to_top_n(keep) + renumbering + tree mask + position ids + children lists, all on the device.
+
+        `prefix_length` (int, list or [batch] tensor) puts that many may-attend columns in front of the tree
+        columns and `skip_nodes` starts the mask rows at that node (Tree.create_attention_mask,
+        cpu_tree.py:263-286).  `mask_out` is a caller's preallocated [batch, 1, rows, max_cache_len] buffer
+        (generators/classic_sd.py:21-55): rows [0, keep - skip_nodes) are written whole, in the buffer's dtype
+        -- bool, or a float dtype for the inverted additive form (utils/utils.py:4-6).  Without it a dense
+        [batch, keep - skip_nodes, mask_cols] tensor of `mask_dtype` is returned (`mask_cols` defaults to
+        max(prefix_length) + keep, which reads the maximum back from the device if the prefix is a tensor).
+        The per-node outputs always describe nodes 0 .. keep - 1; slice them from `skip_nodes` as the
+        reference's get_tree_data(skip_nodes) does.
+        """
         B, dev = self.batch, self.device
-        keep = int(keep)
+        keep, skip = int(keep), int(skip_nodes)
+        if not 0 <= skip <= keep:
+            raise ValueError("skip_nodes must be in [0, keep]")
+        prefix = None if prefix_length is None else _per_sequence_i32(prefix_length, B, dev)
+        if mask_out is not None:
+            if mask_out.dim() == 4 and mask_out.shape[1] == 1:
+                mview = mask_out[:, 0]
+            elif mask_out.dim() == 3:
+                mview = mask_out
+            else:
+                raise ValueError("mask_out must be [batch, 1, rows, cols] or [batch, rows, cols]")
+            if mview.shape[0] != B or mview.shape[1] < keep - skip or mview.stride(2) != 1 or mview.device != dev:
+                raise ValueError("mask_out does not hold [batch, keep - skip_nodes, cols] rows on this device")
+            cols = int(mview.shape[2])
+            tree_mask, kind = mview, _mask_kind(mview.dtype)
+        else:
+            if mask_cols is None:
+                mask_cols = keep + (0 if prefix is None else int(prefix.max()))
+            cols = int(mask_cols)
+            tree_mask = torch.empty(B, keep - skip, cols, dtype=mask_dtype, device=dev)
+            kind = _mask_kind(mask_dtype)
         out = {
             "keep_idx": torch.empty(B, keep, dtype=torch.int32, device=dev),
             "token_ids": torch.empty(B, keep, dtype=torch.int32, device=dev),
@@ -216,7 +322,7 @@ class DraftTreeBatch:
             "depths": torch.empty(B, keep, dtype=torch.int32, device=dev),
             "cumulative_probabilities": torch.empty(B, keep, dtype=torch.float32, device=dev),
             "position_ids": torch.empty(B, keep, dtype=torch.int64, device=dev),
-            "tree_mask": torch.empty(B, keep, keep, dtype=torch.bool, device=dev),
+            "tree_mask": tree_mask,
             "child_off": torch.empty(B, keep + 1, dtype=torch.int32, device=dev),
             "child_idx": torch.zeros(B, keep, dtype=torch.int32, device=dev),
             "n_nodes": torch.empty(B, dtype=torch.int32, device=dev),
@@ -227,12 +333,17 @@ class DraftTreeBatch:
         a.tree_tokens, a.tree_parents = self.tokens.data_ptr(), self.parents.data_ptr()
         a.tree_probs, a.tree_depths = self.probs.data_ptr(), self.depths.data_ptr()
         if position_offset is not None:
-            position_offset = position_offset.to(dev, torch.int32).contiguous()
+            position_offset = _per_sequence_i32(position_offset, B, dev)
             a.position_offset = position_offset.data_ptr()
         a.keep_idx, a.tokens, a.parents = (out[n].data_ptr() for n in ("keep_idx", "token_ids", "parent_indices"))
         a.depths, a.probs = out["depths"].data_ptr(), out["cumulative_probabilities"].data_ptr()
-        a.position_ids, a.mask = out["position_ids"].data_ptr(), out["tree_mask"].data_ptr()
+        a.position_ids, a.mask = out["position_ids"].data_ptr(), tree_mask.data_ptr()
         a.child_off, a.child_idx, a.n_out = (out[n].data_ptr() for n in ("child_off", "child_idx", "n_nodes"))
+        a.dev_status = self.status.data_ptr()
+        a.prefix_length = 0 if prefix is None else prefix.data_ptr()
+        a.skip_nodes, a.mask_kind = skip, kind
+        a.mask_cols = cols
+        a.mask_row_stride, a.mask_seq_stride = int(tree_mask.stride(1)), int(tree_mask.stride(0))
         stream = torch.cuda.current_stream(dev).cuda_stream
         _lib.check(_lib.lib().subspec_tree_finalize(C.byref(a), C.c_void_p(stream)), "subspec_tree_finalize")
         return out

@@ -115,6 +115,50 @@ def sampled_case(seed: int, n_nodes: int, max_depth: int, max_branch: int, vocab
     return tree, logits, uniforms
 
 
+def expand_level_logits(seed: int, level: int, k: int, vocab: int, dtype: torch.dtype, sigma: float = 3.0) -> torch.Tensor:
+    """Draft logits [1, leaves, vocab] of one depth step of one sequence (config 3: sigma * randn; one leaf on
+    the first step, k afterwards).  Every (sequence seed, level) has a generator of its own, so a test can
+    rebuild any level without drawing the ones before it."""
+    gen = torch.Generator().manual_seed(int(seed) * 1000 + int(level))
+    leaves = 1 if level == 0 else int(k)
+    return (torch.randn(1, leaves, vocab, generator=gen) * sigma).to(dtype)
+
+
+def config5_wave(seq_ids, variant: str, device, *, nodes: int = 64, vocab: int = 152064, with_logits: bool = True):
+    """Trees (host) and bf16 logits [len(seq_ids), nodes, vocab] (on `device`) of the sharded-step workload for
+    the given global sequence ids; everything is seeded by the id, so any rank can rebuild any sequence.
+    `variant` "literal": 3 * randn with one drafted child boosted by +6 at 60 % of the inner nodes;
+    "peaked": that child set to the row maximum + 4, so that walks, gates and compaction have work to do."""
+    trees = []
+    for sid in seq_ids:
+        gen = torch.Generator().manual_seed(1_000_003 * 5 + sid)
+        trees.append(random_tree(nodes, 8, 4, vocab, gen))
+    if not with_logits:
+        return trees, None
+    S = len(seq_ids)
+    dgen = torch.Generator(device=device).manual_seed(7_000_001 + seq_ids[0])
+    logits = torch.empty(S, nodes, vocab, dtype=torch.bfloat16, device=device)
+    for b in range(S):  # fp32 noise generated one sequence at a time to bound the transient footprint
+        logits[b] = (torch.randn(nodes, vocab, generator=dgen, device=device) * 3.0).to(torch.bfloat16)
+    bi, ui, ti = [], [], []
+    for b, (sid, st) in enumerate(zip(seq_ids, trees)):
+        cgen = torch.Generator().manual_seed(9_000_011 + sid)
+        ch = st.children()
+        for u in range(st.n):
+            if ch[u] and float(torch.rand((), generator=cgen)) < 0.6:
+                c = ch[u][int(torch.randint(len(ch[u]), (1,), generator=cgen))]
+                bi.append(b)
+                ui.append(u)
+                ti.append(int(st.token_ids[c]))
+    bi, ui, ti = (torch.tensor(x, device=device) for x in (bi, ui, ti))
+    if variant == "peaked":
+        rowmax = logits.float().amax(dim=-1)
+        logits[bi, ui, ti] = (rowmax[bi, ui] + 4.0).to(torch.bfloat16)
+    else:
+        logits[bi, ui, ti] = (logits[bi, ui, ti].float() + 6.0).to(torch.bfloat16)
+    return trees, logits
+
+
 def random_page_table(batch: int, pages_per_seq: int, gen: torch.Generator) -> torch.Tensor:
     """[batch, pages_per_seq] int32: a random permutation of the pool's pages split across sequences."""
     perm = torch.randperm(batch * pages_per_seq, generator=gen)

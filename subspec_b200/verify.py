@@ -102,7 +102,10 @@ class VerifyWorkspace:
         return self._in_host.numpy()[off:off + cnt]
 
     def set_trees(self, flats: Sequence[Tuple[np.ndarray, np.ndarray, np.ndarray, int, int]]) -> None:
-        """Stage `batch` flattened trees: (token_ids, child_off, child_idx, n_rows, root) per sequence."""
+        """Stage `batch` flattened trees: (token_ids, child_off, child_idx, n_rows, root) per sequence.
+
+        Children lists that are not a forest (an index outside the tree, a node listed twice, a loop) are
+        rejected here with ValueError, before anything is launched; so are row counts beyond the node count."""
         B, N = self.batch, self.max_nodes
         if len(flats) != B:
             raise ValueError(f"expected {B} trees, got {len(flats)}")
@@ -116,6 +119,9 @@ class VerifyWorkspace:
                 raise ValueError(f"tree {b} has {n} nodes; workspace holds {N}")
             if n and (int(t.min()) < 0 or int(t.max()) > 0x7FFFFFFF):
                 raise ValueError("token ids must fit in int32")
+            if not 0 <= int(n_rows) <= n:
+                raise ValueError(f"tree {b}: {int(n_rows)} decoded rows for {n} nodes")
+            check_forest(o, i, n, b)
             tok[b, :n] = t
             off[b, :n + 1] = o
             off[b, n + 1:] = o[-1] if n else 0
@@ -154,6 +160,8 @@ class VerifyWorkspace:
             raise ValueError("logits live on another device than the workspace")
         if logits.stride(2) != 1:
             logits = logits.contiguous()
+        if int(self.host_view("n_rows").max(initial=0)) > int(logits.shape[1]):
+            raise ValueError(f"a tree has more decoded rows than logits has rows ({int(logits.shape[1])})")
         a = _lib.VerifyArgs()
         a.struct_size = C.sizeof(_lib.VerifyArgs)
         a.batch, a.max_nodes, a.vocab = B, N, int(logits.shape[2])
@@ -226,11 +234,18 @@ _workspaces: Dict[Tuple[int, int, int], VerifyWorkspace] = {}
 
 
 def get_workspace(batch: int, n_nodes: int, device: torch.device) -> VerifyWorkspace:
-    """Cached workspace, node capacity rounded up to a multiple of 64."""
+    """Cached workspace, node capacity rounded up to a multiple of 64.
+
+    One workspace per (device, batch, capacity) serves every caller of `verify_tree` / `verify_tree_batched`
+    in the process: it is meant for one stream and one host thread at a time, as the reference's generators run
+    (calls that overlap on the GPU would share its scratch and output blocks; give those a `VerifyWorkspace`
+    of their own through the `workspace` argument)."""
     cap = min(1024, max(64, _align(int(n_nodes), 64)))
     if n_nodes > 1024:
         raise ValueError("trees of more than 1024 nodes are not supported")
-    key = (torch.device(device).index or 0, int(batch), cap)
+    dev = torch.device(device)
+    index = dev.index if dev.index is not None else torch.cuda.current_device()  # "cuda" = the current device
+    key = (int(index), int(batch), cap)
     ws = _workspaces.get(key)
     if ws is None:
         ws = _workspaces[key] = VerifyWorkspace(batch, cap, device)
@@ -258,6 +273,38 @@ def flatten_tree(tree, skip_nodes: int = 0, limit: Optional[int] = None, restric
                 idx.append(cl)
         off[v + 1] = len(idx)
     return tok, off, np.asarray(idx, dtype=np.int32)
+
+
+def check_forest(child_off: np.ndarray, child_idx: np.ndarray, n: int, which: int = 0) -> None:
+    """Raise ValueError unless the children lists (CSR over n nodes) describe a forest: offsets ascending from 0,
+    every child index inside [0, n), no node listed as a child twice, no loop.  The kernels bound their walks
+    anyway; a malformed tree is refused here so that no launch ever sees one."""
+    off = np.asarray(child_off, dtype=np.int64).reshape(-1)
+    if off.shape[0] != n + 1 or (n + 1 and off[0] != 0) or np.any(np.diff(off) < 0):
+        raise ValueError(f"tree {which}: children offsets must ascend from 0 over {n} nodes")
+    m = int(off[-1]) if n + 1 else 0
+    idx = np.asarray(child_idx, dtype=np.int64).reshape(-1)
+    if m > n or idx.shape[0] < m:
+        raise ValueError(f"tree {which}: {m} child entries for {n} nodes")
+    if m == 0:
+        return
+    idx = idx[:m]
+    if idx.min() < 0 or idx.max() >= n:
+        raise ValueError(f"tree {which}: a child index lies outside [0, {n})")
+    if np.bincount(idx, minlength=n).max() > 1:
+        raise ValueError(f"tree {which}: a node is listed as a child more than once")
+    parent = np.full(n, -1, dtype=np.int64)
+    parent[idx] = np.repeat(np.arange(n, dtype=np.int64), np.diff(off))
+    if np.all(parent < np.arange(n)):  # children behind their parents, the usual numbering: no loop possible
+        return
+    up = parent.copy()  # pointer jumping: after ceil(log2 n) + 1 doublings every node of a forest has left it
+    for _ in range(max(1, int(n).bit_length()) + 1):
+        live = up >= 0
+        if not live.any():
+            return
+        up = np.where(live, up[np.where(live, up, 0)], -1)
+    if (up >= 0).any():
+        raise ValueError(f"tree {which}: the children lists contain a loop")
 
 
 def _children_csr(children_lists: Sequence[Sequence[int]]):

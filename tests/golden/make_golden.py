@@ -2,7 +2,7 @@
 
 Usage (only where a read-only checkout of NYCU-EDgeAi/subspec is available):
 
-    python tests/golden/make_golden.py --reference /path/to/subspec [--only verify|sampled|expand|kv|lossy_unit]
+    python tests/golden/make_golden.py --reference /path/to/subspec [--only verify|sampled|expand|expand_chain|kv|kv_hf|lossy_unit]
 
 The reference is imported, never copied.  Two third-party modules it imports but
 does not need on this path (`nvtx`, `prettytable`) are replaced by throw-away
@@ -14,7 +14,9 @@ depend on the RNG stream.  Outputs written:
     sampled_cases.json                     verify_tree with do_sample=True and injected uniforms
     lossy_unit_cases.json                  every call made by the reference's tests/test_lossy_tree_verify.py
     expand_cases.json / expand_small.npz   _topk_flatten / Tree / TreeMaskCache results
+    expand_chain.json                      ten-level expansions at the benchmark's vocabulary, pruned to 64 nodes
     kv_cases.json                          KvCachePool.reorder_cache_with_offset checksums
+    kv_hf_cases.json                       TreeStaticCache / TreeDynamicCache.reorder_cache_with_offset checksums
 """
 from __future__ import annotations
 
@@ -51,8 +53,9 @@ def import_reference(ref: str):
     import specdecodes.models.generators.classic_sd as csd
     import specdecodes.models.draft_models.base as db
     import specdecodes.models.utils.flashinfer.cache_manager as cm
+    import specdecodes.models.utils.cache_utils as cu
     from specdecodes.models.utils.wandb_logger import wandb_logger
-    return dict(tv=tv, ltv=ltv, ct=ct, gb=gb, csd=csd, db=db, cm=cm, wandb_logger=wandb_logger)
+    return dict(tv=tv, ltv=ltv, ct=ct, gb=gb, csd=csd, db=db, cm=cm, cu=cu, wandb_logger=wandb_logger)
 
 
 def ref_tree(ct, tree: synthetic.SynthTree):
@@ -375,8 +378,13 @@ def gen_expand(ref, out_dir: Path):
 
     db, ct = ref["db"], ref["ct"]
     cases, small = [], {}
+    # the last four keep at least as many nodes as the tree has: prune_to_top_n then leaves the numbering alone
+    # (cpu_tree.py:176-177), which is the reference's default (max_verify_tokens = max_depth * topk_len + 1)
     cfgs = [(300, 4, 5, "float32", 1.0, 12), (300, 4, 5, "bfloat16", 1.0, 12), (1000, 6, 4, "float16", 0.7, 16),
-            (2048, 16, 3, "float32", 1.0, 32), (97, 3, 6, "float32", 0.2, 10)]
+            (2048, 16, 3, "float32", 1.0, 32), (97, 3, 6, "float32", 0.2, 10),
+            (300, 4, 5, "float32", 1.0, 21), (300, 4, 3, "bfloat16", 1.0, 32), (1000, 6, 4, "float16", 0.7, 25),
+            (500, 5, 4, "float32", 1.0, 64)]
+    PREFIX, SKIP = 7, 2
     for ci, (V, k, depth, dtype, T, keep) in enumerate(cfgs):
         gen = torch.Generator().manual_seed(700 + ci)
         dt = DT[dtype]
@@ -384,6 +392,10 @@ def gen_expand(ref, out_dir: Path):
         tree_data = db.TreeData()
         mask_cache = db.TreeMaskCache(prefix_len=5, sample_len=k, max_cache_len=None, dtype=torch.float32,
                                       device="cpu")
+        static_len = 5 + k * depth + 3
+        static_cache = db.TreeMaskCache(prefix_len=5, sample_len=k, max_cache_len=static_len, dtype=torch.float32,
+                                        device="cpu")
+        assert static_cache.tree_mask_update_method == "static"
         parent_probs = torch.ones(1, 1, dtype=dt)
         steps = []
         for d in range(depth):
@@ -393,9 +405,11 @@ def gen_expand(ref, out_dir: Path):
             tok, val, par = db.DraftModelBase._topk_flatten(holder, probs, parent_probs, k)
             tree_data.update(tok, val, par)
             mask = mask_cache.update_tree_mask(par, return_invert=False)
+            smask = static_cache.update_tree_mask(par, return_invert=False)
             small[f"c{ci}/logits{d}"] = logits.float().numpy()
             steps.append(dict(tokens=tok.tolist(), parents=par.tolist(), probs=val.float().tolist(),
-                              mask=mask[0, 0].to(torch.uint8).tolist()))
+                              mask=mask[0, 0].to(torch.uint8).tolist(),
+                              static_mask=smask[0, 0].to(torch.uint8).tolist()))
             parent_probs = val
         tree = ct.Tree(torch.tensor(7), dt)
         tree.add_nodes(*tree_data.get_data())
@@ -417,10 +431,155 @@ def gen_expand(ref, out_dir: Path):
                         probs=pruned["cumulative_probabilities"].float().tolist(),
                         children=[list(n.children) for n in tree.nodes],
                         leaves=list(tree.available_leaves),
-                        mask=tree.create_attention_mask()[0, 0].to(torch.uint8).tolist())))
+                        mask=tree.create_attention_mask()[0, 0].to(torch.uint8).tolist(),
+                        prefix=PREFIX, skip=SKIP,
+                        mask_prefix_skip=tree.create_attention_mask(prefix_length=PREFIX, skip_nodes=SKIP)[0, 0]
+                        .to(torch.uint8).tolist(),
+                        data_skip={k_: v_.tolist() for k_, v_ in tree.get_tree_data(SKIP).items()
+                                   if k_ != "cumulative_probabilities"})))
     (out_dir / "expand_cases.json").write_text(json.dumps({"cases": cases}))
     np.savez_compressed(out_dir / "expand_small.npz", **small)
     print(f"expand: {len(cases)} cases; cumulative probabilities all distinct: {[c['probs_distinct'] for c in cases]}")
+
+
+def _rule_topk(scores_flat: torch.Tensor, k: int):
+    """The k best flat indices under (value descending, index ascending): the order the CUDA path uses."""
+    v = scores_flat.float()
+    order = sorted(range(v.numel()), key=lambda i: (-float(v[i]), i)) if v.numel() <= 4096 else None
+    if order is None:
+        top = torch.topk(v, min(4 * k, v.numel()), sorted=True)
+        cand = sorted(zip((-top.values).tolist(), top.indices.tolist()))
+        assert cand[k - 1][0] < cand[-1][0] or len(cand) == v.numel(), "the tie at the cut is wider than the margin"
+        return [i for _, i in cand[:k]]
+    return order[:k]
+
+
+def _rounding_margin(p64: torch.Tensor, dt: torch.dtype) -> float:
+    """Smallest relative distance of the exact probabilities `p64` from a rounding boundary of `dt`: a
+    probability computed with a relative error below it rounds to the same 16-bit value."""
+    b = p64.to(dt)
+    bits = b.view(torch.int16).to(torch.int32)
+    up = (bits + 1).to(torch.int16).view(dt).double()
+    dn = (bits - 1).to(torch.int16).view(dt).double()
+    bd = b.double()
+    edge = torch.minimum(((bd + up) / 2 - p64).abs(), ((bd + dn) / 2 - p64).abs())
+    return float((edge / p64).min())
+
+
+def gen_expand_chain(ref, out_dir: Path):
+    """Config-3 expansions through the reference: per sequence ten levels of _topk_flatten at V = 128256, k = 16,
+    TreeData -> Tree.add_nodes -> prune_to_top_n(64) -> get_tree_data / create_attention_mask.  Inputs are
+    rebuilt from seeds (synthetic.expand_level_logits); only results are stored.  `rule_agrees` says whether the
+    reference's choices coincide with the (value desc, index asc) order everywhere, i.e. whether torch.topk's
+    unspecified tie order played no part: those sequences pin indices and structure, the others values only.
+
+    Margin audit: discrete outputs come from floating-point inputs, so a seed is used only if none of the 2k best
+    candidates of any level has an exact (fp64) probability within MARGIN (relative) of a 16-bit rounding
+    boundary, and -- fp32, where indices are compared -- no two of them are closer than MARGIN; for 16-bit
+    dtypes the reference's own CPU probabilities of those candidates must also equal the exactly rounded ones.
+    Other seeds are skipped and the next one is tried.  The smallest margin met is stored."""
+    from types import SimpleNamespace
+
+    db, ct = ref["db"], ref["ct"]
+    V, k, depth, keep = 128256, 16, 10, 64
+    MARGIN = 5e-6
+    seqs, skipped = [], []
+    for dtype, first, want in (("bfloat16", 3000, 32), ("float32", 3100, 4)):
+        dt = DT[dtype]
+        seed, have = first - 1, 0
+        while have < want:
+            seed += 1
+            holder = SimpleNamespace()
+            tree_data = db.TreeData()
+            parent_probs = torch.ones(1, 1, dtype=dt)
+            levels, agrees, margin = [], True, float("inf")
+            for d in range(depth):
+                logits = synthetic.expand_level_logits(seed, d, k, V, dt)
+                probs = torch.softmax(logits / 1.0, dim=-1)
+                tok, val, par = db.DraftModelBase._topk_flatten(holder, probs, parent_probs, k)
+                flat = (par * V + tok)[0].tolist()
+                scores = (probs * parent_probs.unsqueeze(-1)).view(-1)
+                agrees = agrees and flat == _rule_topk(scores, k)
+                p64 = torch.softmax(logits.double(), dim=-1)
+                s64 = (p64 * parent_probs.double().unsqueeze(-1)).view(-1)
+                top = torch.topk(s64, 2 * k, sorted=True)
+                if dt != torch.float32:
+                    margin = min(margin, _rounding_margin(p64.view(-1)[top.indices], dt))
+                    # torch's CPU softmax of a 16-bit tensor is itself up to ~1e-4 off on peaked rows (it adds up
+                    # exponentials already rounded to the dtype), enough to round the other way now and then:
+                    # such seeds pin the CPU build's rounding, not the reference's arithmetic, and are skipped
+                    if not torch.equal(probs.view(-1)[top.indices], p64.view(-1)[top.indices].to(dt)):
+                        margin = 0.0
+                else:
+                    margin = min(margin, float(((top.values[:-1] - top.values[1:]) / top.values[:-1]).min()))
+                tree_data.update(tok, val, par)
+                levels.append(dict(tokens=tok[0].tolist(), parents=par[0].tolist(), probs=val[0].float().tolist()))
+                parent_probs = val
+            if margin < MARGIN:
+                skipped.append(seed)
+                continue
+            have += 1
+            tree = ct.Tree(torch.tensor(11), dt)
+            tree.add_nodes(*tree_data.get_data())
+            cum = torch.tensor([n.cumulative_probability for n in tree.nodes], dtype=dt)
+            keep_idx = tree.prune_to_top_n(keep).tolist()
+            agrees_prune = keep_idx == _rule_topk(cum, keep)
+            data = tree.get_tree_data()
+            mask = tree.create_attention_mask()[0, 0]
+            rows = [int(sum(1 << j for j in range(mask.shape[1]) if bool(mask[i, j]))) for i in range(mask.shape[0])]
+            seqs.append(dict(seed=seed, dtype=dtype, levels=levels, rule_agrees=bool(agrees), min_margin=margin,
+                             rule_agrees_prune=bool(agrees and agrees_prune),
+                             pruned=dict(keep_idx=keep_idx, token_ids=data["token_ids"].tolist(),
+                                         depths=data["depths"].tolist(),
+                                         parent_indices=data["parent_indices"].tolist(),
+                                         probs=data["cumulative_probabilities"].float().tolist(),
+                                         children=[list(n.children) for n in tree.nodes], mask_rows=rows)))
+    (out_dir / "expand_chain.json").write_text(json.dumps(
+        dict(vocab=V, k=k, depth=depth, keep=keep, root_token=11, margin=MARGIN, skipped_seeds=skipped,
+             sequences=seqs)))
+    print(f"expand chain: {len(seqs)} sequences ({len(skipped)} seeds skipped by the margin audit, smallest margin "
+          f"kept {min(s_['min_margin'] for s_ in seqs):.2e}); tie order irrelevant in "
+          f"{sum(s_['rule_agrees'] for s_ in seqs)} expansions and {sum(s_['rule_agrees_prune'] for s_ in seqs)} prunes")
+
+
+def gen_kv_hf(ref, out_dir: Path):
+    """The HF-layout reorders, run by the reference's own methods on a stand-in object that carries the two
+    attributes they touch (`key_cache`, `value_cache`; the installed transformers' cache classes no longer
+    have them, so the classes themselves cannot be instantiated): TreeStaticCache.reorder_cache_with_offset
+    (cache_utils.py:166-208) and TreeDynamicCache.reorder_cache_with_offset (:85-103), called as the
+    generators call them (dim=2, classic_sd.py:254)."""
+    from types import SimpleNamespace
+
+    sys.path.insert(0, str(ROOT))
+    from oracle.kv_oracle import checksum
+    cu = ref["cu"]
+    cases = []
+    seed = 500
+    for (layers, H, T, D, dtype) in [(5, 4, 96, 128, "bfloat16"), (3, 2, 40, 64, "float16"), (2, 1, 33, 8, "float32"),
+                                      (28, 4, 160, 128, "bfloat16")]:
+        for rep in range(3):
+            seed += 1
+            gen = torch.Generator().manual_seed(seed)
+            ks = [torch.randn(1, H, T, D, generator=gen).to(DT[dtype]) for _ in range(layers)]
+            vs = [torch.randn(1, H, T, D, generator=gen).to(DT[dtype]) for _ in range(layers)]
+            tree_n = min(24, T // 2)
+            offset = int(torch.randint(0, T - tree_n + 1, (1,), generator=gen))
+            n = int(torch.randint(1, min(11, tree_n) + 1, (1,), generator=gen))
+            beam = torch.sort(torch.randperm(tree_n - 1, generator=gen)[:n - 1] + 1).values
+            beam = torch.cat([torch.zeros(1, dtype=torch.long), beam]) if rep != 2 else \
+                torch.sort(torch.randperm(tree_n, generator=gen)[:n]).values
+            before = checksum(torch.stack(ks + vs))
+            st = SimpleNamespace(key_cache=[t.clone() for t in ks], value_cache=[t.clone() for t in vs])
+            cu.TreeStaticCache.reorder_cache_with_offset(st, beam, new_chunk_len=tree_n, offset=offset, dim=2)
+            dy = SimpleNamespace(key_cache=[t.clone() for t in ks], value_cache=[t.clone() for t in vs])
+            cu.TreeDynamicCache.reorder_cache_with_offset(dy, beam, new_chunk_len=tree_n, offset=offset, dim=2)
+            cases.append(dict(seed=seed, layers=layers, heads=H, tokens=T, head_dim=D, dtype=dtype, offset=offset,
+                              tree_n=tree_n, beam=beam.tolist(), before=before,
+                              static_after=checksum(torch.stack(st.key_cache + st.value_cache)),
+                              dynamic_after=checksum(torch.stack(dy.key_cache + dy.value_cache)),
+                              dynamic_tokens=int(dy.key_cache[0].shape[2])))
+    (out_dir / "kv_hf_cases.json").write_text(json.dumps({"cases": cases}, indent=1))
+    print(f"kv hf: {len(cases)} cases")
 
 
 def main():
@@ -434,8 +593,12 @@ def main():
         gen_verify(ref, HERE)
     if args.only in (None, "expand"):
         gen_expand(ref, HERE)
+    if args.only in (None, "expand_chain"):
+        gen_expand_chain(ref, HERE)
     if args.only in (None, "kv"):
         gen_kv(ref, HERE)
+    if args.only in (None, "kv_hf"):
+        gen_kv_hf(ref, HERE)
     if args.only in (None, "sampled"):
         gen_sampled(ref, HERE)
     if args.only in (None, "lossy_unit"):

@@ -64,6 +64,31 @@ def kv_pool(case) -> torch.Tensor:
 
 
 @lru_cache(maxsize=None)
+def kv_hf_cases():
+    return json.loads((GOLDEN / "kv_hf_cases.json").read_text())["cases"]
+
+
+def kv_hf_tensors(case):
+    """(key tensors, value tensors), each a list of [1, H, T, D], as the golden generator drew them."""
+    gen = torch.Generator().manual_seed(case["seed"])
+    shape = (1, case["heads"], case["tokens"], case["head_dim"])
+    ks = [torch.randn(shape, generator=gen).to(DT[case["dtype"]]) for _ in range(case["layers"])]
+    vs = [torch.randn(shape, generator=gen).to(DT[case["dtype"]]) for _ in range(case["layers"])]
+    return ks, vs
+
+
+@lru_cache(maxsize=None)
+def expand_chain():
+    """Config-3 expansions run by the reference (ten levels, V = 128256, k = 16, pruned to 64 nodes)."""
+    return json.loads((GOLDEN / "expand_chain.json").read_text())
+
+
+def chain_logits(chain, seq, level: int) -> torch.Tensor:
+    """[1, leaves, vocab] draft logits of one level of one golden sequence, rebuilt from its seed."""
+    return synthetic.expand_level_logits(seq["seed"], level, chain["k"], chain["vocab"], DT[seq["dtype"]])
+
+
+@lru_cache(maxsize=None)
 def expand_cases():
     return json.loads((GOLDEN / "expand_cases.json").read_text())["cases"]
 

@@ -56,28 +56,215 @@ def test_golden_steps_fused_from_logits(cuda_lib):
             pp = ref_vals
 
 
+def _ordered_tree(case):
+    """The tree the stated tie order (value desc, flat index asc) gives on a golden case's probabilities: equal to
+    the reference's wherever no scores tie, and the one deterministic answer where they do."""
+    dt = DT[case["dtype"]]
+    pp = torch.ones(1, 1, dtype=dt)
+    t = eo.FlatTree(7)
+    levels = []
+    for d in range(case["depth"]):
+        probs = eo.draft_probs(golden_io.expand_logits(case, d), case["temperature"])
+        tok, val, par = eo.topk_flatten_ordered(probs, pp, case["k"])
+        t.add_nodes(tok.unsqueeze(0), val.unsqueeze(0), par.unsqueeze(0))
+        levels.append((tok[0].tolist(), par[0].tolist(), val[0].float().tolist()))
+        pp = val
+    return t, levels
+
+
+def _rows_to_lists(mask2d):
+    return mask2d.to(torch.uint8).cpu().tolist()
+
+
 def test_device_resident_tree_matches_reference(cuda_lib):
-    """DraftTreeBatch: expand level by level on the device, finalize = prune_to_top_n + mask + position ids."""
+    """DraftTreeBatch: expand level by level on the device, finalize = prune_to_top_n + mask + position ids.
+    Every golden case, all dtypes, including trees no larger than `keep` (left in insertion order like the
+    reference, cpu_tree.py:176-177).  Where cumulative probabilities tie (16-bit cases) the reference's node
+    order depends on torch.topk's open tie order: there the values are pinned by the golden and the structure
+    by the ordered restatement."""
+    seen_no_prune = seen_16bit = 0
     for case in golden_io.expand_cases():
-        if not case["probs_distinct"] or case["dtype"] != "float32":
-            continue
-        tree = DraftTreeBatch(1, case["k"], case["depth"], "cuda", root_tokens=torch.tensor([7]))
+        dt = DT[case["dtype"]]
+        tree = DraftTreeBatch(1, case["k"], case["depth"], "cuda", root_tokens=torch.tensor([7]), prefix_len=5,
+                              max_cache_len=5 + case["k"] * case["depth"] + 3)
+        oracle_tree, levels = _ordered_tree(case)
+        exact_ref = case["probs_distinct"] and all(
+            lv[0] == g["tokens"][0] and lv[1] == g["parents"][0] for lv, g in zip(levels, case["steps"]))
         for d in range(case["depth"]):
             probs = eo.draft_probs(golden_io.expand_logits(case, d), case["temperature"])
-            tree.expand(probs.cuda(), from_logits=False)
+            tok, val, par = tree.expand(probs.cuda(), from_logits=False)
+            g = case["steps"][d]
+            assert val[0].float().cpu().tolist() == g["probs"][0], (case["name"], d)  # the reference's values
+            assert tok[0].tolist() == levels[d][0] and par[0].tolist() == levels[d][1], (case["name"], d)
+            # draft-side mask of the level, written by the same kernel into the static buffer
+            want = torch.zeros(case["k"], tree.draft_mask.shape[3], dtype=torch.bool)
+            rows = torch.tensor(g["static_mask"], dtype=torch.bool) if exact_ref else None
+            prev = torch.ones(1, 5, dtype=torch.bool)
+            for dd in range(d + 1):
+                prev = eo.mask_rows(prev, levels[dd][1])
+            want[:, :prev.shape[1]] = prev
+            assert torch.equal(tree.get_tree_mask()[0, 0].cpu(), want), (case["name"], d)
+            if rows is not None:
+                assert torch.equal(tree.get_tree_mask()[0, 0].cpu(), rows), (case["name"], d)
+            assert tree.draft_position_ids[0].tolist() == [5 + d] * case["k"]
         out = tree.finalize(case["keep"], position_offset=torch.tensor([11]))
+        tree.check_status()
         g = case["pruned"]
         n = len(g["token_ids"])
+        no_prune = n == len(case["full"]["token_ids"])
+        seen_no_prune += no_prune
+        seen_16bit += dt != torch.float32
         assert int(out["n_nodes"][0]) == n
-        assert out["keep_idx"][0, :n].tolist() == g["keep_idx"]
-        assert out["token_ids"][0, :n].tolist() == g["token_ids"]
-        assert out["parent_indices"][0, :n].tolist() == g["parent_indices"]
-        assert out["depths"][0, :n].tolist() == g["depths"]
-        assert out["cumulative_probabilities"][0, :n].tolist() == g["probs"]
-        assert out["position_ids"][0, :n].tolist() == [d + 11 for d in g["depths"]]
-        assert out["tree_mask"][0, :n, :n].to(torch.uint8).tolist() == g["mask"]
+        assert sorted(out["cumulative_probabilities"][0, :n].tolist(), reverse=True) == sorted(g["probs"], reverse=True)
+        keep_idx = oracle_tree.prune_to_top_n(case["keep"], dt, ordered=True)
+        assert out["keep_idx"][0, :n].tolist() == keep_idx
+        assert out["token_ids"][0, :n].tolist() == oracle_tree.token
+        assert out["parent_indices"][0, :n].tolist() == oracle_tree.parent
+        assert out["depths"][0, :n].tolist() == oracle_tree.depth
+        assert out["position_ids"][0, :n].tolist() == [d + 11 for d in oracle_tree.depth]
+        assert _rows_to_lists(out["tree_mask"][0, :n, :n]) == _rows_to_lists(oracle_tree.mask())
         off, idx = out["child_off"][0].tolist(), out["child_idx"][0].tolist()
-        assert [idx[off[i]:off[i + 1]] for i in range(n)] == g["children"]
+        assert [idx[off[i]:off[i + 1]] for i in range(n)] == oracle_tree.children
+        if no_prune:
+            assert keep_idx == list(range(n))
+        if exact_ref:  # no ties anywhere: the reference's own numbering, node for node
+            assert out["keep_idx"][0, :n].tolist() == g["keep_idx"]
+            assert out["token_ids"][0, :n].tolist() == g["token_ids"]
+            assert out["parent_indices"][0, :n].tolist() == g["parent_indices"]
+            assert out["depths"][0, :n].tolist() == g["depths"]
+            assert out["cumulative_probabilities"][0, :n].tolist() == g["probs"]
+            assert _rows_to_lists(out["tree_mask"][0, :n, :n]) == g["mask"]
+            assert [idx[off[i]:off[i + 1]] for i in range(n)] == g["children"]
+        # padding behind a tree smaller than `keep`: no node, and a row that attends to itself only
+        for r in range(n, case["keep"]):
+            assert int(out["keep_idx"][0, r]) == -1
+            assert out["tree_mask"][0, r].nonzero().flatten().tolist() == [r]
+    assert seen_no_prune >= 4 and seen_16bit >= 4
+
+
+@pytest.mark.parametrize("mask_dtype", [torch.bool, torch.float32, torch.bfloat16, torch.float16])
+def test_finalize_writes_prefix_skip_and_static_buffer(cuda_lib, mask_dtype):
+    """The verifier-side mask in the forms the reference's generator hands to the target forward
+    (generators/classic_sd.py:33-55, 73-77): prefix columns, rows from skip_nodes, spliced into a preallocated
+    [1, 1, max_verify, max_cache_len] buffer, optionally inverted to the additive form (utils/utils.py:4-6)."""
+    from subspec_b200.draft import invert_mask
+
+    checked = 0
+    for case in golden_io.expand_cases():
+        g = case["pruned"]
+        n = len(g["token_ids"])
+        _, levels = _ordered_tree(case)
+        exact_ref = case["probs_distinct"] and all(
+            lv[0] == s["tokens"][0] and lv[1] == s["parents"][0] for lv, s in zip(levels, case["steps"]))
+        if not exact_ref:
+            continue
+        checked += 1
+        tree = DraftTreeBatch(1, case["k"], case["depth"], "cuda", root_tokens=torch.tensor([7]))
+        for d in range(case["depth"]):
+            tree.expand(eo.draft_probs(golden_io.expand_logits(case, d), case["temperature"]).cuda(), from_logits=False)
+        P, S = g["prefix"], g["skip"]
+        max_verify, max_cache_len = case["keep"] + 5, P + case["keep"] + 9
+        base = torch.zeros(1, 1, max_verify, max_cache_len, dtype=torch.bool)
+        partial = torch.tensor(g["mask_prefix_skip"], dtype=torch.bool)[None, None]
+        K, D = partial.shape[2], partial.shape[3]
+        want = base[:, :, :K, :].clone()     # the reference's _get_tree_mask: clone the buffer rows, splice
+        want[:, :, :K, :D] = partial
+        if mask_dtype != torch.bool:
+            want = invert_mask(want, mask_dtype)
+        buf = torch.full((1, 1, max_verify, max_cache_len), 1, dtype=mask_dtype, device="cuda")  # stale contents
+        out = tree.finalize(case["keep"], position_offset=[P], prefix_length=P, skip_nodes=S, mask_out=buf)
+        tree.check_status()
+        got = buf[:, :, :n - S].cpu()
+        assert torch.equal(got.view(torch.uint8) if mask_dtype == torch.bool else
+                           got.view(torch.int32 if mask_dtype == torch.float32 else torch.int16),
+                           want.view(torch.uint8) if mask_dtype == torch.bool else
+                           want.view(torch.int32 if mask_dtype == torch.float32 else torch.int16)), case["name"]
+        assert out["token_ids"][0, S:n].tolist() == g["data_skip"]["token_ids"]
+        assert out["parent_indices"][0, S:n].tolist() == g["data_skip"]["parent_indices"]
+        assert out["position_ids"][0, S:n].tolist() == [d + P for d in g["data_skip"]["depths"]]
+        # rows the call does not own keep their contents
+        assert bool((buf[:, :, case["keep"] - S:] == 1).all())
+        # a dense mask of its own, per-sequence prefix given as a tensor
+        dense = tree.finalize(case["keep"], prefix_length=torch.tensor([P]), skip_nodes=S, mask_dtype=mask_dtype)
+        assert tuple(dense["tree_mask"].shape) == (1, case["keep"] - S, P + case["keep"])
+        assert torch.equal(dense["tree_mask"][0, :n - S, :D].cpu().float(), want[0, 0, :, :D].float())
+    assert checked >= 4
+
+
+def test_finalize_rejects_bad_geometry(cuda_lib):
+    tree = DraftTreeBatch(2, 4, 2, "cuda")
+    probs = torch.rand(2, 1, 50).softmax(-1)
+    tree.expand(probs.cuda(), from_logits=False)
+    with pytest.raises(ValueError):
+        tree.finalize(8, skip_nodes=9)
+    with pytest.raises(ValueError):  # the prefix does not fit the columns the caller asked for
+        tree.finalize(8, prefix_length=[3, 30], mask_cols=20)
+        tree.check_status()
+    tree.finalize(8, prefix_length=[3, 12], mask_cols=20)
+    tree.check_status()
+
+
+def test_config3_chain_matches_reference(cuda_lib):
+    """Config 3 as a chain: 32 bf16 sequences (and 4 fp32 ones), ten `DraftTreeBatch.expand` levels from raw
+    logits at V = 128256 with k = 16, then `finalize(64)`, against what the unmodified reference produced with
+    _topk_flatten -> TreeData -> Tree.add_nodes -> prune_to_top_n(64) -> get_tree_data / create_attention_mask
+    on the same seeded logits.  bf16: every level's values bit-equal, every chosen candidate carries its value,
+    kept probabilities bit-equal; all of these sequences have ties somewhere, where the reference's node order
+    is torch.topk's open choice, so the structure is compared with the ordered restatement.  fp32 (no ties):
+    the reference's own tokens, parents, kept nodes and mask."""
+    chain = golden_io.expand_chain()
+    V, k, depth, keep = chain["vocab"], chain["k"], chain["depth"], chain["keep"]
+    for dtype in ("bfloat16", "float32"):
+        seqs = [s for s in chain["sequences"] if s["dtype"] == dtype]
+        B, dt = len(seqs), DT[dtype]
+        assert B == (32 if dtype == "bfloat16" else 4)
+        tree = DraftTreeBatch(B, k, depth, "cuda", root_tokens=torch.full((B,), chain["root_token"]))
+        oracle = [eo.FlatTree(chain["root_token"]) for _ in range(B)]
+        pp = [torch.ones(1, 1, dtype=dt) for _ in range(B)]
+        for d in range(depth):
+            logits = torch.cat([golden_io.chain_logits(chain, s, d) for s in seqs])
+            tok, val, par = tree.expand(logits.cuda(), from_logits=True, temperature=1.0)
+            tok, val, par = tok.cpu(), val.cpu(), par.cpu()
+            for b, s in enumerate(seqs):
+                g = s["levels"][d]
+                if dtype == "bfloat16":
+                    probs = eo.draft_probs(logits[b:b + 1], 1.0)
+                    assert val[b].float().tolist() == g["probs"], (s["seed"], d)
+                    scores = (probs * pp[b].unsqueeze(-1)).view(1, -1)
+                    assert eo.same_topk(scores, torch.tensor([g["probs"]]).to(dt), val[b:b + 1],
+                                        (par * V + tok)[b:b + 1]), (s["seed"], d)
+                    ot, ov, op = eo.topk_flatten_ordered(probs, pp[b], k)
+                    assert tok[b].tolist() == ot[0].tolist() and par[b].tolist() == op[0].tolist(), (s["seed"], d)
+                    oracle[b].add_nodes(ot.unsqueeze(0), ov.unsqueeze(0), op.unsqueeze(0))
+                    pp[b] = ov
+                else:
+                    assert torch.allclose(val[b], torch.tensor(g["probs"]), rtol=2e-5, atol=0), (s["seed"], d)
+                    assert tok[b].tolist() == g["tokens"] and par[b].tolist() == g["parents"], (s["seed"], d)
+        out = tree.finalize(keep, position_offset=[100 + b for b in range(B)])
+        tree.check_status()
+        assert out["n_nodes"].tolist() == [keep] * B
+        for b, s in enumerate(seqs):
+            g = s["pruned"]
+            got_rows = [int(sum(1 << j for j in r.nonzero().flatten().tolist())) for r in out["tree_mask"][b].cpu()]
+            off, idx = out["child_off"][b].tolist(), out["child_idx"][b].tolist()
+            kids = [idx[off[i]:off[i + 1]] for i in range(keep)]
+            if dtype == "bfloat16":
+                assert out["cumulative_probabilities"][b].tolist() == g["probs"], s["seed"]  # sorted, bit-equal
+                keep_idx = oracle[b].prune_to_top_n(keep, dt, ordered=True)
+                assert out["keep_idx"][b].tolist() == keep_idx
+                assert out["token_ids"][b].tolist() == oracle[b].token
+                assert out["parent_indices"][b].tolist() == oracle[b].parent
+                assert out["depths"][b].tolist() == oracle[b].depth
+                assert got_rows == [int(sum(1 << j for j in range(keep) if bool(m[j]))) for m in oracle[b].mask()]
+                assert kids == oracle[b].children
+            else:
+                assert s["rule_agrees_prune"]
+                assert out["keep_idx"][b].tolist() == g["keep_idx"]
+                assert out["token_ids"][b].tolist() == g["token_ids"]
+                assert out["parent_indices"][b].tolist() == g["parent_indices"]
+                assert out["depths"][b].tolist() == g["depths"]
+                assert got_rows == g["mask_rows"] and kids == g["children"]
+            assert out["position_ids"][b].tolist() == [x + 100 + b for x in out["depths"][b].tolist()]
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])

@@ -117,3 +117,66 @@ def test_prune_to_depth_and_tree_views():
     assert t.available_leaves == [2, 3] and t.nodes[3].has_been_sampled is False
     assert t.prune_to_depth(10).tolist() == [0, 1, 2, 3]
     assert t.get_children_indices(0).tolist() == [1, 2] and t.get_children_ids(1).tolist() == [4]
+
+
+def test_masks_with_prefix_and_skipped_rows_match_reference():
+    """create_attention_mask(prefix_length, skip_nodes), get_tree_data(skip_nodes) and the static draft-side
+    mask buffer, against what the reference's classes returned (also for trees that prune_to_top_n leaves alone)."""
+    no_prune = 0
+    for case in golden_io.expand_cases():
+        dt = DT[case["dtype"]]
+        data = TreeData()
+        for s in case["steps"]:
+            data.update(torch.tensor(s["tokens"]), torch.tensor(s["probs"]).to(dt), torch.tensor(s["parents"]))
+        tree = Tree(torch.tensor(7), dt)
+        tree.add_nodes(*data.get_data())
+        keep = tree.prune_to_top_n(case["keep"])
+        p = case["pruned"]
+        if tree.size() == len(case["full"]["token_ids"]):
+            no_prune += 1
+            assert keep.tolist() == list(range(tree.size())) == p["keep_idx"]
+            assert tree.get_tree_data()["parent_indices"].tolist() == case["full"]["parent_indices"]
+        if case["probs_distinct"] or tree.size() == len(case["full"]["token_ids"]):
+            m = tree.create_attention_mask(prefix_length=p["prefix"], skip_nodes=p["skip"])
+            assert m[0, 0].to(torch.uint8).tolist() == p["mask_prefix_skip"]
+            d = tree.get_tree_data(p["skip"])
+            for key in ("token_ids", "depths", "parent_indices"):
+                assert d[key].tolist() == p["data_skip"][key]
+        cache = TreeMaskCache(prefix_len=5, sample_len=case["k"], max_cache_len=5 + case["k"] * case["depth"] + 3,
+                              dtype=torch.float32, device="cpu")
+        for s in case["steps"]:
+            got = cache.update_tree_mask(torch.tensor(s["parents"]), return_invert=False)
+            assert got[0, 0].to(torch.uint8).tolist() == s["static_mask"]
+    assert no_prune >= 4
+
+
+def test_oracle_reproduces_reference_expansion_chains():
+    """Ten levels at the benchmark's vocabulary (a subset of the golden sequences, to keep the CPU suite short):
+    the restated top-k gives the reference's values at every level, and where torch.topk's open tie order played
+    no part (`rule_agrees`) the ordered variant gives its indices and its pruned tree too."""
+    chain = golden_io.expand_chain()
+    V, k = chain["vocab"], chain["k"]
+    assert len(chain["sequences"]) == 36 and sum(s["dtype"] == "bfloat16" for s in chain["sequences"]) == 32
+    picked = [s for s in chain["sequences"] if s["dtype"] == "bfloat16"][:2] + \
+        [s for s in chain["sequences"] if s["rule_agrees_prune"]][:1]
+    assert len(picked) == 3
+    for seq in picked:
+        dt = DT[seq["dtype"]]
+        pp = torch.ones(1, 1, dtype=dt)
+        tree = eo.FlatTree(chain["root_token"])
+        for d, g in enumerate(seq["levels"]):
+            probs = eo.draft_probs(golden_io.chain_logits(chain, seq, d), 1.0)
+            tok, val, par = eo.topk_flatten_ordered(probs, pp, k)
+            assert val[0].float().tolist() == g["probs"], (seq["seed"], d)
+            scores = (probs * pp.unsqueeze(-1)).view(1, -1)
+            assert eo.same_topk(scores, torch.tensor([g["probs"]]).to(dt), val, par * V + tok)
+            if seq["rule_agrees"]:
+                assert tok[0].tolist() == g["tokens"] and par[0].tolist() == g["parents"]
+            tree.add_nodes(tok.unsqueeze(0), val.unsqueeze(0), par.unsqueeze(0))
+            pp = val
+        keep = tree.prune_to_top_n(chain["keep"], dt, ordered=True)
+        assert sorted(tree.prob, reverse=True) == sorted(seq["pruned"]["probs"], reverse=True)
+        if seq["rule_agrees_prune"]:
+            assert keep == seq["pruned"]["keep_idx"] and tree.parent == seq["pruned"]["parent_indices"]
+            rows = [int(sum(1 << j for j in range(len(keep)) if bool(m[j]))) for m in tree.mask()]
+            assert rows == seq["pruned"]["mask_rows"]

@@ -93,6 +93,33 @@ def test_hf_layout_static_and_dynamic(cuda_lib, dtype):
         assert torch.equal(dyn.key_cache[i].cpu(), ks[i]) and torch.equal(dyn.value_cache[i].cpu(), vs[i])
 
 
+def test_golden_hf_layout_reorders(cuda_lib):
+    """The HF-layout caches against checksums left by the reference's own TreeStaticCache /
+    TreeDynamicCache.reorder_cache_with_offset (tests/golden/kv_hf_cases.json), called the way the generators
+    call them: through KVManager with dim=2 (generators/classic_sd.py:254)."""
+    cases = golden_io.kv_hf_cases()
+    assert len(cases) >= 12
+    for c in cases:
+        dt = golden_io.DT[c["dtype"]]
+        ks, vs = golden_io.kv_hf_tensors(c)
+        beam = torch.tensor(c["beam"])
+        cache = kc.TreeStaticCache(num_layers=c["layers"], num_kv_heads=c["heads"], head_dim=c["head_dim"],
+                                   max_cache_len=c["tokens"], device="cuda", dtype=dt, max_batch_size=1)
+        for i in range(c["layers"]):
+            cache.key_cache[i].copy_(ks[i])
+            cache.value_cache[i].copy_(vs[i])
+        kc.KVManager(cache).reorder_cache_with_offset(beam, new_chunk_len=c["tree_n"], offset=c["offset"], dim=2)
+        got = torch.stack([t.cpu() for t in list(cache.key_cache) + list(cache.value_cache)])
+        assert ko.checksum(got) == c["static_after"], c["seed"]
+        dyn = kc.TreeDynamicCache()
+        for i in range(c["layers"]):
+            dyn.update(ks[i].cuda(), vs[i].cuda(), i)
+        kc.KVManager(dyn).reorder_cache_with_offset(beam, new_chunk_len=c["tree_n"], offset=c["offset"], dim=2)
+        got = torch.stack([t.cpu() for t in list(dyn.key_cache) + list(dyn.value_cache)])
+        assert got.shape[3] == c["dynamic_tokens"]
+        assert ko.checksum(got) == c["dynamic_after"], c["seed"]
+
+
 def test_bad_indices_are_reported(cuda_lib):
     pool = kc.KvCachePool(4, 1, 1, 8, 4, torch.float32, "cuda")
     with pytest.raises(ValueError):

@@ -78,6 +78,26 @@ def test_kv_oracle_matches_reference_pool_reorder():
         assert ko.checksum(pool) == c["after"], c["seed"]
 
 
+def test_kv_oracle_matches_reference_hf_layout_reorders():
+    """hf_static_reorder / hf_dynamic_reorder against checksums left by the reference's own
+    TreeStaticCache / TreeDynamicCache.reorder_cache_with_offset (run on a stand-in object by make_golden.py)."""
+    from oracle import kv_oracle as ko
+
+    cases = golden_io.kv_hf_cases()
+    assert len(cases) >= 12
+    for c in cases:
+        ks, vs = golden_io.kv_hf_tensors(c)
+        assert ko.checksum(torch.stack(ks + vs)) == c["before"]
+        beam = torch.tensor(c["beam"])
+        sk, sv = [t.clone() for t in ks], [t.clone() for t in vs]
+        ko.hf_static_reorder(sk, sv, beam, c["offset"])
+        assert ko.checksum(torch.stack(sk + sv)) == c["static_after"], c["seed"]
+        dk, dv = [t.clone() for t in ks], [t.clone() for t in vs]
+        ko.hf_dynamic_reorder(dk, dv, beam, c["offset"])
+        assert dk[0].shape[2] == c["dynamic_tokens"]
+        assert ko.checksum(torch.stack(dk + dv)) == c["dynamic_after"], c["seed"]
+
+
 def test_kv_oracle_page_table_is_consistent_with_identity():
     from oracle import kv_oracle as ko
 
