@@ -36,6 +36,7 @@ NODES = 64
 KV_LAYERS, KV_HEADS, KV_DIM, KV_TOKENS, PAGE_LEN = 28, 4, 128, 4096, 16
 LOSSY_KW = {"threshold_method": "entropy", "threshold": 0.3, "window_size": 6}
 METRIC = "tree verify+accept steps/s"
+CPU_SAMPLE = 16  # sequences per pass of the CPU path: ~0.5 s on 16 cores, so three passes or twenty steps stay short
 
 
 def parse_args():
@@ -54,9 +55,10 @@ def parse_args():
                     help="verify greedily and lossily in two launches (two passes over the logits) instead of one")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the side measurements of the other kernels")
-    ap.add_argument("--extras-only", choices=["expand", "stochastic", "gemm"], default=None,
+    ap.add_argument("--extras-only", choices=["step", "expand", "stochastic", "gemm"], default=None,
                     help="run one of the side measurements alone on GPU 0 and print it as one JSON line")
-    ap.add_argument("--cpu-sample", type=int, default=0, help="sequences per CPU-baseline sample (0 = auto)")
+    ap.add_argument("--cpu-sample", type=int, default=CPU_SAMPLE,
+                    help="sequences per pass of the CPU path (the cpu_baseline leg and the reference arm use the same)")
     return ap.parse_args()
 
 
@@ -88,7 +90,7 @@ def flats_of(trees):
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
 
-    def __init__(self, device_index: int, period_s: float = 0.002):
+    def __init__(self, device_index: int, period_s: float = 0.0005):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._thread = None
@@ -193,6 +195,27 @@ def cpu_baseline(sample: int, reps: int, variant: str):
                           f"{pool.numel() * 2 / 1e6:.1f} MB pool, as the reference does per sequence")
 
 
+def moved_row_count(out) -> int:
+    """Accepted-path rows whose source differs from their destination (beam[i] != i): the rows compaction moves."""
+    moved = 0
+    for b in range(out["out_meta"].shape[0]):
+        L = int(out["out_meta"][b, 0])
+        moved += int((out["out_hidden"][b, :L] != np.arange(L)).sum())
+    return moved
+
+
+def profiled_traffic(wave: int):
+    """DRAM bytes per verify launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at a wave of
+    64 sequences), read from the summary of that capture; None when the summary does not state it."""
+    import re
+
+    path = ROOT / "profiles" / "verify_rows_kernel_bf16_wave64.md"
+    if not path.exists():
+        return None
+    m = re.search(r"dram_bytes_per_launch_wave64:\s*([0-9.eE+]+)", path.read_text())
+    return float(m.group(1)) * wave / 64 if m else None
+
+
 def spot_check(spot):
     """The GPU's lossy-verify results of a few sequences against the CPU restatement; raises on a mismatch."""
     from oracle import verify_oracle as vo
@@ -211,7 +234,7 @@ def run_reference_arm(args):
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    sample = args.cpu_sample or 4
+    sample = args.cpu_sample
     torch.set_num_threads(cores)
     seq_ids = list(range(sample))
     trees, _ = make_wave_inputs(seq_ids, args.variant, "cpu", with_logits=False)
@@ -285,9 +308,64 @@ def extras(device, peak_gbs, peak_tf):
     """The secondary kernels at their full configurations: one expansion step (config 3), one stochastic
     verification batch (config 2), the W4A16 GEMM shapes (config 4); each on inputs larger than L2."""
     out = {}
+    out.update(extra_step_peaked(device, peak_gbs))
     out.update(extra_expand(device, peak_gbs))
     out.update(extra_stochastic(device, peak_gbs))
     out.update(extra_gemm(device, peak_gbs, peak_tf))
+    return out
+
+
+def extra_step_peaked(device, peak_gbs, wave=64):
+    """One wave of the sharded step on the "peaked" inputs (boosted child = row maximum + 4), where the walks
+    accept tokens, the lossy gate opens and compaction moves real rows; the literal inputs accept next to
+    nothing, so their compaction launch finds every kept row already in place."""
+    from subspec_b200 import synthetic
+    from subspec_b200.step import SpeculativeStepBatch
+
+    pages_per_seq = KV_TOKENS // PAGE_LEN
+    ids = list(range(wave))
+    trees, logits = make_wave_inputs(ids, "peaked", device)
+    sb = SpeculativeStepBatch(wave, NODES, device, kv_layers=KV_LAYERS, kv_heads=KV_HEADS, head_dim=KV_DIM,
+                              page_len=PAGE_LEN, pages_per_seq=pages_per_seq,
+                              page_table=synthetic.random_page_table(wave, pages_per_seq,
+                                                                     torch.Generator().manual_seed(31)))
+    for layer in range(KV_LAYERS):
+        sb.pool[layer].normal_()
+    sb.set_trees(flats_of(trees))
+    sb.set_kv_offsets([KV_TOKENS - NODES] * wave)
+
+    def step():
+        sb.verify(logits, verify_method="exact+lossy", verify_kwargs=LOSSY_KW)
+        sb.compact_kv()
+
+    _spin_up(device)
+    ms_step = _time_ms(step, iters=50, warm=5)
+    res = sb.results()
+    kept, moved = int(res["out_meta"][:, 0].sum()), moved_row_count(res)
+    # the compaction launch alone: its inputs (the verify outputs) stay as the last step left them, and a
+    # repeated compaction moves the same rows again, so every launch does the same work
+    ms_kv = _time_ms(sb.compact_kv, iters=200, warm=10)
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        for _ in range(20):
+            sb.compact_kv()
+    ms_kv_graph = _time_ms(gr.replay, iters=20, warm=3) / 20
+    sb.results()
+    moved_bytes = 2 * moved * sb.kv_row_bytes
+    floor_us = moved_bytes / (peak_gbs * 1e9) * 1e6
+    out = {"step_peaked_wave64": {
+        "ms_verify_plus_compact": ms_step, "sequence_steps_per_s": wave / (ms_step * 1e-3),
+        "accepted_tokens_per_sequence": (kept - wave) / wave, "tokens_emitted_per_s": kept / (ms_step * 1e-3),
+        "kv_compact": {"us_per_launch_eager": ms_kv * 1e3, "us_per_launch_in_graph": ms_kv_graph * 1e3,
+                       "rows_kept": kept, "rows_moved": moved, "bytes_read_plus_written": moved_bytes,
+                       "GB/s": moved_bytes / (ms_kv_graph * 1e-3) / 1e9,
+                       "frac_of_measured_peak": moved_bytes / (ms_kv_graph * 1e-3) / 1e9 / peak_gbs,
+                       "floor_us_at_peak": floor_us,
+                       "bound": "launch and latency: one dependent chain (counts, beam, page table, bulk load, "
+                                "bulk store) per CTA; the bytes alone would take floor_us_at_peak"}}}
+    sb.pool = None
+    del sb, logits
+    torch.cuda.empty_cache()
     return out
 
 
@@ -449,7 +527,9 @@ def run_extras_only(args):
     pk = ROOT / "MEASURED_PEAKS.json"
     peaks = json.loads(pk.read_text()) if pk.exists() else {}
     peak_gbs, peak_tf = float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0))
-    if args.extras_only == "expand":
+    if args.extras_only == "step":
+        out = extra_step_peaked(device, peak_gbs)
+    elif args.extras_only == "expand":
         out = extra_expand(device, peak_gbs)
     elif args.extras_only == "stochastic":
         out = extra_stochastic(device, peak_gbs)
@@ -481,8 +561,12 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
+    from subspec_b200.shard import device_for_rank
+
+    local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
+    dev_index = device_for_rank(local, local_world, torch.cuda.device_count())
+    torch.cuda.set_device(dev_index)
+    device = torch.device("cuda", dev_index)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     if rank == 0:
@@ -548,7 +632,7 @@ def main():
     barrier()
     kernel_events = []
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
+    with ClockSampler(dev_index) as clocks:
         torch.cuda.synchronize()
         t_start.record()
         for _ in range(args.steps):
@@ -562,13 +646,14 @@ def main():
     ms_kv = sum(e[2].elapsed_time(e[3]) for e in kernel_events) / len(kernel_events)
 
     # ---- results of the last step: acceptance statistics + parity spot check ----
-    accepted_tokens, kept_rows = 0, 0
+    accepted_tokens, kept_rows, moved_rows = 0, 0, 0
     outs = []
     for sb, _, _, _ in waves:
         out = sb.results()
         outs.append(out)
         accepted_tokens += int(out["out_meta"][:, 0].sum())
         kept_rows += int(out["out_meta"][:, 0].sum())
+        moved_rows += moved_row_count(out)
     # a few sequences of the first wave, kept on the host for the CPU-baseline leg, which checks the GPU
     # results against the CPU restatement (the only place this script runs it)
     spot = []
@@ -590,6 +675,9 @@ def main():
         ready = [torch.cuda.Event() for _ in range(2)]
         freed = [torch.cuda.Event() for _ in range(2)]
 
+        wave_flats = [flats_of(trees) for _, _, trees, _ in waves]
+        tree_bytes = sum(sb.ws._in_host.numel() * 4 for sb, _, _, _ in waves)
+
         def e2e_step():
             for i, (sb, _, _, _) in enumerate(waves):
                 s = i % 2
@@ -598,6 +686,9 @@ def main():
                     stage[s].copy_(host_logits, non_blocking=True)
                     ready[s].record(copy_stream)
                 with torch.cuda.stream(comp_stream):
+                    # the step's trees: checked, packed into the pinned block and copied (runs on the host while
+                    # the logits copy above is in flight)
+                    sb.set_trees(wave_flats[i])
                     comp_stream.wait_event(ready[s])
                     if args.two_pass:
                         sb.verify(stage[s], verify_method="exact")
@@ -619,15 +710,17 @@ def main():
         dt_e2e = time.perf_counter() - t0
         barrier()
         e2e = {"dt": dt_e2e, "steps": e2e_steps,
-               "h2d": n_waves * host_logits.numel() * 2, "d2h": n_waves * waves[0][0].ws._out_host.numel()}
+               "h2d": n_waves * host_logits.numel() * 2 + tree_bytes,
+               "d2h": n_waves * waves[0][0].ws._out_host.numel()}
 
     # ---- gather (max over ranks of the times; sums of the counts) ----
     red = reduce_stats({"ms_total": ms_total, "ms_exact": ms_exact, "ms_lossy": ms_lossy, "ms_kv": ms_kv,
                         "dt_e2e": e2e["dt"] if e2e else 0.0},
-                       {"accepted_tokens": accepted_tokens, "kept_rows": kept_rows}, device=device)
+                       {"accepted_tokens": accepted_tokens, "kept_rows": kept_rows, "moved_rows": moved_rows},
+                       device=device)
     ms_total, ms_exact, ms_lossy, ms_kv, dt_e2e = (red[k] for k in ("ms_total", "ms_exact", "ms_lossy", "ms_kv",
                                                                      "dt_e2e"))
-    accepted_tokens, kept_rows = red["accepted_tokens"], red["kept_rows"]
+    accepted_tokens, kept_rows, moved_rows = red["accepted_tokens"], red["kept_rows"], red["moved_rows"]
 
     if rank == 0:
         peaks = {}
@@ -655,12 +748,13 @@ def main():
                                    (" (lossy verify)" if args.two_pass else " (greedy + lossy verify, one pass)"),
                          "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
                          "peak_source": peak_src,
-                         # dram__bytes_read + dram__bytes_write of this kernel from the ncu capture summarised in
-                         # profiles/verify_rows_kernel_bf16_wave64.md (1246.38 + 0.47 MB for a wave of 64 sequences)
-                         "traffic": 1246.85e6 * wave / 64, "algorithmic_bytes": rows_bytes,
-                         "exact_kernel_gbs": rows_bytes / (ms_exact * 1e-3) / 1e9 if args.two_pass else None,
-                         "kv_kernel_gbs": 2 * (kept_rows / (world * n_waves)) * waves[0][0].kv_row_bytes
-                         / (ms_kv * 1e-3) / 1e9},
+                         "traffic": profiled_traffic(wave), "algorithmic_bytes": rows_bytes,
+                         "exact_kernel_gbs": rows_bytes / (ms_exact * 1e-3) / 1e9 if args.two_pass else None},
+            # the compaction launch of this workload: rows that really move (beam[i] != i), read + written
+            "kv_compact": {"us_per_launch": ms_kv * 1e3, "rows_kept_per_launch": kept_rows / (world * n_waves),
+                           "rows_moved_per_launch": moved_rows / (world * n_waves),
+                           "GB/s": 2 * (moved_rows / (world * n_waves)) * waves[0][0].kv_row_bytes
+                           / (ms_kv * 1e-3) / 1e9},
             "gpu_launches": args.steps * n_waves * (3 if args.two_pass else 2),
             "clocks": clocks.summary(),
         }
@@ -668,8 +762,12 @@ def main():
             line["e2e"] = {"value": total * e2e["steps"] / dt_e2e, "unit": "steps/s",
                            "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                            "steps": e2e["steps"],
-                           "note": "per GPU and step; logits copied from pinned host memory wave by wave "
-                                   "(double-buffered), results read back to pinned host memory"}
+                           "h2d_GBps_per_rank": e2e["h2d"] * e2e["steps"] / dt_e2e / 1e9,
+                           "gpus_used": [device_for_rank(r, local_world, torch.cuda.device_count())
+                                         for r in range(local_world)],
+                           "note": "bytes are per GPU and step; per wave the logits are copied from pinned host "
+                                   "memory (double-buffered), the trees are checked, packed and copied, and the "
+                                   "results are read back to pinned host memory"}
         if world == 1 and not args.no_extras:
             for w in waves:
                 w[0].pool = None
@@ -677,8 +775,7 @@ def main():
             torch.cuda.empty_cache()
             line["other_kernels"] = extras(device, peak_gbs, float(peaks.get("bf16_tflops", 1590.0)))
         if world == 1 and not args.no_cpu_baseline:
-            sample = args.cpu_sample or 64  # one wave: about ten seconds of CPU work over the three passes
-            v, desc = cpu_baseline(sample, 3, args.variant)
+            v, desc = cpu_baseline(args.cpu_sample, 5, args.variant)
             line["cpu_baseline"] = {"value": v, "unit": "steps/s", "cores": os.cpu_count(), "kind": "port",
                                     "sample": desc, "gpu_results_checked_sequences": spot_check(spot)}
         print(json.dumps(line), flush=True)

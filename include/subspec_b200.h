@@ -102,14 +102,31 @@ SUBSPEC_API const char* subspec_last_cuda_error(void);
  * logits row.  For the lossy method the caller passes n_nodes == n_rows and
  * only children inside the decoded range (tree_verify.py:137-145).
  *
+ * Trees.  The children lists must describe a forest: every index inside
+ * [0, n_nodes), no node listed twice, no loop.  The lossy method's tables are
+ * filled bottom-up whatever the numbering; the reference additionally assumes
+ * that a child's index is larger than its parent's (lossy_tree_verify.py:112).
+ * Indices out of range set SUBSPEC_DEV_BAD_CHILD and are skipped.  Every walk
+ * on the device stops after n_nodes steps and the table fill after n_nodes
+ * rounds, so lists with a loop in them end the launch with
+ * SUBSPEC_DEV_BAD_CHILD instead of hanging it.  Counts outside
+ * 0 <= n_rows <= n_nodes <= max_nodes and children offsets outside
+ * [0, n_nodes] are clamped and reported as SUBSPEC_DEV_BAD_COUNT.  A sequence
+ * with n_rows == 0 gets out_meta = {0, 0, 0, 0}.  Results of a launch that set
+ * any status bit are not meaningful.
+ *
  * Sampling.  do_sample = 0: the target token of a node is the first-index
- * argmax of its row.  do_sample = 1: the row is divided by `temperature`,
- * filtered by nucleus `top_p` with the semantics of transformers'
- * TopPLogitsWarper (top_p >= 1 disables the filter), renormalised, and the
- * target token is the inverse-CDF pick for uniforms[b][u] in vocabulary order
- * (this stands in for torch.multinomial's global RNG).  Supported for bf16 /
- * fp16 logits with the exact method (sample-and-match); other combinations
- * return SUBSPEC_EUNSUPPORTED.
+ * argmax of its row.  do_sample != 0: the row is divided by `temperature`,
+ * filtered by `top_k` (TopKLogitsWarper: scores below the k-th largest go) and
+ * then by nucleus `top_p` with the semantics of transformers' TopPLogitsWarper
+ * (top_p >= 1 disables it), renormalised, and the target token is the
+ * inverse-CDF pick for uniforms[b][u] in vocabulary order (this stands in for
+ * torch.multinomial's global RNG).  Supported: logits of all three dtypes with
+ * either method (for the lossy method the gates then see the filtered
+ * distribution, lossy_tree_verify.py:75-77); probabilities in
+ * (SUBSPEC_IN_PROBS) are drawn from as they are, so a temperature other than
+ * 1, top_k or top_p together with them returns SUBSPEC_EUNSUPPORTED, as does
+ * residual acceptance (below) on fp32 logits or on probabilities.
  *
  * Outputs.  out_tokens / out_hidden are [batch, max_out] int64:
  * accepted draft tokens followed by the bonus token, and for each the local

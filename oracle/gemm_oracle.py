@@ -37,7 +37,7 @@ def w4a16_matmul(x: torch.Tensor, qweight: torch.Tensor, scale: torch.Tensor, ze
 
 
 def config4_case(n: int, k: int, m: int, seed: int):
-    """BASELINE config 4 inputs: uint4 weights, scale ~U(0.005, 0.02), zero ~U(0, 15) in fp16, x ~N(0, 1) bf16."""
+    """The HQQ-style synthetic linear of the GEMM benchmark: uint4 weights, scale ~U(0.005, 0.02), zero ~U(0, 15) in fp16, x ~N(0, 1) bf16."""
     from subspec_b200.synthetic import w4a16_case
 
     return w4a16_case(n, k, m, seed, GROUP)

@@ -430,7 +430,7 @@ class RequestKvCache:
             self.kv_page_indices = self.kv_page_indices[:need]
         elif have < need:
             self.kv_page_indices.extend(self.kvCachePool.allocate(need - have))
-            raise ValueError("need to allocate new pages in reorder cache, should not happen")
+            raise ValueError("a reorder never lengthens a request: it had fewer pages than its kept rows need")
 
     def decrement(self, num_tokens: int = 1):
         if num_tokens <= 0:

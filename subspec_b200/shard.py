@@ -45,6 +45,20 @@ def shard_sequences(total: int, world: int, rank: int, wave: int) -> Shard:
     return Shard(rank=rank, world=world, first=rank * per_rank, count=per_rank, wave=wave, total=per_rank * world)
 
 
+def device_for_rank(local_rank: int, local_world: int, visible: int) -> int:
+    """Which of the box's `visible` GPUs the rank with this local rank takes.
+
+    With as many ranks as GPUs it is the rank's own ordinal.  With fewer, the ranks are spread over the box
+    (stride visible // local_world) instead of packed onto GPUs 0 .. n-1: neighbouring GPUs share PCIe
+    switches and host links, and a job whose steps start with a host-to-device copy of its inputs is bound by
+    exactly those when its ranks sit side by side."""
+    if local_world < 1 or visible < 1 or not 0 <= local_rank < local_world:
+        raise ValueError(f"bad placement request: local_rank={local_rank} local_world={local_world} visible={visible}")
+    if local_world >= visible:
+        return local_rank % visible
+    return local_rank * (visible // local_world)
+
+
 def reduce_stats(times_ms: Dict[str, float], counts: Dict[str, float], device="cpu") -> Dict[str, float]:
     """MAX over ranks of the timings, SUM over ranks of the counters (identity when not distributed)."""
     import torch.distributed as dist

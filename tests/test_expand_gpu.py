@@ -238,8 +238,16 @@ def test_config3_chain_matches_reference(cuda_lib):
                     oracle[b].add_nodes(ot.unsqueeze(0), ov.unsqueeze(0), op.unsqueeze(0))
                     pp[b] = ov
                 else:
-                    assert torch.allclose(val[b], torch.tensor(g["probs"]), rtol=2e-5, atol=0), (s["seed"], d)
+                    # fp32: torch's CPU softmax is itself up to ~2e-5 (relative) off the exact value on these
+                    # rows and the error compounds down the chain, so the yardstick for the values is the exact
+                    # (fp64) chain, within the stated 1e-5; the reference's values bound them more loosely and
+                    # its indices exactly (no ties, margins audited by the generator)
+                    p64 = torch.softmax(logits[b].double(), dim=-1)
+                    exact = torch.stack([p64[l, t] * pp[b][0, l].double() for l, t in zip(g["parents"], g["tokens"])])
+                    assert torch.allclose(val[b].double(), exact, rtol=1e-5, atol=0), (s["seed"], d)
+                    assert torch.allclose(val[b], torch.tensor(g["probs"]), rtol=2e-4, atol=0), (s["seed"], d)
                     assert tok[b].tolist() == g["tokens"] and par[b].tolist() == g["parents"], (s["seed"], d)
+                    pp[b] = exact.view(1, -1)
         out = tree.finalize(keep, position_offset=[100 + b for b in range(B)])
         tree.check_status()
         assert out["n_nodes"].tolist() == [keep] * B

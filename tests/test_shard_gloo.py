@@ -65,3 +65,16 @@ def test_sharding_edges():
     with pytest.raises(IndexError):
         sh.wave_ids(8)
     assert reduce_stats({"a": 1.0}, {"b": 2.0}) == {"a": 1.0, "b": 2.0}   # not distributed: identity
+
+
+def test_ranks_are_spread_over_the_box():
+    from subspec_b200.shard import device_for_rank
+
+    assert [device_for_rank(r, 8, 8) for r in range(8)] == list(range(8))
+    assert [device_for_rank(r, 4, 8) for r in range(4)] == [0, 2, 4, 6]
+    assert [device_for_rank(r, 2, 8) for r in range(2)] == [0, 4]
+    assert device_for_rank(0, 1, 8) == 0
+    assert [device_for_rank(r, 2, 2) for r in range(2)] == [0, 1]
+    assert [device_for_rank(r, 3, 8) for r in range(3)] == [0, 2, 4]
+    with pytest.raises(ValueError):
+        device_for_rank(2, 2, 8)
