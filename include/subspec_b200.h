@@ -522,6 +522,30 @@ SUBSPEC_API int subspec_w4a16_pack(const void* qweight, const void* scale, const
 SUBSPEC_API int subspec_w4a16_scratch_bytes(int32_t m, int32_t n, int32_t k, size_t* bytes);
 SUBSPEC_API int subspec_w4a16_gemm(const subspec_w4a16_args* args, subspec_stream_t stream);
 
+/* Several projections of the same activations in ONE launch: y[i] = x @ W[i]^T for count weight matrices
+ * [n[i], k] packed separately.  The draft's decoder layer calls q/k/v, and gate/up, back to back on one input
+ * (the recipe quantises them alike: specdecodes/helpers/recipes/subspec/hqq_4bit_postspec.py:28-34); apart
+ * they are launches of 1 to 7 MB of weights each, all fixed cost.  The result of every projection is
+ * bit-identical to its own subspec_w4a16_gemm call whenever the two plans split K alike, and within the GEMM's
+ * stated tolerance always.  Scratch: subspec_w4a16_scratch_bytes(m, n[0] + ... + n[count-1], k). */
+#define SUBSPEC_W4A16_MAX_GROUP 4
+typedef struct subspec_w4a16_group_args {
+  uint32_t struct_size;
+  int32_t m, k;
+  int32_t count; /* 1 .. SUBSPEC_W4A16_MAX_GROUP */
+  const void* x; /* bf16 [m, k] */
+  int64_t x_stride;
+  const void* packed[SUBSPEC_W4A16_MAX_GROUP];
+  int32_t n[SUBSPEC_W4A16_MAX_GROUP];
+  void* y[SUBSPEC_W4A16_MAX_GROUP]; /* bf16 [m, n[i]] */
+  int64_t y_stride[SUBSPEC_W4A16_MAX_GROUP];
+  void* scratch;
+  size_t scratch_bytes;
+  uint32_t* dev_status;
+} subspec_w4a16_group_args;
+
+SUBSPEC_API int subspec_w4a16_gemm_grouped(const subspec_w4a16_group_args* args, subspec_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

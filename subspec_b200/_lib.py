@@ -123,6 +123,19 @@ class W4A16Args(C.Structure):
     ]
 
 
+W4A16_MAX_GROUP = 4
+
+
+class W4A16GroupArgs(C.Structure):
+    """Mirror of `subspec_w4a16_group_args`."""
+
+    _fields_ = [
+        ("struct_size", _u32), ("m", _i32), ("k", _i32), ("count", _i32), ("x", _vp), ("x_stride", _i64),
+        ("packed", _vp * W4A16_MAX_GROUP), ("n", _i32 * W4A16_MAX_GROUP), ("y", _vp * W4A16_MAX_GROUP),
+        ("y_stride", _i64 * W4A16_MAX_GROUP), ("scratch", _vp), ("scratch_bytes", C.c_size_t), ("dev_status", _vp),
+    ]
+
+
 # every symbol include/subspec_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "subspec_version": (C.c_char_p, []),
@@ -139,6 +152,7 @@ SYMBOLS = {
     "subspec_w4a16_pack": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),
     "subspec_w4a16_scratch_bytes": (C.c_int, [_i32, _i32, _i32, C.POINTER(C.c_size_t)]),
     "subspec_w4a16_gemm": (C.c_int, [C.POINTER(W4A16Args), _vp]),
+    "subspec_w4a16_gemm_grouped": (C.c_int, [C.POINTER(W4A16GroupArgs), _vp]),
 }
 
 _lib = None

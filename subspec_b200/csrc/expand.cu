@@ -17,9 +17,13 @@
 // create_attention_mask (:263-286), position ids = depth + offset (classic_sd.py:73-75).
 #include <limits.h>
 #include <math.h>
+#include <stdlib.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 #include "mask.cuh"
+#include "tma.cuh"
 
 namespace subspec {
 namespace {
@@ -29,8 +33,6 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kUnroll = 4;
 constexpr int kMaxK = 32;
 constexpr int kMaxRowSplits = 16;   // slices a row may be cut into when a launch has few rows
-constexpr int kPrefetchAhead = 6;  // iterations (16 KB each) a row's L2 prefetch runs ahead of its loads
-constexpr int kQueue = 256;  // per-warp candidate queue: one 16-byte vector per lane, 8 elements each
 
 struct Cand {
   float v;
@@ -40,54 +42,31 @@ __device__ __forceinline__ bool better(float av, int ai, float bv, int bi) {
   return av > bv || (av == bv && ai < bi);
 }
 
-// A warp-wide list of the k best (value desc, index asc): lane i holds entry i.
-struct WarpTopK {
-  float v;
-  int id;
-  int k;
-  __device__ __forceinline__ void init(int k_) {
-    k = k_;
-    v = -INFINITY;
-    id = INT_MAX;
-  }
-  __device__ __forceinline__ float kth_value() const { return __shfl_sync(0xffffffffu, v, k - 1); }
-  __device__ __forceinline__ float value_at(int j) const { return __shfl_sync(0xffffffffu, v, j); }
-  // All lanes call with the same candidate.
-  __device__ __forceinline__ void insert(float cv, int cid) {
-    const int lane = threadIdx.x & 31;
-    const uint32_t ahead = __ballot_sync(0xffffffffu, lane < k && better(v, id, cv, cid));
-    const int pos = __popc(ahead);
-    if (pos >= k) return;
-    const float pv = __shfl_up_sync(0xffffffffu, v, 1);
-    const int pi = __shfl_up_sync(0xffffffffu, id, 1);
-    if (lane > pos) {
-      v = pv;
-      id = pi;
-    } else if (lane == pos) {
-      v = cv;
-      id = cid;
-    }
-    if (lane >= k) {
-      v = -INFINITY;
-      id = INT_MAX;
-    }
-  }
-};
+// Lanes that share one candidate in a rank count over n candidates by kThreads threads: the largest power of
+// two (at most 32) that still gives every candidate its lanes in one sweep.  The latency of a rank count is
+// the n / P compares one lane makes one after the other, and these counts sit between the stages of a CTA
+// that has nothing else to do meanwhile.
+__device__ __forceinline__ int lanes_per_candidate(int n) {
+  int p = 1;
+  while (p < 32 && 2 * p * n <= (int)blockDim.x) p <<= 1;
+  return p;
+}
 
-// k-th largest (k = 1..32) of the 32 lane values: bitonic sort across the warp, descending.
-__device__ __forceinline__ float warp_kth_largest(float v, int k) {
-  const int lane = threadIdx.x & 31;
-#pragma unroll
-  for (int size = 2; size <= 32; size <<= 1) {
-#pragma unroll
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      const float o = __shfl_xor_sync(0xffffffffu, v, stride);
-      const bool desc = (lane & size) == 0;       // direction of this bitonic block
-      const bool lower = (lane & stride) == 0;    // this lane keeps the "first" element of the pair
-      v = (desc == lower) ? fmaxf(v, o) : fminf(v, o);
+// Rank (number of candidates that beat it) of candidate i = base + threadIdx.x / P among get(0..n), counted by
+// its P lanes together; the same value in all of them.  Called by every thread of the CTA (it shuffles).
+template <typename Get>
+__device__ __forceinline__ int coop_rank(int n, int P, int i, const Cand& me, Get&& get) {
+  const int part = threadIdx.x & (P - 1);
+  int rank = 0;
+  if (i < n && me.id != INT_MAX) {
+#pragma unroll 4  // the loads of a group go out together: one after the other they are the whole cost
+    for (int j = part; j < n; j += P) {
+      const Cand o = get(j);
+      rank += (o.id != INT_MAX && better(o.v, o.id, me.v, me.id)) ? 1 : 0;
     }
   }
-  return __shfl_sync(0xffffffffu, v, k - 1);
+  for (int off = P >> 1; off > 0; off >>= 1) rank += __shfl_xor_sync(0xffffffffu, rank, off);
+  return rank;
 }
 
 // The k best (value descending, index ascending) of n candidates, by the whole CTA: every candidate counts
@@ -99,16 +78,13 @@ template <typename Get>
 __device__ __forceinline__ void cta_topk(int n, int k, Get&& get, Cand* out) {
   for (int i = threadIdx.x; i < k; i += blockDim.x) out[i] = Cand{-INFINITY, INT_MAX};
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const Cand me = get(i);
-    if (me.id == INT_MAX) continue;
-    int rank = 0;
-#pragma unroll 8  // the loads of a group go out together: one after the other they are the whole cost
-    for (int j = 0; j < n; ++j) {
-      const Cand o = get(j);
-      rank += (o.id != INT_MAX && better(o.v, o.id, me.v, me.id)) ? 1 : 0;
-    }
-    if (rank < k) out[rank] = me;
+  const int P = lanes_per_candidate(n);
+  const int per_sweep = blockDim.x / P;
+  for (int base = 0; base < n; base += per_sweep) {
+    const int i = base + threadIdx.x / P;
+    const Cand me = i < n ? get(i) : Cand{-INFINITY, INT_MAX};
+    const int rank = coop_rank(n, P, i, me, get);
+    if (i < n && me.id != INT_MAX && (threadIdx.x & (P - 1)) == 0 && rank < k) out[rank] = me;
   }
   __syncthreads();
 }
@@ -120,8 +96,6 @@ struct RowOut {  // per (sequence, leaf) row, in scratch
 struct KArgs {
   subspec_expand_args a;
   int* ticket;     // [batch]
-  RowOut* rowout;  // [batch * leaves]
-  Cand* rowtop;    // [batch * leaves * k]
   float kT;        // scale inside 2^(x * kT - c): log2(e) / temperature, or log2(e) when the logits are pre-scaled
   float invT, T;   // 16-bit dtypes with temperature != 1: the reference rounds logits / T to the dtype first
   int prescale;
@@ -129,8 +103,8 @@ struct KArgs {
   // few rows: every row is cut into `splits` slices, one CTA each; the slices' lists and softmax sums meet
   // in scratch behind a ticket per row, and the last slice to arrive carries on as the row's CTA
   int splits;
+  int dbg;
   int64_t dm_row_stride, dm_seq_stride;  // draft-side mask geometry in elements, defaults resolved
-  int* rowticket;   // [batch * leaves]
   RowOut* partout;  // [batch * leaves * splits]
   Cand* parttop;    // [batch * leaves * splits * k]
 };
@@ -150,6 +124,9 @@ struct Elem<float> {
     return fmaxf(fmaxf(__uint_as_float(q.x), __uint_as_float(q.y)), fmaxf(__uint_as_float(q.z), __uint_as_float(q.w)));
   }
   static __device__ __forceinline__ float round_to(float x) { return x; }
+  // filler for vectors past the end of a slice: the lowest finite value (and the smallest value above it)
+  static __device__ __forceinline__ uint4 lowest() { return make_uint4(0xff7fffffu, 0xff7fffffu, 0xff7fffffu, 0xff7fffffu); }
+  static __device__ __forceinline__ float above_lowest() { return __uint_as_float(0xff7ffffeu); }
   static __device__ __forceinline__ float load(const void* p, size_t i) { return reinterpret_cast<const float*>(p)[i]; }
   static __device__ __forceinline__ void store(void* p, size_t i, float x) { reinterpret_cast<float*>(p)[i] = x; }
 };
@@ -170,6 +147,8 @@ struct Elem<__nv_bfloat16> {
     return fmaxf(__low2float(m), __high2float(m));
   }
   static __device__ __forceinline__ float round_to(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+  static __device__ __forceinline__ uint4 lowest() { return make_uint4(0xff7fff7fu, 0xff7fff7fu, 0xff7fff7fu, 0xff7fff7fu); }
+  static __device__ __forceinline__ float above_lowest() { return __uint_as_float(0xff7e0000u); }
   static __device__ __forceinline__ float load(const void* p, size_t i) {
     return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
   }
@@ -195,6 +174,8 @@ struct Elem<__half> {
     return fmaxf(__low2float(m), __high2float(m));
   }
   static __device__ __forceinline__ float round_to(float x) { return __half2float(__float2half_rn(x)); }
+  static __device__ __forceinline__ uint4 lowest() { return make_uint4(0xfbfffbffu, 0xfbfffbffu, 0xfbfffbffu, 0xfbfffbffu); }
+  static __device__ __forceinline__ float above_lowest() { return -65472.f; }
   static __device__ __forceinline__ float load(const void* p, size_t i) {
     return __half2float(reinterpret_cast<const __half*>(p)[i]);
   }
@@ -256,15 +237,158 @@ __device__ __forceinline__ void combine_soft(float& c, float& s, float oc, float
 }
 
 // ---- per-row streaming kernel ----------------------------------------------------------------
-template <typename T, int KIND>
+// Candidates of a slice are 16-byte VECTORS, not elements: a vector whose maximum reaches the threshold goes,
+// unordered, into a buffer in shared memory as (maximum, index of its first element) -- one atomic and one
+// store, a dozen instructions, which matters because a warp with a single candidate lane pays for every
+// instruction thirty-two-fold.  The threshold is seeded from the first stage (the k-th largest of the 256
+// per-thread maxima is k distinct elements' worth of evidence that the slice's k-th best is at least that)
+// and raised, the buffer cut back to its k best vectors, at the first stage boundary after the buffer has
+// gathered k + kSlack entries: with the threshold at the k-th best of the m stages read so far, stage m + 1
+// brings about k / m candidates.  Only when the slice has been read are the elements looked at: the vectors
+// whose maximum reaches the k-th largest vector maximum are fetched again (a few dozen 16-byte loads, mostly
+// L2 hits) and their elements at or above that value compete by rank counting.  Every element of the true
+// top k sits in a vector that was pushed and kept: a vector is only dropped when k vectors with a better
+// (maximum, index) exist, each of which holds an element that beats all of its elements.  A slice whose
+// candidates outrun the buffer inside one stage (sorted input) is redone by the slow selector below.
+// Rows that cannot be read as vectors, and the few elements behind a row's last whole vector, go through the
+// same buffer as single elements.
+constexpr int kStageVecs = kThreads * kUnroll;  // 16-byte vectors per TMA stage: one group per thread (16 KB)
+constexpr int kStages = 3;                      // shared-memory ring depth
+constexpr int kRingBytes = kStages * kStageVecs * 16;
+constexpr int kCap = kThreads;  // candidate buffer entries: one per thread when the buffer is ranked
+constexpr int kSlack = 48;   // the buffer is cut back to k entries once it has reached k + kSlack
+constexpr int kMaxSeqCands = 4096;  // leaves x slices x k candidates the last CTA of a sequence merges (32 KB)
+constexpr int kMaxSel = kRingBytes / 8 - kMaxSeqCands;  // of which so many may pass the pre-filter (16 KB)
+
+// The elements of a 16-byte vector, two at a time, as floats: f(x0, x1) for pairs in vocabulary order.
+template <typename T, typename F>
+__device__ __forceinline__ void for_pairs(const uint4& q, F&& f) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  if constexpr (sizeof(T) == 4) {
+    f(__uint_as_float(w[0]), __uint_as_float(w[1]));
+    f(__uint_as_float(w[2]), __uint_as_float(w[3]));
+  } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      f(v.x, v.y);
+    }
+  }
+}
+
+struct Slice {
+  Cand* buf;
+  int* cnt;
+  int tighten_at;  // k + kSlack
+  bool hot;        // this thread saw the buffer reach tighten_at
+  __device__ __forceinline__ void push(float v, int id) {
+    const int p = atomicAdd(cnt, 1);
+    if (p < kCap) buf[p] = Cand{v, id};
+    hot |= p >= tighten_at - 1;
+  }
+};
+
+// all 32 lane values in descending order: lane i ends up with the i-th largest
+__device__ __forceinline__ float warp_sort_desc(float v) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      const float o = __shfl_xor_sync(0xffffffffu, v, stride);
+      const bool desc = (lane & size) == 0;
+      const bool lower = (lane & stride) == 0;
+      v = (desc == lower) ? fmaxf(v, o) : fminf(v, o);
+    }
+  }
+  return v;
+}
+
+// A lower bound of the k-th largest of the CTA's 256 per-thread values (-inf = no value), nearly for free:
+// with j = ceil(k / warps), every warp's j-th largest value has j values of that warp at or above it, so the
+// smallest of them over the warps has warps * j >= k values of the CTA at or above it.  (The exact k-th largest
+// by rank counting over the warps' sorted lists cost a tenth of a row's streaming instructions; this bound
+// lets about one and a half times as many candidates through the first stage, which the first cut of the
+// buffer mends.)  `tmp` holds kWarps floats.
+__device__ __forceinline__ float cta_kth_lower_bound(float v, int k, float* tmp) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int j = (k + kWarps - 1) / kWarps;
+  float jth = -INFINITY;
+  for (int r = 0; r < j; ++r) {  // the warp's j-th largest: take the maximum out j times (one instance each time)
+    float m = v;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    jth = m;
+    const uint32_t holders = __ballot_sync(0xffffffffu, v == m);
+    if (holders && lane == __ffs(holders) - 1) v = -INFINITY;
+  }
+  if (lane == 0) tmp[warp] = jth;
+  __syncthreads();
+  float bound = tmp[0];
+#pragma unroll
+  for (int w = 1; w < kWarps; ++w) bound = fminf(bound, tmp[w]);
+  return bound;
+}
+
+// The slow selector: the k best (value desc, index asc) of elements [lo, hi) of a row, one CTA-wide pass per
+// entry (each pass finds the best element that comes after the previous pick in that order).  Only slices
+// whose candidates overflowed the buffer come here.
+template <typename T>
+__device__ void select_slow(const T* rowp, int lo, int hi, int k, Cand* out, Cand* s_red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float pv = INFINITY;
+  int pid = -1;
+  for (int r = 0; r < k; ++r) {
+    float bv = -INFINITY;
+    int bid = INT_MAX;
+    for (int i = lo + threadIdx.x; i < hi; i += kThreads) {
+      const float x = to_f32<T>(rowp[i]);
+      const bool after = x < pv || (x == pv && i > pid);
+      if (after && better(x, i, bv, bid)) {
+        bv = x;
+        bid = i;
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bid, off);
+      if (better(ov, oi, bv, bid)) {
+        bv = ov;
+        bid = oi;
+      }
+    }
+    __syncthreads();
+    if (lane == 0) s_red[warp] = Cand{bv, bid};
+    __syncthreads();
+    bv = s_red[0].v;
+    bid = s_red[0].id;
+    for (int w = 1; w < kWarps; ++w)
+      if (better(s_red[w].v, s_red[w].id, bv, bid)) {
+        bv = s_red[w].v;
+        bid = s_red[w].id;
+      }
+    if (threadIdx.x == 0) out[r] = Cand{bv, bid};
+    pv = bid == INT_MAX ? -INFINITY : bv;
+    pid = bid == INT_MAX ? INT_MAX : bid;
+  }
+  __syncthreads();
+}
+
+template <typename T, int KIND, bool PRESCALE>
 __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka) {
-  __shared__ Cand s_queue[kWarps][kQueue];
-  __shared__ int s_qn[kWarps];
-  __shared__ float s_pub[kWarps];  // each warp's j-th best value: min over warps bounds the k-th best of the row
-  __shared__ Cand s_cand[kMaxK * kMaxK];  // the candidates of a merge across slices or across a sequence's rows
+  extern __shared__ __align__(128) unsigned char smem_raw[];  // the ring; after streaming, the merges' candidates
+  __shared__ Cand s_buf[kCap];
   __shared__ Cand s_best[kMaxK];
+  __shared__ Cand s_red[kWarps];
+  __shared__ float s_tmp[kWarps * kMaxK];
   __shared__ float s_c[kWarps], s_s[kWarps];
-  __shared__ int s_flag;
+  __shared__ __align__(8) uint64_t s_full[kStages];
+  __shared__ float s_thr;
+  __shared__ int s_cnt, s_cnt2, s_flag, s_abort;
 
   const subspec_expand_args& a = ka.a;
   const int L = a.leaves, V = a.vocab, k = a.k;
@@ -275,167 +399,216 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
   const T* rowp = reinterpret_cast<const T*>(a.scores) + (size_t)b * a.seq_stride + (size_t)(row - b * L) * a.row_stride;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int VN = Elem<T>::N;
-  const int jpub = (k + kWarps - 1) / kWarps;  // kWarps * jpub >= k distinct elements
 
-  WarpTopK top;
-  top.init(k);
   SoftAcc soft;
   soft.init(ka.kT);
-  if (lane == 0) {
-    s_qn[warp] = 0;
-    s_pub[warp] = -INFINITY;
+  Slice sl{s_buf, &s_cnt, k + kSlack, false};
+  if (threadIdx.x == 0) {
+    s_cnt = 0;
+    s_cnt2 = 0;
+    s_abort = 0;
+    for (int st = 0; st < kStages; ++st) mbar_init(&s_full[st], 1);
+    mbar_init_fence();
   }
+  fence_async_smem();
   __syncthreads();
   float thr = -INFINITY;
+  bool overflow = false;  // the same in every thread
+
+  // Raise the threshold at a stage boundary: the buffer is cut back to its k best entries (rank counting, every
+  // entry against all others).  Called by the whole CTA between two stages, when nobody is pushing.
+  auto tighten = [&]() {
+    const int n = s_cnt;
+    if (n > kCap) {  // candidates were dropped: this slice goes to the slow selector
+      overflow = true;
+      thr = INFINITY;
+      __syncthreads();
+    } else {
+      const int P = lanes_per_candidate(n);  // n <= kCap = kThreads: one sweep
+      const int i = threadIdx.x / P;
+      const bool mine = i < n && (threadIdx.x & (P - 1)) == 0;
+      const Cand me = i < n ? s_buf[i] : Cand{-INFINITY, INT_MAX};
+      int rank = coop_rank(n, P, i, me, [&](int j) { return s_buf[j]; });
+      if (!mine) rank = INT_MAX;
+      __syncthreads();
+      if (rank < k) s_buf[rank] = me;
+      if (rank == k - 1) s_thr = me.v;
+    }
+    if (threadIdx.x == 0) s_cnt = overflow ? 0 : min(n, k);
+    sl.hot = false;
+    __syncthreads();
+    if (!overflow && n >= k) thr = fmaxf(thr, s_thr);
+  };
 
   const int nvec = ka.vec_ok ? V / VN : 0;
   // this CTA's slice of the row's vectors (the whole row when S == 1); the scalar tail goes with the last slice
   const int vec_per = (nvec + S - 1) / S;
   const int v0 = min(split * vec_per, nvec), v1 = min(v0 + vec_per, nvec);
-  const uint4* vp = reinterpret_cast<const uint4*>(rowp);
-  // One thread asks L2 for the row a few iterations ahead of the loads (bulk prefetch, no registers, no
-  // barrier): a thread has its four loads in flight only while it waits for them, which alone leaves the
-  // SM far short of the bytes in flight that its share of the HBM bandwidth needs.
-  constexpr int kIterVecs = kThreads * kUnroll;  // 16 KB of the row per iteration
-  auto prefetch_iter = [&](int it) {
-    const int p0 = v0 + it * kIterVecs;
-    if (p0 < v1) l2_prefetch(vp + p0, (uint32_t)(min(kIterVecs, v1 - p0) * 16));
-  };
-  if (threadIdx.x == 0)
-    for (int it = 0; it < kPrefetchAhead; ++it) prefetch_iter(it);
-  for (int i0 = v0; i0 < v1; i0 += kThreads * kUnroll) {
-    if (threadIdx.x == 0) prefetch_iter((i0 - v0) / kIterVecs + kPrefetchAhead);
-    // refresh the threshold: own k-th best, and the bound the other warps have published
-    {
-      float t = s_pub[0];
+  int lo_elem = v0 * VN, hi_elem = v1 * VN;  // what the slow selector would scan
+  if (ka.vec_ok) {
+    // The slice is staged through a ring of kStages 16 KB buffers by TMA bulk copies that thread 0 issues
+    // kStages - 1 stages ahead; the barrier at the top of iteration st proves that stage st - 1 has been read
+    // by everyone, so its buffer is refilled, and carries the vote on whether the buffer needs cutting back.
+    const uint4* vp = reinterpret_cast<const uint4*>(rowp);
+    uint4* ring = reinterpret_cast<uint4*>(smem_raw);
+    const int nst = (v1 - v0 + kStageVecs - 1) / kStageVecs;
+    auto issue = [&](int st) {
+      const int a0 = v0 + st * kStageVecs;
+      const uint32_t bytes = (uint32_t)(min(kStageVecs, v1 - a0) * 16);
+      uint64_t* bar = &s_full[st % kStages];
+      mbar_expect_tx(bar, bytes);
+      bulk_g2s(ring + (size_t)(st % kStages) * kStageVecs, vp + a0, bytes, bar);
+    };
+    if (threadIdx.x == 0)
+      for (int st = 0; st < kStages - 1 && st < nst; ++st) issue(st);
+    for (int st = 0; st < nst; ++st) {
+      const int need = __syncthreads_or(sl.hot ? 1 : 0);
+      if (s_abort) break;
+      if (need) tighten();
+      if (threadIdx.x == 0 && st + kStages - 1 < nst) issue(st + kStages - 1);
+      if (!mbar_wait_bounded(&s_full[st % kStages], (uint32_t)(st / kStages) & 1u)) s_abort = 1;
+      const uint4* buf = ring + (size_t)(st % kStages) * kStageVecs;
+      const int a0 = v0 + st * kStageVecs;
+      const bool full = a0 + kStageVecs <= v1;  // all but a slice's last stage
+      uint4 q[kUnroll];
 #pragma unroll
-      for (int w = 1; w < kWarps; ++w) t = fminf(t, s_pub[w]);
-      thr = fmaxf(top.kth_value(), t);
-    }
-    uint4 q[kUnroll];
-    float m[kUnroll];
-    bool have[kUnroll];
+      for (int j = 0; j < kUnroll; ++j)
+        q[j] = (full || a0 + threadIdx.x + j * kThreads < v1) ? buf[threadIdx.x + j * kThreads] : Elem<T>::lowest();
+      float m[kUnroll];
 #pragma unroll
-    for (int j = 0; j < kUnroll; ++j) {
-      const int i = i0 + threadIdx.x + j * kThreads;
-      have[j] = i < v1;
-      if (have[j]) {
-        q[j] = ld_stream_u4(vp + i);
-        m[j] = Elem<T>::vmax(q[j]);
-      } else {
-        q[j] = make_uint4(0, 0, 0, 0);
-        m[j] = -INFINITY;
-      }
-    }
-    const float gm = fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
-    if (i0 == v0) {
-      // First group: the k-th largest of the 32 lane maxima is k distinct elements' worth of evidence that the
-      // warp's k-th best is at least that, which keeps the first round of candidates to a few dozen.
-      thr = fmaxf(thr, warp_kth_largest(gm, k));
-    }
-    if (KIND == SUBSPEC_IN_LOGITS) {
-      // With pre-scaling the sums run over round(x / T); the multiply by 1 / T used here can differ from the
-      // division by one fp32 ulp before rounding, which the k survivors (recomputed exactly below) never see.
-      soft.ensure(ka.prescale ? Elem<T>::round_to(gm * ka.invT) : gm);
+      for (int j = 0; j < kUnroll; ++j) m[j] = Elem<T>::vmax(q[j]);
+      const float gm = fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+      if (st == 0) thr = (ka.dbg & 4) ? INFINITY : fmaxf(thr, cta_kth_lower_bound(gm, k, s_tmp));
+      if (KIND == SUBSPEC_IN_LOGITS && !(ka.dbg & 1)) {
+        // With pre-scaling the sums run over round(x / T); the multiply by 1 / T used here can differ from the
+        // division by one fp32 ulp before rounding, which the k survivors (recomputed exactly below) never see.
+        // Vectors past the end of a last, partial stage hold the lowest finite value: 2^y = 0 for them.
+        soft.ensure(fmaxf(PRESCALE ? Elem<T>::round_to(gm * ka.invT) : gm, -1.0e30f));
 #pragma unroll
-      for (int j = 0; j < kUnroll; ++j) {
-        if (!have[j]) continue;
-        float x[VN];
-        Elem<T>::unpack(q[j], x);
-        if (ka.prescale) {
-#pragma unroll
-          for (int e = 0; e < VN; ++e) x[e] = Elem<T>::round_to(x[e] * ka.invT);
-        }
-#pragma unroll
-        for (int e = 0; e < VN; e += 2) soft.add_pair(x[e], x[e + 1]);
-      }
-    }
-    // candidates: rare after the first groups
-    if (__ballot_sync(0xffffffffu, gm >= thr)) {
-#pragma unroll
-      for (int j = 0; j < kUnroll; ++j) {
-        if (!__ballot_sync(0xffffffffu, m[j] >= thr)) continue;
-        if (m[j] >= thr) {
-          float x[VN];
-          Elem<T>::unpack(q[j], x);
-          const int base = (i0 + threadIdx.x + j * kThreads) * VN;
-#pragma unroll
-          for (int e = 0; e < VN; ++e)
-            if (x[e] >= thr) {
-              const int p = atomicAdd(&s_qn[warp], 1);
-              s_queue[warp][p] = Cand{x[e], base + e};
+        for (int j = 0; j < kUnroll; ++j)
+          for_pairs<T>(q[j], [&](float x0, float x1) {
+            if (PRESCALE) {
+              x0 = Elem<T>::round_to(x0 * ka.invT);
+              x1 = Elem<T>::round_to(x1 * ka.invT);
             }
+            soft.add_pair(x0, x1);
+          });
+      }
+      if (gm >= thr && !(ka.dbg & 2)) {
+        const float t = full ? thr : fmaxf(thr, Elem<T>::above_lowest());  // the filler never qualifies
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j)
+          if (m[j] >= t) sl.push(m[j], (a0 + threadIdx.x + j * kThreads) * VN);
+      }
+    }
+    if (split == S - 1) {  // scalar tail of an aligned row whose length is not a multiple of the vector
+      hi_elem = V;
+      const int i = nvec * VN + threadIdx.x;
+      if (i < V) {
+        const float x = to_f32<T>(rowp[i]);
+        if (KIND == SUBSPEC_IN_LOGITS) {
+          const float xs = PRESCALE ? Elem<T>::round_to(x * ka.invT) : x;
+          soft.ensure(fmaxf(xs, -1.0e30f));
+          soft.add_one(xs);
         }
-        __syncwarp();
-        const int qn = s_qn[warp];
-        for (int i = 0; i < qn; ++i) {
-          const Cand cnd = s_queue[warp][i];
-          top.insert(cnd.v, cnd.id);
-        }
-        const float pub = top.value_at(jpub - 1);
-        thr = fmaxf(thr, top.kth_value());
-        __syncwarp();
-        if (lane == 0) {
-          s_qn[warp] = 0;
-          s_pub[warp] = pub;
-        }
-        __syncwarp();
+        if (x >= thr) sl.push(x, i);
+      }
+    }
+  } else {
+    // Rows that do not start on 16-byte boundaries: the same scheme over "stages" of kThreads * 32 elements read
+    // straight from global memory, thread t taking elements t, t + kThreads, ... of the stage.
+    lo_elem = 0;
+    hi_elem = V;
+    constexpr int kPer = 32;
+    for (int e0 = 0; e0 < V; e0 += kThreads * kPer) {
+      const int need = __syncthreads_or(sl.hot ? 1 : 0);
+      if (need) tighten();
+      float gm = -INFINITY;
+      for (int j = 0; j < kPer; ++j) {
+        const int i = e0 + threadIdx.x + j * kThreads;
+        if (i < V) gm = fmaxf(gm, to_f32<T>(rowp[i]));
+      }
+      if (e0 == 0) thr = fmaxf(thr, cta_kth_lower_bound(gm, k, s_tmp));
+      if (KIND == SUBSPEC_IN_LOGITS && gm != -INFINITY)
+        soft.ensure(fmaxf(PRESCALE ? Elem<T>::round_to(gm * ka.invT) : gm, -1.0e30f));
+      for (int j = 0; j < kPer; ++j) {
+        const int i = e0 + threadIdx.x + j * kThreads;
+        if (i >= V) break;
+        const float x = to_f32<T>(rowp[i]);
+        if (KIND == SUBSPEC_IN_LOGITS) soft.add_one(PRESCALE ? Elem<T>::round_to(x * ka.invT) : x);
+        if (x >= thr) sl.push(x, i);
       }
     }
   }
-  // scalar tail (and whole unaligned rows): lane by lane through the same queue
-  for (int i0 = (split == S - 1 ? nvec * VN : V); i0 < V; i0 += kThreads) {
-    const int i = i0 + threadIdx.x;
-    float x = -INFINITY;
-    if (i < V) x = to_f32<T>(rowp[i]);
-    if (KIND == SUBSPEC_IN_LOGITS && i < V) {
-      const float xs = ka.prescale ? Elem<T>::round_to(x * ka.invT) : x;
-      soft.ensure(fmaxf(xs, -1.0e30f));
-      soft.add_one(xs);
+  {
+    const int need = __syncthreads_or(sl.hot ? 1 : 0);  // every push is in
+    if (s_abort) {  // a bulk copy never completed: report and leave together
+      if (threadIdx.x == 0) flag(a.dev_status, SUBSPEC_DEV_TIMEOUT);
+      return;
     }
-    thr = fmaxf(thr, top.kth_value());
-    if (__ballot_sync(0xffffffffu, i < V && x >= thr)) {
-      if (i < V && x >= thr) {
-        const int p = atomicAdd(&s_qn[warp], 1);
-        s_queue[warp][p] = Cand{x, i};
-      }
-      __syncwarp();
-      const int qn = s_qn[warp];
-      for (int t = 0; t < qn; ++t) {
-        const Cand cnd = s_queue[warp][t];
-        top.insert(cnd.v, cnd.id);
-      }
-      __syncwarp();
-      if (lane == 0) s_qn[warp] = 0;
-      __syncwarp();
-    }
+    if (need && s_cnt > kCap) overflow = true;
   }
 
-  // ---- merge the warps' lists and softmax sums ----
-  if (lane < k) s_cand[warp * k + lane] = Cand{top.v, top.id};  // the warps' lists, back to back
+  if (ka.dbg & 8) return;
+  // ---- the slice's k best, and its softmax sum ----
+  Cand* s_cand = reinterpret_cast<Cand*>(smem_raw);  // 6144 entries: the ring is idle from here on
+  if (overflow) {
+    select_slow<T>(rowp, lo_elem, hi_elem, k, s_best, s_red);
+  } else {
+    // the k-th largest entry of the buffer bounds the k-th best element from below ...
+    const int n = min(s_cnt, kCap);
+    if (threadIdx.x == 0) s_thr = -INFINITY;
+    __syncthreads();
+    {
+      const int P = lanes_per_candidate(n);
+      const int i = threadIdx.x / P;
+      const Cand me = i < n ? s_buf[i] : Cand{-INFINITY, INT_MAX};
+      const int rank = coop_rank(n, P, i, me, [&](int j) { return s_buf[j]; });
+      if (i < n && (threadIdx.x & (P - 1)) == 0 && rank == k - 1) s_thr = me.v;
+    }
+    __syncthreads();
+    // ... and the elements at or above it, all of which sit in buffered vectors, compete
+    const float tv = s_thr;
+    const int vec_end = nvec * VN;  // entries from here on (and all entries of an unaligned row) are single elements
+    for (int i = threadIdx.x; i < n; i += kThreads) {
+      const Cand u = s_buf[i];
+      if (!(u.v >= tv)) continue;
+      if (u.id < vec_end) {
+        float x[VN];
+        Elem<T>::unpack(reinterpret_cast<const uint4*>(rowp)[u.id / VN], x);
+#pragma unroll
+        for (int e = 0; e < VN; ++e)
+          if (x[e] >= tv) s_cand[atomicAdd(&s_cnt2, 1)] = Cand{x[e], u.id + e};
+      } else {
+        s_cand[atomicAdd(&s_cnt2, 1)] = u;
+      }
+    }
+    __syncthreads();
+    cta_topk(s_cnt2, k, [&](int i) { return s_cand[i]; }, s_best);
+  }
   {
-    float c = soft.c, s = soft.sum();
+    float c = soft.c, sm = soft.sum();
     if (KIND != SUBSPEC_IN_LOGITS) {
       c = 0.f;
-      s = 1.f;
+      sm = 1.f;
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
       const float oc = __shfl_xor_sync(0xffffffffu, c, off);
-      const float os = __shfl_xor_sync(0xffffffffu, s, off);
-      combine_soft(c, s, oc, os);
+      const float os = __shfl_xor_sync(0xffffffffu, sm, off);
+      combine_soft(c, sm, oc, os);
     }
     if (lane == 0) {
       s_c[warp] = c;
-      s_s[warp] = s;
+      s_s[warp] = sm;
     }
   }
   __syncthreads();
-  // ---- the k best of the warps' lists: every candidate counts who beats it (see cta_topk) ----
-  cta_topk(
-      kWarps * k, k, [&](int i) { return s_cand[i]; }, s_best);
-  Cand* top_dst = S > 1 ? ka.parttop + ((size_t)row * S + split) * k : ka.rowtop + (size_t)row * k;
-  RowOut* out_dst = S > 1 ? ka.partout + (size_t)row * S + split : ka.rowout + row;
+  if (ka.dbg & 32) return;
+  // ---- the slice's list and softmax sum go to scratch; the last slice of the SEQUENCE to arrive merges ----
+  // (one ticket per sequence counts leaves x slices arrivals: the slices of a row do not meet first, which
+  // would put a second fence / atomic / reload round trip on the path of every row)
+  Cand* top_dst = ka.parttop + ((size_t)row * S + split) * k;
   if (threadIdx.x < k) top_dst[threadIdx.x] = s_best[threadIdx.x];
   if (threadIdx.x == 0) {
     float c = s_c[0], sm = s_s[0];
@@ -444,55 +617,42 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
       c = 0.f;
       sm = 1.f;
     }
-    *out_dst = RowOut{c, sm};
-  }
-  if (S > 1) {
-    // ---- the row's slices meet: the last one to arrive folds all S lists and sums into the row's ----
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) s_flag = (atomicAdd(ka.rowticket + row, 1) == S - 1);
-    __syncthreads();
-    if (!s_flag) return;
-    __threadfence();
-    const int total = S * k;  // <= kMaxRowSplits * kMaxK
-    const volatile Cand* src = ka.parttop + (size_t)row * S * k;
-    for (int t = threadIdx.x; t < total; t += kThreads) s_cand[t] = Cand{src[t].v, src[t].id};
-    __syncthreads();
-    cta_topk(
-        total, k, [&](int i) { return s_cand[i]; }, s_best);
-    if (threadIdx.x < k) ka.rowtop[(size_t)row * k + threadIdx.x] = s_best[threadIdx.x];
-    if (threadIdx.x == 0) {
-      const volatile RowOut* po = ka.partout + (size_t)row * S;
-      float c = po[0].c, sm = po[0].s;
-      for (int i = 1; i < S; ++i) combine_soft(c, sm, po[i].c, po[i].s);
-      ka.rowout[row] = RowOut{c, sm};
-    }
+    ka.partout[(size_t)row * S + split] = RowOut{c, sm};
   }
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) s_flag = (atomicAdd(ka.ticket + b, 1) == L - 1);
+  if (threadIdx.x == 0) s_flag = (atomicAdd(ka.ticket + b, 1) == L * S - 1);
   __syncthreads();
-  if (!s_flag) return;
+  if (!s_flag || (ka.dbg & 16)) return;
   __threadfence();
 
   // ---- the last CTA of the sequence: scores with the reference's rounding, global top-k ----
   {
-    const int total = L * k;  // <= kMaxK * kMaxK
+    // every row's softmax shift and denominator from its slices' (in slice order: the same bits on every run)
+    if (threadIdx.x < L) {
+      const volatile RowOut* po = ka.partout + ((size_t)b * L + threadIdx.x) * S;
+      float c = po[0].c, sm = po[0].s;
+      for (int i = 1; i < S; ++i) combine_soft(c, sm, po[i].c, po[i].s);
+      s_tmp[threadIdx.x] = c;
+      s_tmp[kMaxK + threadIdx.x] = sm;
+    }
+    __syncthreads();
+    const int per_row = S * k;
+    const int total = L * per_row;  // <= kMaxSeqCands (the host picks S accordingly)
     for (int t = threadIdx.x; t < total; t += kThreads) {
-      const int l = t / k;
-      const volatile Cand* src = ka.rowtop + ((size_t)b * L + l) * k + (t - l * k);
+      const int l = t / per_row;
+      const volatile Cand* src = ka.parttop + (size_t)b * total + t;
       const float xv = src->v;
       const int xi = src->id;
       Cand out{-INFINITY, INT_MAX};
       if (xi != INT_MAX) {
-        const volatile RowOut* ro = ka.rowout + (size_t)b * L + l;
         float p = xv;
         if (KIND == SUBSPEC_IN_LOGITS) {
           // The survivors' probabilities in double precision: a 16-bit dtype rounds them next, and an error of
           // 1e-6 in fp32 arithmetic on an exponent near 20 would land on the other side of a rounding boundary
           // a few times per thousand values; what is left is the error of the fp32 denominator (~1e-7).
-          const float xs = ka.prescale ? Elem<T>::round_to(__fdiv_rn(xv, ka.T)) : xv;
-          p = (float)(exp2((double)xs * (double)ka.kT - (double)ro->c) / (double)ro->s);
+          const float xs = PRESCALE ? Elem<T>::round_to(__fdiv_rn(xv, ka.T)) : xv;
+          p = (float)(exp2((double)xs * (double)ka.kT - (double)s_tmp[l]) / (double)s_tmp[kMaxK + l]);
         }
         p = Elem<T>::round_to(p);
         const float pp = a.parent_probs ? Elem<T>::load(a.parent_probs, (size_t)b * L + l) : 1.f;
@@ -500,9 +660,36 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
       }
       s_cand[t] = out;
     }
+    __syncthreads();  // s_tmp is reused below
+    if (threadIdx.x == 0) s_cnt2 = 0;
     __syncthreads();
-    cta_topk(
-        total, k, [&](int i) { return s_cand[i]; }, s_best);
+    // A warp's k-th best score bounds the sequence's k-th best from below (k distinct candidates reach it):
+    // the largest such bound over the warps lets a few dozen of the leaves x k candidates into the rank count.
+    {
+      float wk = -INFINITY;
+      for (int t0 = 0; t0 < total; t0 += kThreads) {  // the same trips in every thread
+        const int t = t0 + threadIdx.x;
+        const float sorted = warp_sort_desc(t < total ? s_cand[t].v : -INFINITY);
+        wk = fmaxf(wk, __shfl_sync(0xffffffffu, sorted, k - 1));
+      }
+      if (lane == 0) s_tmp[warp] = wk;
+      __syncthreads();
+      float bound = s_tmp[0];
+      for (int w = 1; w < kWarps; ++w) bound = fmaxf(bound, s_tmp[w]);
+      Cand* s_sel = s_cand + kMaxSeqCands;
+      for (int t = threadIdx.x; t < total; t += kThreads) {
+        const Cand cnd = s_cand[t];
+        if (cnd.id != INT_MAX && cnd.v >= bound) {
+          const int pos = atomicAdd(&s_cnt2, 1);
+          if (pos < kMaxSel) s_sel[pos] = cnd;
+        }
+      }
+      __syncthreads();
+      if (s_cnt2 <= kMaxSel)
+        cta_topk(s_cnt2, k, [&](int i) { return s_sel[i]; }, s_best);
+      else  // thousands of candidates tied at the bound: rank them all
+        cta_topk(total, k, [&](int i) { return s_cand[i]; }, s_best);
+    }
     if (threadIdx.x < k) {
       const int lane_k = threadIdx.x;
       const Cand best = s_best[lane_k];
@@ -676,10 +863,13 @@ size_t align_up(size_t x, size_t al) { return (x + al - 1) / al * al; }
 
 template <typename T>
 cudaError_t launch_expand(const KArgs& ka, int grid, cudaStream_t st) {
+  void (*kernel)(const KArgs) = expand_rows_kernel<T, SUBSPEC_IN_PROBS, false>;
   if (ka.a.input_kind == SUBSPEC_IN_LOGITS)
-    expand_rows_kernel<T, SUBSPEC_IN_LOGITS><<<grid, kThreads, 0, st>>>(ka);
-  else
-    expand_rows_kernel<T, SUBSPEC_IN_PROBS><<<grid, kThreads, 0, st>>>(ka);
+    kernel = ka.prescale ? expand_rows_kernel<T, SUBSPEC_IN_LOGITS, true> : expand_rows_kernel<T, SUBSPEC_IN_LOGITS, false>;
+  // static + dynamic shared memory pass the 48 KB that need no opt-in
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+  if (e != cudaSuccess) return e;
+  kernel<<<grid, kThreads, kRingBytes, st>>>(ka);
   return cudaGetLastError();
 }
 
@@ -691,9 +881,8 @@ using namespace subspec;
 extern "C" int subspec_expand_scratch_bytes(int32_t batch, int32_t leaves, int32_t k, size_t* bytes) {
   if (!bytes || batch < 0 || leaves < 1 || k < 1 || k > kMaxK) return SUBSPEC_EINVAL;
   const size_t rows = (size_t)batch * leaves;
-  // sequence tickets + row tickets | row sums | row lists | slice sums | slice lists (rows may be cut into slices)
-  *bytes = align_up(sizeof(int) * ((size_t)batch + rows), 256) + align_up(sizeof(RowOut) * rows, 256) +
-           align_up(sizeof(Cand) * rows * k, 256) + align_up(sizeof(RowOut) * rows * kMaxRowSplits, 256) +
+  // sequence tickets | slice sums | slice lists (rows may be cut into up to kMaxRowSplits slices)
+  *bytes = align_up(sizeof(int) * (size_t)batch, 256) + align_up(sizeof(RowOut) * rows * kMaxRowSplits, 256) +
            sizeof(Cand) * rows * kMaxRowSplits * k;
   return SUBSPEC_OK;
 }
@@ -725,17 +914,13 @@ extern "C" int subspec_expand_step(const subspec_expand_args* args, subspec_stre
   if (a.scratch_bytes < need || (reinterpret_cast<uintptr_t>(a.scratch) & 255u)) return SUBSPEC_ESCRATCH;
   KArgs ka;
   ka.a = a;
+  ka.dbg = getenv("SUBSPEC_EXPAND_DBG") ? atoi(getenv("SUBSPEC_EXPAND_DBG")) : 0;
   ka.dm_row_stride = a.draft_mask_row_stride ? a.draft_mask_row_stride : a.draft_mask_cols;
   ka.dm_seq_stride = a.draft_mask_seq_stride ? a.draft_mask_seq_stride : (int64_t)a.k * ka.dm_row_stride;
   char* p = reinterpret_cast<char*>(a.scratch);
   const size_t rows = (size_t)a.batch * a.leaves;
   ka.ticket = reinterpret_cast<int*>(p);
-  ka.rowticket = ka.ticket + a.batch;
-  p += align_up(sizeof(int) * ((size_t)a.batch + rows), 256);
-  ka.rowout = reinterpret_cast<RowOut*>(p);
-  p += align_up(sizeof(RowOut) * rows, 256);
-  ka.rowtop = reinterpret_cast<Cand*>(p);
-  p += align_up(sizeof(Cand) * rows * a.k, 256);
+  p += align_up(sizeof(int) * (size_t)a.batch, 256);
   ka.partout = reinterpret_cast<RowOut*>(p);
   p += align_up(sizeof(RowOut) * rows * kMaxRowSplits, 256);
   ka.parttop = reinterpret_cast<Cand*>(p);
@@ -746,21 +931,27 @@ extern "C" int subspec_expand_step(const subspec_expand_args* args, subspec_stre
   ka.kT = ka.prescale ? kLog2e : (float)(1.4426950408889634 / a.temperature);
   ka.vec_ok = ((reinterpret_cast<uintptr_t>(a.scores) & 15u) == 0) && ((a.seq_stride * esz) % 16 == 0) &&
               ((a.row_stride * esz) % 16 == 0);
-  // Few rows: a row alone takes one CTA ~45 us whatever else runs (sixteen dependent iterations plus the
-  // warm-up and the merges), so a single sequence's step cost almost what 32 sequences' did.  Cut every
-  // row into slices while the slices of all rows still fit the machine at once and each has at least one
-  // full iteration of vectors; at 4 x 148 rows and above nothing changes.
+  // A launch with fewer rows than the machine has CTA slots cuts every row into slices, one CTA each, so that
+  // it still fills the machine (a single sequence's step: 16 rows); a slice is at least one 16 KB stage.
+  // With a row per slot or more, rows stay whole: every slice pays the threshold's warm-up again (its own
+  // first stage, and the k ln(stages) candidates after it), which costs more than the even finish buys.
   ka.splits = 1;
   if (ka.vec_ok) {
     const int64_t slots = 4LL * kNumSMs;
-    const int64_t iters = (a.vocab / (int)(16 / esz)) / (kThreads * kUnroll);  // full iterations in a row
+    const int64_t stages = ((a.vocab / (int)(16 / esz)) + kStageVecs - 1) / kStageVecs;
     int64_t sp = slots / (int64_t)rows;
-    if (sp > iters) sp = iters;
+    if (sp > stages) sp = stages;
     if (sp > kMaxRowSplits) sp = kMaxRowSplits;
+    const int64_t mergeable = kMaxSeqCands / ((int64_t)a.leaves * a.k);  // what the sequence's last CTA can hold
+    if (sp > mergeable) sp = mergeable;
     if (sp >= 2) ka.splits = (int)sp;
+    if (const char* ov = getenv("SUBSPEC_EXPAND_SPLITS")) {
+      const int v = atoi(ov);
+      if (v >= 1 && v <= kMaxRowSplits && v <= stages && v <= mergeable) ka.splits = v;
+    }
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  int rc = cuda_check(cudaMemsetAsync(ka.ticket, 0, sizeof(int) * ((size_t)a.batch + rows), st));
+  int rc = cuda_check(cudaMemsetAsync(ka.ticket, 0, sizeof(int) * (size_t)a.batch, st));
   if (rc) return rc;
   cudaError_t e;
   switch (a.dtype) {

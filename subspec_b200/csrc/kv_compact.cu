@@ -78,6 +78,14 @@ __global__ void __launch_bounds__(32) kv_compact_kernel(const Addr ad, const int
   const int b = blockIdx.x / groups;
   const int g = blockIdx.x - b * groups;
   const int lane = threadIdx.x;
+  if (lane == 0) {
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+  }
+  // Launched as a programmatic dependent of whatever precedes it in the stream: when that is the verify kernel
+  // (which lets its dependents go early), this grid's CTAs are resident by the time it ends, and only from
+  // here on do they look at what it wrote (counts, accepted-path indices).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   int n = n_keep[(size_t)b * n_stride];
   if (n > max_beam) {
     flag(dev_status, SUBSPEC_DEV_BAD_INDEX);
@@ -88,10 +96,6 @@ __global__ void __launch_bounds__(32) kv_compact_kernel(const Addr ad, const int
   const int limit = ad.limit();
   const uint32_t rb = (uint32_t)ad.row_bytes;
 
-  if (lane == 0) {
-    mbar_init(&bar, 1);
-    mbar_init_fence();
-  }
   fence_async_smem();
   __syncwarp();
 
@@ -142,6 +146,22 @@ __global__ void __launch_bounds__(32) kv_compact_kernel(const Addr ad, const int
   bulk_wait0();
 }
 
+template <typename Addr>
+cudaError_t launch_compact(const Addr& ad, unsigned grid, size_t smem, cudaStream_t st, const int32_t* offset,
+                           const int32_t* n, const int64_t* beam, int max_beam, int n_stride, uint32_t* status) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kv_compact_kernel<Addr>, ad, offset, n, beam, max_beam, n_stride, status);
+}
+
 }  // namespace
 }  // namespace subspec
 
@@ -168,9 +188,8 @@ extern "C" int subspec_kv_compact_paged(const subspec_kv_paged_args* args, subsp
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (rc) return rc;
   }
-  kv_compact_kernel<PagedAddr><<<(unsigned)grid, 32, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-      ad, a.offset, a.n, a.beam, a.max_beam, a.n_stride > 0 ? a.n_stride : 1, a.dev_status);
-  return cuda_check(cudaGetLastError());
+  return cuda_check(launch_compact(ad, (unsigned)grid, smem, reinterpret_cast<cudaStream_t>(stream), a.offset, a.n,
+                                   a.beam, a.max_beam, a.n_stride > 0 ? a.n_stride : 1, a.dev_status));
 }
 
 extern "C" int subspec_kv_compact_hf(const subspec_kv_hf_args* args, subspec_stream_t stream) {
@@ -189,7 +208,6 @@ extern "C" int subspec_kv_compact_hf(const subspec_kv_hf_args* args, subspec_str
   if (grid > 0x7fffffffLL) return SUBSPEC_EUNSUPPORTED;
   HfAddr ad{a, row_bytes};
   const size_t smem = row_bytes * kChunk;
-  kv_compact_kernel<HfAddr><<<(unsigned)grid, 32, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-      ad, a.offset, a.n, a.beam, a.max_beam, a.n_stride > 0 ? a.n_stride : 1, a.dev_status);
-  return cuda_check(cudaGetLastError());
+  return cuda_check(launch_compact(ad, (unsigned)grid, smem, reinterpret_cast<cudaStream_t>(stream), a.offset, a.n,
+                                   a.beam, a.max_beam, a.n_stride > 0 ? a.n_stride : 1, a.dev_status));
 }

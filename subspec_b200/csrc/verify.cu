@@ -673,6 +673,9 @@ __global__ void __launch_bounds__(kThreads, 4) verify_rows_kernel(const KArgs ka
   const int split = blockIdx.x - row * splits;
   const int b = row / a.max_nodes;
   const int u = row - b * a.max_nodes;
+  // A kernel launched behind this one as a programmatic dependent (the KV compaction) may be scheduled once
+  // every CTA of this grid has got here or left; it waits for this grid's completion before it reads anything.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   int n_nodes, n_rows;
   seq_counts(a, b, n_nodes, n_rows);
   if (u >= n_rows) {

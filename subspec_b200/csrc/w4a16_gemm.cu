@@ -62,6 +62,8 @@ constexpr int kEarlyChunks = 2;       // packed chunks requested before the prol
 constexpr int kMaxRing = 8;           // packed ring, in chunks of kDeqGroups K blocks (one TMA copy each)
 constexpr int kChunkBytes = kDeqGroups * kRawBytes;
 
+constexpr int kMaxGroup = SUBSPEC_W4A16_MAX_GROUP;
+
 struct GemmArgs {
   const unsigned char* wpk;  // packed weights: [N/128][K/64] blocks of kRawBytes
   const __half* xp;          // prepared activations: [K/64][Mpad][64] fp16, rows swizzled
@@ -72,6 +74,13 @@ struct GemmArgs {
   int M, Mpad, N, K, kblocks, splits, ring_raw, b_slots, b_blocks, b_shift, acc_n, acc_stride, issuers;
   int64_t y_stride;
   int cluster;  // the splits of a tile form a thread-block cluster (1, splits, 1): partial sums meet in shared memory
+  // Grouped call: several weight matrices that share the activations are one launch over the concatenation of
+  // their tiles.  Segment s owns tiles [seg_tile0[s], seg_tile0[s + 1]); wpk / y / y_stride above are segment 0's.
+  int nseg;
+  int seg_tile0[kMaxGroup];
+  const unsigned char* seg_wpk[kMaxGroup];
+  __nv_bfloat16* seg_y[kMaxGroup];
+  int64_t seg_ystride[kMaxGroup];
 };
 
 // try_wait with a suspend-time hint: the warp sleeps in hardware (up to the hint) instead of coming back
@@ -316,6 +325,18 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
   unsigned char* b_ring = smem;                                 // Rb slots, 1024-aligned
   unsigned char* raw_ring = b_ring + (size_t)Rb * slot_bytes;   // Rr chunks of four packed blocks
   const int tile = blockIdx.x, split = blockIdx.y;
+  // the weight matrix this tile belongs to (one in a plain call), and the tile's number inside it
+  int ltile = tile;
+  const unsigned char* wpk = g.wpk;
+  __nv_bfloat16* yout = g.y;
+  int64_t ystride = g.y_stride;
+  for (int sgm = 1; sgm < g.nseg; ++sgm)
+    if (tile >= g.seg_tile0[sgm]) {
+      ltile = tile - g.seg_tile0[sgm];
+      wpk = g.seg_wpk[sgm];
+      yout = g.seg_y[sgm];
+      ystride = g.seg_ystride[sgm];
+    }
   const int kb_per = (g.kblocks + g.splits - 1) / g.splits;
   const int kb0 = min(split * kb_per, g.kblocks), kb1 = min(kb0 + kb_per, g.kblocks);
   const int nkb = kb1 - kb0;
@@ -342,7 +363,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
     // Only kEarlyChunks of them: the copy unit serves an SM's requests in order, and the first activation
     // copy must not queue behind a whole ring of packed data.  This thread is also the producer of that
     // ring and carries on after the barrier.
-    const unsigned char* src = g.wpk + ((size_t)tile * g.kblocks + kb0) * kRawBytes;
+    const unsigned char* src = wpk + ((size_t)ltile * g.kblocks + kb0) * kRawBytes;
     const int nchunks = (nkb + kDeqGroups - 1) / kDeqGroups;
     for (int c = 0; c < min(nchunks, kEarlyChunks); ++c) {
       const uint32_t bytes = (uint32_t)(min(kDeqGroups, nkb - c * kDeqGroups) * kRawBytes);
@@ -373,7 +394,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
       p.advance(kEarlyChunks, Rr);
       const int nchunks = (nkb + kDeqGroups - 1) / kDeqGroups;
       const unsigned char* src =
-          g.wpk + ((size_t)tile * g.kblocks + kb0) * kRawBytes + (size_t)kEarlyChunks * kChunkBytes;
+          wpk + ((size_t)ltile * g.kblocks + kb0) * kRawBytes + (size_t)kEarlyChunks * kChunkBytes;
       for (int c = kEarlyChunks; c < nchunks; ++c, src += kChunkBytes) {
         if (c >= Rr && !wait_or_abort(&raw_empty[p.s], (uint32_t)p.ph ^ 1u, abort_flag)) break;
         const uint32_t bytes = (uint32_t)(min(kDeqGroups, nkb - c * kDeqGroups) * kRawBytes);
@@ -518,7 +539,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
     if (wait_or_abort(&acc_full, 0, abort_flag) && !*abort_flag) {
       tc_fence_after();
       const int ew = warp & 3;  // TMEM lanes 32 ew .. 32 ew + 31 (a warp reaches the quarter given by its id mod 4)
-      const int n = tile * kTileN + ew * 32 + lane;
+      const int n = ltile * kTileN + ew * 32 + lane;
       // each group of four warps takes every (kDeqWarps / 4)-th group of 16 tokens
       // accumulators that were written: an issuer's share has at most four members in use, and the second
       // issuer has work only from two K blocks on
@@ -552,7 +573,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
         if (g.splits == 1) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            if (c0 + j < g.M) g.y[(size_t)(c0 + j) * g.y_stride + n] = __float2bfloat16_rn(v[j]);
+            if (c0 + j < g.M) yout[(size_t)(c0 + j) * ystride + n] = __float2bfloat16_rn(v[j]);
         } else if (g.cluster) {
           // [Mpad][128] fp32 over the rings, which nothing uses any more: every MMA has completed
           float* part = reinterpret_cast<float*>(smem) + (size_t)c0 * kTileN + ew * 32 + lane;
@@ -593,7 +614,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
           acc.w += v[u].w;
         }
         const int m = e / (kTileN / 4), c = (e - m * (kTileN / 4)) * 4;
-        __nv_bfloat16* dst = g.y + (size_t)m * g.y_stride + tile * kTileN + c;
+        __nv_bfloat16* dst = yout + (size_t)m * ystride + ltile * kTileN + c;
         dst[0] = __float2bfloat16_rn(acc.x);
         dst[1] = __float2bfloat16_rn(acc.y);
         dst[2] = __float2bfloat16_rn(acc.z);
@@ -633,7 +654,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const GemmArgs 
           }
         }
         const int m = e / (kTileN / 4), c = (e - m * (kTileN / 4)) * 4;
-        __nv_bfloat16* dst = g.y + (size_t)m * g.y_stride + tile * kTileN + c;
+        __nv_bfloat16* dst = yout + (size_t)m * ystride + ltile * kTileN + c;
         dst[0] = __float2bfloat16_rn(acc.x);
         dst[1] = __float2bfloat16_rn(acc.y);
         dst[2] = __float2bfloat16_rn(acc.z);
@@ -765,29 +786,39 @@ extern "C" int subspec_w4a16_scratch_bytes(int32_t m, int32_t n, int32_t k, size
   return SUBSPEC_OK;
 }
 
-extern "C" int subspec_w4a16_gemm(const subspec_w4a16_args* args, subspec_stream_t stream) {
-  if (!args || args->struct_size != sizeof(subspec_w4a16_args)) return SUBSPEC_EINVAL;
-  const subspec_w4a16_args& a = *args;
-  if (!a.x || !a.packed || !a.y || !a.scratch) return SUBSPEC_EINVAL;
+namespace {
+// One launch over `nseg` weight matrices [n[i], k] that share the activations x [m, k].
+int run_gemm(int m, int k, int nseg, const void* const* packed, const int32_t* n, void* const* y,
+             const int64_t* y_stride, const void* x, int64_t x_stride, void* scratch, size_t scratch_bytes,
+             uint32_t* dev_status, subspec_stream_t stream) {
+  if (!x || !scratch || nseg < 1 || nseg > kMaxGroup) return SUBSPEC_EINVAL;
+  int64_t n_total = 0;
+  for (int i = 0; i < nseg; ++i) {
+    if (!packed[i] || !y[i]) return SUBSPEC_EINVAL;
+    if (n[i] < kTileN || n[i] % kTileN) return SUBSPEC_EUNSUPPORTED;
+    if (y_stride[i] < n[i]) return SUBSPEC_EINVAL;
+    if (reinterpret_cast<uintptr_t>(packed[i]) & 15u) return SUBSPEC_ESCRATCH;
+    n_total += n[i];
+  }
+  if (n_total > (1 << 24)) return SUBSPEC_EUNSUPPORTED;
   Plan p;
-  if (!make_plan(a.m, a.n, a.k, &p)) return SUBSPEC_EUNSUPPORTED;
-  if (a.x_stride < a.k || a.y_stride < a.n) return SUBSPEC_EINVAL;
-  if ((reinterpret_cast<uintptr_t>(a.packed) & 15u) || (reinterpret_cast<uintptr_t>(a.scratch) & 255u))
-    return SUBSPEC_ESCRATCH;
-  if (a.scratch_bytes < p.xp_bytes + p.partial_bytes + p.ticket_bytes) return SUBSPEC_ESCRATCH;
+  if (!make_plan(m, (int)n_total, k, &p)) return SUBSPEC_EUNSUPPORTED;
+  if (x_stride < k) return SUBSPEC_EINVAL;
+  if (reinterpret_cast<uintptr_t>(scratch) & 255u) return SUBSPEC_ESCRATCH;
+  if (scratch_bytes < p.xp_bytes + p.partial_bytes + p.ticket_bytes) return SUBSPEC_ESCRATCH;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  char* sp = reinterpret_cast<char*>(a.scratch);
+  char* sp = reinterpret_cast<char*>(scratch);
   GemmArgs g;
-  g.wpk = reinterpret_cast<const unsigned char*>(a.packed);
+  g.wpk = reinterpret_cast<const unsigned char*>(packed[0]);
   g.xp = reinterpret_cast<const __half*>(sp);
   g.partial = reinterpret_cast<float*>(sp + p.xp_bytes);
   g.ticket = reinterpret_cast<int*>(sp + p.xp_bytes + p.partial_bytes);
-  g.y = reinterpret_cast<__nv_bfloat16*>(a.y);
-  g.dev_status = a.dev_status;
-  g.M = a.m;
+  g.y = reinterpret_cast<__nv_bfloat16*>(y[0]);
+  g.dev_status = dev_status;
+  g.M = m;
   g.Mpad = p.Mpad;
-  g.N = a.n;
-  g.K = a.k;
+  g.N = (int)n_total;
+  g.K = k;
   g.kblocks = p.kblocks;
   g.splits = p.splits;
   g.b_slots = p.b_slots;
@@ -797,7 +828,19 @@ extern "C" int subspec_w4a16_gemm(const subspec_w4a16_args* args, subspec_stream
   g.acc_n = p.acc_n;
   g.acc_stride = p.acc_stride;
   g.issuers = p.issuers;
-  g.y_stride = a.y_stride;
+  g.y_stride = y_stride[0];
+  g.nseg = nseg;
+  {
+    int t0 = 0;
+    for (int i = 0; i < kMaxGroup; ++i) {
+      g.seg_tile0[i] = t0;
+      g.seg_wpk[i] = i < nseg ? reinterpret_cast<const unsigned char*>(packed[i]) : nullptr;
+      g.seg_y[i] = i < nseg ? reinterpret_cast<__nv_bfloat16*>(y[i]) : nullptr;
+      g.seg_ystride[i] = i < nseg ? y_stride[i] : 0;
+      if (i < nseg) t0 += n[i] / kTileN;
+    }
+  }
+  struct { const void* x; int64_t x_stride; int m, k; } a{x, x_stride, m, k};
   int rc;
   {
     const int64_t total = (int64_t)p.kblocks * p.Mpad * 8;
@@ -860,4 +903,24 @@ extern "C" int subspec_w4a16_gemm(const subspec_w4a16_args* args, subspec_stream
     }
   }
   return cuda_check(cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, g));
+}
+}  // namespace
+
+extern "C" int subspec_w4a16_gemm(const subspec_w4a16_args* args, subspec_stream_t stream) {
+  if (!args || args->struct_size != sizeof(subspec_w4a16_args)) return SUBSPEC_EINVAL;
+  const subspec_w4a16_args& a = *args;
+  if (!a.x || !a.packed || !a.y || !a.scratch) return SUBSPEC_EINVAL;
+  const void* packed[1] = {a.packed};
+  void* y[1] = {a.y};
+  const int32_t n[1] = {a.n};
+  const int64_t ys[1] = {a.y_stride};
+  return run_gemm(a.m, a.k, 1, packed, n, y, ys, a.x, a.x_stride, a.scratch, a.scratch_bytes, a.dev_status, stream);
+}
+
+extern "C" int subspec_w4a16_gemm_grouped(const subspec_w4a16_group_args* args, subspec_stream_t stream) {
+  if (!args || args->struct_size != sizeof(subspec_w4a16_group_args)) return SUBSPEC_EINVAL;
+  const subspec_w4a16_group_args& a = *args;
+  if (a.count < 1 || a.count > SUBSPEC_W4A16_MAX_GROUP) return SUBSPEC_EINVAL;
+  return run_gemm(a.m, a.k, a.count, a.packed, a.n, a.y, a.y_stride, a.x, a.x_stride, a.scratch, a.scratch_bytes,
+                  a.dev_status, stream);
 }

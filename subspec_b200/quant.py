@@ -104,6 +104,70 @@ def w4a16_matmul(x: torch.Tensor, packed: torch.Tensor, n: int, k: int, status: 
     return y
 
 
+@torch.no_grad()
+def w4a16_matmul_grouped(x: torch.Tensor, packed, ns, k: int, status: Optional[torch.Tensor] = None):
+    """x bf16 [M, K] (M <= 256) times several packed 4-bit weights [N_i, K] in ONE launch -> list of bf16 [M, N_i].
+
+    The projections a decoder layer applies to the same activations (q/k/v; gate/up) cost one launch instead
+    of one each; every result equals the separate call's within the GEMM's tolerance (bit for bit when both
+    plans split K alike)."""
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != k or x.stride(1) != 1:
+        raise ValueError("x must be a bf16 [M, K] matrix with contiguous rows")
+    if not 1 <= len(packed) <= _lib.W4A16_MAX_GROUP or len(packed) != len(ns):
+        raise ValueError(f"1 to {_lib.W4A16_MAX_GROUP} weight matrices per grouped call")
+    M = int(x.shape[0])
+    dev = x.device
+    need = C.c_size_t(0)
+    _lib.check(_lib.lib().subspec_w4a16_scratch_bytes(M, int(sum(ns)), k, C.byref(need)), "subspec_w4a16_scratch_bytes")
+    buf = _scratch.get(dev.index or 0)
+    if buf is None or buf.numel() < need.value + 256:
+        buf = _scratch[dev.index or 0] = torch.empty(need.value + 256, dtype=torch.uint8, device=dev)
+    ys = [torch.empty(M, int(n), dtype=torch.bfloat16, device=dev) for n in ns]
+    a = _lib.W4A16GroupArgs()
+    a.struct_size = C.sizeof(_lib.W4A16GroupArgs)
+    a.m, a.k, a.count = M, k, len(ns)
+    a.x, a.x_stride = x.data_ptr(), int(x.stride(0))
+    for i, (w, n, y) in enumerate(zip(packed, ns, ys)):
+        a.packed[i], a.n[i], a.y[i], a.y_stride[i] = w.data_ptr(), int(n), y.data_ptr(), int(n)
+    a.scratch, a.scratch_bytes = (buf.data_ptr() + 255) // 256 * 256, need.value
+    a.dev_status = 0 if status is None else status.data_ptr()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    _lib.check(_lib.lib().subspec_w4a16_gemm_grouped(C.byref(a), C.c_void_p(stream)), "subspec_w4a16_gemm_grouped")
+    return ys
+
+
+class W4A16Group:
+    """The `W4A16Linear` children of one module that are applied to the same input (q/k/v; gate/up), evaluated
+    in one launch.  `HqqQuantizer.quantize_model` installs one on the parent of every such set as
+    `parent.w4a16_groups[name]`; module boundaries stay as they are, and a forward that wants the saving calls
+    `parent.w4a16_groups["qkv"](x)` where it used to call the three projections."""
+
+    def __init__(self, linears):
+        linears = list(linears)
+        if not linears or len({m.in_features for m in linears}) != 1:
+            raise ValueError("a group needs W4A16Linear modules with one common in_features")
+        self.linears = linears
+
+    def __call__(self, x: torch.Tensor):
+        k = self.linears[0].in_features
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, k).to(torch.bfloat16)
+        if x2.shape[0] > 256:  # beyond one launch's token limit: the members' own forwards
+            return [m(x) for m in self.linears]
+        ys = w4a16_matmul_grouped(x2.contiguous(), [m.packed for m in self.linears],
+                                  [m.out_features for m in self.linears], k)
+        out = []
+        for m, y in zip(self.linears, ys):
+            if m.bias is not None:
+                y = y + m.bias.to(y.dtype)
+            out.append(y.reshape(*lead, m.out_features).to(x.dtype))
+        return out
+
+
+# names of sibling projections that a decoder layer applies to one input
+_SIBLINGS = {"qkv": ("q_proj", "k_proj", "v_proj"), "gate_up": ("gate_proj", "up_proj")}
+
+
 class W4A16Linear(nn.Module):
     """Drop-in for nn.Linear with 4-bit group-64 weights; forward(x[..., K]) -> [..., N] in x's dtype."""
 
@@ -150,4 +214,13 @@ class HqqQuantizer:
             if not isinstance(lin, nn.Linear):
                 raise ValueError(f"{name} is not an nn.Linear")
             setattr(parent, child, W4A16Linear.from_linear(lin, device))
+        # sibling projections of one input, where all of them were quantised: one launch per set on request
+        for parent in model.modules():
+            groups = {}
+            for gname, members in _SIBLINGS.items():
+                mods = [getattr(parent, m, None) for m in members]
+                if all(isinstance(m, W4A16Linear) for m in mods):
+                    groups[gname] = W4A16Group(mods)
+            if groups:
+                parent.w4a16_groups = groups
         return model

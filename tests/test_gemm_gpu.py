@@ -85,3 +85,59 @@ def test_quantizer_hook_replaces_linears(cuda_lib):
     with pytest.raises(ValueError):
         quant.HqqQuantizer.quantize_model(Net().cuda(), {"layers.0.q_proj": quant.BaseQuantizeConfig(nbits=8)}, None,
                                           "cuda")
+
+
+@pytest.mark.parametrize("m", [16, 64, 256])
+@pytest.mark.parametrize("ns,k", [((3584, 512, 512), 3584), ((18944, 18944), 3584), ((128, 256, 128, 384), 640)])
+def test_grouped_projections_equal_separate_calls(cuda_lib, ns, k, m):
+    """q/k/v and gate/up as one launch each: every projection's result against the oracle, and against its own
+    separate call -- bit for bit where both launches cut K into the same pieces (the partial sums are then
+    added in the same order), within the stated tolerance otherwise."""
+    from subspec_b200 import _lib
+    import ctypes as C
+
+    mats = [go.config4_case(n, k, m, seed=17 + i + n) for i, n in enumerate(ns)]
+    x = mats[0][3]
+    packed = [quant.pack(q.cuda(), s.cuda(), z.cuda()) for q, s, z, _ in mats]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ys = quant.w4a16_matmul_grouped(x.cuda(), packed, list(ns), k, status=status)
+    assert int(status.item()) == 0
+    for (q, s, z, _), n, w, y in zip(mats, ns, packed, ys):
+        assert y.shape == (m, n)
+        assert _rel_err(y, go.w4a16_matmul(x, q, s, z)) < TOL
+        sep = quant.w4a16_matmul(x.cuda(), w, n, k)
+        assert _rel_err(y, sep.float().cpu()) < 4e-3   # fp32 sums added in another order: one bf16 ulp at most
+    again = quant.w4a16_matmul_grouped(x.cuda(), packed, list(ns), k)
+    assert all(torch.equal(a, b) for a, b in zip(ys, again))
+    # a group of one is the plain call
+    one = quant.w4a16_matmul_grouped(x.cuda(), packed[:1], [ns[0]], k)[0]
+    assert torch.equal(one, quant.w4a16_matmul(x.cuda(), packed[0], ns[0], k))
+    a = _lib.W4A16GroupArgs()
+    a.struct_size = C.sizeof(_lib.W4A16GroupArgs)
+    a.m, a.k, a.count = m, k, 5
+    assert cuda_lib.subspec_w4a16_gemm_grouped(C.byref(a), None) == _lib.EINVAL
+
+
+def test_quantizer_installs_sibling_groups(cuda_lib):
+    torch.manual_seed(1)
+
+    class Attn(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj = nn.Linear(256, 384, bias=True)
+            self.k_proj = nn.Linear(256, 128, bias=True)
+            self.v_proj = nn.Linear(256, 128, bias=True)
+            self.o_proj = nn.Linear(384, 256, bias=False)
+
+    net = nn.ModuleList([Attn()]).cuda()
+    cfg = {f"0.{p}": quant.BaseQuantizeConfig(nbits=4, group_size=64, axis=1)
+           for p in ("q_proj", "k_proj", "v_proj", "o_proj")}
+    quant.HqqQuantizer.quantize_model(net, cfg, compute_dtype=torch.bfloat16, device="cuda")
+    attn = net[0]
+    assert set(attn.w4a16_groups) == {"qkv"}
+    x = torch.randn(3, 7, 256, device="cuda", dtype=torch.bfloat16)
+    q, k, v = attn.w4a16_groups["qkv"](x)
+    for got, mod in ((q, attn.q_proj), (k, attn.k_proj), (v, attn.v_proj)):
+        want = mod(x)
+        assert got.shape == want.shape and got.dtype == want.dtype
+        assert float((got.float() - want.float()).abs().max() / want.float().abs().max()) < 4e-3
