@@ -17,7 +17,6 @@
 // create_attention_mask (:263-286), position ids = depth + offset (classic_sd.py:73-75).
 #include <limits.h>
 #include <math.h>
-#include <stdlib.h>
 
 #include <type_traits>
 
@@ -103,7 +102,6 @@ struct KArgs {
   // few rows: every row is cut into `splits` slices, one CTA each; the slices' lists and softmax sums meet
   // in scratch behind a ticket per row, and the last slice to arrive carries on as the row's CTA
   int splits;
-  int dbg;
   int64_t dm_row_stride, dm_seq_stride;  // draft-side mask geometry in elements, defaults resolved
   RowOut* partout;  // [batch * leaves * splits]
   Cand* parttop;    // [batch * leaves * splits * k]
@@ -478,8 +476,8 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
 #pragma unroll
       for (int j = 0; j < kUnroll; ++j) m[j] = Elem<T>::vmax(q[j]);
       const float gm = fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
-      if (st == 0) thr = (ka.dbg & 4) ? INFINITY : fmaxf(thr, cta_kth_lower_bound(gm, k, s_tmp));
-      if (KIND == SUBSPEC_IN_LOGITS && !(ka.dbg & 1)) {
+      if (st == 0) thr = fmaxf(thr, cta_kth_lower_bound(gm, k, s_tmp));
+      if (KIND == SUBSPEC_IN_LOGITS) {
         // With pre-scaling the sums run over round(x / T); the multiply by 1 / T used here can differ from the
         // division by one fp32 ulp before rounding, which the k survivors (recomputed exactly below) never see.
         // Vectors past the end of a last, partial stage hold the lowest finite value: 2^y = 0 for them.
@@ -494,7 +492,7 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
             soft.add_pair(x0, x1);
           });
       }
-      if (gm >= thr && !(ka.dbg & 2)) {
+      if (gm >= thr) {
         const float t = full ? thr : fmaxf(thr, Elem<T>::above_lowest());  // the filler never qualifies
 #pragma unroll
         for (int j = 0; j < kUnroll; ++j)
@@ -549,7 +547,6 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
     if (need && s_cnt > kCap) overflow = true;
   }
 
-  if (ka.dbg & 8) return;
   // ---- the slice's k best, and its softmax sum ----
   Cand* s_cand = reinterpret_cast<Cand*>(smem_raw);  // 6144 entries: the ring is idle from here on
   if (overflow) {
@@ -604,7 +601,6 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
     }
   }
   __syncthreads();
-  if (ka.dbg & 32) return;
   // ---- the slice's list and softmax sum go to scratch; the last slice of the SEQUENCE to arrive merges ----
   // (one ticket per sequence counts leaves x slices arrivals: the slices of a row do not meet first, which
   // would put a second fence / atomic / reload round trip on the path of every row)
@@ -623,7 +619,7 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
   __syncthreads();
   if (threadIdx.x == 0) s_flag = (atomicAdd(ka.ticket + b, 1) == L * S - 1);
   __syncthreads();
-  if (!s_flag || (ka.dbg & 16)) return;
+  if (!s_flag) return;
   __threadfence();
 
   // ---- the last CTA of the sequence: scores with the reference's rounding, global top-k ----
@@ -914,7 +910,6 @@ extern "C" int subspec_expand_step(const subspec_expand_args* args, subspec_stre
   if (a.scratch_bytes < need || (reinterpret_cast<uintptr_t>(a.scratch) & 255u)) return SUBSPEC_ESCRATCH;
   KArgs ka;
   ka.a = a;
-  ka.dbg = getenv("SUBSPEC_EXPAND_DBG") ? atoi(getenv("SUBSPEC_EXPAND_DBG")) : 0;
   ka.dm_row_stride = a.draft_mask_row_stride ? a.draft_mask_row_stride : a.draft_mask_cols;
   ka.dm_seq_stride = a.draft_mask_seq_stride ? a.draft_mask_seq_stride : (int64_t)a.k * ka.dm_row_stride;
   char* p = reinterpret_cast<char*>(a.scratch);
@@ -945,10 +940,6 @@ extern "C" int subspec_expand_step(const subspec_expand_args* args, subspec_stre
     const int64_t mergeable = kMaxSeqCands / ((int64_t)a.leaves * a.k);  // what the sequence's last CTA can hold
     if (sp > mergeable) sp = mergeable;
     if (sp >= 2) ka.splits = (int)sp;
-    if (const char* ov = getenv("SUBSPEC_EXPAND_SPLITS")) {
-      const int v = atoi(ov);
-      if (v >= 1 && v <= kMaxRowSplits && v <= stages && v <= mergeable) ka.splits = v;
-    }
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc = cuda_check(cudaMemsetAsync(ka.ticket, 0, sizeof(int) * (size_t)a.batch, st));

@@ -67,9 +67,8 @@ struct HfAddr {
 };
 
 template <typename Addr>
-__global__ void __launch_bounds__(32) kv_compact_kernel(const Addr ad, const int32_t* __restrict__ offset,
-                                                        const int32_t* __restrict__ n_keep,
-                                                        const int64_t* __restrict__ beam, int max_beam,
+__global__ void __launch_bounds__(32) kv_compact_kernel(const Addr ad, const int32_t* offset, const int32_t* n_keep,
+                                                        const int64_t* beam, int max_beam,
                                                         int n_stride, uint32_t* dev_status) {
   extern __shared__ __align__(128) unsigned char stage[];
   __shared__ __align__(8) uint64_t bar;
@@ -86,13 +85,15 @@ __global__ void __launch_bounds__(32) kv_compact_kernel(const Addr ad, const int
   // (which lets its dependents go early), this grid's CTAs are resident by the time it ends, and only from
   // here on do they look at what it wrote (counts, accepted-path indices).
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  int n = n_keep[(size_t)b * n_stride];
+  // (read past L1, like everything else the grid before this one wrote: this grid is resident while that one
+  // still runs, so nothing it writes may be treated as read-only data)
+  int n = __ldcg(n_keep + (size_t)b * n_stride);
   if (n > max_beam) {
     flag(dev_status, SUBSPEC_DEV_BAD_INDEX);
     n = max_beam;
   }
   if (n <= 0) return;
-  const int off = offset[b];
+  const int off = __ldcg(offset + b);
   const int limit = ad.limit();
   const uint32_t rb = (uint32_t)ad.row_bytes;
 
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(32) kv_compact_kernel(const Addr ad, const int
     char* src = nullptr;
     char* dst = nullptr;
     if (active) {
-      const int64_t bi = beam[(size_t)b * max_beam + i];
+      const int64_t bi = __ldcg(beam + (size_t)b * max_beam + i);
       const int64_t sp = (int64_t)off + bi;
       if (bi < i || sp >= limit || off < 0) {
         flag(dev_status, SUBSPEC_DEV_BAD_INDEX);
