@@ -482,6 +482,78 @@ typedef struct subspec_tree_finalize_args {
 SUBSPEC_API int subspec_tree_finalize(const subspec_tree_finalize_args* args, subspec_stream_t stream);
 
 /* ------------------------------------------------------------------------
+ * Between one verification and the next (the SubSpec-v2 loop), per sequence:
+ *
+ *   - re-rooting: next_root = the child of the last context node that carries
+ *     the bonus token, in the tree's own numbering, or -1
+ *       Tree.find_child_index        specdecodes/models/utils/cpu_tree.py:232-236
+ *       its call site                specdecodes/models/generators/subspec_sd_v2.py:231-236
+ *   - delayed reorder: the step's hidden indices are appended to beam_cache
+ *     (hidden_indices_cache, subspec_sd_v2.py:223-229); when the bonus token
+ *     missed every child, or finished[b] is set, the KV rows gathered since the
+ *     last reorder are to be kept now: reorder_n[b] = their number,
+ *     reorder_offset[b] = kv_len[b] before, kv_len[b] += reorder_n[b], and the
+ *     cache restarts empty; otherwise reorder_n[b] = 0 (subspec_sd_v2.py:250-262).
+ *     subspec_kv_compact_* then takes n = reorder_n, beam = beam_cache,
+ *     offset = reorder_offset, without a host round trip.
+ *
+ * The tree arrays are the ones the verification ran on (local numbering,
+ * node 0 = first decoded node); out_* are its outputs.  skip_nodes[b] is added
+ * to every index that leaves this call (NULL = 0).
+ * ---------------------------------------------------------------------- */
+typedef struct subspec_post_verify_args {
+  uint32_t struct_size;
+  int32_t batch;
+  int32_t max_nodes; /* stride of the per-node arrays, as in subspec_verify_args */
+  int32_t max_out;   /* stride of out_tokens / out_hidden */
+  const int32_t* n_nodes;
+  const int32_t* token_ids;
+  const int32_t* child_off;
+  const int32_t* child_idx;
+  const int64_t* out_tokens;
+  const int64_t* out_hidden;
+  const int32_t* out_meta;
+  const int32_t* skip_nodes; /* [batch] or NULL */
+  const uint8_t* finished;   /* [batch] or NULL */
+  int32_t* next_root;        /* [batch] out */
+  int32_t* accepted;         /* [batch] out, or NULL: next_root >= 0 */
+  int64_t* beam_cache;       /* [batch, beam_stride] in/out */
+  int32_t beam_stride;
+  int32_t* beam_len;       /* [batch] in/out: entries of beam_cache in use */
+  int32_t* reorder_n;      /* [batch] out */
+  int32_t* reorder_offset; /* [batch] out, or NULL */
+  int32_t* kv_len;         /* [batch] in/out, or NULL */
+  uint32_t* dev_status;
+} subspec_post_verify_args;
+
+SUBSPEC_API int subspec_post_verify(const subspec_post_verify_args* args, subspec_stream_t stream);
+
+/* Tree.prune_to_depth (cpu_tree.py:119-173; _post_verify, subspec_sd_v2.py:44-45): keep the nodes with
+ * depth <= max_depth[b] in their original order, in place on the tree arrays [batch, tree_stride]
+ * (n_nodes[b] in use; parents re-linked, -1 for a root); keep_idx[r] = old index of new node r,
+ * n_out[b] = nodes kept.  child_off [batch, tree_stride + 1] / child_idx [batch, tree_stride], when given
+ * (both or neither), are the children lists in subspec_verify_batched's layout and are filtered in place, a
+ * node's kept children in the order its list had them.  tree_stride <= 4096. */
+typedef struct subspec_tree_prune_depth_args {
+  uint32_t struct_size;
+  int32_t batch;
+  int32_t tree_stride;
+  const int32_t* n_nodes;   /* [batch] */
+  const int32_t* max_depth; /* [batch] */
+  int32_t* tokens;
+  int32_t* parents;
+  int32_t* depths;
+  float* probs; /* or NULL */
+  int32_t* keep_idx;
+  int32_t* n_out;
+  int32_t* child_off; /* or NULL */
+  int32_t* child_idx; /* or NULL */
+  uint32_t* dev_status;
+} subspec_tree_prune_depth_args;
+
+SUBSPEC_API int subspec_tree_prune_depth(const subspec_tree_prune_depth_args* args, subspec_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * W4A16 group-wise dequant GEMM (the HQQ 4-bit draft linear).
  *
  *   y[m, n] = sum_k x[m, k] * (q[n, k] - zero[n, k / 64]) * scale[n, k / 64]

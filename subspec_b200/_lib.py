@@ -123,6 +123,28 @@ class W4A16Args(C.Structure):
     ]
 
 
+class PostVerifyArgs(C.Structure):
+    """Mirror of `subspec_post_verify_args`."""
+
+    _fields_ = [
+        ("struct_size", _u32), ("batch", _i32), ("max_nodes", _i32), ("max_out", _i32), ("n_nodes", _vp),
+        ("token_ids", _vp), ("child_off", _vp), ("child_idx", _vp), ("out_tokens", _vp), ("out_hidden", _vp),
+        ("out_meta", _vp), ("skip_nodes", _vp), ("finished", _vp), ("next_root", _vp), ("accepted", _vp),
+        ("beam_cache", _vp), ("beam_stride", _i32), ("beam_len", _vp), ("reorder_n", _vp), ("reorder_offset", _vp),
+        ("kv_len", _vp), ("dev_status", _vp),
+    ]
+
+
+class TreePruneDepthArgs(C.Structure):
+    """Mirror of `subspec_tree_prune_depth_args`."""
+
+    _fields_ = [
+        ("struct_size", _u32), ("batch", _i32), ("tree_stride", _i32), ("n_nodes", _vp), ("max_depth", _vp),
+        ("tokens", _vp), ("parents", _vp), ("depths", _vp), ("probs", _vp), ("keep_idx", _vp), ("n_out", _vp),
+        ("child_off", _vp), ("child_idx", _vp), ("dev_status", _vp),
+    ]
+
+
 W4A16_MAX_GROUP = 4
 
 
@@ -148,6 +170,8 @@ SYMBOLS = {
     "subspec_expand_scratch_bytes": (C.c_int, [_i32, _i32, _i32, C.POINTER(C.c_size_t)]),
     "subspec_expand_step": (C.c_int, [C.POINTER(ExpandArgs), _vp]),
     "subspec_tree_finalize": (C.c_int, [C.POINTER(TreeFinalizeArgs), _vp]),
+    "subspec_post_verify": (C.c_int, [C.POINTER(PostVerifyArgs), _vp]),
+    "subspec_tree_prune_depth": (C.c_int, [C.POINTER(TreePruneDepthArgs), _vp]),
     "subspec_w4a16_packed_bytes": (C.c_int, [_i32, _i32, C.POINTER(C.c_size_t)]),
     "subspec_w4a16_pack": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),
     "subspec_w4a16_scratch_bytes": (C.c_int, [_i32, _i32, _i32, C.POINTER(C.c_size_t)]),

@@ -254,7 +254,7 @@ __global__ void w4a16_pack_kernel(const uint32_t* __restrict__ qweight, const __
 
 // x bf16 [M, K] -> fp16 blocks [K/64][Mpad][64], 16-byte chunk c of row r stored at chunk c ^ (r & 7)
 // (the 128-byte swizzle the tensor core expects); rows >= M are zero.  Also clears the split-K tickets.
-__global__ void w4a16_prep_x_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_stride, __half* __restrict__ xp,
+__global__ void w4a16_prep_x_kernel(const __nv_bfloat16* x, int64_t x_stride, __half* __restrict__ xp,
                                     int M, int Mpad, int K, int* __restrict__ ticket, int tiles) {
   // The GEMM that follows in the stream is launched as a programmatic dependent: it may start now and run
   // its prologue and its weight stream beside this kernel; it waits for this grid's completion (and the
@@ -276,11 +276,13 @@ __global__ void w4a16_prep_x_kernel(const __nv_bfloat16* __restrict__ x, int64_t
     const int kb = (int)(idx / ((int64_t)Mpad * 8));
     uint4 o = make_uint4(0, 0, 0, 0);
     if (r < M) {
-      const __nv_bfloat16* src = x + (size_t)r * x_stride + (size_t)kb * kBlockK + c * 8;
+      // read past L1: this grid is resident while its predecessor, which may have written x, still runs
+      const unsigned short* src =
+          reinterpret_cast<const unsigned short*>(x + (size_t)r * x_stride + (size_t)kb * kBlockK + c * 8);
       __half h[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float f = fminf(fmaxf(__bfloat162float(src[i]), -65504.f), 65504.f);
+        const float f = fminf(fmaxf(__uint_as_float((uint32_t)__ldcg(src + i) << 16), -65504.f), 65504.f);
         h[i] = __float2half_rn(f);
       }
       o = *reinterpret_cast<uint4*>(h);

@@ -2,7 +2,7 @@
 
 Usage (only where a read-only checkout of NYCU-EDgeAi/subspec is available):
 
-    python tests/golden/make_golden.py --reference /path/to/subspec [--only verify|sampled|expand|expand_chain|kv|kv_hf|lossy_unit]
+    python tests/golden/make_golden.py --reference /path/to/subspec [--only verify|sampled|expand|expand_chain|kv|kv_hf|post|lossy_unit]
 
 The reference is imported, never copied.  Two third-party modules it imports but
 does not need on this path (`nvtx`, `prettytable`) are replaced by throw-away
@@ -17,6 +17,7 @@ depend on the RNG stream.  Outputs written:
     expand_chain.json                      ten-level expansions at the benchmark's vocabulary, pruned to 64 nodes
     kv_cases.json                          KvCachePool.reorder_cache_with_offset checksums
     kv_hf_cases.json                       TreeStaticCache / TreeDynamicCache.reorder_cache_with_offset checksums
+    post_cases.json                        Tree.prune_to_depth / Tree.find_child_index results
 """
 from __future__ import annotations
 
@@ -582,6 +583,58 @@ def gen_kv_hf(ref, out_dir: Path):
     print(f"kv hf: {len(cases)} cases")
 
 
+def gen_post(ref, out_dir: Path):
+    """Tree.prune_to_depth and Tree.find_child_index of the reference on seeded trees: level-ordered ones, as
+    Tree.add_nodes builds them, and the same trees after prune_to_top_n, whose nodes are numbered by rank and
+    whose children lists are no longer in ascending order."""
+    ct = ref["ct"]
+    cases = []
+    for seed in range(900, 912):
+        gen = torch.Generator().manual_seed(seed)
+        n = 20 + 7 * (seed % 5)
+        st = synthetic.random_tree(n, 7, 4, 50, gen)   # a small vocabulary: siblings' tokens are probed by value
+        probs = torch.rand(n, generator=gen).tolist()
+        probs[0] = 1.0
+        for i in range(1, n):  # cumulative probabilities fall along a path, as in a real draft tree
+            probs[i] = probs[int(st.parents[i])] * (0.3 + 0.7 * probs[i])
+
+        def build():
+            t = ct.Tree(st.token_ids[0], torch.float32)
+            for i in range(1, n):
+                p = int(st.parents[i])
+                t.nodes.append(ct.TreeNode(parent=p, token_id=int(st.token_ids[i]), cumulative_probability=probs[i],
+                                           depth=int(st.depths[i])))
+                t.nodes[p].children.append(i)
+            t.current_size = n
+            return t
+
+        for ranked in (False, True):
+            base = build()
+            if ranked:
+                base.prune_to_top_n(max(4, (2 * n) // 3))
+            tree0 = dict(token_ids=[int(x.token_id) for x in base.nodes],
+                         parents=[-1 if x.parent is None else int(x.parent) for x in base.nodes],
+                         depths=[int(x.depth) for x in base.nodes], children=[list(x.children) for x in base.nodes])
+            finds = []
+            for node in range(0, len(base.nodes), 3):
+                for tok in {int(base.nodes[c].token_id) for c in base.nodes[node].children} | {49, 0}:
+                    finds.append([node, tok, int(base.find_child_index(node, tok))])
+            prunes = []
+            for d in range(0, int(base.get_depth()) + 2):
+                t = build()
+                if ranked:
+                    t.prune_to_top_n(max(4, (2 * n) // 3))
+                keep = t.prune_to_depth(d).tolist()
+                prunes.append(dict(max_depth=d, keep=keep, token_ids=[int(x.token_id) for x in t.nodes],
+                                   parents=[-1 if x.parent is None else int(x.parent) for x in t.nodes],
+                                   depths=[int(x.depth) for x in t.nodes], children=[list(x.children) for x in t.nodes],
+                                   leaves=list(t.available_leaves)))
+            cases.append(dict(seed=seed, ranked=ranked, tree=tree0, finds=finds, prunes=prunes))
+    (out_dir / "post_cases.json").write_text(json.dumps({"cases": cases}))
+    print(f"post: {len(cases)} trees, {sum(len(c['prunes']) for c in cases)} prunes, "
+          f"{sum(len(c['finds']) for c in cases)} child look-ups")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the unmodified reference repository")
@@ -599,6 +652,8 @@ def main():
         gen_kv(ref, HERE)
     if args.only in (None, "kv_hf"):
         gen_kv_hf(ref, HERE)
+    if args.only in (None, "post"):
+        gen_post(ref, HERE)
     if args.only in (None, "sampled"):
         gen_sampled(ref, HERE)
     if args.only in (None, "lossy_unit"):

@@ -64,6 +64,12 @@ def kv_pool(case) -> torch.Tensor:
 
 
 @lru_cache(maxsize=None)
+def post_cases():
+    """Tree.prune_to_depth / Tree.find_child_index results of the reference on seeded trees."""
+    return json.loads((GOLDEN / "post_cases.json").read_text())["cases"]
+
+
+@lru_cache(maxsize=None)
 def kv_hf_cases():
     return json.loads((GOLDEN / "kv_hf_cases.json").read_text())["cases"]
 

@@ -160,3 +160,23 @@ def test_oracle_matches_reference_sampled_verification():
         assert got == c["expected"], c["name"]
         accepted += r.accept_len
     assert accepted > 50  # the walks go somewhere
+
+
+def test_post_verify_oracle_matches_reference_tree_methods():
+    """find_child_index and prune_to_depth against the reference's Tree on seeded trees, level-ordered and
+    rank-numbered (children lists out of ascending order)."""
+    from oracle import postverify_oracle as po
+
+    cases = golden_io.post_cases()
+    assert len(cases) == 24 and any(c["ranked"] for c in cases)
+    for c in cases:
+        t = c["tree"]
+        for node, tok, want in c["finds"]:
+            assert po.find_child_index(t["token_ids"], t["children"], node, tok) == want
+        for pr in c["prunes"]:
+            keep, tok, par, dep, ch = po.prune_to_depth(t["token_ids"], t["parents"], t["depths"], t["children"],
+                                                        pr["max_depth"])
+            assert keep == pr["keep"] and tok == pr["token_ids"] and par == pr["parents"] and dep == pr["depths"]
+            assert ch == pr["children"]
+            if len(keep) < len(t["token_ids"]):  # an early return leaves the reference's leaf list as it was
+                assert [i for i in range(len(keep)) if not ch[i]] == pr["leaves"]
