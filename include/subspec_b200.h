@@ -554,6 +554,62 @@ typedef struct subspec_tree_prune_depth_args {
 SUBSPEC_API int subspec_tree_prune_depth(const subspec_tree_prune_depth_args* args, subspec_stream_t stream);
 
 /* ------------------------------------------------------------------------
+ * Page bookkeeping of the paged KV cache, for a batch of requests, on the
+ * device: one call per step of a generation loop, no host round trip.
+ *
+ * Replaces (specdecodes/models/utils/flashinfer/cache_manager.py):
+ *   - KvCachePool.allocate / deallocate and the free-page mask      :66-80
+ *   - RequestKvCache.increment / decrement / crop and the bookkeeping
+ *     at the end of reorder_cache_with_offset                       :237-346
+ *   - getKvCacheBatchPosition                                       :350-414
+ *
+ * State (device arrays the caller owns): free_mask, one bit per physical
+ * page, set = free; page_table [batch, pages_per_seq], the first n_pages[b]
+ * entries of a row being request b's pages in order; kv_len, kv_last_page_len.
+ * The call sets kv_len[b] = (set_len ? set_len[b] : kv_len[b]) + add_len[b] +
+ * add_all, returns the pages a request no longer needs (cut from the end of
+ * its list), gives requests that need more the lowest free pages (requests in
+ * batch order), and refreshes kv_last_page_len.  Asking for more pages than
+ * are free, or than a row of page_table holds, sets SUBSPEC_DEV_BAD_PAGE.
+ *
+ * Optional outputs (kv_page_indptr == NULL skips them all): the flattened
+ * page table the attention plan takes -- kv_page_indptr [batch + 1],
+ * kv_page_indices [sum of n_pages], seq_indptr [batch + 1] (tokens appended per
+ * request: kv_len in PREFILL mode, 1 in DECODE, tree_tokens in TREE) -- and, for
+ * the append of those tokens, batch_indices / positions [max_append] (token t
+ * of request b sits at kv_len[b] - appended + t).
+ * ---------------------------------------------------------------------- */
+#define SUBSPEC_PAGES_PREFILL 0
+#define SUBSPEC_PAGES_DECODE 1
+#define SUBSPEC_PAGES_TREE 2
+typedef struct subspec_pages_args {
+  uint32_t struct_size;
+  int32_t batch;
+  int32_t num_pages;
+  int32_t page_len;
+  int32_t pages_per_seq;
+  uint32_t* free_mask;       /* [(num_pages + 31) / 32] */
+  int32_t* page_table;       /* [batch, pages_per_seq] */
+  int32_t* n_pages;          /* [batch] */
+  int32_t* kv_len;           /* [batch] */
+  int32_t* kv_last_page_len; /* [batch] */
+  const int32_t* set_len;    /* [batch] or NULL */
+  const int32_t* add_len;    /* [batch] or NULL */
+  int32_t add_all;
+  int32_t mode;        /* SUBSPEC_PAGES_* */
+  int32_t tree_tokens; /* TREE mode */
+  int32_t max_append;  /* entries of batch_indices / positions */
+  int32_t* seq_indptr;
+  int32_t* kv_page_indptr;
+  int32_t* kv_page_indices;
+  int32_t* batch_indices;
+  int32_t* positions;
+  uint32_t* dev_status;
+} subspec_pages_args;
+
+SUBSPEC_API int subspec_pages_update(const subspec_pages_args* args, subspec_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * W4A16 group-wise dequant GEMM (the HQQ 4-bit draft linear).
  *
  *   y[m, n] = sum_k x[m, k] * (q[n, k] - zero[n, k / 64]) * scale[n, k / 64]

@@ -145,6 +145,21 @@ class TreePruneDepthArgs(C.Structure):
     ]
 
 
+PAGES_PREFILL, PAGES_DECODE, PAGES_TREE = 0, 1, 2
+
+
+class PagesArgs(C.Structure):
+    """Mirror of `subspec_pages_args`."""
+
+    _fields_ = [
+        ("struct_size", _u32), ("batch", _i32), ("num_pages", _i32), ("page_len", _i32), ("pages_per_seq", _i32),
+        ("free_mask", _vp), ("page_table", _vp), ("n_pages", _vp), ("kv_len", _vp), ("kv_last_page_len", _vp),
+        ("set_len", _vp), ("add_len", _vp), ("add_all", _i32), ("mode", _i32), ("tree_tokens", _i32),
+        ("max_append", _i32), ("seq_indptr", _vp), ("kv_page_indptr", _vp), ("kv_page_indices", _vp),
+        ("batch_indices", _vp), ("positions", _vp), ("dev_status", _vp),
+    ]
+
+
 W4A16_MAX_GROUP = 4
 
 
@@ -171,6 +186,7 @@ SYMBOLS = {
     "subspec_expand_step": (C.c_int, [C.POINTER(ExpandArgs), _vp]),
     "subspec_tree_finalize": (C.c_int, [C.POINTER(TreeFinalizeArgs), _vp]),
     "subspec_post_verify": (C.c_int, [C.POINTER(PostVerifyArgs), _vp]),
+    "subspec_pages_update": (C.c_int, [C.POINTER(PagesArgs), _vp]),
     "subspec_tree_prune_depth": (C.c_int, [C.POINTER(TreePruneDepthArgs), _vp]),
     "subspec_w4a16_packed_bytes": (C.c_int, [_i32, _i32, C.POINTER(C.c_size_t)]),
     "subspec_w4a16_pack": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),

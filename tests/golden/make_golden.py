@@ -2,7 +2,7 @@
 
 Usage (only where a read-only checkout of NYCU-EDgeAi/subspec is available):
 
-    python tests/golden/make_golden.py --reference /path/to/subspec [--only verify|sampled|expand|expand_chain|kv|kv_hf|post|lossy_unit]
+    python tests/golden/make_golden.py --reference /path/to/subspec [--only verify|sampled|expand|expand_chain|kv|kv_hf|post|pages|lossy_unit]
 
 The reference is imported, never copied.  Two third-party modules it imports but
 does not need on this path (`nvtx`, `prettytable`) are replaced by throw-away
@@ -18,6 +18,7 @@ depend on the RNG stream.  Outputs written:
     kv_cases.json                          KvCachePool.reorder_cache_with_offset checksums
     kv_hf_cases.json                       TreeStaticCache / TreeDynamicCache.reorder_cache_with_offset checksums
     post_cases.json                        Tree.prune_to_depth / Tree.find_child_index results
+    pages_cases.json                       KvCachePool / RequestKvCache page lists over scripted generation loops
 """
 from __future__ import annotations
 
@@ -635,6 +636,41 @@ def gen_post(ref, out_dir: Path):
           f"{sum(len(c['finds']) for c in cases)} child look-ups")
 
 
+def gen_pages(ref, out_dir: Path):
+    """A scripted generation loop over the reference's KvCachePool / RequestKvCache (CPU, a pool of one float per
+    row: only the bookkeeping matters): several requests share one pool; every step each request is cropped to
+    the length a verification left it with (all requests first), then grows by the next tree (requests in
+    order).  Page lists, lengths and the free count after every step are stored."""
+    cm = ref["cm"]
+    scripts = []
+    for seed, (B, num_pages, page_len, tree_n, steps) in enumerate([(3, 40, 4, 7, 6), (8, 200, 16, 24, 8),
+                                                                    (1, 30, 16, 64, 5), (16, 600, 16, 64, 6)]):
+        gen = torch.Generator().manual_seed(600 + seed)
+        pool = cm.KvCachePool(num_pages, 1, 1, 1, page_len, torch.float32, "cpu")
+        init = [int(torch.randint(1, 3 * page_len, (1,), generator=gen)) for _ in range(B)]
+        reqs = [cm.RequestKvCache(pool, page_len, n) for n in init]
+        rec = []
+
+        def snap():
+            return dict(pages=[list(r.kv_page_indices) for r in reqs], kv_len=[r.kv_len for r in reqs],
+                        last=[r.kv_last_page_len for r in reqs], free=int(pool.num_free_pages()))
+
+        first = snap()
+        for _ in range(steps):
+            for r in reqs:
+                r.increment(tree_n)
+            grown = snap()
+            kept = [int(torch.randint(1, tree_n + 1, (1,), generator=gen)) for _ in range(B)]
+            new_len = [r.kv_len - tree_n + k for r, k in zip(reqs, kept)]
+            for r, n in zip(reqs, new_len):
+                r.crop(n)
+            rec.append(dict(grown=grown, new_len=new_len, cropped=snap()))
+        scripts.append(dict(batch=B, num_pages=num_pages, page_len=page_len, tree_n=tree_n, init=init, first=first,
+                            steps=rec))
+    (out_dir / "pages_cases.json").write_text(json.dumps({"scripts": scripts}))
+    print(f"pages: {len(scripts)} scripted loops, {sum(len(s_['steps']) for s_ in scripts)} steps")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the unmodified reference repository")
@@ -654,6 +690,8 @@ def main():
         gen_kv_hf(ref, HERE)
     if args.only in (None, "post"):
         gen_post(ref, HERE)
+    if args.only in (None, "pages"):
+        gen_pages(ref, HERE)
     if args.only in (None, "sampled"):
         gen_sampled(ref, HERE)
     if args.only in (None, "lossy_unit"):

@@ -70,6 +70,12 @@ def post_cases():
 
 
 @lru_cache(maxsize=None)
+def pages_scripts():
+    """Page lists the reference's KvCachePool / RequestKvCache went through in scripted generation loops."""
+    return json.loads((GOLDEN / "pages_cases.json").read_text())["scripts"]
+
+
+@lru_cache(maxsize=None)
 def kv_hf_cases():
     return json.loads((GOLDEN / "kv_hf_cases.json").read_text())["cases"]
 
