@@ -84,3 +84,62 @@ class SpeculativeStepBatch:
             self.status.zero_()
             raise ValueError("KV compaction rejected its input: " + _lib.dev_status_text(word))
         return out
+
+
+class SpeculativeLoopBatch(SpeculativeStepBatch):
+    """The loop body of the reference's generators for a batch of requests, with nothing read back between steps.
+
+    Per step (generators/subspec_sd_v2.py:170-262, classic_sd.py:225-257, with the paged cache of
+    subspec_sd_fi.py): verify the trees, look the bonus token up among the last context's children (re-rooting),
+    gather the hidden indices, reorder the KV rows of the requests whose bonus token missed the tree (with all
+    the indices gathered since their last reorder), cut their page lists back to the rows kept and grow every
+    request by the next tree -- five launches on the current stream.  The reference runs one request, on the
+    host, with a device synchronisation at each of those points (`assert batch_size == 1`, classic_sd.py:169).
+    """
+
+    def __init__(self, batch: int, max_nodes: int, device, *, kv_layers: int, kv_heads: int = 4, head_dim: int = 128,
+                 page_len: int = 16, pages_per_seq: int, num_pages: Optional[int] = None,
+                 kv_dtype: torch.dtype = torch.bfloat16, init_len=1):
+        from .pages import DevicePagePool
+        from .postverify import PostVerifyState
+
+        super().__init__(batch, max_nodes, device)
+        num_pages = int(num_pages or batch * pages_per_seq)
+        self.pool = torch.empty(kv_layers, num_pages, 2, page_len, kv_heads, head_dim, dtype=kv_dtype,
+                                device=self.device)
+        self.pages = DevicePagePool(batch, num_pages, page_len, pages_per_seq, self.device,
+                                    max_append=batch * max_nodes)
+        self.page_table = self.pages.page_table  # the compaction kernel reads the live table
+        init = torch.as_tensor(init_len, dtype=torch.int32).expand(batch).contiguous()
+        self.pages.update(set_len=init, mode="prefill")
+        self.state = PostVerifyState(batch, 4 * (max_nodes + 1), self.device, kv_len=init)
+        self.tree_tokens = 0
+
+    def begin_step(self, tree_tokens: int):
+        """Room for the next tree in every request's cache (RequestKvCache.increment); returns the page-table
+        tensors of the tree-decoding forward (getKvCacheBatchPosition(mode='tree'))."""
+        self.tree_tokens = int(tree_tokens)
+        return self.pages.update(add_all=self.tree_tokens, mode="tree", tree_tokens=self.tree_tokens)
+
+    def end_step(self, logits: torch.Tensor, *, verify_method: str = "exact", verify_kwargs: Optional[dict] = None,
+                 eos_token_id: Optional[int] = None) -> None:
+        """verify -> re-root / gather -> delayed KV reorder -> page lists cut back.  No synchronisation."""
+        from .postverify import post_verify
+
+        st = self.state
+        # rows of earlier trees that are still waiting for their reorder sit in front of this tree's rows: the
+        # indices that leave this step count from the first of them
+        st.skip_nodes.copy_(self.pages.kv_len - self.tree_tokens - st.kv_len)
+        self.verify(logits, verify_method=verify_method, verify_kwargs=verify_kwargs, eos_token_id=eos_token_id)
+        post_verify(self.ws, self.state)
+        kv_cache.compact_paged(self.pool, page_table=self.page_table, offset=st.reorder_offset, n=st.reorder_n,
+                               beam=st.beam_cache, status=self.status)
+        # rows kept so far plus, for a request whose reorder is put off, the whole tree it still reads from
+        keep = st.kv_len + torch.where(st.reorder_n > 0, 0, self.pages.kv_len - st.kv_len).to(torch.int32)
+        self.pages.update(set_len=keep, mode="decode")
+
+    def check(self) -> None:
+        """Synchronise and raise if any kernel of the loop reported a problem."""
+        self.results()
+        self.state.check_status()
+        self.pages.check_status()

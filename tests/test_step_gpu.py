@@ -110,3 +110,57 @@ def test_step_from_a_cuda_graph(cuda_lib):
         exact, lossy, pool_want = _expected(trees, logits, pool_cpu, table)
         _check(out, exact, lossy)
         assert torch.equal(sb.pool.cpu(), pool_want)
+
+
+def test_loop_runs_without_host_round_trips(cuda_lib):
+    """SpeculativeLoopBatch: five steps of grow -> verify -> re-root -> delayed reorder -> trim for four
+    requests, launched back to back; only the test looks at the device state in between.  Against the oracle's
+    verification, the delayed-reorder bookkeeping and the reference's pool reorder."""
+    from oracle import postverify_oracle as po
+    from subspec_b200.step import SpeculativeLoopBatch
+
+    Bn, n, rows, vocab = 4, 16, 9, 997   # the trees reach past the decoded rows, as after a post-speculation
+    gen = torch.Generator().manual_seed(44)
+    init = [5, 17, 32, 9]
+    loop = SpeculativeLoopBatch(Bn, n, "cuda", kv_layers=2, kv_heads=2, head_dim=64, page_len=16, pages_per_seq=12,
+                                init_len=torch.tensor(init))
+    loop.pool.copy_(torch.randn(loop.pool.shape, generator=gen).to(torch.bfloat16))
+    want_pool = loop.pool.cpu().clone()
+    oracle = [po.DelayedReorder(x) for x in init]
+    pending = [0] * Bn   # rows of earlier trees still waiting for their reorder
+    deferred = 0
+    for step in range(5):
+        sts = [synthetic.random_tree(n, 5, 3, vocab, gen) for _ in range(Bn)]
+        logits = torch.stack([synthetic.verify_logits(s, vocab, gen, dtype=torch.bfloat16, peaked=True, boost_frac=0.9)
+                              for s in sts])
+        flats = []
+        for s in sts:
+            tok, off, idx = flatten_tree(Tree.from_arrays(s.token_ids.tolist(), s.parents.tolist()), 0)
+            flats.append((tok, off, idx, rows, 0))
+        pos = loop.begin_step(rows)
+        assert pos.seq_indptr.tolist() == [b * rows for b in range(Bn + 1)]
+        assert loop.pages.kv_len.tolist() == [oracle[b].kv_len + pending[b] + rows for b in range(Bn)]
+        table = loop.pages.page_table.cpu()
+        loop.set_trees(flats)
+        if step == 4:
+            loop.state.finished.fill_(1)
+        loop.end_step(logits[:, :rows].contiguous().cuda())
+        loop.check()
+        for b, s in enumerate(sts):
+            target = vo.target_probs(logits[b, :rows], upcast=True).argmax(-1).tolist()
+            r = vo.exact_walk(target=target + [-1] * (n - rows), token_ids=s.token_ids.tolist(),
+                              children=s.children(), root=0, n_rows=rows, eos=None)
+            root = po.find_child_index(s.token_ids.tolist(), s.children(), r.hidden[-1], r.tokens[-1])
+            assert int(loop.state.next_root[b]) == (root + pending[b] if root >= 0 else -1)
+            beam, at = oracle[b].step([h + pending[b] for h in r.hidden], root, finished=step == 4)
+            if beam is None:
+                deferred += 1
+                pending[b] += rows
+            else:
+                ko.paged_reorder(want_pool, torch.tensor(beam), at, page_table=table[b].tolist())
+                pending[b] = 0
+            assert int(loop.state.kv_len[b]) == oracle[b].kv_len
+            assert int(loop.pages.kv_len[b]) == oracle[b].kv_len + pending[b]
+            assert int(loop.pages.n_pages[b]) == -(-(oracle[b].kv_len + pending[b]) // 16)
+        assert torch.equal(loop.pool.cpu(), want_pool), step
+    assert deferred >= 1 and pending == [0] * Bn
