@@ -610,6 +610,84 @@ typedef struct subspec_pages_args {
 SUBSPEC_API int subspec_pages_update(const subspec_pages_args* args, subspec_stream_t stream);
 
 /* ------------------------------------------------------------------------
+ * Tree attention over the paged KV cache (one layer), and the append of the
+ * tree's own K / V rows that precedes it.
+ *
+ * Replaces the FlashInfer calls of the reference's paged generators:
+ *   - append_paged_kv_cache
+ *       specdecodes/models/utils/flashinfer/attention_wrapper.py:234-253
+ *   - BatchPrefillWithPagedKVCacheWrapper.plan(custom_mask=...) / run
+ *       attention_wrapper.py:104-151, 288-316;
+ *       specdecodes/models/utils/flashinfer/attention.py:26-102
+ *
+ * The pool is KvCachePool.cache_data, [layers, num_pages, 2, page_len,
+ * num_kv_heads, head_dim] bf16; request b's rows live in the pages
+ * page_table[b][0 .. ], kv_len[b] of them INCLUDING the n_q[b] rows of the tree
+ * (append first).  Query token i of request b is cache row kv_len[b] - n_q[b] + i.
+ * It sees every row below prefix_len[b] (NULL: kv_len[b] - n_q[b]) and, of the
+ * rows from there on, those whose byte in mask[b][i][row] is non-zero: the
+ * [rows, prefix + tree columns] matrix subspec_tree_finalize writes (and
+ * FlashInfer's custom_mask).  q / out are [batch, q_len, num_q_heads, head_dim]
+ * bf16 with element strides; query head h reads KV head h / (num_q_heads /
+ * num_kv_heads).  Softmax in fp32, scores scaled by sm_scale; outputs within
+ * bf16 rounding of an fp32 evaluation.  head_dim = 128 only.
+ * ---------------------------------------------------------------------- */
+typedef struct subspec_tree_attn_args {
+  uint32_t struct_size;
+  int32_t batch;
+  int32_t q_len; /* tree tokens per request the buffers are laid out for */
+  int32_t num_q_heads;
+  int32_t num_kv_heads;
+  int32_t head_dim;
+  int32_t layer;
+  int32_t layers;
+  int32_t num_pages;
+  int32_t page_len;
+  int32_t pages_per_seq;
+  const void* pool;
+  const int32_t* page_table; /* [batch, pages_per_seq] */
+  const int32_t* kv_len;     /* [batch] */
+  const int32_t* n_q;        /* [batch] or NULL (= q_len) */
+  const int32_t* prefix_len; /* [batch] or NULL */
+  const uint8_t* mask;       /* [batch, q_len, >= kv_len] bytes */
+  int64_t mask_batch_stride;
+  int64_t mask_row_stride;
+  const void* q;
+  int64_t q_batch_stride, q_token_stride, q_head_stride; /* elements */
+  void* out;
+  int64_t o_batch_stride, o_token_stride, o_head_stride;
+  double sm_scale;
+  uint32_t* dev_status;
+} subspec_tree_attn_args;
+
+SUBSPEC_API int subspec_tree_attention_paged(const subspec_tree_attn_args* args, subspec_stream_t stream);
+
+/* k / v are [batch, q_len, num_kv_heads, head_dim] (16-bit elements; element strides batch_stride /
+ * token_stride, heads and dims contiguous); token i < n_q[b] goes to cache row kv_len[b] - n_q[b] + i. */
+typedef struct subspec_kv_append_args {
+  uint32_t struct_size;
+  int32_t batch;
+  int32_t q_len;
+  int32_t num_kv_heads;
+  int32_t head_dim;
+  int32_t layer;
+  int32_t layers;
+  int32_t num_pages;
+  int32_t page_len;
+  int32_t pages_per_seq;
+  void* pool;
+  const int32_t* page_table;
+  const int32_t* kv_len;
+  const int32_t* n_q; /* or NULL */
+  const void* k;
+  const void* v;
+  int64_t batch_stride, token_stride;
+  uint32_t* dev_status;
+} subspec_kv_append_args;
+
+SUBSPEC_API int subspec_kv_append_paged(const subspec_kv_append_args* args, subspec_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * W4A16 group-wise dequant GEMM (the HQQ 4-bit draft linear).
  *
  *   y[m, n] = sum_k x[m, k] * (q[n, k] - zero[n, k / 64]) * scale[n, k / 64]

@@ -160,6 +160,31 @@ class PagesArgs(C.Structure):
     ]
 
 
+class TreeAttnArgs(C.Structure):
+    """Mirror of `subspec_tree_attn_args`."""
+
+    _fields_ = [
+        ("struct_size", _u32), ("batch", _i32), ("q_len", _i32), ("num_q_heads", _i32), ("num_kv_heads", _i32),
+        ("head_dim", _i32), ("layer", _i32), ("layers", _i32), ("num_pages", _i32), ("page_len", _i32),
+        ("pages_per_seq", _i32), ("pool", _vp), ("page_table", _vp), ("kv_len", _vp), ("n_q", _vp),
+        ("prefix_len", _vp), ("mask", _vp), ("mask_batch_stride", _i64), ("mask_row_stride", _i64), ("q", _vp),
+        ("q_batch_stride", _i64), ("q_token_stride", _i64), ("q_head_stride", _i64), ("out", _vp),
+        ("o_batch_stride", _i64), ("o_token_stride", _i64), ("o_head_stride", _i64), ("sm_scale", _f64),
+        ("dev_status", _vp),
+    ]
+
+
+class KvAppendArgs(C.Structure):
+    """Mirror of `subspec_kv_append_args`."""
+
+    _fields_ = [
+        ("struct_size", _u32), ("batch", _i32), ("q_len", _i32), ("num_kv_heads", _i32), ("head_dim", _i32),
+        ("layer", _i32), ("layers", _i32), ("num_pages", _i32), ("page_len", _i32), ("pages_per_seq", _i32),
+        ("pool", _vp), ("page_table", _vp), ("kv_len", _vp), ("n_q", _vp), ("k", _vp), ("v", _vp),
+        ("batch_stride", _i64), ("token_stride", _i64), ("dev_status", _vp),
+    ]
+
+
 W4A16_MAX_GROUP = 4
 
 
@@ -187,6 +212,8 @@ SYMBOLS = {
     "subspec_tree_finalize": (C.c_int, [C.POINTER(TreeFinalizeArgs), _vp]),
     "subspec_post_verify": (C.c_int, [C.POINTER(PostVerifyArgs), _vp]),
     "subspec_pages_update": (C.c_int, [C.POINTER(PagesArgs), _vp]),
+    "subspec_tree_attention_paged": (C.c_int, [C.POINTER(TreeAttnArgs), _vp]),
+    "subspec_kv_append_paged": (C.c_int, [C.POINTER(KvAppendArgs), _vp]),
     "subspec_tree_prune_depth": (C.c_int, [C.POINTER(TreePruneDepthArgs), _vp]),
     "subspec_w4a16_packed_bytes": (C.c_int, [_i32, _i32, C.POINTER(C.c_size_t)]),
     "subspec_w4a16_pack": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),

@@ -1,0 +1,99 @@
+"""Tree attention over the paged KV cache: the FlashInfer calls of the reference's paged generators.
+
+Reference (specdecodes/models/utils/flashinfer/attention_wrapper.py:104-151, 234-253, 288-316 and
+attention.py:26-102): per layer, `append_paged_kv_cache` writes the tree tokens' K / V rows into the request's
+pages and `BatchPrefillWithPagedKVCacheWrapper.run` evaluates the tree tokens' queries over the request's cache
+under a custom mask.  Here both are kernels of the C-ABI library (`subspec_kv_append_paged`,
+`subspec_tree_attention_paged`) that take the pool, the page table and the mask as the other kernels of this
+package leave them: `KvCachePool.cache_data`, `DevicePagePool.page_table` / `kv_len`, and the
+[rows, prefix + tree columns] mask `DraftTreeBatch.finalize` writes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+
+def _i32(t: Optional[torch.Tensor], dev, n: int, what: str) -> int:
+    if t is None:
+        return 0
+    if t.dtype != torch.int32 or t.device != dev or t.numel() != n or not t.is_contiguous():
+        raise ValueError(f"{what} must be a contiguous int32 [{n}] tensor on the pool's device")
+    return t.data_ptr()
+
+
+@torch.no_grad()
+def append_paged_kv(pool: torch.Tensor, layer: int, k: torch.Tensor, v: torch.Tensor, *, page_table: torch.Tensor,
+                    kv_len: torch.Tensor, n_q: Optional[torch.Tensor] = None,
+                    status: Optional[torch.Tensor] = None) -> None:
+    """k, v [batch, q_len, kv_heads, head_dim] -> cache rows kv_len[b] - n_q[b] + i of layer `layer`.
+
+    `kv_len` counts the rows AFTER the append (grow the requests first, as `RequestKvCache.increment` does)."""
+    L, P, _, page_len, H, D = pool.shape
+    B, QL = int(k.shape[0]), int(k.shape[1])
+    if k.shape != v.shape or tuple(k.shape[2:]) != (H, D) or k.dtype != pool.dtype or k.stride() != v.stride():
+        raise ValueError("k and v must be [batch, q_len, kv_heads, head_dim] tensors of the pool's dtype and one layout")
+    if k.stride(3) != 1 or k.stride(2) != D:
+        k, v = k.contiguous(), v.contiguous()
+    a = _lib.KvAppendArgs()
+    a.struct_size = C.sizeof(_lib.KvAppendArgs)
+    a.batch, a.q_len, a.num_kv_heads, a.head_dim = B, QL, int(H), int(D)
+    a.layer, a.layers, a.num_pages, a.page_len = int(layer), int(L), int(P), int(page_len)
+    a.pages_per_seq = int(page_table.shape[1])
+    a.pool, a.page_table = pool.data_ptr(), page_table.data_ptr()
+    a.kv_len = _i32(kv_len, pool.device, B, "kv_len")
+    a.n_q = _i32(n_q, pool.device, B, "n_q")
+    a.k, a.v = k.data_ptr(), v.data_ptr()
+    a.batch_stride, a.token_stride = int(k.stride(0)), int(k.stride(1))
+    a.dev_status = 0 if status is None else status.data_ptr()
+    stream = torch.cuda.current_stream(pool.device).cuda_stream
+    _lib.check(_lib.lib().subspec_kv_append_paged(C.byref(a), C.c_void_p(stream)), "subspec_kv_append_paged")
+
+
+@torch.no_grad()
+def tree_attention_paged(q: torch.Tensor, pool: torch.Tensor, layer: int, *, page_table: torch.Tensor,
+                         kv_len: torch.Tensor, mask: torch.Tensor, n_q: Optional[torch.Tensor] = None,
+                         prefix_len: Optional[torch.Tensor] = None, sm_scale: Optional[float] = None,
+                         status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [batch, q_len, q_heads, 128] bf16 -> attention output of the same shape.
+
+    `mask` is bool / uint8 [batch, q_len, cols >= kv_len] (a leading singleton head axis is accepted): row i of
+    request b marks the cache rows its query i may read; rows below `prefix_len[b]` (default kv_len - n_q) are
+    read without looking at the mask."""
+    if q.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16 or q.dim() != 4:
+        raise ValueError("q must be bf16 [batch, q_len, q_heads, head_dim] and the pool bf16")
+    L, P, _, page_len, H, D = pool.shape
+    B, QL, HQ, Dq = (int(x) for x in q.shape)
+    if Dq != D or q.stride(3) != 1:
+        raise ValueError("q's head_dim must equal the pool's and be contiguous")
+    if mask.dim() == 4 and mask.shape[1] == 1:
+        mask = mask[:, 0]
+    if mask.dim() != 3 or mask.shape[0] != B or mask.shape[1] < QL or mask.stride(2) != 1 or \
+            mask.dtype not in (torch.bool, torch.uint8):
+        raise ValueError("mask must be bool / uint8 [batch, q_len, cols] with contiguous columns")
+    if page_table.dtype != torch.int32 or page_table.dim() != 2 or not page_table.is_contiguous():
+        raise ValueError("page_table must be a contiguous int32 [batch, pages_per_seq] tensor")
+    out = torch.empty_like(q)
+    a = _lib.TreeAttnArgs()
+    a.struct_size = C.sizeof(_lib.TreeAttnArgs)
+    a.batch, a.q_len, a.num_q_heads, a.num_kv_heads, a.head_dim = B, QL, HQ, int(H), int(D)
+    a.layer, a.layers, a.num_pages, a.page_len = int(layer), int(L), int(P), int(page_len)
+    a.pages_per_seq = int(page_table.shape[1])
+    a.pool, a.page_table = pool.data_ptr(), page_table.data_ptr()
+    a.kv_len = _i32(kv_len, pool.device, B, "kv_len")
+    a.n_q = _i32(n_q, pool.device, B, "n_q")
+    a.prefix_len = _i32(prefix_len, pool.device, B, "prefix_len")
+    a.mask, a.mask_batch_stride, a.mask_row_stride = mask.data_ptr(), int(mask.stride(0)), int(mask.stride(1))
+    a.q, a.q_batch_stride, a.q_token_stride, a.q_head_stride = q.data_ptr(), *(int(q.stride(i)) for i in range(3))
+    a.out, a.o_batch_stride, a.o_token_stride, a.o_head_stride = out.data_ptr(), *(int(out.stride(i)) for i in range(3))
+    a.sm_scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D)
+    a.dev_status = 0 if status is None else status.data_ptr()
+    stream = torch.cuda.current_stream(pool.device).cuda_stream
+    _lib.check(_lib.lib().subspec_tree_attention_paged(C.byref(a), C.c_void_p(stream)),
+               "subspec_tree_attention_paged")
+    return out

@@ -67,6 +67,7 @@ def test_header_is_plain_c_and_matches_the_ctypes_mirror(tmp_path):
                "subspec_tree_finalize_args": _lib.TreeFinalizeArgs, "subspec_w4a16_args": _lib.W4A16Args,
                "subspec_w4a16_group_args": _lib.W4A16GroupArgs,
                "subspec_post_verify_args": _lib.PostVerifyArgs, "subspec_pages_args": _lib.PagesArgs,
+               "subspec_tree_attn_args": _lib.TreeAttnArgs, "subspec_kv_append_args": _lib.KvAppendArgs,
                "subspec_tree_prune_depth_args": _lib.TreePruneDepthArgs}
     lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "subspec_b200.h"', 'int main(void) {']
     for cname, mirror in structs.items():

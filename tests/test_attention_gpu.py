@@ -1,0 +1,97 @@
+"""Tree attention over the paged cache and the K / V append, against the full-precision restatement."""
+import pytest
+import torch
+
+from oracle import attention_oracle as ao
+from subspec_b200 import synthetic
+from subspec_b200.attention import append_paged_kv, tree_attention_paged
+from subspec_b200.tree import Tree
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(seed, B, QL, HQ, HKV, prefix_lens, n_qs, page_len=16, layers=2, layer=1):
+    D = 128
+    gen = torch.Generator().manual_seed(seed)
+    pages_per_seq = max((p + QL + page_len - 1) // page_len for p in prefix_lens) + 1
+    P = B * pages_per_seq
+    table = synthetic.random_page_table(B, pages_per_seq, gen)
+    pool = torch.randn(layers, P, 2, page_len, HKV, D, generator=gen).to(torch.bfloat16)
+    q = torch.randn(B, QL, HQ, D, generator=gen).to(torch.bfloat16)
+    k = torch.randn(B, QL, HKV, D, generator=gen).to(torch.bfloat16)
+    v = torch.randn(B, QL, HKV, D, generator=gen).to(torch.bfloat16)
+    kv_len = [p + n for p, n in zip(prefix_lens, n_qs)]
+    cols = max(kv_len) + 5
+    mask = torch.zeros(B, QL, cols, dtype=torch.bool)
+    for b in range(B):
+        st = synthetic.random_tree(n_qs[b], 6, 3, 1000, gen)
+        tree = Tree.from_arrays(st.token_ids.tolist(), st.parents.tolist())
+        mask[b, :n_qs[b], :kv_len[b]] = tree.create_attention_mask(prefix_length=prefix_lens[b])[0, 0]
+    return dict(B=B, QL=QL, table=table, pool=pool, q=q, k=k, v=v, kv_len=kv_len, n_q=n_qs, mask=mask,
+                prefix=prefix_lens, layer=layer, page_len=page_len)
+
+
+def _run_and_check(c, tol=2e-2):
+    dev = "cuda"
+    pool = c["pool"].to(dev)
+    table = c["table"].to(dev)
+    kv_len = torch.tensor(c["kv_len"], dtype=torch.int32, device=dev)
+    n_q = torch.tensor(c["n_q"], dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    append_paged_kv(pool, c["layer"], c["k"].to(dev), c["v"].to(dev), page_table=table, kv_len=kv_len, n_q=n_q,
+                    status=status)
+    out = tree_attention_paged(c["q"].to(dev), pool, c["layer"], page_table=table, kv_len=kv_len,
+                               mask=c["mask"].to(dev), n_q=n_q, status=status)
+    assert int(status.item()) == 0
+    # the append: exactly the tree's rows changed, and they hold k / v bit for bit
+    want_pool = c["pool"].clone()
+    for b in range(c["B"]):
+        for i in range(c["n_q"][b]):
+            pos = c["prefix"][b] + i
+            pg, slot = int(c["table"][b, pos // c["page_len"]]), pos % c["page_len"]
+            want_pool[c["layer"], pg, 0, slot] = c["k"][b, i]
+            want_pool[c["layer"], pg, 1, slot] = c["v"][b, i]
+    assert torch.equal(pool.cpu(), want_pool)
+    worst = 0.0
+    for b in range(c["B"]):
+        n, nq = c["kv_len"][b], c["n_q"][b]
+        pages = c["table"][b].tolist()
+        kk, vv = ao.gather_rows(want_pool, c["layer"], pages, n)
+        ref = ao.tree_attention(c["q"][b, :nq], kk, vv, c["mask"][b, :nq, :n])
+        got = out[b, :nq].double().cpu()
+        err = float((got - ref).abs().max() / ref.abs().max())
+        worst = max(worst, err)
+        # no worse than what rounding P to bf16 and the output to bf16 allows
+        assert err < tol, (b, err)
+    return worst
+
+
+def test_small_trees_grouped_heads(cuda_lib):
+    """Qwen2.5-7B's head layout (28 query heads on 4 KV heads), ragged prefixes that end inside a page and inside
+    a 64-row tile, trees smaller than the buffers, a request with an empty prefix."""
+    c = _case(1, B=4, QL=24, HQ=28, HKV=4, prefix_lens=[0, 37, 64, 131], n_qs=[24, 9, 17, 24])
+    assert _run_and_check(c) < 1e-2
+
+
+def test_single_kv_head_and_one_token(cuda_lib):
+    c = _case(2, B=2, QL=8, HQ=4, HKV=1, prefix_lens=[5, 300], n_qs=[1, 8], page_len=8)
+    _run_and_check(c)
+    c = _case(3, B=1, QL=64, HQ=8, HKV=8, prefix_lens=[1000], n_qs=[64], layers=1, layer=0)
+    _run_and_check(c)
+
+
+def test_benchmark_shape(cuda_lib):
+    """One request of the sharded-step workload: a 64-node tree behind 4032 cached rows (4096 in all, page 16),
+    28 query heads on 4 KV heads; linearity in V as a size-independent check beside the oracle."""
+    c = _case(4, B=2, QL=64, HQ=28, HKV=4, prefix_lens=[4032, 2000], n_qs=[64, 64])
+    _run_and_check(c)
+    dev = "cuda"
+    pool = c["pool"].to(dev)
+    table, kv_len = c["table"].to(dev), torch.tensor(c["kv_len"], dtype=torch.int32, device=dev)
+    o1 = tree_attention_paged(c["q"].to(dev), pool, c["layer"], page_table=table, kv_len=kv_len, mask=c["mask"].to(dev))
+    pool[:, :, 1] *= 2   # V doubled: the output doubles exactly (powers of two commute with every rounding)
+    o2 = tree_attention_paged(c["q"].to(dev), pool, c["layer"], page_table=table, kv_len=kv_len, mask=c["mask"].to(dev))
+    assert torch.equal(o2.float(), o1.float() * 2)
+    with pytest.raises(ValueError):
+        tree_attention_paged(c["q"].to(dev)[..., :64].contiguous(), pool, 0, page_table=table, kv_len=kv_len,
+                             mask=c["mask"].to(dev))
