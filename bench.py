@@ -55,7 +55,7 @@ def parse_args():
                     help="verify greedily and lossily in two launches (two passes over the logits) instead of one")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the side measurements of the other kernels")
-    ap.add_argument("--extras-only", choices=["step", "expand", "stochastic", "gemm"], default=None,
+    ap.add_argument("--extras-only", choices=["step", "expand", "attention", "stochastic", "gemm"], default=None,
                     help="run one of the side measurements alone on GPU 0 and print it as one JSON line")
     ap.add_argument("--cpu-sample", type=int, default=CPU_SAMPLE,
                     help="sequences per pass of the CPU path (the cpu_baseline leg and the reference arm use the same)")
@@ -310,6 +310,7 @@ def extras(device, peak_gbs, peak_tf):
     out = {}
     out.update(extra_step_peaked(device, peak_gbs))
     out.update(extra_expand(device, peak_gbs))
+    out.update(extra_attention(device, peak_gbs, peak_tf))
     out.update(extra_stochastic(device, peak_gbs))
     out.update(extra_gemm(device, peak_gbs, peak_tf))
     return out
@@ -367,6 +368,33 @@ def extra_step_peaked(device, peak_gbs, wave=64):
     del sb, logits
     torch.cuda.empty_cache()
     return out
+
+
+def extra_attention(device, peak_gbs, peak_tf, batch=64):
+    """Tree attention of one layer at the sharded-step shape: 64 requests, a 64-node tree behind 4032 cached
+    rows each (4096 in all, page 16, random page table), 28 query heads on 4 KV heads of dim 128."""
+    from subspec_b200 import synthetic
+    from subspec_b200.attention import tree_attention_paged
+
+    QL, HQ, HKV, D, page_len, kv = 64, 28, 4, 128, PAGE_LEN, KV_TOKENS
+    pages = kv // page_len
+    gen = torch.Generator().manual_seed(77)
+    table = synthetic.random_page_table(batch, pages, gen).to(device)
+    pool = torch.empty(1, batch * pages, 2, page_len, HKV, D, dtype=torch.bfloat16, device=device).normal_()
+    q = torch.randn(batch, QL, HQ, D, device=device).to(torch.bfloat16)
+    kv_len = torch.full((batch,), kv, dtype=torch.int32, device=device)
+    mask = torch.zeros(batch, QL, kv, dtype=torch.bool, device=device)
+    mask[:, :, :kv - QL] = True
+    mask[:, :, kv - QL:] = torch.tril(torch.ones(QL, QL, dtype=torch.bool, device=device))  # a chain: the densest tree
+    _spin_up(device)
+    ms = _time_ms(lambda: tree_attention_paged(q, pool, 0, page_table=table, kv_len=kv_len, mask=mask), iters=20, warm=3)
+    flops = 4.0 * batch * QL * HQ * kv * D
+    nbytes = batch * (2 * kv * HKV * D * 2 + 2 * QL * HQ * D * 2)
+    t_roof = max(nbytes / (peak_gbs * 1e9), flops / (peak_tf * 1e12))
+    return {"tree_attention_layer_config5": {
+        "ms": ms, "TFLOP/s": flops / (ms * 1e-3) / 1e12, "GB/s": nbytes / (ms * 1e-3) / 1e9,
+        "roofline_ms": t_roof * 1e3, "frac": t_roof / (ms * 1e-3), "bound": "tensor",
+        "path": "mma.sync bf16 (warp-level tensor path, not tcgen05)", "requests": batch}}
 
 
 def extra_expand(device, peak_gbs):
@@ -531,6 +559,8 @@ def run_extras_only(args):
         out = extra_step_peaked(device, peak_gbs)
     elif args.extras_only == "expand":
         out = extra_expand(device, peak_gbs)
+    elif args.extras_only == "attention":
+        out = extra_attention(device, peak_gbs, peak_tf)
     elif args.extras_only == "stochastic":
         out = extra_stochastic(device, peak_gbs)
     else:

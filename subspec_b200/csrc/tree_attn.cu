@@ -52,6 +52,11 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"((uint32_t)__cvta_generic_to_shared(smem_row)));
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"((uint32_t)__cvta_generic_to_shared(smem_row)));
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -157,12 +162,15 @@ __global__ void __launch_bounds__(kAttnThreads, 1) tree_attn_kernel(const AttnAr
 #pragma unroll
     for (int nt = 0; nt < kTileKV / 8; ++nt) {
       s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-      const __nv_bfloat16* krow = Ks + (size_t)(nt * 8 + (lane >> 2)) * kRowElems + (lane & 3) * 2;
+      // one x4 load = the K fragments of two k-steps: lanes 0-7 / 8-15 / 16-23 / 24-31 address cache rows
+      // nt*8 + 0..7 at dims 32 j + 0 / 8 / 16 / 24
+      const __nv_bfloat16* krow = Ks + (size_t)(nt * 8 + (lane & 7)) * kRowElems + ((lane >> 3) << 3);
 #pragma unroll
-      for (int ks = 0; ks < kD / 16; ++ks) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8);
-        mma_bf16(s[nt], qf[ks], b0, b1);
+      for (int j = 0; j < kD / 32; ++j) {
+        uint32_t kf[4];
+        ldmatrix_x4(kf, krow + j * 32);
+        mma_bf16(s[nt], qf[2 * j], kf[0], kf[1]);
+        mma_bf16(s[nt], qf[2 * j + 1], kf[2], kf[3]);
       }
     }
     // ---- scale, mask, online softmax ----
@@ -192,16 +200,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1) tree_attn_kernel(const AttnAr
     tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 2));
     const float nA = fmaxf(mxA, tmA), nB = fmaxf(mxB, tmB);
     const float uA = nA == -INFINITY ? 0.f : nA, uB = nB == -INFINITY ? 0.f : nB;  // a row with nothing visible yet
-    const float alA = exp2f(mxA - uA), alB = exp2f(mxB - uB);
+    const float alA = ex2f(mxA - uA), alB = ex2f(mxB - uB);
     mxA = nA;
     mxB = nB;
     float sumA = 0.f, sumB = 0.f;
 #pragma unroll
     for (int nt = 0; nt < kTileKV / 8; ++nt) {
-      s[nt][0] = exp2f(s[nt][0] - uA);
-      s[nt][1] = exp2f(s[nt][1] - uA);
-      s[nt][2] = exp2f(s[nt][2] - uB);
-      s[nt][3] = exp2f(s[nt][3] - uB);
+      s[nt][0] = ex2f(s[nt][0] - uA);
+      s[nt][1] = ex2f(s[nt][1] - uA);
+      s[nt][2] = ex2f(s[nt][2] - uB);
+      s[nt][3] = ex2f(s[nt][3] - uB);
       sumA += s[nt][0] + s[nt][1];
       sumB += s[nt][2] + s[nt][3];
     }
