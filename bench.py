@@ -132,6 +132,16 @@ class ClockSampler:
                 pass
             self._stop.wait(self._period)
 
+    def sample_now(self):
+        """One sample from the calling thread (the timed region's launches are queued and still running)."""
+        if self._nv is None:
+            return
+        nv = self._nv
+        try:
+            self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+        except Exception:
+            pass
+
     def __enter__(self):
         if self._nv is not None:
             self._thread = threading.Thread(target=self._loop, daemon=True)
@@ -668,6 +678,7 @@ def main():
         for _ in range(args.steps):
             one_step(kernel_events)
         t_end.record()
+        clocks.sample_now()  # the launches above are still executing: a short region gets its sample under load
         torch.cuda.synchronize()
     barrier()
     ms_total = t_start.elapsed_time(t_end)
