@@ -16,7 +16,11 @@
 // this row of the hot path, and its distance from the tcgen05 roofline is reported as measured.
 #include <math.h>
 
+#include <stdlib.h>
+
 #include "common.cuh"
+#include "tcgen05.cuh"
+#include "tma.cuh"
 
 namespace subspec {
 namespace {
@@ -62,10 +66,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+constexpr int kAhead = 3;  // fragment loads in flight ahead of the MMAs
+
 struct AttnArgs {
   subspec_tree_attn_args a;
   int group;        // query heads per KV head
   float scale_log2; // sm_scale * log2(e)
+  int page_shift;   // log2(page_len) when it is a power of two, else -1
 };
 
 __global__ void __launch_bounds__(kAttnThreads, 1) tree_attn_kernel(const AttnArgs ka) {
@@ -160,17 +167,28 @@ __global__ void __launch_bounds__(kAttnThreads, 1) tree_attn_kernel(const AttnAr
     // ---- S = Q K^T for 64 cache rows: 8 n-tiles of 8 rows ----
     float s[kTileKV / 8][4];
 #pragma unroll
-    for (int nt = 0; nt < kTileKV / 8; ++nt) {
-      s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-      // one x4 load = the K fragments of two k-steps: lanes 0-7 / 8-15 / 16-23 / 24-31 address cache rows
-      // nt*8 + 0..7 at dims 32 j + 0 / 8 / 16 / 24
-      const __nv_bfloat16* krow = Ks + (size_t)(nt * 8 + (lane & 7)) * kRowElems + ((lane >> 3) << 3);
+    for (int nt = 0; nt < kTileKV / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    // k-steps outside, n-tiles inside: consecutive MMAs write different accumulators (eight in flight) instead
+    // of queueing behind one another on the same one.  One x4 load = the K fragments of two k-steps: lanes
+    // 0-7 / 8-15 / 16-23 / 24-31 address cache rows nt*8 + 0..7 at dims 32 j + 0 / 8 / 16 / 24.
+    const __nv_bfloat16* kbase = Ks + (size_t)(lane & 7) * kRowElems + ((lane >> 3) << 3);
+    // The fragment loads run kAhead iterations ahead of the MMAs that use them (both are volatile asm, which
+    // the compiler keeps in program order): a load's latency is covered by the MMAs of the iterations between.
+    {
+      constexpr int kIters = (kD / 32) * (kTileKV / 8);
+      uint32_t kf[kAhead + 1][4];
 #pragma unroll
-      for (int j = 0; j < kD / 32; ++j) {
-        uint32_t kf[4];
-        ldmatrix_x4(kf, krow + j * 32);
-        mma_bf16(s[nt], qf[2 * j], kf[0], kf[1]);
-        mma_bf16(s[nt], qf[2 * j + 1], kf[2], kf[3]);
+      for (int i = 0; i < kAhead; ++i)
+        ldmatrix_x4(kf[i], kbase + (size_t)(i % (kTileKV / 8)) * 8 * kRowElems + (i / (kTileKV / 8)) * 32);
+#pragma unroll
+      for (int i = 0; i < kIters; ++i) {
+        if (i + kAhead < kIters) {
+          const int n = i + kAhead;
+          ldmatrix_x4(kf[n % (kAhead + 1)], kbase + (size_t)(n % (kTileKV / 8)) * 8 * kRowElems + (n / (kTileKV / 8)) * 32);
+        }
+        const int j = i / (kTileKV / 8), nt = i % (kTileKV / 8);
+        mma_bf16(s[nt], qf[2 * j], kf[i % (kAhead + 1)][0], kf[i % (kAhead + 1)][1]);
+        mma_bf16(s[nt], qf[2 * j + 1], kf[i % (kAhead + 1)][2], kf[i % (kAhead + 1)][3]);
       }
     }
     // ---- scale, mask, online softmax ----
@@ -223,22 +241,30 @@ __global__ void __launch_bounds__(kAttnThreads, 1) tree_attn_kernel(const AttnAr
       o[nt][3] *= alB;
     }
     // ---- O += P V: 4 k-steps of 16 cache rows; V row-major [row][dim] is read transposed ----
+    // lanes 0-7 / 8-15 address cache rows ks*16 + 0..7 / 8..15 of dims [16 j, 16 j + 8), lanes 16-31 the same
+    // rows of dims [16 j + 8, 16 j + 16): one x4 load feeds two n-tiles.  Loads run kAhead iterations ahead.
+    {
+      constexpr int kJ = kD / 16, kIters = (kTileKV / 16) * kJ;
+      const __nv_bfloat16* vbase = Vs + (size_t)(lane & 15) * kRowElems + ((lane >> 4) << 3);
+      uint32_t vf[kAhead + 1][4];
 #pragma unroll
-    for (int ks = 0; ks < kTileKV / 16; ++ks) {
+      for (int i = 0; i < kAhead; ++i) ldmatrix_x4_trans(vf[i], vbase + (size_t)(i / kJ) * 16 * kRowElems + (i % kJ) * 16);
       uint32_t pf[4];
-      pf[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
-      pf[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
-      pf[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
-      pf[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
-      // lanes 0-7 / 8-15 address cache rows ks*16 + 0..7 / 8..15 of dims [16 j, 16 j + 8), lanes 16-31 the same
-      // rows of dims [16 j + 8, 16 j + 16): one x4 load feeds two n-tiles
-      const __nv_bfloat16* vrow = Vs + (size_t)(ks * 16 + (lane & 15)) * kRowElems + ((lane >> 4) << 3);
 #pragma unroll
-      for (int j = 0; j < kD / 16; ++j) {
-        uint32_t vf[4];
-        ldmatrix_x4_trans(vf, vrow + j * 16);
-        mma_bf16(o[2 * j], pf, vf[0], vf[1]);
-        mma_bf16(o[2 * j + 1], pf, vf[2], vf[3]);
+      for (int i = 0; i < kIters; ++i) {
+        if (i + kAhead < kIters) {
+          const int n = i + kAhead;
+          ldmatrix_x4_trans(vf[n % (kAhead + 1)], vbase + (size_t)(n / kJ) * 16 * kRowElems + (n % kJ) * 16);
+        }
+        const int ks = i / kJ, j = i % kJ;
+        if (j == 0) {
+          pf[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+          pf[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+          pf[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+          pf[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+        }
+        mma_bf16(o[2 * j], pf, vf[i % (kAhead + 1)][0], vf[i % (kAhead + 1)][1]);
+        mma_bf16(o[2 * j + 1], pf, vf[i % (kAhead + 1)][2], vf[i % (kAhead + 1)][3]);
       }
     }
     __syncthreads();  // the stage is free for the load after next
@@ -258,6 +284,368 @@ __global__ void __launch_bounds__(kAttnThreads, 1) tree_attn_kernel(const AttnAr
     const int c = nt * 8 + (lane & 3) * 2;
     if (okA) *reinterpret_cast<uint32_t*>(oA + c) = pack_bf16(o[nt][0] * invA, o[nt][1] * invA);
     if (okB) *reinterpret_cast<uint32_t*>(oB + c) = pack_bf16(o[nt][2] * invB, o[nt][3] * invB);
+  }
+}
+
+// ================================ the tcgen05 kernel ================================================
+// One CTA = 128 query rows of one (request, KV head), as above.  Tiles of 128 cache rows.
+//
+//   warps 0-3  softmax: thread = query row = lane of tensor memory.  Puts its row of Q into tensor memory once;
+//              per tile reads its row of S (tcgen05.ld), keeps the running maximum and sum, rescales its row of
+//              O in tensor memory when the maximum of any row of the warp moved, writes P = exp2(S c - m) as
+//              packed bf16 into tensor memory (tcgen05.st).
+//   warp 4     one elected thread issues the MMAs: S = Q K^T (A = Q from tensor memory, B = the K tile in
+//              shared memory, K-major) one tile ahead of the softmax, into two S buffers in turn; O += P V
+//              (A = P from tensor memory, B = the V tile, MN-major: V lies [cache row][dim] as the cache has
+//              it, so K and V tiles share one shared-memory layout and the gather never transposes).
+//   warps 5-8  gather: 16-byte cp.async copies, cache row by cache row through the page table, into the
+//              128-byte-swizzled layout the tensor core reads: a tile = two blocks of 64 dims, a block = 128
+//              rows of 128 bytes, 16-byte chunk c of row r stored at chunk c ^ (r & 7).
+//
+// Tensor memory (512 columns, one CTA per SM): S0 | S1 | O | P | Q = 128 + 128 + 128 + 64 + 64.
+constexpr int kTcRows = 128;
+constexpr int kTcKeys = 128;
+constexpr int kTcStages = 3;
+constexpr int kTcBlockBytes = kTcKeys * 128;        // 64 dims of 128 cache rows
+constexpr int kTcTileBytes = 2 * kTcBlockBytes;     // K (or V) of one tile: 32 KB
+constexpr int kTcStageBytes = 2 * kTcTileBytes;     // K then V
+constexpr size_t kTcSmem = (size_t)kTcStages * kTcStageBytes + 1024;  // + room to align to the swizzle atom
+constexpr int kTcSoftmaxWarps = 4;
+constexpr int kTcIssuerWarp = 4;
+constexpr int kTcLoadWarp0 = 5;
+constexpr int kTcLoadWarps = 4;
+constexpr int kTcLoadThreads = 32 * kTcLoadWarps;
+constexpr int kTcThreads = 32 * (kTcLoadWarp0 + kTcLoadWarps);
+constexpr uint32_t kColS = 0, kColO = 256, kColP = 384, kColQ = 448, kTcCols = 512;
+
+// Shared-memory matrix descriptor, 128-byte swizzle, 8-row atoms of 1024 bytes: [0,14) address >> 4, [16,30)
+// leading byte offset >> 4, [32,46) stride byte offset >> 4, [46,48) version 1, [61,64) layout 2.
+// K-major operand (the K tile: N = cache rows, K = dims): stride = 1024 between 8-row groups, leading unused.
+// MN-major operand (the V tile: N = dims, K = cache rows): stride = 1024 between groups of 8 cache rows,
+// leading = the distance between the two 64-dim blocks.
+__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr, uint32_t leading_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(leading_bytes >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor, kind::f16: D fp32 (bit 4), A and B bf16 (1 at [7,10) and [10,13)), bit 16 = B is
+// MN-major, N >> 3 at [17,23), M >> 4 at [24,29).
+__host__ __device__ constexpr uint32_t tc_idesc(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+
+struct TcRing {
+  int s = 0;
+  uint32_t ph = 0;
+  __device__ __forceinline__ void next() {
+    if (++s == kTcStages) {
+      s = 0;
+      ph ^= 1u;
+    }
+  }
+};
+
+__global__ void __launch_bounds__(kTcThreads, 1) tree_attn_tc_kernel(const AttnArgs ka) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full[kTcStages], empty[kTcStages], s_ready[2], p_ready, o_done, q_ready;
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_abort;
+  const subspec_tree_attn_args& a = ka.a;
+  const int b = blockIdx.z, kvh = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = ka.group, QL = a.q_len;
+  if ((int)blockIdx.x * kTcRows >= G * QL) return;
+  int nq = a.n_q ? a.n_q[b] : QL;
+  nq = min(max(nq, 0), QL);
+  int kv_len = a.kv_len[b];
+  const int cap = a.pages_per_seq * a.page_len;
+  if (kv_len < 0 || kv_len > cap) {
+    if (threadIdx.x == 0) flag(a.dev_status, SUBSPEC_DEV_BAD_COUNT);
+    kv_len = min(max(kv_len, 0), cap);
+  }
+  int prefix = a.prefix_len ? a.prefix_len[b] : kv_len - nq;
+  prefix = min(max(prefix, 0), kv_len);
+  const int ntiles = (kv_len + kTcKeys - 1) / kTcKeys;
+
+  // this thread's query row (softmax warps): (head of the group, tree token)
+  const int row = blockIdx.x * kTcRows + (int)threadIdx.x;
+  const int rg = row / QL, ri = row - rg * QL;
+  const bool row_ok = threadIdx.x < kTcRows && rg < G && ri < nq;
+  __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(a.out) + (size_t)b * a.o_batch_stride +
+                           (size_t)ri * a.o_token_stride + (size_t)(kvh * G + rg) * a.o_head_stride;
+  if (ntiles == 0) {  // nothing to attend to: zeros, as the sum of no terms
+    if (row_ok)
+      for (int c = 0; c < kD / 2; ++c) reinterpret_cast<uint32_t*>(out_row)[c] = 0u;
+    return;
+  }
+
+  unsigned char* tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTcStages; ++s) {
+      mbar_init(&full[s], kTcLoadThreads);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&s_ready[0], 1);
+    mbar_init(&s_ready[1], 1);
+    mbar_init(&p_ready, kTcSoftmaxWarps);
+    mbar_init(&q_ready, kTcSoftmaxWarps);
+    mbar_init(&o_done, 1);
+    mbar_init_fence();
+    s_abort = 0;
+  }
+  if (warp == kTcIssuerWarp) {
+    tmem_alloc(&s_tmem, kTcCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp < kTcSoftmaxWarps) {
+    // ================= softmax: thread = query row = tensor-memory lane =================
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    {  // Q -> tensor memory: column c of the lane = dims 2c, 2c + 1 (rows that do not exist: zeros)
+      const __nv_bfloat16* qrow = reinterpret_cast<const __nv_bfloat16*>(a.q) + (size_t)b * a.q_batch_stride +
+                                  (size_t)ri * a.q_token_stride + (size_t)(kvh * G + rg) * a.q_head_stride;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = row_ok ? reinterpret_cast<const uint32_t*>(qrow)[32 * c + j] : 0u;
+        tmem_st32(lane_base + kColQ + 32 * c, r);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_ready);
+    }
+    const uint8_t* mrow = a.mask + (size_t)b * a.mask_batch_stride + (size_t)ri * a.mask_row_stride;
+    const float c2 = ka.scale_log2;
+    float m = -INFINITY, l = 0.f;  // running maximum (in the exponent's units) and sum of this row
+    bool live = true;
+    for (int t = 0; t < ntiles; ++t) {
+      const int sb = t & 1;
+      live = __all_sync(0xffffffffu, wait_or_abort(&s_ready[sb], (uint32_t)(t >> 1) & 1u, abort_flag));
+      if (!live) break;
+      tc_fence_after();
+      const uint32_t s_addr = lane_base + kColS + (uint32_t)(sb * kTcKeys);
+      const int t0 = t * kTcKeys;
+      const bool need_mask = t0 + kTcKeys > prefix;  // tiles inside the prefix are visible to every row
+      uint32_t vis[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t bits = 0;
+          for (int j = 0; j < 32; ++j) {
+            const int pos = t0 + 32 * c + j;
+            const bool v = pos < prefix || (pos < kv_len && row_ok && mrow[pos] != 0);
+            bits |= (v ? 1u : 0u) << j;
+          }
+          vis[c] = bits;
+        }
+      }
+      // ---- pass 1: the row's maximum over the tile ----
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32_async(s_addr + 32 * c, r);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if ((vis[c] >> j) & 1u) tmax = fmaxf(tmax, __uint_as_float(r[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(r[j]));
+        }
+      }
+      const float m_new = fmaxf(m, tmax * c2);                 // c2 > 0: the maximum commutes with the scaling
+      const float u = m_new == -INFINITY ? 0.f : m_new;        // a row with nothing visible yet
+      const float alpha = ex2f(m - u);                         // 0 while m is -inf
+      m = m_new;
+      // ---- the previous tile's O += P V must have landed before P is overwritten and O rescaled ----
+      if (t > 0) {
+        live = __all_sync(0xffffffffu, wait_or_abort(&o_done, (uint32_t)(t - 1) & 1u, abort_flag));
+        if (!live) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld32_async(lane_base + kColO + 32 * c, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+            tmem_st32(lane_base + kColO + 32 * c, r);
+          }
+        }
+      }
+      // ---- pass 2: P = exp2(S c2 - m), the row sum ----
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32_async(s_addr + 32 * c, r);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float p0 = ex2f(fmaf(__uint_as_float(r[2 * j]), c2, -u));
+          float p1 = ex2f(fmaf(__uint_as_float(r[2 * j + 1]), c2, -u));
+          if (need_mask) {
+            p0 = ((vis[c] >> (2 * j)) & 1u) ? p0 : 0.f;
+            p1 = ((vis[c] >> (2 * j + 1)) & 1u) ? p1 : 0.f;
+          }
+          sum += p0 + p1;
+          pk[j] = pack_bf16(p0, p1);
+        }
+        tmem_st16(lane_base + kColP + 16 * c, pk);
+      }
+      l = l * alpha + sum;
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready);
+    }
+    // ---- the result: O / l ----
+    if (live) live = __all_sync(0xffffffffu, wait_or_abort(&o_done, (uint32_t)(ntiles - 1) & 1u, abort_flag));
+    if (live) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32_async(lane_base + kColO + 32 * c, r);
+        tmem_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[8 * j]) * inv, __uint_as_float(r[8 * j + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(r[8 * j + 2]) * inv, __uint_as_float(r[8 * j + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(r[8 * j + 4]) * inv, __uint_as_float(r[8 * j + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(r[8 * j + 6]) * inv, __uint_as_float(r[8 * j + 7]) * inv);
+            reinterpret_cast<uint4*>(out_row)[4 * c + j] = v;
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  } else if (warp == kTcIssuerWarp) {
+    // ================= MMA issue: the whole warp runs the loop, one elected lane issues =================
+    constexpr uint32_t idesc_s = tc_idesc(kTcRows, kTcKeys, false);
+    constexpr uint32_t idesc_o = tc_idesc(kTcRows, kD, true);
+    const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+    const uint32_t tiles_u32 = smem_u32(tiles);
+    // S(t) = Q K(t)^T: 8 steps of 16 dims; a step moves 32 bytes inside a 64-dim block, 4 steps per block
+    auto issue_s = [&](int stage, int sbuf) {
+      const uint32_t kaddr = tiles_u32 + (uint32_t)stage * kTcStageBytes;
+#pragma unroll
+      for (int ks = 0; ks < kD / 16; ++ks)
+        tc_mma_f16_ta(tm + kColS + (uint32_t)(sbuf * kTcKeys), tm + kColQ + (uint32_t)(8 * ks),
+                      tc_desc(kaddr + (uint32_t)((ks >> 2) * kTcBlockBytes + (ks & 3) * 32), 16), idesc_s,
+                      ks > 0 ? 1u : 0u);
+    };
+    bool ok = __all_sync(0xffffffffu, wait_or_abort(&q_ready, 0, abort_flag));
+    TcRing rs;  // the stage S(t + 1) reads, one ahead of the stage O += P V reads
+    ok = ok && __all_sync(0xffffffffu, wait_or_abort(&full[0], 0, abort_flag));
+    if (ok) {
+      tc_fence_after();
+      if (elect_one()) {
+        issue_s(0, 0);
+        tc_commit(&s_ready[0]);
+      }
+      __syncwarp();
+      rs.next();
+      TcRing ro;
+      for (int t = 0; t < ntiles; ++t) {
+        if (t + 1 < ntiles) {
+          if (!__all_sync(0xffffffffu, wait_or_abort(&full[rs.s], rs.ph, abort_flag))) break;
+          tc_fence_after();
+          if (elect_one()) {
+            issue_s(rs.s, (t + 1) & 1);
+            tc_commit(&s_ready[(t + 1) & 1]);
+          }
+          __syncwarp();
+          rs.next();
+        }
+        if (!__all_sync(0xffffffffu, wait_or_abort(&p_ready, (uint32_t)t & 1u, abort_flag))) break;
+        tc_fence_after();
+        if (elect_one()) {
+          // O += P V(t): 8 steps of 16 cache rows = 2048 bytes of the V tile each
+          const uint32_t vaddr = tiles_u32 + (uint32_t)ro.s * kTcStageBytes + kTcTileBytes;
+#pragma unroll
+          for (int ks = 0; ks < kTcKeys / 16; ++ks)
+            tc_mma_f16_ta(tm + kColO, tm + kColP + (uint32_t)(8 * ks), tc_desc(vaddr + (uint32_t)(ks * 2048), kTcBlockBytes),
+                          idesc_o, (t > 0 || ks > 0) ? 1u : 0u);
+          tc_commit(&o_done);
+          tc_commit(&empty[ro.s]);
+        }
+        __syncwarp();
+        ro.next();
+      }
+    }
+  } else {
+    // ================= gather: 16 lanes per cache row (its 16 chunks of 16 bytes), 8 rows per pass =================
+    const int p = (int)threadIdx.x - 32 * kTcLoadWarp0;
+    const int chunk = p & 15, sub = p >> 4;
+    const size_t row_bytes = (size_t)a.num_kv_heads * kD * 2;   // one cache row, all KV heads
+    const size_t kv_plane = (size_t)a.page_len * row_bytes;     // K (or V) of one page
+    const unsigned char* pool = reinterpret_cast<const unsigned char*>(a.pool) +
+                                (size_t)a.layer * a.num_pages * 2 * kv_plane + (size_t)kvh * kD * 2 + chunk * 16;
+    const int* table = a.page_table + (size_t)b * a.pages_per_seq;
+    const uint32_t dst_chunk = (uint32_t)((chunk >> 3) * kTcBlockBytes);
+    TcRing r, done;
+    for (int t = 0; t < ntiles; ++t) {
+      if (t >= kTcStages && !wait_or_abort(&empty[r.s], r.ph ^ 1u, abort_flag)) break;
+      unsigned char* kdst = tiles + (size_t)r.s * kTcStageBytes + dst_chunk;
+#pragma unroll 4
+      for (int pass = 0; pass < kTcKeys / 8; ++pass) {
+        const int rr = pass * 8 + sub;
+        const int pos = t * kTcKeys + rr;
+        const unsigned char* src = pool;
+        int bytes = 0;
+        if (pos < kv_len) {
+          const int pi = ka.page_shift >= 0 ? pos >> ka.page_shift : pos / a.page_len;
+          int page = table[pi];
+          if (page < 0 || page >= a.num_pages) {
+            flag(a.dev_status, SUBSPEC_DEV_BAD_PAGE);
+            page = 0;
+          } else {
+            bytes = 16;
+          }
+          src = pool + (size_t)page * 2 * kv_plane + (size_t)(pos - pi * a.page_len) * row_bytes;
+        }
+        unsigned char* d = kdst + rr * 128 + (((chunk & 7) ^ (rr & 7)) << 4);
+        cp_async16(d, src, bytes);                           // rows past the end: zeros
+        cp_async16(d + kTcTileBytes, src + kv_plane, bytes);
+      }
+      cp_async_commit();
+      if (t > 0) {  // the tile before this one has landed: hand it to the tensor core's proxy
+        cp_async_wait<1>();
+        fence_async_smem();
+        mbar_arrive(&full[done.s]);
+        done.next();
+      }
+      r.next();
+    }
+    cp_async_wait<0>();
+    fence_async_smem();
+    mbar_arrive(&full[done.s]);
+  }
+  __syncthreads();
+  if (s_abort && threadIdx.x == 0) flag(a.dev_status, SUBSPEC_DEV_TIMEOUT);
+  if (warp == kTcIssuerWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTcCols);
   }
 }
 
@@ -317,12 +705,24 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
   ka.a = a;
   ka.group = a.num_q_heads / a.num_kv_heads;
   ka.scale_log2 = (float)(a.sm_scale * 1.4426950408889634);
-  int rc = cuda_check(
-      cudaFuncSetAttribute(tree_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem));
+  ka.page_shift = -1;
+  for (int sft = 0; sft < 31; ++sft)
+    if ((1 << sft) == a.page_len) ka.page_shift = sft;
+  const cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (getenv("SUBSPEC_ATTN_MMA_SYNC")) {
+    int rc = cuda_check(
+        cudaFuncSetAttribute(tree_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem));
+    if (rc) return rc;
+    const dim3 grid((unsigned)((ka.group * a.q_len + kRowsPerCta - 1) / kRowsPerCta), (unsigned)a.num_kv_heads,
+                    (unsigned)a.batch);
+    tree_attn_kernel<<<grid, kAttnThreads, kAttnSmem, st>>>(ka);
+    return cuda_check(cudaGetLastError());
+  }
+  const int rc =
+      cuda_check(cudaFuncSetAttribute(tree_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
   if (rc) return rc;
-  const dim3 grid((unsigned)((ka.group * a.q_len + kRowsPerCta - 1) / kRowsPerCta), (unsigned)a.num_kv_heads,
-                  (unsigned)a.batch);
-  tree_attn_kernel<<<grid, kAttnThreads, kAttnSmem, reinterpret_cast<cudaStream_t>(stream)>>>(ka);
+  const dim3 grid((unsigned)((ka.group * a.q_len + kTcRows - 1) / kTcRows), (unsigned)a.num_kv_heads, (unsigned)a.batch);
+  tree_attn_tc_kernel<<<grid, kTcThreads, kTcSmem, st>>>(ka);
   return cuda_check(cudaGetLastError());
 }
 
