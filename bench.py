@@ -404,7 +404,7 @@ def extra_attention(device, peak_gbs, peak_tf, batch=64):
     return {"tree_attention_layer_config5": {
         "ms": ms, "TFLOP/s": flops / (ms * 1e-3) / 1e12, "GB/s": nbytes / (ms * 1e-3) / 1e9,
         "roofline_ms": t_roof * 1e3, "frac": t_roof / (ms * 1e-3), "bound": "tensor",
-        "path": "mma.sync bf16 (warp-level tensor path, not tcgen05)", "requests": batch}}
+        "path": "tcgen05 (S and O in tensor memory, K/V tiles by tensor copies)", "requests": batch}}
 
 
 def extra_expand(device, peak_gbs):

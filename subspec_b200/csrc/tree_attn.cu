@@ -7,17 +7,12 @@
 // them sees the whole committed prefix and, among the tree's rows, itself and its ancestors (the mask the tree
 // finaliser writes: prefix ones | ancestor-or-self columns | zeros).
 //
-// One CTA = 128 query rows of one (request, KV head): the rows are (head of the GQA group, tree token) pairs,
-// so the seven query heads that share a KV head share its K / V tiles.  K / V tiles of 64 cache rows are
-// gathered page by page with 16-byte cp.async copies into padded shared-memory rows (double-buffered); each
-// warp owns 16 query rows: S = Q K^T and O += P V run on the tensor cores (mma.sync m16n8k16, bf16 in, fp32
-// out), the online softmax in registers in the log2 domain.  Tiles that lie wholly inside the prefix need no
-// mask look-up.  This is the warp-level tensor path, not tcgen05: the kernel is a first, correct version of
-// this row of the hot path, and its distance from the tcgen05 roofline is reported as measured.
+// The rows of the attention problem are (head of the GQA group, tree token) pairs, so the query heads that share
+// a KV head share its K / V tiles.  The kernel runs on the tcgen05 tensor cores; its layout is described where
+// it starts.
 #include <math.h>
 
 #include <cuda.h>
-#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -28,14 +23,6 @@ namespace subspec {
 namespace {
 
 constexpr int kD = 128;           // head dimension (the only one built)
-constexpr int kTileKV = 64;       // cache rows per tile
-constexpr int kAttnThreads = 256;
-constexpr int kAttnWarps = kAttnThreads / 32;
-constexpr int kRowsPerCta = kAttnWarps * 16;
-constexpr int kPad = 8;                     // bf16 elements of padding per shared-memory row (bank spread)
-constexpr int kRowElems = kD + kPad;        // 136 elements = 272 bytes
-constexpr int kTileBytes = kTileKV * kRowElems * 2;
-constexpr size_t kAttnSmem = (size_t)kTileBytes * 2 /*K, V*/ * 2 /*stages*/;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)),
@@ -47,28 +34,10 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"((uint32_t)__cvta_generic_to_shared(smem_row)));
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"((uint32_t)__cvta_generic_to_shared(smem_row)));
-}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
-
-constexpr int kAhead = 3;  // fragment loads in flight ahead of the MMAs
 
 struct AttnArgs {
   subspec_tree_attn_args a;
@@ -78,253 +47,47 @@ struct AttnArgs {
   int box_rows;     // cache rows per tensor copy (0: the page length does not suit them)
 };
 
-__global__ void __launch_bounds__(kAttnThreads, 1) tree_attn_kernel(const AttnArgs ka) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  const subspec_tree_attn_args& a = ka.a;
-  const int b = blockIdx.z, kvh = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int G = ka.group, QL = a.q_len;
-  int nq = a.n_q ? a.n_q[b] : QL;
-  nq = min(max(nq, 0), QL);
-  int kv_len = a.kv_len[b];
-  const int cap = a.pages_per_seq * a.page_len;
-  if (kv_len < 0 || kv_len > cap) {
-    if (threadIdx.x == 0) flag(a.dev_status, SUBSPEC_DEV_BAD_COUNT);
-    kv_len = min(max(kv_len, 0), cap);
-  }
-  int prefix = a.prefix_len ? a.prefix_len[b] : kv_len - nq;
-  prefix = min(max(prefix, 0), kv_len);
-  const int row_base = blockIdx.x * kRowsPerCta + warp * 16;
-  if (blockIdx.x * kRowsPerCta >= G * QL) return;
-
-  // this thread's two query rows: r0 = row_base + lane / 4 and r0 + 8; a row is (head of the group, tree token)
-  const int rA = row_base + (lane >> 2), rB = rA + 8;
-  const int gA = rA / QL, iA = rA - gA * QL, gB = rB / QL, iB = rB - gB * QL;
-  const bool okA = gA < G && iA < nq, okB = gB < G && iB < nq;
-  const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(a.q);
-  const __nv_bfloat16* qA = q + (size_t)b * a.q_batch_stride + (size_t)iA * a.q_token_stride +
-                            (size_t)(kvh * G + gA) * a.q_head_stride;
-  const __nv_bfloat16* qB = q + (size_t)b * a.q_batch_stride + (size_t)iB * a.q_token_stride +
-                            (size_t)(kvh * G + gB) * a.q_head_stride;
-  // Q fragments: 8 k-steps of 16 dims
-  uint32_t qf[kD / 16][4];
-#pragma unroll
-  for (int ks = 0; ks < kD / 16; ++ks) {
-    const int c = ks * 16 + (lane & 3) * 2;
-    qf[ks][0] = okA ? *reinterpret_cast<const uint32_t*>(qA + c) : 0u;
-    qf[ks][1] = okB ? *reinterpret_cast<const uint32_t*>(qB + c) : 0u;
-    qf[ks][2] = okA ? *reinterpret_cast<const uint32_t*>(qA + c + 8) : 0u;
-    qf[ks][3] = okB ? *reinterpret_cast<const uint32_t*>(qB + c + 8) : 0u;
-  }
-  const uint8_t* mA = a.mask + (size_t)b * a.mask_batch_stride + (size_t)iA * a.mask_row_stride;
-  const uint8_t* mB = a.mask + (size_t)b * a.mask_batch_stride + (size_t)iB * a.mask_row_stride;
-
-  float o[kD / 8][4];
-#pragma unroll
-  for (int nt = 0; nt < kD / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-  float mxA = -INFINITY, mxB = -INFINITY, lA = 0.f, lB = 0.f;
-
-  // ---- the gather of one K / V tile: 64 cache rows x 256 bytes each for K and for V, 16 bytes per copy ----
-  const size_t row_bytes = (size_t)a.num_kv_heads * kD * 2;             // one cache row, all KV heads
-  const size_t kv_plane = (size_t)a.page_len * row_bytes;              // K (or V) of one page
-  const unsigned char* pool = reinterpret_cast<const unsigned char*>(a.pool) +
-                              (size_t)a.layer * a.num_pages * 2 * kv_plane + (size_t)kvh * kD * 2;
-  const int* table = a.page_table + (size_t)b * a.pages_per_seq;
-  auto load_tile = [&](int tile, int stage) {
-    unsigned char* ks_ = smem + (size_t)stage * 2 * kTileBytes;
-    unsigned char* vs_ = ks_ + kTileBytes;
-    for (int c = threadIdx.x; c < kTileKV * 16; c += kAttnThreads) {  // 16 copies of 16 bytes per row
-      const int r = c >> 4, part = c & 15;
-      const int pos = tile * kTileKV + r;
-      const unsigned char* src = pool;
-      int bytes = 0;
-      if (pos < kv_len) {
-        int page = table[pos / a.page_len];
-        if (page < 0 || page >= a.num_pages) {
-          flag(a.dev_status, SUBSPEC_DEV_BAD_PAGE);
-          page = 0;
-        } else {
-          bytes = 16;
-        }
-        src = pool + (size_t)page * 2 * kv_plane + (size_t)(pos % a.page_len) * row_bytes + part * 16;
-      }
-      cp_async16(ks_ + (size_t)r * kRowElems * 2 + part * 16, src, bytes);            // rows past the end: zeros
-      cp_async16(vs_ + (size_t)r * kRowElems * 2 + part * 16, src + kv_plane, bytes);
-    }
-    cp_async_commit();
-  };
-
-  const int ntiles = (kv_len + kTileKV - 1) / kTileKV;
-  if (ntiles > 0) load_tile(0, 0);
-  for (int t = 0; t < ntiles; ++t) {
-    if (t + 1 < ntiles) {
-      load_tile(t + 1, (t + 1) & 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
-    const __nv_bfloat16* Ks = reinterpret_cast<const __nv_bfloat16*>(smem + (size_t)(t & 1) * 2 * kTileBytes);
-    const __nv_bfloat16* Vs = Ks + kTileKV * kRowElems;
-
-    // ---- S = Q K^T for 64 cache rows: 8 n-tiles of 8 rows ----
-    float s[kTileKV / 8][4];
-#pragma unroll
-    for (int nt = 0; nt < kTileKV / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-    // k-steps outside, n-tiles inside: consecutive MMAs write different accumulators (eight in flight) instead
-    // of queueing behind one another on the same one.  One x4 load = the K fragments of two k-steps: lanes
-    // 0-7 / 8-15 / 16-23 / 24-31 address cache rows nt*8 + 0..7 at dims 32 j + 0 / 8 / 16 / 24.
-    const __nv_bfloat16* kbase = Ks + (size_t)(lane & 7) * kRowElems + ((lane >> 3) << 3);
-    // The fragment loads run kAhead iterations ahead of the MMAs that use them (both are volatile asm, which
-    // the compiler keeps in program order): a load's latency is covered by the MMAs of the iterations between.
-    {
-      constexpr int kIters = (kD / 32) * (kTileKV / 8);
-      uint32_t kf[kAhead + 1][4];
-#pragma unroll
-      for (int i = 0; i < kAhead; ++i)
-        ldmatrix_x4(kf[i], kbase + (size_t)(i % (kTileKV / 8)) * 8 * kRowElems + (i / (kTileKV / 8)) * 32);
-#pragma unroll
-      for (int i = 0; i < kIters; ++i) {
-        if (i + kAhead < kIters) {
-          const int n = i + kAhead;
-          ldmatrix_x4(kf[n % (kAhead + 1)], kbase + (size_t)(n % (kTileKV / 8)) * 8 * kRowElems + (n / (kTileKV / 8)) * 32);
-        }
-        const int j = i / (kTileKV / 8), nt = i % (kTileKV / 8);
-        mma_bf16(s[nt], qf[2 * j], kf[i % (kAhead + 1)][0], kf[i % (kAhead + 1)][1]);
-        mma_bf16(s[nt], qf[2 * j + 1], kf[i % (kAhead + 1)][2], kf[i % (kAhead + 1)][3]);
-      }
-    }
-    // ---- scale, mask, online softmax ----
-    const int t0 = t * kTileKV;
-    const bool need_mask = t0 + kTileKV > prefix;  // tiles inside the prefix are visible to every row
-    float tmA = -INFINITY, tmB = -INFINITY;
-#pragma unroll
-    for (int nt = 0; nt < kTileKV / 8; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float v = s[nt][e] * ka.scale_log2;
-        if (need_mask) {
-          const int pos = t0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-          const uint8_t* mrow = (e & 2) ? mB : mA;
-          const bool row_ok = (e & 2) ? okB : okA;
-          const bool vis = pos < prefix || (pos < kv_len && row_ok && mrow[pos] != 0);
-          v = vis ? v : -INFINITY;
-        }
-        s[nt][e] = v;
-      }
-      tmA = fmaxf(tmA, fmaxf(s[nt][0], s[nt][1]));
-      tmB = fmaxf(tmB, fmaxf(s[nt][2], s[nt][3]));
-    }
-    tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 1));
-    tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 2));
-    tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 1));
-    tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 2));
-    const float nA = fmaxf(mxA, tmA), nB = fmaxf(mxB, tmB);
-    const float uA = nA == -INFINITY ? 0.f : nA, uB = nB == -INFINITY ? 0.f : nB;  // a row with nothing visible yet
-    const float alA = ex2f(mxA - uA), alB = ex2f(mxB - uB);
-    mxA = nA;
-    mxB = nB;
-    float sumA = 0.f, sumB = 0.f;
-#pragma unroll
-    for (int nt = 0; nt < kTileKV / 8; ++nt) {
-      s[nt][0] = ex2f(s[nt][0] - uA);
-      s[nt][1] = ex2f(s[nt][1] - uA);
-      s[nt][2] = ex2f(s[nt][2] - uB);
-      s[nt][3] = ex2f(s[nt][3] - uB);
-      sumA += s[nt][0] + s[nt][1];
-      sumB += s[nt][2] + s[nt][3];
-    }
-    lA = lA * alA + sumA;  // per-thread partial sums: the quad is added up once, at the end
-    lB = lB * alB + sumB;
-#pragma unroll
-    for (int nt = 0; nt < kD / 8; ++nt) {
-      o[nt][0] *= alA;
-      o[nt][1] *= alA;
-      o[nt][2] *= alB;
-      o[nt][3] *= alB;
-    }
-    // ---- O += P V: 4 k-steps of 16 cache rows; V row-major [row][dim] is read transposed ----
-    // lanes 0-7 / 8-15 address cache rows ks*16 + 0..7 / 8..15 of dims [16 j, 16 j + 8), lanes 16-31 the same
-    // rows of dims [16 j + 8, 16 j + 16): one x4 load feeds two n-tiles.  Loads run kAhead iterations ahead.
-    {
-      constexpr int kJ = kD / 16, kIters = (kTileKV / 16) * kJ;
-      const __nv_bfloat16* vbase = Vs + (size_t)(lane & 15) * kRowElems + ((lane >> 4) << 3);
-      uint32_t vf[kAhead + 1][4];
-#pragma unroll
-      for (int i = 0; i < kAhead; ++i) ldmatrix_x4_trans(vf[i], vbase + (size_t)(i / kJ) * 16 * kRowElems + (i % kJ) * 16);
-      uint32_t pf[4];
-#pragma unroll
-      for (int i = 0; i < kIters; ++i) {
-        if (i + kAhead < kIters) {
-          const int n = i + kAhead;
-          ldmatrix_x4_trans(vf[n % (kAhead + 1)], vbase + (size_t)(n / kJ) * 16 * kRowElems + (n % kJ) * 16);
-        }
-        const int ks = i / kJ, j = i % kJ;
-        if (j == 0) {
-          pf[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
-          pf[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
-          pf[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
-          pf[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
-        }
-        mma_bf16(o[2 * j], pf, vf[i % (kAhead + 1)][0], vf[i % (kAhead + 1)][1]);
-        mma_bf16(o[2 * j + 1], pf, vf[i % (kAhead + 1)][2], vf[i % (kAhead + 1)][3]);
-      }
-    }
-    __syncthreads();  // the stage is free for the load after next
-  }
-  lA += __shfl_xor_sync(0xffffffffu, lA, 1);
-  lA += __shfl_xor_sync(0xffffffffu, lA, 2);
-  lB += __shfl_xor_sync(0xffffffffu, lB, 1);
-  lB += __shfl_xor_sync(0xffffffffu, lB, 2);
-  const float invA = lA > 0.f ? 1.f / lA : 0.f, invB = lB > 0.f ? 1.f / lB : 0.f;
-  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out);
-  __nv_bfloat16* oA = out + (size_t)b * a.o_batch_stride + (size_t)iA * a.o_token_stride +
-                      (size_t)(kvh * G + gA) * a.o_head_stride;
-  __nv_bfloat16* oB = out + (size_t)b * a.o_batch_stride + (size_t)iB * a.o_token_stride +
-                      (size_t)(kvh * G + gB) * a.o_head_stride;
-#pragma unroll
-  for (int nt = 0; nt < kD / 8; ++nt) {
-    const int c = nt * 8 + (lane & 3) * 2;
-    if (okA) *reinterpret_cast<uint32_t*>(oA + c) = pack_bf16(o[nt][0] * invA, o[nt][1] * invA);
-    if (okB) *reinterpret_cast<uint32_t*>(oB + c) = pack_bf16(o[nt][2] * invB, o[nt][3] * invB);
-  }
-}
-
-// ================================ the tcgen05 kernel ================================================
 // One CTA = 256 query rows of one (request, KV head) -- two blocks of 128 rows that share every K / V tile --
-// and tiles of 128 cache rows.
+// and tiles of 64 cache rows.
 //
 //   warps 0-7   softmax, four warps per row block: thread = query row = lane of tensor memory.  Per tile a
 //               thread reads its row of S (tcgen05.ld), keeps the running maximum and sum, rescales its row of O
-//               in tensor memory when the maximum of any row of the warp moved, and writes P = exp2(S c - m)
-//               as packed bf16 over the first half of the S columns it has just read (tcgen05.st).
-//   warp 8      one elected thread issues the MMAs.  S = Q K^T: A = the block's Q tile, B = the K tile, both
-//               K-major in shared memory.  O += P V: A = P from tensor memory, B = the V tile, MN-major: V lies
-//               [cache row][dim] as the cache has it, so K and V tiles share one shared-memory layout and the
-//               gather never transposes.  Order per tile: PV(a), S(a, next tile), PV(b), S(b, next tile): while
-//               one block's softmax runs, the tensor core works for the other.
-//   warps 9-11  gather: 16-byte cp.async copies, row by row (cache rows through the page table), into the
-//               128-byte-swizzled layout the tensor core reads: a tile = two blocks of 64 dims, a block = 128
-//               rows of 128 bytes, 16-byte chunk c of row r stored at chunk c ^ (r & 7).  First the two Q
-//               tiles, then K(0), V(0), K(1), V(1), ... through a ring of five 32 KB entries.
+//               in tensor memory when the maximum of some row of the warp has run far enough ahead, and writes
+//               P = exp2(S c - m) as packed bf16 over the first half of the S columns it has just read.
+//   warps 8, 9  one MMA issuer per row block (an elected thread).  S = Q K^T: A = the block's Q tile, B = the K
+//               tile, both K-major in shared memory.  O += P V: A = P from tensor memory, B = the V tile,
+//               MN-major: V lies [cache row][dim] as the cache has it, so K and V tiles share one shared-memory
+//               layout and the gather never transposes.  A block has two S buffers: S of tile t + 1 is computed
+//               while the softmax works on tile t, and S of tile t + 2 goes over the P of tile t as soon as
+//               O += P V of tile t has been issued (the MMAs of a thread run in order).
+//   warps 10,11 gather.  Whole tiles of whole pages come by tensor copies (TMA) of 64 dims x the page's rows,
+//               which the copy unit lays out in the 128-byte-swizzled form the tensor core reads: a tile = two
+//               halves of 64 dims, a half = 64 rows of 128 bytes, 16-byte chunk c of row r stored at chunk
+//               c ^ (r & 7).  The last, partial tile (and page lengths the tensor copies do not suit) comes by
+//               16-byte cp.async copies, row by row, into the same layout, rows past the end as zeros.  The
+//               ring of ten 16 KB entries is filled in the order the issuers consume it:
+//               K(0), K(1), V(0), K(2), V(1), K(3), ...
 //
-// Tensor memory (512 columns, one CTA per SM): S(a) | S(b) | O(a) | O(b), 128 columns each.
+// Tensor memory (512 columns, one CTA per SM), per row block 256 columns: S0 | S1 (64 each) | O (128).
 constexpr int kTcBlockRows = 128;                   // query rows per row block = MMA M
 constexpr int kTcRows = 2 * kTcBlockRows;           // query rows per CTA
-constexpr int kTcKeys = 128;                        // cache rows per tile
-constexpr int kTcRing = 5;                          // ring entries: one K or V tile each
-constexpr int kTcHalfBytes = kTcKeys * 128;         // 64 dims of 128 rows
-constexpr int kTcTileBytes = 2 * kTcHalfBytes;      // one Q, K or V tile: 32 KB
-constexpr size_t kTcSmem = (size_t)(2 + kTcRing) * kTcTileBytes + 1024;  // + room to align to the swizzle atom
+constexpr int kTcKeys = 64;                         // cache rows per tile
+constexpr int kTcRing = 10;                         // ring entries: one K or V tile each
+constexpr int kTcQHalfBytes = kTcBlockRows * 128;   // 64 dims of a Q tile's 128 rows
+constexpr int kTcQTileBytes = 2 * kTcQHalfBytes;    // 32 KB
+constexpr int kTcHalfBytes = kTcKeys * 128;         // 64 dims of a K / V tile's 64 rows
+constexpr int kTcTileBytes = 2 * kTcHalfBytes;      // 16 KB
+constexpr size_t kTcSmem = (size_t)2 * kTcQTileBytes + (size_t)kTcRing * kTcTileBytes + 1024;  // + alignment room
 constexpr int kTcSoftmaxWarps = 8;
 constexpr int kTcIssuerWarp = 8;                    // warps 8, 9: one issuer per row block
 constexpr int kTcLoadWarp0 = 10;
 constexpr int kTcLoadWarps = 2;                     // twelve warps in all: three per scheduler, 168 registers each
 constexpr int kTcLoadThreads = 32 * kTcLoadWarps;
-constexpr int kTcLoadRows = kTcLoadThreads / 16;    // rows a gather pass covers (16 lanes per row)
+constexpr int kTcLoadRows = kTcLoadThreads / 16;    // rows a cp.async pass covers (16 lanes per row)
 constexpr int kTcThreads = 32 * (kTcLoadWarp0 + kTcLoadWarps);
-constexpr int kTcInflight = 3;                      // ring entries a gather thread keeps in flight
-constexpr uint32_t kColS = 0, kColO = 256, kTcCols = 512;
+constexpr int kTcInflight = 3;                      // cp.async entries a gather thread keeps in flight
+constexpr uint32_t kColBlock = 256, kColO = 128, kTcCols = 512;
+constexpr float kTcRescaleAt = 8.f;                 // log2 units the maximum may run ahead of the exponents' reference
 
 // Shared-memory matrix descriptor, 128-byte swizzle, 8-row atoms of 1024 bytes: [0,14) address >> 4, [16,30)
 // leading byte offset >> 4, [32,46) stride byte offset >> 4, [46,48) version 1, [61,64) layout 2.
@@ -357,20 +120,6 @@ __device__ __forceinline__ void tc_mma_f16_ss(uint32_t tmem_d, uint64_t adesc, u
       : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-
-// The hand-overs between the roles of this kernel are short and on the critical path of every tile: poll the
-// barrier (try_wait comes back as soon as the phase completes) instead of sleeping on a suspend-time hint,
-// which was seen to cost about a microsecond per hand-over.  Bounded like every wait here.
-constexpr uint32_t kTcPollLimit = 1u << 24;
-__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t it = 0; it < kTcPollLimit; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 1023u) == 1023u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
 // Tensor copy (TMA), five coordinates, global -> shared, completion counted in bytes on `bar`.  The innermost
 // coordinate times the element size must be a multiple of 16 bytes (here 0 or 64 bf16).
 __device__ __forceinline__ void tma_load_5d(void* dst_smem, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4,
@@ -380,6 +129,18 @@ __device__ __forceinline__ void tma_load_5d(void* dst_smem, const CUtensorMap* m
       "[%7];" ::"r"(smem_u32(dst_smem)),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar))
       : "memory");
+}
+
+// The hand-overs between the roles of this kernel are short and on the critical path: poll the barrier with
+// test_wait, which never suspends the thread.  Bounded like every wait here.
+constexpr uint32_t kTcPollLimit = 1u << 24;
+__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < kTcPollLimit; ++it) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
 }
 
 struct TcRingPos {
@@ -396,7 +157,7 @@ struct TcRingPos {
 __global__ void __launch_bounds__(kTcThreads, 1)
     tree_attn_tc_kernel(const AttnArgs ka, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t full[kTcRing], empty[kTcRing], s_ready[2], p_ready[2], o_done[2], q_ready;
+  __shared__ __align__(8) uint64_t full[kTcRing], empty[kTcRing], s_ready[2][2], p_ready[2][2], o_done[2][2], q_ready;
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   const subspec_tree_attn_args& a = ka.a;
@@ -431,16 +192,19 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   }
 
   unsigned char* qtiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  unsigned char* ring = qtiles + 2 * kTcTileBytes;
+  unsigned char* ring = qtiles + 2 * kTcQTileBytes;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTcRing; ++s) {
       mbar_init(&full[s], kTcLoadThreads);
       mbar_init(&empty[s], (uint32_t)nblk);  // every row block's issuer lets go of the entry
     }
     for (int k = 0; k < 2; ++k) {
-      mbar_init(&s_ready[k], 1);
-      mbar_init(&p_ready[k], kTcSoftmaxWarps / 2);
-      mbar_init(&o_done[k], 1);
+      mbar_init(&s_ready[k][0], 1);
+      mbar_init(&s_ready[k][1], 1);
+      mbar_init(&p_ready[k][0], kTcSoftmaxWarps / 2);
+      mbar_init(&p_ready[k][1], kTcSoftmaxWarps / 2);
+      mbar_init(&o_done[k][0], 1);
+      mbar_init(&o_done[k][1], 1);
     }
     mbar_init(&q_ready, 32 * kTcSoftmaxWarps);
     mbar_init_fence();
@@ -470,7 +234,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         const unsigned char* src = okr ? qbase + 2 * ((size_t)b * a.q_batch_stride + (size_t)qi * a.q_token_stride +
                                                       (size_t)(kvh * G + qg) * a.q_head_stride)
                                        : qbase;
-        unsigned char* d = qtiles + (size_t)(rr >> 7) * kTcTileBytes + (chunk >> 3) * kTcHalfBytes + (rr & 127) * 128 +
+        unsigned char* d = qtiles + (size_t)(rr >> 7) * kTcQTileBytes + (chunk >> 3) * kTcQHalfBytes + (rr & 127) * 128 +
                            (((chunk & 7) ^ (rr & 7)) << 4);
         cp_async16(d, src, okr ? 16 : 0);
       }
@@ -483,94 +247,114 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     const int row = row0 + (int)threadIdx.x, rg = row / QL, ri = row - rg * QL;
     const bool row_ok = rg < G && ri < nq;
     if (blk < nblk) {
-      const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-      const uint32_t s_addr = lane_base + kColS + (uint32_t)(blk * kTcKeys);
-      const uint32_t o_addr = lane_base + kColO + (uint32_t)(blk * kD);
+      const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)blk * kColBlock;
+      const uint32_t o_addr = lane_base + kColO;
       const uint8_t* mrow = a.mask + (size_t)b * a.mask_batch_stride + (size_t)ri * a.mask_row_stride;
       const float c2 = ka.scale_log2;
-      float m = -INFINITY, l = 0.f;  // running maximum (in the exponent's units) and sum of this row
+      float m = -INFINITY, l = 0.f;  // reference point of the exponents (in their units) and sum of this row
       bool live = true;
       for (int t = 0; t < ntiles; ++t) {
-        // S(t) complete; the MMAs run in order, so the block's O += P V of the tile before is complete too
-        live = __all_sync(0xffffffffu, tc_wait(&s_ready[blk], (uint32_t)t & 1u, abort_flag));
+        const uint32_t s_addr = lane_base + (uint32_t)((t & 1) * kTcKeys);
+        live = __all_sync(0xffffffffu, tc_wait(&s_ready[blk][t & 1], (uint32_t)(t >> 1) & 1u, abort_flag));
         if (!live) break;
         tc_fence_after();
+        uint32_t ra[32], rb[32];
+        tmem_ld32_async(s_addr, ra);
+        tmem_ld32_async(s_addr + 32, rb);
         const int t0 = t * kTcKeys;
         const bool need_mask = t0 + kTcKeys > prefix;  // tiles inside the prefix are visible to every row
-        uint32_t vis[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+        uint32_t vis[2] = {0xffffffffu, 0xffffffffu};
         if (need_mask) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t bits = 0;
+          for (int c = 0; c < 2; ++c) {
+            // all the loads of a chunk first (they are independent: one trip to memory, not thirty-two)
+            uint8_t mb[32];
+#pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int pos = t0 + 32 * c + j;
-              const bool v = pos < prefix || (pos < kv_len && row_ok && mrow[pos] != 0);
-              bits |= (v ? 1u : 0u) << j;
+              mb[j] = (pos >= prefix && pos < kv_len && row_ok) ? mrow[pos] : (uint8_t)0;
+            }
+            uint32_t bits = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int pos = t0 + 32 * c + j;
+              bits |= ((pos < prefix || mb[j] != 0) ? 1u : 0u) << j;
             }
             vis[c] = bits;
           }
         }
-        // ---- pass 1: the row's maximum over the tile (four chains, not one) ----
+        tmem_wait_ld_dep(ra);
+        tmem_wait_ld_dep(rb);
+        // ---- the row's maximum over the tile (four chains, not one) ----
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32_async(s_addr + 32 * c, r);
-          tmem_wait_ld();
-          if (need_mask) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if ((vis[c] >> j) & 1u) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(r[j]));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(r[j]));
+          for (int j = 0; j < 32; ++j) {
+            if ((vis[0] >> j) & 1u) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(ra[j]));
+            if ((vis[1] >> j) & 1u) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(rb[j]));
           }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], fmaxf(__uint_as_float(ra[j]), __uint_as_float(rb[j])));
         }
-        const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        const float m_new = fmaxf(m, tmax * c2);           // c2 > 0: the maximum commutes with the scaling
-        const float u = m_new == -INFINITY ? 0.f : m_new;  // a row with nothing visible yet
-        const float alpha = ex2f(m - u);                   // 0 while m is -inf
-        m = m_new;
+        const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c2;  // c2 > 0: max commutes with scaling
+        // The reference point of the exponents moves only when the row's maximum has grown by more than 2^8
+        // past it: between moves P reaches at most 256, which bf16 and the fp32 sums hold as well as 1, and
+        // the rescaling of O (a pass over tensor memory) becomes rare instead of per tile.
+        float alpha = 1.f;
+        if (tmax > m + kTcRescaleAt || m == -INFINITY) {
+          const float m_new = fmaxf(m, tmax);
+          alpha = ex2f(m - (m_new == -INFINITY ? 0.f : m_new));  // 0 while m is -inf
+          m = m_new;
+        }
+        const float u = m == -INFINITY ? 0.f : m;  // a row with nothing visible yet
         if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          // O += P V of the tile before must have landed before O is rescaled.  The tiles complete on two
+          // barriers in turn, so the phase asked for is unambiguous although most tiles never ask: of this
+          // barrier's tiles all up to t - 3 are known complete (S of this tile was issued behind them) and
+          // none after t - 1 can have been issued.
+          live = __all_sync(0xffffffffu, tc_wait(&o_done[blk][(t - 1) & 1], (uint32_t)((t - 1) >> 1) & 1u, abort_flag));
+          if (!live) break;
+          tc_fence_after();
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld32_async(o_addr + 32 * c, r);
-            tmem_wait_ld();
+            uint32_t rc[32];
+            tmem_ld32_async(o_addr + 32 * c, rc);
+            tmem_wait_ld_dep(rc);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
-            tmem_st32(o_addr + 32 * c, r);
+            for (int j = 0; j < 32; ++j) rc[j] = __float_as_uint(__uint_as_float(rc[j]) * alpha);
+            tmem_st32(o_addr + 32 * c, rc);
           }
         }
-        // ---- pass 2: P = exp2(S c2 - m) over the S columns already read, the row sum ----
+        // ---- P = exp2(S c2 - m) over the first half of the S columns (all read by now), the row sum ----
         float sm[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32_async(s_addr + 32 * c, r);
-          tmem_wait_ld();
+        auto exp_chunk = [&](const uint32_t (&r)[32], uint32_t bits, int c) {
           uint32_t pk[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             float p0 = ex2f(fmaf(__uint_as_float(r[2 * j]), c2, -u));
             float p1 = ex2f(fmaf(__uint_as_float(r[2 * j + 1]), c2, -u));
             if (need_mask) {
-              p0 = ((vis[c] >> (2 * j)) & 1u) ? p0 : 0.f;
-              p1 = ((vis[c] >> (2 * j + 1)) & 1u) ? p1 : 0.f;
+              p0 = ((bits >> (2 * j)) & 1u) ? p0 : 0.f;
+              p1 = ((bits >> (2 * j + 1)) & 1u) ? p1 : 0.f;
             }
             sm[j & 3] += p0 + p1;
             pk[j] = pack_bf16(p0, p1);
           }
-          tmem_st16(s_addr + 16 * c, pk);  // columns [16 c, 16 c + 16) <- keys [32 c, 32 c + 32): behind the reads
-        }
+          tmem_st16(s_addr + 16 * c, pk);  // columns [16 c, 16 c + 16) <- keys [32 c, 32 c + 32)
+        };
+        exp_chunk(ra, vis[0], 0);
+        exp_chunk(rb, vis[1], 1);
         l = l * alpha + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&p_ready[blk]);
+        if (lane == 0) mbar_arrive(&p_ready[blk][t & 1]);
       }
       // ---- the result: O / l ----
-      if (live) live = __all_sync(0xffffffffu, tc_wait(&o_done[blk], (uint32_t)(ntiles - 1) & 1u, abort_flag));
+      if (live)
+        live = __all_sync(0xffffffffu,
+                          tc_wait(&o_done[blk][(ntiles - 1) & 1], (uint32_t)((ntiles - 1) >> 1) & 1u, abort_flag));
       if (live) {
         tc_fence_after();
         const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -580,7 +364,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
           tmem_ld32_async(o_addr + 32 * c, r);
-          tmem_wait_ld();
+          tmem_wait_ld_dep(r);
           if (row_ok) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -598,73 +382,73 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     }
   } else if (warp < kTcLoadWarp0) {
     // ================= MMA issue, one warp per row block: the whole warp runs the loop, one elected lane
-    // issues.  A thread gets a tcgen05.mma out every 150 cycles or so, more than the tensor core needs for a
-    // 128 x 128 x 16 step: two issuing threads keep it busy where one does not. =================
+    // issues (a thread gets a tcgen05.mma out every 50 cycles or so) =================
     const int blk = warp - kTcIssuerWarp;
     if (blk < nblk) {
       constexpr uint32_t idesc_s = tc_idesc(kTcBlockRows, kTcKeys, false);
       constexpr uint32_t idesc_o = tc_idesc(kTcBlockRows, kD, true);
-      const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
-      const uint32_t tm_s = tm + kColS + (uint32_t)(blk * kTcKeys), tm_o = tm + kColO + (uint32_t)(blk * kD);
-      const uint32_t q_u32 = smem_u32(qtiles) + (uint32_t)blk * kTcTileBytes, ring_u32 = smem_u32(ring);
+      const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0) + (uint32_t)blk * kColBlock;
+      const uint32_t q_u32 = smem_u32(qtiles) + (uint32_t)blk * kTcQTileBytes, ring_u32 = smem_u32(ring);
       // S = Q K^T: 8 steps of 16 dims; a step moves 32 bytes inside a 64-dim half, 4 steps per half
-      auto issue_s = [&](int kstage) {
+      auto issue_s = [&](int kstage, int buf) {
         const uint32_t kaddr = ring_u32 + (uint32_t)kstage * kTcTileBytes;
 #pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks) {
-          const uint32_t off = (uint32_t)((ks >> 2) * kTcHalfBytes + (ks & 3) * 32);
-          tc_mma_f16_ss(tm_s, tc_desc(q_u32 + off, 16), tc_desc(kaddr + off, 16), idesc_s, ks > 0 ? 1u : 0u);
-        }
+        for (int ks = 0; ks < kD / 16; ++ks)
+          tc_mma_f16_ss(tm + (uint32_t)(buf * kTcKeys), tc_desc(q_u32 + (uint32_t)((ks >> 2) * kTcQHalfBytes + (ks & 3) * 32), 16),
+                        tc_desc(kaddr + (uint32_t)((ks >> 2) * kTcHalfBytes + (ks & 3) * 32), 16), idesc_s, ks > 0 ? 1u : 0u);
       };
-      // O += P V: 8 steps of 16 cache rows = 2048 bytes of the V tile each; P = the first 64 columns of S
-      auto issue_pv = [&](int vstage, bool first) {
+      // O += P V: 4 steps of 16 cache rows = 2048 bytes of the V tile each; P = the first 32 columns of S
+      auto issue_pv = [&](int vstage, int buf, bool first) {
         const uint32_t vaddr = ring_u32 + (uint32_t)vstage * kTcTileBytes;
 #pragma unroll
         for (int ks = 0; ks < kTcKeys / 16; ++ks)
-          tc_mma_f16_ta(tm_o, tm_s + (uint32_t)(8 * ks), tc_desc(vaddr + (uint32_t)(ks * 2048), kTcHalfBytes), idesc_o,
-                        (!first || ks > 0) ? 1u : 0u);
+          tc_mma_f16_ta(tm + kColO, tm + (uint32_t)(buf * kTcKeys + 8 * ks), tc_desc(vaddr + (uint32_t)(ks * 2048), kTcHalfBytes),
+                        idesc_o, (!first || ks > 0) ? 1u : 0u);
       };
-      TcRingPos pos;  // ring entries in the order they are consumed: K(0), V(0), K(1), V(1), ...
+      TcRingPos pos;  // ring entries in the order they are consumed: K(0), K(1), V(0), K(2), V(1), ...
       bool ok = __all_sync(0xffffffffu, tc_wait(&q_ready, 0, abort_flag));
-      ok = ok && __all_sync(0xffffffffu, tc_wait(&full[pos.s], pos.ph, abort_flag));
-      if (ok) {
+      for (int t = 0; t < min(ntiles, 2) && ok; ++t) {
+        ok = __all_sync(0xffffffffu, tc_wait(&full[pos.s], pos.ph, abort_flag));
+        if (!ok) break;
         tc_fence_after();
         if (elect_one()) {
-          issue_s(pos.s);
-          tc_commit(&s_ready[blk]);
+          issue_s(pos.s, t);
+          tc_commit(&s_ready[blk][t]);
           tc_commit(&empty[pos.s]);
         }
         __syncwarp();
         pos.next();
-        for (int t = 0; t < ntiles; ++t) {
-          // O += P V(t), then S of the next tile over the P just consumed: the MMAs of a thread run in order
-          ok = __all_sync(0xffffffffu, tc_wait(&full[pos.s], pos.ph, abort_flag)) &&
-               __all_sync(0xffffffffu, tc_wait(&p_ready[blk], (uint32_t)t & 1u, abort_flag));
+      }
+      for (int t = 0; t < ntiles && ok; ++t) {
+        // O += P V(t), then S(t + 2) over the P just consumed: the MMAs of a thread run in order.  (The softmax
+        // may be a tile ahead of this loop, hence two P barriers in turn, like the S and O ones.)
+        ok = __all_sync(0xffffffffu, tc_wait(&full[pos.s], pos.ph, abort_flag)) &&
+             __all_sync(0xffffffffu, tc_wait(&p_ready[blk][t & 1], (uint32_t)(t >> 1) & 1u, abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+        if (elect_one()) {
+          issue_pv(pos.s, t & 1, t == 0);
+          tc_commit(&o_done[blk][t & 1]);
+          tc_commit(&empty[pos.s]);
+        }
+        __syncwarp();
+        pos.next();
+        if (t + 2 < ntiles) {
+          ok = __all_sync(0xffffffffu, tc_wait(&full[pos.s], pos.ph, abort_flag));
           if (!ok) break;
           tc_fence_after();
           if (elect_one()) {
-            issue_pv(pos.s, t == 0);
-            tc_commit(&o_done[blk]);
+            issue_s(pos.s, t & 1);
+            tc_commit(&s_ready[blk][t & 1]);
             tc_commit(&empty[pos.s]);
           }
           __syncwarp();
           pos.next();
-          if (t + 1 < ntiles) {
-            if (!__all_sync(0xffffffffu, tc_wait(&full[pos.s], pos.ph, abort_flag))) break;
-            tc_fence_after();
-            if (elect_one()) {
-              issue_s(pos.s);
-              tc_commit(&s_ready[blk]);
-              tc_commit(&empty[pos.s]);
-            }
-            __syncwarp();
-            pos.next();
-          }
         }
       }
     }
   } else {
-    // ================= gather: 16 lanes per row (its 16 chunks of 16 bytes), 4 rows per pass =================
+    // ================= gather =================
     const int p = (int)threadIdx.x - 32 * kTcLoadWarp0;
     const int chunk = p & 15, sub = p >> 4;
     const uint32_t dst_half = (uint32_t)((chunk >> 3) * kTcHalfBytes);
@@ -675,41 +459,53 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     const int* table = a.page_table + (size_t)b * a.pages_per_seq;
     TcRingPos wr, done;
     int pending = 0;  // cp.async entries committed and not yet handed over
-    const int nent = 2 * ntiles;
-    for (int n = 0; n < nent; ++n) {
-      if (n >= kTcRing && !tc_wait(&empty[wr.s], wr.ph ^ 1u, abort_flag)) break;
-      const int t = n >> 1, t0 = t * kTcKeys;
+    int n = 0;        // entries so far
+    bool live = true;
+    // one ring entry: the K (is_v = 0) or V (1) rows of tile t
+    // The page a thread's tensor copy of tile t reads (thread p: page slot p / 2 of the tile, half p % 2), looked
+    // up a tile ahead of its first use: the look-up is a trip to memory, and the copies of an entry must not
+    // wait for one each.  -1: no copy by this thread for that tile.
+    const int tj = p >> 1, thalf = p & 1;
+    auto page_of = [&](int t) -> int {
+      const int kpos = t * kTcKeys + tj * ka.box_rows;
+      if (ka.box_rows <= 0 || tj * ka.box_rows >= kTcKeys || (t + 1) * kTcKeys > kv_len) return -1;
+      return table[ka.page_shift >= 0 ? kpos >> ka.page_shift : kpos / a.page_len];
+    };
+    auto produce = [&](int is_v, int t, int page) {
+      if (!live) return;
+      if (n >= kTcRing && !tc_wait(&empty[wr.s], wr.ph ^ 1u, abort_flag)) {
+        live = false;
+        return;
+      }
+      ++n;
+      const int t0 = t * kTcKeys;
       if (ka.box_rows > 0 && t0 + kTcKeys <= kv_len) {
-        // A whole tile of whole pages: tensor copies (TMA) of box_rows cache rows x 64 dims each, which the copy
-        // unit lays out in the swizzled form itself.  One thread announces the bytes, the others just arrive;
-        // the first 2 * (128 / box_rows) threads issue one copy each.
+        // A whole tile of whole pages: one thread announces the bytes, the others just arrive; the first
+        // 2 * (64 / box_rows) threads issue one tensor copy each (a page's rows x 64 dims).
         if (p == 0)
           mbar_expect_tx(&full[wr.s], (uint32_t)kTcTileBytes);
         else
           mbar_arrive(&full[wr.s]);
-        const int j = p >> 1, half = p & 1;
-        if (j * ka.box_rows < kTcKeys) {
-          const int kpos = t0 + j * ka.box_rows;
+        if (tj * ka.box_rows < kTcKeys) {
+          const int kpos = t0 + tj * ka.box_rows;
           const int pi = ka.page_shift >= 0 ? kpos >> ka.page_shift : kpos / a.page_len;
-          int page = table[pi];
           if (page < 0 || page >= a.num_pages) {
             flag(a.dev_status, SUBSPEC_DEV_BAD_PAGE);
             page = a.num_pages;  // outside the tensor: the copy unit fills zeros and touches no memory
           }
-          tma_load_5d(ring + (size_t)wr.s * kTcTileBytes + half * kTcHalfBytes + (size_t)j * ka.box_rows * 128, &tmap,
-                      half * 64, kvh, kpos - pi * a.page_len, n & 1, page, &full[wr.s]);
+          tma_load_5d(ring + (size_t)wr.s * kTcTileBytes + thalf * kTcHalfBytes + (size_t)tj * ka.box_rows * 128, &tmap,
+                      thalf * 64, kvh, kpos - pi * a.page_len, is_v, page, &full[wr.s]);
         }
         wr.next();
         done = wr;
-        continue;
+        return;
       }
-      // The last, partial tile (or a page length the tensor copies do not cover): 16-byte copies, row by row
-      const size_t plane_off = (n & 1) ? kv_plane : 0;
+      // The last, partial tile (or a page length the tensor copies do not suit): 16-byte copies, row by row
+      const size_t plane_off = is_v ? kv_plane : 0;
       unsigned char* dst = ring + (size_t)wr.s * kTcTileBytes + dst_half;
 #pragma unroll 4
-      for (int pass = 0; pass < (kTcKeys + kTcLoadRows - 1) / kTcLoadRows; ++pass) {
+      for (int pass = 0; pass < kTcKeys / kTcLoadRows; ++pass) {
         const int rr = pass * kTcLoadRows + sub;
-        if (rr >= kTcKeys) break;
         const int kpos = t0 + rr;
         const unsigned char* src = pool;
         int bytes = 0;
@@ -727,6 +523,14 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         cp_async16(dst + rr * 128 + (((chunk & 7) ^ (rr & 7)) << 4), src, bytes);  // rows past the end: zeros
       }
       cp_async_commit();
+      if (ka.box_rows > 0) {  // a lone entry among tensor copies: hand it over as soon as it has landed
+        cp_async_wait<0>();
+        fence_async_smem();
+        mbar_arrive(&full[wr.s]);
+        wr.next();
+        done = wr;
+        return;
+      }
       wr.next();
       if (++pending == kTcInflight) {  // the oldest entry in flight has landed: hand it to the tensor core's proxy
         cp_async_wait<kTcInflight - 1>();
@@ -735,6 +539,17 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         done.next();
         --pending;
       }
+    };
+    int pg0 = page_of(0), pg1 = page_of(1), pg2 = page_of(2);  // tiles t, t + 1, t + 2 of the loop below
+    produce(0, 0, pg0);
+    if (ntiles > 1) produce(0, 1, pg1);
+    for (int t = 0; t < ntiles; ++t) {
+      const int pg3 = page_of(t + 3);  // asked for now, used an iteration later
+      produce(1, t, pg0);
+      if (t + 2 < ntiles) produce(0, t + 2, pg2);
+      pg0 = pg1;
+      pg1 = pg2;
+      pg2 = pg3;
     }
     cp_async_wait<0>();
     fence_async_smem();
@@ -827,15 +642,6 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
   for (int sft = 0; sft < 31; ++sft)
     if ((1 << sft) == a.page_len) ka.page_shift = sft;
   const cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (getenv("SUBSPEC_ATTN_MMA_SYNC")) {
-    int rc = cuda_check(
-        cudaFuncSetAttribute(tree_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem));
-    if (rc) return rc;
-    const dim3 grid((unsigned)((ka.group * a.q_len + kRowsPerCta - 1) / kRowsPerCta), (unsigned)a.num_kv_heads,
-                    (unsigned)a.batch);
-    tree_attn_kernel<<<grid, kAttnThreads, kAttnSmem, st>>>(ka);
-    return cuda_check(cudaGetLastError());
-  }
   const int rc =
       cuda_check(cudaFuncSetAttribute(tree_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
   if (rc) return rc;

@@ -80,6 +80,29 @@ def test_single_kv_head_and_one_token(cuda_lib):
     _run_and_check(c)
 
 
+@pytest.mark.parametrize("page_len", [4, 8, 24, 32, 64, 128, 192])
+def test_page_lengths(cuda_lib, page_len):
+    """Pages that tile the 64-row tiles of the kernel (8, 32, 64), pages that hold whole tiles (128, 192: tensor
+    copies of 64 rows at an offset inside the page) and pages that do neither (4, 24: the row-by-row copies);
+    prefixes that end on a tile boundary, one row before and one row after it; more than 128 query rows per KV
+    head in one request (two row blocks) and fewer (one)."""
+    c = _case(10 + page_len, B=3, QL=40, HQ=8, HKV=2, prefix_lens=[600, 64 * 5 - 1 - 40, 64 * 7 + 1 - 40],
+              n_qs=[40, 40, 40], page_len=page_len)
+    c["kv_len"] = [p + n for p, n in zip(c["prefix"], c["n_q"])]
+    _run_and_check(c)
+    c = _case(20 + page_len, B=2, QL=16, HQ=4, HKV=4, prefix_lens=[64 * 3 - 16, 1], n_qs=[16, 5], page_len=page_len)
+    _run_and_check(c)
+
+
+def test_long_stream_and_peaked_rows(cuda_lib):
+    """A few thousand cache rows behind one request (the ring of tiles goes round many times), and queries
+    scaled so that single keys dominate rows: the running maximum moves by far more than the margin the
+    rescaling of the accumulator allows itself, many times."""
+    c = _case(5, B=1, QL=48, HQ=6, HKV=2, prefix_lens=[5000], n_qs=[48], page_len=16, layers=1, layer=0)
+    c["q"] = (c["q"].float() * 6).to(torch.bfloat16)
+    _run_and_check(c, tol=3e-2)
+
+
 def test_benchmark_shape(cuda_lib):
     """One request of the sharded-step workload: a 64-node tree behind 4032 cached rows (4096 in all, page 16),
     28 query heads on 4 KV heads; linearity in V as a size-independent check beside the oracle."""
