@@ -222,22 +222,18 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 
   if (warp < kTcSoftmaxWarps) {
     // ================= softmax: thread = query row = tensor-memory lane =================
-    {  // the two Q tiles, gathered by all the softmax threads (16 lanes per row, 16 rows per pass): rows that
-       // do not exist are zeros
-      const int chunk = (int)threadIdx.x & 15, sub = (int)threadIdx.x >> 4;
-      const unsigned char* qbase = reinterpret_cast<const unsigned char*>(a.q) + chunk * 16;
-#pragma unroll 4
-      for (int pass = 0; pass < kTcRows / 16; ++pass) {
-        const int rr = pass * 16 + sub;  // row of the CTA; its block = rr / 128
-        const int qrow = row0 + rr, qg = qrow / QL, qi = qrow - qg * QL;
-        const bool okr = qg < G && qi < nq;
-        const unsigned char* src = okr ? qbase + 2 * ((size_t)b * a.q_batch_stride + (size_t)qi * a.q_token_stride +
-                                                      (size_t)(kvh * G + qg) * a.q_head_stride)
-                                       : qbase;
-        unsigned char* d = qtiles + (size_t)(rr >> 7) * kTcQTileBytes + (chunk >> 3) * kTcQHalfBytes + (rr & 127) * 128 +
-                           (((chunk & 7) ^ (rr & 7)) << 4);
-        cp_async16(d, src, okr ? 16 : 0);
-      }
+    {  // the two Q tiles: every softmax thread brings its own row (16 copies of 16 bytes; a row that does not
+       // exist: zeros)
+      const int rr = (int)threadIdx.x;  // row of the CTA; its block = rr / 128
+      const int qrow = row0 + rr, qg = qrow / QL, qi = qrow - qg * QL;
+      const bool okr = qg < G && qi < nq;
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(a.q);
+      if (okr)
+        src += 2 * ((size_t)b * a.q_batch_stride + (size_t)qi * a.q_token_stride + (size_t)(kvh * G + qg) * a.q_head_stride);
+      unsigned char* d = qtiles + (size_t)(rr >> 7) * kTcQTileBytes + (rr & 127) * 128;
+#pragma unroll
+      for (int chunk = 0; chunk < 16; ++chunk)
+        cp_async16(d + (chunk >> 3) * kTcQHalfBytes + (((chunk & 7) ^ (rr & 7)) << 4), src + chunk * 16, okr ? 16 : 0);
       cp_async_commit();
       cp_async_wait<0>();
       fence_async_smem();
@@ -267,12 +263,22 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
-            // all the loads of a chunk first (they are independent: one trip to memory, not thirty-two)
+            // all the loads of a chunk first (they are independent: one trip to memory, not thirty-two), sixteen
+            // bytes at a time where that stays inside the row's columns and is aligned
             uint8_t mb[32];
+            const int p0 = t0 + 32 * c;
+            if (row_ok && p0 + 32 <= kv_len && ((reinterpret_cast<uintptr_t>(mrow + p0) & 15u) == 0)) {
+              const uint4 lo = *reinterpret_cast<const uint4*>(mrow + p0);
+              const uint4 hi = *reinterpret_cast<const uint4*>(mrow + p0 + 16);
+              const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int pos = t0 + 32 * c + j;
-              mb[j] = (pos >= prefix && pos < kv_len && row_ok) ? mrow[pos] : (uint8_t)0;
+              for (int j = 0; j < 32; ++j) mb[j] = (uint8_t)(w[j >> 2] >> (8 * (j & 3)));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int pos = p0 + j;
+                mb[j] = (pos >= prefix && pos < kv_len && row_ok) ? mrow[pos] : (uint8_t)0;
+              }
             }
             uint32_t bits = 0;
 #pragma unroll
