@@ -60,7 +60,7 @@ struct AttnArgs {
 //               layout and the gather never transposes.  A block has two S buffers: S of tile t + 1 is computed
 //               while the softmax works on tile t, and S of tile t + 2 goes over the P of tile t as soon as
 //               O += P V of tile t has been issued (the MMAs of a thread run in order).
-//   warps 10,11 gather.  Whole tiles of whole pages come by tensor copies (TMA) of 64 dims x the page's rows,
+//   warps 10,11 gather, the two warps taking the ring entries in turn.  Whole tiles of whole pages come by tensor copies (TMA) of 64 dims x the page's rows,
 //               which the copy unit lays out in the 128-byte-swizzled form the tensor core reads: a tile = two
 //               halves of 64 dims, a half = 64 rows of 128 bytes, 16-byte chunk c of row r stored at chunk
 //               c ^ (r & 7).  The last, partial tile (and page lengths the tensor copies do not suit) comes by
@@ -82,10 +82,8 @@ constexpr int kTcSoftmaxWarps = 8;
 constexpr int kTcIssuerWarp = 8;                    // warps 8, 9: one issuer per row block
 constexpr int kTcLoadWarp0 = 10;
 constexpr int kTcLoadWarps = 2;                     // twelve warps in all: three per scheduler, 168 registers each
-constexpr int kTcLoadThreads = 32 * kTcLoadWarps;
-constexpr int kTcLoadRows = kTcLoadThreads / 16;    // rows a cp.async pass covers (16 lanes per row)
 constexpr int kTcThreads = 32 * (kTcLoadWarp0 + kTcLoadWarps);
-constexpr int kTcInflight = 3;                      // cp.async entries a gather thread keeps in flight
+constexpr int kTcInflight = 3;                      // row-by-row entries a gather warp keeps in flight
 constexpr uint32_t kColBlock = 256, kColO = 128, kTcCols = 512;
 constexpr float kTcRescaleAt = 8.f;                 // log2 units the maximum may run ahead of the exponents' reference
 
@@ -195,7 +193,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   unsigned char* ring = qtiles + 2 * kTcQTileBytes;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTcRing; ++s) {
-      mbar_init(&full[s], kTcLoadThreads);
+      mbar_init(&full[s], 1);  // the producing warp's one arrival (plus the bytes of its tensor copies)
       mbar_init(&empty[s], (uint32_t)nblk);  // every row block's issuer lets go of the entry
     }
     for (int k = 0; k < 2; ++k) {
@@ -454,96 +452,108 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       }
     }
   } else {
-    // ================= gather =================
-    const int p = (int)threadIdx.x - 32 * kTcLoadWarp0;
-    const int chunk = p & 15, sub = p >> 4;
+    // ================= gather: the two warps take the ring entries in turn =================
+    const int gw = warp - kTcLoadWarp0;
+    const int chunk = lane & 15, sub = lane >> 4;  // row-by-row copies: 16 lanes per row, two rows per pass
     const uint32_t dst_half = (uint32_t)((chunk >> 3) * kTcHalfBytes);
     const size_t row_bytes = (size_t)a.num_kv_heads * kD * 2;   // one cache row, all KV heads
     const size_t kv_plane = (size_t)a.page_len * row_bytes;     // K (or V) of one page
     const unsigned char* pool = reinterpret_cast<const unsigned char*>(a.pool) +
                                 (size_t)a.layer * a.num_pages * 2 * kv_plane + (size_t)kvh * kD * 2 + chunk * 16;
     const int* table = a.page_table + (size_t)b * a.pages_per_seq;
-    TcRingPos wr, done;
-    int pending = 0;  // cp.async entries committed and not yet handed over
-    int n = 0;        // entries so far
+    TcRingPos wr;            // the entry about to be produced (by this warp or the other)
+    TcRingPos q0, q1, q2;    // this warp's row-by-row entries committed and not yet handed over, oldest first
+    int pending = 0;
+    int n = 0;               // entries so far
     bool live = true;
-    // one ring entry: the K (is_v = 0) or V (1) rows of tile t
-    // The page a thread's tensor copy of tile t reads (thread p: page slot p / 2 of the tile, half p % 2), looked
-    // up a tile ahead of its first use: the look-up is a trip to memory, and the copies of an entry must not
-    // wait for one each.  -1: no copy by this thread for that tile.
-    const int tj = p >> 1, thalf = p & 1;
+    // The page a lane's tensor copy of tile t reads (lane l: page slot l / 2 of the tile, half l % 2), looked up
+    // a tile ahead of its first use: the look-up is a trip to memory, and the copies of an entry must not wait
+    // for one each.  -1: no copy by this lane for that tile.
+    const int tj = lane >> 1, thalf = lane & 1;
+    const bool tma_lane = ka.box_rows > 0 && tj * ka.box_rows < kTcKeys;
     auto page_of = [&](int t) -> int {
       const int kpos = t * kTcKeys + tj * ka.box_rows;
-      if (ka.box_rows <= 0 || tj * ka.box_rows >= kTcKeys || (t + 1) * kTcKeys > kv_len) return -1;
+      if (!tma_lane || (t + 1) * kTcKeys > kv_len) return -1;
       return table[ka.page_shift >= 0 ? kpos >> ka.page_shift : kpos / a.page_len];
     };
+    auto hand_over_oldest = [&]() {
+      if (lane == 0) mbar_arrive(&full[q0.s]);
+      q0 = q1;
+      q1 = q2;
+      --pending;
+    };
+    // one ring entry: the K (is_v = 0) or V (1) rows of tile t
     auto produce = [&](int is_v, int t, int page) {
       if (!live) return;
-      if (n >= kTcRing && !tc_wait(&empty[wr.s], wr.ph ^ 1u, abort_flag)) {
+      const bool mine = (n & 1) == gw;
+      if (mine && n >= kTcRing && !tc_wait(&empty[wr.s], wr.ph ^ 1u, abort_flag)) {
         live = false;
         return;
       }
       ++n;
+      const TcRingPos at = wr;
+      wr.next();
+      if (!mine) return;
       const int t0 = t * kTcKeys;
       if (ka.box_rows > 0 && t0 + kTcKeys <= kv_len) {
-        // A whole tile of whole pages: one thread announces the bytes, the others just arrive; the first
-        // 2 * (64 / box_rows) threads issue one tensor copy each (a page's rows x 64 dims).
-        if (p == 0)
-          mbar_expect_tx(&full[wr.s], (uint32_t)kTcTileBytes);
-        else
-          mbar_arrive(&full[wr.s]);
-        if (tj * ka.box_rows < kTcKeys) {
+        // A whole tile of whole pages: lane 0 announces the bytes (the entry's one arrival); the first
+        // 2 * (64 / box_rows) lanes issue one tensor copy each (a page's rows x 64 dims).
+        if (lane == 0) mbar_expect_tx(&full[at.s], (uint32_t)kTcTileBytes);
+        __syncwarp();
+        if (tma_lane) {
           const int kpos = t0 + tj * ka.box_rows;
           const int pi = ka.page_shift >= 0 ? kpos >> ka.page_shift : kpos / a.page_len;
           if (page < 0 || page >= a.num_pages) {
             flag(a.dev_status, SUBSPEC_DEV_BAD_PAGE);
             page = a.num_pages;  // outside the tensor: the copy unit fills zeros and touches no memory
           }
-          tma_load_5d(ring + (size_t)wr.s * kTcTileBytes + thalf * kTcHalfBytes + (size_t)tj * ka.box_rows * 128, &tmap,
-                      thalf * 64, kvh, kpos - pi * a.page_len, is_v, page, &full[wr.s]);
+          tma_load_5d(ring + (size_t)at.s * kTcTileBytes + thalf * kTcHalfBytes + (size_t)tj * ka.box_rows * 128, &tmap,
+                      thalf * 64, kvh, kpos - pi * a.page_len, is_v, page, &full[at.s]);
         }
-        wr.next();
-        done = wr;
         return;
       }
       // The last, partial tile (or a page length the tensor copies do not suit): 16-byte copies, row by row
       const size_t plane_off = is_v ? kv_plane : 0;
-      unsigned char* dst = ring + (size_t)wr.s * kTcTileBytes + dst_half;
+      unsigned char* dst = ring + (size_t)at.s * kTcTileBytes + dst_half;
 #pragma unroll 4
-      for (int pass = 0; pass < kTcKeys / kTcLoadRows; ++pass) {
-        const int rr = pass * kTcLoadRows + sub;
+      for (int pass = 0; pass < kTcKeys / 2; ++pass) {
+        const int rr = pass * 2 + sub;
         const int kpos = t0 + rr;
         const unsigned char* src = pool;
         int bytes = 0;
         if (kpos < kv_len) {
           const int pi = ka.page_shift >= 0 ? kpos >> ka.page_shift : kpos / a.page_len;
-          int page = table[pi];
-          if (page < 0 || page >= a.num_pages) {
+          int pg = table[pi];
+          if (pg < 0 || pg >= a.num_pages) {
             flag(a.dev_status, SUBSPEC_DEV_BAD_PAGE);
-            page = 0;
+            pg = 0;
           } else {
             bytes = 16;
           }
-          src = pool + (size_t)page * 2 * kv_plane + plane_off + (size_t)(kpos - pi * a.page_len) * row_bytes;
+          src = pool + (size_t)pg * 2 * kv_plane + plane_off + (size_t)(kpos - pi * a.page_len) * row_bytes;
         }
         cp_async16(dst + rr * 128 + (((chunk & 7) ^ (rr & 7)) << 4), src, bytes);  // rows past the end: zeros
       }
       cp_async_commit();
-      if (ka.box_rows > 0) {  // a lone entry among tensor copies: hand it over as soon as it has landed
+      if (pending == 0)
+        q0 = at;
+      else if (pending == 1)
+        q1 = at;
+      else
+        q2 = at;
+      ++pending;
+      // among tensor copies a row-by-row entry is handed over as soon as it has landed; among its like, when
+      // kTcInflight of this warp's are in flight the oldest has landed
+      if (ka.box_rows > 0) {
         cp_async_wait<0>();
         fence_async_smem();
-        mbar_arrive(&full[wr.s]);
-        wr.next();
-        done = wr;
-        return;
-      }
-      wr.next();
-      if (++pending == kTcInflight) {  // the oldest entry in flight has landed: hand it to the tensor core's proxy
+        __syncwarp();
+        hand_over_oldest();
+      } else if (pending == kTcInflight) {
         cp_async_wait<kTcInflight - 1>();
         fence_async_smem();
-        mbar_arrive(&full[done.s]);
-        done.next();
-        --pending;
+        __syncwarp();
+        hand_over_oldest();
       }
     };
     int pg0 = page_of(0), pg1 = page_of(1), pg2 = page_of(2);  // tiles t, t + 1, t + 2 of the loop below
@@ -559,10 +569,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     }
     cp_async_wait<0>();
     fence_async_smem();
-    for (; pending > 0; --pending) {
-      mbar_arrive(&full[done.s]);
-      done.next();
-    }
+    __syncwarp();
+    while (pending > 0) hand_over_oldest();
   }
   __syncthreads();
   if (s_abort && threadIdx.x == 0) flag(a.dev_status, SUBSPEC_DEV_TIMEOUT);
