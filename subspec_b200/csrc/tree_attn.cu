@@ -12,6 +12,8 @@
 // it starts.
 #include <math.h>
 
+#include <type_traits>
+
 #include <cuda.h>
 #include <string.h>
 
@@ -331,24 +333,36 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           }
         }
         // ---- P = exp2(S c2 - m) over the first half of the S columns (all read by now), the row sum ----
-        float sm[4] = {0.f, 0.f, 0.f, 0.f};
-        auto exp_chunk = [&](const uint32_t (&r)[32], uint32_t bits, int c) {
+        // (two copies of the loop, with and without the mask: inside the prefix no instruction is spent on it;
+        //  scaling and sums two floats at a time)
+        uint64_t sm2[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
+        const uint64_t c2p = f2_pack(c2, c2), nup = f2_pack(-u, -u);
+        auto exp_chunk = [&](auto masked, const uint32_t (&r)[32], uint32_t bits, int c) {
           uint32_t pk[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            float p0 = ex2f(fmaf(__uint_as_float(r[2 * j]), c2, -u));
-            float p1 = ex2f(fmaf(__uint_as_float(r[2 * j + 1]), c2, -u));
-            if (need_mask) {
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), c2p, nup), x0, x1);
+            float p0 = ex2f(x0), p1 = ex2f(x1);
+            if (decltype(masked)::value) {
               p0 = ((bits >> (2 * j)) & 1u) ? p0 : 0.f;
               p1 = ((bits >> (2 * j + 1)) & 1u) ? p1 : 0.f;
             }
-            sm[j & 3] += p0 + p1;
+            sm2[j & 1] = f2_add(sm2[j & 1], f2_pack(p0, p1));
             pk[j] = pack_bf16(p0, p1);
           }
           tmem_st16(s_addr + 16 * c, pk);  // columns [16 c, 16 c + 16) <- keys [32 c, 32 c + 32)
         };
-        exp_chunk(ra, vis[0], 0);
-        exp_chunk(rb, vis[1], 1);
+        if (need_mask) {
+          exp_chunk(std::true_type{}, ra, vis[0], 0);
+          exp_chunk(std::true_type{}, rb, vis[1], 1);
+        } else {
+          exp_chunk(std::false_type{}, ra, 0u, 0);
+          exp_chunk(std::false_type{}, rb, 0u, 1);
+        }
+        float sm[4];
+        f2_unpack(sm2[0], sm[0], sm[1]);
+        f2_unpack(sm2[1], sm[2], sm[3]);
         l = l * alpha + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
         tmem_wait_st();
         tc_fence_before();
