@@ -41,6 +41,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// 2^x for a pair of exponents without the special-function unit: x = n + f with n = round(x), f in [-0.5, 0.5];
+// 2^f by a cubic (relative error below 8e-5, a twenty-fifth of what rounding P to bf16 costs), n added into
+// the exponent field.  The magic constant 1.5 * 2^23 leaves n in the low mantissa bits of x + magic.
+__device__ __forceinline__ void exp2_pair_fma(float x0, float x1, float& p0, float& p1) {
+  const uint64_t xc = f2_pack(fmaxf(x0, -125.f), fmaxf(x1, -125.f));  // -inf (masked away later) and underflow
+  const uint64_t magic = f2_pack(12582912.f, 12582912.f), nmagic = f2_pack(-12582912.f, -12582912.f);
+  const uint64_t t2 = f2_add(xc, magic);
+  const uint64_t n2 = f2_add(t2, nmagic);
+  const uint64_t f2 = f2_fma(n2, f2_pack(-1.f, -1.f), xc);
+  uint64_t q = f2_fma(f2_pack(0.0551716685f, 0.0551716685f), f2, f2_pack(0.242611125f, 0.242611125f));
+  q = f2_fma(q, f2, f2_pack(0.693260968f, 0.693260968f));
+  q = f2_fma(q, f2, f2_pack(0.999928057f, 0.999928057f));
+  float q0, q1, t0, t1;
+  f2_unpack(q, q0, q1);
+  f2_unpack(t2, t0, t1);
+  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
+}
+
 struct AttnArgs {
   subspec_tree_attn_args a;
   int group;        // query heads per KV head
@@ -62,8 +81,10 @@ struct AttnArgs {
 //               layout and the gather never transposes.  A block has two S buffers: S of tile t + 1 is computed
 //               while the softmax works on tile t, and S of tile t + 2 goes over the P of tile t as soon as
 //               O += P V of tile t has been issued (the MMAs of a thread run in order).
-//   warps 10,11 gather, the two warps taking the ring entries in turn.  Whole tiles of whole pages come by tensor copies (TMA) of 64 dims x the page's rows,
-//               which the copy unit lays out in the 128-byte-swizzled form the tensor core reads: a tile = two
+//   warps 10,11 gather, the two warps taking the ring entries in turn (a tensor copy costs its issuing warp
+//               about 75 cycles whatever its size: one warp issuing them all was the bound of the kernel).
+//               Whole tiles of whole pages come by tensor copies (TMA) of 64 dims x the page's rows, which
+//               the copy unit lays out in the 128-byte-swizzled form the tensor core reads: a tile = two
 //               halves of 64 dims, a half = 64 rows of 128 bytes, 16-byte chunk c of row r stored at chunk
 //               c ^ (r & 7).  The last, partial tile (and page lengths the tensor copies do not suit) comes by
 //               16-byte cp.async copies, row by row, into the same layout, rows past the end as zeros.  The
@@ -343,7 +364,14 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           for (int j = 0; j < 16; ++j) {
             float x0, x1;
             f2_unpack(f2_fma(f2_pack(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), c2p, nup), x0, x1);
-            float p0 = ex2f(x0), p1 = ex2f(x1);
+            float p0, p1;
+            if ((j & 3) == 3 || (j & 7) == 1) {
+              exp2_pair_fma(x0, x1, p0, p1);  // three pairs in eight on the FMA pipe: the special-function unit's
+                                               // queue is what the warps of this role stall on most
+            } else {
+              p0 = ex2f(x0);
+              p1 = ex2f(x1);
+            }
             if (decltype(masked)::value) {
               p0 = ((bits >> (2 * j)) & 1u) ? p0 : 0.f;
               p1 = ((bits >> (2 * j + 1)) & 1u) ? p1 : 0.f;
