@@ -59,8 +59,9 @@ def append_paged_kv(pool: torch.Tensor, layer: int, k: torch.Tensor, v: torch.Te
 def tree_attention_paged(q: torch.Tensor, pool: torch.Tensor, layer: int, *, page_table: torch.Tensor,
                          kv_len: torch.Tensor, mask: torch.Tensor, n_q: Optional[torch.Tensor] = None,
                          prefix_len: Optional[torch.Tensor] = None, sm_scale: Optional[float] = None,
-                         status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """q [batch, q_len, q_heads, 128] bf16 -> attention output of the same shape.
+                         status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [batch, q_len, q_heads, 128] bf16 -> attention output of the same shape (into `out` when given: a
+    captured graph needs a buffer that outlives the capture).
 
     `mask` is bool / uint8 [batch, q_len, cols >= kv_len] (a leading singleton head axis is accepted): row i of
     request b marks the cache rows its query i may read; rows below `prefix_len[b]` (default kv_len - n_q) are
@@ -78,7 +79,10 @@ def tree_attention_paged(q: torch.Tensor, pool: torch.Tensor, layer: int, *, pag
         raise ValueError("mask must be bool / uint8 [batch, q_len, cols] with contiguous columns")
     if page_table.dtype != torch.int32 or page_table.dim() != 2 or not page_table.is_contiguous():
         raise ValueError("page_table must be a contiguous int32 [batch, pages_per_seq] tensor")
-    out = torch.empty_like(q)
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.dtype != q.dtype or out.shape != q.shape or out.device != q.device or out.stride(3) != 1:
+        raise ValueError("out must be a bf16 tensor of q's shape on q's device with contiguous head_dim")
     a = _lib.TreeAttnArgs()
     a.struct_size = C.sizeof(_lib.TreeAttnArgs)
     a.batch, a.q_len, a.num_q_heads, a.num_kv_heads, a.head_dim = B, QL, HQ, int(H), int(D)

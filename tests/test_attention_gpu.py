@@ -118,3 +118,37 @@ def test_benchmark_shape(cuda_lib):
     with pytest.raises(ValueError):
         tree_attention_paged(c["q"].to(dev)[..., :64].contiguous(), pool, 0, page_table=table, kv_len=kv_len,
                              mask=c["mask"].to(dev))
+
+
+def test_inside_a_cuda_graph(cuda_lib):
+    """Append + attention captured once and replayed on new queries and a longer cache: the kernel reads the
+    lengths, the page table and the mask from device memory at run time, and the tensor map of the pool is a
+    launch parameter that the capture keeps."""
+    c = _case(6, B=2, QL=32, HQ=8, HKV=2, prefix_lens=[700, 130], n_qs=[32, 32])
+    dev = "cuda"
+    pool, table = c["pool"].to(dev), c["table"].to(dev)
+    kv_len = torch.tensor(c["kv_len"], dtype=torch.int32, device=dev)
+    q, k, v, mask = (c[n].to(dev) for n in ("q", "k", "v", "mask"))
+    out = torch.empty_like(q)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):  # warm-up outside the capture (function attributes, the driver entry point)
+            append_paged_kv(pool, c["layer"], k, v, page_table=table, kv_len=kv_len)
+            tree_attention_paged(q, pool, c["layer"], page_table=table, kv_len=kv_len, mask=mask, out=out)
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        append_paged_kv(pool, c["layer"], k, v, page_table=table, kv_len=kv_len)
+        tree_attention_paged(q, pool, c["layer"], page_table=table, kv_len=kv_len, mask=mask, out=out)
+    for step in range(2):
+        q.copy_(torch.randn_like(q.float()).to(torch.bfloat16))
+        if step == 1:  # the requests have grown by three rows: same graph, new lengths
+            kv_len += 3
+            mask.copy_(torch.roll(mask, 3, dims=2))
+            mask[:, :, :3] = True
+        g.replay()
+        want = torch.empty_like(q)
+        append_paged_kv(pool, c["layer"], k, v, page_table=table, kv_len=kv_len)
+        tree_attention_paged(q, pool, c["layer"], page_table=table, kv_len=kv_len, mask=mask, out=want)
+        assert torch.equal(out, want)
