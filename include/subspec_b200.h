@@ -621,16 +621,17 @@ SUBSPEC_API int subspec_pages_update(const subspec_pages_args* args, subspec_str
  *       specdecodes/models/utils/flashinfer/attention.py:26-102
  *
  * The pool is KvCachePool.cache_data, [layers, num_pages, 2, page_len,
- * num_kv_heads, head_dim] bf16; request b's rows live in the pages
+ * num_kv_heads, head_dim] bf16 or fp16 (FlashInferCache allocates fp16,
+ * cache_manager.py:462); request b's rows live in the pages
  * page_table[b][0 .. ], kv_len[b] of them INCLUDING the n_q[b] rows of the tree
  * (append first).  Query token i of request b is cache row kv_len[b] - n_q[b] + i.
  * It sees every row below prefix_len[b] (NULL: kv_len[b] - n_q[b]) and, of the
  * rows from there on, those whose byte in mask[b][i][row] is non-zero: the
  * [rows, prefix + tree columns] matrix subspec_tree_finalize writes (and
  * FlashInfer's custom_mask).  q / out are [batch, q_len, num_q_heads, head_dim]
- * bf16 with element strides; query head h reads KV head h / (num_q_heads /
+ * in the pool's type with element strides; query head h reads KV head h / (num_q_heads /
  * num_kv_heads).  Softmax in fp32, scores scaled by sm_scale; outputs within
- * bf16 rounding of an fp32 evaluation.  head_dim = 128 only.
+ * the rounding of the 16-bit type of an fp32 evaluation.  head_dim = 128 only.
  * ---------------------------------------------------------------------- */
 typedef struct subspec_tree_attn_args {
   uint32_t struct_size;
@@ -658,6 +659,8 @@ typedef struct subspec_tree_attn_args {
   int64_t o_batch_stride, o_token_stride, o_head_stride;
   double sm_scale;
   uint32_t* dev_status;
+  int32_t dtype; /* SUBSPEC_BF16 or SUBSPEC_F16: pool, q and out alike (0 is read as SUBSPEC_BF16) */
+  int32_t reserved;
 } subspec_tree_attn_args;
 
 SUBSPEC_API int subspec_tree_attention_paged(const subspec_tree_attn_args* args, subspec_stream_t stream);

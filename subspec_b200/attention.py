@@ -60,14 +60,14 @@ def tree_attention_paged(q: torch.Tensor, pool: torch.Tensor, layer: int, *, pag
                          kv_len: torch.Tensor, mask: torch.Tensor, n_q: Optional[torch.Tensor] = None,
                          prefix_len: Optional[torch.Tensor] = None, sm_scale: Optional[float] = None,
                          status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """q [batch, q_len, q_heads, 128] bf16 -> attention output of the same shape (into `out` when given: a
+    """q [batch, q_len, q_heads, 128] bf16 or fp16 (as the pool) -> attention output of the same shape (into `out` when given: a
     captured graph needs a buffer that outlives the capture).
 
     `mask` is bool / uint8 [batch, q_len, cols >= kv_len] (a leading singleton head axis is accepted): row i of
     request b marks the cache rows its query i may read; rows below `prefix_len[b]` (default kv_len - n_q) are
     read without looking at the mask."""
-    if q.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16 or q.dim() != 4:
-        raise ValueError("q must be bf16 [batch, q_len, q_heads, head_dim] and the pool bf16")
+    if q.dtype not in (torch.bfloat16, torch.float16) or pool.dtype != q.dtype or q.dim() != 4:
+        raise ValueError("q must be bf16 or fp16 [batch, q_len, q_heads, head_dim] and the pool of the same type")
     L, P, _, page_len, H, D = pool.shape
     B, QL, HQ, Dq = (int(x) for x in q.shape)
     if Dq != D or q.stride(3) != 1:
@@ -82,7 +82,7 @@ def tree_attention_paged(q: torch.Tensor, pool: torch.Tensor, layer: int, *, pag
     if out is None:
         out = torch.empty_like(q)
     elif out.dtype != q.dtype or out.shape != q.shape or out.device != q.device or out.stride(3) != 1:
-        raise ValueError("out must be a bf16 tensor of q's shape on q's device with contiguous head_dim")
+        raise ValueError("out must be a tensor of q's type and shape on q's device with contiguous head_dim")
     a = _lib.TreeAttnArgs()
     a.struct_size = C.sizeof(_lib.TreeAttnArgs)
     a.batch, a.q_len, a.num_q_heads, a.num_kv_heads, a.head_dim = B, QL, HQ, int(H), int(D)
@@ -96,6 +96,7 @@ def tree_attention_paged(q: torch.Tensor, pool: torch.Tensor, layer: int, *, pag
     a.q, a.q_batch_stride, a.q_token_stride, a.q_head_stride = q.data_ptr(), *(int(q.stride(i)) for i in range(3))
     a.out, a.o_batch_stride, a.o_token_stride, a.o_head_stride = out.data_ptr(), *(int(out.stride(i)) for i in range(3))
     a.sm_scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D)
+    a.dtype = _lib.BF16 if q.dtype == torch.bfloat16 else _lib.F16
     a.dev_status = 0 if status is None else status.data_ptr()
     stream = torch.cuda.current_stream(pool.device).cuda_stream
     _lib.check(_lib.lib().subspec_tree_attention_paged(C.byref(a), C.c_void_p(stream)),

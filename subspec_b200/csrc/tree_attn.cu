@@ -36,7 +36,13 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+// two floats -> one 32-bit word of the cache's 16-bit type (kHalf: fp16, else bf16), low half first
+template <bool kHalf>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  if (kHalf) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
@@ -124,11 +130,11 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr, uint32_t leading
   d |= (uint64_t)2 << 61;
   return d;
 }
-// Instruction descriptor, kind::f16: D fp32 (bit 4), A and B bf16 (1 at [7,10) and [10,13)), bit 16 = B is
+// Instruction descriptor, kind::f16: D fp32 (bit 4), A and B bf16 (1 at [7,10) and [10,13)) or fp16 (0), bit 16 = B is
 // MN-major, N >> 3 at [17,23), M >> 4 at [24,29).
-__host__ __device__ constexpr uint32_t tc_idesc(int m, int n, bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(m >> 4) << 24);
+__host__ __device__ constexpr uint32_t tc_idesc(int m, int n, bool b_mn_major, bool half) {
+  return (1u << 4) | ((half ? 0u : 1u) << 7) | ((half ? 0u : 1u) << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void tc_mma_f16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -175,6 +181,7 @@ struct TcRingPos {
   }
 };
 
+template <bool kHalf>
 __global__ void __launch_bounds__(kTcThreads, 1)
     tree_attn_tc_kernel(const AttnArgs ka, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ unsigned char smem_raw[];
@@ -377,7 +384,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
               p1 = ((bits >> (2 * j + 1)) & 1u) ? p1 : 0.f;
             }
             sm2[j & 1] = f2_add(sm2[j & 1], f2_pack(p0, p1));
-            pk[j] = pack_bf16(p0, p1);
+            pk[j] = pack16<kHalf>(p0, p1);
           }
           tmem_st16(s_addr + 16 * c, pk);  // columns [16 c, 16 c + 16) <- keys [32 c, 32 c + 32)
         };
@@ -415,10 +422,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 v;
-              v.x = pack_bf16(__uint_as_float(r[8 * j]) * inv, __uint_as_float(r[8 * j + 1]) * inv);
-              v.y = pack_bf16(__uint_as_float(r[8 * j + 2]) * inv, __uint_as_float(r[8 * j + 3]) * inv);
-              v.z = pack_bf16(__uint_as_float(r[8 * j + 4]) * inv, __uint_as_float(r[8 * j + 5]) * inv);
-              v.w = pack_bf16(__uint_as_float(r[8 * j + 6]) * inv, __uint_as_float(r[8 * j + 7]) * inv);
+              v.x = pack16<kHalf>(__uint_as_float(r[8 * j]) * inv, __uint_as_float(r[8 * j + 1]) * inv);
+              v.y = pack16<kHalf>(__uint_as_float(r[8 * j + 2]) * inv, __uint_as_float(r[8 * j + 3]) * inv);
+              v.z = pack16<kHalf>(__uint_as_float(r[8 * j + 4]) * inv, __uint_as_float(r[8 * j + 5]) * inv);
+              v.w = pack16<kHalf>(__uint_as_float(r[8 * j + 6]) * inv, __uint_as_float(r[8 * j + 7]) * inv);
               reinterpret_cast<uint4*>(out_row)[4 * c + j] = v;
             }
           }
@@ -431,8 +438,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     // issues (a thread gets a tcgen05.mma out every 50 cycles or so) =================
     const int blk = warp - kTcIssuerWarp;
     if (blk < nblk) {
-      constexpr uint32_t idesc_s = tc_idesc(kTcBlockRows, kTcKeys, false);
-      constexpr uint32_t idesc_o = tc_idesc(kTcBlockRows, kD, true);
+      constexpr uint32_t idesc_s = tc_idesc(kTcBlockRows, kTcKeys, false, kHalf);
+      constexpr uint32_t idesc_o = tc_idesc(kTcBlockRows, kD, true, kHalf);
       const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0) + (uint32_t)blk * kColBlock;
       const uint32_t q_u32 = smem_u32(qtiles) + (uint32_t)blk * kTcQTileBytes, ring_u32 = smem_u32(ring);
       // S = Q K^T: 8 steps of 16 dims; a step moves 32 bytes inside a 64-dim half, 4 steps per half
@@ -682,6 +689,7 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
       a.layer >= a.layers || a.num_pages < 1 || a.page_len < 1 || a.pages_per_seq < 1)
     return SUBSPEC_EINVAL;
   if (a.head_dim != kD || a.num_q_heads % a.num_kv_heads) return SUBSPEC_EUNSUPPORTED;
+  if (a.dtype != 0 && a.dtype != SUBSPEC_BF16 && a.dtype != SUBSPEC_F16) return SUBSPEC_EINVAL;
   if (a.batch == 0) return SUBSPEC_OK;
   if (!a.q || !a.out || !a.pool || !a.page_table || !a.kv_len || !a.mask) return SUBSPEC_EINVAL;
   if (!(a.sm_scale > 0.0)) return SUBSPEC_EINVAL;
@@ -698,8 +706,9 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
   for (int sft = 0; sft < 31; ++sft)
     if ((1 << sft) == a.page_len) ka.page_shift = sft;
   const cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int rc =
-      cuda_check(cudaFuncSetAttribute(tree_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
+  const bool half = a.dtype == SUBSPEC_F16;
+  auto kernel = half ? tree_attn_tc_kernel<true> : tree_attn_tc_kernel<false>;
+  const int rc = cuda_check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
   if (rc) return rc;
   const dim3 grid((unsigned)((ka.group * a.q_len + kTcRows - 1) / kTcRows), (unsigned)a.num_kv_heads, (unsigned)a.batch);
   // The tensor map of this layer's slab of the pool: [page][K / V][slot][KV head][dim], bf16.  A box is 64 dims of
@@ -723,12 +732,12 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     void* base = const_cast<unsigned char*>(reinterpret_cast<const unsigned char*>(a.pool)) +
                  (size_t)a.layer * a.num_pages * 2 * plane;
-    if (tensor_map_encoder()(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, base, dims, strides, boxdim, estr,
+    if (tensor_map_encoder()(&tmap, half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, base, dims, strides, boxdim, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
       ka.box_rows = box;
   }
-  tree_attn_tc_kernel<<<grid, kTcThreads, kTcSmem, st>>>(ka, tmap);
+  kernel<<<grid, kTcThreads, kTcSmem, st>>>(ka, tmap);
   return cuda_check(cudaGetLastError());
 }
 

@@ -10,16 +10,16 @@ from subspec_b200.tree import Tree
 pytestmark = pytest.mark.gpu
 
 
-def _case(seed, B, QL, HQ, HKV, prefix_lens, n_qs, page_len=16, layers=2, layer=1):
+def _case(seed, B, QL, HQ, HKV, prefix_lens, n_qs, page_len=16, layers=2, layer=1, dtype=torch.bfloat16):
     D = 128
     gen = torch.Generator().manual_seed(seed)
     pages_per_seq = max((p + QL + page_len - 1) // page_len for p in prefix_lens) + 1
     P = B * pages_per_seq
     table = synthetic.random_page_table(B, pages_per_seq, gen)
-    pool = torch.randn(layers, P, 2, page_len, HKV, D, generator=gen).to(torch.bfloat16)
-    q = torch.randn(B, QL, HQ, D, generator=gen).to(torch.bfloat16)
-    k = torch.randn(B, QL, HKV, D, generator=gen).to(torch.bfloat16)
-    v = torch.randn(B, QL, HKV, D, generator=gen).to(torch.bfloat16)
+    pool = torch.randn(layers, P, 2, page_len, HKV, D, generator=gen).to(dtype)
+    q = torch.randn(B, QL, HQ, D, generator=gen).to(dtype)
+    k = torch.randn(B, QL, HKV, D, generator=gen).to(dtype)
+    v = torch.randn(B, QL, HKV, D, generator=gen).to(dtype)
     kv_len = [p + n for p, n in zip(prefix_lens, n_qs)]
     cols = max(kv_len) + 5
     mask = torch.zeros(B, QL, cols, dtype=torch.bool)
@@ -92,6 +92,15 @@ def test_page_lengths(cuda_lib, page_len):
     _run_and_check(c)
     c = _case(20 + page_len, B=2, QL=16, HQ=4, HKV=4, prefix_lens=[64 * 3 - 16, 1], n_qs=[16, 5], page_len=page_len)
     _run_and_check(c)
+
+
+def test_fp16_pool(cuda_lib):
+    """The reference's FlashInferCache allocates its pool in fp16 (cache_manager.py:462): same kernel, the
+    tensor core's other 16-bit format, P and the output rounded to fp16."""
+    c = _case(7, B=3, QL=40, HQ=28, HKV=4, prefix_lens=[900, 63, 0], n_qs=[40, 13, 40], dtype=torch.float16)
+    assert _run_and_check(c, tol=4e-3) < 4e-3
+    c = _case(8, B=1, QL=16, HQ=4, HKV=4, prefix_lens=[333], n_qs=[16], page_len=24, dtype=torch.float16)
+    _run_and_check(c, tol=4e-3)
 
 
 def test_long_stream_and_peaked_rows(cuda_lib):
