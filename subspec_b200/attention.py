@@ -36,10 +36,13 @@ def append_paged_kv(pool: torch.Tensor, layer: int, k: torch.Tensor, v: torch.Te
     `kv_len` counts the rows AFTER the append (grow the requests first, as `RequestKvCache.increment` does)."""
     L, P, _, page_len, H, D = pool.shape
     B, QL = int(k.shape[0]), int(k.shape[1])
-    if k.shape != v.shape or tuple(k.shape[2:]) != (H, D) or k.dtype != pool.dtype or k.stride() != v.stride():
-        raise ValueError("k and v must be [batch, q_len, kv_heads, head_dim] tensors of the pool's dtype and one layout")
+    if k.shape != v.shape or tuple(k.shape[2:]) != (H, D) or k.dtype != pool.dtype or v.dtype != pool.dtype or \
+            k.stride() != v.stride() or pool.element_size() != 2:
+        raise ValueError("k and v must be [batch, q_len, kv_heads, head_dim] tensors of the pool's (16-bit) dtype and one layout")
     if k.stride(3) != 1 or k.stride(2) != D:
         k, v = k.contiguous(), v.contiguous()
+    if page_table.dtype != torch.int32 or page_table.dim() != 2 or not page_table.is_contiguous():
+        raise ValueError("page_table must be a contiguous int32 [batch, pages_per_seq] tensor")
     a = _lib.KvAppendArgs()
     a.struct_size = C.sizeof(_lib.KvAppendArgs)
     a.batch, a.q_len, a.num_kv_heads, a.head_dim = B, QL, int(H), int(D)

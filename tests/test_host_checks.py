@@ -46,3 +46,35 @@ def test_bad_offsets_are_rejected():
         check_forest(np.array([0, 0]), np.array([], dtype=np.int32), 2)
     with pytest.raises(ValueError, match="child entries"):
         check_forest(np.array([0, 3, 3]), np.array([1, 1, 1]), 2)
+
+
+def test_attention_wrapper_rejects_bad_arguments():
+    """The checks of `tree_attention_paged` / `append_paged_kv` that run before any launch, on CPU tensors."""
+    import torch
+
+    from subspec_b200.attention import append_paged_kv, tree_attention_paged
+
+    L, P, page, H, D, B, QL, HQ = 1, 4, 16, 2, 128, 1, 8, 4
+    pool = torch.zeros(L, P, 2, page, H, D, dtype=torch.bfloat16)
+    q = torch.zeros(B, QL, HQ, D, dtype=torch.bfloat16)
+    table = torch.zeros(B, 4, dtype=torch.int32)
+    kv_len = torch.full((B,), 20, dtype=torch.int32)
+    mask = torch.ones(B, QL, 32, dtype=torch.bool)
+    kw = dict(page_table=table, kv_len=kv_len, mask=mask)
+    with pytest.raises(ValueError, match="same type"):  # fp16 queries on a bf16 pool
+        tree_attention_paged(q.half(), pool, 0, **kw)
+    with pytest.raises(ValueError, match="same type"):
+        tree_attention_paged(q.float(), pool.float(), 0, **kw)
+    with pytest.raises(ValueError, match="head_dim"):
+        tree_attention_paged(q[..., :64].contiguous(), pool, 0, **kw)
+    with pytest.raises(ValueError, match="mask"):
+        tree_attention_paged(q, pool, 0, page_table=table, kv_len=kv_len, mask=mask.float())
+    with pytest.raises(ValueError, match="mask"):
+        tree_attention_paged(q, pool, 0, page_table=table, kv_len=kv_len, mask=mask[:, :4])
+    with pytest.raises(ValueError, match="page_table"):
+        tree_attention_paged(q, pool, 0, page_table=table.long(), kv_len=kv_len, mask=mask)
+    with pytest.raises(ValueError, match="out must"):
+        tree_attention_paged(q, pool, 0, out=torch.zeros(B, QL, HQ, D, dtype=torch.float16), **kw)
+    k = torch.zeros(B, QL, H, D, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        append_paged_kv(pool, 0, k, k.half(), page_table=table, kv_len=kv_len)
