@@ -94,6 +94,22 @@ def test_page_lengths(cuda_lib, page_len):
     _run_and_check(c)
 
 
+@pytest.mark.parametrize("seed", range(16))
+def test_random_shapes(cuda_lib, seed):
+    """Seeded random geometry: batch, tree size, head layout, page length, prefixes, partly filled trees, type."""
+    g = torch.Generator().manual_seed(1000 + seed)
+    r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+    B, QL = r(1, 3), r(1, 70)
+    HKV = [1, 2, 4][r(0, 2)]
+    HQ = HKV * [1, 2, 4, 7][r(0, 3)]
+    page_len = [1, 8, 16, 16, 40, 64, 256][r(0, 6)]
+    prefix = [r(0, 700) for _ in range(B)]
+    n_q = [r(1, QL) for _ in range(B)]
+    dtype = [torch.bfloat16, torch.float16][r(0, 1)]
+    c = _case(2000 + seed, B=B, QL=QL, HQ=HQ, HKV=HKV, prefix_lens=prefix, n_qs=n_q, page_len=page_len, dtype=dtype)
+    _run_and_check(c)
+
+
 def test_fp16_pool(cuda_lib):
     """The reference's FlashInferCache allocates its pool in fp16 (cache_manager.py:462): same kernel, the
     tensor core's other 16-bit format, P and the output rounded to fp16."""
