@@ -158,12 +158,14 @@ __device__ __forceinline__ void tma_load_5d(void* dst_smem, const CUtensorMap* m
       : "memory");
 }
 
-// The hand-overs between the roles of this kernel are short and on the critical path: poll the barrier with
-// test_wait, which never suspends the thread.  Bounded like every wait here.
+// The hand-overs between the roles of this kernel are short and on the critical path: try_wait without a
+// suspend-time hint (the waiting warp is parked by the hardware and comes back when the phase completes, so its
+// polls do not fill the queue that the exponentials of the softmax warps pass through).  Bounded like every
+// wait here.
 constexpr uint32_t kTcPollLimit = 1u << 24;
 __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t it = 0; it < kTcPollLimit; ++it) {
-    if (mbar_test_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     if ((it & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;
