@@ -114,6 +114,7 @@ constexpr int kTcLoadWarps = 2;                     // twelve warps in all: thre
 constexpr int kTcThreads = 32 * (kTcLoadWarp0 + kTcLoadWarps);
 constexpr int kTcInflight = 3;                      // row-by-row entries a gather warp keeps in flight
 constexpr uint32_t kColBlock = 256, kColO = 128, kTcCols = 512;
+constexpr float kTcSumLimit = 256.f;                // a row sum up to here proves every P of the tile <= 2^8
 constexpr float kTcRescaleAt = 8.f;                 // log2 units the maximum may run ahead of the exponents' reference
 
 // Shared-memory matrix descriptor, 128-byte swizzle, 8-row atoms of 1024 bytes: [0,14) address >> 4, [16,30)
@@ -321,53 +322,12 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         }
         tmem_wait_ld_dep(ra);
         tmem_wait_ld_dep(rb);
-        // ---- the row's maximum over the tile (four chains, not one) ----
-        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        if (need_mask) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if ((vis[0] >> j) & 1u) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(ra[j]));
-            if ((vis[1] >> j) & 1u) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(rb[j]));
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], fmaxf(__uint_as_float(ra[j]), __uint_as_float(rb[j])));
-        }
-        const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c2;  // c2 > 0: max commutes with scaling
-        // The reference point of the exponents moves only when the row's maximum has grown by more than 2^8
-        // past it: between moves P reaches at most 256, which bf16 and the fp32 sums hold as well as 1, and
-        // the rescaling of O (a pass over tensor memory) becomes rare instead of per tile.
-        float alpha = 1.f;
-        if (tmax > m + kTcRescaleAt || m == -INFINITY) {
-          const float m_new = fmaxf(m, tmax);
-          alpha = ex2f(m - (m_new == -INFINITY ? 0.f : m_new));  // 0 while m is -inf
-          m = m_new;
-        }
-        const float u = m == -INFINITY ? 0.f : m;  // a row with nothing visible yet
-        if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-          // O += P V of the tile before must have landed before O is rescaled.  The tiles complete on two
-          // barriers in turn, so the phase asked for is unambiguous although most tiles never ask: of this
-          // barrier's tiles all up to t - 3 are known complete (S of this tile was issued behind them) and
-          // none after t - 1 can have been issued.
-          live = __all_sync(0xffffffffu, tc_wait(&o_done[blk][(t - 1) & 1], (uint32_t)((t - 1) >> 1) & 1u, abort_flag));
-          if (!live) break;
-          tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t rc[32];
-            tmem_ld32_async(o_addr + 32 * c, rc);
-            tmem_wait_ld_dep(rc);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) rc[j] = __float_as_uint(__uint_as_float(rc[j]) * alpha);
-            tmem_st32(o_addr + 32 * c, rc);
-          }
-        }
-        // ---- P = exp2(S c2 - m) over the first half of the S columns (all read by now), the row sum ----
-        // (two copies of the loop, with and without the mask: inside the prefix no instruction is spent on it;
-        //  scaling and sums two floats at a time)
-        uint64_t sm2[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
-        const uint64_t c2p = f2_pack(c2, c2), nup = f2_pack(-u, -u);
+        // P = exp2(S c2 - u), u the reference point of the row's exponents.  (Two copies of the loop, with and
+        // without the mask: inside the prefix no instruction is spent on it; scaling and sums two floats at a time.)
+        uint64_t sm2[2];
+        float u = m;
         auto exp_chunk = [&](auto masked, const uint32_t (&r)[32], uint32_t bits, int c) {
+          const uint64_t c2p = f2_pack(c2, c2), nup = f2_pack(-u, -u);
           uint32_t pk[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -390,17 +350,77 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           }
           tmem_st16(s_addr + 16 * c, pk);  // columns [16 c, 16 c + 16) <- keys [32 c, 32 c + 32)
         };
-        if (need_mask) {
-          exp_chunk(std::true_type{}, ra, vis[0], 0);
-          exp_chunk(std::true_type{}, rb, vis[1], 1);
-        } else {
+        auto row_sum = [&]() {
+          float e0, e1, e2, e3;
+          f2_unpack(sm2[0], e0, e1);
+          f2_unpack(sm2[1], e2, e3);
+          return (e0 + e1) + (e2 + e3);
+        };
+        // Most tiles move no reference point: try the tile against the old one first, without looking for its
+        // maximum.  Every P is positive, so a row sum of at most 2^8 proves that no P went past 2^8 -- the same
+        // bound the search for the maximum would have enforced -- and anything else (a larger sum, an overflow)
+        // sends the warp down the careful path, which recomputes the tile from the registers it still holds.
+        bool careful = t == 0 || need_mask || __any_sync(0xffffffffu, m == -INFINITY);
+        float alpha = 1.f;
+        if (!careful) {
+          sm2[0] = sm2[1] = f2_pack(0.f, 0.f);
           exp_chunk(std::false_type{}, ra, 0u, 0);
           exp_chunk(std::false_type{}, rb, 0u, 1);
+          const float ts = row_sum();
+          careful = __any_sync(0xffffffffu, !(ts <= kTcSumLimit));
+          if (!careful) l += ts;
         }
-        float sm[4];
-        f2_unpack(sm2[0], sm[0], sm[1]);
-        f2_unpack(sm2[1], sm[2], sm[3]);
-        l = l * alpha + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
+        if (careful) {
+          // ---- the row's maximum over the tile (four chains, not one) ----
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          if (need_mask) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if ((vis[0] >> j) & 1u) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(ra[j]));
+              if ((vis[1] >> j) & 1u) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(rb[j]));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], fmaxf(__uint_as_float(ra[j]), __uint_as_float(rb[j])));
+          }
+          const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c2;  // c2 > 0: max commutes with scaling
+          // The reference point of the exponents moves only when the row's maximum has grown by more than 2^8
+          // past it: between moves P reaches at most 256, which bf16 and the fp32 sums hold as well as 1, and
+          // the rescaling of O (a pass over tensor memory) becomes rare instead of per tile.
+          if (tmax > m + kTcRescaleAt || m == -INFINITY) {
+            const float m_new = fmaxf(m, tmax);
+            alpha = ex2f(m - (m_new == -INFINITY ? 0.f : m_new));  // 0 while m is -inf
+            m = m_new;
+          }
+          u = m == -INFINITY ? 0.f : m;  // a row with nothing visible yet
+          if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+            // O += P V of the tile before must have landed before O is rescaled.  The tiles complete on two
+            // barriers in turn, so the phase asked for is unambiguous although most tiles never ask: of this
+            // barrier's tiles all up to t - 3 are known complete (S of this tile was issued behind them) and
+            // none after t - 1 can have been issued.
+            live = __all_sync(0xffffffffu, tc_wait(&o_done[blk][(t - 1) & 1], (uint32_t)((t - 1) >> 1) & 1u, abort_flag));
+            if (!live) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t rc[32];
+              tmem_ld32_async(o_addr + 32 * c, rc);
+              tmem_wait_ld_dep(rc);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) rc[j] = __float_as_uint(__uint_as_float(rc[j]) * alpha);
+              tmem_st32(o_addr + 32 * c, rc);
+            }
+          }
+          sm2[0] = sm2[1] = f2_pack(0.f, 0.f);
+          if (need_mask) {
+            exp_chunk(std::true_type{}, ra, vis[0], 0);
+            exp_chunk(std::true_type{}, rb, vis[1], 1);
+          } else {
+            exp_chunk(std::false_type{}, ra, 0u, 0);
+            exp_chunk(std::false_type{}, rb, 0u, 1);
+          }
+          l = l * alpha + row_sum();
+        }
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
