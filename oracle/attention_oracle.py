@@ -5,8 +5,13 @@ fp32 / fp64 torch restatement of what the reference obtains from FlashInfer
 specdecodes/models/utils/flashinfer/attention_wrapper.py:104-151, 234-253, 288-316): per request, the tree
 tokens' queries over the request's cache rows, gathered through the page table, under a boolean mask, softmax
 in full precision, grouped-query head mapping h -> h // (q_heads // kv_heads).  FlashInfer is a third-party
-package (flashinfer-python, requirements.txt of the reference) whose kernels need a GPU; its published
-semantics are restated here and no reference test pins them: parity unpinned.  Only tests/ may import this.
+package (flashinfer-python, requirements.txt of the reference) whose kernels need a GPU, so they cannot be run
+where the fixtures are made.  What pins this restatement instead is the attention of the reference's default
+(Hugging Face) path over the same trees: torch's scaled_dot_product_attention behind transformers' repeat_kv,
+with the additive mask the reference builds (Tree.create_attention_mask + invert_mask,
+specdecodes/models/utils/cpu_tree.py:263, specdecodes/models/utils/utils.py:4-6) -- tests/golden/attention_*,
+made by tests/golden/make_golden.py --only attention, agree with this function to fp32 accuracy.  The paged
+gather (`gather_rows`) follows KvCachePool's layout, which the KV goldens pin.  Only tests/ may import this.
 """
 from __future__ import annotations
 

@@ -175,3 +175,16 @@ def w4a16_case(n: int, k: int, m: int, seed: int, group: int = 64):
     zero = (torch.rand(n, k // group, generator=gen) * 15.0).half()
     x = torch.randn(m, k, generator=gen).to(torch.bfloat16)
     return qweight, scale, zero, x
+
+
+def attention_case(seed: int, n_q: int, prefix: int, q_heads: int, kv_heads: int, dtype: torch.dtype, head_dim: int = 128):
+    """Seeded inputs of one tree-attention problem: a random tree of `n_q` nodes behind `prefix` cache rows.
+
+    Returns (tree, q [n_q, q_heads, D], k and v [prefix + n_q, kv_heads, D]) in `dtype`, rows in cache order."""
+    gen = torch.Generator().manual_seed(seed)
+    tree = random_tree(n_q, 6, 3, 1000, gen)
+    n = prefix + n_q
+    q = torch.randn(n_q, q_heads, head_dim, generator=gen).to(dtype)
+    k = torch.randn(n, kv_heads, head_dim, generator=gen).to(dtype)
+    v = torch.randn(n, kv_heads, head_dim, generator=gen).to(dtype)
+    return tree, q, k, v

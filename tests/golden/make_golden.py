@@ -671,6 +671,47 @@ def gen_pages(ref, out_dir: Path):
     print(f"pages: {len(scripts)} scripted loops, {sum(len(s_['steps']) for s_ in scripts)} steps")
 
 
+ATTN_CASES = [  # (seed, tree nodes, prefix rows, query heads, KV heads, dtype)
+    (3100, 12, 37, 4, 2, "bfloat16"), (3101, 16, 0, 4, 4, "bfloat16"), (3102, 20, 150, 7, 1, "float16"),
+    (3103, 1, 9, 4, 1, "bfloat16"), (3104, 17, 64, 6, 3, "float32"),
+]
+
+
+def gen_attention(ref, out_dir: Path):
+    """The attention the reference's default (HF) path computes over a tree: transformers' SDPA attention --
+    `repeat_kv`, then `torch.nn.functional.scaled_dot_product_attention` with an additive mask -- fed with the
+    mask the reference builds (`Tree.create_attention_mask(prefix_length)` and `invert_mask`,
+    specdecodes/models/utils/cpu_tree.py:263, specdecodes/models/utils/utils.py:4-6).  Stored per case: the
+    result computed in fp32 from the inputs (what pins the oracle) and the result in the inputs' own type (what
+    the reference's model would hold).  The inputs are regenerated from the seed (synthetic.attention_case)."""
+    import specdecodes.models.utils.utils as ru
+    arrays, cases = {}, []
+    for seed, n_q, prefix, hq, hkv, dt in ATTN_CASES:
+        dtype = getattr(torch, dt)
+        st, q, k, v = synthetic.attention_case(seed, n_q, prefix, hq, hkv, dtype)
+        rt = ref_tree(ref["ct"], st)
+        mask = rt.create_attention_mask(prefix_length=prefix)  # bool [1, 1, n_q, prefix + n_q]
+        assert tuple(mask.shape) == (1, 1, n_q, prefix + n_q)
+
+        def sdpa(t):
+            qq = q.to(t).permute(1, 0, 2)[None]                      # [1, HQ, n_q, D]
+            kk = k.to(t).permute(1, 0, 2)[None].repeat_interleave(hq // hkv, dim=1)  # repeat_kv
+            vv = v.to(t).permute(1, 0, 2)[None].repeat_interleave(hq // hkv, dim=1)
+            o = torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, attn_mask=ru.invert_mask(mask, t))
+            return o[0].permute(1, 0, 2).contiguous()                 # [n_q, HQ, D]
+
+        name = f"a{seed}"
+        arrays[name + "/exact"] = sdpa(torch.float32).numpy()
+        arrays[name + "/native"] = sdpa(dtype).to(torch.float16 if dtype == torch.float16 else torch.bfloat16).view(
+            torch.int16).numpy()  # the 16-bit patterns (bf16 for the fp32 case)
+        arrays[name + "/mask"] = mask[0, 0].numpy()
+        cases.append(dict(name=name, seed=seed, n_q=n_q, prefix=prefix, q_heads=hq, kv_heads=hkv, dtype=dt))
+    np.savez_compressed(out_dir / "attention_small.npz", **arrays)
+    (out_dir / "attention_cases.json").write_text(json.dumps(dict(
+        generator="tests/golden/make_golden.py --only attention", cases=cases), indent=1))
+    print(f"attention: {len(cases)} cases")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the unmodified reference repository")
@@ -692,6 +733,8 @@ def main():
         gen_post(ref, HERE)
     if args.only in (None, "pages"):
         gen_pages(ref, HERE)
+    if args.only in (None, "attention"):
+        gen_attention(ref, HERE)
     if args.only in (None, "sampled"):
         gen_sampled(ref, HERE)
     if args.only in (None, "lossy_unit"):

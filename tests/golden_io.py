@@ -140,3 +140,25 @@ def sampled_processors(case):
     if case["top_p"] < 1.0:
         procs.append(TopPLogitsWarper(top_p=case["top_p"]))
     return procs
+
+
+@lru_cache(maxsize=None)
+def attention_cases():
+    return json.loads((GOLDEN / "attention_cases.json").read_text())["cases"]
+
+
+@lru_cache(maxsize=None)
+def _attention_small():
+    return dict(np.load(GOLDEN / "attention_small.npz"))
+
+
+def attention_golden(case):
+    """(tree, q, k, v in the case's type, bool mask [n_q, prefix + n_q], SDPA result computed in fp32,
+    SDPA result computed in the case's own type as fp32 values) of one golden attention case."""
+    dtype = DT[case["dtype"]]
+    tree, q, k, v = synthetic.attention_case(case["seed"], case["n_q"], case["prefix"], case["q_heads"],
+                                             case["kv_heads"], dtype)
+    z = _attention_small()
+    name = case["name"]
+    native16 = torch.from_numpy(z[name + "/native"]).view(torch.float16 if dtype == torch.float16 else torch.bfloat16)
+    return tree, q, k, v, torch.from_numpy(z[name + "/mask"]), torch.from_numpy(z[name + "/exact"]), native16.float()

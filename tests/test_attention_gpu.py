@@ -6,6 +6,7 @@ from oracle import attention_oracle as ao
 from subspec_b200 import synthetic
 from subspec_b200.attention import append_paged_kv, tree_attention_paged
 from subspec_b200.tree import Tree
+from tests import golden_io
 
 pytestmark = pytest.mark.gpu
 
@@ -177,3 +178,26 @@ def test_inside_a_cuda_graph(cuda_lib):
         append_paged_kv(pool, c["layer"], k, v, page_table=table, kv_len=kv_len)
         tree_attention_paged(q, pool, c["layer"], page_table=table, kv_len=kv_len, mask=mask, out=want)
         assert torch.equal(out, want)
+
+
+def test_against_sdpa_goldens(cuda_lib):
+    """The kernel against torch SDPA on the reference's masks (tests/golden/attention_*): the rows laid out in
+    pages of 16 through a random page table."""
+    for case in golden_io.attention_cases():
+        if case["dtype"] == "float32":
+            continue  # the kernel takes the 16-bit types
+        st, q, k, v, mask, exact, native = golden_io.attention_golden(case)
+        n_q, n, page_len, dev = case["n_q"], case["prefix"] + case["n_q"], 16, "cuda"
+        pages = (n + page_len - 1) // page_len + 1
+        gen = torch.Generator().manual_seed(case["seed"])
+        table = synthetic.random_page_table(1, pages, gen)
+        pool = torch.zeros(1, pages, 2, page_len, case["kv_heads"], 128, dtype=q.dtype)
+        for pos in range(n):
+            pg = int(table[0, pos // page_len])
+            pool[0, pg, 0, pos % page_len], pool[0, pg, 1, pos % page_len] = k[pos], v[pos]
+        out = tree_attention_paged(q[None].to(dev), pool.to(dev), 0, page_table=table.to(dev),
+                                   kv_len=torch.tensor([n], dtype=torch.int32, device=dev), mask=mask[None].to(dev))
+        got = out[0].float().cpu()
+        tol = 2e-2 if case["dtype"] == "bfloat16" else 3e-3
+        assert float((got - exact).abs().max()) < tol * float(exact.abs().max()), case["name"]
+        assert float((got - native).abs().max()) < 2 * tol * float(exact.abs().max()), case["name"]

@@ -180,3 +180,20 @@ def test_post_verify_oracle_matches_reference_tree_methods():
             assert ch == pr["children"]
             if len(keep) < len(t["token_ids"]):  # an early return leaves the reference's leaf list as it was
                 assert [i for i in range(len(keep)) if not ch[i]] == pr["leaves"]
+
+
+def test_attention_oracle_against_sdpa_on_the_reference_masks():
+    """The attention oracle against torch's scaled_dot_product_attention fed the way transformers' SDPA attention
+    feeds it on the reference's default path (repeat_kv, additive mask from the reference's
+    Tree.create_attention_mask + invert_mask): same numbers to fp32 accuracy, and our Tree builds the same mask."""
+    from oracle import attention_oracle as ao
+    from subspec_b200.tree import Tree
+    for case in golden_io.attention_cases():
+        st, q, k, v, mask, exact, native = golden_io.attention_golden(case)
+        tree = Tree.from_arrays(st.token_ids.tolist(), st.parents.tolist())
+        assert torch.equal(tree.create_attention_mask(prefix_length=case["prefix"])[0, 0], mask)
+        want = ao.tree_attention(q, k, v, mask)
+        assert float((want - exact.double()).abs().max()) < 2e-5 * float(exact.abs().max()), case["name"]
+        # the result in the inputs' own type is the fp32 one up to that type's rounding (of P and of the output)
+        tol = {"bfloat16": 2e-2, "float16": 3e-3, "float32": 8e-3}[case["dtype"]]  # fp32 case: stored as bf16
+        assert float((native.double() - want).abs().max()) < tol * float(want.abs().max()), case["name"]
