@@ -628,8 +628,9 @@ SUBSPEC_API int subspec_pages_update(const subspec_pages_args* args, subspec_str
  * It sees every row below prefix_len[b] (NULL: kv_len[b] - n_q[b]) and, of the
  * rows from there on, those whose byte in mask[b][i][row] is non-zero: the
  * [rows, prefix + tree columns] matrix subspec_tree_finalize writes (and
- * FlashInfer's custom_mask).  q / out are [batch, q_len, num_q_heads, head_dim]
- * in the pool's type with element strides; query head h reads KV head h / (num_q_heads /
+ * FlashInfer's custom_mask, or its additive form: mask_kind).  q / out are
+ * [batch, q_len, num_q_heads, head_dim] in the pool's type with element strides (any
+ * order of the axes in memory, e.g. the [batch, heads, tokens, dim] of an SDPA call); query head h reads KV head h / (num_q_heads /
  * num_kv_heads).  Softmax in fp32, scores scaled by sm_scale; outputs within
  * the rounding of the 16-bit type of an fp32 evaluation.  head_dim = 128 only.
  * ---------------------------------------------------------------------- */
@@ -650,7 +651,7 @@ typedef struct subspec_tree_attn_args {
   const int32_t* kv_len;     /* [batch] */
   const int32_t* n_q;        /* [batch] or NULL (= q_len) */
   const int32_t* prefix_len; /* [batch] or NULL */
-  const uint8_t* mask;       /* [batch, q_len, >= kv_len] bytes */
+  const uint8_t* mask;       /* [batch, q_len, >= kv_len] elements of mask_kind (bytes by default) */
   int64_t mask_batch_stride;
   int64_t mask_row_stride;
   const void* q;
@@ -660,7 +661,15 @@ typedef struct subspec_tree_attn_args {
   double sm_scale;
   uint32_t* dev_status;
   int32_t dtype; /* SUBSPEC_BF16 or SUBSPEC_F16: pool, q and out alike (0 is read as SUBSPEC_BF16) */
-  int32_t reserved;
+  int32_t mask_kind; /* SUBSPEC_MASK_BOOL (bytes, non-zero = visible) or SUBSPEC_MASK_ADD_F32 / _BF16 / _F16
+                        (the additive form invert_mask makes: +-0 = visible, anything else hidden); the mask
+                        strides count elements of that kind */
+  /* Hugging Face static caches (TreeStaticCache: key / value tensors [batch, kv_heads, max_cache_len, head_dim]
+   * of one layer) instead of the paged pool: v_cache != NULL, `pool` is the key tensor, page_len the rows a
+   * batch entry has room for, num_pages = batch, pages_per_seq = 1, page_table may be NULL (request b is
+   * entry b), layer = 0 and layers = 1.  Strides in elements; heads' rows must be head_dim apart or more. */
+  const void* v_cache;
+  int64_t kv_batch_stride, kv_head_stride, kv_row_stride;
 } subspec_tree_attn_args;
 
 SUBSPEC_API int subspec_tree_attention_paged(const subspec_tree_attn_args* args, subspec_stream_t stream);

@@ -170,7 +170,8 @@ class TreeAttnArgs(C.Structure):
         ("prefix_len", _vp), ("mask", _vp), ("mask_batch_stride", _i64), ("mask_row_stride", _i64), ("q", _vp),
         ("q_batch_stride", _i64), ("q_token_stride", _i64), ("q_head_stride", _i64), ("out", _vp),
         ("o_batch_stride", _i64), ("o_token_stride", _i64), ("o_head_stride", _i64), ("sm_scale", _f64),
-        ("dev_status", _vp), ("dtype", _i32), ("reserved", _i32),
+        ("dev_status", _vp), ("dtype", _i32), ("mask_kind", _i32), ("v_cache", _vp),
+        ("kv_batch_stride", _i64), ("kv_head_stride", _i64), ("kv_row_stride", _i64),
     ]
 
 

@@ -72,6 +72,15 @@ struct AttnArgs {
   float scale_log2; // sm_scale * log2(e)
   int page_shift;   // log2(page_len) when it is a power of two, else -1
   int box_rows;     // cache rows per tensor copy (0: the page length does not suit them)
+  // where the rows lie: K (V) row `slot` of page `pg`, KV head h = k_base (v_base) + pg * page_stride +
+  // slot * row_stride + h * head_stride bytes.  The paged pool and the [batch, heads, rows, dim] caches of the
+  // Hugging Face path (a "page" = a batch entry, the page table the identity) differ in these numbers only.
+  const unsigned char* k_base;
+  const unsigned char* v_base;
+  long long page_stride, row_stride, head_stride;
+  int identity_table;
+  int rows_before_heads;  // order of the two middle coordinates of the tensor maps (strides ascend in them)
+  int mask_bytes;   // bytes per mask element: 1 (bool: non-zero = visible), 2 or 4 (additive: +-0 = visible)
 };
 
 // One CTA = 256 query rows of one (request, KV head) -- two blocks of 128 rows that share every K / V tile --
@@ -148,15 +157,69 @@ __device__ __forceinline__ void tc_mma_f16_ss(uint32_t tmem_d, uint64_t adesc, u
       : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// Tensor copy (TMA), five coordinates, global -> shared, completion counted in bytes on `bar`.  The innermost
-// coordinate times the element size must be a multiple of 16 bytes (here 0 or 64 bf16).
-__device__ __forceinline__ void tma_load_5d(void* dst_smem, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4,
+// Tensor copy (TMA), four coordinates (dim, KV head, row of the page, page), global -> shared, completion
+// counted in bytes on `bar`.  The innermost coordinate times the element size must be a multiple of 16 bytes
+// (here 0 or 64 elements of 2 bytes).
+__device__ __forceinline__ void tma_load_4d(void* dst_smem, const CUtensorMap* map, int c0, int c1, int c2, int c3,
                                             uint64_t* bar) {
   asm volatile(
-      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], "
-      "[%7];" ::"r"(smem_u32(dst_smem)),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar))
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+          smem_u32(dst_smem)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
       : "memory");
+}
+
+// Which of 32 consecutive mask elements starting at `p` (element size `bytes`) say "visible": for byte masks a
+// non-zero byte, for the additive kinds a zero of either sign.  `vec`: p's address is 16-byte aligned and all 32
+// elements may be read.  Otherwise element by element, where `readable(j)`.
+template <typename Readable>
+__device__ __forceinline__ uint32_t mask_bits32(const unsigned char* p, int bytes, bool vec, Readable readable) {
+  uint32_t bits = 0;
+  if (bytes == 1) {
+    uint8_t mb[32];
+    if (vec) {
+      const uint4 lo = *reinterpret_cast<const uint4*>(p), hi = *reinterpret_cast<const uint4*>(p + 16);
+      const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+      for (int j = 0; j < 32; ++j) mb[j] = (uint8_t)(w[j >> 2] >> (8 * (j & 3)));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) mb[j] = readable(j) ? p[j] : (uint8_t)0;  // all the loads first: one trip to memory
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) bits |= (mb[j] != 0 ? 1u : 0u) << j;
+  } else if (bytes == 2) {
+    uint16_t mh[32];
+    if (vec) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 v = reinterpret_cast<const uint4*>(p)[q];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mh[8 * q + j] = (uint16_t)(w[j >> 1] >> (16 * (j & 1)));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) mh[j] = readable(j) ? reinterpret_cast<const uint16_t*>(p)[j] : (uint16_t)0xffff;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) bits |= ((mh[j] & 0x7fffu) == 0 ? 1u : 0u) << j;
+  } else {
+    uint32_t mw[32];
+    if (vec) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const uint4 v = reinterpret_cast<const uint4*>(p)[q];
+        mw[4 * q] = v.x, mw[4 * q + 1] = v.y, mw[4 * q + 2] = v.z, mw[4 * q + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) mw[j] = readable(j) ? reinterpret_cast<const uint32_t*>(p)[j] : 0xffffffffu;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) bits |= ((mw[j] & 0x7fffffffu) == 0 ? 1u : 0u) << j;
+  }
+  return bits;
 }
 
 // The hand-overs between the roles of this kernel are short and on the critical path: try_wait without a
@@ -186,7 +249,8 @@ struct TcRingPos {
 
 template <bool kHalf>
 __global__ void __launch_bounds__(kTcThreads, 1)
-    tree_attn_tc_kernel(const AttnArgs ka, const __grid_constant__ CUtensorMap tmap) {
+    tree_attn_tc_kernel(const AttnArgs ka, const __grid_constant__ CUtensorMap tmap_k,
+                        const __grid_constant__ CUtensorMap tmap_v) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full[kTcRing], empty[kTcRing], s_ready[2][2], p_ready[2][2], o_done[2][2], q_ready;
   __shared__ uint32_t s_tmem;
@@ -276,7 +340,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     if (blk < nblk) {
       const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)blk * kColBlock;
       const uint32_t o_addr = lane_base + kColO;
-      const uint8_t* mrow = a.mask + (size_t)b * a.mask_batch_stride + (size_t)ri * a.mask_row_stride;
+      const unsigned char* mrow = a.mask + ((size_t)b * a.mask_batch_stride + (size_t)ri * a.mask_row_stride) * ka.mask_bytes;
       const float c2 = ka.scale_log2;
       float m = -INFINITY, l = 0.f;  // reference point of the exponents (in their units) and sum of this row
       bool live = true;
@@ -294,29 +358,15 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
-            // all the loads of a chunk first (they are independent: one trip to memory, not thirty-two), sixteen
-            // bytes at a time where that stays inside the row's columns and is aligned
-            uint8_t mb[32];
+            // sixteen bytes at a time where that stays inside the row's columns and is aligned
             const int p0 = t0 + 32 * c;
-            if (row_ok && p0 + 32 <= kv_len && ((reinterpret_cast<uintptr_t>(mrow + p0) & 15u) == 0)) {
-              const uint4 lo = *reinterpret_cast<const uint4*>(mrow + p0);
-              const uint4 hi = *reinterpret_cast<const uint4*>(mrow + p0 + 16);
-              const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-#pragma unroll
-              for (int j = 0; j < 32; ++j) mb[j] = (uint8_t)(w[j >> 2] >> (8 * (j & 3)));
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int pos = p0 + j;
-                mb[j] = (pos >= prefix && pos < kv_len && row_ok) ? mrow[pos] : (uint8_t)0;
-              }
-            }
-            uint32_t bits = 0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int pos = t0 + 32 * c + j;
-              bits |= ((pos < prefix || mb[j] != 0) ? 1u : 0u) << j;
-            }
+            const unsigned char* mp = mrow + (size_t)p0 * ka.mask_bytes;
+            const bool vec = row_ok && p0 + 32 <= kv_len && ((reinterpret_cast<uintptr_t>(mp) & 15u) == 0);
+            uint32_t bits = mask_bits32(mp, ka.mask_bytes, vec,
+                                        [&](int j) { return p0 + j >= prefix && p0 + j < kv_len && row_ok; });
+            if (p0 < prefix) bits |= prefix - p0 >= 32 ? 0xffffffffu : (1u << (prefix - p0)) - 1u;  // the prefix is seen
+            if (p0 + 32 > kv_len) bits &= kv_len <= p0 ? 0u : (kv_len - p0 >= 32 ? 0xffffffffu : (1u << (kv_len - p0)) - 1u);
+            if (!row_ok) bits = p0 >= prefix ? 0u : (prefix - p0 >= 32 ? 0xffffffffu : (1u << (prefix - p0)) - 1u);
             vis[c] = bits;
           }
         }
@@ -527,10 +577,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     const int gw = warp - kTcLoadWarp0;
     const int chunk = lane & 15, sub = lane >> 4;  // row-by-row copies: 16 lanes per row, two rows per pass
     const uint32_t dst_half = (uint32_t)((chunk >> 3) * kTcHalfBytes);
-    const size_t row_bytes = (size_t)a.num_kv_heads * kD * 2;   // one cache row, all KV heads
-    const size_t kv_plane = (size_t)a.page_len * row_bytes;     // K (or V) of one page
-    const unsigned char* pool = reinterpret_cast<const unsigned char*>(a.pool) +
-                                (size_t)a.layer * a.num_pages * 2 * kv_plane + (size_t)kvh * kD * 2 + chunk * 16;
+    const unsigned char* kbase = ka.k_base + (size_t)kvh * ka.head_stride + chunk * 16;  // this lane's 16 bytes of a row
+    const unsigned char* vbase = ka.v_base + (size_t)kvh * ka.head_stride + chunk * 16;
     const int* table = a.page_table + (size_t)b * a.pages_per_seq;
     TcRingPos wr;            // the entry about to be produced (by this warp or the other)
     TcRingPos q0, q1, q2;    // this warp's row-by-row entries committed and not yet handed over, oldest first
@@ -545,7 +593,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     auto page_of = [&](int t) -> int {
       const int kpos = t * kTcKeys + tj * ka.box_rows;
       if (!tma_lane || (t + 1) * kTcKeys > kv_len) return -1;
-      return table[ka.page_shift >= 0 ? kpos >> ka.page_shift : kpos / a.page_len];
+      return ka.identity_table ? b : table[ka.page_shift >= 0 ? kpos >> ka.page_shift : kpos / a.page_len];
     };
     auto hand_over_oldest = [&]() {
       if (lane == 0) mbar_arrive(&full[q0.s]);
@@ -578,30 +626,32 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             flag(a.dev_status, SUBSPEC_DEV_BAD_PAGE);
             page = a.num_pages;  // outside the tensor: the copy unit fills zeros and touches no memory
           }
-          tma_load_5d(ring + (size_t)at.s * kTcTileBytes + thalf * kTcHalfBytes + (size_t)tj * ka.box_rows * 128, &tmap,
-                      thalf * 64, kvh, kpos - pi * a.page_len, is_v, page, &full[at.s]);
+          const int slot = kpos - pi * a.page_len;
+          tma_load_4d(ring + (size_t)at.s * kTcTileBytes + thalf * kTcHalfBytes + (size_t)tj * ka.box_rows * 128,
+                      is_v ? &tmap_v : &tmap_k, thalf * 64, ka.rows_before_heads ? slot : kvh,
+                      ka.rows_before_heads ? kvh : slot, page, &full[at.s]);
         }
         return;
       }
       // The last, partial tile (or a page length the tensor copies do not suit): 16-byte copies, row by row
-      const size_t plane_off = is_v ? kv_plane : 0;
+      const unsigned char* base = is_v ? vbase : kbase;
       unsigned char* dst = ring + (size_t)at.s * kTcTileBytes + dst_half;
 #pragma unroll 4
       for (int pass = 0; pass < kTcKeys / 2; ++pass) {
         const int rr = pass * 2 + sub;
         const int kpos = t0 + rr;
-        const unsigned char* src = pool;
+        const unsigned char* src = base;
         int bytes = 0;
         if (kpos < kv_len) {
           const int pi = ka.page_shift >= 0 ? kpos >> ka.page_shift : kpos / a.page_len;
-          int pg = table[pi];
+          int pg = ka.identity_table ? b : table[pi];
           if (pg < 0 || pg >= a.num_pages) {
             flag(a.dev_status, SUBSPEC_DEV_BAD_PAGE);
             pg = 0;
           } else {
             bytes = 16;
           }
-          src = pool + (size_t)pg * 2 * kv_plane + plane_off + (size_t)(kpos - pi * a.page_len) * row_bytes;
+          src = base + (size_t)pg * ka.page_stride + (size_t)(kpos - pi * a.page_len) * ka.row_stride;
         }
         cp_async16(dst + rr * 128 + (((chunk & 7) ^ (rr & 7)) << 4), src, bytes);  // rows past the end: zeros
       }
@@ -712,16 +762,39 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
     return SUBSPEC_EINVAL;
   if (a.head_dim != kD || a.num_q_heads % a.num_kv_heads) return SUBSPEC_EUNSUPPORTED;
   if (a.dtype != 0 && a.dtype != SUBSPEC_BF16 && a.dtype != SUBSPEC_F16) return SUBSPEC_EINVAL;
+  if (a.mask_kind != SUBSPEC_MASK_BOOL && a.mask_kind != SUBSPEC_MASK_ADD_F32 && a.mask_kind != SUBSPEC_MASK_ADD_BF16 &&
+      a.mask_kind != SUBSPEC_MASK_ADD_F16)
+    return SUBSPEC_EINVAL;
   if (a.batch == 0) return SUBSPEC_OK;
-  if (!a.q || !a.out || !a.pool || !a.page_table || !a.kv_len || !a.mask) return SUBSPEC_EINVAL;
+  const bool hf = a.v_cache != nullptr;  // key / value tensors of a static cache instead of the paged pool
+  if (!a.q || !a.out || !a.pool || !a.kv_len || !a.mask || (!hf && !a.page_table)) return SUBSPEC_EINVAL;
+  if (hf && (a.pages_per_seq != 1 || a.num_pages < a.batch || a.layer != 0 || a.kv_row_stride < kD ||
+             a.kv_head_stride < 0 || a.kv_batch_stride < 0))
+    return SUBSPEC_EINVAL;
   if (!(a.sm_scale > 0.0)) return SUBSPEC_EINVAL;
-  // 32-bit loads of query / output pairs, 16-byte copies of cache rows
-  if ((reinterpret_cast<uintptr_t>(a.q) & 3u) || (reinterpret_cast<uintptr_t>(a.out) & 3u) ||
-      (reinterpret_cast<uintptr_t>(a.pool) & 15u) || (a.q_token_stride & 1) || (a.q_head_stride & 1) ||
-      (a.q_batch_stride & 1) || (a.o_token_stride & 1) || (a.o_head_stride & 1) || (a.o_batch_stride & 1))
-    return SUBSPEC_EUNSUPPORTED;
   AttnArgs ka;
   ka.a = a;
+  ka.mask_bytes = a.mask_kind == SUBSPEC_MASK_BOOL ? 1 : (a.mask_kind == SUBSPEC_MASK_ADD_F32 ? 4 : 2);
+  if (hf) {
+    ka.k_base = reinterpret_cast<const unsigned char*>(a.pool);
+    ka.v_base = reinterpret_cast<const unsigned char*>(a.v_cache);
+    ka.page_stride = 2 * a.kv_batch_stride, ka.row_stride = 2 * a.kv_row_stride, ka.head_stride = 2 * a.kv_head_stride;
+    ka.identity_table = a.page_table == nullptr;
+  } else {
+    const long long row_bytes = (long long)a.num_kv_heads * kD * 2, plane = (long long)a.page_len * row_bytes;
+    ka.k_base = reinterpret_cast<const unsigned char*>(a.pool) + (size_t)a.layer * a.num_pages * 2 * plane;
+    ka.v_base = ka.k_base + plane;
+    ka.page_stride = 2 * plane, ka.row_stride = row_bytes, ka.head_stride = kD * 2;
+    ka.identity_table = 0;
+  }
+  // 32-bit loads of query / output pairs, 16-byte copies of cache rows, mask elements at their own alignment
+  if ((reinterpret_cast<uintptr_t>(a.q) & 3u) || (reinterpret_cast<uintptr_t>(a.out) & 3u) ||
+      (reinterpret_cast<uintptr_t>(ka.k_base) & 15u) || (reinterpret_cast<uintptr_t>(ka.v_base) & 15u) ||
+      (ka.page_stride & 15) || (ka.row_stride & 15) || (ka.head_stride & 15) || (a.q_token_stride & 1) ||
+      (a.q_head_stride & 1) || (a.q_batch_stride & 1) || (a.o_token_stride & 1) || (a.o_head_stride & 1) ||
+      (a.o_batch_stride & 1) || (reinterpret_cast<uintptr_t>(a.mask) & (uintptr_t)(ka.mask_bytes - 1)))
+    return SUBSPEC_EUNSUPPORTED;
+  ka.rows_before_heads = ka.row_stride < ka.head_stride;
   ka.group = a.num_q_heads / a.num_kv_heads;
   ka.scale_log2 = (float)(a.sm_scale * 1.4426950408889634);
   ka.page_shift = -1;
@@ -733,11 +806,12 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
   const int rc = cuda_check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
   if (rc) return rc;
   const dim3 grid((unsigned)((ka.group * a.q_len + kTcRows - 1) / kTcRows), (unsigned)a.num_kv_heads, (unsigned)a.batch);
-  // The tensor map of this layer's slab of the pool: [page][K / V][slot][KV head][dim], bf16.  A box is 64 dims of
-  // box_rows consecutive slots of one page and one head; it exists when whole pages tile the 128 cache rows of a
-  // tile (or a page holds whole tiles) and the swizzle atom of 8 rows divides a page.
-  CUtensorMap tmap;
-  memset(&tmap, 0, sizeof(tmap));
+  // Tensor maps of the K and of the V rows: [page][row of the page][KV head][dim] with the strides above.  A box
+  // is 64 dims of box_rows consecutive rows of one page and one head; it exists when whole pages tile the 64
+  // cache rows of a tile (or a page holds whole tiles) and the swizzle atom of 8 rows divides a page.
+  CUtensorMap tmap_k, tmap_v;
+  memset(&tmap_k, 0, sizeof(tmap_k));
+  memset(&tmap_v, 0, sizeof(tmap_v));
   ka.box_rows = 0;
   int box = 0;
   if (a.page_len % 8 == 0) {
@@ -746,20 +820,23 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
     else if (a.page_len % kTcKeys == 0)
       box = kTcKeys;
   }
-  if (box && tensor_map_encoder()) {
-    const cuuint64_t row_bytes = (cuuint64_t)a.num_kv_heads * kD * 2, plane = (cuuint64_t)a.page_len * row_bytes;
-    const cuuint64_t dims[5] = {(cuuint64_t)kD, (cuuint64_t)a.num_kv_heads, (cuuint64_t)a.page_len, 2, (cuuint64_t)a.num_pages};
-    const cuuint64_t strides[4] = {(cuuint64_t)kD * 2, row_bytes, plane, 2 * plane};
-    const cuuint32_t boxdim[5] = {64, 1, (cuuint32_t)box, 1, 1};
-    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-    void* base = const_cast<unsigned char*>(reinterpret_cast<const unsigned char*>(a.pool)) +
-                 (size_t)a.layer * a.num_pages * 2 * plane;
-    if (tensor_map_encoder()(&tmap, half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, base, dims, strides, boxdim, estr,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
-      ka.box_rows = box;
+  if (box && tensor_map_encoder() && ka.head_stride > 0 && ka.page_stride > 0) {
+    const bool rbh = ka.rows_before_heads != 0;
+    const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)(rbh ? a.page_len : a.num_kv_heads),
+                                (cuuint64_t)(rbh ? a.num_kv_heads : a.page_len), (cuuint64_t)a.num_pages};
+    const cuuint64_t strides[3] = {(cuuint64_t)(rbh ? ka.row_stride : ka.head_stride),
+                                   (cuuint64_t)(rbh ? ka.head_stride : ka.row_stride), (cuuint64_t)ka.page_stride};
+    const cuuint32_t boxdim[4] = {64, rbh ? (cuuint32_t)box : 1u, rbh ? 1u : (cuuint32_t)box, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUtensorMapDataType dt = half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    auto encode = [&](CUtensorMap* m, const unsigned char* base) {
+      return tensor_map_encoder()(m, dt, 4, const_cast<unsigned char*>(base), dims, strides, boxdim, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    };
+    if (encode(&tmap_k, ka.k_base) && encode(&tmap_v, ka.v_base)) ka.box_rows = box;
   }
-  kernel<<<grid, kTcThreads, kTcSmem, st>>>(ka, tmap);
+  kernel<<<grid, kTcThreads, kTcSmem, st>>>(ka, tmap_k, tmap_v);
   return cuda_check(cudaGetLastError());
 }
 

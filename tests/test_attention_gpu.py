@@ -4,7 +4,7 @@ import torch
 
 from oracle import attention_oracle as ao
 from subspec_b200 import synthetic
-from subspec_b200.attention import append_paged_kv, tree_attention_paged
+from subspec_b200.attention import append_paged_kv, tree_attention_paged, tree_attention_static
 from subspec_b200.tree import Tree
 from tests import golden_io
 
@@ -201,3 +201,33 @@ def test_against_sdpa_goldens(cuda_lib):
         tol = 2e-2 if case["dtype"] == "bfloat16" else 3e-3
         assert float((got - exact).abs().max()) < tol * float(exact.abs().max()), case["name"]
         assert float((got - native).abs().max()) < 2 * tol * float(exact.abs().max()), case["name"]
+
+
+@pytest.mark.parametrize("mask_dtype", [torch.bool, torch.float32, torch.bfloat16, torch.float16])
+def test_static_caches_against_sdpa_goldens(cuda_lib, mask_dtype):
+    """The Hugging Face layout -- q [batch, heads, tokens, dim], key / value caches [batch, kv_heads, rows, dim],
+    the mask in the `[1, 1, max_verify, max_cache_len]` buffer, bool or as invert_mask leaves it -- against torch
+    SDPA on the reference's masks.  Cache lengths that are multiples of 64 (tensor copies) and not."""
+    dev = "cuda"
+    for case in golden_io.attention_cases():
+        if case["dtype"] == "float32":
+            continue
+        st, q, k, v, mask, exact, native = golden_io.attention_golden(case)
+        n_q, n = case["n_q"], case["prefix"] + case["n_q"]
+        for max_len in (((n + 63) // 64 + 1) * 64, n + 5):
+            B = 2  # the request sits in entry 1 of a two-entry cache; entry 0 holds another, shorter one
+            kc = torch.randn(B, case["kv_heads"], max_len, 128).to(q.dtype)
+            vc = torch.randn(B, case["kv_heads"], max_len, 128).to(q.dtype)
+            kc[1, :, :n], vc[1, :, :n] = k.permute(1, 0, 2), v.permute(1, 0, 2)
+            qq = torch.randn(B, case["q_heads"], n_q, 128).to(q.dtype)
+            qq[1] = q.permute(1, 0, 2)
+            buf = torch.zeros(1, 1, n_q + 3, max_len, dtype=torch.bool)  # a static buffer larger than the tree
+            buf[0, 0, :n_q, :n] = mask
+            if mask_dtype != torch.bool:
+                buf = (~buf).to(mask_dtype) * torch.finfo(mask_dtype).min  # invert_mask
+            kv_len = torch.tensor([min(n, 7), n], dtype=torch.int32, device=dev)
+            nq = torch.tensor([min(n_q, min(n, 7)), n_q], dtype=torch.int32, device=dev)
+            out = tree_attention_static(qq.to(dev), kc.to(dev), vc.to(dev), kv_len=kv_len, n_q=nq, mask=buf.to(dev))
+            got = out[1].permute(1, 0, 2).float().cpu()
+            tol = 2e-2 if case["dtype"] == "bfloat16" else 3e-3
+            assert float((got - exact).abs().max()) < tol * float(exact.abs().max()), (case["name"], max_len)

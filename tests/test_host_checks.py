@@ -68,7 +68,7 @@ def test_attention_wrapper_rejects_bad_arguments():
     with pytest.raises(ValueError, match="head_dim"):
         tree_attention_paged(q[..., :64].contiguous(), pool, 0, **kw)
     with pytest.raises(ValueError, match="mask"):
-        tree_attention_paged(q, pool, 0, page_table=table, kv_len=kv_len, mask=mask.float())
+        tree_attention_paged(q, pool, 0, page_table=table, kv_len=kv_len, mask=mask.long())
     with pytest.raises(ValueError, match="mask"):
         tree_attention_paged(q, pool, 0, page_table=table, kv_len=kv_len, mask=mask[:, :4])
     with pytest.raises(ValueError, match="page_table"):
@@ -78,3 +78,12 @@ def test_attention_wrapper_rejects_bad_arguments():
     k = torch.zeros(B, QL, H, D, dtype=torch.bfloat16)
     with pytest.raises(ValueError):
         append_paged_kv(pool, 0, k, k.half(), page_table=table, kv_len=kv_len)
+    from subspec_b200.attention import tree_attention_static
+    qh = torch.zeros(B, HQ, QL, D, dtype=torch.bfloat16)
+    kc = torch.zeros(B, H, 64, D, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="same type"):
+        tree_attention_static(qh, kc, kc.half(), kv_len=kv_len, mask=mask)
+    with pytest.raises(ValueError, match="one shape"):
+        tree_attention_static(qh, kc, kc[:, :, :32], kv_len=kv_len, mask=mask)
+    with pytest.raises(ValueError, match="mask"):
+        tree_attention_static(qh, kc, kc, kv_len=kv_len, mask=mask.long())
