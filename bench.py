@@ -401,10 +401,26 @@ def extra_attention(device, peak_gbs, peak_tf, batch=64):
     flops = 4.0 * batch * QL * HQ * kv * D
     nbytes = batch * (2 * kv * HKV * D * 2 + 2 * QL * HQ * D * 2)
     t_roof = max(nbytes / (peak_gbs * 1e9), flops / (peak_tf * 1e12))
-    return {"tree_attention_layer_config5": {
+    res = {"tree_attention_layer_config5": {
         "ms": ms, "TFLOP/s": flops / (ms * 1e-3) / 1e12, "GB/s": nbytes / (ms * 1e-3) / 1e9,
         "roofline_ms": t_roof * 1e3, "frac": t_roof / (ms * 1e-3), "bound": "tensor",
         "path": "tcgen05 (S and O in tensor memory, K/V tiles by tensor copies)", "requests": batch}}
+    del pool, table
+    # the same problem on the static caches of the reference's default path, with the additive mask, and what
+    # that path itself runs there: torch's scaled_dot_product_attention (repeat_kv done beforehand, not timed)
+    from subspec_b200.attention import tree_attention_static
+    qh = q.permute(0, 2, 1, 3).contiguous()
+    kc = torch.empty(batch, HKV, kv, D, dtype=torch.bfloat16, device=device).normal_()
+    vc = torch.empty(batch, HKV, kv, D, dtype=torch.bfloat16, device=device).normal_()
+    add = (~mask[:1, None]).to(torch.bfloat16) * torch.finfo(torch.bfloat16).min
+    ms_s = _time_ms(lambda: tree_attention_static(qh, kc, vc, kv_len=kv_len, mask=add), iters=20, warm=3)
+    kk, vv = kc.repeat_interleave(HQ // HKV, dim=1), vc.repeat_interleave(HQ // HKV, dim=1)
+    sdpa = torch.nn.functional.scaled_dot_product_attention
+    ms_t = _time_ms(lambda: sdpa(qh, kk, vv, attn_mask=add), iters=10, warm=3)
+    res["tree_attention_layer_config5"]["static_caches"] = {
+        "ms": ms_s, "TFLOP/s": flops / (ms_s * 1e-3) / 1e12, "mask": "additive bf16 [1,1,q,kv]",
+        "torch_sdpa_ms": ms_t, "note": "torch_sdpa_ms is the library call the reference's default path makes, beside ours"}
+    return res
 
 
 def extra_expand(device, peak_gbs):
