@@ -1,11 +1,13 @@
-// Tree attention over the paged KV cache, and the append of the tree's own K / V rows to it.
+// Tree attention over the KV cache, and the append of the tree's own K / V rows to the paged cache.
 //
 // Reference: the FlashInfer path of the generators -- append_paged_kv_cache followed by
 // BatchPrefillWithPagedKVCacheWrapper.run with a custom mask
 // (specdecodes/models/utils/flashinfer/attention_wrapper.py:104-151, 234-253, 288-316;
-//  specdecodes/models/utils/flashinfer/attention.py:26-102).  The tree's tokens are the queries; every one of
-// them sees the whole committed prefix and, among the tree's rows, itself and its ancestors (the mask the tree
-// finaliser writes: prefix ones | ancestor-or-self columns | zeros).
+//  specdecodes/models/utils/flashinfer/attention.py:26-102) -- and, on the default path, the model's
+// scaled_dot_product_attention over the static caches (specdecodes/models/utils/cache_utils.py, TreeStaticCache)
+// with the additive mask the generators splice into their static buffer (generators/classic_sd.py:57-89).  The
+// tree's tokens are the queries; every one of them sees the whole committed prefix and, among the tree's rows,
+// itself and its ancestors (the mask the tree finaliser writes: prefix ones | ancestor-or-self columns | zeros).
 //
 // The rows of the attention problem are (head of the GQA group, tree token) pairs, so the query heads that share
 // a KV head share its K / V tiles.  The kernel runs on the tcgen05 tensor cores; its layout is described where
@@ -48,8 +50,8 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
 }
 
 // 2^x for a pair of exponents without the special-function unit: x = n + f with n = round(x), f in [-0.5, 0.5];
-// 2^f by a cubic (relative error below 8e-5, a twenty-fifth of what rounding P to bf16 costs), n added into
-// the exponent field.  The magic constant 1.5 * 2^23 leaves n in the low mantissa bits of x + magic.
+// 2^f by a cubic (relative error below 8e-5: a twenty-fifth of what rounding P to bf16 costs, a sixth for fp16),
+// n added into the exponent field.  The magic constant 1.5 * 2^23 leaves n in the low mantissa bits of x + magic.
 __device__ __forceinline__ void exp2_pair_fma(float x0, float x1, float& p0, float& p1) {
   const uint64_t xc = f2_pack(fmaxf(x0, -125.f), fmaxf(x1, -125.f));  // -inf (masked away later) and underflow
   const uint64_t magic = f2_pack(12582912.f, 12582912.f), nmagic = f2_pack(-12582912.f, -12582912.f);
@@ -87,9 +89,10 @@ struct AttnArgs {
 // and tiles of 64 cache rows.
 //
 //   warps 0-7   softmax, four warps per row block: thread = query row = lane of tensor memory.  Per tile a
-//               thread reads its row of S (tcgen05.ld), keeps the running maximum and sum, rescales its row of O
-//               in tensor memory when the maximum of some row of the warp has run far enough ahead, and writes
-//               P = exp2(S c - m) as packed bf16 over the first half of the S columns it has just read.
+//               thread reads its row of S (tcgen05.ld) and writes P = exp2(S c - m) as packed 16-bit values
+//               over the first half of the S columns it has just read, keeping the row sum; m, the reference
+//               point of the row's exponents, moves (and the row of O in tensor memory is rescaled) only when
+//               the row's maximum has run more than 2^8 ahead of it.
 //   warps 8, 9  one MMA issuer per row block (an elected thread).  S = Q K^T: A = the block's Q tile, B = the K
 //               tile, both K-major in shared memory.  O += P V: A = P from tensor memory, B = the V tile,
 //               MN-major: V lies [cache row][dim] as the cache has it, so K and V tiles share one shared-memory
