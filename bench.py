@@ -417,6 +417,30 @@ def extra_attention(device, peak_gbs, peak_tf, batch=64):
     kk, vv = kc.repeat_interleave(HQ // HKV, dim=1), vc.repeat_interleave(HQ // HKV, dim=1)
     sdpa = torch.nn.functional.scaled_dot_product_attention
     ms_t = _time_ms(lambda: sdpa(qh, kk, vv, attn_mask=add), iters=10, warm=3)
+    # one request alone (the reference's own setting): device time inside a CUDA graph of ten calls; the cache
+    # rows are cut into ranges for several CTAs and merged (the wrapper's default for few requests)
+    def graph_us(fn):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for _ in range(10):
+                fn()
+        gr.replay()
+        torch.cuda.synchronize()
+        return _time_ms(gr.replay, iters=5, warm=1) * 100.0  # us per call
+
+    one = {}
+    q1, k1, v1, len1, o1 = qh[:1], kc[:1], vc[:1], kv_len[:1], torch.empty_like(qh[:1])
+    for name, sp in (("whole_cache_per_cta_us", 1), ("split_ranges_us", None)):
+        one[name] = graph_us(lambda: tree_attention_static(q1, k1, v1, kv_len=len1, mask=add, out=o1, kv_splits=sp))
+    kk1, vv1 = kk[:1], vv[:1]
+    one["torch_sdpa_us"] = graph_us(lambda: sdpa(q1, kk1, vv1, attn_mask=add))
+    res["tree_attention_layer_config5"]["one_request"] = one
     res["tree_attention_layer_config5"]["static_caches"] = {
         "ms": ms_s, "TFLOP/s": flops / (ms_s * 1e-3) / 1e12, "mask": "additive bf16 [1,1,q,kv]",
         "torch_sdpa_ms": ms_t, "note": "torch_sdpa_ms is the library call the reference's default path makes, beside ours"}

@@ -670,6 +670,13 @@ typedef struct subspec_tree_attn_args {
    * entry b), layer = 0 and layers = 1.  Strides in elements; heads' rows must be head_dim apart or more. */
   const void* v_cache;
   int64_t kv_batch_stride, kv_head_stride, kv_row_stride;
+  /* kv_splits > 1: that many CTAs share the cache rows of every (request, KV head, 256 query rows) and a second
+   * kernel combines their partial results -- for a few requests with long caches, which would otherwise occupy
+   * batch * num_kv_heads CTAs.  split_scratch: batch * num_q_heads * q_len * kv_splits * 130 floats, 16-byte
+   * aligned, owned by the call until the stream has passed it. */
+  int32_t kv_splits;
+  int32_t reserved;
+  void* split_scratch;
 } subspec_tree_attn_args;
 
 SUBSPEC_API int subspec_tree_attention_paged(const subspec_tree_attn_args* args, subspec_stream_t stream);

@@ -172,6 +172,7 @@ class TreeAttnArgs(C.Structure):
         ("o_batch_stride", _i64), ("o_token_stride", _i64), ("o_head_stride", _i64), ("sm_scale", _f64),
         ("dev_status", _vp), ("dtype", _i32), ("mask_kind", _i32), ("v_cache", _vp),
         ("kv_batch_stride", _i64), ("kv_head_stride", _i64), ("kv_row_stride", _i64),
+        ("kv_splits", _i32), ("reserved", _i32), ("split_scratch", _vp),
     ]
 
 

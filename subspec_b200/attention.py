@@ -31,6 +31,28 @@ _MASK_KINDS = {torch.bool: _lib.MASK_BOOL, torch.uint8: _lib.MASK_BOOL, torch.fl
                torch.bfloat16: _lib.MASK_ADD_BF16, torch.float16: _lib.MASK_ADD_F16}
 
 
+_SMS = 148  # B200
+
+
+def _split_cache(a, batch: int, q_heads: int, kv_heads: int, q_len: int, cap_rows: int, device, kv_splits):
+    """Few requests with long caches would keep batch * kv_heads CTAs busy: cut the cache rows of each into
+    `kv_splits` ranges (partial results combined by a second kernel).  None: as many as fill the SMs once, at
+    most one per four 64-row tiles of the cache's capacity and at most 16 (measured: a lone request behind 4096
+    rows 75 -> 25 us; more CTAs than SMs, or ranges of a tile or two, cost more than they bring).  Returns the
+    scratch tensor to keep alive."""
+    ctas = batch * kv_heads * ((q_heads // kv_heads * q_len + 255) // 256)
+    if kv_splits is None:
+        kv_splits = max(1, min(_SMS // max(ctas, 1), (cap_rows + 63) // 64 // 4, 16))
+    kv_splits = int(kv_splits)
+    if kv_splits < 1 or kv_splits > 1024:
+        raise ValueError("kv_splits must be between 1 and 1024")
+    if kv_splits == 1:
+        return None
+    scratch = torch.empty(batch * q_heads * q_len * kv_splits * 130, dtype=torch.float32, device=device)
+    a.kv_splits, a.split_scratch = kv_splits, scratch.data_ptr()
+    return scratch
+
+
 @torch.no_grad()
 def append_paged_kv(pool: torch.Tensor, layer: int, k: torch.Tensor, v: torch.Tensor, *, page_table: torch.Tensor,
                     kv_len: torch.Tensor, n_q: Optional[torch.Tensor] = None,
@@ -66,7 +88,8 @@ def append_paged_kv(pool: torch.Tensor, layer: int, k: torch.Tensor, v: torch.Te
 def tree_attention_paged(q: torch.Tensor, pool: torch.Tensor, layer: int, *, page_table: torch.Tensor,
                          kv_len: torch.Tensor, mask: torch.Tensor, n_q: Optional[torch.Tensor] = None,
                          prefix_len: Optional[torch.Tensor] = None, sm_scale: Optional[float] = None,
-                         status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                         kv_splits: Optional[int] = None) -> torch.Tensor:
     """q [batch, q_len, q_heads, 128] bf16 or fp16 (as the pool) -> attention output of the same shape (into `out` when given: a
     captured graph needs a buffer that outlives the capture).
 
@@ -109,9 +132,11 @@ def tree_attention_paged(q: torch.Tensor, pool: torch.Tensor, layer: int, *, pag
     a.sm_scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D)
     a.dtype = _lib.BF16 if q.dtype == torch.bfloat16 else _lib.F16
     a.dev_status = 0 if status is None else status.data_ptr()
+    scratch = _split_cache(a, B, HQ, int(H), QL, int(page_table.shape[1]) * int(page_len), pool.device, kv_splits)
     stream = torch.cuda.current_stream(pool.device).cuda_stream
     _lib.check(_lib.lib().subspec_tree_attention_paged(C.byref(a), C.c_void_p(stream)),
                "subspec_tree_attention_paged")
+    del scratch  # (torch's allocator keeps the block for this stream until the kernels have passed)
     return out
 
 
@@ -119,7 +144,8 @@ def tree_attention_paged(q: torch.Tensor, pool: torch.Tensor, layer: int, *, pag
 def tree_attention_static(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, *, kv_len: torch.Tensor,
                           mask: torch.Tensor, n_q: Optional[torch.Tensor] = None,
                           prefix_len: Optional[torch.Tensor] = None, sm_scale: Optional[float] = None,
-                          status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                          kv_splits: Optional[int] = None) -> torch.Tensor:
     """The same kernel over the static caches of the reference's default (Hugging Face) path: what
     `scaled_dot_product_attention(q, repeat_kv(k), repeat_kv(v), attn_mask=mask)` computes for the tree's tokens.
 
@@ -164,7 +190,9 @@ def tree_attention_static(q: torch.Tensor, key_cache: torch.Tensor, value_cache:
     a.sm_scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D)
     a.dtype = _lib.BF16 if q.dtype == torch.bfloat16 else _lib.F16
     a.dev_status = 0 if status is None else status.data_ptr()
+    scratch = _split_cache(a, B, HQ, H, QL, S, q.device, kv_splits)
     stream = torch.cuda.current_stream(q.device).cuda_stream
     _lib.check(_lib.lib().subspec_tree_attention_paged(C.byref(a), C.c_void_p(stream)),
                "subspec_tree_attention_paged")
+    del scratch
     return out

@@ -83,6 +83,9 @@ struct AttnArgs {
   int identity_table;
   int rows_before_heads;  // order of the two middle coordinates of the tensor maps (strides ascend in them)
   int mask_bytes;   // bytes per mask element: 1 (bool: non-zero = visible), 2 or 4 (additive: +-0 = visible)
+  int splits;       // CTAs that share the cache rows of one (request, KV head, 256 query rows); 1: none
+  float* part_o;    // splits > 1: [row][split][128] unnormalised outputs, row = (batch * q_heads + head) * q_len + token
+  float* part_ml;   //             [row][split][2]   reference point (log2 units) and sum of the split
 };
 
 // One CTA = 256 query rows of one (request, KV head) -- two blocks of 128 rows that share every K / V tile --
@@ -262,7 +265,11 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   const int b = blockIdx.z, kvh = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = ka.group, QL = a.q_len;
-  const int row0 = (int)blockIdx.x * kTcRows;
+  // With splits > 1, `splits` consecutive CTAs take consecutive ranges of the cache rows for the same query rows
+  // and leave unnormalised partial results, which a second kernel combines: a lone request has four KV heads'
+  // worth of CTAs otherwise, each walking the whole cache.
+  const int split = (int)blockIdx.x % ka.splits;
+  const int row0 = ((int)blockIdx.x / ka.splits) * kTcRows;
   if (row0 >= G * QL) return;
   const int nblk = row0 + kTcBlockRows < G * QL ? 2 : 1;  // the second row block may be empty
   int nq = a.n_q ? a.n_q[b] : QL;
@@ -275,15 +282,24 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   }
   int prefix = a.prefix_len ? a.prefix_len[b] : kv_len - nq;
   prefix = min(max(prefix, 0), kv_len);
-  const int ntiles = (kv_len + kTcKeys - 1) / kTcKeys;
+  const int all_tiles = (kv_len + kTcKeys - 1) / kTcKeys;
+  const int per_split = (all_tiles + ka.splits - 1) / ka.splits;
+  const int tb = split * per_split;                              // this CTA's first tile
+  const int ntiles = max(min(per_split, all_tiles - tb), 0);     // and how many it takes (t below counts from tb)
 
-  if (ntiles == 0) {  // nothing to attend to: zeros, as the sum of no terms
+  if (ntiles == 0) {  // nothing to attend to: zeros, as the sum of no terms (a split: sum 0, which the merge skips)
     if (threadIdx.x < kTcRows) {
       const int row = row0 + (int)threadIdx.x, rg = row / QL, ri = row - rg * QL;
       if (rg < G && ri < nq) {
-        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + (size_t)b * a.o_batch_stride +
-                           (size_t)ri * a.o_token_stride + (size_t)(kvh * G + rg) * a.o_head_stride;
-        for (int c = 0; c < kD / 2; ++c) reinterpret_cast<uint32_t*>(o)[c] = 0u;
+        if (ka.splits > 1) {
+          float* ml = ka.part_ml + ((((size_t)b * a.num_q_heads + kvh * G + rg) * QL + ri) * ka.splits + split) * 2;
+          ml[0] = -INFINITY;
+          ml[1] = 0.f;
+        } else {
+          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + (size_t)b * a.o_batch_stride +
+                             (size_t)ri * a.o_token_stride + (size_t)(kvh * G + rg) * a.o_head_stride;
+          for (int c = 0; c < kD / 2; ++c) reinterpret_cast<uint32_t*>(o)[c] = 0u;
+        }
       }
     }
     return;
@@ -355,7 +371,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         uint32_t ra[32], rb[32];
         tmem_ld32_async(s_addr, ra);
         tmem_ld32_async(s_addr + 32, rb);
-        const int t0 = t * kTcKeys;
+        const int t0 = (tb + t) * kTcKeys;
         const bool need_mask = t0 + kTcKeys > prefix;  // tiles inside the prefix are visible to every row
         uint32_t vis[2] = {0xffffffffu, 0xffffffffu};
         if (need_mask) {
@@ -488,12 +504,24 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         const float inv = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(a.out) + (size_t)b * a.o_batch_stride +
                                  (size_t)ri * a.o_token_stride + (size_t)(kvh * G + rg) * a.o_head_stride;
+        const size_t prow = (((size_t)b * a.num_q_heads + kvh * G + rg) * QL + ri) * ka.splits + split;
+        if (ka.splits > 1 && row_ok) {
+          ka.part_ml[prow * 2] = m;
+          ka.part_ml[prow * 2 + 1] = l;
+        }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
           tmem_ld32_async(o_addr + 32 * c, r);
           tmem_wait_ld_dep(r);
-          if (row_ok) {
+          if (ka.splits > 1) {  // the unnormalised row, for the merge
+            if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                reinterpret_cast<uint4*>(ka.part_o + prow * kD)[8 * c + j] =
+                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            }
+          } else if (row_ok) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 v;
@@ -594,8 +622,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     const int tj = lane >> 1, thalf = lane & 1;
     const bool tma_lane = ka.box_rows > 0 && tj * ka.box_rows < kTcKeys;
     auto page_of = [&](int t) -> int {
-      const int kpos = t * kTcKeys + tj * ka.box_rows;
-      if (!tma_lane || (t + 1) * kTcKeys > kv_len) return -1;
+      const int kpos = (tb + t) * kTcKeys + tj * ka.box_rows;
+      if (!tma_lane || (tb + t + 1) * kTcKeys > kv_len) return -1;
       return ka.identity_table ? b : table[ka.page_shift >= 0 ? kpos >> ka.page_shift : kpos / a.page_len];
     };
     auto hand_over_oldest = [&]() {
@@ -616,7 +644,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       const TcRingPos at = wr;
       wr.next();
       if (!mine) return;
-      const int t0 = t * kTcKeys;
+      const int t0 = (tb + t) * kTcKeys;
       if (ka.box_rows > 0 && t0 + kTcKeys <= kv_len) {
         // A whole tile of whole pages: lane 0 announces the bytes (the entry's one arrival); the first
         // 2 * (64 / box_rows) lanes issue one tensor copy each (a page's rows x 64 dims).
@@ -702,6 +730,39 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     tc_fence_after();
     tmem_dealloc(tmem, kTcCols);
   }
+}
+
+// Split cache ranges: one warp per (request, query head, token) adds up the splits' unnormalised rows, each
+// weighted by 2^(its reference point - the largest one), and divides by the likewise weighted sum of their sums.
+template <bool kHalf>
+__global__ void __launch_bounds__(128) attn_merge_kernel(const AttnArgs ka) {
+  const subspec_tree_attn_args& a = ka.a;
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const long long rows = (long long)a.batch * a.num_q_heads * a.q_len;
+  if (row >= rows) return;
+  const int i = (int)(row % a.q_len), h = (int)((row / a.q_len) % a.num_q_heads), b = (int)(row / ((long long)a.q_len * a.num_q_heads));
+  int nq = a.n_q ? a.n_q[b] : a.q_len;
+  if (i >= min(max(nq, 0), a.q_len)) return;
+  const float* ml = ka.part_ml + (size_t)row * ka.splits * 2;
+  float mstar = -INFINITY;
+  for (int s = 0; s < ka.splits; ++s)
+    if (ml[2 * s + 1] > 0.f) mstar = fmaxf(mstar, ml[2 * s]);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float lsum = 0.f;
+  for (int s = 0; s < ka.splits; ++s) {
+    const float l = ml[2 * s + 1];
+    if (!(l > 0.f)) continue;  // a split with nothing visible (or nothing at all) left no row behind
+    const float w = ex2f(ml[2 * s] - mstar);
+    const float4 o = reinterpret_cast<const float4*>(ka.part_o + ((size_t)row * ka.splits + s) * kD)[lane];
+    acc.x += w * o.x, acc.y += w * o.y, acc.z += w * o.z, acc.w += w * o.w;
+    lsum += w * l;
+  }
+  const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+  __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(a.out) + (size_t)b * a.o_batch_stride +
+                           (size_t)i * a.o_token_stride + (size_t)h * a.o_head_stride;
+  reinterpret_cast<uint2*>(out_row)[lane] =
+      make_uint2(pack16<kHalf>(acc.x * inv, acc.y * inv), pack16<kHalf>(acc.z * inv, acc.w * inv));
 }
 
 // The tree's own K / V rows into the cache: token i of request b goes to cache row kv_len[b] - n_q[b] + i.
@@ -798,6 +859,16 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
       (a.o_batch_stride & 1) || (reinterpret_cast<uintptr_t>(a.mask) & (uintptr_t)(ka.mask_bytes - 1)))
     return SUBSPEC_EUNSUPPORTED;
   ka.rows_before_heads = ka.row_stride < ka.head_stride;
+  ka.splits = a.kv_splits > 1 ? a.kv_splits : 1;
+  ka.part_o = nullptr, ka.part_ml = nullptr;
+  if (ka.splits > 1) {
+    if (!a.split_scratch || (reinterpret_cast<uintptr_t>(a.split_scratch) & 15u) || ka.splits > 1024) return SUBSPEC_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(a.out) & 7u) || (a.o_token_stride & 3) || (a.o_head_stride & 3) || (a.o_batch_stride & 3))
+      return SUBSPEC_EUNSUPPORTED;  // the merge stores four outputs at a time
+    const size_t rows = (size_t)a.batch * a.num_q_heads * a.q_len;
+    ka.part_o = reinterpret_cast<float*>(a.split_scratch);
+    ka.part_ml = ka.part_o + rows * ka.splits * kD;
+  }
   ka.group = a.num_q_heads / a.num_kv_heads;
   ka.scale_log2 = (float)(a.sm_scale * 1.4426950408889634);
   ka.page_shift = -1;
@@ -808,7 +879,8 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
   auto kernel = half ? tree_attn_tc_kernel<true> : tree_attn_tc_kernel<false>;
   const int rc = cuda_check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
   if (rc) return rc;
-  const dim3 grid((unsigned)((ka.group * a.q_len + kTcRows - 1) / kTcRows), (unsigned)a.num_kv_heads, (unsigned)a.batch);
+  const dim3 grid((unsigned)((ka.group * a.q_len + kTcRows - 1) / kTcRows * ka.splits), (unsigned)a.num_kv_heads,
+                  (unsigned)a.batch);
   // Tensor maps of the K and of the V rows: [page][row of the page][KV head][dim] with the strides above.  A box
   // is 64 dims of box_rows consecutive rows of one page and one head; it exists when whole pages tile the 64
   // cache rows of a tile (or a page holds whole tiles) and the swizzle atom of 8 rows divides a page.
@@ -840,6 +912,11 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
     if (encode(&tmap_k, ka.k_base) && encode(&tmap_v, ka.v_base)) ka.box_rows = box;
   }
   kernel<<<grid, kTcThreads, kTcSmem, st>>>(ka, tmap_k, tmap_v);
+  if (ka.splits > 1) {
+    const long long rows = (long long)a.batch * a.num_q_heads * a.q_len;
+    auto merge = half ? attn_merge_kernel<true> : attn_merge_kernel<false>;
+    merge<<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(ka);
+  }
   return cuda_check(cudaGetLastError());
 }
 

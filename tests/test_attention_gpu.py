@@ -32,7 +32,7 @@ def _case(seed, B, QL, HQ, HKV, prefix_lens, n_qs, page_len=16, layers=2, layer=
                 prefix=prefix_lens, layer=layer, page_len=page_len)
 
 
-def _run_and_check(c, tol=2e-2):
+def _run_and_check(c, tol=2e-2, kv_splits=None):
     dev = "cuda"
     pool = c["pool"].to(dev)
     table = c["table"].to(dev)
@@ -42,7 +42,7 @@ def _run_and_check(c, tol=2e-2):
     append_paged_kv(pool, c["layer"], c["k"].to(dev), c["v"].to(dev), page_table=table, kv_len=kv_len, n_q=n_q,
                     status=status)
     out = tree_attention_paged(c["q"].to(dev), pool, c["layer"], page_table=table, kv_len=kv_len,
-                               mask=c["mask"].to(dev), n_q=n_q, status=status)
+                               mask=c["mask"].to(dev), n_q=n_q, status=status, kv_splits=kv_splits)
     assert int(status.item()) == 0
     # the append: exactly the tree's rows changed, and they hold k / v bit for bit
     want_pool = c["pool"].clone()
@@ -109,6 +109,17 @@ def test_random_shapes(cuda_lib, seed):
     dtype = [torch.bfloat16, torch.float16][r(0, 1)]
     c = _case(2000 + seed, B=B, QL=QL, HQ=HQ, HKV=HKV, prefix_lens=prefix, n_qs=n_q, page_len=page_len, dtype=dtype)
     _run_and_check(c)
+
+
+@pytest.mark.parametrize("kv_splits", [1, 2, 5, 16, 40])
+def test_split_cache_ranges(cuda_lib, kv_splits):
+    """The cache rows of a request cut into ranges for several CTAs and merged (what a lone request with a long
+    cache gets by default): one range (no merge), ranges that end inside the prefix and inside the tree, more
+    ranges than tiles (empty ones), a request with an empty prefix beside a long one."""
+    c = _case(30 + kv_splits, B=2, QL=40, HQ=14, HKV=2, prefix_lens=[1500, 0], n_qs=[40, 23])
+    _run_and_check(c, kv_splits=kv_splits)
+    c = _case(31 + kv_splits, B=1, QL=64, HQ=28, HKV=4, prefix_lens=[4032], n_qs=[64], dtype=torch.float16)
+    _run_and_check(c, tol=4e-3, kv_splits=kv_splits)
 
 
 def test_fp16_pool(cuda_lib):
