@@ -632,7 +632,7 @@ SUBSPEC_API int subspec_pages_update(const subspec_pages_args* args, subspec_str
  * [batch, q_len, num_q_heads, head_dim] in the pool's type with element strides (any
  * order of the axes in memory, e.g. the [batch, heads, tokens, dim] of an SDPA call); query head h reads KV head h / (num_q_heads /
  * num_kv_heads).  Softmax in fp32, scores scaled by sm_scale; outputs within
- * the rounding of the 16-bit type of an fp32 evaluation.  head_dim = 128 only.
+ * the rounding of the 16-bit type of an fp32 evaluation.  head_dim 64 or 128.
  * ---------------------------------------------------------------------- */
 typedef struct subspec_tree_attn_args {
   uint32_t struct_size;
@@ -673,7 +673,8 @@ typedef struct subspec_tree_attn_args {
   /* kv_splits > 1: that many CTAs share the cache rows of every (request, KV head, 256 query rows) and a second
    * kernel combines their partial results -- for a few requests with long caches, which would otherwise occupy
    * batch * num_kv_heads CTAs.  split_scratch: batch * num_q_heads * q_len * kv_splits * 130 floats, 16-byte
-   * aligned, owned by the call until the stream has passed it. */
+   * aligned (head_dim + 2 floats per row and range would do), owned by the call until the stream has
+   * passed it. */
   int32_t kv_splits;
   int32_t reserved;
   void* split_scratch;

@@ -90,7 +90,7 @@ def tree_attention_paged(q: torch.Tensor, pool: torch.Tensor, layer: int, *, pag
                          prefix_len: Optional[torch.Tensor] = None, sm_scale: Optional[float] = None,
                          status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                          kv_splits: Optional[int] = None) -> torch.Tensor:
-    """q [batch, q_len, q_heads, 128] bf16 or fp16 (as the pool) -> attention output of the same shape (into `out` when given: a
+    """q [batch, q_len, q_heads, head_dim (64 or 128)] bf16 or fp16 (as the pool) -> attention output of the same shape (into `out` when given: a
     captured graph needs a buffer that outlives the capture).
 
     `mask` is bool / uint8 [batch or 1, q_len, cols >= kv_len] (a singleton head axis after the batch axis is
@@ -101,8 +101,8 @@ def tree_attention_paged(q: torch.Tensor, pool: torch.Tensor, layer: int, *, pag
         raise ValueError("q must be bf16 or fp16 [batch, q_len, q_heads, head_dim] and the pool of the same type")
     L, P, _, page_len, H, D = pool.shape
     B, QL, HQ, Dq = (int(x) for x in q.shape)
-    if Dq != D or q.stride(3) != 1:
-        raise ValueError("q's head_dim must equal the pool's and be contiguous")
+    if Dq != D or q.stride(3) != 1 or D not in (64, 128):
+        raise ValueError("q's head_dim must equal the pool's, be contiguous and be 64 or 128")
     if mask.dim() == 4 and mask.shape[1] == 1:
         mask = mask[:, 0]
     if mask.dim() != 3 or mask.shape[0] not in (1, B) or mask.shape[1] < QL or mask.stride(2) != 1 or \
@@ -162,8 +162,8 @@ def tree_attention_static(q: torch.Tensor, key_cache: torch.Tensor, value_cache:
         raise ValueError("q and the caches must be bf16 or fp16, all of the same type")
     B, HQ, QL, D = (int(x) for x in q.shape)
     Bk, H, S, Dk = (int(x) for x in key_cache.shape)
-    if Bk < B or Dk != D or q.stride(3) != 1 or key_cache.stride(3) != 1:
-        raise ValueError("the caches must hold the batch, share q's head_dim, and head_dim must be contiguous")
+    if Bk < B or Dk != D or q.stride(3) != 1 or key_cache.stride(3) != 1 or D not in (64, 128):
+        raise ValueError("the caches must hold the batch, share q's head_dim (64 or 128), and head_dim must be contiguous")
     if mask.dim() == 4 and mask.shape[1] == 1:
         mask = mask[:, 0]
     if mask.dim() != 3 or mask.shape[0] not in (1, B) or mask.shape[1] < QL or mask.stride(2) != 1 or \

@@ -26,7 +26,7 @@
 namespace subspec {
 namespace {
 
-constexpr int kD = 128;           // head dimension (the only one built)
+// Head dimensions 64 and 128 (kDim below); shared and tensor memory are laid out for 128 either way.
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)),
@@ -253,7 +253,7 @@ struct TcRingPos {
   }
 };
 
-template <bool kHalf>
+template <bool kHalf, int kDim>
 __global__ void __launch_bounds__(kTcThreads, 1)
     tree_attn_tc_kernel(const AttnArgs ka, const __grid_constant__ CUtensorMap tmap_k,
                         const __grid_constant__ CUtensorMap tmap_v) {
@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         } else {
           __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + (size_t)b * a.o_batch_stride +
                              (size_t)ri * a.o_token_stride + (size_t)(kvh * G + rg) * a.o_head_stride;
-          for (int c = 0; c < kD / 2; ++c) reinterpret_cast<uint32_t*>(o)[c] = 0u;
+          for (int c = 0; c < kDim / 2; ++c) reinterpret_cast<uint32_t*>(o)[c] = 0u;
         }
       }
     }
@@ -346,7 +346,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         src += 2 * ((size_t)b * a.q_batch_stride + (size_t)qi * a.q_token_stride + (size_t)(kvh * G + qg) * a.q_head_stride);
       unsigned char* d = qtiles + (size_t)(rr >> 7) * kTcQTileBytes + (rr & 127) * 128;
 #pragma unroll
-      for (int chunk = 0; chunk < 16; ++chunk)
+      for (int chunk = 0; chunk < kDim / 8; ++chunk)
         cp_async16(d + (chunk >> 3) * kTcQHalfBytes + (((chunk & 7) ^ (rr & 7)) << 4), src + chunk * 16, okr ? 16 : 0);
       cp_async_commit();
       cp_async_wait<0>();
@@ -471,7 +471,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             if (!live) break;
             tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < kDim / 32; ++c) {
               uint32_t rc[32];
               tmem_ld32_async(o_addr + 32 * c, rc);
               tmem_wait_ld_dep(rc);
@@ -510,7 +510,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           ka.part_ml[prow * 2 + 1] = l;
         }
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < kDim / 32; ++c) {
           uint32_t r[32];
           tmem_ld32_async(o_addr + 32 * c, r);
           tmem_wait_ld_dep(r);
@@ -518,7 +518,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             if (row_ok) {
 #pragma unroll
               for (int j = 0; j < 8; ++j)
-                reinterpret_cast<uint4*>(ka.part_o + prow * kD)[8 * c + j] =
+                reinterpret_cast<uint4*>(ka.part_o + prow * kDim)[8 * c + j] =
                     make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
             }
           } else if (row_ok) {
@@ -542,14 +542,14 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     const int blk = warp - kTcIssuerWarp;
     if (blk < nblk) {
       constexpr uint32_t idesc_s = tc_idesc(kTcBlockRows, kTcKeys, false, kHalf);
-      constexpr uint32_t idesc_o = tc_idesc(kTcBlockRows, kD, true, kHalf);
+      constexpr uint32_t idesc_o = tc_idesc(kTcBlockRows, kDim, true, kHalf);
       const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0) + (uint32_t)blk * kColBlock;
       const uint32_t q_u32 = smem_u32(qtiles) + (uint32_t)blk * kTcQTileBytes, ring_u32 = smem_u32(ring);
       // S = Q K^T: 8 steps of 16 dims; a step moves 32 bytes inside a 64-dim half, 4 steps per half
       auto issue_s = [&](int kstage, int buf) {
         const uint32_t kaddr = ring_u32 + (uint32_t)kstage * kTcTileBytes;
 #pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks)
+        for (int ks = 0; ks < kDim / 16; ++ks)
           tc_mma_f16_ss(tm + (uint32_t)(buf * kTcKeys), tc_desc(q_u32 + (uint32_t)((ks >> 2) * kTcQHalfBytes + (ks & 3) * 32), 16),
                         tc_desc(kaddr + (uint32_t)((ks >> 2) * kTcHalfBytes + (ks & 3) * 32), 16), idesc_s, ks > 0 ? 1u : 0u);
       };
@@ -620,7 +620,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     // a tile ahead of its first use: the look-up is a trip to memory, and the copies of an entry must not wait
     // for one each.  -1: no copy by this lane for that tile.
     const int tj = lane >> 1, thalf = lane & 1;
-    const bool tma_lane = ka.box_rows > 0 && tj * ka.box_rows < kTcKeys;
+    const bool tma_lane = ka.box_rows > 0 && tj * ka.box_rows < kTcKeys && thalf < kDim / 64;
     auto page_of = [&](int t) -> int {
       const int kpos = (tb + t) * kTcKeys + tj * ka.box_rows;
       if (!tma_lane || (tb + t + 1) * kTcKeys > kv_len) return -1;
@@ -648,7 +648,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       if (ka.box_rows > 0 && t0 + kTcKeys <= kv_len) {
         // A whole tile of whole pages: lane 0 announces the bytes (the entry's one arrival); the first
         // 2 * (64 / box_rows) lanes issue one tensor copy each (a page's rows x 64 dims).
-        if (lane == 0) mbar_expect_tx(&full[at.s], (uint32_t)kTcTileBytes);
+        if (lane == 0) mbar_expect_tx(&full[at.s], (uint32_t)(kDim / 64 * kTcHalfBytes));
         __syncwarp();
         if (tma_lane) {
           const int kpos = t0 + tj * ka.box_rows;
@@ -684,7 +684,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           }
           src = base + (size_t)pg * ka.page_stride + (size_t)(kpos - pi * a.page_len) * ka.row_stride;
         }
-        cp_async16(dst + rr * 128 + (((chunk & 7) ^ (rr & 7)) << 4), src, bytes);  // rows past the end: zeros
+        if (chunk < kDim / 8)
+          cp_async16(dst + rr * 128 + (((chunk & 7) ^ (rr & 7)) << 4), src, bytes);  // rows past the end: zeros
       }
       cp_async_commit();
       if (pending == 0)
@@ -734,7 +735,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 
 // Split cache ranges: one warp per (request, query head, token) adds up the splits' unnormalised rows, each
 // weighted by 2^(its reference point - the largest one), and divides by the likewise weighted sum of their sums.
-template <bool kHalf>
+template <bool kHalf, int kDim>
 __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnArgs ka) {
   const subspec_tree_attn_args& a = ka.a;
   const int lane = threadIdx.x & 31;
@@ -754,15 +755,17 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnArgs ka) {
     const float l = ml[2 * s + 1];
     if (!(l > 0.f)) continue;  // a split with nothing visible (or nothing at all) left no row behind
     const float w = ex2f(ml[2 * s] - mstar);
-    const float4 o = reinterpret_cast<const float4*>(ka.part_o + ((size_t)row * ka.splits + s) * kD)[lane];
+    const float4 o = lane < kDim / 4 ? reinterpret_cast<const float4*>(ka.part_o + ((size_t)row * ka.splits + s) * kDim)[lane]
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
     acc.x += w * o.x, acc.y += w * o.y, acc.z += w * o.z, acc.w += w * o.w;
     lsum += w * l;
   }
   const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
   __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(a.out) + (size_t)b * a.o_batch_stride +
                            (size_t)i * a.o_token_stride + (size_t)h * a.o_head_stride;
-  reinterpret_cast<uint2*>(out_row)[lane] =
-      make_uint2(pack16<kHalf>(acc.x * inv, acc.y * inv), pack16<kHalf>(acc.z * inv, acc.w * inv));
+  if (lane < kDim / 4)
+    reinterpret_cast<uint2*>(out_row)[lane] =
+        make_uint2(pack16<kHalf>(acc.x * inv, acc.y * inv), pack16<kHalf>(acc.z * inv, acc.w * inv));
 }
 
 // The tree's own K / V rows into the cache: token i of request b goes to cache row kv_len[b] - n_q[b] + i.
@@ -824,7 +827,8 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
   if (a.batch < 0 || a.q_len < 1 || a.num_q_heads < 1 || a.num_kv_heads < 1 || a.layers < 1 || a.layer < 0 ||
       a.layer >= a.layers || a.num_pages < 1 || a.page_len < 1 || a.pages_per_seq < 1)
     return SUBSPEC_EINVAL;
-  if (a.head_dim != kD || a.num_q_heads % a.num_kv_heads) return SUBSPEC_EUNSUPPORTED;
+  if ((a.head_dim != 64 && a.head_dim != 128) || a.num_q_heads % a.num_kv_heads) return SUBSPEC_EUNSUPPORTED;
+  const int hd = a.head_dim;
   if (a.dtype != 0 && a.dtype != SUBSPEC_BF16 && a.dtype != SUBSPEC_F16) return SUBSPEC_EINVAL;
   if (a.mask_kind != SUBSPEC_MASK_BOOL && a.mask_kind != SUBSPEC_MASK_ADD_F32 && a.mask_kind != SUBSPEC_MASK_ADD_BF16 &&
       a.mask_kind != SUBSPEC_MASK_ADD_F16)
@@ -832,7 +836,7 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
   if (a.batch == 0) return SUBSPEC_OK;
   const bool hf = a.v_cache != nullptr;  // key / value tensors of a static cache instead of the paged pool
   if (!a.q || !a.out || !a.pool || !a.kv_len || !a.mask || (!hf && !a.page_table)) return SUBSPEC_EINVAL;
-  if (hf && (a.pages_per_seq != 1 || a.num_pages < a.batch || a.layer != 0 || a.kv_row_stride < kD ||
+  if (hf && (a.pages_per_seq != 1 || a.num_pages < a.batch || a.layer != 0 || a.kv_row_stride < hd ||
              a.kv_head_stride < 0 || a.kv_batch_stride < 0))
     return SUBSPEC_EINVAL;
   if (!(a.sm_scale > 0.0)) return SUBSPEC_EINVAL;
@@ -845,10 +849,10 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
     ka.page_stride = 2 * a.kv_batch_stride, ka.row_stride = 2 * a.kv_row_stride, ka.head_stride = 2 * a.kv_head_stride;
     ka.identity_table = a.page_table == nullptr;
   } else {
-    const long long row_bytes = (long long)a.num_kv_heads * kD * 2, plane = (long long)a.page_len * row_bytes;
+    const long long row_bytes = (long long)a.num_kv_heads * hd * 2, plane = (long long)a.page_len * row_bytes;
     ka.k_base = reinterpret_cast<const unsigned char*>(a.pool) + (size_t)a.layer * a.num_pages * 2 * plane;
     ka.v_base = ka.k_base + plane;
-    ka.page_stride = 2 * plane, ka.row_stride = row_bytes, ka.head_stride = kD * 2;
+    ka.page_stride = 2 * plane, ka.row_stride = row_bytes, ka.head_stride = hd * 2;
     ka.identity_table = 0;
   }
   // 32-bit loads of query / output pairs, 16-byte copies of cache rows, mask elements at their own alignment
@@ -867,7 +871,7 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
       return SUBSPEC_EUNSUPPORTED;  // the merge stores four outputs at a time
     const size_t rows = (size_t)a.batch * a.num_q_heads * a.q_len;
     ka.part_o = reinterpret_cast<float*>(a.split_scratch);
-    ka.part_ml = ka.part_o + rows * ka.splits * kD;
+    ka.part_ml = ka.part_o + rows * ka.splits * hd;
   }
   ka.group = a.num_q_heads / a.num_kv_heads;
   ka.scale_log2 = (float)(a.sm_scale * 1.4426950408889634);
@@ -876,7 +880,8 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
     if ((1 << sft) == a.page_len) ka.page_shift = sft;
   const cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool half = a.dtype == SUBSPEC_F16;
-  auto kernel = half ? tree_attn_tc_kernel<true> : tree_attn_tc_kernel<false>;
+  auto kernel = hd == 128 ? (half ? tree_attn_tc_kernel<true, 128> : tree_attn_tc_kernel<false, 128>)
+                          : (half ? tree_attn_tc_kernel<true, 64> : tree_attn_tc_kernel<false, 64>);
   const int rc = cuda_check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem));
   if (rc) return rc;
   const dim3 grid((unsigned)((ka.group * a.q_len + kTcRows - 1) / kTcRows * ka.splits), (unsigned)a.num_kv_heads,
@@ -897,7 +902,7 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
   }
   if (box && tensor_map_encoder() && ka.head_stride > 0 && ka.page_stride > 0) {
     const bool rbh = ka.rows_before_heads != 0;
-    const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)(rbh ? a.page_len : a.num_kv_heads),
+    const cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)(rbh ? a.page_len : a.num_kv_heads),
                                 (cuuint64_t)(rbh ? a.num_kv_heads : a.page_len), (cuuint64_t)a.num_pages};
     const cuuint64_t strides[3] = {(cuuint64_t)(rbh ? ka.row_stride : ka.head_stride),
                                    (cuuint64_t)(rbh ? ka.head_stride : ka.row_stride), (cuuint64_t)ka.page_stride};
@@ -914,7 +919,8 @@ extern "C" int subspec_tree_attention_paged(const subspec_tree_attn_args* args, 
   kernel<<<grid, kTcThreads, kTcSmem, st>>>(ka, tmap_k, tmap_v);
   if (ka.splits > 1) {
     const long long rows = (long long)a.batch * a.num_q_heads * a.q_len;
-    auto merge = half ? attn_merge_kernel<true> : attn_merge_kernel<false>;
+    auto merge = hd == 128 ? (half ? attn_merge_kernel<true, 128> : attn_merge_kernel<false, 128>)
+                           : (half ? attn_merge_kernel<true, 64> : attn_merge_kernel<false, 64>);
     merge<<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(ka);
   }
   return cuda_check(cudaGetLastError());

@@ -11,8 +11,7 @@ from tests import golden_io
 pytestmark = pytest.mark.gpu
 
 
-def _case(seed, B, QL, HQ, HKV, prefix_lens, n_qs, page_len=16, layers=2, layer=1, dtype=torch.bfloat16):
-    D = 128
+def _case(seed, B, QL, HQ, HKV, prefix_lens, n_qs, page_len=16, layers=2, layer=1, dtype=torch.bfloat16, D=128):
     gen = torch.Generator().manual_seed(seed)
     pages_per_seq = max((p + QL + page_len - 1) // page_len for p in prefix_lens) + 1
     P = B * pages_per_seq
@@ -122,6 +121,16 @@ def test_split_cache_ranges(cuda_lib, kv_splits):
     _run_and_check(c, tol=4e-3, kv_splits=kv_splits)
 
 
+@pytest.mark.parametrize("kv_splits", [1, None, 3])
+def test_head_dim_64(cuda_lib, kv_splits):
+    """The head dimension of the small draft models of the classic-SD generators (Llama-3.2-1B: 32 query heads
+    on 8 KV heads of 64): one 64-dim half per tile, half as many MMA steps, O half as wide."""
+    c = _case(40, B=2, QL=48, HQ=32, HKV=8, prefix_lens=[700, 1], n_qs=[48, 30], D=64)
+    _run_and_check(c, kv_splits=kv_splits)
+    c = _case(41, B=1, QL=9, HQ=6, HKV=2, prefix_lens=[133], n_qs=[9], page_len=24, dtype=torch.float16, D=64)
+    _run_and_check(c, tol=4e-3, kv_splits=kv_splits)
+
+
 def test_fp16_pool(cuda_lib):
     """The reference's FlashInferCache allocates its pool in fp16 (cache_manager.py:462): same kernel, the
     tensor core's other 16-bit format, P and the output rounded to fp16."""
@@ -154,7 +163,7 @@ def test_benchmark_shape(cuda_lib):
     assert torch.equal(o2.float(), o1.float() * 2)
     with pytest.raises(ValueError):
         tree_attention_paged(c["q"].to(dev)[..., :64].contiguous(), pool, 0, page_table=table, kv_len=kv_len,
-                             mask=c["mask"].to(dev))
+                             mask=c["mask"].to(dev))  # a head dimension other than the pool's
 
 
 def test_inside_a_cuda_graph(cuda_lib):
