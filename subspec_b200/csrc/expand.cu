@@ -20,6 +20,8 @@
 
 #include <type_traits>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "mask.cuh"
 #include "tma.cuh"
@@ -751,6 +753,11 @@ __global__ void __launch_bounds__(256) tree_finalize_kernel(const FinArgs fa) {
   int* old_of = rank + n;    // [keep]
   int* par = old_of + keep;  // [n] parents, old numbering (a copy: the loops below read them many times)
   int* coff = par + n;       // [keep + 1] children CSR offsets, new numbering
+  float* ps = reinterpret_cast<float*>(coff + keep + 1);  // [n] cumulative probabilities as they are ranked
+  // The mask rows of a sequence are shared out between the gridDim.y CTAs of the sequence (a static buffer of
+  // [max_verify, max_cache_len] is a quarter of a megabyte to fill); every CTA ranks the nodes for itself, CTA 0
+  // also writes the per-node outputs and the children lists.
+  const int slice = blockIdx.y, nslices = gridDim.y;
   const size_t tb = (size_t)b * a.tree_stride;
   const float* prob = a.tree_probs + tb;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -760,18 +767,19 @@ __global__ void __launch_bounds__(256) tree_finalize_kernel(const FinArgs fa) {
       p = -1;
     }
     par[i] = p;
+    const float pr = i == 0 ? 1.f : prob[i];
+    ps[i] = pr == pr ? pr : -INFINITY;  // the root carries probability 1, NaN counts as -inf
   }
+  __syncthreads();
 
-  // rank by (cumulative probability desc, index asc); the root carries probability 1, NaN counts as -inf
+  // rank by (cumulative probability desc, index asc)
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     int r = i;
     if (!identity) {
-      float pi = i == 0 ? 1.f : prob[i];
-      pi = pi == pi ? pi : -INFINITY;
+      const float pi = ps[i];
       r = 0;
       for (int j = 0; j < n; ++j) {
-        float pj = j == 0 ? 1.f : prob[j];
-        pj = pj == pj ? pj : -INFINITY;
+        const float pj = ps[j];
         r += (pj > pi || (pj == pi && j < i)) ? 1 : 0;
       }
     }
@@ -788,22 +796,26 @@ __global__ void __launch_bounds__(256) tree_finalize_kernel(const FinArgs fa) {
     mask_ok = false;
   }
   uint8_t* mbase = reinterpret_cast<uint8_t*>(a.mask) + (size_t)b * fa.seq_stride * mf.esz;
-  if (mask_ok) mask_fill_rows(mbase, fa.row_stride, a.keep - skip, fa.cols, prefix, mf);
+  const int mrows = a.keep - skip, per_slice = (mrows + nslices - 1) / nslices;
+  const int r0 = min(slice * per_slice, mrows), r1 = min(r0 + per_slice, mrows);  // this CTA's mask rows
+  if (mask_ok) mask_fill_rows(mbase + (size_t)r0 * fa.row_stride * mf.esz, fa.row_stride, r1 - r0, fa.cols, prefix, mf);
   __syncthreads();
   const size_t ob = (size_t)b * a.keep;
   for (int r = threadIdx.x; r < keep; r += blockDim.x) {
     const int o = old_of[r];
     const int p = par[o];
-    const int np = (p >= 0 && rank[p] < keep) ? rank[p] : -1;
-    a.keep_idx[ob + r] = o;
-    a.tokens[ob + r] = a.tree_tokens[tb + o];
-    a.parents[ob + r] = np;
-    const int d = o == 0 ? 0 : a.tree_depths[tb + o];
-    a.depths[ob + r] = d;
-    a.probs[ob + r] = o == 0 ? 1.f : prob[o];
-    a.position_ids[ob + r] = (int64_t)d + (a.position_offset ? a.position_offset[b] : 0);
+    if (slice == 0) {
+      const int np = (p >= 0 && rank[p] < keep) ? rank[p] : -1;
+      a.keep_idx[ob + r] = o;
+      a.tokens[ob + r] = a.tree_tokens[tb + o];
+      a.parents[ob + r] = np;
+      const int d = o == 0 ? 0 : a.tree_depths[tb + o];
+      a.depths[ob + r] = d;
+      a.probs[ob + r] = o == 0 ? 1.f : prob[o];
+      a.position_ids[ob + r] = (int64_t)d + (a.position_offset ? a.position_offset[b] : 0);
+    }
     // ancestor-or-self row (parents are smaller than their children, so the walk ends within n steps)
-    if (mask_ok && r >= skip) {
+    if (mask_ok && r >= skip && r - skip >= r0 && r - skip < r1) {
       uint8_t* mrow = mbase + (size_t)(r - skip) * fa.row_stride * mf.esz;
       int cur = o, guard = 0;
       while (cur >= 0 && guard <= n) {
@@ -814,15 +826,18 @@ __global__ void __launch_bounds__(256) tree_finalize_kernel(const FinArgs fa) {
     }
   }
   for (int r = keep + threadIdx.x; r < a.keep; r += blockDim.x) {  // padding when the tree is smaller than `keep`
-    a.keep_idx[ob + r] = -1;
-    a.tokens[ob + r] = 0;
-    a.parents[ob + r] = -1;
-    a.depths[ob + r] = 0;
-    a.probs[ob + r] = 0.f;
-    a.position_ids[ob + r] = 0;
+    if (slice == 0) {
+      a.keep_idx[ob + r] = -1;
+      a.tokens[ob + r] = 0;
+      a.parents[ob + r] = -1;
+      a.depths[ob + r] = 0;
+      a.probs[ob + r] = 0.f;
+      a.position_ids[ob + r] = 0;
+    }
     // a padding row attends to itself only, so that a caller who runs all `keep` rows has no fully masked row
-    if (mask_ok && r >= skip) mask_store(mbase + (size_t)(r - skip) * fa.row_stride * mf.esz, prefix + r, mf, true);
+    if (mask_ok && r >= skip && r - skip >= r0 && r - skip < r1) mask_store(mbase + (size_t)(r - skip) * fa.row_stride * mf.esz, prefix + r, mf, true);
   }
+  if (slice != 0) return;  // (the whole CTA: the children lists are CTA 0's)
   __syncthreads();
   // children CSR in new numbering; a node's children keep their original relative order
   // (ascending old index), as the reference's re-link loop leaves them (cpu_tree.py:196-199).
@@ -979,7 +994,16 @@ extern "C" int subspec_tree_finalize(const subspec_tree_finalize_args* args, sub
   if (fa.row_stride < fa.cols) return SUBSPEC_EINVAL;
   fa.seq_stride = a.mask_seq_stride ? a.mask_seq_stride : (int64_t)(a.keep - a.skip_nodes) * fa.row_stride;
   if ((reinterpret_cast<uintptr_t>(a.mask) % mask_elem_bytes(a.mask_kind)) != 0) return SUBSPEC_EINVAL;
-  const size_t smem = sizeof(int) * (2 * (size_t)a.n_nodes + 2 * (size_t)a.keep + 1);
-  tree_finalize_kernel<<<a.batch, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(fa);
+  const size_t smem = sizeof(int) * (3 * (size_t)a.n_nodes + 2 * (size_t)a.keep + 1);
+  // CTAs per sequence: one per 32 KB of mask rows, at most 16, and no more than four waves' worth in all
+  const int64_t mask_bytes = (int64_t)(a.keep - a.skip_nodes) * fa.cols * mask_elem_bytes(a.mask_kind);
+  int slices = (int)std::min<int64_t>(16, std::max<int64_t>(1, mask_bytes / 32768));
+  slices = std::max(1, std::min(slices, 4 * kNumSMs / std::max(a.batch, 1)));
+  if (smem > 48 * 1024) {  // more than 3072 nodes: past the default limit of dynamic shared memory
+    static const cudaError_t opted = cudaFuncSetAttribute(tree_finalize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                          (int)(sizeof(int) * (3 * 4096 + 2 * 1024 + 1)));
+    if (opted != cudaSuccess) return cuda_check(opted);
+  }
+  tree_finalize_kernel<<<dim3((unsigned)a.batch, (unsigned)slices), 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(fa);
   return cuda_check(cudaGetLastError());
 }

@@ -191,6 +191,82 @@ def test_finalize_writes_prefix_skip_and_static_buffer(cuda_lib, mask_dtype):
     assert checked >= 4
 
 
+def _finalize_restated(tokens, parents, probs, depths, keep):
+    """prune_to_top_n + renumbering on the host (cpu_tree.py:168-206): stable order by cumulative probability,
+    parents renumbered, ancestor-or-self rows."""
+    n = len(tokens)
+    pr = [1.0] + [float(x) for x in probs[1:]]
+    order = list(range(n)) if n <= keep else sorted(range(n), key=lambda i: (-pr[i], i))[:keep]
+    new_of = {o: r for r, o in enumerate(order)}
+    par = [new_of.get(int(parents[o]), -1) if o else -1 for o in order]
+    mask = torch.zeros(len(order), len(order), dtype=torch.bool)
+    for r in range(len(order)):
+        cur = r
+        while cur >= 0:
+            mask[r, cur] = True
+            cur = par[cur]
+    return order, par, mask
+
+
+@pytest.mark.parametrize("keep,skip,mask_dtype", [(64, 0, torch.bool), (50, 3, torch.bool), (64, 1, torch.bfloat16),
+                                                  (37, 0, torch.float32)])
+def test_finalize_mask_rows_shared_between_ctas(cuda_lib, keep, skip, mask_dtype):
+    """A static [batch, 1, max_verify, max_cache_len] buffer of a long cache is filled by several CTAs per
+    sequence, each owning a range of rows (ranges that do not divide evenly included); a dense mask of the tree's
+    own width is filled by one.  Both must say the same, and both must agree with the host restatement."""
+    from subspec_b200.draft import invert_mask
+
+    B, k, depth, V, P = 3, 16, 10, 4000, 4032
+    g = torch.Generator().manual_seed(keep * 7 + skip)
+    tree = DraftTreeBatch(B, k, depth, "cuda")
+    for lvl in range(depth):
+        tree.expand((torch.randn(B, 1 if lvl == 0 else k, V, generator=g) * 3).cuda())
+    prefix = torch.tensor([P, P - 17, 5])
+    buf = torch.full((B, 1, 70, 4160), 1, dtype=mask_dtype, device="cuda")
+    big = tree.finalize(keep, position_offset=prefix, prefix_length=prefix, skip_nodes=skip, mask_out=buf)
+    big = {key: v.clone() for key, v in big.items() if torch.is_tensor(v) and key != "tree_mask"}
+    small = tree.finalize(keep, position_offset=prefix, skip_nodes=skip, mask_cols=keep)
+    tree.check_status()
+    for key in big:
+        assert torch.equal(big[key], small[key]), key
+    for b in range(B):
+        n = tree.n_nodes
+        order, par, m = _finalize_restated(tree.tokens[b, :n].tolist(), tree.parents[b, :n].tolist(),
+                                           tree.probs[b, :n].tolist(), tree.depths[b, :n].tolist(), keep)
+        assert small["keep_idx"][b].tolist() == order and small["parent_indices"][b].tolist() == par
+        want = torch.zeros(keep - skip, 4160, dtype=torch.bool)
+        pb = int(prefix[b])
+        want[:, :pb] = True
+        want[:, pb:pb + keep] = m[skip:]
+        assert torch.equal(small["tree_mask"][b].cpu(), m[skip:])
+        got = buf[b, 0, :keep - skip].cpu()
+        if mask_dtype == torch.bool:
+            assert torch.equal(got, want), b
+        else:
+            assert torch.equal(got.float(), invert_mask(want, mask_dtype).float()), b
+        assert bool((buf[b, 0, keep - skip:] == 1).all())  # rows past the call's own keep their contents
+
+
+def test_finalize_largest_tree(cuda_lib):
+    """4065 nodes of the 4096 one call takes (more shared memory than a kernel gets by default), 1024 kept."""
+    k, depth, V, keep = 32, 127, 300, 1024
+    g = torch.Generator().manual_seed(5)
+    tree = DraftTreeBatch(2, k, depth, "cuda")
+    for lvl in range(depth):
+        tree.expand((torch.randn(2, 1 if lvl == 0 else k, V, generator=g) * 2).cuda())
+    out = tree.finalize(keep)
+    tree.check_status()
+    n = 1 + k * depth
+    assert n == 4065
+    for b in range(2):
+        order, par, m = _finalize_restated(tree.tokens[b, :n].tolist(), tree.parents[b, :n].tolist(),
+                                           tree.probs[b, :n].tolist(), tree.depths[b, :n].tolist(), keep)
+        assert out["keep_idx"][b].tolist() == order
+        assert out["parent_indices"][b].tolist() == par
+        assert torch.equal(out["tree_mask"][b].cpu(), m)
+        assert out["token_ids"][b].tolist() == [int(tree.tokens[b, o]) for o in order]
+
+
 def test_finalize_rejects_bad_geometry(cuda_lib):
     tree = DraftTreeBatch(2, 4, 2, "cuda")
     probs = torch.rand(2, 1, 50).softmax(-1)
