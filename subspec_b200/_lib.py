@@ -64,6 +64,16 @@ class VerifyArgs(C.Structure):
     ]
 
 
+class LmHeadVerifyArgs(C.Structure):
+    """Mirror of `subspec_lm_head_verify_args`."""
+
+    _fields_ = [
+        ("struct_size", _u32), ("hidden_dim", _i32), ("hidden", _vp), ("hidden_row_stride", _i64),
+        ("weight", _vp), ("weight_row_stride", _i64), ("hidden_seq_rows", _i32), ("reserved", _i32),
+        ("verify", VerifyArgs),
+    ]
+
+
 class KvPagedArgs(C.Structure):
     """Mirror of `subspec_kv_paged_args`."""
 
@@ -207,6 +217,8 @@ SYMBOLS = {
     "subspec_verify_scratch_bytes": (C.c_int, [_i32, _i32, C.POINTER(C.c_size_t)]),
     "subspec_verify_batched": (C.c_int, [C.POINTER(VerifyArgs), _vp]),
     "subspec_verify_batched_static_scratch": (C.c_int, [C.POINTER(VerifyArgs), _vp]),
+    "subspec_lm_head_verify_scratch_bytes": (C.c_int, [_i32, _i32, _i32, _i32, C.POINTER(C.c_size_t)]),
+    "subspec_lm_head_verify": (C.c_int, [C.POINTER(LmHeadVerifyArgs), _vp]),
     "subspec_kv_compact_paged": (C.c_int, [C.POINTER(KvPagedArgs), _vp]),
     "subspec_kv_compact_hf": (C.c_int, [C.POINTER(KvHfArgs), _vp]),
     "subspec_expand_scratch_bytes": (C.c_int, [_i32, _i32, _i32, C.POINTER(C.c_size_t)]),

@@ -18,6 +18,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "lm_head.cuh"
 #include "tma.cuh"
 
 namespace subspec {
@@ -2594,6 +2595,110 @@ cudaError_t launch_sampler(const KArgs& ka, int n, cudaStream_t st) {
 #undef SUBSPEC_SAMPLER
 }
 
+// ---- the tail behind the lm_head GEMM with a statistics epilogue --------------------------------
+// One CTA per decoded row: the row's statistics are the combination of its per-tile records; the logits of
+// the children's tokens, which the lossy gates need as probabilities, are 16-bit-rounded dot products of the
+// row's hidden state with those tokens' weight rows (a few dozen per tree); then the same per-node outputs,
+// the same ticket and the same walk as the streaming kernel's.
+static_assert(sizeof(LmHeadStat) == sizeof(RowStat), "the GEMM's records are read as row statistics");
+struct LmTailArgs {
+  const LmHeadStat* partial;  // [batch * seq_rows, ntiles]
+  int ntiles, seq_rows, dim;
+  const __nv_bfloat16* hidden;
+  int64_t hidden_stride;
+  const __nv_bfloat16* weight;
+  int64_t weight_stride;
+};
+
+template <bool SOFT>
+__global__ void __launch_bounds__(kThreads) lm_head_tail_kernel(const KArgs ka, const LmTailArgs lt) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ RowStat s_warp[kWarps];
+  __shared__ RowStat s_row;
+  __shared__ int s_flag;
+  const subspec_verify_args& a = ka.a;
+  const int row = blockIdx.x;
+  const int b = row / a.max_nodes;
+  const int u = row - b * a.max_nodes;
+  int n_nodes, n_rows;
+  seq_counts(a, b, n_nodes, n_rows);
+  if (u >= n_rows) {
+    if (n_rows == 0 && u == 0 && threadIdx.x == 0) write_empty_result(a, b);
+    return;
+  }
+  // (a row count beyond the rows the caller laid out per sequence: reported, the row counts as empty)
+  const bool have = u < lt.seq_rows;
+  if (!have && threadIdx.x == 0) flag(a.dev_status, SUBSPEC_DEV_BAD_COUNT);
+  const size_t grow = (size_t)b * lt.seq_rows + (have ? u : 0);  // the row of the GEMM
+  RowStat st = empty_stat(false);
+  for (int i = threadIdx.x; have && i < lt.ntiles; i += kThreads) {
+    const LmHeadStat p = lt.partial[grow * lt.ntiles + i];
+    RowStat q;
+    q.c = p.c, q.s = p.s, q.t2 = p.t2, q.vmax = p.vmax, q.amax = p.amax;
+    st = combine(st, q);
+  }
+  block_reduce<SUBSPEC_IN_LOGITS>(st, s_warp, &s_row);
+  const RowStat r = s_row;
+  const size_t nb = (size_t)b * a.max_nodes;
+  if (threadIdx.x == 0) {
+    a.node_target[nb + u] = r.amax == INT_MAX ? 0 : r.amax;
+    float ent = 0.f;
+    if (SOFT) {
+      const float denom = a.vocab > 1 ? logf((float)a.vocab) : 1.f;
+      ent = kLn2 * (lg2f(r.s) - r.t2 / r.s) / denom;
+    }
+    a.node_entropy[nb + u] = ent;
+    a.node_rowmax[nb + u] = r.c;
+    a.node_rowsum[nb + u] = r.s;
+  }
+  if (SOFT) {
+    int cb, ce;
+    child_range(a, b, u, n_nodes, cb, ce);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint4* h = reinterpret_cast<const uint4*>(lt.hidden + grow * lt.hidden_stride);
+    for (int e = cb + warp; e < ce; e += kWarps) {  // a warp per child
+      const int c = a.child_idx[nb + e];
+      if (c < 0 || c >= n_nodes) {
+        if (lane == 0) flag(a.dev_status, SUBSPEC_DEV_BAD_CHILD);
+        continue;
+      }
+      const int tok = a.token_ids[nb + c];
+      float p = 0.f;
+      if (tok < 0 || tok >= a.vocab) {
+        if (lane == 0) flag(a.dev_status, SUBSPEC_DEV_BAD_TOKEN);
+      } else {
+        const uint4* wv = reinterpret_cast<const uint4*>(lt.weight + (size_t)tok * lt.weight_stride);
+        float acc = 0.f;
+        for (int i = lane; i < lt.dim / 8; i += 32) {
+          const uint4 hv = h[i], wq = wv[i];
+          const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w}, ww[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc = fmaf(__uint_as_float(hw[j] << 16), __uint_as_float(ww[j] << 16), acc);
+            acc = fmaf(__uint_as_float(hw[j] & 0xffff0000u), __uint_as_float(ww[j] & 0xffff0000u), acc);
+          }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        const float x = __bfloat162float(__float2bfloat16_rn(acc));
+        p = ex2f(fmaf(x, ka.k, -r.c)) / r.s;
+      }
+      if (lane == 0) a.node_child_prob[nb + c] = p;
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(ka.sc.seq_ticket + b, 1);
+    s_flag = (t == n_rows - 1);
+    if (s_flag) ka.sc.seq_ticket[b] = 0;
+  }
+  __syncthreads();
+  if (!s_flag) return;
+  __threadfence();
+  run_walk(ka, b, smem_raw);
+}
+
 // Dynamic shared memory: the TMA ring while streaming, reused for the walk's tree arrays afterwards.
 size_t kernel_smem_bytes(int max_nodes) {
   const size_t walk = sizeof(int) * (9 * (size_t)max_nodes + 1);
@@ -2736,6 +2841,87 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
       break;
   }
   return cuda_check(e);
+}
+
+// ---- lm_head + verify without the logits in between ---------------------------------
+static size_t lm_head_stats_bytes(int64_t rows, int vocab) {
+  return align_up(sizeof(LmHeadStat) * (size_t)rows * (size_t)((vocab + kLmTileN - 1) / kLmTileN), 256);
+}
+
+extern "C" int subspec_lm_head_verify_scratch_bytes(int32_t batch, int32_t max_nodes, int32_t hidden_seq_rows,
+                                                    int32_t vocab, size_t* bytes) {
+  if (!bytes || batch < 0 || max_nodes < 1 || max_nodes > kMaxNodes || hidden_seq_rows < 1 || vocab < 1 ||
+      vocab > (1 << 20))
+    return SUBSPEC_EINVAL;
+  *bytes = ticket_bytes(batch, max_nodes) + lm_head_stats_bytes((int64_t)batch * hidden_seq_rows, vocab);
+  return SUBSPEC_OK;
+}
+
+extern "C" int subspec_lm_head_verify(const subspec_lm_head_verify_args* args, subspec_stream_t stream) {
+  if (!args || args->struct_size != sizeof(subspec_lm_head_verify_args) ||
+      args->verify.struct_size != sizeof(subspec_verify_args))
+    return SUBSPEC_EINVAL;
+  const subspec_verify_args& a = args->verify;
+  if (a.batch < 0 || a.max_nodes < 1 || a.vocab < 1 || a.max_out < 2 || args->hidden_dim < 8 ||
+      args->hidden_seq_rows < 1)
+    return SUBSPEC_EINVAL;
+  if (a.max_nodes > kMaxNodes || a.vocab > (1 << 20) || args->hidden_dim % 8) return SUBSPEC_EUNSUPPORTED;
+  if (a.dtype != SUBSPEC_BF16) return SUBSPEC_EUNSUPPORTED;  // the logits this call stands for are bf16
+  if (a.do_sample || a.acceptance) return SUBSPEC_EUNSUPPORTED;  // sampled targets need the whole row
+  if (a.method != SUBSPEC_VERIFY_EXACT && a.method != SUBSPEC_VERIFY_LOSSY &&
+      a.method != SUBSPEC_VERIFY_EXACT_AND_LOSSY)
+    return SUBSPEC_EINVAL;
+  if (a.method == SUBSPEC_VERIFY_EXACT_AND_LOSSY && (!a.out2_tokens || !a.out2_hidden || !a.out2_meta))
+    return SUBSPEC_EINVAL;
+  if (a.gate != SUBSPEC_GATE_PROB && a.gate != SUBSPEC_GATE_ENTROPY) return SUBSPEC_EINVAL;
+  if (a.batch == 0) return SUBSPEC_OK;
+  if (!args->hidden || !args->weight || !a.n_nodes || !a.n_rows || !a.token_ids || !a.child_off || !a.child_idx ||
+      !a.root || !a.out_tokens || !a.out_hidden || !a.out_meta || !a.node_target || !a.node_entropy ||
+      !a.node_child_prob || !a.node_rowmax || !a.node_rowsum || !a.node_exact_after || !a.node_best_len ||
+      !a.node_best_next || !a.scratch)
+    return SUBSPEC_EINVAL;
+  const int64_t rows = (int64_t)a.batch * args->hidden_seq_rows;
+  if (rows > INT_MAX || (int64_t)a.batch * a.max_nodes > INT_MAX) return SUBSPEC_EUNSUPPORTED;
+  size_t need = 0;
+  subspec_lm_head_verify_scratch_bytes(a.batch, a.max_nodes, args->hidden_seq_rows, a.vocab, &need);
+  if (a.scratch_bytes < need || (reinterpret_cast<uintptr_t>(a.scratch) & 255u)) return SUBSPEC_ESCRATCH;
+  const int64_t hs = args->hidden_row_stride ? args->hidden_row_stride : args->hidden_dim;
+  const int64_t ws = args->weight_row_stride ? args->weight_row_stride : args->hidden_dim;
+
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  KArgs ka = {};
+  ka.a = a;
+  ka.sc = carve(a.scratch, a.batch, a.max_nodes);
+  ka.splits = 1;
+  ka.k = kLog2e;
+  const bool soft = a.method != SUBSPEC_VERIFY_EXACT;
+  LmHeadGemmArgs ga;
+  ga.hidden = args->hidden, ga.hidden_stride = hs, ga.weight = args->weight, ga.weight_stride = ws;
+  ga.rows = (int)rows, ga.vocab = a.vocab, ga.dim = args->hidden_dim;
+  ga.soft = soft ? 1 : 0;
+  ga.k = ka.k;
+  ga.partial = reinterpret_cast<LmHeadStat*>(reinterpret_cast<char*>(a.scratch) + ticket_bytes(a.batch, a.max_nodes));
+  ga.dev_status = a.dev_status;
+  int rc = SUBSPEC_OK;
+  if (!(a.flags & SUBSPEC_VERIFY_SCRATCH_CLEAN))
+    rc = cuda_check(cudaMemsetAsync(a.scratch, 0, ticket_bytes(a.batch, a.max_nodes), st));
+  if (rc) return rc;
+  cudaError_t e = launch_lm_head_stats(ga, st);
+  if (e == cudaErrorInvalidValue) return SUBSPEC_EINVAL;  // addresses or strides not multiples of 16 bytes
+  if (e != cudaSuccess) return cuda_check(e);
+  LmTailArgs lt;
+  lt.partial = ga.partial, lt.ntiles = (a.vocab + kLmTileN - 1) / kLmTileN, lt.seq_rows = args->hidden_seq_rows;
+  lt.dim = args->hidden_dim;
+  lt.hidden = reinterpret_cast<const __nv_bfloat16*>(args->hidden), lt.hidden_stride = hs;
+  lt.weight = reinterpret_cast<const __nv_bfloat16*>(args->weight), lt.weight_stride = ws;
+  const size_t smem = sizeof(int) * (9 * (size_t)a.max_nodes + 1);
+  const int grid = a.batch * a.max_nodes;
+  if (soft) {
+    lm_head_tail_kernel<true><<<grid, kThreads, smem, st>>>(ka, lt);
+  } else {
+    lm_head_tail_kernel<false><<<grid, kThreads, smem, st>>>(ka, lt);
+  }
+  return cuda_check(cudaGetLastError());
 }
 
 // ---- no-allocation variant -------------------------------------------------------

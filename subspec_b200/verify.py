@@ -202,6 +202,61 @@ class VerifyWorkspace:
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _lib.check(_lib.lib().subspec_verify_batched(C.byref(a), C.c_void_p(stream)), "subspec_verify_batched")
 
+    def run_lm_head(self, hidden: torch.Tensor, weight: torch.Tensor, *, method: int, gate: int = _lib.GATE_PROB,
+                    threshold: float = 0.0, window: int = 1, eos: Optional[int] = None) -> None:
+        """lm_head and verification in one call (greedy targets): `hidden` [batch, rows, dim] bf16 are the
+        target's last hidden states of the tree rows, `weight` [vocab, dim] bf16 the lm_head's weight.  Stands
+        for `logits = lm_head(hidden)` (generators/classic_sd.py:100-109) followed by `run(logits, ...)`;
+        the logits are never written.  Results as `run`'s, up to the rounding of a different GEMM."""
+        B, N = self.batch, self.max_nodes
+        if hidden.dim() != 3 or hidden.shape[0] != B or weight.dim() != 2 or weight.shape[1] != hidden.shape[2]:
+            raise ValueError(f"hidden must be [batch={B}, rows, dim] and weight [vocab, dim], got "
+                             f"{tuple(hidden.shape)} and {tuple(weight.shape)}")
+        if hidden.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+            raise ValueError("hidden and weight must be bfloat16")
+        if hidden.device != self.device or weight.device != self.device:
+            raise ValueError("hidden / weight live on another device than the workspace")
+        if not hidden.is_contiguous():
+            hidden = hidden.contiguous()
+        if weight.stride(1) != 1:
+            weight = weight.contiguous()
+        rows, dim, vocab = int(hidden.shape[1]), int(hidden.shape[2]), int(weight.shape[0])
+        if int(self.host_view("n_rows").max(initial=0)) > rows:
+            raise ValueError(f"a tree has more decoded rows than hidden has rows ({rows})")
+        key = (rows, vocab)
+        if getattr(self, "_lm_key", None) != key:
+            need = C.c_size_t(0)
+            _lib.check(_lib.lib().subspec_lm_head_verify_scratch_bytes(B, N, rows, vocab, C.byref(need)),
+                       "subspec_lm_head_verify_scratch_bytes")
+            self._lm_scratch = torch.zeros(need.value + 256, dtype=torch.uint8, device=self.device)
+            self._lm_key, self._lm_bytes = key, need.value
+        la = _lib.LmHeadVerifyArgs()
+        la.struct_size = C.sizeof(_lib.LmHeadVerifyArgs)
+        la.hidden_dim, la.hidden_seq_rows = dim, rows
+        la.hidden, la.hidden_row_stride = hidden.data_ptr(), int(hidden.stride(1))
+        la.weight, la.weight_row_stride = weight.data_ptr(), int(weight.stride(0))
+        a = la.verify
+        a.struct_size = C.sizeof(_lib.VerifyArgs)
+        a.batch, a.max_nodes, a.vocab = B, N, vocab
+        a.dtype, a.input_kind = _lib.torch_dtype_code(torch.bfloat16), _lib.IN_LOGITS
+        for name in ("n_nodes", "n_rows", "token_ids", "child_off", "child_idx", "root"):
+            setattr(a, name, self._in_ptr(name))
+        a.temperature, a.top_p = 1.0, 1.0
+        a.method, a.gate = int(method), int(gate)
+        a.threshold, a.window = float(threshold), int(window)
+        a.eos = -1 if eos is None else int(eos)
+        a.max_out = self.max_out
+        for name in ("out_tokens", "out_hidden", "out_meta", "node_target", "node_entropy", "node_child_prob",
+                     "node_rowmax", "node_rowsum", "node_exact_after", "node_best_len", "node_best_next",
+                     "dev_status", "out2_tokens", "out2_hidden", "out2_meta"):
+            setattr(a, name, self._out_ptr(name))
+        a.scratch, a.scratch_bytes = _align(self._lm_scratch.data_ptr(), 256), self._lm_bytes
+        a.flags = _lib.VERIFY_SCRATCH_CLEAN if self.scratch_clean else 0
+        self._rows = rows
+        self._keepalive = (hidden, weight)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(_lib.lib().subspec_lm_head_verify(C.byref(la), C.c_void_p(stream)), "subspec_lm_head_verify")
+
     def clear_status(self) -> None:
         self.dev_view("dev_status").zero_()
 
@@ -545,13 +600,19 @@ def _prepare_tree(tree, root_ind: int, skip_nodes: int, rows: int, method: int):
 
 
 @torch.no_grad()
-def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logits: torch.Tensor,
+def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logits: Optional[torch.Tensor] = None,
                         eos_token_id: Optional[int], logits_processor=None, do_sample: bool = False,
                         skip_nodes=0, verify_method: str = "exact", verify_kwargs: Optional[dict] = None,
                         uniforms: Optional[torch.Tensor] = None, workspace: Optional[VerifyWorkspace] = None,
                         log_diagnostics: bool = False, draft_logits: Optional[torch.Tensor] = None,
-                        accept_uniforms: Optional[torch.Tensor] = None) -> List[VerifyOutput]:
+                        accept_uniforms: Optional[torch.Tensor] = None,
+                        hidden_states: Optional[torch.Tensor] = None,
+                        lm_head_weight: Optional[torch.Tensor] = None) -> List[VerifyOutput]:
     """Verify `len(trees)` independent draft trees against `logits` [batch, rows, vocab] in one launch.
+
+    Instead of `logits`, `hidden_states` [batch, rows, dim] and `lm_head_weight` [vocab, dim] (both bf16) may be
+    given (greedy targets only): the lm_head product and the verification then run as one call that never
+    writes the logits (`VerifyWorkspace.run_lm_head`).
 
     Per sequence the result equals the reference's `verify_tree` on
     `logits[b:b+1]` (tree_verify.py:7-163).  `verify_method="exact+lossy"` returns, per sequence, the pair
@@ -567,11 +628,23 @@ def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logit
     method = _method_code(verify_method)
     vk = dict(verify_kwargs or {})
     B = len(trees)
-    if logits.dim() != 3 or logits.shape[0] != B:
-        raise ValueError(f"logits must be [batch={B}, rows, vocab]")
-    device = _device_of(logits)
-    logits = logits.to(device)
-    rows = int(logits.shape[1])
+    fused = hidden_states is not None
+    if fused:
+        if logits is not None or lm_head_weight is None:
+            raise ValueError("give either logits, or hidden_states together with lm_head_weight")
+        if do_sample:
+            raise ValueError("hidden_states / lm_head_weight: greedy targets only (sampling needs the whole row)")
+        if hidden_states.dim() != 3 or hidden_states.shape[0] != B:
+            raise ValueError(f"hidden_states must be [batch={B}, rows, dim]")
+        device = _device_of(hidden_states)
+        hidden_states, lm_head_weight = hidden_states.to(device), lm_head_weight.to(device)
+        rows = int(hidden_states.shape[1])
+    else:
+        if logits is None or logits.dim() != 3 or logits.shape[0] != B:
+            raise ValueError(f"logits must be [batch={B}, rows, vocab]")
+        device = _device_of(logits)
+        logits = logits.to(device)
+        rows = int(logits.shape[1])
     skips = [int(skip_nodes)] * B if isinstance(skip_nodes, int) else [int(s) for s in skip_nodes]
     flats = [_prepare_tree(t, r, s, rows, method) for t, r, s in zip(trees, root_inds, skips)]
     gate, threshold, window = _lib.GATE_PROB, 0.0, 1
@@ -608,9 +681,13 @@ def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logit
             ws.accept_uniforms.view(B, ws.max_nodes)[:, :au.shape[1]].copy_(au)
     else:
         draft_logits = None
-    ws.run(logits, input_kind=_lib.IN_LOGITS, method=method, gate=gate, threshold=threshold, window=window,
-           eos=eos_token_id, do_sample=sample_mode, temperature=temperature, top_p=top_p, top_k=top_k,
-           draft_logits=draft_logits, draft_temperature=float(vk.get("draft_temperature", 1.0)))
+    if fused:
+        ws.run_lm_head(hidden_states, lm_head_weight, method=method, gate=gate, threshold=threshold, window=window,
+                       eos=eos_token_id)
+    else:
+        ws.run(logits, input_kind=_lib.IN_LOGITS, method=method, gate=gate, threshold=threshold, window=window,
+               eos=eos_token_id, do_sample=sample_mode, temperature=temperature, top_p=top_p, top_k=top_k,
+               draft_logits=draft_logits, draft_temperature=float(vk.get("draft_temperature", 1.0)))
     out = ws.fetch()
     results: List[Any] = []
     for b in range(B):
