@@ -796,8 +796,8 @@ SUBSPEC_API int subspec_w4a16_gemm_grouped(const subspec_w4a16_group_args* args,
  * Results against a library GEMM + subspec_verify_batched: the accumulation
  * order of a GEMM is its own, so a logit that sits within fp32 rounding of a
  * bf16 rounding boundary may come out one bf16 step apart; targets can
- * differ where the two largest logits of a row are that close, probabilities
- * by one bf16 step of the logit (0.8 % relative).
+ * differ where the two largest logits of a row are that close, and a child's
+ * probability by the factor e^(one bf16 step of its logit).
  * Limits: hidden_dim % 8 == 0, strides % 8 == 0, addresses 16-byte aligned
  * (SUBSPEC_EINVAL otherwise); vocab <= 2^20.
  * ---------------------------------------------------------------------- */
