@@ -55,7 +55,7 @@ def parse_args():
                     help="verify greedily and lossily in two launches (two passes over the logits) instead of one")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the side measurements of the other kernels")
-    ap.add_argument("--extras-only", choices=["step", "expand", "attention", "stochastic", "gemm", "lmhead"], default=None,
+    ap.add_argument("--extras-only", choices=["step", "expand", "attention", "stochastic", "gemm", "lmhead", "lmhead-small"], default=None,
                     help="run one of the side measurements alone on GPU 0 and print it as one JSON line")
     ap.add_argument("--cpu-sample", type=int, default=CPU_SAMPLE,
                     help="sequences per pass of the CPU path (the cpu_baseline leg and the reference arm use the same)")
@@ -596,33 +596,61 @@ def extra_gemm(device, peak_gbs, peak_tf):
     return out
 
 
-def extra_lm_head(device, peak_gbs, peak_tf_sustained, wave=64):
-    """What a fused lm_head + verification would have to beat, measured: the target's last projection as the
-    library GEMM ([wave * nodes, hidden] x [hidden, vocab] bf16, Qwen2.5-7B's 3584 x 152064) writing the logits,
-    then this repository's verify launch reading them.  Not part of the default run (the GEMM takes milliseconds)."""
+def extra_lm_head(device, peak_gbs, peak_tf, peak_tf_sustained, wave=64, vocab=VOCAB):
+    """The target's last projection and the verification of one wave ([wave * nodes, hidden] x [hidden, vocab] bf16,
+    Qwen2.5-7B's 3584 x 152064): this repository's fused call (tcgen05 GEMM whose epilogue keeps the row statistics,
+    no logits written) beside the library GEMM writing the logits followed by the streaming verify launch that
+    reads them.  Each variant is timed twice: as a loop of back-to-back calls (the state a GPU is in behind a
+    target forward: power-capped) and as single calls after a pause.  Not part of the default run (milliseconds
+    per call).  `vocab` below the model's: a short case of the same kernels (weights still larger than L2) for a
+    profiler capture."""
     from subspec_b200 import synthetic
     from subspec_b200.step import SpeculativeStepBatch
 
     hidden = 3584
     rows = wave * NODES
     gen = torch.Generator(device=device).manual_seed(5)
-    h = (torch.randn(rows, hidden, generator=gen, device=device) * 0.5).to(torch.bfloat16)
-    w = (torch.randn(VOCAB, hidden, generator=gen, device=device) * 0.02).to(torch.bfloat16)
-    logits = torch.empty(wave, NODES, VOCAB, dtype=torch.bfloat16, device=device)
-    trees, _ = make_wave_inputs(list(range(wave)), "literal", device, with_logits=False)
+    h = (torch.randn(wave, NODES, hidden, generator=gen, device=device) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(vocab, hidden, generator=gen, device=device) * 0.02).to(torch.bfloat16)
+    logits = torch.empty(wave, NODES, vocab, dtype=torch.bfloat16, device=device)
+    trees, _ = synthetic.config5_wave(list(range(wave)), "literal", device, nodes=NODES, vocab=vocab, with_logits=False)
     sb = SpeculativeStepBatch(wave, NODES, device, kv_layers=1, kv_heads=KV_HEADS, head_dim=KV_DIM,
                               pages_per_seq=KV_TOKENS // PAGE_LEN, page_len=PAGE_LEN)
     sb.set_trees(flats_of(trees))
     _spin_up(device)
-    ms_gemm = _time_ms(lambda: torch.matmul(h, w.t(), out=logits.view(rows, VOCAB)), iters=5, warm=2)
-    ms_verify = _time_ms(lambda: sb.verify(logits, verify_method="exact+lossy", verify_kwargs=LOSSY_KW), iters=5, warm=2)
-    flops = 2.0 * rows * hidden * VOCAB
-    return {"lm_head_then_verify_wave64": {
-        "library_gemm_ms": ms_gemm, "library_gemm_TFLOP/s": flops / (ms_gemm * 1e-3) / 1e12,
-        "gemm_roofline_ms_at_sustained_peak": flops / (peak_tf_sustained * 1e12) * 1e3,
-        "verify_ms": ms_verify, "logits_bytes": rows * VOCAB * 2,
-        "note": "a fused kernel saves the logits' write and read (2 x logits_bytes at the copy peak: "
-                f"{2 * rows * VOCAB * 2 / (peak_gbs * 1e9) * 1e3:.3f} ms) if its GEMM part keeps the library's pace"}}
+    flops = 2.0 * rows * hidden * vocab
+
+    def single_ms(fn, n=5):  # one call at a time, the device idle for a moment before each
+        fn()
+        torch.cuda.synchronize(device)
+        ts = []
+        for _ in range(n):
+            time.sleep(0.05)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize(device)
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[len(ts) // 2]
+
+    out = {"flop_per_wave": flops, "vocab": vocab, "logits_bytes": rows * vocab * 2,
+           "gemm_roofline_ms": {"burst_peak": flops / (peak_tf * 1e12) * 1e3,
+                                "sustained_peak": flops / (peak_tf_sustained * 1e12) * 1e3}}
+    gemm = lambda: torch.matmul(h.view(rows, hidden), w.t(), out=logits.view(rows, vocab))
+    out["library_gemm_ms"] = {"loop": _time_ms(gemm, iters=5, warm=2), "single": single_ms(gemm)}
+    for name, method, kw in (("greedy", "exact", None), ("lossy", "lossy", LOSSY_KW)):
+        def pair():
+            gemm()
+            sb.verify(logits, verify_method=method, verify_kwargs=kw)
+        fused = lambda: sb.verify_from_hidden(h, w, verify_method=method, verify_kwargs=kw)
+        r = {"library_gemm_then_verify_ms": {"loop": _time_ms(pair, iters=5, warm=2), "single": single_ms(pair)},
+             "fused_ms": {"loop": _time_ms(fused, iters=5, warm=2), "single": single_ms(fused)}}
+        r["fused_TFLOP/s_single"] = flops / (r["fused_ms"]["single"] * 1e-3) / 1e12
+        r["fused_frac_of_burst_peak"] = r["fused_TFLOP/s_single"] / peak_tf
+        out[name] = r
+    sb.ws.fetch()
+    return {"lm_head_verify_wave64": out}
 
 
 def run_extras_only(args):
@@ -642,8 +670,9 @@ def run_extras_only(args):
         out = extra_attention(device, peak_gbs, peak_tf)
     elif args.extras_only == "stochastic":
         out = extra_stochastic(device, peak_gbs)
-    elif args.extras_only == "lmhead":
-        out = extra_lm_head(device, peak_gbs, float(peaks.get("bf16_tflops_sustained", peak_tf)))
+    elif args.extras_only in ("lmhead", "lmhead-small"):
+        out = extra_lm_head(device, peak_gbs, peak_tf, float(peaks.get("bf16_tflops_sustained", peak_tf)),
+                            vocab=VOCAB if args.extras_only == "lmhead" else 32768)
     else:
         out = extra_gemm(device, peak_gbs, peak_tf)
     print(json.dumps(out), flush=True)

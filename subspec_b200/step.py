@@ -67,6 +67,20 @@ class SpeculativeStepBatch:
         self.ws.run(logits, input_kind=_lib.IN_LOGITS, method=method, gate=gate, threshold=threshold, window=window,
                     eos=eos_token_id)
 
+    def verify_from_hidden(self, hidden: torch.Tensor, lm_head_weight: torch.Tensor, *, verify_method: str = "exact",
+                           verify_kwargs: Optional[dict] = None, eos_token_id: Optional[int] = None) -> None:
+        """`verify(lm_head(hidden))` without the logits: `hidden` [batch, rows, dim] and `lm_head_weight`
+        [vocab, dim], bf16; greedy targets (generators/classic_sd.py:100-116 for a batch).  No synchronisation."""
+        method = _method_code(verify_method)
+        vk = dict(verify_kwargs or {})
+        gate, threshold, window = _lib.GATE_PROB, 0.0, 1
+        if method != _lib.VERIFY_EXACT:
+            gate = _gate_code(vk.get("threshold_method", "prob") or "prob")
+            threshold = float(vk.get("threshold", 0.0))
+            window = max(0, int(vk.get("window_size", 1)))
+        self.ws.run_lm_head(hidden, lm_head_weight, method=method, gate=gate, threshold=threshold, window=window,
+                            eos=eos_token_id)
+
     def compact_kv(self) -> None:
         """Move the accepted path's KV rows into place, reading the verify kernel's outputs on the device."""
         if self.pool is None:

@@ -52,6 +52,25 @@ def test_argument_validation(cuda_lib):
     assert cuda_lib.subspec_verify_batched(C.byref(a), None) == _lib.EINVAL
     a.max_nodes = 4096
     assert cuda_lib.subspec_verify_batched(C.byref(a), None) == _lib.EUNSUPPORTED
+    # lm_head + verify: sizes, the embedded verify arguments, what the fused path does not take
+    assert cuda_lib.subspec_lm_head_verify_scratch_bytes(4, 64, 64, 152064, C.byref(n)) == _lib.OK
+    assert n.value >= 4 * 64 * 594 * 20
+    assert cuda_lib.subspec_lm_head_verify_scratch_bytes(4, 64, 0, 152064, C.byref(n)) == _lib.EINVAL
+    la = _lib.LmHeadVerifyArgs()
+    la.struct_size = C.sizeof(_lib.LmHeadVerifyArgs)
+    assert cuda_lib.subspec_lm_head_verify(C.byref(la), None) == _lib.EINVAL  # verify.struct_size not set
+    v = la.verify
+    v.struct_size = C.sizeof(_lib.VerifyArgs)
+    v.batch, v.max_nodes, v.vocab, v.max_out, v.dtype = 1, 8, 512, 9, _lib.torch_dtype_code(__import__("torch").bfloat16)
+    la.hidden_dim, la.hidden_seq_rows = 64, 8
+    assert cuda_lib.subspec_lm_head_verify(C.byref(la), None) == _lib.EINVAL  # null pointers
+    la.hidden_dim = 60
+    assert cuda_lib.subspec_lm_head_verify(C.byref(la), None) == _lib.EUNSUPPORTED
+    la.hidden_dim = 64
+    v.do_sample = 1
+    assert cuda_lib.subspec_lm_head_verify(C.byref(la), None) == _lib.EUNSUPPORTED
+    v.do_sample, v.batch = 0, 0
+    assert cuda_lib.subspec_lm_head_verify(C.byref(la), None) == _lib.OK  # an empty batch touches nothing
 
 
 def test_header_is_plain_c_and_matches_the_ctypes_mirror(tmp_path):
@@ -68,7 +87,8 @@ def test_header_is_plain_c_and_matches_the_ctypes_mirror(tmp_path):
                "subspec_w4a16_group_args": _lib.W4A16GroupArgs,
                "subspec_post_verify_args": _lib.PostVerifyArgs, "subspec_pages_args": _lib.PagesArgs,
                "subspec_tree_attn_args": _lib.TreeAttnArgs, "subspec_kv_append_args": _lib.KvAppendArgs,
-               "subspec_tree_prune_depth_args": _lib.TreePruneDepthArgs}
+               "subspec_tree_prune_depth_args": _lib.TreePruneDepthArgs,
+               "subspec_lm_head_verify_args": _lib.LmHeadVerifyArgs}
     lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "subspec_b200.h"', 'int main(void) {']
     for cname, mirror in structs.items():
         lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')
