@@ -89,18 +89,23 @@ struct RingPos {
   }
 };
 
-// Folds 32 consecutive columns of a row (fp32 accumulators in r) into the row's statistics.  `valid` columns
-// of the chunk lie inside the vocabulary (>= 32 everywhere but in the last tile).
+// 16 fp32 accumulators -> 8 bf16 pairs: the logits as the reference sees them, rounded to bf16.
+__device__ __forceinline__ void round_pairs(const uint32_t (&r)[16], uint32_t* p) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(p[j]) : "f"(__uint_as_float(r[2 * j + 1])), "f"(__uint_as_float(r[2 * j])));
+}
+
+// Folds 32 consecutive columns of a row, held as 16 bf16 pairs, into the row's statistics.  `valid` columns of
+// the chunk lie inside the vocabulary (>= 32 everywhere but in the last tile).
 template <bool SOFT>
-__device__ __forceinline__ void fold_chunk(const uint32_t (&r)[32], int col0, int valid, float k, float& c, uint64_t& s2,
+__device__ __forceinline__ void fold_chunk(const uint32_t* p, int col0, int valid, float k, float& c, uint64_t& s2,
                                            uint64_t& t2, float& vmax, int& amax) {
   float x[32];
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {  // the logits as the reference sees them: rounded to bf16
-    uint32_t p;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(p) : "f"(__uint_as_float(r[2 * j + 1])), "f"(__uint_as_float(r[2 * j])));
-    x[2 * j] = __uint_as_float(p << 16);
-    x[2 * j + 1] = __uint_as_float(p & 0xffff0000u);
+  for (int j = 0; j < 16; ++j) {
+    x[2 * j] = __uint_as_float(p[j] << 16);
+    x[2 * j + 1] = __uint_as_float(p[j] & 0xffff0000u);
   }
   if (valid < 32) {
     // columns past the vocabulary (the copy engine filled their weights with zeros): far below any logit, and
@@ -252,22 +257,29 @@ __global__ void __launch_bounds__(kThreads, 1)
       float c = -INFINITY, vmax = -INFINITY;
       int amax = INT_MAX;
       uint64_t s2 = 0, t2 = 0;
-      uint32_t ra[32], rb[32];
-      tmem_ld32_async(tbase, ra);
-#pragma unroll 1
-      for (int ch = 0; ch < kLmTileN / 32; ch += 2) {
-        tmem_wait_ld_dep(ra);
-        tmem_ld32_async(tbase + (uint32_t)((ch + 1) * 32), rb);
-        if (col0 + ch * 32 < ga.vocab)
-          fold_chunk<SOFT>(ra, col0 + ch * 32, ga.vocab - (col0 + ch * 32), ga.k, c, s2, t2, vmax, amax);
-        tmem_wait_ld_dep(rb);
-        if (ch + 2 < kLmTileN / 32) tmem_ld32_async(tbase + (uint32_t)((ch + 2) * 32), ra);
-        if (col0 + (ch + 1) * 32 < ga.vocab)
-          fold_chunk<SOFT>(rb, col0 + (ch + 1) * 32, ga.vocab - (col0 + (ch + 1) * 32), ga.k, c, s2, t2, vmax, amax);
+      // The whole row of the tile comes out of tensor memory first, as bf16 pairs (128 registers), and the
+      // accumulators go back to the MMA warp: the arithmetic below runs under the next tile's MMAs.
+      uint32_t p[kLmTileN / 2];
+      {
+        uint32_t ra[16], rb[16];
+        tmem_ld16_async(tbase, ra);
+#pragma unroll
+        for (int sc = 0; sc < kLmTileN / 16; sc += 2) {
+          tmem_wait_ld_dep(ra);
+          tmem_ld16_async(tbase + (uint32_t)((sc + 1) * 16), rb);
+          round_pairs(ra, p + sc * 8);
+          tmem_wait_ld_dep(rb);
+          if (sc + 2 < kLmTileN / 16) tmem_ld16_async(tbase + (uint32_t)((sc + 2) * 16), ra);
+          round_pairs(rb, p + (sc + 1) * 8);
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_free);
+#pragma unroll
+      for (int ch = 0; ch < kLmTileN / 32; ++ch)
+        if (col0 + ch * 32 < ga.vocab)
+          fold_chunk<SOFT>(p + ch * 16, col0 + ch * 32, ga.vocab - (col0 + ch * 32), ga.k, c, s2, t2, vmax, amax);
       if (row < ga.rows) {
         float s_lo, s_hi, t_lo, t_hi;
         f2_unpack(s2, s_lo, s_hi);
