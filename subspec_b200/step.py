@@ -135,16 +135,25 @@ class SpeculativeLoopBatch(SpeculativeStepBatch):
         self.tree_tokens = int(tree_tokens)
         return self.pages.update(add_all=self.tree_tokens, mode="tree", tree_tokens=self.tree_tokens)
 
-    def end_step(self, logits: torch.Tensor, *, verify_method: str = "exact", verify_kwargs: Optional[dict] = None,
-                 eos_token_id: Optional[int] = None) -> None:
-        """verify -> re-root / gather -> delayed KV reorder -> page lists cut back.  No synchronisation."""
+    def end_step(self, logits: Optional[torch.Tensor] = None, *, verify_method: str = "exact",
+                 verify_kwargs: Optional[dict] = None, eos_token_id: Optional[int] = None,
+                 hidden_states: Optional[torch.Tensor] = None, lm_head_weight: Optional[torch.Tensor] = None) -> None:
+        """verify -> re-root / gather -> delayed KV reorder -> page lists cut back.  No synchronisation.
+        With `hidden_states` and `lm_head_weight` instead of `logits` the lm_head product is part of the
+        verification call and the logits are never written (`verify_from_hidden`)."""
         from .postverify import post_verify
 
         st = self.state
         # rows of earlier trees that are still waiting for their reorder sit in front of this tree's rows: the
         # indices that leave this step count from the first of them
         st.skip_nodes.copy_(self.pages.kv_len - self.tree_tokens - st.kv_len)
-        self.verify(logits, verify_method=verify_method, verify_kwargs=verify_kwargs, eos_token_id=eos_token_id)
+        if hidden_states is not None:
+            if logits is not None or lm_head_weight is None:
+                raise ValueError("give either logits, or hidden_states together with lm_head_weight")
+            self.verify_from_hidden(hidden_states, lm_head_weight, verify_method=verify_method,
+                                    verify_kwargs=verify_kwargs, eos_token_id=eos_token_id)
+        else:
+            self.verify(logits, verify_method=verify_method, verify_kwargs=verify_kwargs, eos_token_id=eos_token_id)
         post_verify(self.ws, self.state)
         kv_cache.compact_paged(self.pool, page_table=self.page_table, offset=st.reorder_offset, n=st.reorder_n,
                                beam=st.beam_cache, status=self.status)

@@ -216,3 +216,50 @@ def test_wave_of_the_benchmark_against_the_streaming_kernel(cuda_lib):
                 total += st.n - 1
             assert close > 0.97 * total
     assert accepted > B
+
+
+def test_loop_step_from_hidden_states(cuda_lib):
+    """SpeculativeLoopBatch.end_step with hidden states and the lm_head weight leaves the loop in the state that
+    the same step with the library GEMM's logits leaves it in (targets, re-rooting, page lists, KV rows)."""
+    from subspec_b200.step import SpeculativeLoopBatch
+    from subspec_b200.verify import flatten_tree
+
+    Bn, n, dim, vocab = 4, 16, 128, 997
+    sts, hidden, weight = _case(Bn, n, dim, vocab, seed=21)
+    sts = [synthetic.random_tree(n, 5, 3, vocab, torch.Generator().manual_seed(100 + b)) for b in range(Bn)]
+    for b, st in enumerate(sts):
+        kids = st.children()
+        for u in range(st.n):
+            if kids[u]:
+                hidden[b, u] += (weight[int(st.token_ids[kids[u][0]])].float() * 2.0).to(torch.bfloat16)
+    h, w = hidden.cuda(), weight.cuda()
+    logits = (h.view(-1, dim) @ w.t()).view(Bn, n, vocab)
+    flats = []
+    for s in sts:
+        tok, off, idx = flatten_tree(Tree.from_arrays(s.token_ids.tolist(), s.parents.tolist()), 0)
+        flats.append((tok, off, idx, n, 0))
+    states = []
+    for fused in (False, True):
+        loop = SpeculativeLoopBatch(Bn, n, "cuda", kv_layers=2, kv_heads=2, head_dim=64, page_len=16, pages_per_seq=12,
+                                    init_len=torch.tensor([5, 17, 32, 9]))
+        loop.pool.copy_(torch.randn(loop.pool.shape, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16))
+        loop.begin_step(n)
+        loop.set_trees(flats)
+        if fused:
+            loop.end_step(hidden_states=h, lm_head_weight=w)
+        else:
+            loop.end_step(logits)
+        loop.check()
+        out = loop.ws.fetch()
+        states.append((out["node_target"].copy(), out["out_tokens"].copy(), out["out_hidden"].copy(), out["out_meta"].copy(),
+                       loop.state.next_root.cpu(), loop.state.kv_len.cpu(), loop.pages.kv_len.cpu(), loop.pool.cpu()))
+    assert int(states[0][3][:, 1].sum()) > Bn  # tokens were accepted
+    if not np.array_equal(states[0][0], states[1][0]):
+        # a target decided by the rounding of two different GEMMs: it must be within one bf16 step of the maximum,
+        # and the states behind it are not comparable
+        lg = logits.float().cpu()
+        at = lg.gather(2, torch.from_numpy(states[1][0].astype(np.int64))[..., None]).squeeze(-1)
+        assert bool((at >= lg.max(-1).values - _bf16_step(lg.max(-1).values)).all())
+        pytest.skip("a row's two largest logits are within one bf16 step: the two GEMMs chose differently")
+    for x, y in zip(*states):
+        assert (np.array_equal(x, y) if isinstance(x, np.ndarray) else torch.equal(x, y))
