@@ -263,3 +263,38 @@ def test_loop_step_from_hidden_states(cuda_lib):
         pytest.skip("a row's two largest logits are within one bf16 step: the two GEMMs chose differently")
     for x, y in zip(*states):
         assert (np.array_equal(x, y) if isinstance(x, np.ndarray) else torch.equal(x, y))
+
+
+def test_exact_and_lossy_from_one_call(cuda_lib):
+    """`verify_method="exact+lossy"` (the pair of results a step that verifies greedily and then lossily needs)
+    through the fused call: both results equal those of the streaming kernel on the library GEMM's logits."""
+    B, n, dim, vocab = 6, 48, 768, 32000
+    sts, hidden, weight = _case(B, n, dim, vocab, seed=5)
+    sts = [synthetic.random_tree(n, 6, 4, vocab, torch.Generator().manual_seed(50 + b)) for b in range(B)]  # all rows decoded
+    for b, st in enumerate(sts):
+        kids = st.children()
+        for u in range(st.n):
+            if kids[u] and (u + b) % 3:
+                hidden[b, u] += (weight[int(st.token_ids[kids[u][0]])].float() * 2.0).to(torch.bfloat16)
+    h, w = hidden.cuda(), weight.cuda()
+    logits = (h.view(-1, dim) @ w.t()).view(B, n, vocab)
+    trees = [_build(st) for st in sts]
+    kw = {"threshold_method": "prob", "threshold": 0.02, "window_size": 1}
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ref = verify_tree_batched(trees=trees, root_inds=[0] * B, logits=logits, eos_token_id=None,
+                              verify_method="exact+lossy", verify_kwargs=kw)
+    ref_tgt = get_workspace(B, n, dev).fetch()["node_target"].copy()
+    got = verify_tree_batched(trees=trees, root_inds=[0] * B, hidden_states=h, lm_head_weight=w, eos_token_id=None,
+                              verify_method="exact+lossy", verify_kwargs=kw)
+    out = get_workspace(B, n, dev).fetch()
+    assert int(out["dev_status"][0]) == 0
+    compared = 0
+    for b in range(B):
+        if not np.array_equal(out["node_target"][b], ref_tgt[b]):
+            continue  # a target decided by the rounding of two different GEMMs (checked against the rule elsewhere)
+        compared += 1
+        for r, g in zip(ref[b], got[b]):  # (exact result, lossy result)
+            assert g.sampled_tokens.tolist() == r.sampled_tokens.tolist() and g.hidden_indices.tolist() == r.hidden_indices.tolist()
+            assert (g.total_len, g.accept_len) == (r.total_len, r.accept_len)
+    assert compared >= B - 1
+    assert sum(r[1].accept_len for r in ref) >= sum(r[0].accept_len for r in ref) > 0
