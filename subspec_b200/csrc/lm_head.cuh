@@ -16,7 +16,8 @@ struct LmHeadStat {
   int amax;
 };
 
-constexpr int kLmTileN = 256;  // vocabulary columns per tile
+constexpr int kLmTileN = 256;     // vocabulary columns per tile, at most
+constexpr int kLmMinTileN = 192;  // ... and at least (the launcher picks a multiple of 16 in between)
 
 struct LmHeadGemmArgs {
   const void* hidden;       // [rows, dim] bf16
@@ -26,13 +27,14 @@ struct LmHeadGemmArgs {
   int rows, vocab, dim;
   int soft;                 // 0: maxima only (greedy targets); 1: softmax sums as well
   float k;                  // log2(e) / temperature
-  LmHeadStat* partial;      // [rows, ntiles], ntiles = ceil(vocab / kLmTileN)
+  LmHeadStat* partial;      // [rows, ntiles], room for ntiles = ceil(vocab / kLmMinTileN)
   uint32_t* dev_status;
 };
 
-// Launches the GEMM; cudaErrorInvalidValue when the operands cannot be described to the copy engine
-// (addresses and strides have to be multiples of 16 bytes).
-cudaError_t launch_lm_head_stats(const LmHeadGemmArgs& args, cudaStream_t stream);
+// Launches the GEMM and reports how many column tiles (records per row) it cut the vocabulary into;
+// cudaErrorInvalidValue when the operands cannot be described to the copy engine (addresses and strides have
+// to be multiples of 16 bytes).
+cudaError_t launch_lm_head_stats(const LmHeadGemmArgs& args, cudaStream_t stream, int* ntiles);
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link libcuda).
 typedef CUresult (*tensor_map_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

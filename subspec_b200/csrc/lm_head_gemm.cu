@@ -56,16 +56,18 @@ __device__ __forceinline__ uint64_t kmajor_desc(uint32_t smem_addr) {
 }
 // Instruction descriptor, kind::f16: D fp32 (bit 4), A and B bf16 (1 at [7,10) and [10,13)), both K-major,
 // N >> 3 at [17,23), M >> 4 at [24,29).
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kLmTileN >> 3) << 17) |
-                            ((uint32_t)(kBlockRows >> 4) << 24);
+__device__ __forceinline__ uint32_t make_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBlockRows >> 4) << 24);
+}
 
-__device__ __forceinline__ void mma_bf16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void mma_bf16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       :
-      : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
+      : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Tensor copy (TMA), two coordinates (element of the row, row), global -> shared, completion counted in bytes
@@ -149,10 +151,12 @@ __device__ __forceinline__ void fold_chunk(const uint32_t* p, int col0, int vali
   }
 }
 
-template <bool SOFT>
+// FLEX: the column tile's width is a run-time value (a multiple of 16 up to 256) and a row block without rows
+// is skipped -- the build for a single request's tree; without it the width is 256 and both blocks always run.
+template <bool SOFT, bool FLEX>
 __global__ void __launch_bounds__(kThreads, 1)
-    lm_head_stats_kernel(const LmHeadGemmArgs ga, const int ntiles, const __grid_constant__ CUtensorMap map_a,
-                         const __grid_constant__ CUtensorMap map_b) {
+    lm_head_stats_kernel(const LmHeadGemmArgs ga, const int ntiles, const int tile_n_arg,
+                         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full[kStages], empty[kStages], acc_ready, acc_free;
   __shared__ uint32_t s_tmem;
@@ -180,6 +184,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after();
   const uint32_t tmem = s_tmem;
 
+  const int tile_n = FLEX ? tile_n_arg : kLmTileN;
   const int mtiles = (ga.rows + kTileRows - 1) / kTileRows;
   const int total = mtiles * ntiles;
   const int nkb = (ga.dim + kTileK - 1) / kTileK;
@@ -197,9 +202,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
           unsigned char* stage = ring + (size_t)pos.s * kStageBytes;
-          mbar_expect_tx(&full[pos.s], kStageBytes);
+          mbar_expect_tx(&full[pos.s], (uint32_t)(kABytes + tile_n * kTileK * 2));
           tma_load_2d(stage, &map_a, kb * kTileK, mt * kTileRows, &full[pos.s]);
-          tma_load_2d(stage + kABytes, &map_b, kb * kTileK, nt * kLmTileN, &full[pos.s]);
+          tma_load_2d(stage + kABytes, &map_b, kb * kTileK, nt * tile_n, &full[pos.s]);
           pos.next();
           ++issued;
         }
@@ -219,7 +224,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       RingPos pos;
       bool ok = true;
       uint32_t it = 0;
+      const uint32_t idesc = make_idesc(tile_n);
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++it) {
+        const int mt = tile % mtiles;
+        const int nblk = FLEX && ga.rows - mt * kTileRows <= kBlockRows ? 1 : 2;  // a second row block with rows in it?
         // the epilogue of the tile before has to be out of the accumulators
         if (!lm_wait(&acc_free, (it & 1u) ^ 1u, abort_flag)) break;
         tc_fence_after();
@@ -235,8 +243,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint64_t bdesc = kmajor_desc(b_addr + kk * 32);
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk)
+              if (blk < nblk)
               mma_bf16_ss(tmem + (uint32_t)(blk * kLmTileN), kmajor_desc(a_addr + blk * (kABytes / 2) + kk * 32), bdesc,
-                          (kb | kk) != 0 ? 1u : 0u);
+                          idesc, (kb | kk) != 0 ? 1u : 0u);
           }
           tc_commit(&empty[pos.s]);  // the stage is free once these MMAs have read it
           pos.next();
@@ -253,7 +262,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (!__all_sync(0xffffffffu, lm_wait(&acc_ready, it & 1u, abort_flag))) break;
       tc_fence_after();
       const int row = mt * kTileRows + blk * kBlockRows + quarter * 32 + lane;
-      const int col0 = nt * kLmTileN;
+      const int col0 = nt * tile_n;
+      const int col_end = min(col0 + tile_n, ga.vocab);
+      if (FLEX && mt * kTileRows + blk * kBlockRows >= ga.rows) {  // the block holds no row: nothing was computed for it
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_free);
+        continue;
+      }
       float c = -INFINITY, vmax = -INFINITY;
       int amax = INT_MAX;
       uint64_t s2 = 0, t2 = 0;
@@ -265,6 +280,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         tmem_ld16_async(tbase, ra);
 #pragma unroll
         for (int sc = 0; sc < kLmTileN / 16; sc += 2) {
+          // (columns past the tile's width hold an earlier tile's values: loaded, never looked at)
           tmem_wait_ld_dep(ra);
           tmem_ld16_async(tbase + (uint32_t)((sc + 1) * 16), rb);
           round_pairs(ra, p + sc * 8);
@@ -278,8 +294,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (lane == 0) mbar_arrive(&acc_free);
 #pragma unroll
       for (int ch = 0; ch < kLmTileN / 32; ++ch)
-        if (col0 + ch * 32 < ga.vocab)
-          fold_chunk<SOFT>(p + ch * 16, col0 + ch * 32, ga.vocab - (col0 + ch * 32), ga.k, c, s2, t2, vmax, amax);
+        if (col0 + ch * 32 < col_end)
+          fold_chunk<SOFT>(p + ch * 16, col0 + ch * 32, col_end - (col0 + ch * 32), ga.k, c, s2, t2, vmax, amax);
       if (row < ga.rows) {
         float s_lo, s_hi, t_lo, t_hi;
         f2_unpack(s2, s_lo, s_hi);
@@ -314,22 +330,42 @@ bool encode_rows_map(CUtensorMap* m, const void* base, int64_t stride_elems, int
 
 }  // namespace
 
-cudaError_t launch_lm_head_stats(const LmHeadGemmArgs& ga, cudaStream_t stream) {
+cudaError_t launch_lm_head_stats(const LmHeadGemmArgs& ga, cudaStream_t stream, int* ntiles_out) {
   if (!tensor_map_encoder()) return cudaErrorNotSupported;
   if ((reinterpret_cast<uintptr_t>(ga.hidden) & 15u) || (reinterpret_cast<uintptr_t>(ga.weight) & 15u) ||
       (ga.hidden_stride % 8) || (ga.weight_stride % 8) || ga.hidden_stride < ga.dim || ga.weight_stride < ga.dim)
     return cudaErrorInvalidValue;
+  // Width of a column tile.  256 keeps the MMAs at their best.  With no more than one 128-row block (a single
+  // request's tree) the call is a stream of the weights through HBM, the MMAs idle, and the number of rounds of
+  // tiles the CTAs go through decides (594 tiles of 256 on 148 SMs are five rounds, 732 of 208 five shorter
+  // ones): there, take the width with the smallest rounds x (width + fixed cost).  (With more rows narrower
+  // tiles lost: 1024 rows 0.96 ms at 208 against 0.71 ms at 256.)
+  const int64_t mtiles = (ga.rows + kTileRows - 1) / kTileRows;
+  int tile_n = kLmTileN;
+  double best = 1e30;
+  for (int wdt = kLmTileN; wdt >= (ga.rows <= kBlockRows ? kLmMinTileN : kLmTileN); wdt -= 16) {
+    const int64_t tiles = mtiles * ((ga.vocab + wdt - 1) / wdt);
+    const int64_t rounds = (tiles + kNumSMs - 1) / kNumSMs;
+    const double cost = (double)rounds * (wdt + 12);
+    if (cost < best * 0.97) {  // a narrower tile has to gain 3 % to be taken
+      best = cost;
+      tile_n = wdt;
+    }
+  }
   CUtensorMap map_a, map_b;
   if (!encode_rows_map(&map_a, ga.hidden, ga.hidden_stride, ga.rows, ga.dim, kTileRows) ||
-      !encode_rows_map(&map_b, ga.weight, ga.weight_stride, ga.vocab, ga.dim, kLmTileN))
+      !encode_rows_map(&map_b, ga.weight, ga.weight_stride, ga.vocab, ga.dim, tile_n))
     return cudaErrorInvalidValue;
-  const int ntiles = (ga.vocab + kLmTileN - 1) / kLmTileN;
-  const int64_t total = (int64_t)((ga.rows + kTileRows - 1) / kTileRows) * ntiles;
+  const int ntiles = (ga.vocab + tile_n - 1) / tile_n;
+  const int64_t total = mtiles * ntiles;
   const int grid = (int)(total < kNumSMs ? total : kNumSMs);
-  auto kernel = ga.soft ? lm_head_stats_kernel<true> : lm_head_stats_kernel<false>;
+  const bool flex = ga.rows <= kBlockRows;
+  auto kernel = flex ? (ga.soft ? lm_head_stats_kernel<true, true> : lm_head_stats_kernel<false, true>)
+                     : (ga.soft ? lm_head_stats_kernel<true, false> : lm_head_stats_kernel<false, false>);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
   if (e != cudaSuccess) return e;
-  kernel<<<grid, kThreads, kSmem, stream>>>(ga, ntiles, map_a, map_b);
+  kernel<<<grid, kThreads, kSmem, stream>>>(ga, ntiles, tile_n, map_a, map_b);
+  *ntiles_out = ntiles;
   return cudaGetLastError();
 }
 

@@ -2845,7 +2845,7 @@ extern "C" int subspec_verify_batched(const subspec_verify_args* args, subspec_s
 
 // ---- lm_head + verify without the logits in between ---------------------------------
 static size_t lm_head_stats_bytes(int64_t rows, int vocab) {
-  return align_up(sizeof(LmHeadStat) * (size_t)rows * (size_t)((vocab + kLmTileN - 1) / kLmTileN), 256);
+  return align_up(sizeof(LmHeadStat) * (size_t)rows * (size_t)((vocab + kLmMinTileN - 1) / kLmMinTileN), 256);
 }
 
 extern "C" int subspec_lm_head_verify_scratch_bytes(int32_t batch, int32_t max_nodes, int32_t hidden_seq_rows,
@@ -2906,11 +2906,12 @@ extern "C" int subspec_lm_head_verify(const subspec_lm_head_verify_args* args, s
   if (!(a.flags & SUBSPEC_VERIFY_SCRATCH_CLEAN))
     rc = cuda_check(cudaMemsetAsync(a.scratch, 0, ticket_bytes(a.batch, a.max_nodes), st));
   if (rc) return rc;
-  cudaError_t e = launch_lm_head_stats(ga, st);
+  int ntiles = 0;
+  cudaError_t e = launch_lm_head_stats(ga, st, &ntiles);
   if (e == cudaErrorInvalidValue) return SUBSPEC_EINVAL;  // addresses or strides not multiples of 16 bytes
   if (e != cudaSuccess) return cuda_check(e);
   LmTailArgs lt;
-  lt.partial = ga.partial, lt.ntiles = (a.vocab + kLmTileN - 1) / kLmTileN, lt.seq_rows = args->hidden_seq_rows;
+  lt.partial = ga.partial, lt.ntiles = ntiles, lt.seq_rows = args->hidden_seq_rows;
   lt.dim = args->hidden_dim;
   lt.hidden = reinterpret_cast<const __nv_bfloat16*>(args->hidden), lt.hidden_stride = hs;
   lt.weight = reinterpret_cast<const __nv_bfloat16*>(args->weight), lt.weight_stride = ws;
