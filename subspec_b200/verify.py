@@ -715,11 +715,12 @@ def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logit
 
 
 @torch.no_grad()
-def verify_tree(*, tree, root_ind: int, logits: torch.Tensor, sample_token_fn=None, verify_step_fn=None,
-                eos_token_id: Optional[int], logits_processor, do_sample: bool, skip_nodes: int = 0,
-                verify_method: str = "exact", verify_kwargs: Optional[dict] = None,
+def verify_tree(*, tree, root_ind: int, logits: Optional[torch.Tensor] = None, sample_token_fn=None,
+                verify_step_fn=None, eos_token_id: Optional[int], logits_processor=None, do_sample: bool = False,
+                skip_nodes: int = 0, verify_method: str = "exact", verify_kwargs: Optional[dict] = None,
                 uniforms: Optional[torch.Tensor] = None, draft_logits: Optional[torch.Tensor] = None,
-                accept_uniforms: Optional[torch.Tensor] = None):
+                accept_uniforms: Optional[torch.Tensor] = None, hidden_states: Optional[torch.Tensor] = None,
+                lm_head_weight: Optional[torch.Tensor] = None):
     """Drop-in for the reference's `verify_tree` (tree_verify.py:7-163).
 
     `sample_token_fn` and `verify_step_fn` are accepted so call sites need not
@@ -729,7 +730,11 @@ def verify_tree(*, tree, root_ind: int, logits: torch.Tensor, sample_token_fn=No
     (drawn on the device when not supplied) instead of `torch.multinomial`.
     `draft_logits` [rows, vocab] and `accept_uniforms` [nodes] serve
     `verify_kwargs={"acceptance": "residual"}` (see `verify_tree_batched`).
+    `hidden_states` [1, rows, dim] with `lm_head_weight` [vocab, dim] instead of `logits` (greedy targets): the
+    lm_head product is part of the call and the logits are never written.
     """
+    if hidden_states is not None and hidden_states.dim() == 2:
+        hidden_states = hidden_states.unsqueeze(0)
     if draft_logits is not None and draft_logits.dim() == 2:
         draft_logits = draft_logits.unsqueeze(0)
     if accept_uniforms is not None:
@@ -738,5 +743,6 @@ def verify_tree(*, tree, root_ind: int, logits: torch.Tensor, sample_token_fn=No
                               logits_processor=logits_processor, do_sample=do_sample, skip_nodes=int(skip_nodes),
                               verify_method=verify_method, verify_kwargs=verify_kwargs,
                               uniforms=None if uniforms is None else torch.as_tensor(uniforms).reshape(1, -1),
-                              log_diagnostics=True, draft_logits=draft_logits, accept_uniforms=accept_uniforms)
+                              log_diagnostics=True, draft_logits=draft_logits, accept_uniforms=accept_uniforms,
+                              hidden_states=hidden_states, lm_head_weight=lm_head_weight)
     return res[0].as_tuple()

@@ -298,3 +298,25 @@ def test_exact_and_lossy_from_one_call(cuda_lib):
             assert (g.total_len, g.accept_len) == (r.total_len, r.accept_len)
     assert compared >= B - 1
     assert sum(r[1].accept_len for r in ref) >= sum(r[0].accept_len for r in ref) > 0
+
+
+def test_single_tree_call(cuda_lib):
+    """`verify_tree(..., hidden_states=, lm_head_weight=)`: the reference's call for one tree, fed with the
+    target's last hidden states instead of logits."""
+    from subspec_b200.verify import verify_tree
+
+    sts, hidden, weight = _case(1, 40, 384, 3000, seed=9)
+    st = sts[0]
+    ref = _ref_logits(hidden, weight)
+    toks, hid, (total, acc) = verify_tree(tree=_build(st), root_ind=0, hidden_states=hidden[0, :st.n].cuda(),
+                                          lm_head_weight=weight.cuda(), eos_token_id=None)
+    tgt = get_workspace(1, st.n, torch.device("cuda", torch.cuda.current_device())).fetch()["node_target"][0, :st.n]
+    lg = ref[0, :st.n].float()
+    at = lg.gather(1, torch.from_numpy(tgt.astype(np.int64))[:, None]).squeeze(1)
+    assert bool((at >= lg.max(-1).values - _bf16_step(lg.max(-1).values)).all())
+    r = vo.exact_walk(target=tgt.tolist(), token_ids=st.token_ids.tolist(), children=st.children(), root=0,
+                      n_rows=st.n, eos=None)
+    assert toks.squeeze(0).tolist() == r.tokens and hid.tolist() == r.hidden and (total, acc) == (r.total_len, r.accept_len)
+    with pytest.raises(ValueError):
+        verify_tree(tree=_build(st), root_ind=0, hidden_states=hidden[0, :st.n].cuda(), lm_head_weight=weight.cuda(),
+                    eos_token_id=None, do_sample=True)
