@@ -314,15 +314,18 @@ def _time_ms(fn, iters=10, warm=3):
     return a.elapsed_time(b) / iters
 
 
-def extras(device, peak_gbs, peak_tf):
+def extras(device, peak_gbs, peak_tf, peak_tf_sustained=None):
     """The secondary kernels at their full configurations: one expansion step (config 3), one stochastic
-    verification batch (config 2), the W4A16 GEMM shapes (config 4); each on inputs larger than L2."""
+    verification batch (config 2), the W4A16 GEMM shapes (config 4), tree attention, and the lm_head product fused
+    with the verification of a wave; each on inputs larger than L2."""
     out = {}
     out.update(extra_step_peaked(device, peak_gbs))
     out.update(extra_expand(device, peak_gbs))
     out.update(extra_attention(device, peak_gbs, peak_tf))
     out.update(extra_stochastic(device, peak_gbs))
     out.update(extra_gemm(device, peak_gbs, peak_tf))
+    torch.cuda.empty_cache()
+    out.update(extra_lm_head(device, peak_gbs, peak_tf, peak_tf_sustained or peak_tf))
     return out
 
 
@@ -934,7 +937,8 @@ def main():
                 w[0].pool = None
             del waves[:]
             torch.cuda.empty_cache()
-            line["other_kernels"] = extras(device, peak_gbs, float(peaks.get("bf16_tflops", 1590.0)))
+            line["other_kernels"] = extras(device, peak_gbs, float(peaks.get("bf16_tflops", 1590.0)),
+                                           float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops", 1590.0))))
         if world == 1 and not args.no_cpu_baseline:
             v, desc = cpu_baseline(args.cpu_sample, 5, args.variant)
             line["cpu_baseline"] = {"value": v, "unit": "steps/s", "cores": os.cpu_count(), "kind": "port",
