@@ -780,33 +780,34 @@ SUBSPEC_API int subspec_w4a16_gemm_grouped(const subspec_w4a16_group_args* args,
  * rows (generators/classic_sd.py:100-109) followed by verify_tree / the lossy
  * bottom-up verify (verify/exact_tree_verify.py:11-68,
  * verify/lossy_tree_verify.py:27-226).  The GEMM runs on the tensor cores
- * and its epilogue folds every accumulator tile, rounded to bf16 as the
- * reference's lm_head output is, into per-row statistics (maximum, first
+ * and its epilogue folds every accumulator tile, rounded to the model's
+ * 16-bit dtype as the reference's lm_head output is, into per-row statistics (maximum, first
  * arg-max, sum 2^y, sum y 2^y); a second small kernel combines them per row,
  * computes the probabilities of the children's tokens from dot products of the
  * row's hidden state with those tokens' weight rows, and runs the same walk
  * as subspec_verify_batched.  The [rows, vocab] logits are never written.
  *
  * `verify` is a subspec_verify_args as for subspec_verify_batched with:
- * logits / seq_stride / row_stride / input_kind ignored, dtype = SUBSPEC_BF16,
- * do_sample = 0, acceptance = 0; every method and gate is accepted.  Its
+ * logits / seq_stride / row_stride / input_kind ignored, dtype = SUBSPEC_BF16
+ * or SUBSPEC_F16 (the dtype of `hidden`, `weight` and of the logits the call
+ * stands for), do_sample = 0, acceptance = 0; every method and gate is accepted.  Its
  * scratch must hold subspec_lm_head_verify_scratch_bytes bytes.  Row u of
  * sequence b is row b * hidden_seq_rows + u of `hidden`.
  *
  * Results against a library GEMM + subspec_verify_batched: the accumulation
  * order of a GEMM is its own, so a logit that sits within fp32 rounding of a
- * bf16 rounding boundary may come out one bf16 step apart; targets can
+ * 16-bit rounding boundary may come out one step of that dtype apart; targets can
  * differ where the two largest logits of a row are that close, and a child's
- * probability by the factor e^(one bf16 step of its logit).
+ * probability by the factor e^(one such step of its logit).
  * Limits: hidden_dim % 8 == 0, strides % 8 == 0, addresses 16-byte aligned
  * (SUBSPEC_EINVAL otherwise); vocab <= 2^20.
  * ---------------------------------------------------------------------- */
 typedef struct subspec_lm_head_verify_args {
   uint32_t struct_size;
   int32_t hidden_dim;        /* K */
-  const void* hidden;        /* bf16 [batch * hidden_seq_rows, hidden_dim] */
+  const void* hidden;        /* bf16 / fp16 [batch * hidden_seq_rows, hidden_dim] */
   int64_t hidden_row_stride; /* elements; 0 = hidden_dim */
-  const void* weight;        /* bf16 [vocab, hidden_dim]: the lm_head's weight as nn.Linear holds it */
+  const void* weight;        /* same dtype, [vocab, hidden_dim]: the lm_head's weight as nn.Linear holds it */
   int64_t weight_row_stride; /* elements; 0 = hidden_dim */
   int32_t hidden_seq_rows;   /* rows of `hidden` per sequence, >= every n_rows[b] */
   int32_t reserved;

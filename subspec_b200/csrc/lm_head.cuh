@@ -20,9 +20,10 @@ constexpr int kLmTileN = 256;     // vocabulary columns per tile, at most
 constexpr int kLmMinTileN = 192;  // ... and at least (the launcher picks a multiple of 16 in between)
 
 struct LmHeadGemmArgs {
-  const void* hidden;       // [rows, dim] bf16
+  int half;                 // operands and the logits' rounding: 0 bf16, 1 fp16
+  const void* hidden;       // [rows, dim]
   int64_t hidden_stride;    // elements between rows
-  const void* weight;       // [vocab, dim] bf16
+  const void* weight;       // [vocab, dim]
   int64_t weight_stride;
   int rows, vocab, dim;
   int soft;                 // 0: maxima only (greedy targets); 1: softmax sums as well

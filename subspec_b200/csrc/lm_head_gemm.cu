@@ -5,7 +5,8 @@
 // a [rows, vocab] bf16 tensor written and read again, 2 x 1.25 GB per wave of 64 trees of 64 nodes.  Here the
 // accumulator tile of the GEMM is folded in place: every element is rounded to bf16 (what the reference's
 // lm_head returns) and goes into the row's maximum / first arg-max and, for the lossy gates, into
-// sum 2^y and sum y 2^y; what leaves the kernel is one 20-byte record per (row, 256-column tile).
+// sum 2^y and sum y 2^y; what leaves the kernel is one 20-byte record per (row, 256-column tile).  fp16 models
+// (the reference's usual dtype) take the same path with fp16 operands and fp16 rounding.
 //
 // One persistent CTA per SM walks (row tile, column tile) pairs, the row tiles of one column tile next to each
 // other so that CTAs running at the same time share weight tiles in L2.  A tile is 256 rows x 256 columns: two
@@ -54,10 +55,11 @@ __device__ __forceinline__ uint64_t kmajor_desc(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;
   return d;
 }
-// Instruction descriptor, kind::f16: D fp32 (bit 4), A and B bf16 (1 at [7,10) and [10,13)), both K-major,
+// Instruction descriptor, kind::f16: D fp32 (bit 4), A and B bf16 (1 at [7,10) and [10,13)) or fp16 (0), both K-major,
 // N >> 3 at [17,23), M >> 4 at [24,29).
-__device__ __forceinline__ uint32_t make_idesc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBlockRows >> 4) << 24);
+__device__ __forceinline__ uint32_t make_idesc(int n, bool half) {
+  const uint32_t fmt = half ? 0u : 1u;  // fp16 : bf16
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBlockRows >> 4) << 24);
 }
 
 __device__ __forceinline__ void mma_bf16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -91,23 +93,35 @@ struct RingPos {
   }
 };
 
-// 16 fp32 accumulators -> 8 bf16 pairs: the logits as the reference sees them, rounded to bf16.
+// 16 fp32 accumulators -> 8 pairs of 16-bit floats: the logits as the reference sees them, rounded to the
+// model's dtype (HALF: fp16, else bf16).
+template <bool HALF>
 __device__ __forceinline__ void round_pairs(const uint32_t (&r)[16], uint32_t* p) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j)
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(p[j]) : "f"(__uint_as_float(r[2 * j + 1])), "f"(__uint_as_float(r[2 * j])));
+  for (int j = 0; j < 8; ++j) {
+    if (HALF)
+      asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(p[j]) : "f"(__uint_as_float(r[2 * j + 1])), "f"(__uint_as_float(r[2 * j])));
+    else
+      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(p[j]) : "f"(__uint_as_float(r[2 * j + 1])), "f"(__uint_as_float(r[2 * j])));
+  }
 }
 
-// Folds 32 consecutive columns of a row, held as 16 bf16 pairs, into the row's statistics.  `valid` columns of
-// the chunk lie inside the vocabulary (>= 32 everywhere but in the last tile).
-template <bool SOFT>
+// Folds 32 consecutive columns of a row, held as 16 pairs of 16-bit floats, into the row's statistics.  `valid`
+// columns of the chunk lie inside the tile and the vocabulary (>= 32 everywhere but at their ends).
+template <bool SOFT, bool HALF>
 __device__ __forceinline__ void fold_chunk(const uint32_t* p, int col0, int valid, float k, float& c, uint64_t& s2,
                                            uint64_t& t2, float& vmax, int& amax) {
   float x[32];
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
-    x[2 * j] = __uint_as_float(p[j] << 16);
-    x[2 * j + 1] = __uint_as_float(p[j] & 0xffff0000u);
+    if (HALF) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&p[j]));
+      x[2 * j] = f.x;
+      x[2 * j + 1] = f.y;
+    } else {
+      x[2 * j] = __uint_as_float(p[j] << 16);
+      x[2 * j + 1] = __uint_as_float(p[j] & 0xffff0000u);
+    }
   }
   if (valid < 32) {
     // columns past the vocabulary (the copy engine filled their weights with zeros): far below any logit, and
@@ -153,7 +167,7 @@ __device__ __forceinline__ void fold_chunk(const uint32_t* p, int col0, int vali
 
 // FLEX: the column tile's width is a run-time value (a multiple of 16 up to 256) and a row block without rows
 // is skipped -- the build for a single request's tree; without it the width is 256 and both blocks always run.
-template <bool SOFT, bool FLEX>
+template <bool SOFT, bool FLEX, bool HALF>
 __global__ void __launch_bounds__(kThreads, 1)
     lm_head_stats_kernel(const LmHeadGemmArgs ga, const int ntiles, const int tile_n_arg,
                          const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b) {
@@ -224,7 +238,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       RingPos pos;
       bool ok = true;
       uint32_t it = 0;
-      const uint32_t idesc = make_idesc(tile_n);
+      const uint32_t idesc = make_idesc(tile_n, HALF);
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++it) {
         const int mt = tile % mtiles;
         const int nblk = FLEX && ga.rows - mt * kTileRows <= kBlockRows ? 1 : 2;  // a second row block with rows in it?
@@ -283,10 +297,10 @@ __global__ void __launch_bounds__(kThreads, 1)
           // (columns past the tile's width hold an earlier tile's values: loaded, never looked at)
           tmem_wait_ld_dep(ra);
           tmem_ld16_async(tbase + (uint32_t)((sc + 1) * 16), rb);
-          round_pairs(ra, p + sc * 8);
+          round_pairs<HALF>(ra, p + sc * 8);
           tmem_wait_ld_dep(rb);
           if (sc + 2 < kLmTileN / 16) tmem_ld16_async(tbase + (uint32_t)((sc + 2) * 16), ra);
-          round_pairs(rb, p + (sc + 1) * 8);
+          round_pairs<HALF>(rb, p + (sc + 1) * 8);
         }
       }
       tc_fence_before();
@@ -295,7 +309,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
       for (int ch = 0; ch < kLmTileN / 32; ++ch)
         if (col0 + ch * 32 < col_end)
-          fold_chunk<SOFT>(p + ch * 16, col0 + ch * 32, col_end - (col0 + ch * 32), ga.k, c, s2, t2, vmax, amax);
+          fold_chunk<SOFT, HALF>(p + ch * 16, col0 + ch * 32, col_end - (col0 + ch * 32), ga.k, c, s2, t2, vmax, amax);
       if (row < ga.rows) {
         float s_lo, s_hi, t_lo, t_hi;
         f2_unpack(s2, s_lo, s_hi);
@@ -318,12 +332,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0 && s_abort) flag(ga.dev_status, SUBSPEC_DEV_TIMEOUT);
 }
 
-bool encode_rows_map(CUtensorMap* m, const void* base, int64_t stride_elems, int rows, int dim, int box_rows) {
+bool encode_rows_map(CUtensorMap* m, const void* base, int64_t stride_elems, int rows, int dim, int box_rows, bool half) {
   const cuuint64_t dims[2] = {(cuuint64_t)dim, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)stride_elems * 2};
   const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  return tensor_map_encoder()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  return tensor_map_encoder()(m, half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -353,15 +367,21 @@ cudaError_t launch_lm_head_stats(const LmHeadGemmArgs& ga, cudaStream_t stream, 
     }
   }
   CUtensorMap map_a, map_b;
-  if (!encode_rows_map(&map_a, ga.hidden, ga.hidden_stride, ga.rows, ga.dim, kTileRows) ||
-      !encode_rows_map(&map_b, ga.weight, ga.weight_stride, ga.vocab, ga.dim, tile_n))
+  const bool half = ga.half != 0;
+  if (!encode_rows_map(&map_a, ga.hidden, ga.hidden_stride, ga.rows, ga.dim, kTileRows, half) ||
+      !encode_rows_map(&map_b, ga.weight, ga.weight_stride, ga.vocab, ga.dim, tile_n, half))
     return cudaErrorInvalidValue;
   const int ntiles = (ga.vocab + tile_n - 1) / tile_n;
   const int64_t total = mtiles * ntiles;
   const int grid = (int)(total < kNumSMs ? total : kNumSMs);
   const bool flex = ga.rows <= kBlockRows;
-  auto kernel = flex ? (ga.soft ? lm_head_stats_kernel<true, true> : lm_head_stats_kernel<false, true>)
-                     : (ga.soft ? lm_head_stats_kernel<true, false> : lm_head_stats_kernel<false, false>);
+  using Kernel = void (*)(const LmHeadGemmArgs, const int, const int, const CUtensorMap, const CUtensorMap);
+  static const Kernel kernels[8] = {
+      lm_head_stats_kernel<false, false, false>, lm_head_stats_kernel<false, false, true>,
+      lm_head_stats_kernel<false, true, false>,  lm_head_stats_kernel<false, true, true>,
+      lm_head_stats_kernel<true, false, false>,  lm_head_stats_kernel<true, false, true>,
+      lm_head_stats_kernel<true, true, false>,   lm_head_stats_kernel<true, true, true>};
+  const Kernel kernel = kernels[(ga.soft ? 4 : 0) + (flex ? 2 : 0) + (half ? 1 : 0)];
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
   if (e != cudaSuccess) return e;
   kernel<<<grid, kThreads, kSmem, stream>>>(ga, ntiles, tile_n, map_a, map_b);

@@ -2604,11 +2604,22 @@ static_assert(sizeof(LmHeadStat) == sizeof(RowStat), "the GEMM's records are rea
 struct LmTailArgs {
   const LmHeadStat* partial;  // [batch * seq_rows, ntiles]
   int ntiles, seq_rows, dim;
-  const __nv_bfloat16* hidden;
+  int half;  // 16-bit operands: 0 bf16, 1 fp16
+  const uint16_t* hidden;
   int64_t hidden_stride;
-  const __nv_bfloat16* weight;
+  const uint16_t* weight;
   int64_t weight_stride;
 };
+
+// the two 16-bit floats of a word as fp32
+__device__ __forceinline__ void pair_to_f32(uint32_t w, bool half, float& lo, float& hi) {
+  if (half) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    lo = f.x, hi = f.y;
+  } else {
+    lo = __uint_as_float(w << 16), hi = __uint_as_float(w & 0xffff0000u);
+  }
+}
 
 template <bool SOFT>
 __global__ void __launch_bounds__(kThreads) lm_head_tail_kernel(const KArgs ka, const LmTailArgs lt) {
@@ -2674,13 +2685,16 @@ __global__ void __launch_bounds__(kThreads) lm_head_tail_kernel(const KArgs ka, 
           const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w}, ww[4] = {wq.x, wq.y, wq.z, wq.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            acc = fmaf(__uint_as_float(hw[j] << 16), __uint_as_float(ww[j] << 16), acc);
-            acc = fmaf(__uint_as_float(hw[j] & 0xffff0000u), __uint_as_float(ww[j] & 0xffff0000u), acc);
+            float h0, h1, w0, w1;
+            pair_to_f32(hw[j], lt.half != 0, h0, h1);
+            pair_to_f32(ww[j], lt.half != 0, w0, w1);
+            acc = fmaf(h0, w0, acc);
+            acc = fmaf(h1, w1, acc);
           }
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-        const float x = __bfloat162float(__float2bfloat16_rn(acc));
+        const float x = lt.half ? __half2float(__float2half_rn(acc)) : __bfloat162float(__float2bfloat16_rn(acc));
         p = ex2f(fmaf(x, ka.k, -r.c)) / r.s;
       }
       if (lane == 0) a.node_child_prob[nb + c] = p;
@@ -2866,7 +2880,8 @@ extern "C" int subspec_lm_head_verify(const subspec_lm_head_verify_args* args, s
       args->hidden_seq_rows < 1)
     return SUBSPEC_EINVAL;
   if (a.max_nodes > kMaxNodes || a.vocab > (1 << 20) || args->hidden_dim % 8) return SUBSPEC_EUNSUPPORTED;
-  if (a.dtype != SUBSPEC_BF16) return SUBSPEC_EUNSUPPORTED;  // the logits this call stands for are bf16
+  // the dtype of hidden states and weight, and of the logits this call stands for
+  if (a.dtype != SUBSPEC_BF16 && a.dtype != SUBSPEC_F16) return SUBSPEC_EUNSUPPORTED;
   if (a.do_sample || a.acceptance) return SUBSPEC_EUNSUPPORTED;  // sampled targets need the whole row
   if (a.method != SUBSPEC_VERIFY_EXACT && a.method != SUBSPEC_VERIFY_LOSSY &&
       a.method != SUBSPEC_VERIFY_EXACT_AND_LOSSY)
@@ -2896,6 +2911,7 @@ extern "C" int subspec_lm_head_verify(const subspec_lm_head_verify_args* args, s
   ka.k = kLog2e;
   const bool soft = a.method != SUBSPEC_VERIFY_EXACT;
   LmHeadGemmArgs ga;
+  ga.half = a.dtype == SUBSPEC_F16 ? 1 : 0;
   ga.hidden = args->hidden, ga.hidden_stride = hs, ga.weight = args->weight, ga.weight_stride = ws;
   ga.rows = (int)rows, ga.vocab = a.vocab, ga.dim = args->hidden_dim;
   ga.soft = soft ? 1 : 0;
@@ -2913,8 +2929,9 @@ extern "C" int subspec_lm_head_verify(const subspec_lm_head_verify_args* args, s
   LmTailArgs lt;
   lt.partial = ga.partial, lt.ntiles = ntiles, lt.seq_rows = args->hidden_seq_rows;
   lt.dim = args->hidden_dim;
-  lt.hidden = reinterpret_cast<const __nv_bfloat16*>(args->hidden), lt.hidden_stride = hs;
-  lt.weight = reinterpret_cast<const __nv_bfloat16*>(args->weight), lt.weight_stride = ws;
+  lt.half = ga.half;
+  lt.hidden = reinterpret_cast<const uint16_t*>(args->hidden), lt.hidden_stride = hs;
+  lt.weight = reinterpret_cast<const uint16_t*>(args->weight), lt.weight_stride = ws;
   const size_t smem = sizeof(int) * (9 * (size_t)a.max_nodes + 1);
   const int grid = a.batch * a.max_nodes;
   if (soft) {

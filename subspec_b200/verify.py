@@ -204,16 +204,16 @@ class VerifyWorkspace:
 
     def run_lm_head(self, hidden: torch.Tensor, weight: torch.Tensor, *, method: int, gate: int = _lib.GATE_PROB,
                     threshold: float = 0.0, window: int = 1, eos: Optional[int] = None) -> None:
-        """lm_head and verification in one call (greedy targets): `hidden` [batch, rows, dim] bf16 are the
-        target's last hidden states of the tree rows, `weight` [vocab, dim] bf16 the lm_head's weight.  Stands
+        """lm_head and verification in one call (greedy targets): `hidden` [batch, rows, dim] (bf16 or fp16) are the
+        target's last hidden states of the tree rows, `weight` [vocab, dim] (same dtype) the lm_head's weight.  Stands
         for `logits = lm_head(hidden)` (generators/classic_sd.py:100-109) followed by `run(logits, ...)`;
         the logits are never written.  Results as `run`'s, up to the rounding of a different GEMM."""
         B, N = self.batch, self.max_nodes
         if hidden.dim() != 3 or hidden.shape[0] != B or weight.dim() != 2 or weight.shape[1] != hidden.shape[2]:
             raise ValueError(f"hidden must be [batch={B}, rows, dim] and weight [vocab, dim], got "
                              f"{tuple(hidden.shape)} and {tuple(weight.shape)}")
-        if hidden.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
-            raise ValueError("hidden and weight must be bfloat16")
+        if hidden.dtype not in (torch.bfloat16, torch.float16) or weight.dtype != hidden.dtype:
+            raise ValueError("hidden and weight must both be bfloat16 or both float16")
         if hidden.device != self.device or weight.device != self.device:
             raise ValueError("hidden / weight live on another device than the workspace")
         if not hidden.is_contiguous():
@@ -238,7 +238,7 @@ class VerifyWorkspace:
         a = la.verify
         a.struct_size = C.sizeof(_lib.VerifyArgs)
         a.batch, a.max_nodes, a.vocab = B, N, vocab
-        a.dtype, a.input_kind = _lib.torch_dtype_code(torch.bfloat16), _lib.IN_LOGITS
+        a.dtype, a.input_kind = _lib.torch_dtype_code(hidden.dtype), _lib.IN_LOGITS
         for name in ("n_nodes", "n_rows", "token_ids", "child_off", "child_idx", "root"):
             setattr(a, name, self._in_ptr(name))
         a.temperature, a.top_p = 1.0, 1.0
@@ -610,7 +610,7 @@ def verify_tree_batched(*, trees: Sequence[Any], root_inds: Sequence[int], logit
                         lm_head_weight: Optional[torch.Tensor] = None) -> List[VerifyOutput]:
     """Verify `len(trees)` independent draft trees against `logits` [batch, rows, vocab] in one launch.
 
-    Instead of `logits`, `hidden_states` [batch, rows, dim] and `lm_head_weight` [vocab, dim] (both bf16) may be
+    Instead of `logits`, `hidden_states` [batch, rows, dim] and `lm_head_weight` [vocab, dim] (both bf16 or fp16) may be
     given (greedy targets only): the lm_head product and the verification then run as one call that never
     writes the logits (`VerifyWorkspace.run_lm_head`).
 

@@ -29,30 +29,31 @@ def _build(st: synthetic.SynthTree) -> Tree:
     return Tree.from_arrays(st.token_ids.tolist(), st.parents.tolist())
 
 
-def _case(B, n, dim, vocab, seed, boost=True):
+def _case(B, n, dim, vocab, seed, boost=True, dtype=torch.bfloat16):
     gen = torch.Generator().manual_seed(seed)
     sts = [synthetic.random_tree(n - (b % 3), 6, 4, vocab, gen) for b in range(B)]
-    hidden = torch.randn(B, n, dim, generator=gen).to(torch.bfloat16)
-    weight = (torch.randn(vocab, dim, generator=gen) * (3.0 / dim ** 0.5)).to(torch.bfloat16)
+    hidden = torch.randn(B, n, dim, generator=gen).to(dtype)
+    weight = (torch.randn(vocab, dim, generator=gen) * (3.0 / dim ** 0.5)).to(dtype)
     if boost:
         # make the draft right most of the time: the hidden state of a node points at the weight row of its
         # first child's token, so that walks accept and the lossy gates see probabilities that matter
         for b, st in enumerate(sts):
             kids = st.children()
             for u in range(st.n):
-                if kids[u] and (u + b) % 4:
-                    hidden[b, u] += (weight[int(st.token_ids[kids[u][0]])].float() * 1.5).to(torch.bfloat16)
+                if kids[u] and (u + b) % 4 != 3:
+                    hidden[b, u] += (weight[int(st.token_ids[kids[u][0]])].float() * 1.5).to(dtype)
     return sts, hidden, weight
 
 
 def _ref_logits(hidden, weight):
     B, n, dim = hidden.shape
-    return (hidden.float().view(-1, dim) @ weight.float().t()).view(B, n, -1).to(torch.bfloat16)
+    return (hidden.float().view(-1, dim) @ weight.float().t()).view(B, n, -1).to(hidden.dtype)
 
 
-def _bf16_step(x: torch.Tensor) -> torch.Tensor:
-    """The distance from |x| to the next bf16 value above it."""
-    return torch.maximum(x.abs().float(), torch.tensor(2.0 ** -126)).log2().floor().exp2() * 2.0 ** -7
+def _bf16_step(x: torch.Tensor, mantissa_bits: int = 7) -> torch.Tensor:
+    """The distance from |x| to the next bf16 value above it (with 10 mantissa bits: the next fp16 value; a bf16
+    step is never smaller, so it serves as the tolerance for both)."""
+    return torch.maximum(x.abs().float(), torch.tensor(2.0 ** -126)).log2().floor().exp2() * 2.0 ** -mantissa_bits
 
 
 def _check_against(sts, ref_logits, got, out, ref_results, exact_outputs=True):
@@ -71,11 +72,16 @@ def _check_against(sts, ref_logits, got, out, ref_results, exact_outputs=True):
             assert (got[b].total_len, got[b].accept_len) == r[2], b
 
 
-@pytest.mark.parametrize("B,n,dim,vocab", [(4, 33, 512, 5000),      # fewer rows than a tile, ragged last tile
-                                           (3, 64, 264, 255),        # one column tile, dim not a multiple of 64
-                                           (9, 40, 1024, 8192 + 40)])
-def test_matches_oracle_on_rounded_logits(cuda_lib, B, n, dim, vocab):
-    sts, hidden, weight = _case(B, n, dim, vocab, seed=B * 7 + n)
+@pytest.mark.parametrize("B,n,dim,vocab,dtype", [
+    (4, 33, 512, 5000, torch.bfloat16),      # fewer rows than a tile, ragged last tile
+    (3, 64, 264, 255, torch.bfloat16),        # one column tile, dim not a multiple of 64
+    (9, 40, 1024, 8192 + 40, torch.bfloat16),
+    (1, 64, 768, 40000, torch.bfloat16),      # one request: narrowed column tiles, second row block skipped
+    (4, 33, 512, 5000, torch.float16),        # the reference's usual dtype
+    (1, 50, 768, 30001, torch.float16),
+    (7, 48, 1024, 9000, torch.float16)])
+def test_matches_oracle_on_rounded_logits(cuda_lib, B, n, dim, vocab, dtype):
+    sts, hidden, weight = _case(B, n, dim, vocab, seed=B * 7 + n, dtype=dtype)
     ref = _ref_logits(hidden, weight)
     trees = [_build(st) for st in sts]
     accepted = 0
@@ -156,14 +162,14 @@ def test_rows_per_sequence_and_strides(cuda_lib):
     for b, st in enumerate(sts):
         assert out["node_target"][b, :st.n].tolist() == want[b, :st.n].tolist()
         assert out["node_target"][b, :st.n].tolist() == ref[b, :st.n].float().argmax(-1).tolist()
-    # arguments the call refuses: a stride that is not a multiple of 16 bytes, sampled targets, fp16
+    # arguments the call refuses: a stride that is not a multiple of 16 bytes, sampled targets, fp32 operands
     la.hidden_row_stride = hd.stride(1) + 1
     assert _lib.lib().subspec_lm_head_verify(C.byref(la), C.c_void_p(stream)) == _lib.EINVAL
     la.hidden_row_stride = hd.stride(1)
     a.do_sample = 1
     assert _lib.lib().subspec_lm_head_verify(C.byref(la), C.c_void_p(stream)) == _lib.EUNSUPPORTED
     a.do_sample = 0
-    a.dtype = _lib.torch_dtype_code(torch.float16)
+    a.dtype = _lib.torch_dtype_code(torch.float32)
     assert _lib.lib().subspec_lm_head_verify(C.byref(la), C.c_void_p(stream)) == _lib.EUNSUPPORTED
     a.dtype = _lib.torch_dtype_code(torch.bfloat16)
     a.scratch_bytes = need.value - 256
