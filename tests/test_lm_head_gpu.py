@@ -326,3 +326,39 @@ def test_single_tree_call(cuda_lib):
     with pytest.raises(ValueError):
         verify_tree(tree=_build(st), root_ind=0, hidden_states=hidden[0, :st.n].cuda(), lm_head_weight=weight.cuda(),
                     eos_token_id=None, do_sample=True)
+
+
+def test_fused_call_in_a_cuda_graph(cuda_lib):
+    """The call captures into a CUDA graph (no allocation, no synchronisation inside) and a replay on new hidden
+    states in the same buffer gives that input's results."""
+    B, n, dim, vocab = 3, 32, 512, 6000
+    sts, hidden, weight = _case(B, n, dim, vocab, seed=13)
+    _, hidden2, _ = _case(B, n, dim, vocab, seed=14)
+    trees = [_build(st) for st in sts]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    from subspec_b200.verify import _prepare_tree
+    ws = get_workspace(B, max(st.n for st in sts), dev)
+    ws.set_trees([_prepare_tree(t, 0, 0, n, _lib.VERIFY_LOSSY) for t in trees])
+    h, w = hidden.cuda(), weight.cuda()
+    kw = dict(method=_lib.VERIFY_LOSSY, gate=_lib.GATE_ENTROPY, threshold=0.3, window=1)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ws.run_lm_head(h, w, **kw)   # first call outside the capture: sizes the scratch
+    torch.cuda.current_stream().wait_stream(side)
+    eager = {k: v.copy() for k, v in ws.fetch().items()}
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ws.run_lm_head(h, w, **kw)
+    graph.replay()
+    out = ws.fetch()
+    for key in ("out_tokens", "out_hidden", "out_meta", "node_target", "node_entropy"):
+        assert np.array_equal(out[key], eager[key]), key
+    h.copy_(hidden2.cuda())
+    graph.replay()
+    out2 = {k: v.copy() for k, v in ws.fetch().items()}
+    ws.run_lm_head(h, w, **kw)
+    want2 = ws.fetch()
+    assert not np.array_equal(out2["node_target"], eager["node_target"])
+    for key in ("out_tokens", "out_hidden", "out_meta", "node_target", "node_entropy"):
+        assert np.array_equal(out2[key], want2[key]), key
