@@ -15,6 +15,8 @@
 // (256 x 64 hidden, 256 x 64 weight) pairs; warp 9 issues tcgen05.mma (both operands in shared memory, K-major,
 // accumulators in tensor memory: 2 x 256 columns); warps 0-7 are the epilogue, thread = row = tensor-memory
 // lane.  All waits are bounded.
+#include <limits.h>
+
 #include "lm_head.cuh"
 #include "tcgen05.cuh"
 
@@ -373,6 +375,7 @@ cudaError_t launch_lm_head_stats(const LmHeadGemmArgs& ga, cudaStream_t stream, 
     return cudaErrorInvalidValue;
   const int ntiles = (ga.vocab + tile_n - 1) / tile_n;
   const int64_t total = mtiles * ntiles;
+  if (total > INT_MAX) return cudaErrorInvalidValue;  // the kernel counts tiles in 32 bits
   const int grid = (int)(total < kNumSMs ? total : kNumSMs);
   const bool flex = ga.rows <= kBlockRows;
   using Kernel = void (*)(const LmHeadGemmArgs, const int, const int, const CUtensorMap, const CUtensorMap);
