@@ -392,7 +392,7 @@ typedef struct subspec_expand_args {
   int32_t* tree_parents;
   float* tree_probs;
   int32_t* tree_depths;
-  void* scratch; /* subspec_expand_scratch_bytes(), 256-byte aligned, no initialisation needed */
+  void* scratch; /* subspec_expand_scratch_bytes(), 256-byte aligned, no initialisation needed (but see flags) */
   size_t scratch_bytes;
   uint32_t* dev_status;
   /* Optional (needs the tree arrays): the draft-side tree mask of the new level and its position ids. */
@@ -403,7 +403,15 @@ typedef struct subspec_expand_args {
   int64_t draft_mask_seq_stride; /* elements; 0 = k * row stride */
   const int32_t* prefix_len;     /* [batch] tokens in front of the tree's first level, or NULL (= 0) */
   int64_t* draft_position_ids;   /* [batch, k] = prefix_len[b] + level, or NULL */
+  uint32_t flags;                /* 0, or SUBSPEC_EXPAND_SCRATCH_CLEAN */
+  uint32_t reserved;
 } subspec_expand_args;
+
+/* The caller promises that the first 4 * batch bytes of `scratch` (rounded up to 256) were zero before the
+ * first call that used the buffer, and that only subspec_expand_step calls with this `batch` whose dev_status
+ * stayed clear have used it since: every such call leaves them zero, and the entry point then puts no clearing
+ * operation in front of the kernel (one launch fewer per level of the draft tree). */
+#define SUBSPEC_EXPAND_SCRATCH_CLEAN 1u
 
 SUBSPEC_API int subspec_expand_scratch_bytes(int32_t batch, int32_t leaves, int32_t k, size_t* bytes);
 SUBSPEC_API int subspec_expand_step(const subspec_expand_args* args, subspec_stream_t stream);

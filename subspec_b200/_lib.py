@@ -16,6 +16,7 @@ F32, BF16, F16 = 0, 1, 2
 IN_LOGITS, IN_PROBS = 0, 1
 VERIFY_EXACT, VERIFY_LOSSY, VERIFY_EXACT_AND_LOSSY = 0, 1, 2
 VERIFY_SCRATCH_CLEAN = 1  # SUBSPEC_VERIFY_SCRATCH_CLEAN
+EXPAND_SCRATCH_CLEAN = 1  # SUBSPEC_EXPAND_SCRATCH_CLEAN
 GATE_PROB, GATE_ENTROPY = 0, 1
 DEV_BAD_TOKEN, DEV_BAD_CHILD, DEV_BAD_ROOT, DEV_BAD_PAGE, DEV_BAD_INDEX, DEV_TIMEOUT, DEV_HIST_OVERFLOW = 1, 2, 4, 8, 16, 32, 64
 DEV_BAD_PARENT, DEV_BAD_COUNT = 128, 256
@@ -107,6 +108,7 @@ class ExpandArgs(C.Structure):
         ("tree_depths", _vp), ("scratch", _vp), ("scratch_bytes", C.c_size_t), ("dev_status", _vp),
         ("draft_mask", _vp), ("draft_mask_kind", _i32), ("draft_mask_cols", _i64), ("draft_mask_row_stride", _i64),
         ("draft_mask_seq_stride", _i64), ("prefix_len", _vp), ("draft_position_ids", _vp),
+        ("flags", _u32), ("reserved", _u32),
     ]
 
 

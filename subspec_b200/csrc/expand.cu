@@ -619,7 +619,10 @@ __global__ void __launch_bounds__(kThreads, 4) expand_rows_kernel(const KArgs ka
   }
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) s_flag = (atomicAdd(ka.ticket + b, 1) == L * S - 1);
+  if (threadIdx.x == 0) {
+    s_flag = (atomicAdd(ka.ticket + b, 1) == L * S - 1);
+    if (s_flag) ka.ticket[b] = 0;  // everybody has been: left as found, zero, for the next launch
+  }
   __syncthreads();
   if (!s_flag) return;
   __threadfence();
@@ -957,7 +960,11 @@ extern "C" int subspec_expand_step(const subspec_expand_args* args, subspec_stre
     if (sp >= 2) ka.splits = (int)sp;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  int rc = cuda_check(cudaMemsetAsync(ka.ticket, 0, sizeof(int) * (size_t)a.batch, st));
+  // The tickets have to be zero; every launch leaves them so (the last arrival resets its ticket), so a caller
+  // who vouches for the buffer saves this node in front of the kernel.
+  int rc = SUBSPEC_OK;
+  if (!(a.flags & SUBSPEC_EXPAND_SCRATCH_CLEAN))
+    rc = cuda_check(cudaMemsetAsync(ka.ticket, 0, sizeof(int) * (size_t)a.batch, st));
   if (rc) return rc;
   cudaError_t e;
   switch (a.dtype) {

@@ -105,12 +105,16 @@ _scratch: Dict[Tuple[int, int], torch.Tensor] = {}
 
 
 def _scratch_for(device: torch.device, batch: int, leaves: int, k: int) -> Tuple[int, int]:
+    """One buffer per (device, batch), zeroed when it is made: the ticket words at its start depend on `batch`
+    alone and every launch leaves them zero, so the calls can vouch for it (SUBSPEC_EXPAND_SCRATCH_CLEAN) and
+    the library puts no clearing operation in front of the kernel.  Like the verify workspaces, a buffer serves
+    one stream at a time."""
     need = C.c_size_t(0)
     _lib.check(_lib.lib().subspec_expand_scratch_bytes(batch, leaves, k, C.byref(need)), "subspec_expand_scratch_bytes")
-    key = (device.index or 0, 0)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), int(batch))
     buf = _scratch.get(key)
     if buf is None or buf.numel() < need.value + 256:
-        buf = _scratch[key] = torch.empty(need.value + 256, dtype=torch.uint8, device=device)
+        buf = _scratch[key] = torch.zeros(need.value + 256, dtype=torch.uint8, device=device)
     ptr = (buf.data_ptr() + 255) // 256 * 256
     return ptr, need.value
 
@@ -157,6 +161,7 @@ def _expand(scores: torch.Tensor, parent_probs: Optional[torch.Tensor], k: int, 
             a.prefix_len = tree.prefix_len.data_ptr()
             a.draft_position_ids = tree.draft_position_ids.data_ptr()
     a.scratch, a.scratch_bytes = _scratch_for(dev, B, L, k)
+    a.flags = _lib.EXPAND_SCRATCH_CLEAN
     stream = torch.cuda.current_stream(dev).cuda_stream
     _lib.check(_lib.lib().subspec_expand_step(C.byref(a), C.c_void_p(stream)), "subspec_expand_step")
     return out_tokens, out_probs, out_parents
