@@ -168,7 +168,8 @@ __device__ __forceinline__ void fold_chunk(const uint32_t* p, int col0, int vali
 }
 
 // FLEX: the column tile's width is a run-time value (a multiple of 16 up to 256) and a row block without rows
-// is skipped -- the build for a single request's tree; without it the width is 256 and both blocks always run.
+// is skipped -- the build for launches of one row tile (up to four requests' trees of 64 nodes); without it the
+// width is 256 and both blocks always run.
 template <bool SOFT, bool FLEX, bool HALF>
 __global__ void __launch_bounds__(kThreads, 1)
     lm_head_stats_kernel(const LmHeadGemmArgs ga, const int ntiles, const int tile_n_arg,
@@ -351,15 +352,15 @@ cudaError_t launch_lm_head_stats(const LmHeadGemmArgs& ga, cudaStream_t stream, 
   if ((reinterpret_cast<uintptr_t>(ga.hidden) & 15u) || (reinterpret_cast<uintptr_t>(ga.weight) & 15u) ||
       (ga.hidden_stride % 8) || (ga.weight_stride % 8) || ga.hidden_stride < ga.dim || ga.weight_stride < ga.dim)
     return cudaErrorInvalidValue;
-  // Width of a column tile.  256 keeps the MMAs at their best.  With no more than one 128-row block (a single
-  // request's tree) the call is a stream of the weights through HBM, the MMAs idle, and the number of rounds of
+  // Width of a column tile.  256 keeps the MMAs at their best.  With no more than one row tile (up to four
+  // requests' trees) the call is a stream of the weights through HBM, the MMAs idle, and the number of rounds of
   // tiles the CTAs go through decides (594 tiles of 256 on 148 SMs are five rounds, 732 of 208 five shorter
   // ones): there, take the width with the smallest rounds x (width + fixed cost).  (With more rows narrower
   // tiles lost: 512 rows 447 us at 240 against 393 us at 256, though both need nine rounds.)
   const int64_t mtiles = (ga.rows + kTileRows - 1) / kTileRows;
   int tile_n = kLmTileN;
   double best = 1e30;
-  for (int wdt = kLmTileN; wdt >= (ga.rows <= kBlockRows ? kLmMinTileN : kLmTileN); wdt -= 16) {
+  for (int wdt = kLmTileN; wdt >= (ga.rows <= kTileRows ? kLmMinTileN : kLmTileN); wdt -= 16) {
     const int64_t tiles = mtiles * ((ga.vocab + wdt - 1) / wdt);
     const int64_t rounds = (tiles + kNumSMs - 1) / kNumSMs;
     const double cost = (double)rounds * (wdt + 12);
@@ -377,7 +378,7 @@ cudaError_t launch_lm_head_stats(const LmHeadGemmArgs& ga, cudaStream_t stream, 
   const int64_t total = mtiles * ntiles;
   if (total > INT_MAX) return cudaErrorInvalidValue;  // the kernel counts tiles in 32 bits
   const int grid = (int)(total < kNumSMs ? total : kNumSMs);
-  const bool flex = ga.rows <= kBlockRows;
+  const bool flex = ga.rows <= kTileRows;
   using Kernel = void (*)(const LmHeadGemmArgs, const int, const int, const CUtensorMap, const CUtensorMap);
   static const Kernel kernels[8] = {
       lm_head_stats_kernel<false, false, false>, lm_head_stats_kernel<false, false, true>,
