@@ -87,3 +87,29 @@ def test_attention_wrapper_rejects_bad_arguments():
         tree_attention_static(qh, kc, kc[:, :, :32], kv_len=kv_len, mask=mask)
     with pytest.raises(ValueError, match="mask"):
         tree_attention_static(qh, kc, kc, kv_len=kv_len, mask=mask.long())
+
+
+def test_fused_lm_head_arguments_are_checked_before_any_launch():
+    """`verify_tree_batched(hidden_states=, lm_head_weight=)`: the argument combinations it refuses are refused
+    on the host, before a device is touched."""
+    import torch
+
+    from subspec_b200.tree import Tree
+    from subspec_b200.verify import verify_tree_batched
+
+    tree = Tree.from_arrays([1, 2, 3], [-1, 0, 0])
+    hidden = torch.zeros(1, 3, 64, dtype=torch.bfloat16)
+    weight = torch.zeros(100, 64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="either logits"):
+        verify_tree_batched(trees=[tree], root_inds=[0], logits=torch.zeros(1, 3, 100), hidden_states=hidden,
+                            lm_head_weight=weight, eos_token_id=None)
+    with pytest.raises(ValueError, match="either logits"):
+        verify_tree_batched(trees=[tree], root_inds=[0], hidden_states=hidden, eos_token_id=None)
+    with pytest.raises(ValueError, match="greedy targets only"):
+        verify_tree_batched(trees=[tree], root_inds=[0], hidden_states=hidden, lm_head_weight=weight,
+                            eos_token_id=None, do_sample=True)
+    with pytest.raises(ValueError, match="hidden_states must be"):
+        verify_tree_batched(trees=[tree], root_inds=[0], hidden_states=hidden[0], lm_head_weight=weight,
+                            eos_token_id=None)
+    with pytest.raises(ValueError, match="logits must be"):
+        verify_tree_batched(trees=[tree], root_inds=[0], eos_token_id=None)
