@@ -773,8 +773,10 @@ def main():
                 ev[0].record()
             if args.two_pass:
                 sb.verify(logits, verify_method="exact")
-            if events is not None:
-                ev[1].record()
+                if events is not None:
+                    ev[1].record()
+            elif events is not None:
+                ev[1] = ev[0]  # no separate greedy launch: nothing to bracket, one command fewer in the stream
             # greedy and lossy results of the step; by default from one launch = one pass over the logits
             sb.verify(logits, verify_method="lossy" if args.two_pass else "exact+lossy", verify_kwargs=LOSSY_KW)
             if events is not None:
