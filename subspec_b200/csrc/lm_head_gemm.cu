@@ -2,19 +2,20 @@
 //
 // The reference's target forward ends in `logits = lm_head(hidden)` and the verifier then reads those logits
 // once per row (generators/classic_sd.py:100-116, verify/exact_tree_verify.py:23-28, lossy_tree_verify.py:84-100):
-// a [rows, vocab] bf16 tensor written and read again, 2 x 1.25 GB per wave of 64 trees of 64 nodes.  Here the
-// accumulator tile of the GEMM is folded in place: every element is rounded to bf16 (what the reference's
-// lm_head returns) and goes into the row's maximum / first arg-max and, for the lossy gates, into
-// sum 2^y and sum y 2^y; what leaves the kernel is one 20-byte record per (row, 256-column tile).  fp16 models
-// (the reference's usual dtype) take the same path with fp16 operands and fp16 rounding.
+// a [rows, vocab] 16-bit tensor written and read again, 2 x 1.25 GB per wave of 64 trees of 64 nodes.  Here every
+// element of the GEMM's accumulator tile is rounded to the model's dtype (bf16 or fp16: what the reference's
+// lm_head returns) and goes into the row's maximum / first arg-max and, for the lossy gates, into sum 2^y and
+// sum y 2^y; what leaves the kernel is one 20-byte record per (row, column tile).
 //
 // One persistent CTA per SM walks (row tile, column tile) pairs, the row tiles of one column tile next to each
 // other so that CTAs running at the same time share weight tiles in L2.  A tile is 256 rows x 256 columns: two
 // 128-row blocks (the MMA's M) share every weight tile, which halves the shared-memory traffic per flop
 // against one block.  Roles: warp 8 issues the tensor copies (TMA, 128-byte swizzle) into a three-stage ring of
 // (256 x 64 hidden, 256 x 64 weight) pairs; warp 9 issues tcgen05.mma (both operands in shared memory, K-major,
-// accumulators in tensor memory: 2 x 256 columns); warps 0-7 are the epilogue, thread = row = tensor-memory
-// lane.  All waits are bounded.
+// accumulators in tensor memory: 2 x 256 columns, all there is); warps 0-7 are the epilogue, thread = row =
+// tensor-memory lane: they first move the tile's row out of tensor memory, rounded and packed two to a
+// register, hand the accumulators back, and do the arithmetic while the next tile's MMAs run.  All waits are
+// bounded.
 #include <limits.h>
 
 #include "lm_head.cuh"
@@ -261,8 +262,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk)
               if (blk < nblk)
-              mma_bf16_ss(tmem + (uint32_t)(blk * kLmTileN), kmajor_desc(a_addr + blk * (kABytes / 2) + kk * 32), bdesc,
-                          idesc, (kb | kk) != 0 ? 1u : 0u);
+                mma_bf16_ss(tmem + (uint32_t)(blk * kLmTileN), kmajor_desc(a_addr + blk * (kABytes / 2) + kk * 32),
+                            bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
           }
           tc_commit(&empty[pos.s]);  // the stage is free once these MMAs have read it
           pos.next();
@@ -289,8 +290,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       float c = -INFINITY, vmax = -INFINITY;
       int amax = INT_MAX;
       uint64_t s2 = 0, t2 = 0;
-      // The whole row of the tile comes out of tensor memory first, as bf16 pairs (128 registers), and the
-      // accumulators go back to the MMA warp: the arithmetic below runs under the next tile's MMAs.
+      // The whole row of the tile comes out of tensor memory first, as pairs of 16-bit floats (128 registers),
+      // and the accumulators go back to the MMA warp: the arithmetic below runs under the next tile's MMAs.
       uint32_t p[kLmTileN / 2];
       {
         uint32_t ra[16], rb[16];
@@ -340,8 +341,8 @@ bool encode_rows_map(CUtensorMap* m, const void* base, int64_t stride_elems, int
   const cuuint64_t strides[1] = {(cuuint64_t)stride_elems * 2};
   const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  return tensor_map_encoder()(m, half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  return tensor_map_encoder()(m, half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
