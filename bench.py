@@ -767,10 +767,14 @@ def main():
     torch.cuda.synchronize()
 
     def one_step(events=None):
+        last = None  # the event behind the previous wave's compaction is the one in front of this wave's verify
         for sb, logits, _, _ in waves:
             if events is not None:
                 ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-                ev[0].record()
+                if last is None:
+                    ev[0].record()
+                else:
+                    ev[0] = last
             if args.two_pass:
                 sb.verify(logits, verify_method="exact")
                 if events is not None:
@@ -785,6 +789,7 @@ def main():
             if events is not None:
                 ev[3].record()
                 events.append(ev)
+                last = ev[3]
 
     def barrier():
         if world > 1:
