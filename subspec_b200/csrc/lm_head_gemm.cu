@@ -332,7 +332,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == kMmaWarp) tmem_dealloc(tmem, kCols);
+  if (warp == kMmaWarp) {
+    __syncwarp();  // lane 0 comes out of the issue loop, the others straight from the top: one warp again
+    tmem_dealloc(tmem, kCols);
+  }
   if (threadIdx.x == 0 && s_abort) flag(ga.dev_status, SUBSPEC_DEV_TIMEOUT);
 }
 
